@@ -1,0 +1,185 @@
+/*
+ * torchair-b200 C ABI: the device side of the W8A8 expert-parallel MoE path on NVIDIA B200 (sm_100a).
+ *
+ * The shared library libtorchair_b200.so exports exactly the functions declared here.  They are what a
+ * foreign-function binding of the reference's operators for this path would call in place of the closed
+ * vendor kernels.  Each declaration cites the reference interface it stands in for (paths are inside the
+ * Ascend/torchair project; "converter" = python/torchair/_ge_concrete_graph/ge_converter/custom).
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer owned by the caller unless the comment says "host".
+ *   - Nothing is allocated, freed or synchronised inside a call; all work is enqueued on `stream`
+ *     (a cudaStream_t), so calls are legal during CUDA-graph capture.  Scratch memory is passed in as
+ *     `workspace`; the matching *_workspace_bytes function says how much is needed.
+ *   - Return value: 0 on success, a negative tab_status otherwise.  tab_last_error() returns a message for
+ *     the calling thread's most recent failure.  No call aborts or throws.
+ *   - dtype arguments use the c10::ScalarType integers the reference's converters use
+ *     (python/torchair/ge/_ge_graph.py:215-270): 1 int8, 3 int32, 5 float16, 6 float32, 15 bfloat16.
+ *   - Row-major, contiguous tensors; rows of 8-bit data must be 16-byte multiples.
+ */
+#ifndef TAB_API_H_
+#define TAB_API_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* tab_stream_t; /* cudaStream_t */
+
+#if defined(__GNUC__)
+#define TAB_API __attribute__((visibility("default")))
+#else
+#define TAB_API
+#endif
+
+enum tab_status {
+  TAB_OK = 0,
+  TAB_ERR_BAD_ARG = -1,     /* null pointer, negative size, inconsistent shapes */
+  TAB_ERR_UNSUPPORTED = -2, /* dtype / mode outside the path */
+  TAB_ERR_ALIGNMENT = -3,   /* pointer or row pitch not 16-byte aligned */
+  TAB_ERR_WORKSPACE = -4,   /* workspace too small */
+  TAB_ERR_CUDA = -5,        /* a CUDA runtime/driver call failed; message holds its text */
+  TAB_ERR_TIMEOUT = -6      /* a bounded device-side wait gave up (read back via tab_gmm_status) */
+};
+
+enum tab_dtype { TAB_I8 = 1, TAB_I32 = 3, TAB_F16 = 5, TAB_F32 = 6, TAB_BF16 = 15 };
+
+/* Library version (major*10000 + minor*100 + patch).  Nearest reference analogue: the pybind module
+ * `_torchair` (torchair/core/npu_wrapper.cpp:28-84). */
+TAB_API int tab_version(void);
+
+/* Message of the calling thread's last failing call.  Stands in for tng::Status -> RuntimeError
+ * (torchair/core/torchair.cpp:98-120). */
+TAB_API const char* tab_last_error(void);
+
+/* ---------------------------------------------------------------------------------------------------
+ * npu_dynamic_quant  (converter npu_dynamic_quant.py:8-40 -> DynamicQuant, nn_quantize.h:28-54)
+ * x [rows, cols] of x_dtype (5, 6 or 15); smooth [cols] of x_dtype or NULL.
+ * y int8 [rows, cols]; scale fp32 [rows] = amax(|x*smooth|)/127; y = clamp(rint(v/scale), +-127).
+ * ------------------------------------------------------------------------------------------------- */
+TAB_API int tab_dynamic_quant(const void* x, int x_dtype, const void* smooth, int64_t rows, int64_t cols,
+                      int8_t* y, float* scale, tab_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------
+ * npu_swiglu  (converter npu_swiglu.py:8-14 -> SwiGlu), last-dimension split only.
+ * x [rows, cols] (cols even) of dtype 5, 6 or 15; y [rows, cols/2] = silu(x[:, :cols/2]) * x[:, cols/2:].
+ * ------------------------------------------------------------------------------------------------- */
+TAB_API int tab_swiglu(const void* x, int dtype, int64_t rows, int64_t cols, void* y, tab_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------
+ * npu_dequant_swiglu_quant, dynamic mode (converter npu_dequant_swiglu_quant.py:5-64 ->
+ * DequantSwigluQuant, experiment_ops.h:3764-3811).
+ * x int32 [rows, cols]; weight_scale fp32 [ws_groups, cols] (ws_groups == 1: one row for all) or NULL;
+ * activation_scale fp32 [rows] or NULL; group_index int64 [num_groups] per-group row COUNTS or NULL
+ * (required when ws_groups > 1; rows past their sum give y = 0, scale = 0).
+ * y int8 [rows, cols/2]; scale fp32 [rows].
+ * ------------------------------------------------------------------------------------------------- */
+TAB_API int tab_dequant_swiglu_quant(const int32_t* x, const float* weight_scale, int64_t ws_groups,
+                             const float* activation_scale, const int64_t* group_index, int64_t num_groups,
+                             int activate_left, int64_t rows, int64_t cols, int8_t* y, float* scale,
+                             tab_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------
+ * npu_moe_init_routing  (converter moe_init_routing.py:10-21 -> MoeInitRouting, experiment_ops.h:2111-2134)
+ * x [T, H] of x_dtype; row_idx, expert_idx int32 [T, K]; expert ids must lie in [0, expert_bound).
+ * expanded_x [min(T, active_num)*K, H]; expanded_row_idx, expanded_expert_idx int32 [T*K].
+ * Stable counting sort of the T*K pairs by expert id (ties by flattened index), row gather.
+ * ------------------------------------------------------------------------------------------------- */
+TAB_API int tab_moe_init_routing_workspace_bytes(int64_t T, int64_t K, int64_t expert_bound, size_t* bytes);
+TAB_API int tab_moe_init_routing(const void* x, int x_dtype, const int32_t* row_idx, const int32_t* expert_idx,
+                         int64_t T, int64_t K, int64_t H, int64_t active_num, int64_t expert_bound,
+                         void* expanded_x, int32_t* expanded_row_idx, int32_t* expanded_expert_idx,
+                         void* workspace, size_t workspace_bytes, tab_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------
+ * npu_moe_distribute_dispatch, sender side (converter moe_distribute_dispatch.py:4-45 ->
+ * MoeDistributeDispatch).  Sorts this rank's T*K copies by global expert id (stable), quantises every
+ * token once (quant_mode 2: int8 rows + fp32 scales; quant_mode 0: rows keep x_dtype, scales = 0) and
+ * writes the copies in sorted order:
+ *   send_rows [T*K, H], send_scales fp32 [T*K], expand_idx int32 [T*K] (position of pair t*K+k),
+ *   expert_counts int32 [num_experts] (copies per global expert).
+ * With one rank this is the whole dispatch: send_rows is expand_x and expert_counts the token counts.
+ * ------------------------------------------------------------------------------------------------- */
+TAB_API int tab_moe_dispatch_pack_workspace_bytes(int64_t T, int64_t K, int64_t num_experts, size_t* bytes);
+TAB_API int tab_moe_dispatch_pack(const void* x, int x_dtype, const int32_t* expert_ids, int64_t T, int64_t K,
+                          int64_t H, int64_t num_experts, int quant_mode, void* send_rows,
+                          float* send_scales, int32_t* expand_idx, int32_t* expert_counts,
+                          void* workspace, size_t workspace_bytes, tab_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------
+ * npu_moe_distribute_dispatch, receiver side, and npu_moe_distribute_combine, expert side
+ * (converters moe_distribute_dispatch.py:4-45, moe_distribute_combine.py:4-60).
+ * recv_counts int32 [R, E_l]: rows this rank received from source rank s for its local expert e.  The
+ * wire buffer holds them source-major: rank s's block starts at row s*slot_rows (slot_rows > 0: fixed
+ * slots) or at the running total (slot_rows == 0: packed).  The expert-side buffer orders rows by
+ * (local expert, source rank).
+ *   tab_moe_exchange_plan   writes  plan int32 [2*R*E_l + 1] (row offsets on both sides),
+ *                           expert_token_nums int64 [E_l] (counts if nums_type == 1 else cumsum),
+ *                           ep_recv_count int32 [E_l*R] (count of expert e from rank s at e*R+s).
+ *   tab_moe_exchange_rows   direction 0: wire -> expert order (rows + optional fp32 scales);
+ *                           direction 1: expert order -> wire.  dst has dst_rows rows; rows of dst not
+ *                           covered by the plan are zero-filled when zero_fill != 0.
+ * ------------------------------------------------------------------------------------------------- */
+TAB_API int tab_moe_exchange_plan(const int32_t* recv_counts, int64_t R, int64_t E_l, int64_t slot_rows,
+                          int nums_type, int32_t* plan, int64_t* expert_token_nums,
+                          int32_t* ep_recv_count, tab_stream_t stream);
+TAB_API int tab_moe_exchange_rows(const void* src, const float* src_scales, const int32_t* plan, int64_t R,
+                          int64_t E_l, int64_t slot_rows, int direction, int64_t row_bytes,
+                          int64_t dst_rows, int zero_fill, void* dst, float* dst_scales,
+                          tab_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------
+ * npu_moe_distribute_combine, receiving side (converter moe_distribute_combine.py:4-60 ->
+ * MoeDistributeCombine): out[t] = sum_k expert_scales[t,k] * rows[expand_idx[t*K+k]] (+ shared[t]),
+ * fp32 accumulation in ascending k, one rounding to dtype (5 or 15).
+ * rows [*, H]; expand_idx int32 [T*K]; expert_scales fp32 [T, K]; shared [T, H] or NULL; out [T, H].
+ * ------------------------------------------------------------------------------------------------- */
+TAB_API int tab_moe_combine(const void* rows, int dtype, const int32_t* expand_idx, const float* expert_scales,
+                    const void* shared, int64_t T, int64_t K, int64_t H, void* out, tab_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------
+ * npu_grouped_matmul, W8A8 (converter grouped_matmul.py:210-365 -> GroupedMatmul,
+ * experiment_ops.h:3616-3652).
+ *
+ * tab_prepack_weight_i8: one-off relayout of weight int8 [E, Kd, N] (the operator's layout, N contiguous)
+ *   into packed int8 [E, N, Kd] (Kd contiguous), the K-major form the tcgen05 shared-memory descriptors
+ *   read.  B200 counterpart of the reference's host-side weight format cast
+ *   (torchair/npu_utils/npu_format_cast_via_cpu.cpp).
+ *
+ * tab_grouped_matmul_w8a8: x int8 [M, Kd]; packed weight; group_list int64 [E] (group_list_type 0 =
+ *   cumulative row ends, 1 = row counts); expert e owns a contiguous row range.
+ *   out_dtype 3: y int32 [M, N] raw accumulators (scale, per_token_scale ignored);
+ *   out_dtype 15 / 5: y = (float(acc) * per_token_scale[m]) * scale[e, n], scale fp32 [E, N],
+ *   per_token_scale fp32 [M] (either may be NULL = 1).  Rows outside every group are left untouched.
+ *   Requires Kd % 16 == 0.
+ *
+ * tab_grouped_matmul_swiglu_quant: gate_up GEMM with the DequantSwigluQuant epilogue fused
+ *   (grouped_matmul.py:210-365 followed by npu_dequant_swiglu_quant.py:5-64; the reference's own fused
+ *   form is converter grouped_matmul_swiglu_quant_v2.py:86-166).  packed weight [E, 2*I, Kd];
+ *   weight_scale fp32 [E, 2*I]; x_scale fp32 [M]; yq int8 [M, I]; y_scale fp32 [M]; rows outside every
+ *   group give yq = 0, y_scale = 0.  Workspace holds the fp32 SwiGLU values between the two phases.
+ *
+ * tab_gmm_status: host-side; copies the device status word of the last GEMM launches on this device
+ *   (0 = fine, otherwise the code of the bounded wait that gave up) after synchronising `stream`.
+ * ------------------------------------------------------------------------------------------------- */
+TAB_API int tab_prepack_weight_i8(const int8_t* weight, int64_t E, int64_t Kd, int64_t N, int8_t* packed,
+                          tab_stream_t stream);
+TAB_API int tab_grouped_matmul_w8a8(const int8_t* x, const int8_t* packed_weight, const float* scale,
+                            const float* per_token_scale, const int64_t* group_list, int group_list_type,
+                            int64_t M, int64_t Kd, int64_t N, int64_t E, int out_dtype, void* y,
+                            tab_stream_t stream);
+TAB_API int tab_grouped_matmul_swiglu_quant_workspace_bytes(int64_t M, int64_t I, size_t* bytes);
+TAB_API int tab_grouped_matmul_swiglu_quant(const int8_t* x, const int8_t* packed_weight, const float* weight_scale,
+                                    const float* x_scale, const int64_t* group_list, int group_list_type,
+                                    int64_t M, int64_t Kd, int64_t I, int64_t E, int activate_left,
+                                    int8_t* yq, float* y_scale, void* workspace, size_t workspace_bytes,
+                                    tab_stream_t stream);
+TAB_API int tab_gmm_status(int* status_host, tab_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TAB_API_H_ */

@@ -1,0 +1,450 @@
+"""CPU oracle for the W8A8 expert-parallel MoE path (TEST INFRASTRUCTURE, not product code).
+
+Only tests, the smoke check and the benchmark's CPU-baseline legs may import this module; the
+shipped ops never call it and have no CPU fallback.
+
+PARITY UNPINNED: the reference (Ascend/torchair) contains no arithmetic for these ops -- each is a
+converter that lowers ``torch.ops.npu.<op>`` to one graph-IR node whose kernel is a closed vendor
+binary, and none of the reference's tests pins a numerical result for them.  What the reference does
+pin (op names, argument order, defaults, dtypes, output arity, a few shape rules) is checked by the
+conformance tests.  The value semantics below follow the IR prototypes' doc comments and the
+benchmark description (scale = amax/127, round-half-even, clamp +-127, per-channel weight scales,
+per-token activation scales), evaluated in eager torch on CPU.  Every function cites the reference
+file:line whose contract it restates; choices the reference leaves open are marked "decision".
+
+Reference anchors (paths inside the reference project):
+  python/torchair/_ge_concrete_graph/ge_converter/custom/moe_init_routing.py:10-21
+  python/torchair/_ge_concrete_graph/ge_converter/custom/npu_dynamic_quant.py:8-40
+  python/torchair/_ge_concrete_graph/ge_converter/custom/npu_swiglu.py:8-14
+  python/torchair/_ge_concrete_graph/ge_converter/custom/npu_dequant_swiglu_quant.py:5-64
+  python/torchair/_ge_concrete_graph/ge_converter/custom/grouped_matmul.py:210-365
+  python/torchair/_ge_concrete_graph/ge_converter/custom/moe_distribute_dispatch.py:4-45
+  python/torchair/_ge_concrete_graph/ge_converter/custom/moe_distribute_combine.py:4-60
+  third_party/ascend/include/ops/op_proto/inc/experiment_ops.h:2111-2134, 3616-3652, 3764-3811
+  third_party/ascend/include/ops/op_proto/inc/nn_quantize.h:28-54
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+import torch.nn.functional as F
+
+# c10 ScalarType integers the converters compare dtype arguments against
+# (python/torchair/ge/_ge_graph.py:215-270).
+SCALAR_TYPE = {1: torch.int8, 3: torch.int32, 5: torch.float16, 6: torch.float32, 15: torch.bfloat16}
+
+
+# --------------------------------------------------------------------------------------------------
+# gating (not an op of the path; needed to make inputs)
+# --------------------------------------------------------------------------------------------------
+def gating_topk(logits: torch.Tensor, k: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """softmax(logits fp32) -> top-k by stable descending sort -> weights renormalised to sum 1.
+
+    Decision: ties keep the lower expert id first.  Returns (expert_ids int32 [T,k], weights fp32 [T,k]).
+    """
+    p = torch.softmax(logits.float(), dim=-1)
+    order = torch.sort(p, dim=-1, descending=True, stable=True)
+    ids = order.indices[:, :k].to(torch.int32)
+    w = order.values[:, :k]
+    w = w / w.sum(dim=-1, keepdim=True)
+    return ids.contiguous(), w.contiguous()
+
+
+# --------------------------------------------------------------------------------------------------
+# npu_moe_init_routing
+# --------------------------------------------------------------------------------------------------
+def moe_init_routing(x: torch.Tensor, row_idx: torch.Tensor, expert_idx: torch.Tensor, active_num: int):
+    """MoeInitRouting (experiment_ops.h:2111-2134; converter moe_init_routing.py:10-21).
+
+    Stable sort of the T*K (token, k) pairs by expert id.  Decision: ties are ordered by the flattened
+    index t*K+k.  With ``row_idx_sorted[i]`` the row_idx value of the i-th sorted pair:
+      expanded_expert_idx[i]               = sorted expert id
+      expanded_row_idx[row_idx_sorted[i]]  = i                      (inverse permutation)
+      expanded_x[i]                        = x[row_idx_sorted[i] mod T]   for i < min(T, active_num)*K
+    """
+    T, K = expert_idx.shape
+    flat_e = expert_idx.reshape(-1).to(torch.int64)
+    order = torch.sort(flat_e, stable=True)
+    sorted_e = order.values.to(torch.int32)
+    row_sorted = row_idx.reshape(-1).to(torch.int64)[order.indices]
+    expanded_row_idx = torch.empty(T * K, dtype=torch.int32)
+    expanded_row_idx[row_sorted] = torch.arange(T * K, dtype=torch.int32)
+    n_rows = min(T, active_num) * K
+    expanded_x = x[(row_sorted % T)[:n_rows]].contiguous()
+    return expanded_x, expanded_row_idx, sorted_e
+
+
+# --------------------------------------------------------------------------------------------------
+# npu_dynamic_quant
+# --------------------------------------------------------------------------------------------------
+def quantize_rows_f32(v: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-row symmetric int8 quantiser on fp32 values (DynamicQuant, nn_quantize.h:28-54).
+
+    scale = amax(|v|)/127 (fp32 IEEE division); q = clamp(rint(v/scale), -127, 127) with IEEE division
+    (not multiply-by-reciprocal) and round-half-even.  Decision: an all-zero row gives scale 0, q 0.
+    """
+    v = v.float()
+    amax = v.abs().amax(dim=-1)
+    scale = amax / 127.0
+    safe = torch.where(scale > 0, scale, torch.ones_like(scale))
+    q = torch.round(v / safe.unsqueeze(-1))
+    q = torch.where(scale.unsqueeze(-1) > 0, q, torch.zeros_like(q))
+    q = q.clamp_(-127, 127).to(torch.int8)
+    return q, scale
+
+
+def dynamic_quant(x: torch.Tensor, smooth_scales: Optional[torch.Tensor] = None):
+    """npu_dynamic_quant(input, *, smooth_scales=None, ...) -> (int8, fp32 scale of shape input.shape[:-1]).
+
+    Converter npu_dynamic_quant.py:8-40.  smooth_scales ([H], same dtype as input) multiplies the input in
+    fp32 before the row quantiser (decision: product taken in fp32, not rounded to the input dtype).
+    """
+    v = x.float()
+    if smooth_scales is not None:
+        v = v * smooth_scales.float()
+    q, s = quantize_rows_f32(v.reshape(-1, x.shape[-1]))
+    return q.reshape(x.shape), s.reshape(x.shape[:-1])
+
+
+# --------------------------------------------------------------------------------------------------
+# npu_swiglu
+# --------------------------------------------------------------------------------------------------
+def swiglu(x: torch.Tensor, dim: int = -1) -> torch.Tensor:
+    """SwiGlu (converter npu_swiglu.py:8-14): a, b = halves of x along dim; y = silu(a)*b in fp32, cast back."""
+    a, b = torch.chunk(x.float(), 2, dim=dim)
+    return (F.silu(a) * b).to(x.dtype)
+
+
+# --------------------------------------------------------------------------------------------------
+# group bookkeeping
+# --------------------------------------------------------------------------------------------------
+def group_bounds(group_list: torch.Tensor, group_list_type: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(start, count) per group from a cumsum (type 0) or counts (type 1) list (grouped_matmul.py:306-361)."""
+    g = group_list.to(torch.int64)
+    if group_list_type == 0:
+        ends = g
+        starts = torch.cat([torch.zeros(1, dtype=torch.int64), g[:-1]])
+        return starts, ends - starts
+    if group_list_type == 1:
+        ends = torch.cumsum(g, 0)
+        return ends - g, g
+    raise ValueError("group_list_type must be 0 (cumsum) or 1 (counts)")
+
+
+def int8_matmul(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """Exact int8 x int8 -> int32 product ([m,k] @ [k,n])."""
+    if a.shape[0] == 0:
+        return torch.zeros(0, b.shape[1], dtype=torch.int32)
+    try:
+        return torch._int_mm(a.contiguous(), b.contiguous())
+    except RuntimeError:
+        return a.to(torch.int32) @ b.to(torch.int32)
+
+
+# --------------------------------------------------------------------------------------------------
+# npu_grouped_matmul, W8A8 mode
+# --------------------------------------------------------------------------------------------------
+def grouped_matmul_w8a8(x: torch.Tensor, weight: torch.Tensor, scale: Optional[torch.Tensor],
+                        per_token_scale: Optional[torch.Tensor], group_list: torch.Tensor,
+                        group_list_type: int = 0, output_dtype: int = 15,
+                        bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """GroupedMatmul, int8 x int8 (experiment_ops.h:3616-3652; converter grouped_matmul.py:210-361).
+
+    Expert e owns rows [s_e, s_e+c_e).  acc = x[rows] @ weight[e] in exact int32 (+ int32 bias[e]).
+    output_dtype 3 -> raw int32 accumulators; 15/5 -> bf16/fp16 of
+    (float(acc) * per_token_scale[m]) * scale[e, n]   (decision: this order, no fused multiply-add).
+    Rows not covered by any group are zero.
+    """
+    M = x.shape[0]
+    E, Kd, N = weight.shape
+    starts, counts = group_bounds(group_list, group_list_type)
+    out_dt = SCALAR_TYPE[output_dtype]
+    y = torch.zeros(M, N, dtype=out_dt)
+    for e in range(E):
+        s, c = int(starts[e]), int(counts[e])
+        if c <= 0:
+            continue
+        acc = int8_matmul(x[s:s + c], weight[e])
+        if bias is not None:
+            acc = acc + bias[e].to(torch.int32)
+        if out_dt == torch.int32:
+            y[s:s + c] = acc
+        else:
+            v = acc.float()
+            if per_token_scale is not None:
+                v = v * per_token_scale[s:s + c].float().unsqueeze(-1)
+            if scale is not None:
+                v = v * scale[e].float().unsqueeze(0)
+            y[s:s + c] = v.to(out_dt)
+    return y
+
+
+# --------------------------------------------------------------------------------------------------
+# npu_dequant_swiglu_quant
+# --------------------------------------------------------------------------------------------------
+def dequant_swiglu_f32(x: torch.Tensor, weight_scale: Optional[torch.Tensor], activation_scale: Optional[torch.Tensor],
+                       group_index: Optional[torch.Tensor], activate_left: bool) -> torch.Tensor:
+    """fp32 value that the quantiser of DequantSwigluQuant sees (experiment_ops.h:3764-3811).
+
+    v = (float(x) * activation_scale[m]) * weight_scale[g, n]; halves (left, right) of the last dim;
+    activate_left True -> silu(left)*right, False -> silu(right)*left (experiment_ops.h:3782-3784).
+    Decision: group_index holds per-group row COUNTS; rows beyond their sum produce zeros.
+    """
+    M = x.shape[0]
+    v = x.float()
+    if activation_scale is not None:
+        v = v * activation_scale.float().reshape(M, 1)
+    if weight_scale is not None:
+        ws = weight_scale.float()
+        if ws.dim() == 1 or ws.shape[0] == 1 and group_index is None:
+            v = v * ws.reshape(1, -1)
+        else:
+            _, counts = group_bounds(group_index, 1)
+            gid = torch.repeat_interleave(torch.arange(ws.shape[0]), counts.clamp(min=0))
+            valid = gid.shape[0]
+            vv = torch.zeros_like(v)
+            vv[:valid] = v[:valid] * ws[gid]
+            v = vv
+    left, right = torch.chunk(v, 2, dim=-1)
+    h = F.silu(left) * right if activate_left else F.silu(right) * left
+    if group_index is not None:
+        valid = int(group_bounds(group_index, 1)[1].clamp(min=0).sum())
+        h[valid:] = 0
+    return h
+
+
+def dequant_swiglu_quant(x: torch.Tensor, weight_scale=None, activation_scale=None, group_index=None,
+                         activate_left: bool = False, quant_mode: int = 0):
+    """npu_dequant_swiglu_quant with quant_mode=1 (dynamic) -> (int8 [M, N/2], fp32 [M]).
+
+    Converter npu_dequant_swiglu_quant.py:5-64; shape rule
+    python/torchair/_contrib/custom_torch_ops/auto_register_custom_torch_ops.py:121-156.
+    SwiGLU runs on the un-rounded fp32 dequantised value, then the row quantiser of dynamic_quant.
+    """
+    if quant_mode != 1:
+        raise NotImplementedError("oracle covers the dynamic quant mode only")
+    h = dequant_swiglu_f32(x, weight_scale, activation_scale, group_index, activate_left)
+    return quantize_rows_f32(h)
+
+
+# --------------------------------------------------------------------------------------------------
+# combine, single rank (= finalize routing)
+# --------------------------------------------------------------------------------------------------
+def weighted_gather_sum(y: torch.Tensor, pos: torch.Tensor, weights: torch.Tensor,
+                        shared: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = sum_k weights[t,k] * y[pos[t,k]] in fp32, ascending k, one rounding to y.dtype.
+
+    Decision: product and sum are separate fp32 operations (no fused multiply-add); the optional shared
+    expert row is added last in fp32.
+    """
+    T, K = weights.shape
+    acc = torch.zeros(T, y.shape[1], dtype=torch.float32)
+    for k in range(K):
+        term = weights[:, k].float().unsqueeze(-1) * y[pos[:, k].long()].float()
+        acc = term if k == 0 else acc + term
+    if shared is not None:
+        acc = acc + shared.float()
+    return acc.to(y.dtype)
+
+
+# --------------------------------------------------------------------------------------------------
+# npu_moe_distribute_dispatch / combine: R ranks simulated in one process
+# --------------------------------------------------------------------------------------------------
+@dataclass
+class DispatchOut:
+    expand_x: torch.Tensor          # [A, H] int8 (quant_mode 2) or input dtype (quant_mode 0)
+    dynamic_scales: torch.Tensor    # [A] fp32
+    expand_idx: torch.Tensor        # [T*K] int32: position of pair t*K+k in this rank's send order
+    expert_token_nums: torch.Tensor  # [E_l] int64 counts (type 1) or cumsum (type 0)
+    ep_recv_count: torch.Tensor     # [E_l*R] int32: rows for local expert e from source rank s at [e*R+s]
+    tp_recv_count: torch.Tensor     # [1] int32, zero
+    expand_scales: torch.Tensor     # [A] fp32, zero
+
+
+def dispatch_rows(T: int, R: int, E: int, K: int) -> int:
+    """Static worst-case row count of expand_x when global_bs == 0 (decision): T*R*min(E/R, K)."""
+    return T * R * min(E // R, K)
+
+
+def moe_distribute_dispatch(xs: Sequence[torch.Tensor], ids: Sequence[torch.Tensor], E: int,
+                            quant_mode: int = 2, expert_token_nums_type: int = 1) -> List[DispatchOut]:
+    """MoeDistributeDispatch for all R ranks at once (converter moe_distribute_dispatch.py:4-45).
+
+    Rank r owns experts [r*E_l, (r+1)*E_l).  Each rank quantises its tokens once (quant_mode 2), sorts
+    its T*K copies by expert id (stable in t*K+k) and sends each copy to the owner of its expert.  The
+    receiver orders rows by (local expert, source rank, send order).  Decisions: the contents of the
+    handshake tensors (see DispatchOut) and zero fill of rows past the received total.
+    """
+    R = len(xs)
+    E_l = E // R
+    T, K = ids[0].shape
+    H = xs[0].shape[1]
+    A = dispatch_rows(T, R, E, K)
+    send_rows, send_scales, send_e, expand_idx = [], [], [], []
+    for r in range(R):
+        if quant_mode == 2:
+            q, s = dynamic_quant(xs[r])
+        elif quant_mode == 0:
+            q, s = xs[r], torch.zeros(T, dtype=torch.float32)
+        else:
+            raise NotImplementedError("quant_mode must be 0 or 2")
+        flat_e = ids[r].reshape(-1).to(torch.int64)
+        order = torch.sort(flat_e, stable=True)
+        tok = order.indices // K
+        send_rows.append(q[tok])
+        send_scales.append(s[tok])
+        send_e.append(order.values)
+        inv = torch.empty(T * K, dtype=torch.int32)
+        inv[order.indices] = torch.arange(T * K, dtype=torch.int32)
+        expand_idx.append(inv)
+    outs = []
+    for d in range(R):
+        rows, scales = [], []
+        cnt = torch.zeros(E_l, R, dtype=torch.int32)
+        for e in range(E_l):
+            for s in range(R):
+                sel = send_e[s] == d * E_l + e
+                rows.append(send_rows[s][sel])
+                scales.append(send_scales[s][sel])
+                cnt[e, s] = int(sel.sum())
+        rows = torch.cat(rows)
+        scales = torch.cat(scales)
+        ex = torch.zeros(A, H, dtype=rows.dtype)
+        ds = torch.zeros(A, dtype=torch.float32)
+        ex[:rows.shape[0]] = rows
+        ds[:rows.shape[0]] = scales
+        per_e = cnt.sum(dim=1).to(torch.int64)
+        nums = per_e if expert_token_nums_type == 1 else torch.cumsum(per_e, 0)
+        outs.append(DispatchOut(ex, ds, expand_idx[d], nums, cnt.reshape(-1).contiguous(),
+                                torch.zeros(1, dtype=torch.int32), torch.zeros(A, dtype=torch.float32)))
+    return outs
+
+
+def moe_distribute_combine(ys: Sequence[torch.Tensor], ids: Sequence[torch.Tensor],
+                           disp: Sequence[DispatchOut], weights: Sequence[torch.Tensor], E: int,
+                           shared: Optional[Sequence[torch.Tensor]] = None) -> List[torch.Tensor]:
+    """MoeDistributeCombine for all R ranks (converter moe_distribute_combine.py:4-60).
+
+    Every expert-output row returns to the rank that sent it, landing at its position in that rank's send
+    order; then out[t] = sum_k expert_scales[t,k] * row(t,k) as in weighted_gather_sum.
+    """
+    R = len(ys)
+    E_l = E // R
+    T, K = ids[0].shape
+    H = ys[0].shape[1]
+    back = [[None] * R for _ in range(R)]      # back[src][owner] -> list of row blocks in expert order
+    for d in range(R):
+        cnt = disp[d].ep_recv_count.reshape(E_l, R).long()
+        off = 0
+        blocks = [[] for _ in range(R)]
+        for e in range(E_l):
+            for s in range(R):
+                c = int(cnt[e, s])
+                blocks[s].append(ys[d][off:off + c])
+                off += c
+        for s in range(R):
+            back[s][d] = torch.cat(blocks[s]) if blocks[s] else torch.zeros(0, H, dtype=ys[d].dtype)
+    outs = []
+    for s in range(R):
+        recv = torch.cat([back[s][d] for d in range(R)])      # == send order (sorted by global expert id)
+        pos = disp[s].expand_idx.reshape(T, K)
+        outs.append(weighted_gather_sum(recv, pos, weights[s], None if shared is None else shared[s]))
+    return outs
+
+
+# --------------------------------------------------------------------------------------------------
+# whole layer
+# --------------------------------------------------------------------------------------------------
+@dataclass
+class MoeWeights:
+    w1: torch.Tensor   # [E, H, 2I] int8 gate_up
+    s1: torch.Tensor   # [E, 2I] fp32
+    w2: torch.Tensor   # [E, I, H] int8 down
+    s2: torch.Tensor   # [E, H] fp32
+
+
+def expert_ffn(ex: torch.Tensor, xs: torch.Tensor, counts: torch.Tensor, w: MoeWeights,
+               collect: Optional[dict] = None) -> torch.Tensor:
+    """gate_up GEMM (int32) -> dequant+SwiGLU+requant -> down GEMM (bf16) on rows grouped by expert."""
+    h32 = grouped_matmul_w8a8(ex, w.w1, None, None, counts, 1, output_dtype=3)
+    hq, hs = dequant_swiglu_quant(h32, w.s1, xs, counts, activate_left=True, quant_mode=1)
+    y = grouped_matmul_w8a8(hq, w.w2, w.s2, hs, counts, 1, output_dtype=15)
+    if collect is not None:
+        collect.update(h32=h32, hq=hq, hs=hs, y=y)
+    return y
+
+
+def moe_layer(xs: Sequence[torch.Tensor], ids: Sequence[torch.Tensor], weights: Sequence[torch.Tensor],
+              w: MoeWeights, collect: Optional[list] = None) -> List[torch.Tensor]:
+    """The expert-parallel layer over R simulated ranks (R = len(xs); R = 1 is the single-GPU layer).
+
+    dispatch(quant) -> expert FFN on each owner's slice of the weights -> combine.
+    """
+    R = len(xs)
+    E = w.w1.shape[0]
+    E_l = E // R
+    disp = moe_distribute_dispatch(xs, ids, E, quant_mode=2, expert_token_nums_type=1)
+    ys = []
+    for r in range(R):
+        sl = slice(r * E_l, (r + 1) * E_l)
+        wr = MoeWeights(w.w1[sl], w.s1[sl], w.w2[sl], w.s2[sl])
+        c = {} if collect is not None else None
+        ys.append(expert_ffn(disp[r].expand_x, disp[r].dynamic_scales, disp[r].expert_token_nums, wr, c))
+        if collect is not None:
+            c.update(disp=disp[r])
+            collect.append(c)
+    return moe_distribute_combine(ys, ids, disp, weights, E)
+
+
+# --------------------------------------------------------------------------------------------------
+# seeded synthetic inputs of the benchmark configurations
+# --------------------------------------------------------------------------------------------------
+@dataclass
+class MoeConfig:
+    name: str
+    T: int      # tokens per rank
+    H: int
+    E: int
+    K: int
+    I: int
+    zipf_s: float = 0.0
+
+
+CONFIGS = {
+    "cfg0": MoeConfig("cfg0", 64, 1024, 8, 2, 512),
+    "cfg1": MoeConfig("cfg1", 256, 7168, 256, 8, 2048),
+    "cfg2": MoeConfig("cfg2", 128, 7168, 256, 8, 2048),
+    "cfg3": MoeConfig("cfg3", 8192, 7168, 256, 8, 2048, zipf_s=1.2),
+    "cfg4": MoeConfig("cfg4", 4096, 4096, 128, 8, 1536),
+}
+
+
+def make_tokens(cfg: MoeConfig, seed: int = 0, rank: int = 0):
+    """x bf16 ~ N(0,1) [T,H]; router logits fp32 ~ N(0,1) (+ Zipf bias when cfg.zipf_s > 0) -> ids, weights."""
+    g = torch.Generator().manual_seed(seed * 1000 + rank)
+    x = torch.randn(cfg.T, cfg.H, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    logits = torch.randn(cfg.T, cfg.E, generator=g, dtype=torch.float32)
+    if cfg.zipf_s > 0:
+        gp = torch.Generator().manual_seed(seed)
+        perm = torch.randperm(cfg.E, generator=gp)
+        p = (torch.arange(cfg.E, dtype=torch.float64) + 1.0) ** (-cfg.zipf_s)
+        p = p / p.sum()
+        logits = logits + torch.log(p)[perm].float()
+    ids, w = gating_topk(logits, cfg.K)
+    return x, ids, w
+
+
+def make_weights(cfg: MoeConfig, seed: int = 0, experts: Optional[range] = None) -> MoeWeights:
+    """int8 weights uniform in [-127,127]; per-output-channel fp32 scales ~ U(1e-3, 1e-2)."""
+    experts = range(cfg.E) if experts is None else experts
+    w1, s1, w2, s2 = [], [], [], []
+    for e in experts:
+        g = torch.Generator().manual_seed(seed * 100003 + 7919 * e + 1)
+        w1.append(torch.randint(-127, 128, (cfg.H, 2 * cfg.I), generator=g, dtype=torch.int8))
+        w2.append(torch.randint(-127, 128, (cfg.I, cfg.H), generator=g, dtype=torch.int8))
+        s1.append(torch.rand(2 * cfg.I, generator=g) * 9e-3 + 1e-3)
+        s2.append(torch.rand(cfg.H, generator=g) * 9e-3 + 1e-3)
+    return MoeWeights(torch.stack(w1), torch.stack(s1), torch.stack(w2), torch.stack(s2))

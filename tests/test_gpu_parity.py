@@ -1,0 +1,377 @@
+"""GPU parity tests: every CUDA path, called through torch.ops.npu.* -> ctypes -> C ABI, against the CPU oracle.
+
+Bars: integer, byte and index outputs bit-exact; fp32 scales within 1 ulp (they are in fact equal); int8 outputs
+that follow an exp() (SwiGLU) may differ by one step where CPU and GPU exp differ in the last place, which the
+tests bound in size and rate; bf16 layer outputs within rtol 1e-2 / atol 1e-2.
+"""
+import os
+
+import pytest
+import torch
+
+import torchair_b200
+from oracle import moe_oracle as O
+from oracle.ep_standins import OracleKernels
+from torchair_b200 import ep, ops
+from torchair_b200.layer import moe_layer
+
+pytestmark = pytest.mark.gpu
+npu = torch.ops.npu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "cfg0_golden.pt")
+
+
+@pytest.fixture(scope="module")
+def dev():
+    return torch.device("cuda:0")
+
+
+def _ulp_equal(a, b, ulps=1):
+    a, b = a.float().cpu(), b.float().cpu()
+    return bool(((a.view(torch.int32) - b.view(torch.int32)).abs() <= ulps).all())
+
+
+def _gmm_ok(dev):
+    assert torchair_b200.gmm_status(dev) == 0, "a bounded wait inside the grouped GEMM gave up"
+
+
+# ---------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("shape", [(64, 1024), (2048, 7168), (3, 16), (5, 24576), (2, 3, 512), (0, 64)])
+def test_dynamic_quant_bit_exact(dev, dtype, shape):
+    g = torch.Generator().manual_seed(11)
+    x = (torch.randn(*shape, generator=g) * 2).to(dtype)
+    if x.numel():
+        x.view(-1, shape[-1])[0] = 0            # an all-zero row: scale 0, q 0
+    q, s = O.dynamic_quant(x)
+    qg, sg = npu.npu_dynamic_quant(x.to(dev))
+    assert qg.dtype == torch.int8 and sg.dtype == torch.float32 and sg.shape == x.shape[:-1]
+    assert torch.equal(q, qg.cpu())
+    assert _ulp_equal(s, sg) and torch.equal(s, sg.cpu())
+
+
+def test_dynamic_quant_smooth_scales_and_unsupported_modes(dev):
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(130, 2048, generator=g).to(torch.bfloat16)
+    sm = (torch.rand(2048, generator=g) + 0.5).to(torch.bfloat16)
+    q, s = O.dynamic_quant(x, sm)
+    qg, sg = npu.npu_dynamic_quant(x.to(dev), smooth_scales=sm.to(dev))
+    assert torch.equal(q, qg.cpu()) and torch.equal(s, sg.cpu())
+    with pytest.raises(NotImplementedError):
+        npu.npu_dynamic_quant(x.to(dev), dst_type=16)
+    with pytest.raises(NotImplementedError):
+        npu.npu_dynamic_quant(x.to(dev), quant_mode="pergroup")
+    with pytest.raises(RuntimeError, match="multiple of 16"):
+        npu.npu_dynamic_quant(x[:, :24].to(dev))
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-6), (torch.bfloat16, 0.0), (torch.float16, 0.0)])
+def test_swiglu(dev, dtype, tol):
+    g = torch.Generator().manual_seed(13)
+    x = (torch.randn(257, 4096, generator=g) * 3).to(dtype)
+    ref = O.swiglu(x)
+    got = npu.npu_swiglu(x.to(dev)).cpu()
+    assert got.shape == (257, 2048) and got.dtype == dtype
+    if dtype == torch.float32:
+        # fp32 tolerance: CPU and GPU exp() may differ in the last place
+        torch.testing.assert_close(got, ref, rtol=tol, atol=1e-7)
+    else:
+        # 16-bit outputs: identical except where the fp32 value sits on a rounding boundary
+        mism = (got != ref).float().mean().item()
+        assert mism < 1e-3
+        torch.testing.assert_close(got.float(), ref.float(), rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("T,K,E,H,active", [(3, 2, 4, 8, 3), (64, 2, 8, 1024, 64), (256, 8, 256, 7168, 256),
+                                            (3000, 8, 256, 64, 3000), (100, 4, 1000, 32, 7), (1, 1, 1, 16, 1)])
+def test_init_routing_bit_exact(dev, T, K, E, H, active):
+    g = torch.Generator().manual_seed(T * 31 + K)
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    ids = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int32)
+    row = torch.arange(T * K, dtype=torch.int32).view(K, T).t().contiguous()
+    a = O.moe_init_routing(x, row, ids, active)
+    b = npu.npu_moe_init_routing(x.to(dev), row.to(dev), ids.to(dev), active)
+    for u, v in zip(a, b):
+        assert u.shape == v.shape and torch.equal(u, v.cpu())
+    xf = x.float()
+    bf = npu.npu_moe_init_routing(xf.to(dev), row.to(dev), ids.to(dev), active)
+    assert torch.equal(O.moe_init_routing(xf, row, ids, active)[0], bf[0].cpu())
+
+
+@pytest.mark.parametrize("cfg_name,quant_mode,nums_type", [("cfg0", 2, 1), ("cfg0", 0, 0), ("cfg1", 2, 1)])
+def test_single_rank_dispatch_bit_exact(dev, cfg_name, quant_mode, nums_type):
+    cfg = O.CONFIGS[cfg_name]
+    x, ids, wt = O.make_tokens(cfg, seed=3)
+    d = O.moe_distribute_dispatch([x], [ids], cfg.E, quant_mode=quant_mode, expert_token_nums_type=nums_type)[0]
+    g = npu.npu_moe_distribute_dispatch(x.to(dev), ids.to(dev), "", 1, 0, cfg.E, quant_mode=quant_mode,
+                                        expert_token_nums_type=nums_type)
+    want = (d.expand_x, d.dynamic_scales, d.expand_idx, d.expert_token_nums, d.ep_recv_count, d.tp_recv_count, d.expand_scales)
+    for u, v in zip(want, g):
+        assert u.dtype == v.dtype and torch.equal(u, v.cpu())
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("T,K,H,shared", [(64, 2, 1024, False), (256, 8, 7168, True), (7, 3, 64, False)])
+def test_single_rank_combine_bit_exact(dev, dtype, T, K, H, shared):
+    g = torch.Generator().manual_seed(17)
+    y = torch.randn(T * K, H, generator=g).to(dtype)
+    pos = torch.randperm(T * K, generator=g).to(torch.int32).view(T, K)
+    wt = torch.rand(T, K, generator=g)
+    sh = torch.randn(T, H, generator=g).to(dtype) if shared else None
+    ref = O.weighted_gather_sum(y, pos, wt, sh)
+    ids = torch.zeros(T, K, dtype=torch.int32)
+    got = npu.npu_moe_distribute_combine(y.to(dev), ids.to(dev), pos.reshape(-1).to(dev),
+                                         torch.zeros(1, dtype=torch.int32, device=dev), wt.to(dev), "", 1, 0, 1,
+                                         shared_expert_x=None if sh is None else sh.to(dev))
+    assert torch.equal(ref, got.cpu())
+
+
+@pytest.mark.parametrize("R,E_l,slot", [(2, 4, 0), (8, 32, 0), (4, 3, 0), (2, 4, 40), (1, 8, 0)])
+def test_exchange_plan_and_rows_bit_exact(dev, R, E_l, slot):
+    g = torch.Generator().manual_seed(R * 100 + E_l)
+    counts = torch.randint(0, 6, (R, E_l), generator=g, dtype=torch.int32)
+    counts[0, 0] = 0
+    H = 64
+    for nums_type in (0, 1):
+        pc, nc, ec = OracleKernels.exchange_plan(counts, R, E_l, slot, nums_type)
+        pg, ng, eg = ep.CudaKernels.exchange_plan(counts.to(dev), R, E_l, slot, nums_type)
+        assert torch.equal(pc, pg.cpu()) and torch.equal(nc, ng.cpu()) and torch.equal(ec, eg.cpu())
+    total = int(counts.sum())
+    wire_rows = R * slot if slot else total
+    wire = torch.randint(-127, 128, (wire_rows, H), generator=g, dtype=torch.int8)
+    wsc = torch.rand(wire_rows, generator=g)
+    A = total + 5
+    dc, sc = OracleKernels.exchange_rows(wire, wsc, pc, R, E_l, slot, 0, A, True)
+    dg, sg = ep.CudaKernels.exchange_rows(wire.to(dev), wsc.to(dev), pg, R, E_l, slot, 0, A, True)
+    assert torch.equal(dc, dg.cpu()) and torch.equal(sc, sg.cpu())
+    y = torch.randn(A, H, generator=g).to(torch.bfloat16)
+    bc, _ = OracleKernels.exchange_rows(y, None, pc, R, E_l, slot, 1, wire_rows, True)
+    bg, _ = ep.CudaKernels.exchange_rows(y.to(dev), None, pg, R, E_l, slot, 1, wire_rows, True)
+    assert torch.equal(bc, bg.cpu())
+
+
+# ---------------------------------------------------------------------------------------------------
+GMM_SHAPES = [  # M, Kd, N, E
+    (128, 1024, 1024, 8), (64, 512, 256, 4), (700, 1024, 384, 3), (2048, 2048, 512, 64), (5, 64, 128, 2),
+    (1000, 1536, 640, 2), (33, 7168, 256, 16), (4096, 256, 128, 1),
+]
+
+
+@pytest.mark.parametrize("M,Kd,N,E", GMM_SHAPES)
+def test_grouped_matmul_int32_bit_exact(dev, M, Kd, N, E):
+    g = torch.Generator().manual_seed(M + Kd + N + E)
+    x = torch.randint(-127, 128, (M, Kd), generator=g, dtype=torch.int8)
+    w = torch.randint(-127, 128, (E, Kd, N), generator=g, dtype=torch.int8)
+    cnt = torch.bincount(torch.randint(0, E, (M,), generator=g), minlength=E)
+    ref = O.grouped_matmul_w8a8(x, w, None, None, cnt, 1, 3)
+    got = npu.npu_grouped_matmul([x.to(dev)], [w.to(dev)], group_list=cnt.to(dev), split_item=2, group_type=0,
+                                 group_list_type=1, output_dtype=3)[0]
+    _gmm_ok(dev)
+    assert torch.equal(ref, got.cpu())
+    got0 = npu.npu_grouped_matmul([x.to(dev)], [w.to(dev)], group_list=torch.cumsum(cnt, 0).to(dev), split_item=3,
+                                  group_type=0, group_list_type=0, output_dtype=3)[0]
+    assert torch.equal(ref, got0.cpu())
+
+
+@pytest.mark.parametrize("out_dtype", [15, 5])
+@pytest.mark.parametrize("M,Kd,N,E", [(300, 1024, 1024, 8), (2048, 2048, 7168, 32), (17, 512, 136, 3)])
+def test_grouped_matmul_scaled_output(dev, out_dtype, M, Kd, N, E):
+    g = torch.Generator().manual_seed(M + N)
+    x = torch.randint(-127, 128, (M, Kd), generator=g, dtype=torch.int8)
+    w = torch.randint(-127, 128, (E, Kd, N), generator=g, dtype=torch.int8)
+    sc = torch.rand(E, N, generator=g) * 9e-3 + 1e-3
+    pts = torch.rand(M, generator=g) * 1e-2
+    covered = M - M // 10                         # the tail rows belong to no group and must come back zero
+    cnt = torch.bincount(torch.randint(0, E, (covered,), generator=g), minlength=E)
+    ref = O.grouped_matmul_w8a8(x, w, sc, pts, cnt, 1, out_dtype)
+    got = npu.npu_grouped_matmul([x.to(dev)], [w.to(dev)], scale=[sc.to(dev)], per_token_scale=[pts.to(dev)],
+                                 group_list=cnt.to(dev), split_item=2, group_type=0, group_list_type=1,
+                                 output_dtype=out_dtype)[0]
+    _gmm_ok(dev)
+    assert got.dtype == O.SCALAR_TYPE[out_dtype]
+    assert torch.equal(ref, got.cpu()), "same fp32 operation order must give identical 16-bit results"
+
+
+def test_grouped_matmul_skewed_and_empty_groups(dev):
+    g = torch.Generator().manual_seed(99)
+    M, Kd, N, E = 3000, 512, 256, 16
+    x = torch.randint(-127, 128, (M, Kd), generator=g, dtype=torch.int8)
+    w = torch.randint(-127, 128, (E, Kd, N), generator=g, dtype=torch.int8)
+    cnt = torch.tensor([0, 2500, 0, 1, 0, 0, 300, 17, 0, 0, 0, 100, 0, 0, 0, 82])
+    ref = O.grouped_matmul_w8a8(x, w, None, None, cnt, 1, 3)
+    got = npu.npu_grouped_matmul([x.to(dev)], [w.to(dev)], group_list=cnt.to(dev), split_item=2, group_type=0,
+                                 group_list_type=1, output_dtype=3)[0]
+    _gmm_ok(dev)
+    assert torch.equal(ref, got.cpu())
+    zero = npu.npu_grouped_matmul([x.to(dev)], [w.to(dev)], group_list=torch.zeros(E, dtype=torch.int64, device=dev),
+                                  split_item=2, group_type=0, group_list_type=1, output_dtype=3)[0]
+    _gmm_ok(dev)
+    assert int(zero.abs().sum()) == 0
+
+
+def test_packed_weight_cache_follows_storage_lifetime_and_version(dev):
+    g = torch.Generator().manual_seed(5)
+    x = torch.randint(-127, 128, (64, 256), generator=g, dtype=torch.int8).to(dev)
+    cnt = torch.tensor([64], device=dev)
+
+    def run(w):
+        return npu.npu_grouped_matmul([x], [w], group_list=cnt, split_item=2, group_type=0, group_list_type=1, output_dtype=3)[0]
+    for i in range(3):      # fresh weights that are likely to reuse the freed address must not hit a stale entry
+        w = torch.randint(-127, 128, (1, 256, 128), generator=g, dtype=torch.int8).to(dev)
+        assert torch.equal(run(w).cpu(), (x.cpu().int() @ w[0].cpu().int()))
+        del w
+    w = torch.randint(-127, 128, (1, 256, 128), generator=g, dtype=torch.int8).to(dev)
+    run(w)
+    w.neg_()                # in-place update bumps the version counter
+    assert torch.equal(run(w).cpu(), (x.cpu().int() @ w[0].cpu().int()))
+
+
+def _swiglu_quant_close(q_gpu, s_gpu, q_ref, s_ref):
+    diff = (q_gpu.cpu().int() - q_ref.int()).abs()
+    assert int(diff.max()) <= 1, "int8 after SwiGLU may differ by at most one step"
+    assert float((diff > 0).float().mean()) < 2e-3
+    assert _ulp_equal(s_gpu, s_ref, ulps=4)
+
+
+@pytest.mark.parametrize("activate_left", [True, False])
+def test_dequant_swiglu_quant_standalone(dev, activate_left):
+    g = torch.Generator().manual_seed(23)
+    M, N2, E = 300, 1024, 6
+    acc = torch.randint(-2_000_000, 2_000_000, (M, N2), generator=g, dtype=torch.int32)
+    ws = torch.rand(E, N2, generator=g) * 9e-3 + 1e-3
+    a = torch.rand(M, generator=g) * 1e-3
+    cnt = torch.tensor([50, 0, 100, 70, 30, 20])          # 270 of 300 rows
+    q, s = O.dequant_swiglu_quant(acc, ws, a, cnt, activate_left, 1)
+    qg, sg = npu.npu_dequant_swiglu_quant(acc.to(dev), weight_scale=ws.to(dev), activation_scale=a.to(dev),
+                                          group_index=cnt.to(dev), activate_left=activate_left, quant_mode=1)
+    _swiglu_quant_close(qg, sg, q, s)
+    assert int(qg[270:].abs().sum()) == 0 and float(sg[270:].abs().sum()) == 0
+    # the quantiser itself is bit-exact: feed the GPU's own fp32 SwiGLU values to the oracle quantiser
+    q1, s1 = O.dequant_swiglu_quant(acc, ws[:1], a, None, activate_left, 1)
+    qg1, sg1 = npu.npu_dequant_swiglu_quant(acc.to(dev), weight_scale=ws[:1].to(dev), activation_scale=a.view(-1, 1).to(dev),
+                                            activate_left=activate_left, quant_mode=1)
+    _swiglu_quant_close(qg1, sg1, q1, s1)
+
+
+@pytest.mark.parametrize("cfg_name", ["cfg0"])
+def test_fused_gate_up_matches_unfused_and_oracle(dev, cfg_name):
+    cfg = O.CONFIGS[cfg_name]
+    w = O.make_weights(cfg, 0)
+    x, ids, wt = O.make_tokens(cfg, 0)
+    collect = []
+    O.moe_layer([x], [ids], [wt], w, collect)
+    c = collect[0]
+    d = c["disp"]
+    args = (d.expand_x.to(dev), [w.w1.to(dev)], [w.s1.to(dev)], d.dynamic_scales.to(dev), d.expert_token_nums.to(dev))
+    hq, hs = npu.npu_grouped_matmul_swiglu_quant_v2(*args, group_list_type=1)
+    _gmm_ok(dev)
+    _swiglu_quant_close(hq, hs, c["hq"], c["hs"])
+    h32 = npu.npu_grouped_matmul([args[0]], args[1], group_list=args[4], split_item=2, group_type=0, group_list_type=1,
+                                 output_dtype=3)[0]
+    assert torch.equal(h32.cpu(), c["h32"])
+    q2, s2 = npu.npu_dequant_swiglu_quant(h32, weight_scale=args[2][0], activation_scale=args[3], group_index=args[4],
+                                          activate_left=True, quant_mode=1)
+    assert torch.equal(q2, hq) and torch.equal(s2, hs), "fused and unfused GPU paths must agree bit for bit"
+
+
+def test_layer_cfg0_against_oracle_and_golden(dev):
+    cfg = O.CONFIGS["cfg0"]
+    gold = torch.load(GOLDEN)
+    w = O.make_weights(cfg, 0)
+    x, ids, wt = O.make_tokens(cfg, 0)
+    assert torch.equal(ids, gold["expert_ids"]) and torch.equal(wt, gold["expert_scales"])
+    gw = [t.to(dev) for t in (w.w1, w.s1, w.w2, w.s2)]
+    for fused in (True, False):
+        out = moe_layer(x.to(dev), ids.to(dev), wt.to(dev), *gw, fused=fused).cpu()
+        _gmm_ok(dev)
+        torch.testing.assert_close(out.float(), gold["out"].float(), rtol=1e-2, atol=1e-2)
+    d = npu.npu_moe_distribute_dispatch(x.to(dev), ids.to(dev), "", 1, 0, cfg.E, quant_mode=2)
+    assert torch.equal(d[0].cpu(), gold["expand_x"]) and torch.equal(d[1].cpu(), gold["dynamic_scales"])
+    assert torch.equal(d[2].cpu(), gold["expand_idx"]) and torch.equal(d[3].cpu(), gold["expert_token_nums"])
+
+
+def test_layer_decode_shape_sampled_experts(dev):
+    """Config-1 architecture at a reduced expert count (32 experts, 32 tokens: the same ~8 rows per expert)."""
+    cfg = O.MoeConfig("cfg1_small", 32, 7168, 32, 8, 2048)
+    w = O.make_weights(cfg, 1)
+    x, ids, wt = O.make_tokens(cfg, 1)
+    ref = O.moe_layer([x], [ids], [wt], w)[0]
+    out = moe_layer(x.to(dev), ids.to(dev), wt.to(dev), w.w1.to(dev), w.s1.to(dev), w.w2.to(dev), w.s2.to(dev)).cpu()
+    _gmm_ok(dev)
+    torch.testing.assert_close(out.float(), ref.float(), rtol=1e-2, atol=1e-2)
+
+
+def test_layer_prefill_shape_with_skew(dev):
+    """Qwen3-shaped experts (H 4096 -> 512 here, I 1536) with Zipf routing: large, uneven groups, 256-token tiles."""
+    cfg = O.MoeConfig("skew", 2048, 512, 16, 4, 1536, zipf_s=1.2)
+    w = O.make_weights(cfg, 2)
+    x, ids, wt = O.make_tokens(cfg, 2)
+    ref = O.moe_layer([x], [ids], [wt], w)[0]
+    out = moe_layer(x.to(dev), ids.to(dev), wt.to(dev), w.w1.to(dev), w.s1.to(dev), w.w2.to(dev), w.s2.to(dev)).cpu()
+    _gmm_ok(dev)
+    torch.testing.assert_close(out.float(), ref.float(), rtol=1e-2, atol=1e-2)
+
+
+def test_full_size_decode_layer_properties(dev):
+    """Config 1 at full size (256 experts, 11 GB of int8 weights generated on the device): checked through
+    properties instead of a full CPU run -- sampled experts against the oracle, linearity in the routing weights,
+    and zero output for zero weights."""
+    cfg = O.CONFIGS["cfg1"]
+    g = torch.Generator(device=dev).manual_seed(7)
+    w1 = torch.randint(-127, 128, (cfg.E, cfg.H, 2 * cfg.I), generator=g, dtype=torch.int8, device=dev)
+    w2 = torch.randint(-127, 128, (cfg.E, cfg.I, cfg.H), generator=g, dtype=torch.int8, device=dev)
+    s1 = torch.rand(cfg.E, 2 * cfg.I, generator=g, device=dev) * 9e-3 + 1e-3
+    s2 = torch.rand(cfg.E, cfg.H, generator=g, device=dev) * 9e-3 + 1e-3
+    x, ids, wt = O.make_tokens(cfg, 0)
+    xd, idd, wtd = x.to(dev), ids.to(dev), wt.to(dev)
+    ex, xs, expand_idx, nums, ep_recv, _, _ = npu.npu_moe_distribute_dispatch(xd, idd, "", 1, 0, cfg.E, quant_mode=2)
+    hq, hs = npu.npu_grouped_matmul_swiglu_quant_v2(ex, [w1], [s1], xs, nums, group_list_type=1)
+    y = npu.npu_grouped_matmul([hq], [w2], scale=[s2], per_token_scale=[hs], group_list=nums, split_item=2, group_type=0,
+                               group_list_type=1, output_dtype=15)[0]
+    _gmm_ok(dev)
+    starts = (torch.cumsum(nums, 0) - nums).cpu()
+    for e in (0, 101, 255):
+        s0, c = int(starts[e]), int(nums[e])
+        if c == 0:
+            continue
+        we = O.MoeWeights(w1[e:e + 1].cpu(), s1[e:e + 1].cpu(), w2[e:e + 1].cpu(), s2[e:e + 1].cpu())
+        col = {}
+        yref = O.expert_ffn(ex[s0:s0 + c].cpu(), xs[s0:s0 + c].cpu(), torch.tensor([c]), we, col)
+        _swiglu_quant_close(hq[s0:s0 + c], hs[s0:s0 + c], col["hq"], col["hs"])
+        torch.testing.assert_close(y[s0:s0 + c].cpu().float(), yref.float(), rtol=1e-2, atol=1e-2)
+    out = npu.npu_moe_distribute_combine(y, idd, expand_idx, ep_recv, wtd, "", 1, 0, cfg.E)
+    out2 = npu.npu_moe_distribute_combine(y, idd, expand_idx, ep_recv, wtd * 2, "", 1, 0, cfg.E)
+    torch.testing.assert_close(out2.float(), out.float() * 2, rtol=1e-2, atol=1e-2)
+    out0 = npu.npu_moe_distribute_combine(y, idd, expand_idx, ep_recv, torch.zeros_like(wtd), "", 1, 0, cfg.E)
+    assert float(out0.float().abs().sum()) == 0
+    del w1, w2
+    torchair_b200.clear_weight_cache()
+    torch.cuda.empty_cache()
+
+
+def test_torch_compile_backend_runs_the_ops_and_captures_a_cuda_graph(dev):
+    from torchair_b200 import backend
+    cfg = O.CONFIGS["cfg0"]
+    w = O.make_weights(cfg, 0)
+    x, ids, wt = O.make_tokens(cfg, 0)
+    ref = O.moe_layer([x], [ids], [wt], w)[0]
+
+    class Layer(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            for n, t in (("w1", w.w1), ("s1", w.s1), ("w2", w.w2), ("s2", w.s2)):
+                self.register_buffer(n, t.to(dev))
+
+        def forward(self, x, ids, wt):
+            return moe_layer(x, ids, wt, self.w1, self.s1, self.w2, self.s2, fused=False)
+
+    config = torchair_b200.CompilerConfig()
+    config.mode = "reduce-overhead"
+    fused_before, cap_before = backend.counters["fused_gate_up"], backend.counters["captures"]
+    model = torch.compile(Layer(), backend=torchair_b200.get_npu_backend(compiler_config=config), fullgraph=True, dynamic=False)
+    with torch.no_grad():
+        for i in range(3):
+            out = model(x.to(dev), ids.to(dev), wt.to(dev))
+    _gmm_ok(dev)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=1e-2, atol=1e-2)
+    assert backend.counters["fused_gate_up"] == fused_before + 1, "the FX pass should fuse gate_up with its epilogue"
+    assert backend.counters["captures"] == cap_before + 1 and backend.counters["replays"] >= 3

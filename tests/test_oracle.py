@@ -1,0 +1,167 @@
+"""CPU tests of the oracle: golden vectors, known answers and the properties the domain offers."""
+import os
+
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+from tests.golden.make_golden import build as build_golden, checksum
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "cfg0_golden.pt")
+
+
+def _eq(a, b):
+    if isinstance(a, dict):
+        return set(a) == set(b) and all(_eq(a[k], b[k]) for k in a)
+    if isinstance(a, (list, tuple)):
+        return len(a) == len(b) and all(_eq(x, y) for x, y in zip(a, b))
+    if isinstance(a, torch.Tensor):
+        return a.dtype == b.dtype and torch.equal(a, b)
+    return a == b
+
+
+def test_oracle_matches_committed_golden_vectors():
+    gold = torch.load(GOLDEN)
+    now = build_golden()
+    assert now["input_checksums"] == gold["input_checksums"], "seeded input stream changed"
+    for k in gold:
+        assert _eq(now[k], gold[k]), f"oracle output {k} differs from the committed golden vector"
+
+
+def test_init_routing_known_answer():
+    # shape of the reference's only declared case: x F32(3,4), row_idx/expert_idx I32(3,2), active_num=3
+    # (python/torchair/_ge_concrete_graph/ge_converter/custom/moe_init_routing.py:4-8)
+    x = torch.arange(12, dtype=torch.float32).view(3, 4)
+    expert = torch.tensor([[1, 0], [0, 2], [1, 2]], dtype=torch.int32)
+    row = torch.arange(6, dtype=torch.int32).view(2, 3).t().contiguous()      # value k*T + t
+    ex, eri, eei = O.moe_init_routing(x, row, expert, 3)
+    assert eei.tolist() == [0, 0, 1, 1, 2, 2]
+    # sorted pairs (flat t*K+k): (0,1)->e0, (1,0)->e0, (0,0)->e1, (2,0)->e1, (1,1)->e2, (2,1)->e2
+    assert torch.equal(ex, x[[0, 1, 0, 2, 1, 2]])
+    # row_idx values of those pairs: 3, 1, 0, 2, 4, 5 -> inverse
+    assert eri.tolist() == [2, 1, 3, 0, 4, 5]
+    ex2, _, _ = O.moe_init_routing(x, row, expert, 2)
+    assert ex2.shape == (4, 4) and torch.equal(ex2, ex[:4])
+
+
+def test_dynamic_quant_known_answers_half_even_and_clamp():
+    x = torch.tensor([[127.0, 63.5, 62.5, -0.5, -1.5, 2.5, 0.0, -127.0]])
+    q, s = O.dynamic_quant(x)
+    assert float(s) == 1.0
+    assert q.tolist() == [[127, 64, 62, 0, -2, 2, 0, -127]]
+    q0, s0 = O.dynamic_quant(torch.zeros(2, 16))
+    assert float(s0.abs().sum()) == 0 and int(q0.abs().sum()) == 0
+    x3 = torch.randn(2, 3, 32, dtype=torch.float32).to(torch.bfloat16)
+    q3, s3 = O.dynamic_quant(x3)
+    assert q3.shape == (2, 3, 32) and s3.shape == (2, 3) and q3.dtype == torch.int8 and s3.dtype == torch.float32
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_dynamic_quant_properties(dtype):
+    g = torch.Generator().manual_seed(3)
+    x = (torch.randn(257, 512, generator=g) * 3).to(dtype)
+    q, s = O.dynamic_quant(x)
+    assert int(q.abs().max()) <= 127
+    assert bool((q.abs().amax(dim=1) == 127).all()), "the row maximum must map to +-127"
+    err = (x.float() - q.float() * s[:, None]).abs()
+    assert bool((err <= s[:, None] * 0.5 * (1 + 1e-5) + 1e-12).all())
+    sm = torch.rand(512, generator=g).to(dtype)
+    q2, s2 = O.dynamic_quant(x, sm)
+    qa, sa = O.quantize_rows_f32(x.float() * sm.float())
+    assert torch.equal(q2, qa) and torch.equal(s2, sa)
+
+
+def test_swiglu_and_dequant_swiglu_quant_halves():
+    x = torch.tensor([[1.0, -2.0, 3.0, 0.5]])
+    y = O.swiglu(x)
+    ref = torch.nn.functional.silu(torch.tensor([1.0, -2.0])) * torch.tensor([3.0, 0.5])
+    assert torch.allclose(y, ref.view(1, 2))
+    acc = torch.tensor([[100, -200, 300, 50]], dtype=torch.int32)
+    ws = torch.tensor([0.01, 0.02, 0.03, 0.04])
+    a = torch.tensor([0.5])
+    left = O.dequant_swiglu_f32(acc, ws, a, None, True)
+    right = O.dequant_swiglu_f32(acc, ws, a, None, False)
+    v = acc.float() * 0.5 * ws
+    assert torch.allclose(left, torch.nn.functional.silu(v[:, :2]) * v[:, 2:])
+    assert torch.allclose(right, torch.nn.functional.silu(v[:, 2:]) * v[:, :2])
+    q, s = O.dequant_swiglu_quant(acc, ws, a, None, True, 1)
+    assert q.dtype == torch.int8 and q.shape == (1, 2) and s.shape == (1,)
+    with pytest.raises(NotImplementedError):
+        O.dequant_swiglu_quant(acc, ws, a, None, True, 0)
+
+
+def test_grouped_matmul_group_list_types_and_uncovered_rows():
+    g = torch.Generator().manual_seed(5)
+    M, Kd, N, E = 37, 64, 48, 5
+    x = torch.randint(-127, 128, (M, Kd), generator=g, dtype=torch.int8)
+    w = torch.randint(-127, 128, (E, Kd, N), generator=g, dtype=torch.int8)
+    counts = torch.tensor([5, 0, 12, 9, 4])                  # 30 of 37 rows covered
+    y1 = O.grouped_matmul_w8a8(x, w, None, None, counts, 1, 3)
+    y0 = O.grouped_matmul_w8a8(x, w, None, None, torch.cumsum(counts, 0), 0, 3)
+    assert torch.equal(y0, y1)
+    assert int(y1[30:].abs().sum()) == 0
+    ref = (x[5:17].double() @ w[2].double()).to(torch.int32)
+    assert torch.equal(y1[5:17], ref)
+    sc, pts = torch.rand(E, N, generator=g), torch.rand(M, generator=g)
+    yb = O.grouped_matmul_w8a8(x, w, sc, pts, counts, 1, 15)
+    want = ((y1[17:26].float() * pts[17:26, None]) * sc[3][None]).to(torch.bfloat16)
+    assert torch.equal(yb[17:26], want)
+
+
+def test_dispatch_is_a_valid_permutation_and_counts_add_up():
+    cfg = O.CONFIGS["cfg0"]
+    x, ids, wt = O.make_tokens(cfg, seed=1)
+    d = O.moe_distribute_dispatch([x], [ids], cfg.E)[0]
+    M = cfg.T * cfg.K
+    assert sorted(d.expand_idx.tolist()) == list(range(M))
+    assert int(d.expert_token_nums.sum()) == M
+    q, s = O.dynamic_quant(x)
+    pos = d.expand_idx.view(cfg.T, cfg.K).long()
+    for k in range(cfg.K):
+        assert torch.equal(d.expand_x[pos[:, k]], q) and torch.equal(d.dynamic_scales[pos[:, k]], s)
+    # rows are grouped by expert in ascending order
+    sorted_e = torch.repeat_interleave(torch.arange(cfg.E), d.expert_token_nums)
+    assert torch.equal(sorted_e[pos.reshape(-1)].to(torch.int32), ids.reshape(-1))
+
+
+def test_dispatch_then_combine_with_identity_experts_is_weighted_sum():
+    cfg = O.CONFIGS["cfg0"]
+    for R in (1, 2, 4):
+        xs, idl, wl = zip(*[O.make_tokens(cfg, 2, r) for r in range(R)])
+        disp = O.moe_distribute_dispatch(xs, idl, cfg.E, quant_mode=0)
+        ys = [d.expand_x for d in disp]
+        outs = O.moe_distribute_combine(ys, idl, disp, wl, cfg.E)
+        for r in range(R):
+            acc = None
+            for k in range(cfg.K):
+                term = wl[r][:, k:k + 1] * xs[r].float()
+                acc = term if acc is None else acc + term
+            assert torch.equal(outs[r], acc.to(torch.bfloat16))
+
+
+@pytest.mark.parametrize("R", [2, 4, 8])
+def test_r_rank_layer_equals_one_rank_layer(R):
+    cfg = O.CONFIGS["cfg0"]
+    w = O.make_weights(cfg, seed=0)
+    xs, idl, wl = zip(*[O.make_tokens(cfg, 0, r) for r in range(R)])
+    multi = O.moe_layer(xs, idl, wl, w)
+    for r in range(R):
+        single = O.moe_layer([xs[r]], [idl[r]], [wl[r]], w)[0]
+        assert torch.equal(single, multi[r])
+
+
+def test_zipf_routing_is_skewed_and_gating_is_normalised():
+    cfg = O.MoeConfig("skew", 512, 64, 64, 8, 32, zipf_s=1.2)
+    _, ids, wt = O.make_tokens(cfg, seed=0)
+    assert torch.allclose(wt.sum(1), torch.ones(cfg.T), atol=1e-5)
+    assert all(len(set(r)) == cfg.K for r in ids.tolist()), "top-k experts of a token are distinct"
+    hist = torch.bincount(ids.reshape(-1).long(), minlength=cfg.E).float()
+    assert hist.max() / hist.mean() > 3.0
+    _, ids_u, _ = O.make_tokens(O.MoeConfig("flat", 512, 64, 64, 8, 32), seed=0)
+    hist_u = torch.bincount(ids_u.reshape(-1).long(), minlength=64).float()
+    assert hist_u.max() / hist_u.mean() < 2.0
+
+
+def test_checksum_is_order_sensitive():
+    a = torch.arange(16, dtype=torch.int32)
+    assert checksum(a) != checksum(a.flip(0))

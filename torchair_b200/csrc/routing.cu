@@ -1,0 +1,545 @@
+// Routing kernels of the MoE path: stable counting sort of (token, k) pairs by expert id
+// (npu_moe_init_routing, sender side of npu_moe_distribute_dispatch), the fused quantise-and-scatter of
+// token rows, the receiver-side row permutations around the all-to-all, and the weighted gather-sum of
+// npu_moe_distribute_combine.  Integer/byte movers: HBM-bound, 16-byte accesses, grids sized to the SMs.
+#include "tab_common.cuh"
+
+namespace tab {
+
+constexpr int kChunk = 1024;        // pairs per CTA in the sort kernels (32 warps x 32 lanes)
+constexpr int kMaxExperts = 2048;   // bins of the counting sort
+
+// Exclusive scan of vals[0..n) (n <= 2*blockDim.x, blockDim.x == 1024) in shared memory; returns the total.
+__device__ int block_exclusive_scan(int* vals, int n, int* warp_sums) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int i0 = 2 * tid, i1 = 2 * tid + 1;
+  const int a = i0 < n ? vals[i0] : 0;
+  const int b = i1 < n ? vals[i1] : 0;
+  int s = a + b;
+  int incl = s;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    int t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  if (lane == 31) warp_sums[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    int w = warp_sums[lane];
+    int wi = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int t = __shfl_up_sync(0xffffffffu, wi, o);
+      if (lane >= o) wi += t;
+    }
+    warp_sums[lane] = wi - w;  // exclusive
+    if (lane == 31) warp_sums[32] = wi;
+  }
+  __syncthreads();
+  const int excl = warp_sums[warp] + incl - s;
+  if (i0 < n) vals[i0] = excl;
+  if (i1 < n) vals[i1] = excl + a;
+  const int total = warp_sums[32];
+  __syncthreads();
+  return total;
+}
+
+__device__ __forceinline__ int clamp_expert(int key, int nb, int* status) {
+  if (key < 0 || key >= nb) {
+    *status = 1;  // expert id outside [0, bound): clamped so that no access goes out of range
+    key = key < 0 ? 0 : nb - 1;
+  }
+  return key;
+}
+
+// Phase 1: per-chunk histogram of expert ids.  chunk_hist [nchunks, nb].
+__global__ void __launch_bounds__(kChunk) route_hist_kernel(const int32_t* __restrict__ expert, int n, int nb,
+                                                            int* __restrict__ chunk_hist, int* status) {
+  extern __shared__ int s_hist[];
+  for (int i = threadIdx.x; i < nb; i += kChunk) s_hist[i] = 0;
+  __syncthreads();
+  const int f = blockIdx.x * kChunk + threadIdx.x;
+  if (f < n) atomicAdd(&s_hist[clamp_expert(expert[f], nb, status)], 1);
+  __syncthreads();
+  for (int i = threadIdx.x; i < nb; i += kChunk) chunk_hist[blockIdx.x * nb + i] = s_hist[i];
+}
+
+// Phase 2 (one CTA): totals per expert, their exclusive scan, and the base offset of every (chunk, expert).
+// chunk_hist is overwritten in place with those bases.  expert_count int32 [nb] (optional second copy out).
+__global__ void __launch_bounds__(1024) route_scan_kernel(int* __restrict__ chunk_hist, int nchunks, int nb,
+                                                          int* __restrict__ expert_count,
+                                                          int* __restrict__ expert_count_out) {
+  __shared__ int s_tot[kMaxExperts];
+  __shared__ int s_warp[33];
+  for (int e = threadIdx.x; e < nb; e += 1024) {
+    int t = 0;
+    for (int c = 0; c < nchunks; ++c) t += chunk_hist[c * nb + e];
+    s_tot[e] = t;
+    expert_count[e] = t;
+    if (expert_count_out) expert_count_out[e] = t;
+  }
+  __syncthreads();
+  block_exclusive_scan(s_tot, nb, s_warp);
+  for (int e = threadIdx.x; e < nb; e += 1024) {
+    int run = s_tot[e];
+    for (int c = 0; c < nchunks; ++c) {
+      const int h = chunk_hist[c * nb + e];
+      chunk_hist[c * nb + e] = run;
+      run += h;
+    }
+  }
+}
+
+// Phase 3: stable rank of every pair inside its chunk (warp match + per-warp counts) plus the chunk base.
+//   sorted_expert[pos] = expert id, sorted_src[pos] = src_val[f] (or f when src_val is null),
+//   inverse[inv_key] = pos where inv_key = src_val[f] (init_routing: expanded_row_idx is indexed by the
+//   row_idx VALUE) or f (dispatch: expand_idx is indexed by the flattened pair index).
+__global__ void __launch_bounds__(kChunk) route_scatter_kernel(const int32_t* __restrict__ expert,
+                                                               const int32_t* __restrict__ src_val, int n, int nb,
+                                                               const int* __restrict__ chunk_base,
+                                                               int32_t* __restrict__ sorted_expert,
+                                                               int32_t* __restrict__ sorted_src,
+                                                               int32_t* __restrict__ inverse, int* status) {
+  extern __shared__ unsigned short s_wcnt[];  // [32 warps][nb]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int i = tid; i < 32 * nb; i += kChunk) s_wcnt[i] = 0;
+  __syncthreads();
+  const int f = blockIdx.x * kChunk + tid;
+  const bool valid = f < n;
+  const int key = valid ? clamp_expert(expert[f], nb, status) : -1;
+  const unsigned peers = __match_any_sync(0xffffffffu, key);
+  const int rank_in_warp = __popc(peers & ((1u << lane) - 1u));
+  if (valid && rank_in_warp == 0) s_wcnt[warp * nb + key] = static_cast<unsigned short>(__popc(peers));
+  __syncthreads();
+  for (int e = tid; e < nb; e += kChunk) {  // exclusive prefix over the 32 warps, per expert column
+    int run = 0;
+#pragma unroll 8
+    for (int w = 0; w < 32; ++w) {
+      const int c = s_wcnt[w * nb + e];
+      s_wcnt[w * nb + e] = static_cast<unsigned short>(run);
+      run += c;
+    }
+  }
+  __syncthreads();
+  if (valid) {
+    const int pos = chunk_base[blockIdx.x * nb + key] + s_wcnt[warp * nb + key] + rank_in_warp;
+    const int sv = src_val ? src_val[f] : f;
+    sorted_expert[pos] = key;
+    if (sorted_src) sorted_src[pos] = sv;
+    inverse[sv] = pos;
+  }
+}
+
+struct SortScratch {
+  int* chunk_hist;    // [nchunks, nb]
+  int* expert_count;  // [nb]
+  int* status;        // [1]
+  int32_t* sorted_src;     // [n]
+  int32_t* sorted_expert;  // [n] (dispatch only; init_routing writes the caller's output)
+};
+
+static size_t sort_scratch_bytes(int64_t n, int64_t nb, bool need_sorted_expert) {
+  const int64_t nchunks = (n + kChunk - 1) / kChunk;
+  size_t ints = static_cast<size_t>(nchunks * nb + nb + 4 + n + (need_sorted_expert ? n : 0));
+  return (ints * 4 + 255) / 256 * 256;
+}
+
+static SortScratch carve(void* ws, int64_t n, int64_t nb, bool need_sorted_expert) {
+  const int64_t nchunks = (n + kChunk - 1) / kChunk;
+  SortScratch s;
+  int* p = static_cast<int*>(ws);
+  s.chunk_hist = p; p += nchunks * nb;
+  s.expert_count = p; p += nb;
+  s.status = p; p += 4;
+  s.sorted_src = p; p += n;
+  s.sorted_expert = need_sorted_expert ? p : nullptr;
+  return s;
+}
+
+static int run_sort(const int32_t* expert, const int32_t* src_val, int64_t n, int64_t nb, const SortScratch& s,
+                    int32_t* sorted_expert, int32_t* inverse, int32_t* expert_count_out, cudaStream_t st) {
+  const int nchunks = static_cast<int>((n + kChunk - 1) / kChunk);
+  const size_t scatter_smem = static_cast<size_t>(32) * nb * sizeof(unsigned short);
+  if (scatter_smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(route_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(scatter_smem));
+    if (e != cudaSuccess) return fail(TAB_ERR_CUDA, "routing: shared memory opt-in failed: %s", cudaGetErrorString(e));
+  }
+  route_hist_kernel<<<nchunks, kChunk, nb * sizeof(int), st>>>(expert, (int)n, (int)nb, s.chunk_hist, s.status);
+  route_scan_kernel<<<1, 1024, 0, st>>>(s.chunk_hist, nchunks, (int)nb, s.expert_count, expert_count_out);
+  route_scatter_kernel<<<nchunks, kChunk, scatter_smem, st>>>(expert, src_val, (int)n, (int)nb, s.chunk_hist,
+                                                             sorted_expert, s.sorted_src, inverse, s.status);
+  return check_launch("routing sort");
+}
+
+// dst[i] = src[(idx[i] % mod)] for i < rows; one CTA per row, 16-byte vectors.
+__global__ void __launch_bounds__(256) gather_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ idx,
+                                                          int mod, int64_t rows, int vec_per_row,
+                                                          uint4* __restrict__ dst) {
+  for (int64_t i = blockIdx.x; i < rows; i += gridDim.x) {
+    const int64_t s = idx[i] % mod;
+    const uint4* sp = src + s * vec_per_row;
+    uint4* dp = dst + i * vec_per_row;
+    for (int v = threadIdx.x; v < vec_per_row; v += 256) dp[v] = sp[v];
+  }
+}
+
+// Sender side of dispatch: one CTA per token; quantise the row once (or copy it), then write the K copies
+// to their sorted positions.  cols % 16 == 0.
+constexpr int kPackThreads = 256;
+constexpr int kPackChunks = 8;
+template <typename T, bool kQuant>
+__global__ void __launch_bounds__(kPackThreads) dispatch_pack_kernel(const T* __restrict__ x,
+                                                                    const int32_t* __restrict__ expand_idx,
+                                                                    int64_t tokens, int K, int cols,
+                                                                    void* __restrict__ send_rows,
+                                                                    float* __restrict__ send_scales) {
+  __shared__ float red[32];
+  const int nchunk = cols >> 3;
+  for (int64_t t = blockIdx.x; t < tokens; t += gridDim.x) {
+    const T* xr = x + t * cols;
+    if constexpr (kQuant) {
+      float v[kPackChunks][8];
+      float amax = 0.f;
+#pragma unroll
+      for (int c = 0; c < kPackChunks; ++c) {
+        const int ch = threadIdx.x + c * kPackThreads;
+        if (ch < nchunk) {
+          Elem<T>::load8(xr + ch * 8, v[c]);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[c][i]));
+        }
+      }
+      for (int ch = threadIdx.x + kPackChunks * kPackThreads; ch < nchunk; ch += kPackThreads) {
+        float tmp[8];
+        Elem<T>::load8(xr + ch * 8, tmp);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(tmp[i]));
+      }
+      amax = warp_max(amax);
+      if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+      __syncthreads();
+      float r = (threadIdx.x & 31) < (kPackThreads >> 5) ? red[threadIdx.x & 31] : 0.f;
+      amax = warp_max(r);
+      __syncthreads();
+      const float sc = __fdiv_rn(amax, 127.0f);
+      int8_t* out = static_cast<int8_t*>(send_rows);
+#pragma unroll
+      for (int c = 0; c < kPackChunks; ++c) {
+        const int ch = threadIdx.x + c * kPackThreads;
+        if (ch < nchunk) {
+          uint2 o;
+          o.x = pack4_i8(quant_i8(v[c][0], sc), quant_i8(v[c][1], sc), quant_i8(v[c][2], sc), quant_i8(v[c][3], sc));
+          o.y = pack4_i8(quant_i8(v[c][4], sc), quant_i8(v[c][5], sc), quant_i8(v[c][6], sc), quant_i8(v[c][7], sc));
+          for (int k = 0; k < K; ++k) {
+            const int64_t pos = expand_idx[t * K + k];
+            *reinterpret_cast<uint2*>(out + pos * cols + ch * 8) = o;
+          }
+        }
+      }
+      for (int ch = threadIdx.x + kPackChunks * kPackThreads; ch < nchunk; ch += kPackThreads) {
+        float tmp[8];
+        Elem<T>::load8(xr + ch * 8, tmp);
+        uint2 o;
+        o.x = pack4_i8(quant_i8(tmp[0], sc), quant_i8(tmp[1], sc), quant_i8(tmp[2], sc), quant_i8(tmp[3], sc));
+        o.y = pack4_i8(quant_i8(tmp[4], sc), quant_i8(tmp[5], sc), quant_i8(tmp[6], sc), quant_i8(tmp[7], sc));
+        for (int k = 0; k < K; ++k) {
+          const int64_t pos = expand_idx[t * K + k];
+          *reinterpret_cast<uint2*>(out + pos * cols + ch * 8) = o;
+        }
+      }
+      if (threadIdx.x < K) send_scales[expand_idx[t * K + threadIdx.x]] = sc;
+    } else {
+      T* out = static_cast<T*>(send_rows);
+      const int nvec = cols * static_cast<int>(sizeof(T)) / 16;
+      const uint4* sp = reinterpret_cast<const uint4*>(xr);
+      for (int vi = threadIdx.x; vi < nvec; vi += kPackThreads) {
+        const uint4 val = sp[vi];
+        for (int k = 0; k < K; ++k) {
+          const int64_t pos = expand_idx[t * K + k];
+          reinterpret_cast<uint4*>(out + pos * cols)[vi] = val;
+        }
+      }
+      if (threadIdx.x < K) send_scales[expand_idx[t * K + threadIdx.x]] = 0.f;
+    }
+  }
+}
+
+// ---- receiver side ---------------------------------------------------------------------------------
+// plan = wire_off[R*E_l] (index s*E_l+e) ++ exp_off[R*E_l + 1] (index e*R+s, last = total rows).
+__global__ void __launch_bounds__(1024) exchange_plan_kernel(const int32_t* __restrict__ recv_counts, int R, int E_l,
+                                                            int slot_rows, int nums_type, int32_t* __restrict__ plan,
+                                                            int64_t* __restrict__ expert_token_nums,
+                                                            int32_t* __restrict__ ep_recv_count) {
+  __shared__ int s_wire[kMaxExperts];
+  __shared__ int s_exp[kMaxExperts];
+  __shared__ int s_warp[33];
+  const int n = R * E_l;
+  for (int i = threadIdx.x; i < n; i += 1024) {
+    const int c = max(recv_counts[i], 0);
+    s_wire[i] = c;                       // i = s*E_l + e
+    const int s = i / E_l, e = i - s * E_l;
+    s_exp[e * R + s] = c;
+    ep_recv_count[e * R + s] = c;
+  }
+  __syncthreads();
+  block_exclusive_scan(s_wire, n, s_warp);
+  const int total = block_exclusive_scan(s_exp, n, s_warp);
+  for (int i = threadIdx.x; i < n; i += 1024) {
+    const int s = i / E_l;
+    int w = s_wire[i];
+    if (slot_rows > 0) w = w - s_wire[s * E_l] + s * slot_rows;  // offset inside the source's fixed slot
+    plan[i] = w;
+    plan[n + i] = s_exp[i];
+  }
+  if (threadIdx.x == 0) plan[2 * n] = total;
+  for (int e = threadIdx.x; e < E_l; e += 1024) {
+    const int begin = s_exp[e * R];
+    const int end = (e + 1 < E_l) ? s_exp[(e + 1) * R] : total;
+    expert_token_nums[e] = nums_type == 1 ? static_cast<int64_t>(end - begin) : static_cast<int64_t>(end);
+  }
+}
+
+// Last index b in [lo, hi) with off[b] <= i (off is non-decreasing on the range, off[lo] <= i).
+__device__ __forceinline__ int last_le(const int32_t* __restrict__ off, int lo, int hi, int i) {
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (off[mid] <= i) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+__global__ void __launch_bounds__(256) exchange_rows_kernel(const uint4* __restrict__ src, const float* __restrict__ src_scales,
+                                                            const int32_t* __restrict__ plan, int R, int E_l,
+                                                            int slot_rows, int direction, int vec_per_row,
+                                                            int64_t dst_rows, int zero_fill, uint4* __restrict__ dst,
+                                                            float* __restrict__ dst_scales) {
+  const int n = R * E_l;
+  const int32_t* wire_off = plan;
+  const int32_t* exp_off = plan + n;
+  const int total = exp_off[n];
+  for (int64_t i = blockIdx.x; i < dst_rows; i += gridDim.x) {
+    int64_t srow = -1;
+    if (direction == 0) {           // dst in expert order
+      if (i < total) {
+        const int b = last_le(exp_off, 0, n, static_cast<int>(i));   // b = e*R + s
+        const int e = b / R, s = b - e * R;
+        srow = wire_off[s * E_l + e] + (i - exp_off[b]);
+      }
+    } else {                        // dst is the wire buffer
+      int lo = 0, hi = n;
+      bool in_range = true;
+      if (slot_rows > 0) {
+        const int s = static_cast<int>(i / slot_rows);
+        in_range = s < R;
+        lo = s * E_l;
+        hi = lo + E_l;
+      } else {
+        in_range = i < total;
+      }
+      if (in_range) {
+        const int b = last_le(wire_off, lo, hi, static_cast<int>(i));  // b = s*E_l + e
+        const int s = b / E_l, e = b - s * E_l;
+        const int eb = e * R + s;
+        const int64_t j = i - wire_off[b];
+        if (j < exp_off[eb + 1] - exp_off[eb]) srow = exp_off[eb] + j;
+      }
+    }
+    uint4* dp = dst + i * vec_per_row;
+    if (srow >= 0) {
+      const uint4* sp = src + srow * vec_per_row;
+      for (int v = threadIdx.x; v < vec_per_row; v += 256) dp[v] = sp[v];
+      if (dst_scales && threadIdx.x == 0) dst_scales[i] = src_scales[srow];
+    } else if (zero_fill) {
+      for (int v = threadIdx.x; v < vec_per_row; v += 256) dp[v] = make_uint4(0, 0, 0, 0);
+      if (dst_scales && threadIdx.x == 0) dst_scales[i] = 0.f;
+    }
+  }
+}
+
+// out[t] = sum_k w[t,k] * rows[idx[t*K+k]] (+ shared[t]); fp32, separate multiply and add, ascending k.
+template <typename T>
+__global__ void __launch_bounds__(256) combine_kernel(const T* __restrict__ rows, const int32_t* __restrict__ expand_idx,
+                                                      const float* __restrict__ weights, const T* __restrict__ shared,
+                                                      int64_t tokens, int K, int cols, T* __restrict__ out) {
+  extern __shared__ int s_meta[];  // [K] positions, [K] weights
+  int* s_pos = s_meta;
+  float* s_w = reinterpret_cast<float*>(s_meta + K);
+  const int nchunk = cols >> 3;
+  for (int64_t t = blockIdx.x; t < tokens; t += gridDim.x) {
+    __syncthreads();
+    for (int k = threadIdx.x; k < K; k += 256) {
+      s_pos[k] = expand_idx[t * K + k];
+      s_w[k] = weights[t * K + k];
+    }
+    __syncthreads();
+    for (int ch = threadIdx.x; ch < nchunk; ch += 256) {
+      float acc[8];
+#pragma unroll 4
+      for (int k = 0; k < K; ++k) {
+        float v[8];
+        Elem<T>::load8(rows + static_cast<int64_t>(s_pos[k]) * cols + ch * 8, v);
+        const float w = s_w[k];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float term = __fmul_rn(w, v[i]);
+          acc[i] = k == 0 ? term : __fadd_rn(acc[i], term);
+        }
+      }
+      if (shared) {
+        float v[8];
+        Elem<T>::load8(shared + t * cols + ch * 8, v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], v[i]);
+      }
+      Elem<T>::store8(out + t * cols + ch * 8, acc);
+    }
+  }
+}
+
+static int elem_size(int dtype) {
+  switch (dtype) {
+    case TAB_BF16: case TAB_F16: return 2;
+    case TAB_F32: case TAB_I32: return 4;
+    case TAB_I8: return 1;
+    default: return 0;
+  }
+}
+
+}  // namespace tab
+
+using namespace tab;
+
+extern "C" int tab_moe_init_routing_workspace_bytes(int64_t T, int64_t K, int64_t expert_bound, size_t* bytes) {
+  if (!bytes || T < 0 || K <= 0 || expert_bound <= 0 || expert_bound > kMaxExperts)
+    return fail(TAB_ERR_BAD_ARG, "init_routing: T=%lld K=%lld expert_bound=%lld (bound must be in [1, %d])", (long long)T, (long long)K, (long long)expert_bound, kMaxExperts);
+  *bytes = sort_scratch_bytes(T * K, expert_bound, false);
+  return TAB_OK;
+}
+
+extern "C" int tab_moe_init_routing(const void* x, int x_dtype, const int32_t* row_idx, const int32_t* expert_idx,
+                                    int64_t T, int64_t K, int64_t H, int64_t active_num, int64_t expert_bound,
+                                    void* expanded_x, int32_t* expanded_row_idx, int32_t* expanded_expert_idx,
+                                    void* workspace, size_t workspace_bytes, tab_stream_t stream) {
+  size_t need = 0;
+  int rc = tab_moe_init_routing_workspace_bytes(T, K, expert_bound, &need);
+  if (rc != TAB_OK) return rc;
+  const int es = elem_size(x_dtype);
+  if (es != 2 && es != 4) return fail(TAB_ERR_UNSUPPORTED, "init_routing: x dtype %d (want 5, 6 or 15)", x_dtype);
+  if (H <= 0 || active_num < 0) return fail(TAB_ERR_BAD_ARG, "init_routing: H=%lld active_num=%lld", (long long)H, (long long)active_num);
+  const int64_t n = T * K;
+  if (n == 0) return TAB_OK;
+  if (n > (1LL << 30)) return fail(TAB_ERR_UNSUPPORTED, "init_routing: T*K too large");
+  if (!x || !row_idx || !expert_idx || !expanded_x || !expanded_row_idx || !expanded_expert_idx || !workspace)
+    return fail(TAB_ERR_BAD_ARG, "init_routing: null pointer");
+  if (workspace_bytes < need) return fail(TAB_ERR_WORKSPACE, "init_routing: workspace %zu < %zu bytes", workspace_bytes, need);
+  if ((H * es) % 16 != 0 || !aligned16(x) || !aligned16(expanded_x) || !aligned16(workspace))
+    return fail(TAB_ERR_ALIGNMENT, "init_routing: rows must be 16-byte multiples and pointers 16-byte aligned");
+  cudaStream_t st = as_stream(stream);
+  SortScratch s = carve(workspace, n, expert_bound, false);
+  rc = run_sort(expert_idx, row_idx, n, expert_bound, s, expanded_expert_idx, expanded_row_idx, nullptr, st);
+  if (rc != TAB_OK) return rc;
+  const int64_t out_rows = (T < active_num ? T : active_num) * K;
+  if (out_rows > 0) {
+    gather_rows_kernel<<<grid_for(out_rows, 8), 256, 0, st>>>(static_cast<const uint4*>(x), s.sorted_src, (int)T, out_rows,
+                                                              (int)(H * es / 16), static_cast<uint4*>(expanded_x));
+    rc = check_launch("init_routing gather");
+  }
+  return rc;
+}
+
+extern "C" int tab_moe_dispatch_pack_workspace_bytes(int64_t T, int64_t K, int64_t num_experts, size_t* bytes) {
+  if (!bytes || T < 0 || K <= 0 || num_experts <= 0 || num_experts > kMaxExperts)
+    return fail(TAB_ERR_BAD_ARG, "dispatch_pack: T=%lld K=%lld experts=%lld (experts must be in [1, %d])", (long long)T, (long long)K, (long long)num_experts, kMaxExperts);
+  *bytes = sort_scratch_bytes(T * K, num_experts, true);
+  return TAB_OK;
+}
+
+extern "C" int tab_moe_dispatch_pack(const void* x, int x_dtype, const int32_t* expert_ids, int64_t T, int64_t K,
+                                     int64_t H, int64_t num_experts, int quant_mode, void* send_rows,
+                                     float* send_scales, int32_t* expand_idx, int32_t* expert_counts,
+                                     void* workspace, size_t workspace_bytes, tab_stream_t stream) {
+  size_t need = 0;
+  int rc = tab_moe_dispatch_pack_workspace_bytes(T, K, num_experts, &need);
+  if (rc != TAB_OK) return rc;
+  if (quant_mode != 0 && quant_mode != 2) return fail(TAB_ERR_UNSUPPORTED, "dispatch_pack: quant_mode %d (want 0 or 2)", quant_mode);
+  const int es = elem_size(x_dtype);
+  if (x_dtype != TAB_BF16 && x_dtype != TAB_F16) return fail(TAB_ERR_UNSUPPORTED, "dispatch_pack: x dtype %d (want 5 or 15)", x_dtype);
+  if (!expert_counts) return fail(TAB_ERR_BAD_ARG, "dispatch_pack: null pointer");
+  cudaStream_t st = as_stream(stream);
+  const int64_t n = T * K;
+  if (n == 0) {
+    cudaError_t e = cudaMemsetAsync(expert_counts, 0, num_experts * sizeof(int32_t), st);
+    return e == cudaSuccess ? TAB_OK : fail(TAB_ERR_CUDA, "dispatch_pack: memset: %s", cudaGetErrorString(e));
+  }
+  if (n > (1LL << 30) || K > 256) return fail(TAB_ERR_UNSUPPORTED, "dispatch_pack: T*K too large or K > 256");
+  if (!x || !expert_ids || !send_rows || !send_scales || !expand_idx || !workspace)
+    return fail(TAB_ERR_BAD_ARG, "dispatch_pack: null pointer");
+  if (workspace_bytes < need) return fail(TAB_ERR_WORKSPACE, "dispatch_pack: workspace %zu < %zu bytes", workspace_bytes, need);
+  if (H <= 0 || H % 16 != 0 || !aligned16(x) || !aligned16(send_rows) || !aligned16(workspace))
+    return fail(TAB_ERR_ALIGNMENT, "dispatch_pack: H=%lld must be a multiple of 16 and pointers 16-byte aligned", (long long)H);
+  (void)es;
+  SortScratch s = carve(workspace, n, num_experts, true);
+  rc = run_sort(expert_ids, nullptr, n, num_experts, s, s.sorted_expert, expand_idx, expert_counts, st);
+  if (rc != TAB_OK) return rc;
+  const int grid = grid_for(T, 8);
+  if (x_dtype == TAB_BF16) {
+    if (quant_mode == 2)
+      dispatch_pack_kernel<__nv_bfloat16, true><<<grid, kPackThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), expand_idx, T, (int)K, (int)H, send_rows, send_scales);
+    else
+      dispatch_pack_kernel<__nv_bfloat16, false><<<grid, kPackThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), expand_idx, T, (int)K, (int)H, send_rows, send_scales);
+  } else {
+    if (quant_mode == 2)
+      dispatch_pack_kernel<__half, true><<<grid, kPackThreads, 0, st>>>(static_cast<const __half*>(x), expand_idx, T, (int)K, (int)H, send_rows, send_scales);
+    else
+      dispatch_pack_kernel<__half, false><<<grid, kPackThreads, 0, st>>>(static_cast<const __half*>(x), expand_idx, T, (int)K, (int)H, send_rows, send_scales);
+  }
+  return check_launch("dispatch_pack");
+}
+
+extern "C" int tab_moe_exchange_plan(const int32_t* recv_counts, int64_t R, int64_t E_l, int64_t slot_rows,
+                                     int nums_type, int32_t* plan, int64_t* expert_token_nums,
+                                     int32_t* ep_recv_count, tab_stream_t stream) {
+  if (!recv_counts || !plan || !expert_token_nums || !ep_recv_count) return fail(TAB_ERR_BAD_ARG, "exchange_plan: null pointer");
+  if (R <= 0 || E_l <= 0 || R * E_l > kMaxExperts || slot_rows < 0 || slot_rows > (1LL << 30))
+    return fail(TAB_ERR_BAD_ARG, "exchange_plan: R=%lld E_l=%lld (R*E_l must be in [1, %d])", (long long)R, (long long)E_l, kMaxExperts);
+  if (nums_type != 0 && nums_type != 1) return fail(TAB_ERR_BAD_ARG, "exchange_plan: nums_type %d", nums_type);
+  exchange_plan_kernel<<<1, 1024, 0, as_stream(stream)>>>(recv_counts, (int)R, (int)E_l, (int)slot_rows, nums_type, plan,
+                                                         expert_token_nums, ep_recv_count);
+  return check_launch("exchange_plan");
+}
+
+extern "C" int tab_moe_exchange_rows(const void* src, const float* src_scales, const int32_t* plan, int64_t R,
+                                     int64_t E_l, int64_t slot_rows, int direction, int64_t row_bytes,
+                                     int64_t dst_rows, int zero_fill, void* dst, float* dst_scales,
+                                     tab_stream_t stream) {
+  if (dst_rows == 0) return TAB_OK;
+  if (!src || !plan || !dst) return fail(TAB_ERR_BAD_ARG, "exchange_rows: null pointer");
+  if (R <= 0 || E_l <= 0 || R * E_l > kMaxExperts || dst_rows < 0 || dst_rows > (1LL << 30) || (direction != 0 && direction != 1))
+    return fail(TAB_ERR_BAD_ARG, "exchange_rows: bad R/E_l/rows/direction");
+  if ((dst_scales != nullptr) != (src_scales != nullptr)) return fail(TAB_ERR_BAD_ARG, "exchange_rows: scales must be given on both sides or neither");
+  if (row_bytes <= 0 || row_bytes % 16 != 0 || !aligned16(src) || !aligned16(dst))
+    return fail(TAB_ERR_ALIGNMENT, "exchange_rows: row_bytes=%lld must be a multiple of 16 and pointers 16-byte aligned", (long long)row_bytes);
+  exchange_rows_kernel<<<grid_for(dst_rows, 8), 256, 0, as_stream(stream)>>>(
+      static_cast<const uint4*>(src), src_scales, plan, (int)R, (int)E_l, (int)slot_rows, direction, (int)(row_bytes / 16),
+      dst_rows, zero_fill, static_cast<uint4*>(dst), dst_scales);
+  return check_launch("exchange_rows");
+}
+
+extern "C" int tab_moe_combine(const void* rows, int dtype, const int32_t* expand_idx, const float* expert_scales,
+                               const void* shared, int64_t T, int64_t K, int64_t H, void* out, tab_stream_t stream) {
+  if (T < 0 || K <= 0 || K > 1024 || H <= 0) return fail(TAB_ERR_BAD_ARG, "combine: T=%lld K=%lld H=%lld", (long long)T, (long long)K, (long long)H);
+  if (T == 0) return TAB_OK;
+  if (!rows || !expand_idx || !expert_scales || !out) return fail(TAB_ERR_BAD_ARG, "combine: null pointer");
+  if (H % 8 != 0 || !aligned16(rows) || !aligned16(out) || (shared && !aligned16(shared)))
+    return fail(TAB_ERR_ALIGNMENT, "combine: H=%lld must be a multiple of 8 and pointers 16-byte aligned", (long long)H);
+  cudaStream_t st = as_stream(stream);
+  const int grid = grid_for(T, 8);
+  const size_t smem = static_cast<size_t>(K) * 8;
+  if (dtype == TAB_BF16)
+    combine_kernel<__nv_bfloat16><<<grid, 256, smem, st>>>(static_cast<const __nv_bfloat16*>(rows), expand_idx, expert_scales, static_cast<const __nv_bfloat16*>(shared), T, (int)K, (int)H, static_cast<__nv_bfloat16*>(out));
+  else if (dtype == TAB_F16)
+    combine_kernel<__half><<<grid, 256, smem, st>>>(static_cast<const __half*>(rows), expand_idx, expert_scales, static_cast<const __half*>(shared), T, (int)K, (int)H, static_cast<__half*>(out));
+  else
+    return fail(TAB_ERR_UNSUPPORTED, "combine: dtype %d (want 5 or 15)", dtype);
+  return check_launch("combine");
+}

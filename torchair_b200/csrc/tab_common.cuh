@@ -1,0 +1,124 @@
+// Shared host/device helpers for the torchair-b200 kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/tab_api.h"
+
+namespace tab {
+
+// Records a formatted message for tab_last_error() and returns `code`.
+int fail(int code, const char* fmt, ...);
+
+inline cudaStream_t as_stream(tab_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
+
+// Reports a failed launch (bad configuration and the like) without synchronising.
+int check_launch(const char* what);
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs
+
+// Grid size for a grid-stride kernel: enough CTAs to fill the machine `waves` times, never more than the work.
+inline int grid_for(int64_t work_items, int ctas_per_sm) {
+  int64_t cap = static_cast<int64_t>(kNumSMs) * ctas_per_sm;
+  int64_t g = work_items < cap ? work_items : cap;
+  return static_cast<int>(g < 1 ? 1 : g);
+}
+
+// ---- element loads: 8 consecutive elements (16 bytes of 16-bit data, 32 bytes of fp32) as fp32 ----
+template <typename T>
+struct Elem;
+
+template <>
+struct Elem<__nv_bfloat16> {
+  static __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
+    uint4 r = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 f = __bfloat1622float2(h[i]);
+      v[2 * i] = f.x;
+      v[2 * i + 1] = f.y;
+    }
+  }
+  static __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
+    uint4 r;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = r;
+  }
+  static __device__ __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f32(float x) { return __float2bfloat16_rn(x); }
+};
+
+template <>
+struct Elem<__half> {
+  static __device__ __forceinline__ void load8(const __half* p, float (&v)[8]) {
+    uint4 r = *reinterpret_cast<const uint4*>(p);
+    const __half2* h = reinterpret_cast<const __half2*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 f = __half22float2(h[i]);
+      v[2 * i] = f.x;
+      v[2 * i + 1] = f.y;
+    }
+  }
+  static __device__ __forceinline__ void store8(__half* p, const float (&v)[8]) {
+    uint4 r;
+    __half2* h = reinterpret_cast<__half2*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = r;
+  }
+  static __device__ __forceinline__ float to_f32(__half x) { return __half2float(x); }
+  static __device__ __forceinline__ __half from_f32(float x) { return __float2half_rn(x); }
+};
+
+template <>
+struct Elem<float> {
+  static __device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+    float4 a = *reinterpret_cast<const float4*>(p);
+    float4 b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+  static __device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  }
+  static __device__ __forceinline__ float to_f32(float x) { return x; }
+  static __device__ __forceinline__ float from_f32(float x) { return x; }
+};
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Symmetric int8 quantisation of one value given its row scale: IEEE division, round-half-even,
+// clamp to +-127.  scale == 0 (all-zero row) gives 0.
+__device__ __forceinline__ int quant_i8(float v, float scale) {
+  if (!(scale > 0.f)) return 0;
+  int q = __float2int_rn(__fdiv_rn(v, scale));
+  return max(-127, min(127, q));
+}
+
+__device__ __forceinline__ uint32_t pack4_i8(int a, int b, int c, int d) {
+  return (static_cast<uint32_t>(a) & 0xffu) | ((static_cast<uint32_t>(b) & 0xffu) << 8) |
+         ((static_cast<uint32_t>(c) & 0xffu) << 16) | ((static_cast<uint32_t>(d) & 0xffu) << 24);
+}
+
+// silu(a) * b with separately rounded fp32 operations: a / (1 + exp(-a)) * b.
+__device__ __forceinline__ float silu_mul(float a, float b) {
+  float s = __fdiv_rn(a, __fadd_rn(1.0f, expf(-a)));
+  return __fmul_rn(s, b);
+}
+
+}  // namespace tab

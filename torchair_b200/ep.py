@@ -1,0 +1,250 @@
+"""Expert-parallel dispatch / combine: host logic around the pack, permute and reduce kernels.
+
+Experts are sharded in contiguous blocks (expert e lives on rank e // (E / R)); tokens stay data-parallel.
+One exchange each way: dispatch sends int8 rows plus fp32 scales to the experts' owners, combine sends the
+bf16 expert outputs back (reference converters moe_distribute_dispatch.py:4-45 and
+moe_distribute_combine.py:4-60 under python/torchair/_ge_concrete_graph/ge_converter/custom).  The
+collectives are torch.distributed all_to_all_single calls (NCCL over NVLink on GPUs); with one rank there is
+no collective at all.
+
+The device work is reached through a small "kernels" provider so that the same host logic can be driven by
+CPU stand-ins in multi-process gloo tests; the shipped provider is CudaKernels and nothing else is ever
+selected implicitly.
+
+`group_ep` is a string in the reference (an HCCL communicator name from get_hccl_comm_name,
+python/torchair/_ge_concrete_graph/hcom_utils.py:13-15).  Here it names a process group registered with
+register_ep_group().
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+
+_ST_INV = {torch.int8: 1, torch.int32: 3, torch.float16: 5, torch.float32: 6, torch.bfloat16: 15}
+
+_groups: Dict[str, object] = {}
+# host-side split sizes remembered between a dispatch and its combine, keyed by the handshake tensors
+_splits: Dict[Tuple[int, int], Tuple[List[int], List[int]]] = {}
+_SPLITS_MAX = 64
+
+counters = {"dispatch_calls": 0, "combine_calls": 0, "wire_bytes_sent": 0}
+
+
+def register_ep_group(name: str, process_group) -> None:
+    """Associates a group_ep name with a torch.distributed process group."""
+    if not isinstance(name, str) or not name:
+        raise ValueError("group name must be a non-empty string")
+    _groups[name] = process_group
+
+
+def get_ep_group(name: str):
+    if name in _groups:
+        return _groups[name]
+    raise RuntimeError(f"expert-parallel group {name!r} is not registered; call "
+                       "torchair_b200.register_ep_group(name, process_group) first")
+
+
+def dispatch_rows(T: int, R: int, E: int, K: int) -> int:
+    """Static row count of expand_x (global_bs == 0): every rank may send min(E/R, K) copies of each token."""
+    return T * R * min(E // R, K)
+
+
+def check_dispatch_args(x, expert_ids, R, rank, E, scales, x_active_mask, tp_world_size, expert_shard_type,
+                        shared_expert_rank_num, quant_mode, global_bs, nums_type):
+    op = "npu_moe_distribute_dispatch"
+    if x.dim() != 2 or expert_ids.dim() != 2 or x.shape[0] != expert_ids.shape[0]:
+        raise RuntimeError(f"{op}: x must be [T, H] and expert_ids [T, K]")
+    if R < 1 or E < 1 or E % R != 0 or not (0 <= rank < R):
+        raise RuntimeError(f"{op}: ep_world_size={R}, ep_rank_id={rank}, moe_expert_num={E} are inconsistent")
+    if scales is not None or x_active_mask is not None:
+        raise NotImplementedError(f"{op}: `scales` and `x_active_mask` are outside the W8A8 MoE path")
+    if tp_world_size not in (0, 1):
+        raise NotImplementedError(f"{op}: tensor parallelism inside an expert (tp_world_size={tp_world_size}) is not sharded here")
+    if expert_shard_type != 0 or shared_expert_rank_num != 0:
+        raise NotImplementedError(f"{op}: shared-expert ranks / expert_shard_type != 0 are not sharded here")
+    if quant_mode not in (0, 2):
+        raise NotImplementedError(f"{op}: quant_mode must be 0 (none) or 2 (per-token dynamic int8)")
+    if global_bs != 0:
+        raise NotImplementedError(f"{op}: global_bs must be 0 (every rank holds the same number of tokens)")
+    if nums_type not in (0, 1):
+        raise RuntimeError(f"{op}: expert_token_nums_type must be 0 (cumsum) or 1 (counts)")
+
+
+def check_combine_args(expand_x, expert_ids, expert_scales, R, rank, E, x_active_mask, activation_scale, weight_scale,
+                       group_list, tp_world_size, expert_shard_type, shared_expert_rank_num, global_bs, out_dtype,
+                       comm_quant_mode):
+    op = "npu_moe_distribute_combine"
+    if expand_x.dim() != 2 or expert_ids.dim() != 2 or expert_scales.shape != expert_ids.shape:
+        raise RuntimeError(f"{op}: expand_x must be [A, H]; expert_ids and expert_scales [T, K]")
+    if R < 1 or E < 1 or E % R != 0 or not (0 <= rank < R):
+        raise RuntimeError(f"{op}: ep_world_size={R}, ep_rank_id={rank}, moe_expert_num={E} are inconsistent")
+    if x_active_mask is not None or activation_scale is not None or weight_scale is not None or group_list is not None:
+        raise NotImplementedError(f"{op}: x_active_mask / dequant-in-combine arguments are outside the W8A8 MoE path")
+    if tp_world_size not in (0, 1) or expert_shard_type != 0 or shared_expert_rank_num != 0:
+        raise NotImplementedError(f"{op}: tensor-parallel / shared-expert-rank sharding is not supported")
+    if global_bs != 0 or comm_quant_mode != 0 or out_dtype != 0:
+        raise NotImplementedError(f"{op}: global_bs, comm_quant_mode and out_dtype must be 0")
+
+
+def _ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream(t):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+class CudaKernels:
+    """The shipped provider: every step is one or more sm_100a kernels behind the C ABI."""
+
+    @staticmethod
+    def dispatch_pack(x, expert_ids, E, quant_mode):
+        if not x.is_cuda:
+            raise RuntimeError("torchair_b200 kernels need CUDA tensors; there is no CPU implementation")
+        if expert_ids.dtype != torch.int32:
+            raise RuntimeError("npu_moe_distribute_dispatch: expert_ids must be int32")
+        if x.dtype not in (torch.bfloat16, torch.float16):
+            raise NotImplementedError("npu_moe_distribute_dispatch: x must be bfloat16 or float16")
+        x, expert_ids = x.contiguous(), expert_ids.contiguous()
+        T, K = expert_ids.shape
+        H = x.shape[1]
+        dev = x.device
+        rows = torch.empty((T * K, H), dtype=torch.int8 if quant_mode == 2 else x.dtype, device=dev)
+        scales = torch.empty((T * K,), dtype=torch.float32, device=dev)
+        expand_idx = torch.empty((T * K,), dtype=torch.int32, device=dev)
+        counts = torch.empty((E,), dtype=torch.int32, device=dev)
+        nbytes = _lib.workspace_bytes("tab_moe_dispatch_pack_workspace_bytes", T, K, E)
+        ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=dev)
+        _lib.call("tab_moe_dispatch_pack", _ptr(x), _ST_INV[x.dtype], _ptr(expert_ids), T, K, H, E, quant_mode, _ptr(rows),
+                  _ptr(scales), _ptr(expand_idx), _ptr(counts), _ptr(ws), ws.numel(), _stream(x))
+        return rows, scales, expand_idx, counts
+
+    @staticmethod
+    def exchange_plan(recv_counts, R, E_l, slot_rows, nums_type):
+        dev = recv_counts.device
+        plan = torch.empty((2 * R * E_l + 1,), dtype=torch.int32, device=dev)
+        nums = torch.empty((E_l,), dtype=torch.int64, device=dev)
+        ep_recv = torch.empty((E_l * R,), dtype=torch.int32, device=dev)
+        _lib.call("tab_moe_exchange_plan", _ptr(recv_counts.contiguous()), R, E_l, slot_rows, nums_type, _ptr(plan), _ptr(nums),
+                  _ptr(ep_recv), _stream(recv_counts))
+        return plan, nums, ep_recv
+
+    @staticmethod
+    def exchange_rows(src, src_scales, plan, R, E_l, slot_rows, direction, dst_rows, zero_fill):
+        dst = torch.empty((dst_rows, src.shape[1]), dtype=src.dtype, device=src.device)
+        dst_scales = None if src_scales is None else torch.empty((dst_rows,), dtype=torch.float32, device=src.device)
+        if src.shape[0] == 0:  # nothing arrived: the kernel would have no source pointer to read
+            dst.zero_()
+            if dst_scales is not None:
+                dst_scales.zero_()
+            return dst, dst_scales
+        _lib.call("tab_moe_exchange_rows", _ptr(src), _ptr(src_scales), _ptr(plan), R, E_l, slot_rows, direction,
+                  src.shape[1] * src.element_size(), dst_rows, int(zero_fill), _ptr(dst), _ptr(dst_scales), _stream(src))
+        return dst, dst_scales
+
+    @staticmethod
+    def combine(rows, expand_idx, expert_scales, shared, T, K):
+        if rows.dtype not in (torch.bfloat16, torch.float16):
+            raise NotImplementedError("npu_moe_distribute_combine: expand_x must be bfloat16 or float16")
+        rows = rows.contiguous()
+        out = torch.empty((T, rows.shape[1]), dtype=rows.dtype, device=rows.device)
+        if expand_idx.dtype != torch.int32 or expert_scales.dtype != torch.float32:
+            raise RuntimeError("npu_moe_distribute_combine: expand_idx must be int32 and expert_scales float32")
+        if shared is not None:
+            if shared.dtype != rows.dtype or shared.shape != out.shape:
+                raise RuntimeError("npu_moe_distribute_combine: shared_expert_x must match the output")
+            shared = shared.contiguous()
+        _lib.call("tab_moe_combine", _ptr(rows), _ST_INV[rows.dtype], _ptr(expand_idx.contiguous()),
+                  _ptr(expert_scales.contiguous()), _ptr(shared), T, K, rows.shape[1], _ptr(out), _stream(rows))
+        return out
+
+
+def _remember(key, value):
+    if len(_splits) >= _SPLITS_MAX:
+        _splits.pop(next(iter(_splits)))
+    _splits[key] = value
+
+
+def dispatch(kern, x, expert_ids, group_ep, R, rank, E, quant_mode, nums_type, tp_slots=1):
+    """Returns the seven outputs of npu_moe_distribute_dispatch.
+
+    Handshake tensors (consumed only by combine): expand_idx[t*K+k] = position of that copy in this rank's
+    send order (sorted by global expert id, stable); ep_recv_count[e*R+s] = rows received for local expert e
+    from rank s; tp_recv_count and expand_scales are zero.
+    """
+    counters["dispatch_calls"] += 1
+    T, K = expert_ids.shape
+    H = x.shape[1]
+    E_l = E // R
+    A = dispatch_rows(T, R, E, K)
+    dev = x.device
+    send_rows, send_scales, expand_idx, counts = kern.dispatch_pack(x, expert_ids, E, quant_mode)
+    tp_recv = torch.zeros((tp_slots,), dtype=torch.int32, device=dev)
+    expand_scales = torch.zeros((A,), dtype=torch.float32, device=dev)
+    if R == 1:
+        nums = counts.to(torch.int64)
+        if nums_type == 0:
+            nums = torch.cumsum(nums, 0)
+        if A != T * K:  # K > E: cannot happen with distinct experts per token, kept for shape safety
+            pad_rows = torch.zeros((A, H), dtype=send_rows.dtype, device=dev)
+            pad_rows[:T * K] = send_rows
+            pad_scales = torch.zeros((A,), dtype=torch.float32, device=dev)
+            pad_scales[:T * K] = send_scales
+            send_rows, send_scales = pad_rows, pad_scales
+        return send_rows, send_scales, expand_idx, nums, counts, tp_recv, expand_scales
+
+    pg = get_ep_group(group_ep)
+    if dist.get_world_size(pg) != R or dist.get_rank(pg) != rank:
+        raise RuntimeError(f"npu_moe_distribute_dispatch: group {group_ep!r} has size/rank "
+                           f"{dist.get_world_size(pg)}/{dist.get_rank(pg)}, arguments say {R}/{rank}")
+    recv_counts = torch.empty_like(counts)                       # [R, E_l]: rows from rank s for my expert e
+    dist.all_to_all_single(recv_counts, counts, group=pg)
+    sums = torch.stack([counts.view(R, E_l).sum(1), recv_counts.view(R, E_l).sum(1)]).cpu()   # the one host read
+    send_splits = [int(v) for v in sums[0]]
+    recv_splits = [int(v) for v in sums[1]]
+    total = sum(recv_splits)
+    if total > A:
+        raise RuntimeError(f"npu_moe_distribute_dispatch: received {total} rows but expand_x holds {A}; "
+                           "every rank must pass the same number of tokens when global_bs == 0")
+    wire_rows = torch.empty((total, H), dtype=send_rows.dtype, device=dev)
+    wire_scales = torch.empty((total,), dtype=torch.float32, device=dev)
+    dist.all_to_all_single(wire_rows, send_rows, recv_splits, send_splits, group=pg)
+    dist.all_to_all_single(wire_scales, send_scales, recv_splits, send_splits, group=pg)
+    counters["wire_bytes_sent"] += (sum(send_splits) - send_splits[rank]) * (H * send_rows.element_size() + 4)
+    plan, nums, ep_recv = kern.exchange_plan(recv_counts.view(R, E_l), R, E_l, 0, nums_type)
+    expand_x, dyn_scales = kern.exchange_rows(wire_rows, wire_scales, plan, R, E_l, 0, 0, A, True)
+    _remember((ep_recv.data_ptr(), expand_idx.data_ptr()), (send_splits, recv_splits))
+    return expand_x, dyn_scales, expand_idx, nums, ep_recv, tp_recv, expand_scales
+
+
+def combine(kern, expand_x, expert_ids, expand_idx, ep_send_counts, expert_scales, group_ep, R, rank, E, shared=None):
+    """out[t] = sum_k expert_scales[t,k] * (expert output of copy (t,k)), after returning rows to their senders."""
+    counters["combine_calls"] += 1
+    T, K = expert_ids.shape
+    H = expand_x.shape[1]
+    if R == 1:
+        return kern.combine(expand_x, expand_idx, expert_scales, shared, T, K)
+    pg = get_ep_group(group_ep)
+    E_l = E // R
+    remembered = _splits.get((ep_send_counts.data_ptr(), expand_idx.data_ptr()))
+    if remembered is not None:
+        send_splits, recv_splits = remembered
+    else:  # handshake tensors were copied: rebuild the split sizes (one host read)
+        got = ep_send_counts.view(E_l, R).sum(0)
+        sent = torch.bincount((expert_ids.reshape(-1) // E_l).to(torch.int64), minlength=R).to(got.dtype)
+        sums = torch.stack([sent, got]).cpu()
+        send_splits = [int(v) for v in sums[0]]
+        recv_splits = [int(v) for v in sums[1]]
+    recv_counts = ep_send_counts.view(E_l, R).t().contiguous()
+    plan, _, _ = kern.exchange_plan(recv_counts, R, E_l, 0, 1)
+    total = sum(recv_splits)
+    wire, _ = kern.exchange_rows(expand_x.contiguous(), None, plan, R, E_l, 0, 1, total, False)
+    back = torch.empty((T * K, H), dtype=expand_x.dtype, device=expand_x.device)
+    dist.all_to_all_single(back, wire, send_splits, recv_splits, group=pg)
+    counters["wire_bytes_sent"] += (total - recv_splits[rank]) * H * expand_x.element_size()
+    return kern.combine(back, expand_idx, expert_scales, shared, T, K)

@@ -1,0 +1,37 @@
+"""The quantised expert-parallel MoE layer as a composition of torch.ops.npu.* calls.
+
+This is the op sequence that serving stacks built on the reference emit for a W8A8 MoE feed-forward block
+(each op is one converter under python/torchair/_ge_concrete_graph/ge_converter/custom): dispatch with per-token
+int8 quantisation -> gate_up grouped matmul -> dequant + SwiGLU + requant -> down grouped matmul -> combine.
+With ep_world_size == 1 no collective runs.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import ops  # noqa: F401  (registers torch.ops.npu.*)
+
+
+def moe_layer(x, expert_ids, expert_scales, w1, s1, w2, s2, *, group_ep: str = "", ep_world_size: int = 1,
+              ep_rank_id: int = 0, moe_expert_num: int = None, fused: bool = True):
+    """x [T, H] bf16; expert_ids int32 [T, K]; expert_scales fp32 [T, K]; w1 int8 [E_l, H, 2I]; s1 fp32 [E_l, 2I];
+    w2 int8 [E_l, I, H]; s2 fp32 [E_l, H] (this rank's experts).  Returns [T, H] bf16.
+
+    fused=True issues gate_up + SwiGLU + requant as npu_grouped_matmul_swiglu_quant_v2; fused=False issues the
+    int32 grouped matmul and npu_dequant_swiglu_quant separately (what the FX fusion pass rewrites).
+    """
+    npu = torch.ops.npu
+    R = ep_world_size
+    E = moe_expert_num if moe_expert_num is not None else w1.shape[0] * R
+    ex, xs, expand_idx, nums, ep_recv, _tp, _es = npu.npu_moe_distribute_dispatch(
+        x, expert_ids, group_ep, R, ep_rank_id, E, quant_mode=2, expert_token_nums_type=1)
+    if fused:
+        hq, hs = npu.npu_grouped_matmul_swiglu_quant_v2(ex, [w1], [s1], xs, nums, group_list_type=1)
+    else:
+        h32 = npu.npu_grouped_matmul([ex], [w1], group_list=nums, split_item=2, group_type=0, group_list_type=1,
+                                     output_dtype=3)[0]
+        hq, hs = npu.npu_dequant_swiglu_quant(h32, weight_scale=s1, activation_scale=xs, group_index=nums,
+                                              activate_left=True, quant_mode=1)
+    y = npu.npu_grouped_matmul([hq], [w2], scale=[s2], per_token_scale=[hs], group_list=nums, split_item=2,
+                               group_type=0, group_list_type=1, output_dtype=15)[0]
+    return npu.npu_moe_distribute_combine(y, expert_ids, expand_idx, ep_recv, expert_scales, group_ep, R, ep_rank_id, E)

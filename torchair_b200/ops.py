@@ -1,0 +1,480 @@
+"""torch.ops.npu.* operators of the W8A8 MoE path, registered with torch.library and backed by the C ABI.
+
+Schemas keep the names, argument order, keyword names and defaults that the reference's converters bind to
+(python/torchair/_ge_concrete_graph/ge_converter/custom/{moe_init_routing, npu_dynamic_quant, npu_swiglu,
+npu_dequant_swiglu_quant, grouped_matmul, moe_distribute_dispatch, moe_distribute_combine,
+grouped_matmul_swiglu_quant_v2}.py).  "Meta" implementations carry the shape rules; "CUDA" implementations
+launch the sm_100a kernels on the current stream.  There is deliberately no CPU implementation: calling an
+op on CPU tensors raises from the dispatcher, and argument combinations outside the path raise
+NotImplementedError instead of falling back.
+"""
+from __future__ import annotations
+
+import ctypes
+import weakref
+from typing import List, Optional
+
+import torch
+from torch.library import Library
+
+from . import _lib, ep
+
+# c10::ScalarType integers used for dtype arguments (python/torchair/ge/_ge_graph.py:215-270).
+_ST = {1: torch.int8, 3: torch.int32, 5: torch.float16, 6: torch.float32, 15: torch.bfloat16}
+_ST_INV = {v: k for k, v in _ST.items()}
+
+# npu_moe_init_routing has no expert-count argument; ids must lie below this bound (bins of the counting sort).
+INIT_ROUTING_EXPERT_BOUND = 1024
+
+_npu = Library("npu", "FRAGMENT")
+
+_npu.define("npu_moe_init_routing(Tensor x, Tensor row_idx, Tensor expert_idx, int active_num) -> (Tensor, Tensor, Tensor)")
+_npu.define("npu_dynamic_quant(Tensor input, *, Tensor? smooth_scales=None, Tensor? group_index=None, int? dst_type=None, "
+            "str quant_mode=\"pertoken\", float dst_type_max=0.0) -> (Tensor, Tensor)")
+_npu.define("npu_dynamic_quant_asymmetric(Tensor input, *, Tensor? smooth_scales=None, Tensor? group_index=None, "
+            "int? dst_type=None, str quant_mode=\"pertoken\", float dst_type_max=0.0) -> (Tensor, Tensor, Tensor)")
+_npu.define("npu_swiglu(Tensor self, int dim=-1) -> Tensor")
+_npu.define("npu_dequant_swiglu_quant(Tensor x, *, Tensor? weight_scale=None, Tensor? activation_scale=None, "
+            "Tensor? bias=None, Tensor? quant_scale=None, Tensor? quant_offset=None, Tensor? group_index=None, "
+            "bool activate_left=False, int quant_mode=0, int? dst_type=None, int? round_mode=None, "
+            "int? activate_dim=None, int swiglu_mode=0, float clamp_limit=7.0, float glu_alpha=1.702, "
+            "float glu_bias=1.0) -> (Tensor, Tensor)")
+_GMM_TAIL = ("Tensor[]? activation_input=None, Tensor[]? activation_quant_scale=None, "
+             "Tensor[]? activation_quant_offset=None, int? split_item=0, int? group_type=-1, int? group_list_type=0, "
+             "int? act_type=0, int[]? tuning_config=None, int? output_dtype=None, int? x_dtype=None, "
+             "int? weight_dtype=None, int? scale_dtype=None, int? per_token_scale_dtype=None) -> Tensor[]")
+_GMM_HEAD = ("(Tensor[] x, Tensor[] weight, *, Tensor[]? bias=None, Tensor[]? scale=None, Tensor[]? offset=None, "
+             "Tensor[]? antiquant_scale=None, Tensor[]? antiquant_offset=None, Tensor[]? per_token_scale=None, ")
+_npu.define("npu_grouped_matmul" + _GMM_HEAD + "Tensor? group_list=None, " + _GMM_TAIL)
+_npu.define("npu_grouped_matmul.List" + _GMM_HEAD + "int[]? group_list=None, " + _GMM_TAIL)
+_npu.define("npu_grouped_matmul_swiglu_quant_v2(Tensor x, Tensor[] weight, Tensor[] weight_scale, Tensor x_scale, "
+            "Tensor group_list, *, Tensor? smooth_scale=None, Tensor[]? weight_assist_matrix=None, Tensor? bias=None, "
+            "int? dequant_mode=0, int? dequant_dtype=0, int? quant_mode=0, int? quant_dtype=1, int? group_list_type=0, "
+            "int[]? tuning_config=None, int? x_dtype=None, int? weight_dtype=None, int? weight_scale_dtype=None, "
+            "int? x_scale_dtype=None) -> (Tensor, Tensor)")
+_npu.define("npu_moe_distribute_dispatch(Tensor x, Tensor expert_ids, str group_ep, int ep_world_size, int ep_rank_id, "
+            "int moe_expert_num, *, Tensor? scales=None, Tensor? x_active_mask=None, Tensor? expert_scales=None, "
+            "str group_tp=\"\", int tp_world_size=0, int tp_rank_id=0, int expert_shard_type=0, int shared_expert_num=1, "
+            "int shared_expert_rank_num=0, int quant_mode=0, int global_bs=0, int expert_token_nums_type=1) "
+            "-> (Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor)")
+_npu.define("npu_moe_distribute_combine(Tensor expand_x, Tensor expert_ids, Tensor expand_idx, Tensor ep_send_counts, "
+            "Tensor expert_scales, str group_ep, int ep_world_size, int ep_rank_id, int moe_expert_num, *, "
+            "Tensor? tp_send_counts=None, Tensor? x_active_mask=None, Tensor? activation_scale=None, "
+            "Tensor? weight_scale=None, Tensor? group_list=None, Tensor? expand_scales=None, Tensor? shared_expert_x=None, "
+            "str group_tp=\"\", int tp_world_size=0, int tp_rank_id=0, int expert_shard_type=0, int shared_expert_num=1, "
+            "int shared_expert_rank_num=0, int global_bs=0, int out_dtype=0, int comm_quant_mode=0, "
+            "int group_list_type=0) -> Tensor")
+
+
+# --------------------------------------------------------------------------------------------------
+# helpers
+# --------------------------------------------------------------------------------------------------
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream(t: torch.Tensor):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _st(dtype: torch.dtype, what: str) -> int:
+    if dtype not in _ST_INV:
+        raise NotImplementedError(f"{what}: dtype {dtype} is outside the W8A8 MoE path")
+    return _ST_INV[dtype]
+
+
+def _workspace(nbytes: int, device) -> torch.Tensor:
+    return torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
+
+
+def _only_none(op: str, **kwargs):
+    for k, v in kwargs.items():
+        if v is not None:
+            raise NotImplementedError(f"{op}: argument `{k}` is outside the W8A8 MoE path and must be None")
+
+
+def _only_default(op: str, **pairs):
+    for k, (v, d) in pairs.items():
+        if v != d:
+            raise NotImplementedError(f"{op}: `{k}`={v!r} is outside the W8A8 MoE path (supported: {d!r})")
+
+
+# --------------------------------------------------------------------------------------------------
+# npu_moe_init_routing
+# --------------------------------------------------------------------------------------------------
+def _init_routing_meta(x, row_idx, expert_idx, active_num):
+    if x.dim() != 2 or expert_idx.dim() != 2 or row_idx.shape != expert_idx.shape:
+        raise RuntimeError("npu_moe_init_routing: x must be [T, H]; row_idx and expert_idx [T, K]")
+    T, K = expert_idx.shape
+    rows = min(T, active_num) * K
+    return (x.new_empty((rows, x.shape[1])), expert_idx.new_empty((T * K,)), expert_idx.new_empty((T * K,)))
+
+
+def _init_routing_cuda(x, row_idx, expert_idx, active_num):
+    ex, eri, eei = _init_routing_meta(x, row_idx, expert_idx, active_num)
+    if row_idx.dtype != torch.int32 or expert_idx.dtype != torch.int32:
+        raise RuntimeError("npu_moe_init_routing: row_idx and expert_idx must be int32")
+    T, K = expert_idx.shape
+    x, row_idx, expert_idx = x.contiguous(), row_idx.contiguous(), expert_idx.contiguous()
+    ws = _workspace(_lib.workspace_bytes("tab_moe_init_routing_workspace_bytes", T, K, INIT_ROUTING_EXPERT_BOUND), x.device)
+    _lib.call("tab_moe_init_routing", _ptr(x), _st(x.dtype, "npu_moe_init_routing"), _ptr(row_idx), _ptr(expert_idx),
+              T, K, x.shape[1], active_num, INIT_ROUTING_EXPERT_BOUND, _ptr(ex), _ptr(eri), _ptr(eei), _ptr(ws),
+              ws.numel(), _stream(x))
+    return ex, eri, eei
+
+
+# --------------------------------------------------------------------------------------------------
+# npu_dynamic_quant
+# --------------------------------------------------------------------------------------------------
+def _dynamic_quant_check(op, group_index, dst_type, quant_mode, dst_type_max):
+    _only_none(op, group_index=group_index)
+    if dst_type not in (None, 1):
+        raise NotImplementedError(f"{op}: dst_type={dst_type} (only 1 = int8 is on the path)")
+    _only_default(op, quant_mode=(quant_mode, "pertoken"), dst_type_max=(dst_type_max, 0.0))
+
+
+def _dynamic_quant_meta(input, *, smooth_scales=None, group_index=None, dst_type=None, quant_mode="pertoken", dst_type_max=0.0):
+    _dynamic_quant_check("npu_dynamic_quant", group_index, dst_type, quant_mode, dst_type_max)
+    if input.dim() < 1:
+        raise RuntimeError("npu_dynamic_quant: input must have at least one dimension")
+    return (torch.empty(input.shape, dtype=torch.int8, device=input.device),
+            torch.empty(input.shape[:-1], dtype=torch.float32, device=input.device))
+
+
+def _dynamic_quant_cuda(input, *, smooth_scales=None, group_index=None, dst_type=None, quant_mode="pertoken", dst_type_max=0.0):
+    y, scale = _dynamic_quant_meta(input, smooth_scales=smooth_scales, group_index=group_index, dst_type=dst_type,
+                                   quant_mode=quant_mode, dst_type_max=dst_type_max)
+    x = input.contiguous()
+    cols = x.shape[-1]
+    rows = x.numel() // cols if cols else 0
+    if smooth_scales is not None:
+        if smooth_scales.dtype != x.dtype or smooth_scales.numel() != cols:
+            raise RuntimeError("npu_dynamic_quant: smooth_scales must be [H] of the input dtype")
+        smooth_scales = smooth_scales.contiguous()
+    _lib.call("tab_dynamic_quant", _ptr(x), _st(x.dtype, "npu_dynamic_quant"), _ptr(smooth_scales), rows, cols,
+              _ptr(y), _ptr(scale), _stream(x))
+    return y, scale
+
+
+def _dynamic_quant_asym(input, *, smooth_scales=None, group_index=None, dst_type=None, quant_mode="pertoken", dst_type_max=0.0):
+    raise NotImplementedError("npu_dynamic_quant_asymmetric is outside the W8A8 MoE path (symmetric per-token int8 only)")
+
+
+# --------------------------------------------------------------------------------------------------
+# npu_swiglu
+# --------------------------------------------------------------------------------------------------
+def _swiglu_meta(self, dim=-1):
+    d = dim if dim >= 0 else dim + self.dim()
+    if d < 0 or d >= self.dim() or self.shape[d] % 2:
+        raise RuntimeError("npu_swiglu: the split dimension must exist and be even")
+    shape = list(self.shape)
+    shape[d] //= 2
+    return self.new_empty(shape)
+
+
+def _swiglu_cuda(self, dim=-1):
+    out = _swiglu_meta(self, dim)
+    d = dim if dim >= 0 else dim + self.dim()
+    if d != self.dim() - 1:
+        raise NotImplementedError("npu_swiglu: only the last dimension can be split on this path")
+    x = self.contiguous()
+    cols = x.shape[-1]
+    rows = x.numel() // cols if cols else 0
+    _lib.call("tab_swiglu", _ptr(x), _st(x.dtype, "npu_swiglu"), rows, cols, _ptr(out), _stream(x))
+    return out
+
+
+# --------------------------------------------------------------------------------------------------
+# npu_dequant_swiglu_quant
+# --------------------------------------------------------------------------------------------------
+def _dsq_meta(x, *, weight_scale=None, activation_scale=None, bias=None, quant_scale=None, quant_offset=None,
+              group_index=None, activate_left=False, quant_mode=0, dst_type=None, round_mode=None, activate_dim=None,
+              swiglu_mode=0, clamp_limit=7.0, glu_alpha=1.702, glu_bias=1.0):
+    # shape rule of python/torchair/_contrib/custom_torch_ops/auto_register_custom_torch_ops.py:121-156
+    activate_dim = -1 if activate_dim is None else activate_dim
+    select = activate_dim if activate_dim >= 0 else activate_dim + x.dim()
+    if x.dim() <= 1:
+        raise RuntimeError("x dim should larger than 1")
+    if select < 0 or select >= x.dim():
+        raise RuntimeError("activate dim should less than x dim")
+    if x.size(select) % 2 != 0:
+        raise RuntimeError("x last dim should be even")
+    if quant_mode not in (0, 1):
+        raise RuntimeError("quant_mode only support 0 or 1, but got " + str(quant_mode))
+    y_size = [x.size(i) // 2 if i == select else x.size(i) for i in range(x.dim())]
+    return (torch.empty(y_size, dtype=torch.int8, device=x.device),
+            torch.empty(y_size[:-1], dtype=torch.float32, device=x.device))
+
+
+def _dsq_cuda(x, *, weight_scale=None, activation_scale=None, bias=None, quant_scale=None, quant_offset=None,
+              group_index=None, activate_left=False, quant_mode=0, dst_type=None, round_mode=None, activate_dim=None,
+              swiglu_mode=0, clamp_limit=7.0, glu_alpha=1.702, glu_bias=1.0):
+    op = "npu_dequant_swiglu_quant"
+    y, scale = _dsq_meta(x, quant_mode=quant_mode, activate_dim=activate_dim)
+    _only_none(op, bias=bias, quant_scale=quant_scale, quant_offset=quant_offset)
+    if quant_mode != 1:
+        raise NotImplementedError(f"{op}: only quant_mode=1 (dynamic) is on the path")
+    if dst_type not in (None, 1) or round_mode not in (None, 0) or swiglu_mode != 0:
+        raise NotImplementedError(f"{op}: only int8 output, rint rounding and swiglu_mode=0 are on the path")
+    if activate_dim not in (None, -1, x.dim() - 1):
+        raise NotImplementedError(f"{op}: only the last dimension can be split on this path")
+    if x.dtype != torch.int32:
+        raise NotImplementedError(f"{op}: x must be int32 accumulators on this path")
+    x = x.contiguous()
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    ws_groups = 0
+    if weight_scale is not None:
+        if weight_scale.dtype != torch.float32 or weight_scale.shape[-1] != cols:
+            raise RuntimeError(f"{op}: weight_scale must be fp32 [.., {cols}]")
+        weight_scale = weight_scale.contiguous()
+        ws_groups = weight_scale.numel() // cols
+    if activation_scale is not None:
+        if activation_scale.dtype != torch.float32 or activation_scale.numel() != rows:
+            raise RuntimeError(f"{op}: activation_scale must be fp32 with one value per row")
+        activation_scale = activation_scale.contiguous()
+    ngroups = 0
+    if group_index is not None:
+        group_index = group_index.to(torch.int64).contiguous()
+        ngroups = group_index.numel()
+    _lib.call("tab_dequant_swiglu_quant", _ptr(x), _ptr(weight_scale), ws_groups, _ptr(activation_scale), _ptr(group_index),
+              ngroups, int(bool(activate_left)), rows, cols, _ptr(y), _ptr(scale), _stream(x))
+    return y, scale
+
+
+# --------------------------------------------------------------------------------------------------
+# npu_grouped_matmul (W8A8) and the packed-weight cache
+# --------------------------------------------------------------------------------------------------
+_packed_cache = {}
+
+
+def clear_weight_cache() -> None:
+    """Drops the cached K-major relayouts of expert weights (call after freeing or replacing weights)."""
+    _packed_cache.clear()
+
+
+def packed_weight(weight: torch.Tensor) -> torch.Tensor:
+    """int8 [E, Kd, N] -> cached int8 [E, N, Kd] (the K-major operand layout the tcgen05 descriptors read).
+
+    One-off per weight tensor.  The cache entry is tied to the life of the weight's storage (it is dropped by a
+    finaliser when the storage is freed, so a new tensor that reuses the address never sees a stale relayout)
+    and to the tensor's version counter (an in-place update of the weights triggers a fresh relayout).
+    """
+    storage = weight.untyped_storage()
+    ident = (storage._cdata, weight.storage_offset(), tuple(weight.shape), tuple(weight.stride()))
+    hit = _packed_cache.get(ident)
+    if hit is not None and hit[0] == weight._version:
+        return hit[1]
+    w = weight.contiguous()
+    E, Kd, N = w.shape
+    out = torch.empty((E, N, Kd), dtype=torch.int8, device=w.device)
+    _lib.call("tab_prepack_weight_i8", _ptr(w), E, Kd, N, _ptr(out), _stream(w))
+    if hit is None:
+        weakref.finalize(storage, _packed_cache.pop, ident, None)
+    _packed_cache[ident] = (weight._version, out)
+    return out
+
+
+def _gmm_common_check(op, x, weight, split_item, group_type, group_list, act_type):
+    if len(x) != 1 or len(weight) != 1:
+        raise NotImplementedError(f"{op}: exactly one x and one weight tensor (split_item 2/3 form) are on the path")
+    xs, w = x[0], weight[0]
+    if xs.dtype != torch.int8 or w.dtype != torch.int8:
+        raise NotImplementedError(f"{op}: only int8 x int8 (W8A8) is on the path, got {xs.dtype} x {w.dtype}")
+    if xs.dim() != 2 or w.dim() != 3 or xs.shape[1] != w.shape[1]:
+        raise RuntimeError(f"{op}: x must be [M, K] and weight [E, K, N]")
+    if split_item not in (2, 3):
+        raise NotImplementedError(f"{op}: split_item must be 2 or 3 (single output tensor)")
+    if group_type != 0:
+        raise NotImplementedError(f"{op}: group_type must be 0 (groups split the M axis)")
+    if group_list is None:
+        raise RuntimeError(f"{op}: group_list is required")
+    if act_type not in (None, 0):
+        raise NotImplementedError(f"{op}: act_type must be 0")
+    return xs, w
+
+
+def _gmm_out_dtype(output_dtype):
+    # converter grouped_matmul.py:178-195: fp16 -> 0, bf16 -> 1, int32 -> 2; int8 is rejected
+    if output_dtype is None:
+        raise NotImplementedError("npu_grouped_matmul: output_dtype is required for int8 inputs (3, 5 or 15)")
+    if output_dtype not in (3, 5, 15):
+        raise ValueError(f"output_dtype should be int32, float16 or bfloat16, but got {output_dtype}")
+    return _ST[output_dtype]
+
+
+def _gmm_meta(x, weight, *, bias=None, scale=None, offset=None, antiquant_scale=None, antiquant_offset=None,
+              per_token_scale=None, group_list=None, activation_input=None, activation_quant_scale=None,
+              activation_quant_offset=None, split_item=0, group_type=-1, group_list_type=0, act_type=0,
+              tuning_config=None, output_dtype=None, x_dtype=None, weight_dtype=None, scale_dtype=None,
+              per_token_scale_dtype=None):
+    xs, w = _gmm_common_check("npu_grouped_matmul", x, weight, split_item, group_type, group_list, act_type)
+    return [torch.empty((xs.shape[0], w.shape[2]), dtype=_gmm_out_dtype(output_dtype), device=xs.device)]
+
+
+def _gmm_cuda(x, weight, *, bias=None, scale=None, offset=None, antiquant_scale=None, antiquant_offset=None,
+              per_token_scale=None, group_list=None, activation_input=None, activation_quant_scale=None,
+              activation_quant_offset=None, split_item=0, group_type=-1, group_list_type=0, act_type=0,
+              tuning_config=None, output_dtype=None, x_dtype=None, weight_dtype=None, scale_dtype=None,
+              per_token_scale_dtype=None):
+    op = "npu_grouped_matmul"
+    xs, w = _gmm_common_check(op, x, weight, split_item, group_type, group_list, act_type)
+    for name, v in (("bias", bias), ("offset", offset), ("antiquant_scale", antiquant_scale),
+                    ("antiquant_offset", antiquant_offset), ("activation_input", activation_input),
+                    ("activation_quant_scale", activation_quant_scale), ("activation_quant_offset", activation_quant_offset)):
+        if v is not None and len(v) > 0:
+            raise NotImplementedError(f"{op}: `{name}` is outside the W8A8 MoE path")
+    _only_none(op, x_dtype=x_dtype, weight_dtype=weight_dtype, scale_dtype=scale_dtype, per_token_scale_dtype=per_token_scale_dtype)
+    out_dt = _gmm_out_dtype(output_dtype)
+    M, Kd = xs.shape
+    E, _, N = w.shape
+    if isinstance(group_list, (list, tuple)):
+        group_list = torch.tensor(list(group_list), dtype=torch.int64, device=xs.device)
+    if group_list.numel() != E:
+        raise RuntimeError(f"{op}: group_list must have one entry per expert ({E})")
+    group_list = group_list.to(torch.int64).contiguous()
+    sc = scale[0] if scale is not None and len(scale) else None
+    pts = per_token_scale[0] if per_token_scale is not None and len(per_token_scale) else None
+    if out_dt != torch.int32:
+        if sc is not None:
+            if sc.dtype != torch.float32 or sc.numel() != E * N:
+                raise NotImplementedError(f"{op}: scale must be fp32 [E, N] on this path")
+            sc = sc.contiguous()
+        if pts is not None:
+            if pts.dtype != torch.float32 or pts.numel() != M:
+                raise RuntimeError(f"{op}: per_token_scale must be fp32 [M]")
+            pts = pts.contiguous()
+    xs = xs.contiguous()
+    wp = packed_weight(w)
+    # rows outside every group are defined to be zero
+    y = torch.zeros((M, N), dtype=out_dt, device=xs.device)
+    _lib.call("tab_grouped_matmul_w8a8", _ptr(xs), _ptr(wp), _ptr(sc), _ptr(pts), _ptr(group_list), int(group_list_type or 0),
+              M, Kd, N, E, _ST_INV[out_dt], _ptr(y), _stream(xs))
+    return [y]
+
+
+def _gmm_sq_meta(x, weight, weight_scale, x_scale, group_list, *, smooth_scale=None, weight_assist_matrix=None, bias=None,
+                 dequant_mode=0, dequant_dtype=0, quant_mode=0, quant_dtype=1, group_list_type=0, tuning_config=None,
+                 x_dtype=None, weight_dtype=None, weight_scale_dtype=None, x_scale_dtype=None):
+    if len(weight) != 1 or weight[0].dim() != 3 or x.dim() != 2 or weight[0].shape[2] % 2:
+        raise RuntimeError("npu_grouped_matmul_swiglu_quant_v2: x [M, K], one weight [E, K, 2*I]")
+    M, I = x.shape[0], weight[0].shape[2] // 2
+    return (torch.empty((M, I), dtype=torch.int8, device=x.device), torch.empty((M,), dtype=torch.float32, device=x.device))
+
+
+def _gmm_sq_cuda(x, weight, weight_scale, x_scale, group_list, *, smooth_scale=None, weight_assist_matrix=None, bias=None,
+                 dequant_mode=0, dequant_dtype=0, quant_mode=0, quant_dtype=1, group_list_type=0, tuning_config=None,
+                 x_dtype=None, weight_dtype=None, weight_scale_dtype=None, x_scale_dtype=None):
+    op = "npu_grouped_matmul_swiglu_quant_v2"
+    yq, ys = _gmm_sq_meta(x, weight, weight_scale, x_scale, group_list)
+    _only_none(op, smooth_scale=smooth_scale, bias=bias, x_dtype=x_dtype, weight_dtype=weight_dtype,
+               weight_scale_dtype=weight_scale_dtype, x_scale_dtype=x_scale_dtype)
+    if weight_assist_matrix is not None and len(weight_assist_matrix):
+        raise NotImplementedError(f"{op}: weight_assist_matrix is outside the W8A8 MoE path")
+    _only_default(op, dequant_mode=(dequant_mode or 0, 0), quant_mode=(quant_mode or 0, 0), quant_dtype=(quant_dtype or 1, 1))
+    return fused_gate_up(x, weight[0], weight_scale[0], x_scale, group_list, int(group_list_type or 0), True, yq, ys)
+
+
+def fused_gate_up(x, w, w_scale, x_scale, group_list, group_list_type, activate_left, yq=None, ys=None):
+    """gate_up grouped GEMM + dequant + SwiGLU + per-row int8 requant in one call (two kernels)."""
+    if x.dtype != torch.int8 or w.dtype != torch.int8:
+        raise NotImplementedError("fused gate_up: only int8 x int8 (W8A8) is on the path")
+    M, Kd = x.shape
+    E, _, N2 = w.shape
+    I = N2 // 2
+    if yq is None:
+        yq = torch.empty((M, I), dtype=torch.int8, device=x.device)
+        ys = torch.empty((M,), dtype=torch.float32, device=x.device)
+    if w_scale.dtype != torch.float32 or w_scale.numel() != E * N2 or x_scale.dtype != torch.float32 or x_scale.numel() != M:
+        raise RuntimeError("fused gate_up: weight_scale must be fp32 [E, 2*I] and x_scale fp32 [M]")
+    if group_list.numel() != E:
+        raise RuntimeError(f"fused gate_up: group_list must have one entry per expert ({E})")
+    group_list = group_list.to(torch.int64).contiguous()
+    x, w_scale, x_scale = x.contiguous(), w_scale.contiguous(), x_scale.contiguous()
+    wp = packed_weight(w)
+    ws = _workspace(_lib.workspace_bytes("tab_grouped_matmul_swiglu_quant_workspace_bytes", M, I), x.device)
+    _lib.call("tab_grouped_matmul_swiglu_quant", _ptr(x), _ptr(wp), _ptr(w_scale), _ptr(x_scale), _ptr(group_list),
+              group_list_type, M, Kd, I, E, int(bool(activate_left)), _ptr(yq), _ptr(ys), _ptr(ws), ws.numel(), _stream(x))
+    return yq, ys
+
+
+def gmm_status(device=None) -> int:
+    """Synchronises the current stream and returns the GEMM kernels' device status word (0 = fine)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        st = ctypes.c_int(0)
+        _lib.call("tab_gmm_status", ctypes.byref(st), ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+        return int(st.value)
+
+
+# --------------------------------------------------------------------------------------------------
+# npu_moe_distribute_dispatch / combine
+# --------------------------------------------------------------------------------------------------
+def _dispatch_meta(x, expert_ids, group_ep, ep_world_size, ep_rank_id, moe_expert_num, *, scales=None, x_active_mask=None,
+                   expert_scales=None, group_tp="", tp_world_size=0, tp_rank_id=0, expert_shard_type=0, shared_expert_num=1,
+                   shared_expert_rank_num=0, quant_mode=0, global_bs=0, expert_token_nums_type=1):
+    ep.check_dispatch_args(x, expert_ids, ep_world_size, ep_rank_id, moe_expert_num, scales, x_active_mask, tp_world_size,
+                           expert_shard_type, shared_expert_rank_num, quant_mode, global_bs, expert_token_nums_type)
+    T, K = expert_ids.shape
+    R = ep_world_size
+    E_l = moe_expert_num // R
+    A = ep.dispatch_rows(T, R, moe_expert_num, K)
+    dev = x.device
+    return (torch.empty((A, x.shape[1]), dtype=torch.int8 if quant_mode == 2 else x.dtype, device=dev),
+            torch.empty((A,), dtype=torch.float32, device=dev),
+            torch.empty((T * K,), dtype=torch.int32, device=dev),
+            torch.empty((E_l,), dtype=torch.int64, device=dev),
+            torch.empty((E_l * R,), dtype=torch.int32, device=dev),
+            torch.empty((max(tp_world_size, 1),), dtype=torch.int32, device=dev),
+            torch.empty((A,), dtype=torch.float32, device=dev))
+
+
+def _dispatch_cuda(x, expert_ids, group_ep, ep_world_size, ep_rank_id, moe_expert_num, *, scales=None, x_active_mask=None,
+                   expert_scales=None, group_tp="", tp_world_size=0, tp_rank_id=0, expert_shard_type=0, shared_expert_num=1,
+                   shared_expert_rank_num=0, quant_mode=0, global_bs=0, expert_token_nums_type=1):
+    ep.check_dispatch_args(x, expert_ids, ep_world_size, ep_rank_id, moe_expert_num, scales, x_active_mask, tp_world_size,
+                           expert_shard_type, shared_expert_rank_num, quant_mode, global_bs, expert_token_nums_type)
+    return ep.dispatch(ep.CudaKernels, x, expert_ids, group_ep, ep_world_size, ep_rank_id, moe_expert_num, quant_mode,
+                       expert_token_nums_type, max(tp_world_size, 1))
+
+
+def _combine_meta(expand_x, expert_ids, expand_idx, ep_send_counts, expert_scales, group_ep, ep_world_size, ep_rank_id,
+                  moe_expert_num, *, tp_send_counts=None, x_active_mask=None, activation_scale=None, weight_scale=None,
+                  group_list=None, expand_scales=None, shared_expert_x=None, group_tp="", tp_world_size=0, tp_rank_id=0,
+                  expert_shard_type=0, shared_expert_num=1, shared_expert_rank_num=0, global_bs=0, out_dtype=0,
+                  comm_quant_mode=0, group_list_type=0):
+    ep.check_combine_args(expand_x, expert_ids, expert_scales, ep_world_size, ep_rank_id, moe_expert_num, x_active_mask,
+                          activation_scale, weight_scale, group_list, tp_world_size, expert_shard_type,
+                          shared_expert_rank_num, global_bs, out_dtype, comm_quant_mode)
+    return expand_x.new_empty((expert_ids.shape[0], expand_x.shape[1]))
+
+
+def _combine_cuda(expand_x, expert_ids, expand_idx, ep_send_counts, expert_scales, group_ep, ep_world_size, ep_rank_id,
+                  moe_expert_num, *, tp_send_counts=None, x_active_mask=None, activation_scale=None, weight_scale=None,
+                  group_list=None, expand_scales=None, shared_expert_x=None, group_tp="", tp_world_size=0, tp_rank_id=0,
+                  expert_shard_type=0, shared_expert_num=1, shared_expert_rank_num=0, global_bs=0, out_dtype=0,
+                  comm_quant_mode=0, group_list_type=0):
+    ep.check_combine_args(expand_x, expert_ids, expert_scales, ep_world_size, ep_rank_id, moe_expert_num, x_active_mask,
+                          activation_scale, weight_scale, group_list, tp_world_size, expert_shard_type,
+                          shared_expert_rank_num, global_bs, out_dtype, comm_quant_mode)
+    return ep.combine(ep.CudaKernels, expand_x, expert_ids, expand_idx, ep_send_counts, expert_scales, group_ep,
+                      ep_world_size, ep_rank_id, moe_expert_num, shared_expert_x)
+
+
+for _name, _meta, _cuda in (
+        ("npu_moe_init_routing", _init_routing_meta, _init_routing_cuda),
+        ("npu_dynamic_quant", _dynamic_quant_meta, _dynamic_quant_cuda),
+        ("npu_swiglu", _swiglu_meta, _swiglu_cuda),
+        ("npu_dequant_swiglu_quant", _dsq_meta, _dsq_cuda),
+        ("npu_grouped_matmul", _gmm_meta, _gmm_cuda),
+        ("npu_grouped_matmul.List", _gmm_meta, _gmm_cuda),
+        ("npu_grouped_matmul_swiglu_quant_v2", _gmm_sq_meta, _gmm_sq_cuda),
+        ("npu_moe_distribute_dispatch", _dispatch_meta, _dispatch_cuda),
+        ("npu_moe_distribute_combine", _combine_meta, _combine_cuda)):
+    _npu.impl(_name, _meta, "Meta")
+    _npu.impl(_name, _cuda, "CUDA")
+_npu.impl("npu_dynamic_quant_asymmetric", _dynamic_quant_asym, "CompositeExplicitAutograd")
+
+OP_NAMES = ["npu_moe_init_routing", "npu_dynamic_quant", "npu_dynamic_quant_asymmetric", "npu_swiglu",
+            "npu_dequant_swiglu_quant", "npu_grouped_matmul", "npu_grouped_matmul_swiglu_quant_v2",
+            "npu_moe_distribute_dispatch", "npu_moe_distribute_combine"]
