@@ -1,0 +1,358 @@
+#!/usr/bin/env python
+"""Benchmark of the W8A8 expert-parallel MoE layer: int8 MoE-layer tokens/s on 1/2/4/8 B200.
+
+    python bench.py --gpus 1 --steps K --warmup W            # this repository's CUDA path
+    python bench.py --impl reference --steps K --warmup W     # the CPU formulas of the path on the host cores
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One step = one pass of the layer (dispatch with per-token int8 quantisation -> gate_up grouped GEMM with the
+dequant+SwiGLU+requant epilogue -> down grouped GEMM -> combine) over one batch of seeded synthetic tokens.
+N = 1 runs the decode shape with all 256 experts local (256 tokens, hidden 7168, top-8, intermediate 2048);
+N > 1 runs the expert-parallel decode shape (128 tokens per rank, 256/N experts per rank, NCCL all-to-all).
+Prints ONE JSON line on rank 0.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "int8_moe_layer_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (N=1)")
+    return ap.parse_args()
+
+
+def workload(n_gpus):
+    """(name, T per rank, H, E total, K, I) of the configuration benchmarked at this GPU count."""
+    if n_gpus == 1:
+        return "cfg1: 1xB200 decode MoE layer, DeepSeek-V3 shape, 256 tokens, all 256 experts local", 256, 7168, 256, 8, 2048
+    return (f"cfg2: {n_gpus}xB200 expert-parallel decode, DeepSeek-V3 shape, 128 tokens/rank, {256 // n_gpus} experts/rank",
+            128, 7168, 256, 8, 2048)
+
+
+# ---------------------------------------------------------------------------------------------------
+# CPU arm: the oracle on the host cores, on a bounded sample of the workload
+# ---------------------------------------------------------------------------------------------------
+def cpu_sample_config():
+    """1/8 of the decode layer: 32 tokens routed top-8 over 32 experts of the full expert shape, i.e. the same
+    ~8 rows per expert and the same bytes of weight per token as the full 256-token / 256-expert layer."""
+    from oracle import moe_oracle as O
+    return O.MoeConfig("cfg1_sample", 32, 7168, 32, 8, 2048)
+
+
+def run_cpu(steps, warmup, seed):
+    import torch
+    from oracle import moe_oracle as O
+    torch.set_num_threads(os.cpu_count() or 1)
+    cfg = cpu_sample_config()
+    w = O.make_weights(cfg, seed)
+    x, ids, wt = O.make_tokens(cfg, seed)
+    for _ in range(warmup):
+        O.moe_layer([x], [ids], [wt], w)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        O.moe_layer([x], [ids], [wt], w)
+    dt = time.perf_counter() - t0
+    return {"value": cfg.T * steps / dt, "ms_per_step": dt / steps * 1e3, "cores": torch.get_num_threads(),
+            "sample": f"{cfg.T} tokens top-{cfg.K} over {cfg.E} experts (hidden {cfg.H}, intermediate {cfg.I}): 1/8 of the "
+                      f"256-token/256-expert layer at the same rows per expert; {steps} passes after {warmup} warm-up",
+            "cpu_model": _cpu_model(), "torch": torch.__version__}
+
+
+def _cpu_model():
+    try:
+        for line in open("/proc/cpuinfo"):
+            if line.startswith("model name"):
+                return line.split(":", 1)[1].strip()
+    except OSError:
+        pass
+    return "unknown"
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 100))         # a pass is ~0.2 s of CPU work: the whole run stays well under a minute
+    warmup = max(1, min(args.warmup, 3))
+    r = run_cpu(steps, warmup, args.seed)
+    name = workload(args.gpus)[0]
+    line = {"impl": "reference", "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+            "warmup": warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": name, "sample": r["sample"]},
+            "cpu_baseline": {"value": r["value"], "unit": UNIT, "cores": r["cores"], "kind": "port", "sample": r["sample"],
+                             "cpu_model": r["cpu_model"], "torch": r["torch"]},
+            "e2e": {"value": r["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0,
+            "note": "the reference's arithmetic for this path is closed vendor code; this arm times its op formulas "
+                    "(eager torch on CPU) on the host cores"}
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------
+# clock sampling during the measured sections
+# ---------------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.samples = []
+        self.proc = None
+        self.thread = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
+                                          "-i", str(gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 7:
+                try:
+                    self.samples.append((time.time(), float(parts[0]), float(parts[1]), parts[2], parts[3:7]))
+                except ValueError:
+                    pass
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self, windows):
+        inside = [s for s in self.samples if any(a <= s[0] <= b for a, b in windows)]
+        used = inside if len(inside) >= 3 else self.samples
+        if not used:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for s in used for n, v in zip(names, s[4]) if v.lower().startswith("active")})
+        return {"sm_mhz": statistics.median(s[1] for s in used), "sm_max_mhz": max(s[2] for s in used), "reasons": reasons,
+                "samples": len(used), "window": "timed regions" if used is inside else "whole run (timed regions too short to sample)"}
+
+
+# ---------------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------------
+def gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+    import torchair_b200
+    from torchair_b200 import ep, ops
+    from torchair_b200.layer import moe_layer
+    from oracle import moe_oracle as O
+
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the CUDA path has no CPU fallback (use --impl reference for the CPU arm)")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise RuntimeError(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch N>1 with torch.distributed.run")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+        ep.register_ep_group("ep", dist.group.WORLD)
+    name, T, H, E, K, I = workload(world)
+    E_l = E // world
+    cfg = O.MoeConfig("bench", T, H, E, K, I)
+
+    # weights of this rank's experts, generated on the device; tokens generated on the host (seeded)
+    g = torch.Generator(device=dev).manual_seed(args.seed * 100003 + rank)
+    w1 = torch.randint(-127, 128, (E_l, H, 2 * I), generator=g, dtype=torch.int8, device=dev)
+    w2 = torch.randint(-127, 128, (E_l, I, H), generator=g, dtype=torch.int8, device=dev)
+    s1 = torch.rand(E_l, 2 * I, generator=g, device=dev) * 9e-3 + 1e-3
+    s2 = torch.rand(E_l, H, generator=g, device=dev) * 9e-3 + 1e-3
+    x_h, ids_h, wt_h = O.make_tokens(cfg, args.seed, rank)
+    x_h, ids_h, wt_h = x_h.pin_memory(), ids_h.pin_memory(), wt_h.pin_memory()
+    out_h = torch.empty((T, H), dtype=torch.bfloat16).pin_memory()
+    x_d, ids_d, wt_d = x_h.to(dev), ids_h.to(dev), wt_h.to(dev)
+
+    def layer(x, ids, wt):
+        return moe_layer(x, ids, wt, w1, s1, w2, s2, group_ep="ep", ep_world_size=world, ep_rank_id=rank, moe_expert_num=E)
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    windows = []
+
+    # warm-up (also fills the packed-weight cache); single rank: capture the layer into one CUDA graph
+    for _ in range(max(args.warmup, 3)):
+        out = layer(x_d, ids_d, wt_d)
+    torch.cuda.synchronize()
+    graph = None
+    if world == 1:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            out = layer(x_d, ids_d, wt_d)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+
+    def step_resident():
+        if graph is not None:
+            graph.replay()
+        else:
+            layer(x_d, ids_d, wt_d)
+
+    def timed(fn, steps):
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t_a = time.time()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t_b = time.time()
+        if world > 1:
+            dist.barrier()
+        windows.append((t_a, t_b))
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    # (1) device-resident inputs
+    for _ in range(args.warmup):
+        step_resident()
+    total_ms = timed(step_resident, args.steps)
+    ms_per_step = total_ms / args.steps
+    value = T * world * args.steps / (total_ms * 1e-3)
+
+    # (2) end to end through the public ops with host buffers: H2D of the step's inputs, layer, D2H of the result
+    def step_e2e():
+        x_d.copy_(x_h, non_blocking=True)
+        ids_d.copy_(ids_h, non_blocking=True)
+        wt_d.copy_(wt_h, non_blocking=True)
+        if graph is not None:
+            graph.replay()
+            out_h.copy_(out, non_blocking=True)
+        else:
+            out_h.copy_(layer(x_d, ids_d, wt_d), non_blocking=True)
+        torch.cuda.current_stream().synchronize()     # the caller reads the result every step
+
+    for _ in range(args.warmup):
+        step_e2e()
+    e2e_ms = timed(step_e2e, args.steps)
+    e2e_value = T * world * args.steps / (e2e_ms * 1e-3)
+    h2d = x_h.numel() * 2 + ids_h.numel() * 4 + wt_h.numel() * 4
+    d2h = out_h.numel() * 2
+
+    # (3) the dominant kernel alone: gate_up grouped GEMM (+ its two helper launches) and the down GEMM
+    npu = torch.ops.npu
+    ex, xs, expand_idx, nums, ep_recv, _, _ = npu.npu_moe_distribute_dispatch(x_d, ids_d, "ep", world, rank, E, quant_mode=2)
+    M = ex.shape[0]
+    hq, hs = npu.npu_grouped_matmul_swiglu_quant_v2(ex, [w1], [s1], xs, nums, group_list_type=1)
+    rows = int(nums.sum().item())
+    experts_hit = int((nums > 0).sum().item())
+
+    def time_each(fn, reps):
+        times = []
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        t_a = time.time()
+        for _ in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            b.synchronize()
+            times.append(a.elapsed_time(b))
+        windows.append((t_a, time.time()))
+        return sum(times) / len(times)
+
+    reps = max(10, min(args.steps, 100))
+    ms_up = time_each(lambda: npu.npu_grouped_matmul_swiglu_quant_v2(ex, [w1], [s1], xs, nums, group_list_type=1), reps)
+    ms_down = time_each(lambda: npu.npu_grouped_matmul([hq], [w2], scale=[s2], per_token_scale=[hs], group_list=nums, split_item=2,
+                                                       group_type=0, group_list_type=1, output_dtype=15), reps)
+    ms_disp = time_each(lambda: npu.npu_moe_distribute_dispatch(x_d, ids_d, "", 1, 0, E, quant_mode=2), reps) if world == 1 else None
+    bytes_up = experts_hit * H * 2 * I + rows * H + rows * I * 4 + experts_hit * 2 * I * 4 + rows * 4   # weights + A + fp32 h + scales
+    bytes_down = experts_hit * I * H + rows * I + rows * H * 2 + experts_hit * H * 4 + rows * 4
+    status = torchair_b200.gmm_status(dev)
+    if status != 0:
+        raise RuntimeError(f"grouped GEMM reported a timed-out wait (code {status})")
+
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except (OSError, ValueError):
+        pass
+    peak_gbs = float(peaks.get("hbm_gbs", 6650.0))
+    achieved = bytes_up / (ms_up * 1e-3) / 1e9
+    roofline = {"kernel": "gmm_i8_kernel<NT,fused> gate_up (timed with its memset and requantise helper launches)",
+                "bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs,
+                "peak_source": "measured (MEASURED_PEAKS.json)" if "hbm_gbs" in peaks else "fallback 6650 GB/s",
+                "algorithmic_bytes": bytes_up, "ms_per_launch": ms_up, "traffic": None,
+                "int8_tops": 2.0 * rows * H * 2 * I / (ms_up * 1e-3) / 1e12,
+                "others": {"down_gemm": {"ms": ms_down, "GB/s": bytes_down / (ms_down * 1e-3) / 1e9},
+                           "dispatch_sort_quant_scatter": None if ms_disp is None else
+                           {"ms": ms_disp, "GB/s": (2 * T * H + M * H + 4 * M) / (ms_disp * 1e-3) / 1e9}}}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        r = run_cpu(steps=50, warmup=2, seed=args.seed)     # ~10-20 s of CPU work
+        cpu = {"value": r["value"], "unit": UNIT, "cores": r["cores"], "kind": "port", "sample": r["sample"],
+               "cpu_model": r["cpu_model"], "torch": r["torch"]}
+
+    if sampler is not None:
+        sampler.stop()
+    if rank == 0:
+        launches_per_step = 8 if world == 1 else 12   # sort x3, pack, gemm, requant, gemm, combine (+ plan/permute x2 each way)
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
+                "data": "synthetic",
+                "config": {"workload": name, "tokens_per_rank": T, "hidden": H, "experts": E, "experts_per_rank": E_l, "top_k": K,
+                           "intermediate": I, "parallelism": f"ep{world}", "cuda_graph": graph is not None,
+                           "l2": "inputs larger than L2: every step streams this rank's int8 expert weights "
+                                 f"({(w1.numel() + w2.numel()) / 1e9:.2f} GB) from HBM"},
+                "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                        "ms_per_step": e2e_ms / args.steps},
+                "gpu_launches": launches_per_step * args.steps,
+                "roofline": roofline, "cpu_baseline": cpu,
+                "clocks": sampler.summary(windows) if sampler is not None else None}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+    else:
+        gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()
