@@ -95,6 +95,25 @@ TAB_API int tab_moe_init_routing(const void* x, int x_dtype, const int32_t* row_
                          void* workspace, size_t workspace_bytes, tab_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------
+ * tab_moe_init_routing_static: npu_moe_init_routing for callers that cannot hand over scratch memory.
+ * No counterpart in the reference: it exists for hosts that bind this library without a device allocator of
+ * their own -- a plugin running inside another framework's memory pool, a real-time loop that fixed its
+ * allocations at start-up -- and so can neither cudaMalloc a workspace nor ask torch for one.  Inputs and
+ * outputs are still the caller's; the sort's scratch is a 256 KiB array inside the library's device image,
+ * present once on every GPU that loads the library until the process exits.
+ * Limits: T*K <= 32768 and expert_bound <= 512; larger problems are rejected with TAB_ERR_UNSUPPORTED (use
+ * tab_moe_init_routing with a workspace).  The call itself allocates and frees nothing.
+ * The first call on each device looks up the array's device address (with that device current); make that
+ * first call before starting any stream capture.  All calls on a device share the one array: calls that may
+ * overlap on the GPU (different streams, no ordering between them) race on it and must be serialised by the
+ * caller.  Same arguments and results as tab_moe_init_routing otherwise.
+ * ------------------------------------------------------------------------------------------------- */
+TAB_API int tab_moe_init_routing_static(const void* x, int x_dtype, const int32_t* row_idx, const int32_t* expert_idx,
+                                int64_t T, int64_t K, int64_t H, int64_t active_num, int64_t expert_bound,
+                                void* expanded_x, int32_t* expanded_row_idx, int32_t* expanded_expert_idx,
+                                tab_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------
  * npu_moe_distribute_dispatch, sender side (converter moe_distribute_dispatch.py:4-45 ->
  * MoeDistributeDispatch).  Sorts this rank's T*K copies by global expert id (stable), quantises every
  * token once (quant_mode 2: int8 rows + fp32 scales; quant_mode 0: rows keep x_dtype, scales = 0) and

@@ -2,6 +2,8 @@
 // (npu_moe_init_routing, sender side of npu_moe_distribute_dispatch), the fused quantise-and-scatter of
 // token rows, the receiver-side row permutations around the all-to-all, and the weighted gather-sum of
 // npu_moe_distribute_combine.  Integer/byte movers: HBM-bound, 16-byte accesses, grids sized to the SMs.
+#include <mutex>
+
 #include "tab_common.cuh"
 
 namespace tab {
@@ -542,4 +544,63 @@ extern "C" int tab_moe_combine(const void* rows, int dtype, const int32_t* expan
   else
     return fail(TAB_ERR_UNSUPPORTED, "combine: dtype %d (want 5 or 15)", dtype);
   return check_launch("combine");
+}
+
+// ---- routing without caller-provided scratch -----------------------------------------------------------
+// Same work as tab_moe_init_routing, but the sort's scratch (chunk histograms, expert totals, sorted source
+// rows) lives in a fixed array inside the library's device image instead of a caller-supplied workspace.
+namespace tab {
+
+constexpr int64_t kStaticMaxPairs = 32768;    // T*K
+constexpr int64_t kStaticMaxExperts = 512;    // expert_bound
+constexpr size_t kStaticScratchBytes = 256 * 1024;
+static_assert(((kStaticMaxPairs / kChunk) * kStaticMaxExperts + kStaticMaxExperts + 4 + kStaticMaxPairs) * 4 + 256 <=
+                  kStaticScratchBytes, "static routing scratch must hold the largest accepted problem");
+
+// One copy per GPU that loads the library, resident until the process exits.
+static __device__ __align__(256) unsigned char g_static_routing_scratch[kStaticScratchBytes];
+
+static std::mutex g_static_mutex;
+static void* g_static_scratch_addr[64] = {nullptr};
+
+// In host code `g_static_routing_scratch` is only a handle for the symbol, not a device address; the address on
+// the current device comes from cudaGetSymbolAddress, looked up once per device and remembered.
+static int static_scratch_on_current_device(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(TAB_ERR_CUDA, "init_routing_static: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= 64) return fail(TAB_ERR_UNSUPPORTED, "init_routing_static: device index %d", dev);
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_scratch_addr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_routing_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return fail(TAB_ERR_CUDA, "init_routing_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    g_static_scratch_addr[dev] = p;
+  }
+  *out = g_static_scratch_addr[dev];
+  return TAB_OK;
+}
+
+}  // namespace tab
+
+extern "C" int tab_moe_init_routing_static(const void* x, int x_dtype, const int32_t* row_idx, const int32_t* expert_idx,
+                                           int64_t T, int64_t K, int64_t H, int64_t active_num, int64_t expert_bound,
+                                           void* expanded_x, int32_t* expanded_row_idx, int32_t* expanded_expert_idx,
+                                           tab_stream_t stream) {
+  if (T < 0 || K <= 0 || expert_bound <= 0)
+    return fail(TAB_ERR_BAD_ARG, "init_routing_static: T=%lld K=%lld expert_bound=%lld", (long long)T, (long long)K, (long long)expert_bound);
+  if (T * K > kStaticMaxPairs || expert_bound > kStaticMaxExperts)
+    return fail(TAB_ERR_UNSUPPORTED,
+                "init_routing_static: T*K=%lld (max %lld) or expert_bound=%lld (max %lld) exceeds the built-in scratch; "
+                "use tab_moe_init_routing with a workspace",
+                (long long)(T * K), (long long)kStaticMaxPairs, (long long)expert_bound, (long long)kStaticMaxExperts);
+  if (T * K == 0) return TAB_OK;
+  void* scratch = nullptr;
+  int rc = static_scratch_on_current_device(&scratch);
+  if (rc != TAB_OK) return rc;
+  // Every scratch word the kernels read is written earlier in the same call (histograms, totals and sorted rows
+  // are fully overwritten), so nothing left over from the previous call needs clearing.
+  return tab_moe_init_routing(x, x_dtype, row_idx, expert_idx, T, K, H, active_num, expert_bound, expanded_x,
+                              expanded_row_idx, expanded_expert_idx, scratch, kStaticScratchBytes, stream);
 }
