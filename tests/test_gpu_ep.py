@@ -1,0 +1,90 @@
+"""Expert parallelism on real GPUs: R ranks (one process per GPU, NCCL) against the oracle's simulated ranks.
+
+Needs at least two visible GPUs; skipped otherwise.  No failure is injected here (host-side failure handling is
+covered by the gloo tests on CPU).
+"""
+import os
+import socket
+import traceback
+
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, outdir):
+    try:
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        import torch.distributed as dist
+        import torchair_b200
+        from torchair_b200.layer import moe_layer
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        torchair_b200.register_ep_group("ep", dist.group.WORLD)
+        results = {}
+        for cfg_name, cfg in (("cfg0", O.CONFIGS["cfg0"]), ("skew", O.MoeConfig("skew", 96, 512, 16, 4, 256, zipf_s=1.2))):
+            E_l = cfg.E // world
+            w = O.make_weights(cfg, 0, experts=range(rank * E_l, (rank + 1) * E_l))
+            x, ids, wt = O.make_tokens(cfg, 0, rank)
+            xd, idd, wtd = x.to(dev), ids.to(dev), wt.to(dev)
+            disp = torch.ops.npu.npu_moe_distribute_dispatch(xd, idd, "ep", world, rank, cfg.E, quant_mode=2)
+            for fused in (True, False):
+                out = moe_layer(xd, idd, wtd, w.w1.to(dev), w.s1.to(dev), w.w2.to(dev), w.s2.to(dev), group_ep="ep",
+                                ep_world_size=world, ep_rank_id=rank, moe_expert_num=cfg.E, fused=fused)
+                results[(cfg_name, fused)] = out.cpu()
+            results[(cfg_name, "disp")] = [t.cpu() for t in disp]
+        results["status"] = torchair_b200.gmm_status(dev)
+        torch.save(results, os.path.join(outdir, f"rank{rank}.pt"))
+        dist.barrier()
+        dist.destroy_process_group()
+        open(os.path.join(outdir, f"ok{rank}"), "w").write("ok")
+    except Exception:
+        open(os.path.join(outdir, f"err{rank}"), "w").write(traceback.format_exc())
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_expert_parallel_layer_on_gpus_matches_oracle(world, tmp_path):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=_worker, args=(r, world, port, str(tmp_path))) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=600)
+        if p.is_alive():
+            p.kill()
+    for r in range(world):
+        err = os.path.join(str(tmp_path), f"err{r}")
+        assert not os.path.exists(err), open(err).read()
+        assert os.path.exists(os.path.join(str(tmp_path), f"ok{r}")), f"rank {r} did not finish"
+    got = [torch.load(os.path.join(str(tmp_path), f"rank{r}.pt")) for r in range(world)]
+    for cfg_name, cfg in (("cfg0", O.CONFIGS["cfg0"]), ("skew", O.MoeConfig("skew", 96, 512, 16, 4, 256, zipf_s=1.2))):
+        w = O.make_weights(cfg, 0)
+        xs, idl, wl = zip(*[O.make_tokens(cfg, 0, r) for r in range(world)])
+        collect = []
+        ref = O.moe_layer(xs, idl, wl, w, collect)
+        for r in range(world):
+            assert got[r]["status"] == 0
+            d = collect[r]["disp"]
+            g = got[r][(cfg_name, "disp")]
+            want = (d.expand_x, d.dynamic_scales, d.expand_idx, d.expert_token_nums, d.ep_recv_count)
+            for a, b in zip(want, g):
+                assert torch.equal(a, b), "dispatch outputs (int8 rows, scales, indices, counts) must be bit-exact"
+            for fused in (True, False):
+                torch.testing.assert_close(got[r][(cfg_name, fused)].float(), ref[r].float(), rtol=1e-2, atol=1e-2)
+            assert torch.equal(got[r][(cfg_name, True)], got[r][(cfg_name, False)])
