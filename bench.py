@@ -36,6 +36,8 @@ def parse_args():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (N=1)")
+    ap.add_argument("--kernels", action="store_true",
+                    help="also time every kernel of the path alone and write the table to stderr (study aid, N=1)")
     ap.add_argument("--workload", default="auto", choices=["auto"] + sorted(EXTRA_WORKLOADS),
                     help="auto = the headline configuration for this GPU count; the others are single-GPU study cases")
     return ap.parse_args()
@@ -347,6 +349,35 @@ def gpu_arm(args):
                                               "int8_tops": ops_down / (ms_down * 1e-3) / 1e12},
                                 "dispatch_sort_quant_scatter": None if ms_disp is None else
                                 {"ms": ms_disp, "GB/s": (2 * T * H + M * H + 4 * M) / (ms_disp * 1e-3) / 1e9}}})
+
+    if args.kernels and world == 1:
+        def gbs(nbytes, ms):
+            return round(nbytes / (ms * 1e-3) / 1e9, 1)
+        row_idx = torch.arange(T * K, dtype=torch.int32, device=dev).view(K, T).t().contiguous()
+        y_bf16 = npu.npu_grouped_matmul([hq], [w2], scale=[s2], per_token_scale=[hs], group_list=nums, split_item=2,
+                                        group_type=0, group_list_type=1, output_dtype=15)[0]
+        exb = x_d[torch.arange(M, device=dev) % T].contiguous()          # [M, H] bf16 rows for the quantiser
+        h32 = torch.randint(-2000000, 2000000, (min(M, 16384), 2 * I), dtype=torch.int32, device=dev)
+        hb = torch.randn((M, 2 * I), dtype=torch.float32, device=dev).to(torch.bfloat16)
+        m32 = h32.shape[0]
+        ones = torch.ones(m32, dtype=torch.float32, device=dev)
+        table = {
+            "init_routing": (time_each(lambda: npu.npu_moe_init_routing(x_d, row_idx, ids_d, T), reps), 2 * T * H + 2 * M * H + 24 * M),
+            "dynamic_quant": (time_each(lambda: npu.npu_dynamic_quant(exb), reps), 2 * M * H + M * H + 4 * M),
+            "dispatch_pack(sort+quant+scatter)": (time_each(lambda: npu.npu_moe_distribute_dispatch(x_d, ids_d, "", 1, 0, E, quant_mode=2), reps),
+                                                  2 * T * H + M * H + 4 * M),
+            "swiglu_bf16": (time_each(lambda: npu.npu_swiglu(hb), reps), 2 * M * 2 * I + 2 * M * I),
+            "dequant_swiglu_quant": (time_each(lambda: npu.npu_dequant_swiglu_quant(h32, weight_scale=s1[:1], activation_scale=ones,
+                                                                                   activate_left=True, quant_mode=1), reps),
+                                     m32 * (8 * I + I + 8)),
+            "combine": (time_each(lambda: npu.npu_moe_distribute_combine(y_bf16, ids_d, expand_idx, ep_recv, wt_d, "", 1, 0, E), reps),
+                        2 * M * H + 4 * M + 2 * T * H),
+            "gmm_gate_up_fused": (ms_up, bytes_up), "gmm_down": (ms_down, bytes_down),
+        }
+        report = {k: {"ms": round(ms, 4), "GB/s": gbs(b, ms), "frac_hbm": round(gbs(b, ms) / peak_gbs, 3)} for k, (ms, b) in table.items()}
+        report["gmm_gate_up_fused"]["int8_tops"] = round(tops_up, 1)
+        report["gmm_down"]["int8_tops"] = round(ops_down / (ms_down * 1e-3) / 1e12, 1)
+        print("KERNELS " + json.dumps({"workload": name, "kernels": report}), file=sys.stderr, flush=True)
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
