@@ -341,9 +341,12 @@ def gpu_arm(args):
                 "peak_source": ("2 x measured bf16 GEMM burst (MEASURED_PEAKS.json); nominal int8 dense is 4500"
                                 if measured else "2 x fallback bf16 1590; nominal int8 dense is 4500"),
                 "frac_of_nominal_4500": tops_up / 4500.0}
+    # DRAM bytes per launch from the ncu capture of the 1/8-scale decode case (profiles/gmm_i8_kernel_decode_small.md):
+    # 948.42 MB for 32 experts; traffic is one pass over each hit expert's weights, so it scales with experts_hit.
+    traffic = 948.417e6 / 32 * experts_hit if (H, I) == (7168, 2048) and rows <= 16 * experts_hit else None
     roofline = dict(main)
     roofline.update({"kernel": "gmm_i8_kernel<NT,fused> gate_up (timed with its memset and requantise helper launches)",
-                     "algorithmic_bytes": bytes_up, "algorithmic_ops": ops_up, "ms_per_launch": ms_up, "traffic": None,
+                     "algorithmic_bytes": bytes_up, "algorithmic_ops": ops_up, "ms_per_launch": ms_up, "traffic": traffic,
                      "GB/s": gbs_up, "int8_tops": tops_up, "rows": rows, "experts_hit": experts_hit,
                      "others": {"down_gemm": {"ms": ms_down, "GB/s": bytes_down / (ms_down * 1e-3) / 1e9,
                                               "int8_tops": ops_down / (ms_down * 1e-3) / 1e12},
