@@ -48,6 +48,8 @@ EXTRA_WORKLOADS = {
     "cfg1_small": ("cfg1_small: decode shape at 1/8 scale (32 tokens, 32 experts; 1.4 GB of weights)", 32, 7168, 32, 8, 2048, 0.0),
     "cfg3_rank": ("cfg3_rank: one rank's share of the skewed 8-GPU prefill (65536 rows over 32 local experts, Zipf 1.2)",
                   8192, 7168, 32, 8, 2048, 1.2),
+    "prefill_small": ("prefill_small: 2048 tokens top-8 over 8 experts of the DeepSeek-V3 expert shape (16384 rows, 2048 per expert)",
+                      2048, 7168, 8, 8, 2048, 0.0),
     "cfg4": ("cfg4: Qwen3-235B-A22B shape, 4096 tokens, 128 experts local", 4096, 4096, 128, 8, 1536, 0.0),
 }
 

@@ -19,19 +19,13 @@
 
 #include <mutex>
 
-#include "ptx_sm100.cuh"
-#include "tab_common.cuh"
+#include <stdlib.h>
+#include <string.h>
+
+#include "gmm_common.cuh"
+#include "gmm_i8_prefill.cuh"
 
 namespace tab {
-
-__device__ int g_gmm_status = 0;
-
-constexpr int kGmmThreads = 192;
-constexpr int kBlockK = 128;               // bytes of K per stage row = one swizzle span
-constexpr int kWTileBytes = 128 * kBlockK;  // one 128-channel weight tile
-constexpr int kMaxGroups = 1024;
-constexpr long long kWaitCycles = 400000000LL;  // bound of every device-side wait (~0.2 s)
-constexpr int kSmemLimit = 232448;
 
 template <int NT>
 struct GmmCfg {
@@ -44,62 +38,6 @@ struct GmmCfg {
   static constexpr int kTmemCols = kBufs * 2 * NT < 32 ? 32 : kBufs * 2 * NT;
   static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kCtrlBytes + kTableBytes;
 };
-
-struct GmmParams {
-  const int64_t* group_list;
-  int group_list_type;
-  int E;
-  int M;
-  int N;           // channels of the packed weight (plain: N; fused: 2*I)
-  int Kd;
-  int chan_tiles;  // plain: ceil(N/256); fused: ceil(I/128)
-  int half;        // fused: I
-  const float* w_scale;    // [E, N] or null
-  const float* tok_scale;  // [M] or null
-  void* out;               // plain: [M, N] of out_dtype
-  int out_dtype;
-  float* h_out;            // fused: [M, I] fp32
-  unsigned int* amax;      // fused: [M] row amax as fp32 bits
-  int activate_left;
-};
-
-// Waits for a phase of an mbarrier; gives up after kWaitCycles or when another role already gave up.
-__device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
-  if (ptx::mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  unsigned spins = 0;
-  while (!ptx::mbar_try_wait(bar, parity)) {
-    if ((++spins & 255u) == 0) {
-      if (*abort_flag != 0) return false;
-      if (clock64() - t0 > kWaitCycles) {
-        *abort_flag = code;
-        atomicCAS(&g_gmm_status, 0, code);
-        return false;
-      }
-    }
-  }
-  return true;
-}
-
-struct WorkItem {
-  int e, ct, tt;
-};
-
-__device__ __forceinline__ WorkItem decode_item(int w, int chan_tiles, int E, const int* s_pref) {
-  const int q = w / chan_tiles;
-  int lo = 0, hi = E;
-  while (hi - lo > 1) {
-    const int mid = (lo + hi) >> 1;
-    if (s_pref[mid] <= q) lo = mid; else hi = mid;
-  }
-  const int ntt = s_pref[lo + 1] - s_pref[lo];
-  const int local = w - chan_tiles * s_pref[lo];
-  WorkItem it;
-  it.e = lo;
-  it.ct = local / ntt;
-  it.tt = local - it.ct * ntt;
-  return it;
-}
 
 template <int NT, bool FUSED>
 __global__ void __launch_bounds__(kGmmThreads, 1)
@@ -145,45 +83,7 @@ gmm_i8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
   }
   if (warp == 1) ptx::tmem_alloc<Cfg::kTmemCols>(ptx::smem_u32(s_tmem));
   if (warp == 0) {
-    // Row ranges and token-tile prefix of every expert, 32 experts per step.
-    long long run_rows = 0;
-    int run_tiles = 0;
-    for (int e0 = 0; e0 < E; e0 += 32) {
-      const int e = e0 + lane;
-      long long c = 0;
-      if (e < E) {
-        const long long g = p.group_list[e];
-        c = p.group_list_type == 1 ? g : g - (e > 0 ? p.group_list[e - 1] : 0);
-        if (c < 0) c = 0;
-      }
-      long long incl = c;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const long long t = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += t;
-      }
-      long long end = run_rows + incl, start = end - c;
-      if (end > p.M) end = p.M;
-      if (start > p.M) start = p.M;
-      const int cnt = static_cast<int>(end - start);
-      const int tiles = (cnt + NT - 1) / NT;
-      int tincl = tiles;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int t = __shfl_up_sync(0xffffffffu, tincl, o);
-        if (lane >= o) tincl += t;
-      }
-      if (e < E) {
-        s_start[e] = static_cast<int>(start);
-        s_pref[e] = run_tiles + tincl - tiles;
-      }
-      run_rows += __shfl_sync(0xffffffffu, incl, 31);
-      run_tiles += __shfl_sync(0xffffffffu, tincl, 31);
-    }
-    if (lane == 0) {
-      s_start[E] = static_cast<int>(run_rows > p.M ? p.M : run_rows);
-      s_pref[E] = run_tiles;
-    }
+    build_group_tables(p, NT, lane, s_start, s_pref);
   }
   ptx::tc_fence_before();
   __syncthreads();
@@ -290,6 +190,7 @@ gmm_i8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
         const float wu = (cvalid && p.w_scale) ? p.w_scale[static_cast<int64_t>(it.e) * p.N + p.half + cg] : 1.f;
         for (int col0 = 0; col0 < nvalid; col0 += 16) {
           int g[16], u[16];
+          __syncwarp();
           ptx::tmem_ld16(t0 + col0, g);
           ptx::tmem_ld16(t0 + NT + col0, u);
           ptx::tmem_ld_wait();
@@ -317,6 +218,7 @@ gmm_i8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
         const float w1 = (v1 && p.w_scale) ? p.w_scale[static_cast<int64_t>(it.e) * p.N + c1] : 1.f;
         for (int col0 = 0; col0 < nvalid; col0 += 16) {
           int a[16], b[16];
+          __syncwarp();
           ptx::tmem_ld16(t0 + col0, a);
           ptx::tmem_ld16(t0 + NT + col0, b);
           ptx::tmem_ld_wait();
@@ -454,8 +356,32 @@ static int launch_one(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const Gm
   return check_launch("grouped_matmul");
 }
 
+// Orientation: experts with many rows run the prefill kernel (128-token tiles, overlapped epilogue); a handful of
+// rows per expert run the decode kernel (weights stationary, narrow token tile).  TAB_GMM_ORIENTATION=decode|prefill
+// overrides the choice (tuning aid).
+static bool use_prefill(int64_t M, int64_t E) {
+  const char* f = getenv("TAB_GMM_ORIENTATION");
+  if (f != nullptr) {
+    if (strcmp(f, "prefill") == 0) return true;
+    if (strcmp(f, "decode") == 0) return false;
+  }
+  return M > 64 * E;
+}
+
+template <bool FUSED>
+static int launch_prefill(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GmmParams& p, cudaStream_t st) {
+  const int64_t max_items = ((static_cast<int64_t>(p.M) + kPfTokens - 1) / kPfTokens + p.E) * p.chan_tiles;
+  const int sms = num_sms();
+  const int grid = static_cast<int>(max_items < sms ? max_items : sms);
+  cudaError_t e = cudaFuncSetAttribute(gmm_i8_prefill_kernel<FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmemBytes);
+  if (e != cudaSuccess) return fail(TAB_ERR_CUDA, "grouped_matmul: shared memory opt-in failed: %s", cudaGetErrorString(e));
+  gmm_i8_prefill_kernel<FUSED><<<grid, kGmmThreads, kPfSmemBytes, st>>>(tm_w, tm_x, p);
+  return check_launch("grouped_matmul (prefill)");
+}
+
 template <bool FUSED>
 static int launch_gmm(int nt, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GmmParams& p, cudaStream_t st) {
+  if (nt == 0) return launch_prefill<FUSED>(tm_w, tm_x, p, st);
   const int64_t max_items = ((static_cast<int64_t>(p.M) + nt - 1) / nt + p.E) * p.chan_tiles;
   const int sms = num_sms();
   const int grid = static_cast<int>(max_items < sms ? max_items : sms);
@@ -507,9 +433,9 @@ extern "C" int tab_grouped_matmul_w8a8(const int8_t* x, const int8_t* packed_wei
     return fail(TAB_ERR_UNSUPPORTED, "grouped_matmul: output dtype %d (want 3, 5 or 15)", out_dtype);
   if (M == 0) return TAB_OK;
   if (!y) return fail(TAB_ERR_BAD_ARG, "grouped_matmul: null output");
-  const int nt = pick_nt(M, E);
+  const int nt = use_prefill(M, E) ? 0 : pick_nt(M, E);     // 0 selects the prefill orientation
   CUtensorMap tm_w, tm_x;
-  rc = make_maps(x, packed_weight, M, Kd, N, E, nt, &tm_w, &tm_x);
+  rc = make_maps(x, packed_weight, M, Kd, N, E, nt == 0 ? kPfTokens : nt, &tm_w, &tm_x);
   if (rc != TAB_OK) return rc;
   GmmParams p = {};
   p.group_list = group_list;
@@ -551,9 +477,9 @@ extern "C" int tab_grouped_matmul_swiglu_quant(const int8_t* x, const int8_t* pa
   float* h = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + amax_bytes);
   cudaError_t ce = cudaMemsetAsync(amax, 0, amax_bytes, st);
   if (ce != cudaSuccess) return fail(TAB_ERR_CUDA, "grouped_matmul_swiglu_quant: memset: %s", cudaGetErrorString(ce));
-  const int nt = pick_nt(M, E);
+  const int nt = use_prefill(M, E) ? 0 : pick_nt(M, E);     // 0 selects the prefill orientation
   CUtensorMap tm_w, tm_x;
-  rc = make_maps(x, packed_weight, M, Kd, 2 * I, E, nt, &tm_w, &tm_x);
+  rc = make_maps(x, packed_weight, M, Kd, 2 * I, E, nt == 0 ? kPfTokens : nt, &tm_w, &tm_x);
   if (rc != TAB_OK) return rc;
   GmmParams p = {};
   p.group_list = group_list;

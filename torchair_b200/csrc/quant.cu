@@ -1,91 +1,76 @@
 // Per-row dynamic int8 quantisation (npu_dynamic_quant), SwiGLU (npu_swiglu) and the standalone
-// dequant + SwiGLU + requant (npu_dequant_swiglu_quant).  All three are HBM-bound row kernels: one CTA
-// per row, 16-byte loads, the row kept in registers between the amax pass and the store pass.
+// dequant + SwiGLU + requant (npu_dequant_swiglu_quant).  All are HBM-bound row kernels: one CTA per row
+// (64, 128 or 256 threads, picked so that a thread owns a few 16-byte chunks), the row kept in registers in its
+// raw form between the amax pass and the store pass, many small CTAs per SM so that loads of one row overlap the
+// reduction and stores of others.
 #include "tab_common.cuh"
 
 namespace tab {
 
-constexpr int kRowThreads = 256;
-constexpr int kMaxChunks = 8;  // 8 elements each: rows up to 256*8*8 = 16384 columns stay in registers
+constexpr int kMaxChunks = 8;  // chunks of 8 elements a thread keeps in registers; longer rows re-read their tail
 
-__device__ __forceinline__ float block_max(float v, float* red) {
-  v = warp_max(v);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (lane == 0) red[warp] = v;
-  __syncthreads();
-  float r = (lane < (blockDim.x >> 5)) ? red[lane] : 0.f;
-  r = warp_max(r);
-  __syncthreads();
-  return r;
-}
-
-__device__ __forceinline__ void store8_i8(int8_t* p, const float (&v)[8], float scale) {
-  uint2 o;
-  o.x = pack4_i8(quant_i8(v[0], scale), quant_i8(v[1], scale), quant_i8(v[2], scale), quant_i8(v[3], scale));
-  o.y = pack4_i8(quant_i8(v[4], scale), quant_i8(v[5], scale), quant_i8(v[6], scale), quant_i8(v[7], scale));
-  *reinterpret_cast<uint2*>(p) = o;
-}
-
-// x [rows, cols] -> y int8, scale fp32.  cols % 8 == 0.  Rows with more than kMaxChunks*kRowThreads
-// chunks re-read the tail from global memory (it is still in L2) in the store pass.
-template <typename T>
-__global__ void __launch_bounds__(kRowThreads) dynamic_quant_kernel(const T* __restrict__ x,
-                                                                   const T* __restrict__ smooth,
-                                                                   int64_t rows, int cols,
-                                                                   int8_t* __restrict__ y,
-                                                                   float* __restrict__ scale) {
-  __shared__ float red[32];
+// x [rows, cols] -> y int8, scale fp32.  cols % 8 == 0.
+template <typename T, int THREADS>
+__global__ void __launch_bounds__(THREADS) dynamic_quant_kernel(const T* __restrict__ x, const T* __restrict__ smooth,
+                                                               int64_t rows, int cols, int8_t* __restrict__ y,
+                                                               float* __restrict__ scale) {
+  __shared__ float red[THREADS / 32];
   const int nchunk = cols >> 3;
+  auto value = [&](const Raw8<T>& raw, int ch, float (&v)[8]) {
+    raw.unpack(v);
+    if (smooth != nullptr) {
+      float s[8];
+      Elem<T>::load8(smooth + ch * 8, s);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(v[i], s[i]);
+    }
+  };
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const T* xr = x + row * cols;
-    float v[kMaxChunks][8];
+    Raw8<T> raw[kMaxChunks];
+#pragma unroll
+    for (int c = 0; c < kMaxChunks; ++c) {
+      const int ch = threadIdx.x + c * THREADS;
+      if (ch < nchunk) raw[c].load(xr + ch * 8);
+    }
     float amax = 0.f;
 #pragma unroll
     for (int c = 0; c < kMaxChunks; ++c) {
-      const int ch = threadIdx.x + c * kRowThreads;
+      const int ch = threadIdx.x + c * THREADS;
       if (ch < nchunk) {
-        Elem<T>::load8(xr + ch * 8, v[c]);
-        if (smooth != nullptr) {
-          float s[8];
-          Elem<T>::load8(smooth + ch * 8, s);
+        float v[8];
+        value(raw[c], ch, v);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) v[c][i] = __fmul_rn(v[c][i], s[i]);
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[c][i]));
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
       }
     }
-    for (int ch = threadIdx.x + kMaxChunks * kRowThreads; ch < nchunk; ch += kRowThreads) {
-      float t[8];
-      Elem<T>::load8(xr + ch * 8, t);
-      if (smooth != nullptr) {
-        float s[8];
-        Elem<T>::load8(smooth + ch * 8, s);
+    for (int ch = threadIdx.x + kMaxChunks * THREADS; ch < nchunk; ch += THREADS) {
+      Raw8<T> t;
+      t.load(xr + ch * 8);
+      float v[8];
+      value(t, ch, v);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) t[i] = __fmul_rn(t[i], s[i]);
-      }
-#pragma unroll
-      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(t[i]));
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
     }
-    amax = block_max(amax, red);
+    amax = cta_max<THREADS>(amax, red);
     const float sc = __fdiv_rn(amax, 127.0f);
     if (threadIdx.x == 0) scale[row] = sc;
     int8_t* yr = y + row * cols;
 #pragma unroll
     for (int c = 0; c < kMaxChunks; ++c) {
-      const int ch = threadIdx.x + c * kRowThreads;
-      if (ch < nchunk) store8_i8(yr + ch * 8, v[c], sc);
-    }
-    for (int ch = threadIdx.x + kMaxChunks * kRowThreads; ch < nchunk; ch += kRowThreads) {
-      float t[8];
-      Elem<T>::load8(xr + ch * 8, t);
-      if (smooth != nullptr) {
-        float s[8];
-        Elem<T>::load8(smooth + ch * 8, s);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) t[i] = __fmul_rn(t[i], s[i]);
+      const int ch = threadIdx.x + c * THREADS;
+      if (ch < nchunk) {
+        float v[8];
+        value(raw[c], ch, v);
+        *reinterpret_cast<uint2*>(yr + ch * 8) = quant8(v, sc);
       }
-      store8_i8(yr + ch * 8, t, sc);
+    }
+    for (int ch = threadIdx.x + kMaxChunks * THREADS; ch < nchunk; ch += THREADS) {
+      Raw8<T> t;
+      t.load(xr + ch * 8);   // still in L2
+      float v[8];
+      value(t, ch, v);
+      *reinterpret_cast<uint2*>(yr + ch * 8) = quant8(v, sc);
     }
   }
 }
@@ -109,109 +94,138 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const T* __restrict__ x, in
   }
 }
 
-// Finds the group of `row` from per-group counts; returns -1 past their sum.  Warp-cooperative would be
-// overkill: groups <= 1024 and the scan runs once per CTA-row out of L1/L2.
-__device__ __forceinline__ int group_of_row(const int64_t* __restrict__ counts, int num_groups, int64_t row) {
-  int64_t end = 0;
-  for (int g = 0; g < num_groups; ++g) {
-    int64_t c = counts[g];
-    end += c > 0 ? c : 0;
-    if (row < end) return g;
+// Row ends (inclusive prefix of the per-group counts) in shared memory, computed once per CTA.
+constexpr int kMaxDsqGroups = 4096;
+template <int THREADS>
+__device__ void group_ends_to_smem(const int64_t* __restrict__ counts, int num_groups, int* s_end) {
+  if (threadIdx.x < 32) {   // one warp scans 32 groups per step
+    const int lane = threadIdx.x;
+    long long run = 0;
+    for (int g0 = 0; g0 < num_groups; g0 += 32) {
+      const int g = g0 + lane;
+      long long c = g < num_groups ? counts[g] : 0;
+      if (c < 0) c = 0;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const long long t = __shfl_up_sync(0xffffffffu, c, o);
+        if (lane >= o) c += t;
+      }
+      if (g < num_groups) s_end[g] = static_cast<int>(min(run + c, 2147483647LL));
+      run += __shfl_sync(0xffffffffu, c, 31);
+    }
   }
-  return -1;
+  __syncthreads();
+}
+
+// First group whose end is > row, or -1 when the row lies past every group.
+__device__ __forceinline__ int group_of_row(const int* s_end, int num_groups, int64_t row) {
+  if (num_groups == 0 || row >= s_end[num_groups - 1]) return -1;
+  int lo = 0, hi = num_groups - 1;   // invariant: s_end[hi] > row
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (s_end[mid] > row) hi = mid; else lo = mid + 1;
+  }
+  return lo;
 }
 
 // x int32 [rows, 2*half] -> y int8 [rows, half], scale [rows]; one CTA per row.
-constexpr int kDsqChunks = 4;  // half up to 256*8*4 = 8192 kept in registers
-__global__ void __launch_bounds__(kRowThreads) dequant_swiglu_quant_kernel(
-    const int32_t* __restrict__ x, const float* __restrict__ wscale, int ws_groups,
-    const float* __restrict__ ascale, const int64_t* __restrict__ group_index, int num_groups,
-    int activate_left, int64_t rows, int half, int8_t* __restrict__ y, float* __restrict__ scale) {
-  __shared__ float red[32];
-  __shared__ int s_group;
+constexpr int kDsqChunks = 4;
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS) dequant_swiglu_quant_kernel(
+    const int32_t* __restrict__ x, const float* __restrict__ wscale, int ws_groups, const float* __restrict__ ascale,
+    const int64_t* __restrict__ group_index, int num_groups, int activate_left, int64_t rows, int half,
+    int8_t* __restrict__ y, float* __restrict__ scale) {
+  __shared__ float red[THREADS / 32];
+  extern __shared__ int s_end[];
+  if (group_index != nullptr) group_ends_to_smem<THREADS>(group_index, num_groups, s_end);
   const int nchunk = half >> 3;
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
-    if (threadIdx.x == 0) s_group = group_index ? group_of_row(group_index, num_groups, row) : 0;
-    __syncthreads();
-    const int g = s_group;
+    const int g = group_index != nullptr ? group_of_row(s_end, num_groups, row) : 0;   // uniform over the CTA
     int8_t* yr = y + row * half;
     if (g < 0) {  // row outside every group
-      for (int ch = threadIdx.x; ch < nchunk; ch += kRowThreads) *reinterpret_cast<uint2*>(yr + ch * 8) = make_uint2(0, 0);
+      for (int ch = threadIdx.x; ch < nchunk; ch += THREADS) *reinterpret_cast<uint2*>(yr + ch * 8) = make_uint2(0, 0);
       if (threadIdx.x == 0) scale[row] = 0.f;
-      __syncthreads();
       continue;
     }
     const float as = ascale ? ascale[row] : 1.0f;
     const float* ws = wscale ? wscale + (ws_groups > 1 ? static_cast<int64_t>(g) * 2 * half : 0) : nullptr;
     const int32_t* xr = x + row * 2 * half;
-    float h[kDsqChunks][8];
-    float amax = 0.f;
     auto compute = [&](int ch, float (&o)[8]) {
       const int c = ch * 8;
-      int4 l0 = *reinterpret_cast<const int4*>(xr + c), l1 = *reinterpret_cast<const int4*>(xr + c + 4);
-      int4 r0 = *reinterpret_cast<const int4*>(xr + half + c), r1 = *reinterpret_cast<const int4*>(xr + half + c + 4);
-      const int li[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
-      const int ri[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+      const int4 l0 = *reinterpret_cast<const int4*>(xr + c), l1 = *reinterpret_cast<const int4*>(xr + c + 4);
+      const int4 r0 = *reinterpret_cast<const int4*>(xr + half + c), r1 = *reinterpret_cast<const int4*>(xr + half + c + 4);
+      float l[8] = {__int2float_rn(l0.x), __int2float_rn(l0.y), __int2float_rn(l0.z), __int2float_rn(l0.w),
+                    __int2float_rn(l1.x), __int2float_rn(l1.y), __int2float_rn(l1.z), __int2float_rn(l1.w)};
+      float r[8] = {__int2float_rn(r0.x), __int2float_rn(r0.y), __int2float_rn(r0.z), __int2float_rn(r0.w),
+                    __int2float_rn(r1.x), __int2float_rn(r1.y), __int2float_rn(r1.z), __int2float_rn(r1.w)};
+      float wl[8], wr[8];
+      if (ws) {
+        Elem<float>::load8(ws + c, wl);
+        Elem<float>::load8(ws + half + c, wr);
+      }
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        float l = __fmul_rn(__int2float_rn(li[k]), as);
-        float r = __fmul_rn(__int2float_rn(ri[k]), as);
+        float lv = __fmul_rn(l[k], as), rv = __fmul_rn(r[k], as);
         if (ws) {
-          l = __fmul_rn(l, ws[c + k]);
-          r = __fmul_rn(r, ws[half + c + k]);
+          lv = __fmul_rn(lv, wl[k]);
+          rv = __fmul_rn(rv, wr[k]);
         }
-        o[k] = activate_left ? silu_mul(l, r) : silu_mul(r, l);
+        o[k] = activate_left ? silu_mul(lv, rv) : silu_mul(rv, lv);
       }
     };
+    float h[kDsqChunks][8];
+    float amax = 0.f;
 #pragma unroll
     for (int cc = 0; cc < kDsqChunks; ++cc) {
-      const int ch = threadIdx.x + cc * kRowThreads;
+      const int ch = threadIdx.x + cc * THREADS;
       if (ch < nchunk) {
         compute(ch, h[cc]);
 #pragma unroll
         for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(h[cc][k]));
       }
     }
-    for (int ch = threadIdx.x + kDsqChunks * kRowThreads; ch < nchunk; ch += kRowThreads) {
+    for (int ch = threadIdx.x + kDsqChunks * THREADS; ch < nchunk; ch += THREADS) {
       float t[8];
       compute(ch, t);
 #pragma unroll
       for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(t[k]));
     }
-    amax = block_max(amax, red);
+    amax = cta_max<THREADS>(amax, red);
     const float sc = __fdiv_rn(amax, 127.0f);
     if (threadIdx.x == 0) scale[row] = sc;
 #pragma unroll
     for (int cc = 0; cc < kDsqChunks; ++cc) {
-      const int ch = threadIdx.x + cc * kRowThreads;
-      if (ch < nchunk) store8_i8(yr + ch * 8, h[cc], sc);
+      const int ch = threadIdx.x + cc * THREADS;
+      if (ch < nchunk) *reinterpret_cast<uint2*>(yr + ch * 8) = quant8(h[cc], sc);
     }
-    for (int ch = threadIdx.x + kDsqChunks * kRowThreads; ch < nchunk; ch += kRowThreads) {
+    for (int ch = threadIdx.x + kDsqChunks * THREADS; ch < nchunk; ch += THREADS) {
       float t[8];
       compute(ch, t);
-      store8_i8(yr + ch * 8, t, sc);
+      *reinterpret_cast<uint2*>(yr + ch * 8) = quant8(t, sc);
     }
   }
 }
 
-// Second phase of the fused gate_up GEMM: h fp32 [rows, cols] + row amax bits -> int8 + scale; rows at or
-// past *valid_rows give zeros.  Also used nowhere else; lives here with the other row quantisers.
-__global__ void __launch_bounds__(kRowThreads) quant_from_f32_kernel(const float* __restrict__ h,
-                                                                    const uint32_t* __restrict__ amax_bits,
-                                                                    const int64_t* __restrict__ group_list,
-                                                                    int group_list_type, int num_groups,
-                                                                    int64_t rows, int cols,
-                                                                    int8_t* __restrict__ y,
-                                                                    float* __restrict__ scale) {
-  __shared__ int64_t s_valid;
-  if (threadIdx.x == 0) {
-    int64_t v = 0;
+// Second phase of the fused gate_up GEMM: h fp32 [rows, cols] + row amax bits -> int8 + scale; rows at or past the
+// rows covered by group_list give zeros.
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS) quant_from_f32_kernel(const float* __restrict__ h,
+                                                                const uint32_t* __restrict__ amax_bits,
+                                                                const int64_t* __restrict__ group_list,
+                                                                int group_list_type, int num_groups, int64_t rows,
+                                                                int cols, int8_t* __restrict__ y,
+                                                                float* __restrict__ scale) {
+  __shared__ long long s_valid;
+  if (threadIdx.x < 32) {
+    long long v = 0;
     if (group_list_type == 0) {
       v = num_groups > 0 ? group_list[num_groups - 1] : 0;
     } else {
-      for (int g = 0; g < num_groups; ++g) v += group_list[g] > 0 ? group_list[g] : 0;
+      for (int g = threadIdx.x; g < num_groups; g += 32) v += group_list[g] > 0 ? group_list[g] : 0;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     }
-    s_valid = v;
+    if (threadIdx.x == 0) s_valid = v;
   }
   __syncthreads();
   const int64_t valid = s_valid;
@@ -219,28 +233,52 @@ __global__ void __launch_bounds__(kRowThreads) quant_from_f32_kernel(const float
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     int8_t* yr = y + row * cols;
     if (row >= valid) {
-      for (int ch = threadIdx.x; ch < nchunk; ch += kRowThreads) *reinterpret_cast<uint2*>(yr + ch * 8) = make_uint2(0, 0);
+      for (int ch = threadIdx.x; ch < nchunk; ch += THREADS) *reinterpret_cast<uint2*>(yr + ch * 8) = make_uint2(0, 0);
       if (threadIdx.x == 0) scale[row] = 0.f;
       continue;
     }
     const float sc = __fdiv_rn(__uint_as_float(amax_bits[row]), 127.0f);
     if (threadIdx.x == 0) scale[row] = sc;
     const float* hr = h + row * cols;
-    for (int ch = threadIdx.x; ch < nchunk; ch += kRowThreads) {
-      float t[8];
-      Elem<float>::load8(hr + ch * 8, t);
-      store8_i8(yr + ch * 8, t, sc);
+    for (int ch0 = threadIdx.x; ch0 < nchunk; ch0 += 4 * THREADS) {
+      float t[4][8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (ch0 + i * THREADS < nchunk) Elem<float>::load8(hr + (ch0 + i * THREADS) * 8, t[i]);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (ch0 + i * THREADS < nchunk) *reinterpret_cast<uint2*>(yr + (ch0 + i * THREADS) * 8) = quant8(t[i], sc);
     }
   }
 }
+
+// CTAs per SM for a row kernel of THREADS threads (register-limited estimate), times the SM count.
+static int row_grid(int64_t rows, int threads) { return grid_for(rows, threads >= 256 ? 5 : threads >= 128 ? 10 : 16); }
 
 int launch_quant_from_f32(const float* h, const uint32_t* amax_bits, const int64_t* group_list,
                           int group_list_type, int num_groups, int64_t rows, int cols, int8_t* y,
                           float* scale, cudaStream_t st) {
   if (rows == 0) return TAB_OK;
-  quant_from_f32_kernel<<<grid_for(rows, 8), kRowThreads, 0, st>>>(h, amax_bits, group_list, group_list_type,
-                                                                   num_groups, rows, cols, y, scale);
+  const int nchunk = cols / 8;
+  if (nchunk <= 256)
+    quant_from_f32_kernel<64><<<row_grid(rows, 64), 64, 0, st>>>(h, amax_bits, group_list, group_list_type, num_groups, rows, cols, y, scale);
+  else
+    quant_from_f32_kernel<256><<<row_grid(rows, 256), 256, 0, st>>>(h, amax_bits, group_list, group_list_type, num_groups, rows, cols, y, scale);
   return check_launch("quant_from_f32");
+}
+
+template <typename T>
+static void launch_dynamic_quant(const void* x, const void* smooth, int64_t rows, int cols, int8_t* y, float* scale,
+                                 cudaStream_t st) {
+  const int nchunk = cols / 8;
+  const T* xp = static_cast<const T*>(x);
+  const T* sp = static_cast<const T*>(smooth);
+  if (nchunk <= 64 * kMaxChunks / 2)
+    dynamic_quant_kernel<T, 64><<<row_grid(rows, 64), 64, 0, st>>>(xp, sp, rows, cols, y, scale);
+  else if (nchunk <= 128 * kMaxChunks)
+    dynamic_quant_kernel<T, 128><<<row_grid(rows, 128), 128, 0, st>>>(xp, sp, rows, cols, y, scale);
+  else
+    dynamic_quant_kernel<T, 256><<<row_grid(rows, 256), 256, 0, st>>>(xp, sp, rows, cols, y, scale);
 }
 
 }  // namespace tab
@@ -255,19 +293,11 @@ extern "C" int tab_dynamic_quant(const void* x, int x_dtype, const void* smooth,
   if (cols % 16 != 0 || cols > (1 << 24)) return fail(TAB_ERR_ALIGNMENT, "dynamic_quant: cols=%lld must be a multiple of 16", (long long)cols);
   if (!aligned16(x) || !aligned16(y) || (smooth && !aligned16(smooth))) return fail(TAB_ERR_ALIGNMENT, "dynamic_quant: pointers must be 16-byte aligned");
   cudaStream_t st = as_stream(stream);
-  const int grid = grid_for(rows, 8);
   switch (x_dtype) {
-    case TAB_BF16:
-      dynamic_quant_kernel<__nv_bfloat16><<<grid, kRowThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(smooth), rows, (int)cols, y, scale);
-      break;
-    case TAB_F16:
-      dynamic_quant_kernel<__half><<<grid, kRowThreads, 0, st>>>(static_cast<const __half*>(x), static_cast<const __half*>(smooth), rows, (int)cols, y, scale);
-      break;
-    case TAB_F32:
-      dynamic_quant_kernel<float><<<grid, kRowThreads, 0, st>>>(static_cast<const float*>(x), static_cast<const float*>(smooth), rows, (int)cols, y, scale);
-      break;
-    default:
-      return fail(TAB_ERR_UNSUPPORTED, "dynamic_quant: input dtype %d (want 5, 6 or 15)", x_dtype);
+    case TAB_BF16: launch_dynamic_quant<__nv_bfloat16>(x, smooth, rows, (int)cols, y, scale, st); break;
+    case TAB_F16: launch_dynamic_quant<__half>(x, smooth, rows, (int)cols, y, scale, st); break;
+    case TAB_F32: launch_dynamic_quant<float>(x, smooth, rows, (int)cols, y, scale, st); break;
+    default: return fail(TAB_ERR_UNSUPPORTED, "dynamic_quant: input dtype %d (want 5, 6 or 15)", x_dtype);
   }
   return check_launch("dynamic_quant");
 }
@@ -305,11 +335,19 @@ extern "C" int tab_dequant_swiglu_quant(const int32_t* x, const float* weight_sc
   if (rows == 0) return TAB_OK;
   if (!x || !y || !scale) return fail(TAB_ERR_BAD_ARG, "dequant_swiglu_quant: null pointer");
   const int64_t half = cols / 2;
-  if (half % 8 != 0 || !aligned16(x) || !aligned16(y)) return fail(TAB_ERR_ALIGNMENT, "dequant_swiglu_quant: cols/2=%lld must be a multiple of 8 and pointers 16-byte aligned", (long long)half);
+  if (half % 8 != 0 || !aligned16(x) || !aligned16(y) || (weight_scale && !aligned16(weight_scale)))
+    return fail(TAB_ERR_ALIGNMENT, "dequant_swiglu_quant: cols/2=%lld must be a multiple of 8 and pointers 16-byte aligned", (long long)half);
   if (weight_scale && ws_groups > 1 && (!group_index || num_groups != ws_groups))
     return fail(TAB_ERR_BAD_ARG, "dequant_swiglu_quant: per-group weight_scale [%lld, cols] needs group_index of the same length (got %lld)", (long long)ws_groups, (long long)num_groups);
-  if (num_groups > 4096) return fail(TAB_ERR_UNSUPPORTED, "dequant_swiglu_quant: more than 4096 groups");
-  dequant_swiglu_quant_kernel<<<grid_for(rows, 8), kRowThreads, 0, as_stream(stream)>>>(
-      x, weight_scale, (int)ws_groups, activation_scale, group_index, (int)num_groups, activate_left, rows, (int)half, y, scale);
+  if (num_groups > kMaxDsqGroups) return fail(TAB_ERR_UNSUPPORTED, "dequant_swiglu_quant: more than %d groups", kMaxDsqGroups);
+  cudaStream_t st = as_stream(stream);
+  const int nchunk = (int)(half / 8);
+  const size_t smem = group_index ? static_cast<size_t>(num_groups) * sizeof(int) : 0;
+  if (nchunk <= 64 * kDsqChunks)
+    dequant_swiglu_quant_kernel<64><<<row_grid(rows, 64), 64, smem, st>>>(x, weight_scale, (int)ws_groups, activation_scale, group_index, (int)num_groups, activate_left, rows, (int)half, y, scale);
+  else if (nchunk <= 128 * kDsqChunks)
+    dequant_swiglu_quant_kernel<128><<<row_grid(rows, 128), 128, smem, st>>>(x, weight_scale, (int)ws_groups, activation_scale, group_index, (int)num_groups, activate_left, rows, (int)half, y, scale);
+  else
+    dequant_swiglu_quant_kernel<256><<<row_grid(rows, 256), 256, smem, st>>>(x, weight_scale, (int)ws_groups, activation_scale, group_index, (int)num_groups, activate_left, rows, (int)half, y, scale);
   return check_launch("dequant_swiglu_quant");
 }

@@ -66,29 +66,31 @@ __global__ void __launch_bounds__(kChunk) route_hist_kernel(const int32_t* __res
   for (int i = threadIdx.x; i < nb; i += kChunk) chunk_hist[blockIdx.x * nb + i] = s_hist[i];
 }
 
-// Phase 2 (one CTA): totals per expert, their exclusive scan, and the base offset of every (chunk, expert).
-// chunk_hist is overwritten in place with those bases.  expert_count int32 [nb] (optional second copy out).
-__global__ void __launch_bounds__(1024) route_scan_kernel(int* __restrict__ chunk_hist, int nchunks, int nb,
-                                                          int* __restrict__ expert_count,
-                                                          int* __restrict__ expert_count_out) {
-  __shared__ int s_tot[kMaxExperts];
-  __shared__ int s_warp[33];
-  for (int e = threadIdx.x; e < nb; e += 1024) {
-    int t = 0;
-    for (int c = 0; c < nchunks; ++c) t += chunk_hist[c * nb + e];
-    s_tot[e] = t;
-    expert_count[e] = t;
-    if (expert_count_out) expert_count_out[e] = t;
-  }
-  __syncthreads();
-  block_exclusive_scan(s_tot, nb, s_warp);
-  for (int e = threadIdx.x; e < nb; e += 1024) {
-    int run = s_tot[e];
-    for (int c = 0; c < nchunks; ++c) {
-      const int h = chunk_hist[c * nb + e];
-      chunk_hist[c * nb + e] = run;
-      run += h;
+// Phase 2: one warp per expert turns that expert's column of chunk_hist into an exclusive prefix over the chunks
+// (in place) and writes the expert's total.  expert_count int32 [nb] (optional second copy out).
+constexpr int kScanWarps = 8;
+__global__ void __launch_bounds__(kScanWarps * 32) route_scan_kernel(int* __restrict__ chunk_hist, int nchunks, int nb,
+                                                                    int* __restrict__ expert_count,
+                                                                    int* __restrict__ expert_count_out) {
+  const int lane = threadIdx.x & 31;
+  const int e = blockIdx.x * kScanWarps + (threadIdx.x >> 5);
+  if (e >= nb) return;
+  int run = 0;
+  for (int c0 = 0; c0 < nchunks; c0 += 32) {
+    const int c = c0 + lane;
+    const int h = c < nchunks ? chunk_hist[c * nb + e] : 0;
+    int incl = h;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
     }
+    if (c < nchunks) chunk_hist[c * nb + e] = run + incl - h;
+    run += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  if (lane == 0) {
+    expert_count[e] = run;
+    if (expert_count_out) expert_count_out[e] = run;
   }
 }
 
@@ -99,13 +101,18 @@ __global__ void __launch_bounds__(1024) route_scan_kernel(int* __restrict__ chun
 __global__ void __launch_bounds__(kChunk) route_scatter_kernel(const int32_t* __restrict__ expert,
                                                                const int32_t* __restrict__ src_val, int n, int nb,
                                                                const int* __restrict__ chunk_base,
+                                                               const int* __restrict__ expert_count,
                                                                int32_t* __restrict__ sorted_expert,
                                                                int32_t* __restrict__ sorted_src,
                                                                int32_t* __restrict__ inverse, int* status) {
-  extern __shared__ unsigned short s_wcnt[];  // [32 warps][nb]
+  extern __shared__ unsigned short s_wcnt[];  // [32 warps][nb], then int s_base[nb]
+  __shared__ int s_warp[33];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int* s_base = reinterpret_cast<int*>(s_wcnt + 32 * nb);   // first row of every expert = exclusive scan of totals
   for (int i = tid; i < 32 * nb; i += kChunk) s_wcnt[i] = 0;
+  for (int i = tid; i < nb; i += kChunk) s_base[i] = expert_count[i];
   __syncthreads();
+  block_exclusive_scan(s_base, nb, s_warp);
   const int f = blockIdx.x * kChunk + tid;
   const bool valid = f < n;
   const int key = valid ? clamp_expert(expert[f], nb, status) : -1;
@@ -124,7 +131,7 @@ __global__ void __launch_bounds__(kChunk) route_scatter_kernel(const int32_t* __
   }
   __syncthreads();
   if (valid) {
-    const int pos = chunk_base[blockIdx.x * nb + key] + s_wcnt[warp * nb + key] + rank_in_warp;
+    const int pos = s_base[key] + chunk_base[blockIdx.x * nb + key] + s_wcnt[warp * nb + key] + rank_in_warp;
     const int sv = src_val ? src_val[f] : f;
     sorted_expert[pos] = key;
     if (sorted_src) sorted_src[pos] = sv;
@@ -161,108 +168,118 @@ static SortScratch carve(void* ws, int64_t n, int64_t nb, bool need_sorted_exper
 static int run_sort(const int32_t* expert, const int32_t* src_val, int64_t n, int64_t nb, const SortScratch& s,
                     int32_t* sorted_expert, int32_t* inverse, int32_t* expert_count_out, cudaStream_t st) {
   const int nchunks = static_cast<int>((n + kChunk - 1) / kChunk);
-  const size_t scatter_smem = static_cast<size_t>(32) * nb * sizeof(unsigned short);
+  const size_t scatter_smem = static_cast<size_t>(32) * nb * sizeof(unsigned short) + static_cast<size_t>(nb) * sizeof(int);
   if (scatter_smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(route_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(scatter_smem));
     if (e != cudaSuccess) return fail(TAB_ERR_CUDA, "routing: shared memory opt-in failed: %s", cudaGetErrorString(e));
   }
   route_hist_kernel<<<nchunks, kChunk, nb * sizeof(int), st>>>(expert, (int)n, (int)nb, s.chunk_hist, s.status);
-  route_scan_kernel<<<1, 1024, 0, st>>>(s.chunk_hist, nchunks, (int)nb, s.expert_count, expert_count_out);
-  route_scatter_kernel<<<nchunks, kChunk, scatter_smem, st>>>(expert, src_val, (int)n, (int)nb, s.chunk_hist,
+  route_scan_kernel<<<(int)((nb + kScanWarps - 1) / kScanWarps), kScanWarps * 32, 0, st>>>(s.chunk_hist, nchunks, (int)nb,
+                                                                                          s.expert_count, expert_count_out);
+  route_scatter_kernel<<<nchunks, kChunk, scatter_smem, st>>>(expert, src_val, (int)n, (int)nb, s.chunk_hist, s.expert_count,
                                                              sorted_expert, s.sorted_src, inverse, s.status);
   return check_launch("routing sort");
 }
 
 // dst[i] = src[(idx[i] % mod)] for i < rows; one CTA per row, 16-byte vectors.
-__global__ void __launch_bounds__(256) gather_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ idx,
-                                                          int mod, int64_t rows, int vec_per_row,
-                                                          uint4* __restrict__ dst) {
+constexpr int kRowCopyThreads = 128;
+__global__ void __launch_bounds__(kRowCopyThreads) gather_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ idx,
+                                                                      int mod, int64_t rows, int vec_per_row,
+                                                                      uint4* __restrict__ dst) {
   for (int64_t i = blockIdx.x; i < rows; i += gridDim.x) {
     const int64_t s = idx[i] % mod;
-    const uint4* sp = src + s * vec_per_row;
-    uint4* dp = dst + i * vec_per_row;
-    for (int v = threadIdx.x; v < vec_per_row; v += 256) dp[v] = sp[v];
+    copy_row16<kRowCopyThreads>(dst + i * vec_per_row, src + s * vec_per_row, vec_per_row);
   }
 }
 
 // Sender side of dispatch: one CTA per token; quantise the row once (or copy it), then write the K copies
-// to their sorted positions.  cols % 16 == 0.
-constexpr int kPackThreads = 256;
+// to their sorted positions.  cols % 16 == 0.  The row stays in registers in raw form between the passes.
 constexpr int kPackChunks = 8;
-template <typename T, bool kQuant>
-__global__ void __launch_bounds__(kPackThreads) dispatch_pack_kernel(const T* __restrict__ x,
-                                                                    const int32_t* __restrict__ expand_idx,
-                                                                    int64_t tokens, int K, int cols,
-                                                                    void* __restrict__ send_rows,
-                                                                    float* __restrict__ send_scales) {
-  __shared__ float red[32];
+constexpr int kPackMaxK = 256;
+template <typename T, bool kQuant, int THREADS>
+__global__ void __launch_bounds__(THREADS) dispatch_pack_kernel(const T* __restrict__ x,
+                                                               const int32_t* __restrict__ expand_idx,
+                                                               int64_t tokens, int K, int cols,
+                                                               void* __restrict__ send_rows,
+                                                               float* __restrict__ send_scales) {
+  __shared__ float red[THREADS / 32];
+  __shared__ int s_pos[kPackMaxK];
   const int nchunk = cols >> 3;
   for (int64_t t = blockIdx.x; t < tokens; t += gridDim.x) {
     const T* xr = x + t * cols;
+    __syncthreads();   // previous token's positions are no longer read
+    for (int k = threadIdx.x; k < K; k += THREADS) s_pos[k] = expand_idx[t * K + k];
     if constexpr (kQuant) {
-      float v[kPackChunks][8];
+      Raw8<T> raw[kPackChunks];
+#pragma unroll
+      for (int c = 0; c < kPackChunks; ++c) {
+        const int ch = threadIdx.x + c * THREADS;
+        if (ch < nchunk) raw[c].load(xr + ch * 8);
+      }
       float amax = 0.f;
 #pragma unroll
       for (int c = 0; c < kPackChunks; ++c) {
-        const int ch = threadIdx.x + c * kPackThreads;
+        const int ch = threadIdx.x + c * THREADS;
         if (ch < nchunk) {
-          Elem<T>::load8(xr + ch * 8, v[c]);
+          float v[8];
+          raw[c].unpack(v);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[c][i]));
+          for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
         }
       }
-      for (int ch = threadIdx.x + kPackChunks * kPackThreads; ch < nchunk; ch += kPackThreads) {
-        float tmp[8];
-        Elem<T>::load8(xr + ch * 8, tmp);
+      for (int ch = threadIdx.x + kPackChunks * THREADS; ch < nchunk; ch += THREADS) {
+        float v[8];
+        Elem<T>::load8(xr + ch * 8, v);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(tmp[i]));
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
       }
-      amax = warp_max(amax);
-      if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
-      __syncthreads();
-      float r = (threadIdx.x & 31) < (kPackThreads >> 5) ? red[threadIdx.x & 31] : 0.f;
-      amax = warp_max(r);
-      __syncthreads();
+      amax = cta_max<THREADS>(amax, red);   // its barriers also publish s_pos
       const float sc = __fdiv_rn(amax, 127.0f);
       int8_t* out = static_cast<int8_t*>(send_rows);
 #pragma unroll
       for (int c = 0; c < kPackChunks; ++c) {
-        const int ch = threadIdx.x + c * kPackThreads;
+        const int ch = threadIdx.x + c * THREADS;
         if (ch < nchunk) {
-          uint2 o;
-          o.x = pack4_i8(quant_i8(v[c][0], sc), quant_i8(v[c][1], sc), quant_i8(v[c][2], sc), quant_i8(v[c][3], sc));
-          o.y = pack4_i8(quant_i8(v[c][4], sc), quant_i8(v[c][5], sc), quant_i8(v[c][6], sc), quant_i8(v[c][7], sc));
-          for (int k = 0; k < K; ++k) {
-            const int64_t pos = expand_idx[t * K + k];
-            *reinterpret_cast<uint2*>(out + pos * cols + ch * 8) = o;
-          }
+          float v[8];
+          raw[c].unpack(v);
+          const uint2 o = quant8(v, sc);
+          for (int k = 0; k < K; ++k) *reinterpret_cast<uint2*>(out + static_cast<int64_t>(s_pos[k]) * cols + ch * 8) = o;
         }
       }
-      for (int ch = threadIdx.x + kPackChunks * kPackThreads; ch < nchunk; ch += kPackThreads) {
-        float tmp[8];
-        Elem<T>::load8(xr + ch * 8, tmp);
-        uint2 o;
-        o.x = pack4_i8(quant_i8(tmp[0], sc), quant_i8(tmp[1], sc), quant_i8(tmp[2], sc), quant_i8(tmp[3], sc));
-        o.y = pack4_i8(quant_i8(tmp[4], sc), quant_i8(tmp[5], sc), quant_i8(tmp[6], sc), quant_i8(tmp[7], sc));
-        for (int k = 0; k < K; ++k) {
-          const int64_t pos = expand_idx[t * K + k];
-          *reinterpret_cast<uint2*>(out + pos * cols + ch * 8) = o;
-        }
+      for (int ch = threadIdx.x + kPackChunks * THREADS; ch < nchunk; ch += THREADS) {
+        float v[8];
+        Elem<T>::load8(xr + ch * 8, v);
+        const uint2 o = quant8(v, sc);
+        for (int k = 0; k < K; ++k) *reinterpret_cast<uint2*>(out + static_cast<int64_t>(s_pos[k]) * cols + ch * 8) = o;
       }
-      if (threadIdx.x < K) send_scales[expand_idx[t * K + threadIdx.x]] = sc;
+      if (threadIdx.x < K) send_scales[s_pos[threadIdx.x]] = sc;
+      for (int k = threadIdx.x + THREADS; k < K; k += THREADS) send_scales[s_pos[k]] = sc;
     } else {
+      __syncthreads();
       T* out = static_cast<T*>(send_rows);
       const int nvec = cols * static_cast<int>(sizeof(T)) / 16;
       const uint4* sp = reinterpret_cast<const uint4*>(xr);
-      for (int vi = threadIdx.x; vi < nvec; vi += kPackThreads) {
+      for (int vi = threadIdx.x; vi < nvec; vi += THREADS) {
         const uint4 val = sp[vi];
-        for (int k = 0; k < K; ++k) {
-          const int64_t pos = expand_idx[t * K + k];
-          reinterpret_cast<uint4*>(out + pos * cols)[vi] = val;
-        }
+        for (int k = 0; k < K; ++k) reinterpret_cast<uint4*>(out + static_cast<int64_t>(s_pos[k]) * cols)[vi] = val;
       }
-      if (threadIdx.x < K) send_scales[expand_idx[t * K + threadIdx.x]] = 0.f;
+      for (int k = threadIdx.x; k < K; k += THREADS) send_scales[s_pos[k]] = 0.f;
     }
+  }
+}
+
+template <typename T>
+static void launch_pack(const void* x, const int32_t* expand_idx, int64_t T_, int K, int H, int quant_mode, void* rows,
+                        float* scales, cudaStream_t st) {
+  const T* xp = static_cast<const T*>(x);
+  const bool small = H / 8 <= 128 * kPackChunks;
+  const int grid = grid_for(T_, small ? 10 : 5);
+  if (quant_mode == 2) {
+    if (small) dispatch_pack_kernel<T, true, 128><<<grid, 128, 0, st>>>(xp, expand_idx, T_, K, H, rows, scales);
+    else dispatch_pack_kernel<T, true, 256><<<grid, 256, 0, st>>>(xp, expand_idx, T_, K, H, rows, scales);
+  } else {
+    if (small) dispatch_pack_kernel<T, false, 128><<<grid, 128, 0, st>>>(xp, expand_idx, T_, K, H, rows, scales);
+    else dispatch_pack_kernel<T, false, 256><<<grid, 256, 0, st>>>(xp, expand_idx, T_, K, H, rows, scales);
   }
 }
 
@@ -310,7 +327,7 @@ __device__ __forceinline__ int last_le(const int32_t* __restrict__ off, int lo, 
   return lo;
 }
 
-__global__ void __launch_bounds__(256) exchange_rows_kernel(const uint4* __restrict__ src, const float* __restrict__ src_scales,
+__global__ void __launch_bounds__(kRowCopyThreads) exchange_rows_kernel(const uint4* __restrict__ src, const float* __restrict__ src_scales,
                                                             const int32_t* __restrict__ plan, int R, int E_l,
                                                             int slot_rows, int direction, int vec_per_row,
                                                             int64_t dst_rows, int zero_fill, uint4* __restrict__ dst,
@@ -348,11 +365,10 @@ __global__ void __launch_bounds__(256) exchange_rows_kernel(const uint4* __restr
     }
     uint4* dp = dst + i * vec_per_row;
     if (srow >= 0) {
-      const uint4* sp = src + srow * vec_per_row;
-      for (int v = threadIdx.x; v < vec_per_row; v += 256) dp[v] = sp[v];
+      copy_row16<kRowCopyThreads>(dp, src + srow * vec_per_row, vec_per_row);
       if (dst_scales && threadIdx.x == 0) dst_scales[i] = src_scales[srow];
     } else if (zero_fill) {
-      for (int v = threadIdx.x; v < vec_per_row; v += 256) dp[v] = make_uint4(0, 0, 0, 0);
+      for (int v = threadIdx.x; v < vec_per_row; v += kRowCopyThreads) dp[v] = make_uint4(0, 0, 0, 0);
       if (dst_scales && threadIdx.x == 0) dst_scales[i] = 0.f;
     }
   }
@@ -442,7 +458,7 @@ extern "C" int tab_moe_init_routing(const void* x, int x_dtype, const int32_t* r
   if (rc != TAB_OK) return rc;
   const int64_t out_rows = (T < active_num ? T : active_num) * K;
   if (out_rows > 0) {
-    gather_rows_kernel<<<grid_for(out_rows, 8), 256, 0, st>>>(static_cast<const uint4*>(x), s.sorted_src, (int)T, out_rows,
+    gather_rows_kernel<<<grid_for(out_rows, 16), kRowCopyThreads, 0, st>>>(static_cast<const uint4*>(x), s.sorted_src, (int)T, out_rows,
                                                               (int)(H * es / 16), static_cast<uint4*>(expanded_x));
     rc = check_launch("init_routing gather");
   }
@@ -483,18 +499,8 @@ extern "C" int tab_moe_dispatch_pack(const void* x, int x_dtype, const int32_t* 
   SortScratch s = carve(workspace, n, num_experts, true);
   rc = run_sort(expert_ids, nullptr, n, num_experts, s, s.sorted_expert, expand_idx, expert_counts, st);
   if (rc != TAB_OK) return rc;
-  const int grid = grid_for(T, 8);
-  if (x_dtype == TAB_BF16) {
-    if (quant_mode == 2)
-      dispatch_pack_kernel<__nv_bfloat16, true><<<grid, kPackThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), expand_idx, T, (int)K, (int)H, send_rows, send_scales);
-    else
-      dispatch_pack_kernel<__nv_bfloat16, false><<<grid, kPackThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), expand_idx, T, (int)K, (int)H, send_rows, send_scales);
-  } else {
-    if (quant_mode == 2)
-      dispatch_pack_kernel<__half, true><<<grid, kPackThreads, 0, st>>>(static_cast<const __half*>(x), expand_idx, T, (int)K, (int)H, send_rows, send_scales);
-    else
-      dispatch_pack_kernel<__half, false><<<grid, kPackThreads, 0, st>>>(static_cast<const __half*>(x), expand_idx, T, (int)K, (int)H, send_rows, send_scales);
-  }
+  if (x_dtype == TAB_BF16) launch_pack<__nv_bfloat16>(x, expand_idx, T, (int)K, (int)H, quant_mode, send_rows, send_scales, st);
+  else launch_pack<__half>(x, expand_idx, T, (int)K, (int)H, quant_mode, send_rows, send_scales, st);
   return check_launch("dispatch_pack");
 }
 
@@ -521,7 +527,7 @@ extern "C" int tab_moe_exchange_rows(const void* src, const float* src_scales, c
   if ((dst_scales != nullptr) != (src_scales != nullptr)) return fail(TAB_ERR_BAD_ARG, "exchange_rows: scales must be given on both sides or neither");
   if (row_bytes <= 0 || row_bytes % 16 != 0 || !aligned16(src) || !aligned16(dst))
     return fail(TAB_ERR_ALIGNMENT, "exchange_rows: row_bytes=%lld must be a multiple of 16 and pointers 16-byte aligned", (long long)row_bytes);
-  exchange_rows_kernel<<<grid_for(dst_rows, 8), 256, 0, as_stream(stream)>>>(
+  exchange_rows_kernel<<<grid_for(dst_rows, 16), kRowCopyThreads, 0, as_stream(stream)>>>(
       static_cast<const uint4*>(src), src_scales, plan, (int)R, (int)E_l, (int)slot_rows, direction, (int)(row_bytes / 16),
       dst_rows, zero_fill, static_cast<uint4*>(dst), dst_scales);
   return check_launch("exchange_rows");

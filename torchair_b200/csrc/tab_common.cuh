@@ -121,4 +121,83 @@ __device__ __forceinline__ float silu_mul(float a, float b) {
   return __fmul_rn(s, b);
 }
 
+
+// ---- raw (unconverted) storage of 8 consecutive elements, to keep a row in few registers between passes ----
+template <typename T>
+struct Raw8 {
+  uint4 r;
+  __device__ __forceinline__ void load(const T* p) { r = *reinterpret_cast<const uint4*>(p); }
+  __device__ __forceinline__ void unpack(float (&v)[8]) const;
+};
+
+template <>
+__device__ __forceinline__ void Raw8<__nv_bfloat16>::unpack(float (&v)[8]) const {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 f = __bfloat1622float2(h[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+
+template <>
+__device__ __forceinline__ void Raw8<__half>::unpack(float (&v)[8]) const {
+  const __half2* h = reinterpret_cast<const __half2*>(&r);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 f = __half22float2(h[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+
+template <>
+struct Raw8<float> {
+  float4 a, b;
+  __device__ __forceinline__ void load(const float* p) {
+    a = *reinterpret_cast<const float4*>(p);
+    b = *reinterpret_cast<const float4*>(p + 4);
+  }
+  __device__ __forceinline__ void unpack(float (&v)[8]) const {
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+};
+
+// Maximum over the CTA; `red` holds one float per warp.  All threads must call it.
+template <int THREADS>
+__device__ __forceinline__ float cta_max(float v, float* red) {
+  v = warp_max(v);
+  if constexpr (THREADS == 32) return v;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = lane < THREADS / 32 ? red[lane] : 0.f;
+  r = warp_max(r);
+  __syncthreads();
+  return r;
+}
+
+__device__ __forceinline__ uint2 quant8(const float (&v)[8], float scale) {
+  uint2 o;
+  o.x = pack4_i8(quant_i8(v[0], scale), quant_i8(v[1], scale), quant_i8(v[2], scale), quant_i8(v[3], scale));
+  o.y = pack4_i8(quant_i8(v[4], scale), quant_i8(v[5], scale), quant_i8(v[6], scale), quant_i8(v[7], scale));
+  return o;
+}
+
+// Copies one row of nvec 16-byte vectors with the CTA, four loads in flight per thread before the stores.
+template <int THREADS>
+__device__ __forceinline__ void copy_row16(uint4* __restrict__ dst, const uint4* __restrict__ src, int nvec) {
+  for (int v = threadIdx.x; v < nvec; v += 4 * THREADS) {
+    uint4 t[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (v + i * THREADS < nvec) t[i] = src[v + i * THREADS];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (v + i * THREADS < nvec) dst[v + i * THREADS] = t[i];
+  }
+}
+
 }  // namespace tab
