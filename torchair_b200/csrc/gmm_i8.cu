@@ -375,7 +375,7 @@ static int launch_prefill(const CUtensorMap& tm_w, const CUtensorMap& tm_x, cons
   const int grid = static_cast<int>(max_items < sms ? max_items : sms);
   cudaError_t e = cudaFuncSetAttribute(gmm_i8_prefill_kernel<FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmemBytes);
   if (e != cudaSuccess) return fail(TAB_ERR_CUDA, "grouped_matmul: shared memory opt-in failed: %s", cudaGetErrorString(e));
-  gmm_i8_prefill_kernel<FUSED><<<grid, kGmmThreads, kPfSmemBytes, st>>>(tm_w, tm_x, p);
+  gmm_i8_prefill_kernel<FUSED><<<grid, kPfThreads, kPfSmemBytes, st>>>(tm_w, tm_x, p);
   return check_launch("grouped_matmul (prefill)");
 }
 

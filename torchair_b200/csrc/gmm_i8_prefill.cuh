@@ -28,10 +28,13 @@ constexpr int kPfTableBytes = 2 * (kMaxGroups + 1) * 4;
 constexpr int kPfSmemBytes = 1024 + kPfStages * kPfStageBytes + kPfCtrlBytes + kPfScaleBytes + kPfTableBytes;
 static_assert(kPfSmemBytes <= kSmemLimit, "prefill GEMM shared memory");
 
-__device__ __forceinline__ void epilogue_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+constexpr int kPfEpiWarps = 8;                       // two warps per TMEM lane quarter, each takes half of the columns
+constexpr int kPfThreads = 64 + kPfEpiWarps * 32;    // producer warp + MMA warp + epilogue warps
+
+__device__ __forceinline__ void epilogue_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 template <bool FUSED>
-__global__ void __launch_bounds__(kGmmThreads, 1)
+__global__ void __launch_bounds__(kPfThreads, 1)
 gmm_i8_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const GmmParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
@@ -61,7 +64,7 @@ gmm_i8_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
     }
     for (int b = 0; b < kPfBufs; ++b) {
       ptx::mbar_init(bar_tfull(b), 1);
-      ptx::mbar_init(bar_tempty(b), 4);
+      ptx::mbar_init(bar_tempty(b), kPfEpiWarps);
     }
     ptx::mbar_init(bar_drain, 1);
     *s_abort = 0;
@@ -145,10 +148,11 @@ gmm_i8_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
       }
     }
   } else {
-    // ---------------- epilogue: warps 2..5, thread = token row ----------------
+    // ---------------- epilogue: warps 2..9, thread = token row, two warps split the columns of a row ----------------
     const int quarter = warp & 3;
     const int r_local = quarter * 32 + lane;          // TMEM lane = token row inside the tile
-    const int et = threadIdx.x - 64;                  // 0..127 among the epilogue threads
+    const int et = threadIdx.x - 64;                  // 0..255 among the epilogue threads
+    const int chalf = (warp - 2) >> 2;                // which half of the tile's columns this warp handles
     int buf = 0;
     uint32_t tphase = 0;
     for (int w = blockIdx.x; w < total_items; w += gridDim.x) {
@@ -160,8 +164,8 @@ gmm_i8_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
         const int c_second = FUSED ? p.half + it.ct * 128 : it.ct * 256 + 128;
         const int lim_first = FUSED ? p.half : p.N;
         const float* wrow = p.w_scale ? p.w_scale + static_cast<int64_t>(it.e) * p.N : nullptr;
-        ws[et] = (wrow && c_first + et < lim_first) ? wrow[c_first + et] : 1.f;
-        ws[128 + et] = (wrow && c_second + et < p.N) ? wrow[c_second + et] : 1.f;
+        if (et < 128) ws[et] = (wrow && c_first + et < lim_first) ? wrow[c_first + et] : 1.f;
+        else ws[et] = (wrow && c_second + et - 128 < p.N) ? wrow[c_second + et - 128] : 1.f;
       }
       if (et == 0) s_got[buf] = bounded_wait(bar_tfull(buf), tphase, s_abort, 14) ? 1 : 0;
       epilogue_bar_sync();
@@ -176,7 +180,7 @@ gmm_i8_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
         float amax = 0.f;
         float* hrow = p.h_out + static_cast<int64_t>(row) * p.half + cg0;
 #pragma unroll 1
-        for (int c = 0; c < 128; c += 16) {
+        for (int c = chalf * 64; c < chalf * 64 + 64; c += 16) {
           int g[16], u[16];
           __syncwarp();
           ptx::tmem_ld16(t0 + c, g);
@@ -209,7 +213,7 @@ gmm_i8_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
         const int c0 = it.ct * 256;
         const bool vec_ok = (p.N & 7) == 0;
 #pragma unroll 1
-        for (int c = 0; c < 256; c += 16) {
+        for (int c = chalf * 128; c < chalf * 128 + 128; c += 16) {
           int a[16];
           __syncwarp();                                // the loads below are warp-collective
           ptx::tmem_ld16(t0 + c, a);
