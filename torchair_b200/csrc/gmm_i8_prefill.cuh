@@ -24,8 +24,10 @@ constexpr int kPfStages = 4;
 constexpr int kPfBufs = 2;
 constexpr int kPfCtrlBytes = 256;
 constexpr int kPfScaleBytes = 2 * kPfCols * 4;       // weight scales of the tile, double-buffered
-constexpr int kPfTableBytes = 2 * (kMaxGroups + 1) * 4;
-constexpr int kPfSmemBytes = 1024 + kPfStages * kPfStageBytes + kPfCtrlBytes + kPfScaleBytes + kPfTableBytes;
+constexpr int kPfTableBytes = (2 * (kMaxGroups + 1) * 4 + 15) / 16 * 16;
+constexpr int kPfOutPitch = 80;                      // bytes per staged row: 32 16-bit values + 16 bytes of padding
+constexpr int kPfOutStageBytes = 8 * 32 * kPfOutPitch;   // per epilogue warp: 32 rows x 32 columns of 16-bit output
+constexpr int kPfSmemBytes = 1024 + kPfStages * kPfStageBytes + kPfCtrlBytes + kPfScaleBytes + kPfTableBytes + kPfOutStageBytes;
 static_assert(kPfSmemBytes <= kSmemLimit, "prefill GEMM shared memory");
 
 constexpr int kPfEpiWarps = 8;                       // two warps per TMEM lane quarter, each takes half of the columns
@@ -53,6 +55,7 @@ gmm_i8_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   float* s_wscale = reinterpret_cast<float*>(ctrl + kPfCtrlBytes);     // [2][256]
   int* s_start = reinterpret_cast<int*>(ctrl + kPfCtrlBytes + kPfScaleBytes);
   int* s_pref = s_start + (kMaxGroups + 1);
+  uint8_t* s_out = ctrl + kPfCtrlBytes + kPfScaleBytes + kPfTableBytes;   // 16-byte aligned: every part above is
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int E = p.E;
@@ -212,6 +215,56 @@ gmm_i8_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
       } else {
         const int c0 = it.ct * 256;
         const bool vec_ok = (p.N & 7) == 0;
+        if (p.out_dtype != TAB_I32 && vec_ok) {
+          // 16-bit output: 32 columns at a time go through a per-warp shared-memory patch so that global stores
+          // are 64-byte row segments (four lanes per row) instead of one 16-byte piece per lane and row.
+          uint8_t* patch = s_out + (warp - 2) * 32 * kPfOutPitch;
+          const int row_base = s_start[it.e] + it.tt * kPfTokens + quarter * 32;
+          const int row_end = s_start[it.e + 1];
+          const int esz = 2;
+#pragma unroll 1
+          for (int c = chalf * 128; c < chalf * 128 + 128; c += 32) {
+            int a[16], b[16];
+            __syncwarp();                              // the loads below are warp-collective; the patch is free again
+            ptx::tmem_ld16(t0 + c, a);
+            ptx::tmem_ld16(t0 + c + 16, b);
+            ptx::tmem_ld_wait();
+            float f[32];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              f[j] = __fmul_rn(__fmul_rn(__int2float_rn(a[j]), ts), ws[c + j]);
+              f[16 + j] = __fmul_rn(__fmul_rn(__int2float_rn(b[j]), ts), ws[c + 16 + j]);
+            }
+            uint4* prow = reinterpret_cast<uint4*>(patch + lane * kPfOutPitch);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              uint4 v;
+              if (p.out_dtype == TAB_BF16) {
+                __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) h2[i] = __floats2bfloat162_rn(f[8 * k + 2 * i], f[8 * k + 2 * i + 1]);
+              } else {
+                __half2* h2 = reinterpret_cast<__half2*>(&v);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) h2[i] = __floats2half2_rn(f[8 * k + 2 * i], f[8 * k + 2 * i + 1]);
+              }
+              prow[k] = v;
+            }
+            __syncwarp();
+            const int piece = lane & 3;                // 16-byte piece of the 64-byte row segment
+            const bool cvalid = c0 + c + piece * 8 < p.N;
+#pragma unroll
+            for (int it8 = 0; it8 < 4; ++it8) {
+              const int r = it8 * 8 + (lane >> 2);
+              const int grow = row_base + r;
+              if (grow < row_end && cvalid) {
+                const uint4 v = *reinterpret_cast<const uint4*>(patch + r * kPfOutPitch + piece * 16);
+                uint8_t* o = static_cast<uint8_t*>(p.out) + (static_cast<int64_t>(grow) * p.N + c0 + c) * esz + piece * 16;
+                *reinterpret_cast<uint4*>(o) = v;
+              }
+            }
+          }
+        } else {
 #pragma unroll 1
         for (int c = chalf * 128; c < chalf * 128 + 128; c += 16) {
           int a[16];
@@ -219,45 +272,25 @@ gmm_i8_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
           ptx::tmem_ld16(t0 + c, a);
           ptx::tmem_ld_wait();
           if (rvalid && c0 + c < p.N) {
-          const bool full = c0 + c + 16 <= p.N;
-          if (p.out_dtype == TAB_I32) {
-            int* o = static_cast<int*>(p.out) + static_cast<int64_t>(row) * p.N + c0 + c;
-            if (full && (p.N & 3) == 0) {
+            if (p.out_dtype == TAB_I32) {
+              int* o = static_cast<int*>(p.out) + static_cast<int64_t>(row) * p.N + c0 + c;
+              if (c0 + c + 16 <= p.N && (p.N & 3) == 0) {
 #pragma unroll
-              for (int j = 0; j < 16; j += 4) *reinterpret_cast<int4*>(o + j) = make_int4(a[j], a[j + 1], a[j + 2], a[j + 3]);
-            } else {
-              for (int j = 0; j < 16; ++j)
-                if (c0 + c + j < p.N) o[j] = a[j];
-            }
-          } else {
-            float f[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) f[j] = __fmul_rn(__fmul_rn(__int2float_rn(a[j]), ts), ws[c + j]);
-            if (p.out_dtype == TAB_BF16) {
-              __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(row) * p.N + c0 + c;
-              if (full && vec_ok) {
-                const float (&f0)[8] = *reinterpret_cast<const float (*)[8]>(f);
-                const float (&f1)[8] = *reinterpret_cast<const float (*)[8]>(f + 8);
-                Elem<__nv_bfloat16>::store8(o, f0);
-                Elem<__nv_bfloat16>::store8(o + 8, f1);
+                for (int j = 0; j < 16; j += 4) *reinterpret_cast<int4*>(o + j) = make_int4(a[j], a[j + 1], a[j + 2], a[j + 3]);
               } else {
                 for (int j = 0; j < 16; ++j)
-                  if (c0 + c + j < p.N) o[j] = __float2bfloat16_rn(f[j]);
+                  if (c0 + c + j < p.N) o[j] = a[j];
               }
             } else {
-              __half* o = static_cast<__half*>(p.out) + static_cast<int64_t>(row) * p.N + c0 + c;
-              if (full && vec_ok) {
-                const float (&f0)[8] = *reinterpret_cast<const float (*)[8]>(f);
-                const float (&f1)[8] = *reinterpret_cast<const float (*)[8]>(f + 8);
-                Elem<__half>::store8(o, f0);
-                Elem<__half>::store8(o + 8, f1);
-              } else {
-                for (int j = 0; j < 16; ++j)
-                  if (c0 + c + j < p.N) o[j] = __float2half_rn(f[j]);
+              for (int j = 0; j < 16; ++j) {
+                if (c0 + c + j >= p.N) break;
+                const float f = __fmul_rn(__fmul_rn(__int2float_rn(a[j]), ts), ws[c + j]);
+                if (p.out_dtype == TAB_BF16) static_cast<__nv_bfloat16*>(p.out)[static_cast<int64_t>(row) * p.N + c0 + c + j] = __float2bfloat16_rn(f);
+                else static_cast<__half*>(p.out)[static_cast<int64_t>(row) * p.N + c0 + c + j] = __float2half_rn(f);
               }
             }
           }
-          }
+        }
         }
       }
       ptx::tc_fence_before();
