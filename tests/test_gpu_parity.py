@@ -375,3 +375,21 @@ def test_torch_compile_backend_runs_the_ops_and_captures_a_cuda_graph(dev):
     torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=1e-2, atol=1e-2)
     assert backend.counters["fused_gate_up"] == fused_before + 1, "the FX pass should fuse gate_up with its epilogue"
     assert backend.counters["captures"] == cap_before + 1 and backend.counters["replays"] >= 3
+
+
+def test_quantiser_fast_path_is_exact_at_ties_and_extreme_scales(dev):
+    """The quantiser approximates v/scale by v*(1/scale) and redoes the division only near rounding ties: rows built
+    from exact ties (k + 0.5) * scale, denormal-scale rows and huge rows must still match IEEE division bit for bit."""
+    g = torch.Generator().manual_seed(77)
+    rows = []
+    for s in (1.0, 3.0, 0.1, 1.0 / 3.0, 7e-3, 1e-38, 3e38 / 127):
+        k = torch.arange(-127, 127, dtype=torch.float32) + 0.5
+        r = torch.cat([k * s, torch.tensor([127.0 * s, -127.0 * s])])
+        rows.append(r)
+        rows.append(r * (1 + 2.0 ** -23))
+        rows.append(r * (1 - 2.0 ** -23))
+    x = torch.stack(rows)
+    x = torch.cat([x, torch.randn(64, x.shape[1], generator=g) * 1e-3])
+    q, s = O.dynamic_quant(x)
+    qg, sg = npu.npu_dynamic_quant(x.to(dev))
+    assert torch.equal(s, sg.cpu()) and torch.equal(q, qg.cpu())

@@ -38,10 +38,14 @@ __global__ void __launch_bounds__(THREADS) dynamic_quant_kernel(const T* __restr
     for (int c = 0; c < kMaxChunks; ++c) {
       const int ch = threadIdx.x + c * THREADS;
       if (ch < nchunk) {
-        float v[8];
-        value(raw[c], ch, v);
+        if (smooth == nullptr) {
+          amax = fmaxf(amax, raw_amax(raw[c]));
+        } else {
+          float v[8];
+          value(raw[c], ch, v);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+          for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+        }
       }
     }
     for (int ch = threadIdx.x + kMaxChunks * THREADS; ch < nchunk; ch += THREADS) {
@@ -53,8 +57,8 @@ __global__ void __launch_bounds__(THREADS) dynamic_quant_kernel(const T* __restr
       for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
     }
     amax = cta_max<THREADS>(amax, red);
-    const float sc = __fdiv_rn(amax, 127.0f);
-    if (threadIdx.x == 0) scale[row] = sc;
+    const RowQuant sc = make_row_quant(amax);
+    if (threadIdx.x == 0) scale[row] = sc.scale;
     int8_t* yr = y + row * cols;
 #pragma unroll
     for (int c = 0; c < kMaxChunks; ++c) {
@@ -62,7 +66,7 @@ __global__ void __launch_bounds__(THREADS) dynamic_quant_kernel(const T* __restr
       if (ch < nchunk) {
         float v[8];
         value(raw[c], ch, v);
-        *reinterpret_cast<uint2*>(yr + ch * 8) = quant8(v, sc);
+        __stcs(reinterpret_cast<uint2*>(yr + ch * 8), quant8(v, sc));
       }
     }
     for (int ch = threadIdx.x + kMaxChunks * THREADS; ch < nchunk; ch += THREADS) {
@@ -191,8 +195,8 @@ __global__ void __launch_bounds__(THREADS) dequant_swiglu_quant_kernel(
       for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(t[k]));
     }
     amax = cta_max<THREADS>(amax, red);
-    const float sc = __fdiv_rn(amax, 127.0f);
-    if (threadIdx.x == 0) scale[row] = sc;
+    const RowQuant sc = make_row_quant(amax);
+    if (threadIdx.x == 0) scale[row] = sc.scale;
 #pragma unroll
     for (int cc = 0; cc < kDsqChunks; ++cc) {
       const int ch = threadIdx.x + cc * THREADS;
@@ -237,8 +241,8 @@ __global__ void __launch_bounds__(THREADS) quant_from_f32_kernel(const float* __
       if (threadIdx.x == 0) scale[row] = 0.f;
       continue;
     }
-    const float sc = __fdiv_rn(__uint_as_float(amax_bits[row]), 127.0f);
-    if (threadIdx.x == 0) scale[row] = sc;
+    const RowQuant sc = make_row_quant(__uint_as_float(amax_bits[row]));
+    if (threadIdx.x == 0) scale[row] = sc.scale;
     const float* hr = h + row * cols;
     for (int ch0 = threadIdx.x; ch0 < nchunk; ch0 += 4 * THREADS) {
       float t[4][8];
@@ -274,11 +278,11 @@ static void launch_dynamic_quant(const void* x, const void* smooth, int64_t rows
   const T* xp = static_cast<const T*>(x);
   const T* sp = static_cast<const T*>(smooth);
   if (nchunk <= 64 * kMaxChunks / 2)
-    dynamic_quant_kernel<T, 64><<<row_grid(rows, 64), 64, 0, st>>>(xp, sp, rows, cols, y, scale);
+    dynamic_quant_kernel<T, 64><<<grid_for(rows, 16), 64, 0, st>>>(xp, sp, rows, cols, y, scale);
   else if (nchunk <= 128 * kMaxChunks)
-    dynamic_quant_kernel<T, 128><<<row_grid(rows, 128), 128, 0, st>>>(xp, sp, rows, cols, y, scale);
+    dynamic_quant_kernel<T, 128><<<grid_for(rows, 8), 128, 0, st>>>(xp, sp, rows, cols, y, scale);
   else
-    dynamic_quant_kernel<T, 256><<<row_grid(rows, 256), 256, 0, st>>>(xp, sp, rows, cols, y, scale);
+    dynamic_quant_kernel<T, 256><<<grid_for(rows, 4), 256, 0, st>>>(xp, sp, rows, cols, y, scale);
 }
 
 }  // namespace tab

@@ -186,8 +186,11 @@ constexpr int kRowCopyThreads = 128;
 __global__ void __launch_bounds__(kRowCopyThreads) gather_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ idx,
                                                                       int mod, int64_t rows, int vec_per_row,
                                                                       uint4* __restrict__ dst) {
-  for (int64_t i = blockIdx.x; i < rows; i += gridDim.x) {
-    const int64_t s = idx[i] % mod;
+  int64_t i = blockIdx.x;
+  int next = i < rows ? idx[i] : 0;
+  for (; i < rows; i += gridDim.x) {
+    const int64_t s = next % mod;
+    if (i + gridDim.x < rows) next = idx[i + gridDim.x];   // fetched while this row is being copied
     copy_row16<kRowCopyThreads>(dst + i * vec_per_row, src + s * vec_per_row, vec_per_row);
   }
 }
@@ -220,12 +223,7 @@ __global__ void __launch_bounds__(THREADS) dispatch_pack_kernel(const T* __restr
 #pragma unroll
       for (int c = 0; c < kPackChunks; ++c) {
         const int ch = threadIdx.x + c * THREADS;
-        if (ch < nchunk) {
-          float v[8];
-          raw[c].unpack(v);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-        }
+        if (ch < nchunk) amax = fmaxf(amax, raw_amax(raw[c]));
       }
       for (int ch = threadIdx.x + kPackChunks * THREADS; ch < nchunk; ch += THREADS) {
         float v[8];
@@ -234,7 +232,8 @@ __global__ void __launch_bounds__(THREADS) dispatch_pack_kernel(const T* __restr
         for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
       }
       amax = cta_max<THREADS>(amax, red);   // its barriers also publish s_pos
-      const float sc = __fdiv_rn(amax, 127.0f);
+      const RowQuant rq = make_row_quant(amax);
+      const float sc = rq.scale;
       int8_t* out = static_cast<int8_t*>(send_rows);
 #pragma unroll
       for (int c = 0; c < kPackChunks; ++c) {
@@ -242,15 +241,15 @@ __global__ void __launch_bounds__(THREADS) dispatch_pack_kernel(const T* __restr
         if (ch < nchunk) {
           float v[8];
           raw[c].unpack(v);
-          const uint2 o = quant8(v, sc);
-          for (int k = 0; k < K; ++k) *reinterpret_cast<uint2*>(out + static_cast<int64_t>(s_pos[k]) * cols + ch * 8) = o;
+          const uint2 o = quant8(v, rq);
+          for (int k = 0; k < K; ++k) __stcs(reinterpret_cast<uint2*>(out + static_cast<int64_t>(s_pos[k]) * cols + ch * 8), o);
         }
       }
       for (int ch = threadIdx.x + kPackChunks * THREADS; ch < nchunk; ch += THREADS) {
         float v[8];
         Elem<T>::load8(xr + ch * 8, v);
-        const uint2 o = quant8(v, sc);
-        for (int k = 0; k < K; ++k) *reinterpret_cast<uint2*>(out + static_cast<int64_t>(s_pos[k]) * cols + ch * 8) = o;
+        const uint2 o = quant8(v, rq);
+        for (int k = 0; k < K; ++k) __stcs(reinterpret_cast<uint2*>(out + static_cast<int64_t>(s_pos[k]) * cols + ch * 8), o);
       }
       if (threadIdx.x < K) send_scales[s_pos[threadIdx.x]] = sc;
       for (int k = threadIdx.x + THREADS; k < K; k += THREADS) send_scales[s_pos[k]] = sc;

@@ -179,24 +179,93 @@ __device__ __forceinline__ float cta_max(float v, float* red) {
   return r;
 }
 
-__device__ __forceinline__ uint2 quant8(const float (&v)[8], float scale) {
+// ---- fast exact row quantiser ------------------------------------------------------------------------------
+// Produces rint(v / scale) clamped to +-127 -- bit for bit what IEEE division gives -- in about six full-rate FP32
+// instructions per element (conversion instructions issue at 1/8 rate and IEEE division costs a dozen more):
+//   * the quotient is approximated by r = v * (1/scale), at most 2 ulp (< 1.6e-5 for |r| <= 127) from the exact one;
+//     |v| <= amax keeps |r| below 127.5, so no clamp is needed;
+//   * adding 1.5 * 2^23 rounds r half-to-even and leaves the integer in the low mantissa bits (its low byte is the
+//     two's-complement int8);
+//   * the residual v - q * scale (one FMA) tells how far the exact quotient is from q: only when that distance exceeds
+//     0.5 - 4e-5 (a rounding tie is within reach: about one value in ten thousand) are the eight values of the chunk
+//     redone with the IEEE division.  Rows whose scale is too small for a finite reciprocal use the division throughout.
+struct RowQuant {
+  float scale, inv, half_lo;
+  bool exact;   // every element takes the IEEE division
+};
+
+__device__ __forceinline__ RowQuant make_row_quant(float amax) {
+  RowQuant rq;
+  rq.scale = __fdiv_rn(amax, 127.0f);
+  rq.inv = __frcp_rn(rq.scale);
+  rq.half_lo = rq.scale * 0.49996f;
+  rq.exact = !(rq.scale > 1e-30f) || !(rq.inv < 1e30f);
+  return rq;
+}
+
+constexpr float kRoundMagic = 12582912.0f;   // 1.5 * 2^23
+
+// Word whose low byte is clamp(rint(v / scale)), by IEEE division.
+__device__ __forceinline__ uint32_t quant_word_exact(float v, float scale) {
+  const float r = fminf(fmaxf(__fdiv_rn(v, scale), -127.f), 127.f);
+  return __float_as_uint(__fadd_rn(r, kRoundMagic));
+}
+
+__device__ __forceinline__ uint32_t pack4_words(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+}
+
+__device__ __forceinline__ uint2 quant8(const float (&v)[8], const RowQuant& rq) {
+  if (!(rq.scale > 0.f)) return make_uint2(0u, 0u);
+  uint32_t w[8];
+  bool redo = rq.exact;
+  if (!redo) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float t = __fadd_rn(__fmul_rn(v[i], rq.inv), kRoundMagic);
+      const float q = __fadd_rn(t, -kRoundMagic);
+      const float e = __fmaf_rn(-q, rq.scale, v[i]);
+      redo |= fabsf(e) > rq.half_lo;
+      w[i] = __float_as_uint(t);
+    }
+  }
+  if (redo) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w[i] = quant_word_exact(v[i], rq.scale);
+  }
   uint2 o;
-  o.x = pack4_i8(quant_i8(v[0], scale), quant_i8(v[1], scale), quant_i8(v[2], scale), quant_i8(v[3], scale));
-  o.y = pack4_i8(quant_i8(v[4], scale), quant_i8(v[5], scale), quant_i8(v[6], scale), quant_i8(v[7], scale));
+  o.x = pack4_words(w[0], w[1], w[2], w[3]);
+  o.y = pack4_words(w[4], w[5], w[6], w[7]);
   return o;
 }
 
-// Copies one row of nvec 16-byte vectors with the CTA, four loads in flight per thread before the stores.
+// max |x| over the 8 packed 16-bit elements of a raw chunk, without unpacking
+__device__ __forceinline__ float raw_amax(const Raw8<__nv_bfloat16>& raw) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw.r);
+  __nv_bfloat162 m = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
+  return fmaxf(__low2float(m), __high2float(m));
+}
+__device__ __forceinline__ float raw_amax(const Raw8<__half>& raw) {
+  const __half2* h = reinterpret_cast<const __half2*>(&raw.r);
+  __half2 m = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
+  return fmaxf(__low2float(m), __high2float(m));
+}
+__device__ __forceinline__ float raw_amax(const Raw8<float>& raw) {
+  return fmaxf(fmaxf(fmaxf(fabsf(raw.a.x), fabsf(raw.a.y)), fmaxf(fabsf(raw.a.z), fabsf(raw.a.w))),
+               fmaxf(fmaxf(fabsf(raw.b.x), fabsf(raw.b.y)), fmaxf(fabsf(raw.b.z), fabsf(raw.b.w))));
+}
+
+// Copies one row of nvec 16-byte vectors with the CTA, eight loads in flight per thread before the stores.
 template <int THREADS>
 __device__ __forceinline__ void copy_row16(uint4* __restrict__ dst, const uint4* __restrict__ src, int nvec) {
-  for (int v = threadIdx.x; v < nvec; v += 4 * THREADS) {
-    uint4 t[4];
+  for (int v = threadIdx.x; v < nvec; v += 8 * THREADS) {
+    uint4 t[8];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < 8; ++i)
       if (v + i * THREADS < nvec) t[i] = src[v + i * THREADS];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-      if (v + i * THREADS < nvec) dst[v + i * THREADS] = t[i];
+    for (int i = 0; i < 8; ++i)
+      if (v + i * THREADS < nvec) __stcs(dst + v + i * THREADS, t[i]);   // streamed: keep the gathered source rows in L2
   }
 }
 
