@@ -36,6 +36,8 @@ def parse_args():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (N=1)")
+    ap.add_argument("--ep-transport", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: rows move by this library's peer-memory kernels (default) or by NCCL all-to-all")
     ap.add_argument("--kernels", action="store_true",
                     help="also time every kernel of the path alone and write the table to stderr (study aid, N=1)")
     ap.add_argument("--workload", default="auto", choices=["auto"] + sorted(EXTRA_WORKLOADS),
@@ -196,7 +198,7 @@ def gpu_arm(args):
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
-        ep.register_ep_group("ep", dist.group.WORLD)
+        ep.register_ep_group("ep", dist.group.WORLD, transport=args.ep_transport)
     name, T, H, E, K, I, zipf = workload(world, args.workload)
     E_l = E // world
     cfg = O.MoeConfig("bench", T, H, E, K, I, zipf_s=zipf)
@@ -228,7 +230,7 @@ def gpu_arm(args):
         out = layer(x_d, ids_d, wt_d)
     torch.cuda.synchronize()
     graph = None
-    if world == 1:
+    if world == 1 or args.ep_transport == "peer":     # the peer-memory exchange has no host read: one graph per rank
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             out = layer(x_d, ids_d, wt_d)
@@ -320,6 +322,8 @@ def gpu_arm(args):
     status = torchair_b200.gmm_status(dev)
     if status != 0:
         raise RuntimeError(f"grouped GEMM reported a timed-out wait (code {status})")
+    if ep.peer_status() != 0:
+        raise RuntimeError(f"a peer-memory flag wait ran out of time (code {ep.peer_status()})")
 
     peaks = {}
     try:
@@ -399,6 +403,7 @@ def gpu_arm(args):
                 "data": "synthetic",
                 "config": {"workload": name, "tokens_per_rank": T, "hidden": H, "experts": E, "experts_per_rank": E_l, "top_k": K,
                            "intermediate": I, "parallelism": f"ep{world}", "cuda_graph": graph is not None,
+                           "ep_transport": None if world == 1 else args.ep_transport,
                            "l2": "inputs larger than L2: every step streams this rank's int8 expert weights "
                                  f"({(w1.numel() + w2.numel()) / 1e9:.2f} GB) from HBM"},
                 "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

@@ -151,6 +151,40 @@ TAB_API int tab_moe_exchange_rows(const void* src, const float* src_scales, cons
                           tab_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------
+ * npu_moe_distribute_dispatch / npu_moe_distribute_combine over peer memory, for the GPUs of one node
+ * (converters moe_distribute_dispatch.py:4-45, moe_distribute_combine.py:4-60; the reference's kernels also
+ * communicate from inside the operator).  Rows are stored straight into the destination GPU's receive
+ * buffer; no library collective and no host read is involved, so the exchange can be captured in a CUDA
+ * graph.  The caller provides peer-mapped (symmetric) memory: `peer_*` arguments are DEVICE arrays of R
+ * device pointers, one per rank (entry r points into rank r's memory, this rank's own entry included).
+ *   layout on every rank: recv [R][slot_rows][row_bytes + 16] (the 16-byte tail carries the fp32 scale),
+ *   counts int32 [R][E_l], ret [R][slot_rows][row_bytes], flag arrays uint64 [R], counters uint64.
+ *   tab_ep_signal      stores (counter + 1) into peer_flags[r] for every r, then counter += 1.
+ *   tab_ep_wait        waits (bounded, ~4 s) until flags[s] >= counter + pre_increment for every s, then
+ *                      counter += 1; on expiry writes `code` into *status (device int) and continues.
+ *   tab_ep_send_rows   sender: row p of the expert-sorted rows goes to rank d = owner of its expert, slot
+ *                      [my_rank][p - first row of d]; per-expert counts go to peer_counts; expand_idx_slot[f]
+ *                      = d*slot_rows + offset is the position at which the combined row comes back.
+ *   tab_ep_unpack_rows receiver: slot records -> rows in (local expert, source) order + scales; `plan` from
+ *                      tab_moe_exchange_plan(counts, R, E_l, slot_rows, ...).
+ *   tab_ep_return_rows expert side of combine: outputs go back to slot [my_rank][send offset] of the source
+ *                      rank's `ret` buffer; the source then runs tab_moe_combine on its ret buffer with
+ *                      expand_idx_slot.
+ * ------------------------------------------------------------------------------------------------- */
+TAB_API int tab_ep_signal(void* const* peer_flags, void* counter, int64_t R, tab_stream_t stream);
+TAB_API int tab_ep_wait(const void* flags, void* counter, int64_t R, int pre_increment, int* status, int code,
+                tab_stream_t stream);
+TAB_API int tab_ep_send_rows(const void* rows, const float* scales, const int32_t* expert_counts,
+                     const int32_t* expand_idx, int64_t R, int64_t E_l, int64_t slot_rows, int64_t row_bytes,
+                     int64_t M, int64_t my_rank, void* const* peer_recv, void* const* peer_counts,
+                     int32_t* expand_idx_slot, tab_stream_t stream);
+TAB_API int tab_ep_unpack_rows(const void* recv, const int32_t* plan, int64_t R, int64_t E_l, int64_t row_bytes,
+                       int64_t dst_rows, int zero_fill, void* dst, float* dst_scales, tab_stream_t stream);
+TAB_API int tab_ep_return_rows(const void* y, const int32_t* plan, int64_t R, int64_t E_l, int64_t slot_rows,
+                       int64_t row_bytes, int64_t max_rows, int64_t my_rank, void* const* peer_ret,
+                       tab_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------
  * npu_moe_distribute_combine, receiving side (converter moe_distribute_combine.py:4-60 ->
  * MoeDistributeCombine): out[t] = sum_k expert_scales[t,k] * rows[expand_idx[t*K+k]] (+ shared[t]),
  * fp32 accumulation in ascending k, one rounding to dtype (5 or 15).

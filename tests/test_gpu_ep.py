@@ -21,7 +21,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, outdir):
+def _worker(rank, world, port, outdir, transport):
     try:
         os.environ["MASTER_ADDR"] = "127.0.0.1"
         os.environ["MASTER_PORT"] = str(port)
@@ -32,7 +32,7 @@ def _worker(rank, world, port, outdir):
         torch.cuda.set_device(rank)
         dev = torch.device("cuda", rank)
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
-        torchair_b200.register_ep_group("ep", dist.group.WORLD)
+        torchair_b200.register_ep_group("ep", dist.group.WORLD, transport=transport)
         results = {}
         for cfg_name, cfg in (("cfg0", O.CONFIGS["cfg0"]), ("skew", O.MoeConfig("skew", 96, 512, 16, 4, 256, zipf_s=1.2))):
             E_l = cfg.E // world
@@ -46,6 +46,8 @@ def _worker(rank, world, port, outdir):
                 results[(cfg_name, fused)] = out.cpu()
             results[(cfg_name, "disp")] = [t.cpu() for t in disp]
         results["status"] = torchair_b200.gmm_status(dev)
+        from torchair_b200 import ep as _ep
+        results["peer_status"] = _ep.peer_status()
         torch.save(results, os.path.join(outdir, f"rank{rank}.pt"))
         dist.barrier()
         dist.destroy_process_group()
@@ -54,14 +56,15 @@ def _worker(rank, world, port, outdir):
         open(os.path.join(outdir, f"err{rank}"), "w").write(traceback.format_exc())
 
 
+@pytest.mark.parametrize("transport", ["peer", "nccl"])
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_expert_parallel_layer_on_gpus_matches_oracle(world, tmp_path):
+def test_expert_parallel_layer_on_gpus_matches_oracle(world, transport, tmp_path):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
     port = _free_port()
     ctx = mp.get_context("spawn")
-    procs = [ctx.Process(target=_worker, args=(r, world, port, str(tmp_path))) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, str(tmp_path), transport)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
@@ -82,7 +85,17 @@ def test_expert_parallel_layer_on_gpus_matches_oracle(world, tmp_path):
             assert got[r]["status"] == 0
             d = collect[r]["disp"]
             g = got[r][(cfg_name, "disp")]
-            want = (d.expand_x, d.dynamic_scales, d.expand_idx, d.expert_token_nums, d.ep_recv_count)
+            assert got[r]["peer_status"] == 0, "a peer-memory flag wait ran out of time"
+            want_idx = d.expand_idx
+            if transport == "peer":
+                # the peer transport hands combine the slot position: owner rank * C + offset inside that owner's rows
+                E_l = cfg.E // world
+                C = cfg.T * min(E_l, cfg.K)
+                sent = torch.bincount(idl[r].reshape(-1).long() // E_l, minlength=world)
+                base = torch.cumsum(sent, 0) - sent
+                owner = torch.bucketize(d.expand_idx.long(), torch.cumsum(sent, 0), right=True)
+                want_idx = (owner * C + d.expand_idx.long() - base[owner]).to(torch.int32)
+            want = (d.expand_x, d.dynamic_scales, want_idx, d.expert_token_nums, d.ep_recv_count)
             for a, b in zip(want, g):
                 assert torch.equal(a, b), "dispatch outputs (int8 rows, scales, indices, counts) must be bit-exact"
             for fused in (True, False):

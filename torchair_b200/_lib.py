@@ -29,6 +29,11 @@ SIGNATURES = {
     "tab_moe_dispatch_pack": [_P, _I, _P, _L, _L, _L, _L, _I, _P, _P, _P, _P, _P, c_size_t, _P],
     "tab_moe_exchange_plan": [_P, _L, _L, _L, _I, _P, _P, _P, _P],
     "tab_moe_exchange_rows": [_P, _P, _P, _L, _L, _L, _I, _L, _L, _I, _P, _P, _P],
+    "tab_ep_signal": [_P, _P, _L, _P],
+    "tab_ep_wait": [_P, _P, _L, _I, _P, _I, _P],
+    "tab_ep_send_rows": [_P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P, _P, _P, _P],
+    "tab_ep_unpack_rows": [_P, _P, _L, _L, _L, _L, _I, _P, _P, _P],
+    "tab_ep_return_rows": [_P, _P, _L, _L, _L, _L, _L, _L, _P, _P],
     "tab_moe_combine": [_P, _I, _P, _P, _P, _L, _L, _L, _P, _P],
     "tab_prepack_weight_i8": [_P, _L, _L, _L, _P, _P],
     "tab_grouped_matmul_w8a8": [_P, _P, _P, _P, _P, _I, _L, _L, _L, _L, _I, _P, _P],

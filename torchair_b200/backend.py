@@ -123,8 +123,11 @@ def _has_multi_rank_exchange(gm: torch.fx.GraphModule) -> bool:
     for n in gm.graph.nodes:
         if n.op == "call_function" and n.target in ex and len(n.args) > 3:
             ws = n.args[3] if n.target is ex[0] else n.args[6]
+            group = n.args[2] if n.target is ex[0] else n.args[5]
             if not isinstance(ws, int) or ws > 1:
-                return True
+                from . import ep
+                if not (isinstance(group, str) and ep.transport_of(group, True) == "peer"):
+                    return True     # NCCL all-to-all with exact splits reads the sizes on the host
     return False
 
 

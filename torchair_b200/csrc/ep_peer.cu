@@ -1,0 +1,241 @@
+// Expert-parallel exchange over peer memory (NVLink / NVSwitch) for GPUs of one node.
+//
+// Dispatch and combine move rows with plain stores into the destination GPU's receive buffer (peer-mapped symmetric
+// memory) instead of a library collective: no host read of the split sizes, every step is a kernel on the caller's
+// stream, so a whole expert-parallel layer can live in one CUDA graph.  Remote memory is only ever WRITTEN from here,
+// with ordinary st.global; everything a later kernel reads (TMA loads of the GEMM included) is local memory.
+//
+// Buffers of rank r (all inside one symmetric allocation, same offsets on every rank):
+//   recv   [R sources][C rows][row_bytes + 16]   dispatch rows; the 16-byte tail holds the fp32 activation scale
+//   counts [R sources][E_l]  int32               rows per local expert sent by each source
+//   ret    [R owners][C rows][row_bytes]         expert outputs coming back, at the sender's own send positions
+//   flags  4 x [R] uint64                        arrival / consumption counters written by the peers
+// C = T * min(E_l, K) is the most rows one rank can send to another.
+//
+// Hand-over: a sender signals "data n is there" by storing n into its slot of the receiver's flag array after the
+// data kernel (stream order + __threadfence_system + a release store); the receiver's wait kernel spins, bounded, with
+// acquire loads.  The receiver acknowledges after it has copied the rows out, and a sender waits for the previous
+// acknowledgement before it overwrites a peer's buffer.  Counters live on the device so that a replayed CUDA graph
+// keeps counting.  A wait that runs out of time records a code in the status word and lets the stream continue.
+#include "tab_common.cuh"
+
+namespace tab {
+
+constexpr int kEpMaxRanks = 64;
+constexpr long long kEpWaitCycles = 8000000000LL;   // ~4 s: peers may be seconds apart on their first call
+
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+// One thread per peer stores the next sequence number into that peer's flag slot for this rank.
+__global__ void ep_signal_kernel(unsigned long long* const* __restrict__ peer_flags, unsigned long long* counter, int R) {
+  __shared__ unsigned long long s_value;
+  if (threadIdx.x == 0) s_value = *counter + 1;
+  __syncthreads();
+  __threadfence_system();
+  if (threadIdx.x < R) st_release_sys(peer_flags[threadIdx.x], s_value);
+  __syncthreads();
+  if (threadIdx.x == 0) *counter = s_value;
+}
+
+// Waits until every source's flag has reached the expected sequence number.  pre_increment = 1: expect counter + 1
+// (new data); 0: expect the current counter (acknowledgement of the previous round).  The counter advances either way.
+__global__ void ep_wait_kernel(const unsigned long long* __restrict__ flags, unsigned long long* counter, int R,
+                               int pre_increment, int* status, int code) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+  const unsigned long long expect = *counter + (pre_increment ? 1ull : 0ull);
+  if (threadIdx.x < R) {
+    const long long t0 = clock64();
+    while (ld_acquire_sys(flags + threadIdx.x) < expect) {
+      if (clock64() - t0 > kEpWaitCycles) {
+        s_fail = 1;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (s_fail) atomicCAS(status, 0, code);
+    *counter = *counter + 1;
+  }
+}
+
+// First sorted position of every destination rank's rows, from the per-expert counts (E = R * E_l entries).
+__device__ __forceinline__ void rank_bases_to_smem(const int32_t* __restrict__ expert_counts, int R, int E_l, int* s_base) {
+  if (threadIdx.x < R) {
+    int c = 0;
+    for (int e = 0; e < E_l; ++e) c += max(expert_counts[threadIdx.x * E_l + e], 0);
+    s_base[threadIdx.x + 1] = c;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    s_base[0] = 0;
+    for (int r = 0; r < R; ++r) s_base[r + 1] += s_base[r];
+  }
+  __syncthreads();
+}
+
+__device__ __forceinline__ int rank_of_position(const int* s_base, int R, int p) {
+  int d = 0;
+  while (d + 1 < R && s_base[d + 1] <= p) ++d;
+  return d;
+}
+
+constexpr int kEpThreads = 128;
+
+// Sender: row p of the expert-sorted send buffer goes to slot [my_rank][p - base(d)] of rank d's receive buffer.
+// CTA 0 also delivers the per-expert counts, and every pair index f gets its slot position for the combine.
+__global__ void __launch_bounds__(kEpThreads) ep_send_kernel(const uint4* __restrict__ rows, const float* __restrict__ scales,
+                                                            const int32_t* __restrict__ expert_counts,
+                                                            const int32_t* __restrict__ expand_idx, int R, int E_l, int C,
+                                                            int vec_per_row, int M, int my_rank,
+                                                            uint8_t* const* __restrict__ peer_recv,
+                                                            int32_t* const* __restrict__ peer_counts,
+                                                            int32_t* __restrict__ expand_idx_slot) {
+  __shared__ int s_base[kEpMaxRanks + 1];
+  rank_bases_to_smem(expert_counts, R, E_l, s_base);
+  const int64_t slot_bytes = static_cast<int64_t>(vec_per_row + 1) * 16;
+  if (blockIdx.x == 0) {
+    for (int i = threadIdx.x; i < R * E_l; i += kEpThreads) {
+      const int d = i / E_l, e = i - d * E_l;
+      peer_counts[d][my_rank * E_l + e] = max(expert_counts[i], 0);
+    }
+  }
+  for (int p = blockIdx.x; p < M; p += gridDim.x) {
+    const int d = rank_of_position(s_base, R, p);
+    uint8_t* slot = peer_recv[d] + (static_cast<int64_t>(my_rank) * C + (p - s_base[d])) * slot_bytes;
+    copy_row16<kEpThreads>(reinterpret_cast<uint4*>(slot), rows + static_cast<int64_t>(p) * vec_per_row, vec_per_row);
+    if (threadIdx.x == 0) {
+      const float sc = scales ? scales[p] : 0.f;
+      *reinterpret_cast<uint4*>(slot + static_cast<int64_t>(vec_per_row) * 16) = make_uint4(__float_as_uint(sc), 0u, 0u, 0u);
+    }
+  }
+  for (int f = blockIdx.x * kEpThreads + threadIdx.x; f < M; f += gridDim.x * kEpThreads) {
+    const int p = expand_idx[f];
+    const int d = rank_of_position(s_base, R, p);
+    expand_idx_slot[f] = d * C + (p - s_base[d]);
+  }
+}
+
+__device__ __forceinline__ int ep_last_le(const int32_t* __restrict__ off, int lo, int hi, int i) {
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (off[mid] <= i) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+// Receiver: slot records -> rows in (local expert, source rank) order plus their scales.  plan as written by
+// tab_moe_exchange_plan with slot_rows = C.
+__global__ void __launch_bounds__(kEpThreads) ep_unpack_kernel(const uint8_t* __restrict__ recv, const int32_t* __restrict__ plan,
+                                                              int R, int E_l, int vec_per_row, int64_t dst_rows, int zero_fill,
+                                                              uint4* __restrict__ dst, float* __restrict__ dst_scales) {
+  const int n = R * E_l;
+  const int32_t* wire_off = plan;
+  const int32_t* exp_off = plan + n;
+  const int total = exp_off[n];
+  const int64_t slot_bytes = static_cast<int64_t>(vec_per_row + 1) * 16;
+  for (int64_t i = blockIdx.x; i < dst_rows; i += gridDim.x) {
+    uint4* dp = dst + i * vec_per_row;
+    if (i < total) {
+      const int b = ep_last_le(exp_off, 0, n, static_cast<int>(i));   // b = e*R + s
+      const int e = b / R, s = b - e * R;
+      const uint8_t* rec = recv + (static_cast<int64_t>(wire_off[s * E_l + e]) + (i - exp_off[b])) * slot_bytes;
+      copy_row16<kEpThreads>(dp, reinterpret_cast<const uint4*>(rec), vec_per_row);
+      if (threadIdx.x == 0) dst_scales[i] = *reinterpret_cast<const float*>(rec + static_cast<int64_t>(vec_per_row) * 16);
+    } else if (zero_fill) {
+      for (int v = threadIdx.x; v < vec_per_row; v += kEpThreads) dp[v] = make_uint4(0, 0, 0, 0);
+      if (threadIdx.x == 0) dst_scales[i] = 0.f;
+    }
+  }
+}
+
+// Expert side of combine: row i of the (expert, source) ordered outputs returns to slot [my_rank][its send offset] of
+// the source rank's return buffer.
+__global__ void __launch_bounds__(kEpThreads) ep_return_kernel(const uint4* __restrict__ y, const int32_t* __restrict__ plan, int R,
+                                                              int E_l, int C, int vec_per_row, int my_rank,
+                                                              uint8_t* const* __restrict__ peer_ret) {
+  const int n = R * E_l;
+  const int32_t* wire_off = plan;
+  const int32_t* exp_off = plan + n;
+  const int total = exp_off[n];
+  for (int i = blockIdx.x; i < total; i += gridDim.x) {
+    const int b = ep_last_le(exp_off, 0, n, i);
+    const int e = b / R, s = b - e * R;
+    const int within = wire_off[s * E_l + e] - s * C + (i - exp_off[b]);
+    uint8_t* dstp = peer_ret[s] + (static_cast<int64_t>(my_rank) * C + within) * vec_per_row * 16;
+    copy_row16<kEpThreads>(reinterpret_cast<uint4*>(dstp), y + static_cast<int64_t>(i) * vec_per_row, vec_per_row);
+  }
+}
+
+}  // namespace tab
+
+using namespace tab;
+
+extern "C" int tab_ep_signal(void* const* peer_flags, void* counter, int64_t R, tab_stream_t stream) {
+  if (!peer_flags || !counter || R < 1 || R > kEpMaxRanks) return fail(TAB_ERR_BAD_ARG, "ep_signal: bad argument (R=%lld)", (long long)R);
+  ep_signal_kernel<<<1, 64, 0, as_stream(stream)>>>(reinterpret_cast<unsigned long long* const*>(peer_flags),
+                                                   static_cast<unsigned long long*>(counter), (int)R);
+  return check_launch("ep_signal");
+}
+
+extern "C" int tab_ep_wait(const void* flags, void* counter, int64_t R, int pre_increment, int* status, int code,
+                           tab_stream_t stream) {
+  if (!flags || !counter || !status || R < 1 || R > kEpMaxRanks) return fail(TAB_ERR_BAD_ARG, "ep_wait: bad argument (R=%lld)", (long long)R);
+  ep_wait_kernel<<<1, 64, 0, as_stream(stream)>>>(static_cast<const unsigned long long*>(flags),
+                                                 static_cast<unsigned long long*>(counter), (int)R, pre_increment, status, code);
+  return check_launch("ep_wait");
+}
+
+extern "C" int tab_ep_send_rows(const void* rows, const float* scales, const int32_t* expert_counts, const int32_t* expand_idx,
+                                int64_t R, int64_t E_l, int64_t slot_rows, int64_t row_bytes, int64_t M, int64_t my_rank,
+                                void* const* peer_recv, void* const* peer_counts, int32_t* expand_idx_slot,
+                                tab_stream_t stream) {
+  if (!expert_counts || !peer_recv || !peer_counts || R < 1 || R > kEpMaxRanks || E_l < 1 || slot_rows < 1 || my_rank < 0 || my_rank >= R)
+    return fail(TAB_ERR_BAD_ARG, "ep_send_rows: bad argument");
+  if (M > 0 && (!rows || !expand_idx || !expand_idx_slot)) return fail(TAB_ERR_BAD_ARG, "ep_send_rows: null pointer");
+  if (row_bytes <= 0 || row_bytes % 16 != 0 || (M > 0 && !aligned16(rows)) || M > (1LL << 30) || R * slot_rows > (1LL << 30))
+    return fail(TAB_ERR_ALIGNMENT, "ep_send_rows: row_bytes=%lld must be a multiple of 16, rows 16-byte aligned", (long long)row_bytes);
+  const int grid = grid_for(M > 0 ? M : 1, 16);
+  ep_send_kernel<<<grid, kEpThreads, 0, as_stream(stream)>>>(static_cast<const uint4*>(rows), scales, expert_counts, expand_idx, (int)R,
+                                                            (int)E_l, (int)slot_rows, (int)(row_bytes / 16), (int)M, (int)my_rank,
+                                                            reinterpret_cast<uint8_t* const*>(peer_recv),
+                                                            reinterpret_cast<int32_t* const*>(peer_counts), expand_idx_slot);
+  return check_launch("ep_send_rows");
+}
+
+extern "C" int tab_ep_unpack_rows(const void* recv, const int32_t* plan, int64_t R, int64_t E_l, int64_t row_bytes, int64_t dst_rows,
+                                  int zero_fill, void* dst, float* dst_scales, tab_stream_t stream) {
+  if (dst_rows == 0) return TAB_OK;
+  if (!recv || !plan || !dst || !dst_scales || R < 1 || E_l < 1 || R * E_l > 2048 || dst_rows < 0 || dst_rows > (1LL << 30))
+    return fail(TAB_ERR_BAD_ARG, "ep_unpack_rows: bad argument");
+  if (row_bytes <= 0 || row_bytes % 16 != 0 || !aligned16(recv) || !aligned16(dst))
+    return fail(TAB_ERR_ALIGNMENT, "ep_unpack_rows: row_bytes=%lld must be a multiple of 16 and pointers 16-byte aligned", (long long)row_bytes);
+  ep_unpack_kernel<<<grid_for(dst_rows, 16), kEpThreads, 0, as_stream(stream)>>>(static_cast<const uint8_t*>(recv), plan, (int)R, (int)E_l,
+                                                                              (int)(row_bytes / 16), dst_rows, zero_fill,
+                                                                              static_cast<uint4*>(dst), dst_scales);
+  return check_launch("ep_unpack_rows");
+}
+
+extern "C" int tab_ep_return_rows(const void* y, const int32_t* plan, int64_t R, int64_t E_l, int64_t slot_rows, int64_t row_bytes,
+                                  int64_t max_rows, int64_t my_rank, void* const* peer_ret, tab_stream_t stream) {
+  if (max_rows == 0) return TAB_OK;
+  if (!y || !plan || !peer_ret || R < 1 || R > kEpMaxRanks || E_l < 1 || R * E_l > 2048 || slot_rows < 1 || my_rank < 0 || my_rank >= R ||
+      max_rows < 0 || max_rows > (1LL << 30))
+    return fail(TAB_ERR_BAD_ARG, "ep_return_rows: bad argument");
+  if (row_bytes <= 0 || row_bytes % 16 != 0 || !aligned16(y))
+    return fail(TAB_ERR_ALIGNMENT, "ep_return_rows: row_bytes=%lld must be a multiple of 16 and y 16-byte aligned", (long long)row_bytes);
+  ep_return_kernel<<<grid_for(max_rows, 16), kEpThreads, 0, as_stream(stream)>>>(static_cast<const uint4*>(y), plan, (int)R, (int)E_l,
+                                                                              (int)slot_rows, (int)(row_bytes / 16), (int)my_rank,
+                                                                              reinterpret_cast<uint8_t* const*>(peer_ret));
+  return check_launch("ep_return_rows");
+}

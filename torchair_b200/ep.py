@@ -18,6 +18,7 @@ register_ep_group().
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -35,11 +36,33 @@ _SPLITS_MAX = 64
 counters = {"dispatch_calls": 0, "combine_calls": 0, "wire_bytes_sent": 0}
 
 
-def register_ep_group(name: str, process_group) -> None:
-    """Associates a group_ep name with a torch.distributed process group."""
+_transport: Dict[str, str] = {}
+_peer: Dict[tuple, "PeerExchange"] = {}
+
+
+def register_ep_group(name: str, process_group, transport: str = "auto") -> None:
+    """Associates a group_ep name with a torch.distributed process group.
+
+    transport: "peer" = rows are stored straight into the owner's receive buffer over NVLink peer memory by this
+    library's kernels (one node, CUDA-graph capturable, no host read); "nccl" = all_to_all_single with exact split
+    sizes (one host read per dispatch; also the path used for CPU tensors in tests); "auto" = peer for CUDA tensors
+    when symmetric memory can be set up, else nccl.  Every rank of the group must pass the same value.
+    """
     if not isinstance(name, str) or not name:
         raise ValueError("group name must be a non-empty string")
+    if transport not in ("auto", "peer", "nccl"):
+        raise ValueError("transport must be 'auto', 'peer' or 'nccl'")
     _groups[name] = process_group
+    _transport[name] = transport
+
+
+def transport_of(name: str, is_cuda: bool) -> str:
+    t = _transport.get(name, "auto")
+    if t == "auto":
+        t = "peer" if is_cuda and os.environ.get("TORCHAIR_B200_EP_TRANSPORT", "peer") == "peer" else "nccl"
+    if t == "peer" and not is_cuda:
+        raise RuntimeError("the peer-memory transport needs CUDA tensors")
+    return t
 
 
 def get_ep_group(name: str):
@@ -164,6 +187,138 @@ class CudaKernels:
         return out
 
 
+class PeerExchange:
+    """Peer-mapped buffers, flags and counters of one exchange configuration (see csrc/ep_peer.cu for the layout).
+
+    Built collectively (every rank of the group at the same call) on first use of a (group, T, K, H, E) combination.
+    """
+
+    KIND_DATA_D, KIND_ACK_D, KIND_DATA_C, KIND_ACK_C = 0, 1, 2, 3
+
+    def __init__(self, pg, R, rank, T, K, H, E, disp_row_bytes, device):
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer stores only
+        import torch.distributed._symmetric_memory as symm
+        self.R, self.rank, self.E_l = R, rank, E // R
+        self.C = T * min(self.E_l, K)
+        self.H = H
+        self.disp_row_bytes = disp_row_bytes
+        self.ret_row_bytes = H * 2
+        al = lambda n: (n + 255) // 256 * 256
+        self.off_recv = 0
+        self.off_counts = al(R * self.C * (disp_row_bytes + 16))
+        self.off_ret = self.off_counts + al(R * self.E_l * 4)
+        self.off_ctrl = self.off_ret + al(R * self.C * self.ret_row_bytes)
+        ctrl_bytes = al(4 * R * 8) + 256
+        total = self.off_ctrl + ctrl_bytes
+        self.buf = symm.empty(total, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        torch.cuda.synchronize(device)
+        self.hdl = symm.rendezvous(self.buf, pg)
+        ptrs = [int(p) for p in self.hdl.buffer_ptrs]
+        dev_ptrs = lambda offs: torch.tensor(offs, dtype=torch.int64, device=device)
+        self.peer_recv = dev_ptrs([p + self.off_recv for p in ptrs])
+        self.peer_counts = dev_ptrs([p + self.off_counts for p in ptrs])
+        self.peer_ret = dev_ptrs([p + self.off_ret for p in ptrs])
+        # flag array k of a rank lives at off_ctrl + k*R*8; this rank's slot in it is entry `rank`
+        self.peer_flags = [dev_ptrs([p + self.off_ctrl + k * R * 8 + rank * 8 for p in ptrs]) for k in range(4)]
+        base = self.buf.data_ptr()
+        self.flags_local = [base + self.off_ctrl + k * R * 8 for k in range(4)]
+        cbase = base + self.off_ctrl + al(4 * R * 8)
+        self.sig_counter = [cbase + k * 8 for k in range(4)]
+        self.wait_counter = [cbase + 32 + k * 8 for k in range(4)]
+        self.status_ptr = cbase + 64
+        self.recv_local = self.buf[self.off_recv:self.off_counts]
+        self.counts_local = self.buf[self.off_counts:self.off_counts + R * self.E_l * 4].view(torch.int32)
+        self.ret_local = self.buf[self.off_ret:self.off_ret + R * self.C * self.ret_row_bytes]
+        dist.barrier(pg)     # nobody signals into a buffer that is not zeroed and mapped yet
+
+    def _stream(self):
+        return ctypes.c_void_p(torch.cuda.current_stream(self.buf.device).cuda_stream)
+
+    def signal(self, kind):
+        _lib.call("tab_ep_signal", _ptr(self.peer_flags[kind]), ctypes.c_void_p(self.sig_counter[kind]), self.R, self._stream())
+
+    def wait(self, kind, pre_increment):
+        _lib.call("tab_ep_wait", ctypes.c_void_p(self.flags_local[kind]), ctypes.c_void_p(self.wait_counter[kind]), self.R,
+                  int(pre_increment), ctypes.c_void_p(self.status_ptr), 100 + kind, self._stream())
+
+    def status(self) -> int:
+        """Synchronises and returns 0, or 100 + kind of the first flag wait that ran out of time."""
+        torch.cuda.synchronize(self.buf.device)
+        off = self.status_ptr - self.buf.data_ptr()
+        return int(self.buf[off:off + 4].view(torch.int32).item())
+
+
+def peer_exchange(group_ep, pg, R, rank, T, K, H, E, disp_row_bytes, device) -> PeerExchange:
+    key = (group_ep, R, rank, T, K, H, E, disp_row_bytes, device.index)
+    px = _peer.get(key)
+    if px is None:
+        px = PeerExchange(pg, R, rank, T, K, H, E, disp_row_bytes, device)
+        _peer[key] = px
+    return px
+
+
+def peer_status() -> int:
+    """0 if no peer-memory wait ever timed out on this rank (synchronises the device)."""
+    for px in _peer.values():
+        st = px.status()
+        if st:
+            return st
+    return 0
+
+
+def _dispatch_peer(kern, x, expert_ids, group_ep, pg, R, rank, E, quant_mode, nums_type, send, tp_recv, expand_scales):
+    send_rows, send_scales, expand_idx, counts = send
+    T, K = expert_ids.shape
+    H = x.shape[1]
+    E_l = E // R
+    dev = x.device
+    row_bytes = H * send_rows.element_size()
+    px = peer_exchange(group_ep, pg, R, rank, T, K, H, E, row_bytes, dev)
+    A = R * px.C
+    st = px._stream()
+    slot_idx = torch.empty_like(expand_idx)
+    px.wait(px.KIND_ACK_D, 0)                     # the peers have copied my previous rows out of their buffers
+    _lib.call("tab_ep_send_rows", _ptr(send_rows), _ptr(send_scales), _ptr(counts), _ptr(expand_idx), R, E_l, px.C, row_bytes,
+              T * K, rank, _ptr(px.peer_recv), _ptr(px.peer_counts), _ptr(slot_idx), st)
+    px.signal(px.KIND_DATA_D)
+    px.wait(px.KIND_DATA_D, 1)                    # every source's rows and counts have landed here
+    plan, nums, ep_recv = kern.exchange_plan(px.counts_local.view(R, E_l), R, E_l, px.C, nums_type)
+    expand_x = torch.empty((A, H), dtype=send_rows.dtype, device=dev)
+    dyn = torch.empty((A,), dtype=torch.float32, device=dev)
+    _lib.call("tab_ep_unpack_rows", _ptr(px.recv_local), _ptr(plan), R, E_l, row_bytes, A, 1, _ptr(expand_x), _ptr(dyn), st)
+    px.signal(px.KIND_ACK_D)
+    counters["wire_bytes_sent"] += T * K * (row_bytes + 16)
+    return expand_x, dyn, slot_idx, nums, ep_recv, tp_recv, expand_scales
+
+
+def _combine_peer(kern, expand_x, expert_ids, expand_idx, ep_send_counts, expert_scales, group_ep, pg, R, rank, E, shared):
+    T, K = expert_ids.shape
+    H = expand_x.shape[1]
+    E_l = E // R
+    if expand_x.element_size() != 2:
+        raise NotImplementedError("npu_moe_distribute_combine over peer memory: expand_x must be bfloat16 or float16")
+    px = None
+    for key, cand in _peer.items():
+        if key[0] == group_ep and key[1:7] == (R, rank, T, K, H, E) and key[8] == expand_x.device.index:
+            px = cand
+    if px is None:
+        raise RuntimeError("npu_moe_distribute_combine: no matching npu_moe_distribute_dispatch ran on this group")
+    st = px._stream()
+    y = expand_x.contiguous()
+    recv_counts = ep_send_counts.view(E_l, R).t().contiguous()
+    plan, _, _ = kern.exchange_plan(recv_counts, R, E_l, px.C, 1)
+    px.wait(px.KIND_ACK_C, 0)                     # the sources have reduced the rows of the previous combine
+    _lib.call("tab_ep_return_rows", _ptr(y), _ptr(plan), R, E_l, px.C, H * 2, y.shape[0], rank, _ptr(px.peer_ret), st)
+    px.signal(px.KIND_DATA_C)
+    px.wait(px.KIND_DATA_C, 1)
+    back = px.ret_local.view(expand_x.dtype).view(R * px.C, H)
+    out = kern.combine(back, expand_idx, expert_scales, shared, T, K)
+    px.signal(px.KIND_ACK_C)
+    counters["wire_bytes_sent"] += T * K * H * 2
+    return out
+
+
 def _remember(key, value):
     if len(_splits) >= _SPLITS_MAX:
         _splits.pop(next(iter(_splits)))
@@ -202,6 +357,9 @@ def dispatch(kern, x, expert_ids, group_ep, R, rank, E, quant_mode, nums_type, t
     if dist.get_world_size(pg) != R or dist.get_rank(pg) != rank:
         raise RuntimeError(f"npu_moe_distribute_dispatch: group {group_ep!r} has size/rank "
                            f"{dist.get_world_size(pg)}/{dist.get_rank(pg)}, arguments say {R}/{rank}")
+    if transport_of(group_ep, x.is_cuda) == "peer":
+        return _dispatch_peer(kern, x, expert_ids, group_ep, pg, R, rank, E, quant_mode, nums_type,
+                              (send_rows, send_scales, expand_idx, counts), tp_recv, expand_scales)
     recv_counts = torch.empty_like(counts)                       # [R, E_l]: rows from rank s for my expert e
     dist.all_to_all_single(recv_counts, counts, group=pg)
     sums = torch.stack([counts.view(R, E_l).sum(1), recv_counts.view(R, E_l).sum(1)]).cpu()   # the one host read
@@ -231,6 +389,8 @@ def combine(kern, expand_x, expert_ids, expand_idx, ep_send_counts, expert_scale
         return kern.combine(expand_x, expand_idx, expert_scales, shared, T, K)
     pg = get_ep_group(group_ep)
     E_l = E // R
+    if transport_of(group_ep, expand_x.is_cuda) == "peer":
+        return _combine_peer(kern, expand_x, expert_ids, expand_idx, ep_send_counts, expert_scales, group_ep, pg, R, rank, E, shared)
     remembered = _splits.get((ep_send_counts.data_ptr(), expand_idx.data_ptr()))
     if remembered is not None:
         send_splits, recv_splits = remembered
