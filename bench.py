@@ -48,6 +48,7 @@ def parse_args():
 # single-GPU study cases: name -> (description, T, H, E, K, I, zipf exponent)
 EXTRA_WORKLOADS = {
     "cfg1_small": ("cfg1_small: decode shape at 1/8 scale (32 tokens, 32 experts; 1.4 GB of weights)", 32, 7168, 32, 8, 2048, 0.0),
+    "cfg2_rank": ("cfg2_rank: one rank's expert work of the 8-GPU decode (1024 rows over 32 local experts)", 128, 7168, 32, 8, 2048, 0.0),
     "cfg3_rank": ("cfg3_rank: one rank's share of the skewed 8-GPU prefill (65536 rows over 32 local experts, Zipf 1.2)",
                   8192, 7168, 32, 8, 2048, 1.2),
     "prefill_small": ("prefill_small: 2048 tokens top-8 over 8 experts of the DeepSeek-V3 expert shape (16384 rows, 2048 per expert)",

@@ -194,6 +194,41 @@ TAB_API int tab_moe_combine(const void* rows, int dtype, const int32_t* expand_i
                     const void* shared, int64_t T, int64_t K, int64_t H, void* out, tab_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------
+ * Operators next to the path.
+ *
+ * npu_moe_compute_expert_tokens (converter npu_moe_compute_expert_tokens.py:4-11 -> MoeComputeExpertTokens):
+ *   sorted_experts int32 [n] ascending; out int32 [num_experts], out[e] = number of entries <= e.
+ *
+ * npu_moe_gating_top_k_softmax (converter moe_gating_top_k_softmax.py:9-19 -> MoeGatingTopKSoftmax,
+ *   experiment_ops.h:2222-2241), `finished` absent: softmax over the experts in fp32, then the k largest
+ *   (ties: lower expert id).  x [tokens, num_experts] of dtype 5, 6 or 15 (num_experts <= 1024);
+ *   y [tokens, k] same dtype; expert_idx, row_idx int32 [tokens, k], row_idx[t, j] = j*tokens + t.
+ *
+ * npu_moe_finalize_routing (converter npu_moe_finalize_routing.py:21-41 -> MoeFinalizeRouting(V2)), drop_pad_mode 0:
+ *   out[t] = sum_k scales[t,k] * (rows[src_to_dst[k*T + t]] + bias[expert_for_row[t,k]]) + skip1[t] + skip2[t];
+ *   fp32 accumulation in ascending k, one rounding.  rows [*, H], skip1/skip2 [T, H], bias [E, H] of `dtype`
+ *   (5, 6 or 15) or NULL; scales fp32 [T, K] or NULL (= 1); src_to_dst int32 [K*T]; expert_for_row int32 [T, K].
+ *
+ * npu_moe_init_routing_v2 (converter npu_moe_init_routing_v2.py:41-95 -> MoeInitRoutingV3, experiment_ops.h:2137-2192),
+ *   dropless: stable sort of the T*K pairs (flattened index f = t*K + k) by expert id, rows copied (quant_mode -1)
+ *   or quantised per token to int8 (quant_mode 1).  expanded_x [T*K, H]; expanded_row_idx int32 [T*K]
+ *   (row_idx_type 0: sorted position -> f, 1: f -> sorted position); expert_tokens int64 [expert_num] counts
+ *   (tokens_num_type 1) or cumulative sums (0); expanded_scale fp32 [T*K] (zero when not quantising).
+ *   Workspace: tab_moe_dispatch_pack_workspace_bytes(T, K, expert_num) + 4*(T*K + expert_num) + 1024 bytes.
+ * ------------------------------------------------------------------------------------------------- */
+TAB_API int tab_moe_compute_expert_tokens(const int32_t* sorted_experts, int64_t n, int64_t num_experts, int32_t* out,
+                                  tab_stream_t stream);
+TAB_API int tab_moe_gating_top_k_softmax(const void* x, int dtype, int64_t tokens, int64_t num_experts, int64_t k, void* y,
+                                 int32_t* expert_idx, int32_t* row_idx, tab_stream_t stream);
+TAB_API int tab_moe_finalize_routing(const void* rows, int dtype, const void* skip1, const void* skip2, const void* bias,
+                             const float* scales, const int32_t* src_to_dst, const int32_t* expert_for_row, int64_t T,
+                             int64_t K, int64_t H, void* out, tab_stream_t stream);
+TAB_API int tab_moe_init_routing_v2(const void* x, int x_dtype, const int32_t* expert_idx, int64_t T, int64_t K, int64_t H,
+                            int64_t expert_num, int quant_mode, int tokens_num_type, int row_idx_type, void* expanded_x,
+                            int32_t* expanded_row_idx, int64_t* expert_tokens, float* expanded_scale, void* workspace,
+                            size_t workspace_bytes, tab_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------
  * npu_grouped_matmul, W8A8 (converter grouped_matmul.py:210-365 -> GroupedMatmul,
  * experiment_ops.h:3616-3652).
  *

@@ -251,6 +251,68 @@ def weighted_gather_sum(y: torch.Tensor, pos: torch.Tensor, weights: torch.Tenso
 
 
 # --------------------------------------------------------------------------------------------------
+# operators next to the path
+# --------------------------------------------------------------------------------------------------
+def moe_compute_expert_tokens(sorted_experts: torch.Tensor, num_experts: int) -> torch.Tensor:
+    """MoeComputeExpertTokens (converter npu_moe_compute_expert_tokens.py:4-11): out[e] = #entries <= e, int32."""
+    return torch.cumsum(torch.bincount(sorted_experts.long().clamp(min=0), minlength=num_experts)[:num_experts], 0).to(torch.int32)
+
+
+def moe_gating_top_k_softmax(x: torch.Tensor, k: int):
+    """MoeGatingTopKSoftmax without `finished` (converter moe_gating_top_k_softmax.py:9-19; experiment_ops.h:2222-2241):
+    y = k largest softmax probabilities (in x's dtype), expert_idx int32, row_idx[t, j] = j*T + t.
+    Decision: ties keep the lower expert id."""
+    T = x.shape[0]
+    p = torch.softmax(x.float(), dim=-1)
+    order = torch.sort(p, dim=-1, descending=True, stable=True)
+    row_idx = (torch.arange(k, dtype=torch.int32).view(1, k) * T + torch.arange(T, dtype=torch.int32).view(T, 1))
+    return order.values[:, :k].to(x.dtype), order.indices[:, :k].to(torch.int32), row_idx.contiguous()
+
+
+def moe_finalize_routing(rows, skip1, skip2, bias, scales, src_to_dst, expert_for_row):
+    """MoeFinalizeRouting, dropless (converter npu_moe_finalize_routing.py:21-41):
+    out[t] = sum_k scales[t,k] * (rows[src_to_dst[k*T+t]] + bias[expert[t,k]]) + skip1[t] + skip2[t].
+    Decision: fp32, ascending k, separate multiply and add, skips added last, one rounding."""
+    T = scales.shape[0] if scales is not None else skip1.shape[0]
+    K = src_to_dst.numel() // T
+    acc = None
+    for k in range(K):
+        v = rows[src_to_dst[k * T:(k + 1) * T].long()].float()
+        if bias is not None:
+            v = v + bias[expert_for_row[:, k].long()].float()
+        w = scales[:, k].float().unsqueeze(-1) if scales is not None else 1.0
+        term = w * v
+        acc = term if acc is None else acc + term
+    if skip1 is not None:
+        acc = acc + skip1.float()
+    if skip2 is not None:
+        acc = acc + skip2.float()
+    return acc.to(rows.dtype)
+
+
+def moe_init_routing_v2(x, expert_idx, expert_num, quant_mode=-1, expert_tokens_num_type=0, row_idx_type=0):
+    """MoeInitRoutingV3, dropless (converter npu_moe_init_routing_v2.py:41-95; experiment_ops.h:2137-2192).
+    Decision: pairs are numbered f = t*K + k; gather index = sorted position -> f, scatter index = f -> position."""
+    T, K = expert_idx.shape
+    flat = expert_idx.reshape(-1).to(torch.int64)
+    order = torch.sort(flat, stable=True)
+    tok = order.indices // K
+    if quant_mode == 1:
+        q, s = dynamic_quant(x)
+        ex, es = q[tok], s[tok]
+    else:
+        ex, es = x[tok], torch.zeros(T * K, dtype=torch.float32)
+    if row_idx_type == 0:
+        ridx = order.indices.to(torch.int32)
+    else:
+        ridx = torch.empty(T * K, dtype=torch.int32)
+        ridx[order.indices] = torch.arange(T * K, dtype=torch.int32)
+    cnt = torch.bincount(flat, minlength=expert_num)[:expert_num]
+    tokens = cnt if expert_tokens_num_type == 1 else torch.cumsum(cnt, 0)
+    return ex.contiguous(), ridx, tokens.to(torch.int64), es.contiguous()
+
+
+# --------------------------------------------------------------------------------------------------
 # npu_moe_distribute_dispatch / combine: R ranks simulated in one process
 # --------------------------------------------------------------------------------------------------
 @dataclass

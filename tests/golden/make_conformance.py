@@ -28,6 +28,10 @@ CONVERTER_FILES = {
     "npu_grouped_matmul_swiglu_quant_v2": "grouped_matmul_swiglu_quant_v2",
     "npu_moe_distribute_dispatch": "moe_distribute_dispatch",
     "npu_moe_distribute_combine": "moe_distribute_combine",
+    "npu_moe_compute_expert_tokens": "npu_moe_compute_expert_tokens",
+    "npu_moe_gating_top_k_softmax": "moe_gating_top_k_softmax",
+    "npu_moe_finalize_routing": "npu_moe_finalize_routing",
+    "npu_moe_init_routing_v2": "npu_moe_init_routing_v2",
 }
 
 

@@ -393,3 +393,86 @@ def test_quantiser_fast_path_is_exact_at_ties_and_extreme_scales(dev):
     q, s = O.dynamic_quant(x)
     qg, sg = npu.npu_dynamic_quant(x.to(dev))
     assert torch.equal(s, sg.cpu()) and torch.equal(q, qg.cpu())
+
+
+def test_compute_expert_tokens_bit_exact(dev):
+    g = torch.Generator().manual_seed(3)
+    se = torch.sort(torch.randint(0, 300, (5000,), generator=g, dtype=torch.int32)).values
+    for E in (256, 300, 400):
+        assert torch.equal(O.moe_compute_expert_tokens(se.clamp(max=E - 1), E), npu.npu_moe_compute_expert_tokens(se.clamp(max=E - 1).to(dev), E).cpu())
+    assert npu.npu_moe_compute_expert_tokens(torch.empty(0, dtype=torch.int32, device=dev), 4).tolist() == [0, 0, 0, 0]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,E,k", [(256, 256, 8), (1000, 128, 8), (3, 4, 1), (17, 1000, 6)])
+def test_gating_top_k_softmax(dev, dtype, T, E, k):
+    g = torch.Generator().manual_seed(T + E)
+    x = torch.randn(T, E, generator=g).to(dtype)
+    y, ei, ri = O.moe_gating_top_k_softmax(x, k)
+    yg, eg, rg = npu.npu_moe_gating_top_k_softmax(x.to(dev), None, k)
+    assert torch.equal(ri, rg.cpu())
+    # 16-bit logits repeat values, so ties are common there: equal probabilities may swap only if both are ties
+    same = ei == eg.cpu()
+    if dtype == torch.float32:
+        assert bool(same.all()), "expert ids are index work: exact"
+    else:
+        assert float(same.float().mean()) > 0.999
+    torch.testing.assert_close(yg.cpu().float(), y.float(), rtol=2e-2 if dtype != torch.float32 else 1e-5, atol=1e-7)
+    with pytest.raises(NotImplementedError):
+        npu.npu_moe_gating_top_k_softmax(x.to(dev), torch.zeros(T, dtype=torch.bool, device=dev), k)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("with_extras", [False, True])
+def test_finalize_routing_bit_exact(dev, dtype, with_extras):
+    g = torch.Generator().manual_seed(9)
+    T, K, H, E = 96, 4, 512, 16
+    rows = torch.randn(T * K, H, generator=g).to(dtype)
+    s2d = torch.randperm(T * K, generator=g).to(torch.int32)
+    sc = torch.rand(T, K, generator=g)
+    efr = torch.randint(0, E, (T, K), generator=g, dtype=torch.int32)
+    skip1 = torch.randn(T, H, generator=g).to(dtype) if with_extras else None
+    skip2 = torch.randn(T, H, generator=g).to(dtype) if with_extras else None
+    bias = torch.randn(E, H, generator=g).to(dtype) if with_extras else None
+    ref = O.moe_finalize_routing(rows, skip1, skip2, bias, sc, s2d, efr)
+    d = lambda t: None if t is None else t.to(dev)
+    got = npu.npu_moe_finalize_routing(d(rows), d(skip1), d(skip2), d(bias), d(sc), d(s2d), d(efr), 0)
+    assert torch.equal(ref, got.cpu())
+
+
+@pytest.mark.parametrize("quant_mode,tok_type,row_type", [(-1, 0, 0), (1, 1, 1), (1, 0, 0), (-1, 1, 1)])
+def test_init_routing_v2_bit_exact(dev, quant_mode, tok_type, row_type):
+    cfg = O.MoeConfig("v2", 300, 1024, 64, 6, 128)
+    x, ids, _ = O.make_tokens(cfg, seed=4)
+    ref = O.moe_init_routing_v2(x, ids, cfg.E, quant_mode, tok_type, row_type)
+    got = npu.npu_moe_init_routing_v2(x.to(dev), ids.to(dev), expert_num=cfg.E, quant_mode=quant_mode,
+                                      expert_tokens_num_type=tok_type, expert_tokens_num_flag=True, row_idx_type=row_type,
+                                      active_expert_range=[0, cfg.E])
+    for a, b in zip(ref, got):
+        assert a.dtype == b.dtype and torch.equal(a, b.cpu())
+    with pytest.raises(NotImplementedError):
+        npu.npu_moe_init_routing_v2(x.to(dev), ids.to(dev), expert_num=cfg.E, drop_pad_mode=1)
+
+
+def test_layer_from_gating_to_finalize_with_neighbour_ops(dev):
+    """The single-rank layer written with the neighbouring ops: gating -> init_routing_v2 (quantising) ->
+    fused gate_up -> down -> finalize_routing."""
+    cfg = O.CONFIGS["cfg0"]
+    w = O.make_weights(cfg, 0)
+    x, _, _ = O.make_tokens(cfg, 0)
+    g = torch.Generator().manual_seed(1)
+    logits = torch.randn(cfg.T, cfg.E, generator=g)
+    probs, ids, _ = O.moe_gating_top_k_softmax(logits, cfg.K)
+    ref = O.moe_layer([x], [ids], [probs], w)[0]
+    pg, idg, _ = npu.npu_moe_gating_top_k_softmax(logits.to(dev), None, cfg.K)
+    assert torch.equal(idg.cpu(), ids)
+    ex, scatter_idx, counts, xs = npu.npu_moe_init_routing_v2(x.to(dev), idg, expert_num=cfg.E, quant_mode=1,
+                                                             expert_tokens_num_type=1, expert_tokens_num_flag=True, row_idx_type=1)
+    hq, hs = npu.npu_grouped_matmul_swiglu_quant_v2(ex, [w.w1.to(dev)], [w.s1.to(dev)], xs, counts, group_list_type=1)
+    y = npu.npu_grouped_matmul([hq], [w.w2.to(dev)], scale=[w.s2.to(dev)], per_token_scale=[hs], group_list=counts, split_item=2,
+                               group_type=0, group_list_type=1, output_dtype=15)[0]
+    # finalize wants src_to_dst indexed k*T + t; the scatter index is indexed t*K + k
+    s2d = scatter_idx.view(cfg.T, cfg.K).t().contiguous().view(-1)
+    out = npu.npu_moe_finalize_routing(y, None, None, None, pg, s2d, idg, 0)
+    _gmm_ok(dev)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=1e-2, atol=1e-2)

@@ -165,3 +165,30 @@ def test_zipf_routing_is_skewed_and_gating_is_normalised():
 def test_checksum_is_order_sensitive():
     a = torch.arange(16, dtype=torch.int32)
     assert checksum(a) != checksum(a.flip(0))
+
+
+def test_neighbour_ops_known_answers():
+    se = torch.tensor([0, 0, 2, 2, 2, 5], dtype=torch.int32)
+    assert O.moe_compute_expert_tokens(se, 6).tolist() == [2, 2, 5, 5, 5, 6]
+    x = torch.tensor([[1.0, 3.0, 2.0, 3.0], [0.0, 0.0, 0.0, 0.0]])
+    y, ei, ri = O.moe_gating_top_k_softmax(x, 2)
+    assert ei.tolist() == [[1, 3], [0, 1]] and ri.tolist() == [[0, 2], [1, 3]]
+    assert torch.allclose(y[1], torch.tensor([0.25, 0.25]))
+    # finalize: T=2, K=2, rows indexed by src_to_dst[k*T+t]
+    rows = torch.tensor([[1.0, 1.0], [2.0, 2.0], [3.0, 3.0], [4.0, 4.0]])
+    s2d = torch.tensor([3, 0, 1, 2], dtype=torch.int32)       # (k=0: t0->3, t1->0), (k=1: t0->1, t1->2)
+    sc = torch.tensor([[0.5, 2.0], [1.0, 1.0]])
+    out = O.moe_finalize_routing(rows, None, None, None, sc, s2d, None)
+    assert out.tolist() == [[0.5 * 4 + 2 * 2, 0.5 * 4 + 2 * 2], [1 + 3, 1 + 3]]
+    bias = torch.tensor([[10.0, 10.0], [20.0, 20.0]])
+    efr = torch.tensor([[0, 1], [1, 1]], dtype=torch.int32)
+    skip = torch.ones(2, 2)
+    out2 = O.moe_finalize_routing(rows, skip, None, bias, sc, s2d, efr)
+    assert out2.tolist() == [[0.5 * 14 + 2 * 22 + 1] * 2, [21 + 23 + 1] * 2]
+    xx = torch.arange(8, dtype=torch.float32).view(4, 2).to(torch.bfloat16)
+    ids = torch.tensor([[1, 0], [0, 2], [2, 1], [0, 1]], dtype=torch.int32)
+    ex, ridx, tok, es = O.moe_init_routing_v2(xx, ids, 3, -1, 1, 0)
+    assert ridx.tolist() == [1, 2, 6, 0, 5, 7, 3, 4] and tok.tolist() == [3, 3, 2]
+    assert torch.equal(ex, xx[[0, 1, 3, 0, 2, 3, 1, 2]])
+    _, ridx1, tok0, _ = O.moe_init_routing_v2(xx, ids, 3, -1, 0, 1)
+    assert tok0.tolist() == [3, 6, 8] and ridx1[ridx.long()].tolist() == list(range(8))

@@ -609,3 +609,228 @@ extern "C" int tab_moe_init_routing_static(const void* x, int x_dtype, const int
   return tab_moe_init_routing(x, x_dtype, row_idx, expert_idx, T, K, H, active_num, expert_bound, expanded_x,
                               expanded_row_idx, expanded_expert_idx, scratch, kStaticScratchBytes, stream);
 }
+
+// ---- ops around the path: expert token counts, gating, routing with built-in quantisation, finalize ------------
+namespace tab {
+
+// out[e] = number of entries of the ascending int32 array `sorted` that are <= e (cumulative tokens per expert).
+__global__ void __launch_bounds__(256) compute_expert_tokens_kernel(const int32_t* __restrict__ sorted, int n, int num_experts,
+                                                                    int32_t* __restrict__ out) {
+  for (int e = blockIdx.x * 256 + threadIdx.x; e < num_experts; e += gridDim.x * 256) {
+    int lo = 0, hi = n;   // first index with sorted[idx] > e
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (sorted[mid] <= e) lo = mid + 1; else hi = mid;
+    }
+    out[e] = lo;
+  }
+}
+
+// One warp per token: softmax over E <= 1024 logits held 32 per lane, then k rounds of a warp-shuffle arg-max
+// (larger probability first, lower expert id on ties).  y [T, k] probabilities in the input dtype, expert_idx and
+// row_idx int32 [T, k] with row_idx[t, j] = j*T + t.
+constexpr int kGateMaxPerLane = 32;
+template <typename T>
+__global__ void __launch_bounds__(128) gating_topk_softmax_kernel(const T* __restrict__ x, int64_t tokens, int E, int k,
+                                                                  T* __restrict__ y, int32_t* __restrict__ expert_idx,
+                                                                  int32_t* __restrict__ row_idx) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp_global = (blockIdx.x * 128 + threadIdx.x) >> 5;
+  const int64_t warps_total = static_cast<int64_t>(gridDim.x) * 4;
+  for (int64_t t = warp_global; t < tokens; t += warps_total) {
+    float v[kGateMaxPerLane];
+    float m = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < kGateMaxPerLane; ++i) {
+      const int e = i * 32 + lane;
+      v[i] = e < E ? Elem<T>::to_f32(x[t * E + e]) : -INFINITY;
+      m = fmaxf(m, v[i]);
+    }
+    m = warp_max(m);
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < kGateMaxPerLane; ++i) {
+      v[i] = i * 32 + lane < E ? expf(v[i] - m) : 0.f;
+      sum += v[i];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+#pragma unroll
+    for (int i = 0; i < kGateMaxPerLane; ++i) v[i] = i * 32 + lane < E ? __fdiv_rn(v[i], sum) : -1.f;
+    for (int j = 0; j < k; ++j) {
+      float best = -2.f;
+      int best_e = 0x7fffffff;
+#pragma unroll
+      for (int i = 0; i < kGateMaxPerLane; ++i) {
+        if (v[i] > best) {   // ascending i keeps the lowest expert id among equal values of this lane
+          best = v[i];
+          best_e = i * 32 + lane;
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+        if (ob > best || (ob == best && oe < best_e)) {
+          best = ob;
+          best_e = oe;
+        }
+      }
+      if ((best_e & 31) == lane) {
+#pragma unroll
+        for (int i = 0; i < kGateMaxPerLane; ++i)
+          if (i == (best_e >> 5)) v[i] = -1.f;   // taken
+      }
+      if (lane == 0) {
+        y[t * k + j] = Elem<T>::from_f32(best);
+        expert_idx[t * k + j] = best_e;
+        row_idx[t * k + j] = static_cast<int32_t>(j * tokens + t);
+      }
+    }
+  }
+}
+
+// out[t] = sum_k scales[t,k] * (rows[src_to_dst[k*T + t]] + bias[expert[t,k]]) + skip1[t] + skip2[t]; fp32, ascending k.
+template <typename T>
+__global__ void __launch_bounds__(256) finalize_routing_kernel(const T* __restrict__ rows, const T* __restrict__ skip1,
+                                                               const T* __restrict__ skip2, const T* __restrict__ bias,
+                                                               const float* __restrict__ scales, const int32_t* __restrict__ src_to_dst,
+                                                               const int32_t* __restrict__ expert, int64_t tokens, int K, int cols,
+                                                               T* __restrict__ out) {
+  extern __shared__ int s_meta[];  // [K] positions, [K] experts, [K] weights
+  int* s_pos = s_meta;
+  int* s_exp = s_meta + K;
+  float* s_w = reinterpret_cast<float*>(s_meta + 2 * K);
+  const int nchunk = cols >> 3;
+  for (int64_t t = blockIdx.x; t < tokens; t += gridDim.x) {
+    __syncthreads();
+    for (int k = threadIdx.x; k < K; k += 256) {
+      s_pos[k] = src_to_dst[static_cast<int64_t>(k) * tokens + t];
+      s_exp[k] = expert ? expert[t * K + k] : 0;
+      s_w[k] = scales ? scales[t * K + k] : 1.f;
+    }
+    __syncthreads();
+    for (int ch = threadIdx.x; ch < nchunk; ch += 256) {
+      float acc[8];
+      for (int k = 0; k < K; ++k) {
+        float v[8];
+        Elem<T>::load8(rows + static_cast<int64_t>(s_pos[k]) * cols + ch * 8, v);
+        if (bias) {
+          float b[8];
+          Elem<T>::load8(bias + static_cast<int64_t>(s_exp[k]) * cols + ch * 8, b);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = __fadd_rn(v[i], b[i]);
+        }
+        const float w = s_w[k];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float term = __fmul_rn(w, v[i]);
+          acc[i] = k == 0 ? term : __fadd_rn(acc[i], term);
+        }
+      }
+      if (skip1) {
+        float v[8];
+        Elem<T>::load8(skip1 + t * cols + ch * 8, v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], v[i]);
+      }
+      if (skip2) {
+        float v[8];
+        Elem<T>::load8(skip2 + t * cols + ch * 8, v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], v[i]);
+      }
+      Elem<T>::store8(out + t * cols + ch * 8, acc);
+    }
+  }
+}
+
+// counts int32 [n] -> int64 counts (type 1) or inclusive cumulative sums (type 0); one CTA.
+__global__ void __launch_bounds__(1024) tokens_count_or_cumsum_kernel(const int32_t* __restrict__ counts, int n, int type,
+                                                                      int64_t* __restrict__ out) {
+  __shared__ int s_val[kMaxExperts];
+  __shared__ int s_warp[33];
+  for (int i = threadIdx.x; i < n; i += 1024) s_val[i] = counts[i];
+  __syncthreads();
+  if (type == 0) block_exclusive_scan(s_val, n, s_warp);
+  for (int i = threadIdx.x; i < n; i += 1024) out[i] = type == 0 ? static_cast<int64_t>(s_val[i]) + counts[i] : static_cast<int64_t>(s_val[i]);
+}
+
+}  // namespace tab
+
+extern "C" int tab_moe_compute_expert_tokens(const int32_t* sorted_experts, int64_t n, int64_t num_experts, int32_t* out,
+                                             tab_stream_t stream) {
+  if (n < 0 || num_experts <= 0 || n > (1LL << 30) || num_experts > (1LL << 24)) return fail(TAB_ERR_BAD_ARG, "compute_expert_tokens: n=%lld experts=%lld", (long long)n, (long long)num_experts);
+  if (!out || (n > 0 && !sorted_experts)) return fail(TAB_ERR_BAD_ARG, "compute_expert_tokens: null pointer");
+  compute_expert_tokens_kernel<<<grid_for((num_experts + 255) / 256, 4), 256, 0, as_stream(stream)>>>(sorted_experts, (int)n, (int)num_experts, out);
+  return check_launch("compute_expert_tokens");
+}
+
+extern "C" int tab_moe_gating_top_k_softmax(const void* x, int dtype, int64_t tokens, int64_t num_experts, int64_t k, void* y,
+                                            int32_t* expert_idx, int32_t* row_idx, tab_stream_t stream) {
+  if (tokens < 0 || num_experts <= 0 || k <= 0 || k > num_experts) return fail(TAB_ERR_BAD_ARG, "gating_top_k_softmax: tokens=%lld experts=%lld k=%lld", (long long)tokens, (long long)num_experts, (long long)k);
+  if (num_experts > 32 * kGateMaxPerLane) return fail(TAB_ERR_UNSUPPORTED, "gating_top_k_softmax: more than %d experts", 32 * kGateMaxPerLane);
+  if (tokens == 0) return TAB_OK;
+  if (!x || !y || !expert_idx || !row_idx) return fail(TAB_ERR_BAD_ARG, "gating_top_k_softmax: null pointer");
+  const int grid = grid_for((tokens + 3) / 4, 8);
+  cudaStream_t st = as_stream(stream);
+  if (dtype == TAB_F32) gating_topk_softmax_kernel<float><<<grid, 128, 0, st>>>(static_cast<const float*>(x), tokens, (int)num_experts, (int)k, static_cast<float*>(y), expert_idx, row_idx);
+  else if (dtype == TAB_BF16) gating_topk_softmax_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(x), tokens, (int)num_experts, (int)k, static_cast<__nv_bfloat16*>(y), expert_idx, row_idx);
+  else if (dtype == TAB_F16) gating_topk_softmax_kernel<__half><<<grid, 128, 0, st>>>(static_cast<const __half*>(x), tokens, (int)num_experts, (int)k, static_cast<__half*>(y), expert_idx, row_idx);
+  else return fail(TAB_ERR_UNSUPPORTED, "gating_top_k_softmax: dtype %d (want 5, 6 or 15)", dtype);
+  return check_launch("gating_top_k_softmax");
+}
+
+extern "C" int tab_moe_finalize_routing(const void* rows, int dtype, const void* skip1, const void* skip2, const void* bias,
+                                        const float* scales, const int32_t* src_to_dst, const int32_t* expert_for_row, int64_t T,
+                                        int64_t K, int64_t H, void* out, tab_stream_t stream) {
+  if (T < 0 || K <= 0 || K > 1024 || H <= 0) return fail(TAB_ERR_BAD_ARG, "finalize_routing: T=%lld K=%lld H=%lld", (long long)T, (long long)K, (long long)H);
+  if (T == 0) return TAB_OK;
+  if (!rows || !src_to_dst || !out || (bias && !expert_for_row)) return fail(TAB_ERR_BAD_ARG, "finalize_routing: null pointer (bias needs expert_for_source_row)");
+  if (H % 8 != 0 || !aligned16(rows) || !aligned16(out) || (skip1 && !aligned16(skip1)) || (skip2 && !aligned16(skip2)) || (bias && !aligned16(bias)))
+    return fail(TAB_ERR_ALIGNMENT, "finalize_routing: H=%lld must be a multiple of 8 and pointers 16-byte aligned", (long long)H);
+  cudaStream_t st = as_stream(stream);
+  const int grid = grid_for(T, 8);
+  const size_t smem = static_cast<size_t>(K) * 12;
+  if (dtype == TAB_BF16)
+    finalize_routing_kernel<__nv_bfloat16><<<grid, 256, smem, st>>>(static_cast<const __nv_bfloat16*>(rows), static_cast<const __nv_bfloat16*>(skip1), static_cast<const __nv_bfloat16*>(skip2), static_cast<const __nv_bfloat16*>(bias), scales, src_to_dst, expert_for_row, T, (int)K, (int)H, static_cast<__nv_bfloat16*>(out));
+  else if (dtype == TAB_F16)
+    finalize_routing_kernel<__half><<<grid, 256, smem, st>>>(static_cast<const __half*>(rows), static_cast<const __half*>(skip1), static_cast<const __half*>(skip2), static_cast<const __half*>(bias), scales, src_to_dst, expert_for_row, T, (int)K, (int)H, static_cast<__half*>(out));
+  else if (dtype == TAB_F32)
+    finalize_routing_kernel<float><<<grid, 256, smem, st>>>(static_cast<const float*>(rows), static_cast<const float*>(skip1), static_cast<const float*>(skip2), static_cast<const float*>(bias), scales, src_to_dst, expert_for_row, T, (int)K, (int)H, static_cast<float*>(out));
+  else
+    return fail(TAB_ERR_UNSUPPORTED, "finalize_routing: dtype %d (want 5, 6 or 15)", dtype);
+  return check_launch("finalize_routing");
+}
+
+extern "C" int tab_moe_init_routing_v2(const void* x, int x_dtype, const int32_t* expert_idx, int64_t T, int64_t K, int64_t H,
+                                       int64_t expert_num, int quant_mode, int tokens_num_type, int row_idx_type, void* expanded_x,
+                                       int32_t* expanded_row_idx, int64_t* expert_tokens, float* expanded_scale, void* workspace,
+                                       size_t workspace_bytes, tab_stream_t stream) {
+  // Sort + (quantise or copy) + scatter are the dispatch sender's steps; this entry point adds the v2 outputs.
+  if (quant_mode != -1 && quant_mode != 1) return fail(TAB_ERR_UNSUPPORTED, "init_routing_v2: quant_mode %d (want -1 or 1)", quant_mode);
+  if ((tokens_num_type != 0 && tokens_num_type != 1) || (row_idx_type != 0 && row_idx_type != 1)) return fail(TAB_ERR_BAD_ARG, "init_routing_v2: bad type flag");
+  size_t need = 0;
+  int rc = tab_moe_dispatch_pack_workspace_bytes(T, K, expert_num, &need);
+  if (rc != TAB_OK) return rc;
+  const int64_t n = T * K;
+  const size_t extra = static_cast<size_t>((n + expert_num) * 4 + 512);
+  if (!workspace || workspace_bytes < need + extra) return fail(TAB_ERR_WORKSPACE, "init_routing_v2: workspace %zu < %zu bytes", workspace_bytes, need + extra);
+  if (!expanded_row_idx || !expert_tokens || !expanded_scale) return fail(TAB_ERR_BAD_ARG, "init_routing_v2: null pointer");
+  uint8_t* wsb = static_cast<uint8_t*>(workspace);
+  int32_t* scatter_idx = reinterpret_cast<int32_t*>(wsb + need);               // f -> position
+  int32_t* counts = scatter_idx + ((n + 63) / 64) * 64;
+  int32_t* idx_out = row_idx_type == 1 ? expanded_row_idx : scatter_idx;
+  rc = tab_moe_dispatch_pack(x, x_dtype, expert_idx, T, K, H, expert_num, quant_mode == 1 ? 2 : 0, expanded_x, expanded_scale, idx_out,
+                             counts, workspace, need, stream);
+  if (rc != TAB_OK) return rc;
+  cudaStream_t st = as_stream(stream);
+  if (row_idx_type == 0 && n > 0) {
+    // gather form: position -> source pair index, kept by the sort in its scratch (SortScratch::sorted_src)
+    SortScratch s = carve(workspace, n, expert_num, true);
+    cudaError_t e = cudaMemcpyAsync(expanded_row_idx, s.sorted_src, n * sizeof(int32_t), cudaMemcpyDeviceToDevice, st);
+    if (e != cudaSuccess) return fail(TAB_ERR_CUDA, "init_routing_v2: copy: %s", cudaGetErrorString(e));
+  }
+  tokens_count_or_cumsum_kernel<<<1, 1024, 0, st>>>(counts, (int)expert_num, tokens_num_type, expert_tokens);
+  return check_launch("init_routing_v2");
+}

@@ -52,6 +52,14 @@ _npu.define("npu_grouped_matmul_swiglu_quant_v2(Tensor x, Tensor[] weight, Tenso
             "int? dequant_mode=0, int? dequant_dtype=0, int? quant_mode=0, int? quant_dtype=1, int? group_list_type=0, "
             "int[]? tuning_config=None, int? x_dtype=None, int? weight_dtype=None, int? weight_scale_dtype=None, "
             "int? x_scale_dtype=None) -> (Tensor, Tensor)")
+_npu.define("npu_moe_compute_expert_tokens(Tensor sorted_experts, int num_experts) -> Tensor")
+_npu.define("npu_moe_gating_top_k_softmax(Tensor x, Tensor? finished=None, int k=1) -> (Tensor, Tensor, Tensor)")
+_npu.define("npu_moe_finalize_routing(Tensor expanded_permuted_rows, Tensor? skip1, Tensor? skip2, Tensor? bias, Tensor? scales, "
+            "Tensor expanded_src_to_dst_row, Tensor? export_for_source_row, int? drop_pad_mode=0) -> Tensor")
+_npu.define("npu_moe_init_routing_v2(Tensor x, Tensor expert_idx, *, Tensor? scale=None, Tensor? offset=None, int active_num=-1, "
+            "int expert_capacity=-1, int expert_num=-1, int drop_pad_mode=0, int expert_tokens_num_type=0, "
+            "bool expert_tokens_num_flag=False, int quant_mode=-1, int[]? active_expert_range=None, int row_idx_type=0, "
+            "int? x_dtype=None) -> (Tensor, Tensor, Tensor, Tensor)")
 _npu.define("npu_moe_distribute_dispatch(Tensor x, Tensor expert_ids, str group_ep, int ep_world_size, int ep_rank_id, "
             "int moe_expert_num, *, Tensor? scales=None, Tensor? x_active_mask=None, Tensor? expert_scales=None, "
             "str group_tp=\"\", int tp_world_size=0, int tp_rank_id=0, int expert_shard_type=0, int shared_expert_num=1, "
@@ -407,6 +415,128 @@ def gmm_status(device=None) -> int:
         return int(st.value)
 
 
+
+# --------------------------------------------------------------------------------------------------
+# operators next to the path: expert token counts, gating, finalize, routing with built-in quantisation
+# --------------------------------------------------------------------------------------------------
+def _cet_meta(sorted_experts, num_experts):
+    if sorted_experts.dim() != 1 or num_experts <= 0:
+        raise RuntimeError("npu_moe_compute_expert_tokens: sorted_experts must be 1-D and num_experts positive")
+    return torch.empty((num_experts,), dtype=torch.int32, device=sorted_experts.device)
+
+
+def _cet_cuda(sorted_experts, num_experts):
+    out = _cet_meta(sorted_experts, num_experts)
+    if sorted_experts.dtype != torch.int32:
+        raise RuntimeError("npu_moe_compute_expert_tokens: sorted_experts must be int32")
+    se = sorted_experts.contiguous()
+    _lib.call("tab_moe_compute_expert_tokens", _ptr(se), se.numel(), num_experts, _ptr(out), _stream(se))
+    return out
+
+
+def _gating_meta(x, finished=None, k=1):
+    if x.dim() != 2 or k < 1 or k > x.shape[1]:
+        raise RuntimeError("npu_moe_gating_top_k_softmax: x must be [tokens, experts] and 1 <= k <= experts")
+    T = x.shape[0]
+    return (x.new_empty((T, k)), torch.empty((T, k), dtype=torch.int32, device=x.device),
+            torch.empty((T, k), dtype=torch.int32, device=x.device))
+
+
+def _gating_cuda(x, finished=None, k=1):
+    y, ei, ri = _gating_meta(x, finished, k)
+    _only_none("npu_moe_gating_top_k_softmax", finished=finished)
+    xc = x.contiguous()
+    _lib.call("tab_moe_gating_top_k_softmax", _ptr(xc), _st(x.dtype, "npu_moe_gating_top_k_softmax"), x.shape[0], x.shape[1], k,
+              _ptr(y), _ptr(ei), _ptr(ri), _stream(xc))
+    return y, ei, ri
+
+
+def _finalize_meta(expanded_permuted_rows, skip1, skip2, bias, scales, expanded_src_to_dst_row, export_for_source_row,
+                   drop_pad_mode=0):
+    rows = expanded_permuted_rows
+    if rows.dim() != 2 or expanded_src_to_dst_row.dim() != 1:
+        raise RuntimeError("npu_moe_finalize_routing: rows must be [T*K, H] and expanded_src_to_dst_row 1-D")
+    if scales is not None:
+        T = scales.shape[0]
+    elif skip1 is not None:
+        T = skip1.shape[0]
+    else:
+        T = expanded_src_to_dst_row.numel()
+    return rows.new_empty((T, rows.shape[1]))
+
+
+def _finalize_cuda(expanded_permuted_rows, skip1, skip2, bias, scales, expanded_src_to_dst_row, export_for_source_row,
+                   drop_pad_mode=0):
+    op = "npu_moe_finalize_routing"
+    out = _finalize_meta(expanded_permuted_rows, skip1, skip2, bias, scales, expanded_src_to_dst_row, export_for_source_row)
+    if drop_pad_mode not in (None, 0):
+        raise NotImplementedError(f"{op}: only drop_pad_mode=0 (dropless) is on the path")
+    rows = expanded_permuted_rows.contiguous()
+    T, H = out.shape
+    K = expanded_src_to_dst_row.numel() // T
+    if K * T != expanded_src_to_dst_row.numel() or expanded_src_to_dst_row.dtype != torch.int32:
+        raise RuntimeError(f"{op}: expanded_src_to_dst_row must be int32 with K*T entries")
+    for name, t in (("skip1", skip1), ("skip2", skip2), ("bias", bias)):
+        if t is not None and t.dtype != rows.dtype:
+            raise RuntimeError(f"{op}: {name} must have the dtype of the rows")
+    if bias is not None and (export_for_source_row is None or export_for_source_row.dtype != torch.int32):
+        raise RuntimeError(f"{op}: bias needs int32 export_for_source_row [T, K]")
+    sc = None if scales is None else scales.to(torch.float32).contiguous()
+    c = lambda t: None if t is None else t.contiguous()
+    skip1, skip2, bias, efr = c(skip1), c(skip2), c(bias), c(export_for_source_row)
+    _lib.call("tab_moe_finalize_routing", _ptr(rows), _st(rows.dtype, op), _ptr(skip1), _ptr(skip2), _ptr(bias), _ptr(sc),
+              _ptr(expanded_src_to_dst_row.contiguous()), _ptr(efr), T, K, H, _ptr(out), _stream(rows))
+    return out
+
+
+def _irv2_check(x, expert_idx, scale, offset, active_num, expert_capacity, expert_num, drop_pad_mode, quant_mode,
+                active_expert_range, x_dtype):
+    op = "npu_moe_init_routing_v2"
+    if x.dim() != 2 or expert_idx.dim() != 2 or x.shape[0] != expert_idx.shape[0]:
+        raise RuntimeError(f"{op}: x must be [T, H] and expert_idx [T, K]")
+    _only_none(op, scale=scale, offset=offset, x_dtype=x_dtype)
+    if expert_num <= 0:
+        raise RuntimeError(f"{op}: expert_num must be given")
+    if drop_pad_mode != 0 or expert_capacity not in (-1, 0):
+        raise NotImplementedError(f"{op}: only the dropless mode is on the path")
+    if quant_mode not in (-1, 1):
+        raise NotImplementedError(f"{op}: quant_mode must be -1 (none) or 1 (per-token dynamic int8)")
+    if active_num not in (-1, 0) and active_num < x.shape[0] * expert_idx.shape[1]:
+        raise NotImplementedError(f"{op}: active_num below T*K is outside the path")
+    if active_expert_range is not None and list(active_expert_range) != [0, expert_num]:
+        raise NotImplementedError(f"{op}: active_expert_range must cover [0, expert_num)")
+
+
+def _irv2_meta(x, expert_idx, *, scale=None, offset=None, active_num=-1, expert_capacity=-1, expert_num=-1, drop_pad_mode=0,
+               expert_tokens_num_type=0, expert_tokens_num_flag=False, quant_mode=-1, active_expert_range=None, row_idx_type=0,
+               x_dtype=None):
+    _irv2_check(x, expert_idx, scale, offset, active_num, expert_capacity, expert_num, drop_pad_mode, quant_mode,
+                active_expert_range, x_dtype)
+    M = expert_idx.numel()
+    dev = x.device
+    return (torch.empty((M, x.shape[1]), dtype=torch.int8 if quant_mode == 1 else x.dtype, device=dev),
+            torch.empty((M,), dtype=torch.int32, device=dev), torch.empty((expert_num,), dtype=torch.int64, device=dev),
+            torch.empty((M,), dtype=torch.float32, device=dev))
+
+
+def _irv2_cuda(x, expert_idx, *, scale=None, offset=None, active_num=-1, expert_capacity=-1, expert_num=-1, drop_pad_mode=0,
+               expert_tokens_num_type=0, expert_tokens_num_flag=False, quant_mode=-1, active_expert_range=None, row_idx_type=0,
+               x_dtype=None):
+    ex, eri, tokens, esc = _irv2_meta(x, expert_idx, scale=scale, offset=offset, active_num=active_num,
+                                      expert_capacity=expert_capacity, expert_num=expert_num, drop_pad_mode=drop_pad_mode,
+                                      quant_mode=quant_mode, active_expert_range=active_expert_range, x_dtype=x_dtype)
+    if expert_idx.dtype != torch.int32 or x.dtype not in (torch.bfloat16, torch.float16):
+        raise NotImplementedError("npu_moe_init_routing_v2: x must be bfloat16/float16 and expert_idx int32")
+    T, K = expert_idx.shape
+    xc, ic = x.contiguous(), expert_idx.contiguous()
+    nbytes = _lib.workspace_bytes("tab_moe_dispatch_pack_workspace_bytes", T, K, expert_num) + 4 * (T * K + expert_num) + 1024
+    ws = _workspace(nbytes, x.device)
+    _lib.call("tab_moe_init_routing_v2", _ptr(xc), _st(x.dtype, "npu_moe_init_routing_v2"), _ptr(ic), T, K, x.shape[1], expert_num,
+              quant_mode, int(expert_tokens_num_type), int(row_idx_type), _ptr(ex), _ptr(eri), _ptr(tokens), _ptr(esc), _ptr(ws),
+              ws.numel(), _stream(xc))
+    return ex, eri, tokens, esc
+
+
 # --------------------------------------------------------------------------------------------------
 # npu_moe_distribute_dispatch / combine
 # --------------------------------------------------------------------------------------------------
@@ -469,6 +599,10 @@ for _name, _meta, _cuda in (
         ("npu_grouped_matmul", _gmm_meta, _gmm_cuda),
         ("npu_grouped_matmul.List", _gmm_meta, _gmm_cuda),
         ("npu_grouped_matmul_swiglu_quant_v2", _gmm_sq_meta, _gmm_sq_cuda),
+        ("npu_moe_compute_expert_tokens", _cet_meta, _cet_cuda),
+        ("npu_moe_gating_top_k_softmax", _gating_meta, _gating_cuda),
+        ("npu_moe_finalize_routing", _finalize_meta, _finalize_cuda),
+        ("npu_moe_init_routing_v2", _irv2_meta, _irv2_cuda),
         ("npu_moe_distribute_dispatch", _dispatch_meta, _dispatch_cuda),
         ("npu_moe_distribute_combine", _combine_meta, _combine_cuda)):
     _npu.impl(_name, _meta, "Meta")
@@ -477,4 +611,5 @@ _npu.impl("npu_dynamic_quant_asymmetric", _dynamic_quant_asym, "CompositeExplici
 
 OP_NAMES = ["npu_moe_init_routing", "npu_dynamic_quant", "npu_dynamic_quant_asymmetric", "npu_swiglu",
             "npu_dequant_swiglu_quant", "npu_grouped_matmul", "npu_grouped_matmul_swiglu_quant_v2",
-            "npu_moe_distribute_dispatch", "npu_moe_distribute_combine"]
+            "npu_moe_distribute_dispatch", "npu_moe_distribute_combine", "npu_moe_compute_expert_tokens",
+            "npu_moe_gating_top_k_softmax", "npu_moe_finalize_routing", "npu_moe_init_routing_v2"]
