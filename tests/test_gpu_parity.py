@@ -476,3 +476,21 @@ def test_layer_from_gating_to_finalize_with_neighbour_ops(dev):
     out = npu.npu_moe_finalize_routing(y, None, None, None, pg, s2d, idg, 0)
     _gmm_ok(dev)
     torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=1e-2, atol=1e-2)
+
+
+def test_quantiser_equals_ieee_division_on_a_large_sample(dev):
+    """470 M values, bf16 and fp32 inputs: the branch-free quotient correction must reproduce rint(x / scale) of IEEE
+    division everywhere (checked on the GPU against torch's own division)."""
+    g = torch.Generator(device=dev).manual_seed(5)
+    for dtype, rows in ((torch.bfloat16, 65536), (torch.float32, 16384)):
+        x = (torch.randn(rows, 7168, generator=g, device=dev) * 3).to(dtype)
+        q, s = npu.npu_dynamic_quant(x)
+        xf = x.float()
+        amax = xf.abs().amax(dim=1)
+        want_s = amax / torch.full_like(amax, 127.0)     # tensor / tensor: IEEE division (a scalar divisor becomes a multiply)
+        assert torch.equal(s, want_s)
+        bad = 0
+        for lo in range(0, rows, 8192):
+            want_q = torch.round(xf[lo:lo + 8192] / want_s[lo:lo + 8192, None]).clamp_(-127, 127).to(torch.int8)
+            bad += int((want_q != q[lo:lo + 8192]).sum())
+        assert bad == 0

@@ -180,32 +180,32 @@ __device__ __forceinline__ float cta_max(float v, float* red) {
 }
 
 // ---- fast exact row quantiser ------------------------------------------------------------------------------
-// Produces rint(v / scale) clamped to +-127 -- bit for bit what IEEE division gives -- in about six full-rate FP32
-// instructions per element (conversion instructions issue at 1/8 rate and IEEE division costs a dozen more):
-//   * the quotient is approximated by r = v * (1/scale), at most 2 ulp (< 1.6e-5 for |r| <= 127) from the exact one;
-//     |v| <= amax keeps |r| below 127.5, so no clamp is needed;
-//   * adding 1.5 * 2^23 rounds r half-to-even and leaves the integer in the low mantissa bits (its low byte is the
-//     two's-complement int8);
-//   * the residual v - q * scale (one FMA) tells how far the exact quotient is from q: only when that distance exceeds
-//     0.5 - 4e-5 (a rounding tie is within reach: about one value in ten thousand) are the eight values of the chunk
-//     redone with the IEEE division.  Rows whose scale is too small for a finite reciprocal use the division throughout.
+// Produces rint(v / scale) clamped to +-127 -- bit for bit what IEEE division gives -- in four full-rate FP32
+// instructions per element, without branches (conversion instructions issue at 1/8 rate, and the library division is a
+// dozen instructions with a slow path):
+//   * one correctly rounded reciprocal per row, inv = RN(1/scale);
+//   * q0 = RN(v * inv); r = fma(-q0, scale, v) is the exact remainder; q1 = fma(r, inv, q0) is then the correctly
+//     rounded quotient RN(v / scale) (Markstein's correction step; it needs a correctly rounded reciprocal and fails
+//     only for a divisor whose significand is all ones, which is sent down the library path together with scales too
+//     small for a finite reciprocal or an exact remainder);
+//   * adding 1.5 * 2^23 rounds q1 half-to-even and leaves the integer in the low mantissa bits (its low byte is the
+//     two's-complement int8).  |v| <= amax keeps |q1| <= 127, so no clamp is needed.
 struct RowQuant {
-  float scale, inv, half_lo;
-  bool exact;   // every element takes the IEEE division
+  float scale, inv;
+  bool exact;   // every element takes the library's IEEE division
 };
 
 __device__ __forceinline__ RowQuant make_row_quant(float amax) {
   RowQuant rq;
   rq.scale = __fdiv_rn(amax, 127.0f);
   rq.inv = __frcp_rn(rq.scale);
-  rq.half_lo = rq.scale * 0.49996f;
-  rq.exact = !(rq.scale > 1e-30f) || !(rq.inv < 1e30f);
+  rq.exact = !(rq.scale > 1e-28f) || !(rq.inv < 1e30f) || (__float_as_uint(rq.scale) & 0x7fffffu) == 0x7fffffu;
   return rq;
 }
 
 constexpr float kRoundMagic = 12582912.0f;   // 1.5 * 2^23
 
-// Word whose low byte is clamp(rint(v / scale)), by IEEE division.
+// Word whose low byte is clamp(rint(v / scale)), by the library's IEEE division.
 __device__ __forceinline__ uint32_t quant_word_exact(float v, float scale) {
   const float r = fminf(fmaxf(__fdiv_rn(v, scale), -127.f), 127.f);
   return __float_as_uint(__fadd_rn(r, kRoundMagic));
@@ -218,18 +218,15 @@ __device__ __forceinline__ uint32_t pack4_words(uint32_t a, uint32_t b, uint32_t
 __device__ __forceinline__ uint2 quant8(const float (&v)[8], const RowQuant& rq) {
   if (!(rq.scale > 0.f)) return make_uint2(0u, 0u);
   uint32_t w[8];
-  bool redo = rq.exact;
-  if (!redo) {
+  if (!rq.exact) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const float t = __fadd_rn(__fmul_rn(v[i], rq.inv), kRoundMagic);
-      const float q = __fadd_rn(t, -kRoundMagic);
-      const float e = __fmaf_rn(-q, rq.scale, v[i]);
-      redo |= fabsf(e) > rq.half_lo;
-      w[i] = __float_as_uint(t);
+      const float q0 = __fmul_rn(v[i], rq.inv);
+      const float r = __fmaf_rn(-q0, rq.scale, v[i]);
+      const float q1 = __fmaf_rn(r, rq.inv, q0);
+      w[i] = __float_as_uint(__fadd_rn(q1, kRoundMagic));
     }
-  }
-  if (redo) {
+  } else {
 #pragma unroll
     for (int i = 0; i < 8; ++i) w[i] = quant_word_exact(v[i], rq.scale);
   }
