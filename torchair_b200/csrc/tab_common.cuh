@@ -115,9 +115,17 @@ __device__ __forceinline__ uint32_t pack4_i8(int a, int b, int c, int d) {
          ((static_cast<uint32_t>(c) & 0xffu) << 16) | ((static_cast<uint32_t>(d) & 0xffu) << 24);
 }
 
-// silu(a) * b with separately rounded fp32 operations: a / (1 + exp(-a)) * b.
+// silu(a) * b = a / (1 + exp(-a)) * b in fp32.  The quotient is formed as an approximate reciprocal followed by one
+// remainder correction (two FMAs), which is within half an ulp and a bit of the IEEE quotient at a third of the
+// instructions of the library division; -a is capped at 80 so that the denominator stays finite (the capped results are
+// below 2e-33 in magnitude).
 __device__ __forceinline__ float silu_mul(float a, float b) {
-  float s = __fdiv_rn(a, __fadd_rn(1.0f, expf(-a)));
+  const float d = __fadd_rn(1.0f, expf(fminf(-a, 80.0f)));
+  float y;
+  asm("rcp.approx.f32 %0, %1;" : "=f"(y) : "f"(d));
+  const float q0 = __fmul_rn(a, y);
+  const float r = __fmaf_rn(-q0, d, a);
+  const float s = __fmaf_rn(r, y, q0);
   return __fmul_rn(s, b);
 }
 
