@@ -38,6 +38,7 @@ counters = {"dispatch_calls": 0, "combine_calls": 0, "wire_bytes_sent": 0}
 
 _transport: Dict[str, str] = {}
 _peer: Dict[tuple, "PeerExchange"] = {}
+_last_dispatch: Dict[tuple, "PeerExchange"] = {}
 
 
 def register_ep_group(name: str, process_group, transport: str = "auto") -> None:
@@ -275,6 +276,7 @@ def _dispatch_peer(kern, x, expert_ids, group_ep, pg, R, rank, E, quant_mode, nu
     dev = x.device
     row_bytes = H * send_rows.element_size()
     px = peer_exchange(group_ep, pg, R, rank, T, K, H, E, row_bytes, dev)
+    _last_dispatch[(group_ep, R, rank, T, K, H, E, dev.index)] = px     # the matching combine returns through the same buffers
     A = R * px.C
     st = px._stream()
     slot_idx = torch.empty_like(expand_idx)
@@ -298,10 +300,7 @@ def _combine_peer(kern, expand_x, expert_ids, expand_idx, ep_send_counts, expert
     E_l = E // R
     if expand_x.element_size() != 2:
         raise NotImplementedError("npu_moe_distribute_combine over peer memory: expand_x must be bfloat16 or float16")
-    px = None
-    for key, cand in _peer.items():
-        if key[0] == group_ep and key[1:7] == (R, rank, T, K, H, E) and key[8] == expand_x.device.index:
-            px = cand
+    px = _last_dispatch.get((group_ep, R, rank, T, K, H, E, expand_x.device.index))
     if px is None:
         raise RuntimeError("npu_moe_distribute_combine: no matching npu_moe_distribute_dispatch ran on this group")
     st = px._stream()
