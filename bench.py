@@ -72,18 +72,25 @@ def workload(n_gpus, name="auto"):
 # ---------------------------------------------------------------------------------------------------
 # CPU arm: the oracle on the host cores, on a bounded sample of the workload
 # ---------------------------------------------------------------------------------------------------
-def cpu_sample_config():
-    """1/8 of the decode layer: 32 tokens routed top-8 over 32 experts of the full expert shape, i.e. the same
-    ~8 rows per expert and the same bytes of weight per token as the full 256-token / 256-expert layer."""
+def cpu_sample_config(n_gpus=1):
+    """A bounded sample with the workload's rows per expert and expert shape.  N = 1: 32 tokens routed top-8 over 32
+    experts (1/8 of the 256-token / 256-expert layer).  N > 1: a 32-expert slice of one rank's experts with the tokens
+    scaled alike (128 tokens per rank spread over 256/N local experts)."""
     from oracle import moe_oracle as O
-    return O.MoeConfig("cfg1_sample", 32, 7168, 32, 8, 2048)
+    if n_gpus == 1:
+        return O.MoeConfig("cfg1_sample", 32, 7168, 32, 8, 2048), "1/8 of the 256-token/256-expert layer at the same rows per expert"
+    e_l = 256 // n_gpus
+    e_s = min(e_l, 32)
+    t_s = max(8, 128 * e_s // e_l)
+    return (O.MoeConfig("cfg2_sample", t_s, 7168, e_s, 8, 2048),
+            f"{e_s} of the {e_l} experts of one rank with {t_s} of its 128 tokens (same rows per expert)")
 
 
-def run_cpu(steps, warmup, seed):
+def run_cpu(steps, warmup, seed, n_gpus=1):
     import torch
     from oracle import moe_oracle as O
     torch.set_num_threads(os.cpu_count() or 1)
-    cfg = cpu_sample_config()
+    cfg, what = cpu_sample_config(n_gpus)
     w = O.make_weights(cfg, seed)
     x, ids, wt = O.make_tokens(cfg, seed)
     for _ in range(warmup):
@@ -93,8 +100,8 @@ def run_cpu(steps, warmup, seed):
         O.moe_layer([x], [ids], [wt], w)
     dt = time.perf_counter() - t0
     return {"value": cfg.T * steps / dt, "ms_per_step": dt / steps * 1e3, "cores": torch.get_num_threads(),
-            "sample": f"{cfg.T} tokens top-{cfg.K} over {cfg.E} experts (hidden {cfg.H}, intermediate {cfg.I}): 1/8 of the "
-                      f"256-token/256-expert layer at the same rows per expert; {steps} passes after {warmup} warm-up",
+            "sample": f"{cfg.T} tokens top-{cfg.K} over {cfg.E} experts (hidden {cfg.H}, intermediate {cfg.I}): {what}; "
+                      f"{steps} passes after {warmup} warm-up",
             "cpu_model": _cpu_model(), "torch": torch.__version__}
 
 
@@ -114,7 +121,7 @@ def reference_arm(args):
         return
     steps = max(1, min(args.steps, 100))         # a pass is ~0.2 s of CPU work: the whole run stays well under a minute
     warmup = max(1, min(args.warmup, 3))
-    r = run_cpu(steps, warmup, args.seed)
+    r = run_cpu(steps, warmup, args.seed, args.gpus)
     name = workload(args.gpus)[0]
     line = {"impl": "reference", "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
             "warmup": warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak",
@@ -384,6 +391,11 @@ def gpu_arm(args):
                         2 * M * H + 4 * M + 2 * T * H),
             "gmm_gate_up_fused": (ms_up, bytes_up), "gmm_down": (ms_down, bytes_down),
         }
+        # context: what plain torch kernels reach on this GPU for write-only and copy traffic of 1 GiB
+        probe = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
+        probe2 = torch.empty_like(probe)
+        table["context: torch fill (write only)"] = (time_each(lambda: probe.fill_(1), reps), probe.numel())
+        table["context: torch copy (read + write)"] = (time_each(lambda: probe2.copy_(probe), reps), 2 * probe.numel())
         report = {k: {"ms": round(ms, 4), "GB/s": gbs(b, ms), "frac_hbm": round(gbs(b, ms) / peak_gbs, 3)} for k, (ms, b) in table.items()}
         report["gmm_gate_up_fused"]["int8_tops"] = round(tops_up, 1)
         report["gmm_down"]["int8_tops"] = round(ops_down / (ms_down * 1e-3) / 1e12, 1)
@@ -398,7 +410,9 @@ def gpu_arm(args):
     if sampler is not None:
         sampler.stop()
     if rank == 0:
-        launches_per_step = 8 if world == 1 else 12   # sort x3, pack, gemm, requant, gemm, combine (+ plan/permute x2 each way)
+        # sort x3, pack, gemm, requant, gemm, combine; nccl adds plan + permute each way; peer adds send/unpack/return,
+        # two plans and eight flag kernels
+        launches_per_step = 8 if world == 1 else (21 if args.ep_transport == "peer" else 12)
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
                 "data": "synthetic",
