@@ -40,7 +40,7 @@ def parse_args():
                     help="N > 1: rows move by this library's peer-memory kernels (default) or by NCCL all-to-all")
     ap.add_argument("--kernels", action="store_true",
                     help="also time every kernel of the path alone and write the table to stderr (study aid, N=1)")
-    ap.add_argument("--workload", default="auto", choices=["auto"] + sorted(EXTRA_WORKLOADS),
+    ap.add_argument("--workload", default="auto", choices=["auto", "cfg3"] + sorted(EXTRA_WORKLOADS),
                     help="auto = the headline configuration for this GPU count; the others are single-GPU study cases")
     return ap.parse_args()
 
@@ -57,11 +57,21 @@ EXTRA_WORKLOADS = {
 }
 
 
+# expert-parallel prefill cases (tokens per rank, total experts): usable at N > 1
+EP_WORKLOADS = {
+    "cfg3": ("cfg3: expert-parallel prefill with Zipf(1.2) routing skew, DeepSeek-V3 shape, 8192 tokens/rank", 8192, 7168, 256, 8, 2048, 1.2),
+    "cfg4": ("cfg4: Qwen3-235B-A22B shape, 4096 tokens/rank", 4096, 4096, 128, 8, 1536, 0.0),
+}
+
+
 def workload(n_gpus, name="auto"):
     """(name, T per rank, H, E total, K, I, zipf) of the configuration benchmarked at this GPU count."""
+    if name in EP_WORKLOADS and n_gpus > 1:
+        desc, T, H, E, K, I, z = EP_WORKLOADS[name]
+        return f"{desc}, {n_gpus}xB200, {E // n_gpus} experts/rank", T, H, E, K, I, z
     if name != "auto":
         if n_gpus != 1:
-            raise RuntimeError("study workloads run on one GPU")
+            raise RuntimeError("this study workload runs on one GPU")
         return EXTRA_WORKLOADS[name]
     if n_gpus == 1:
         return "cfg1: 1xB200 decode MoE layer, DeepSeek-V3 shape, 256 tokens, all 256 experts local", 256, 7168, 256, 8, 2048, 0.0
