@@ -66,7 +66,7 @@ EP_WORKLOADS = {
 
 def workload(n_gpus, name="auto"):
     """(name, T per rank, H, E total, K, I, zipf) of the configuration benchmarked at this GPU count."""
-    if name in EP_WORKLOADS and n_gpus > 1:
+    if name in EP_WORKLOADS and (n_gpus > 1 or name not in EXTRA_WORKLOADS):
         desc, T, H, E, K, I, z = EP_WORKLOADS[name]
         return f"{desc}, {n_gpus}xB200, {E // n_gpus} experts/rank", T, H, E, K, I, z
     if name != "auto":
