@@ -248,7 +248,7 @@ TAB_API int tab_moe_init_routing_v2(const void* x, int x_dtype, const int32_t* e
  *   (grouped_matmul.py:210-365 followed by npu_dequant_swiglu_quant.py:5-64; the reference's own fused
  *   form is converter grouped_matmul_swiglu_quant_v2.py:86-166).  packed weight [E, 2*I, Kd];
  *   weight_scale fp32 [E, 2*I]; x_scale fp32 [M]; yq int8 [M, I]; y_scale fp32 [M]; rows outside every
- *   group give yq = 0, y_scale = 0.  Workspace holds the fp32 SwiGLU values between the two phases.
+ *   group are left untouched.  Workspace holds the fp32 SwiGLU values between the two phases.
  *
  * tab_gmm_status: host-side; copies the device status word of the last GEMM launches on this device
  *   (0 = fine, otherwise the code of the bounded wait that gave up) after synchronising `stream`.

@@ -156,7 +156,8 @@ def grouped_matmul_w8a8(x: torch.Tensor, weight: torch.Tensor, scale: Optional[t
     Expert e owns rows [s_e, s_e+c_e).  acc = x[rows] @ weight[e] in exact int32 (+ int32 bias[e]).
     output_dtype 3 -> raw int32 accumulators; 15/5 -> bf16/fp16 of
     (float(acc) * per_token_scale[m]) * scale[e, n]   (decision: this order, no fused multiply-add).
-    Rows not covered by any group are zero.
+    Rows not covered by any group are zero here; the CUDA path leaves them unwritten (with expert parallelism the
+    input is sized for the worst case and the uncovered tail is never read), so tests compare covered rows only.
     """
     M = x.shape[0]
     E, Kd, N = weight.shape

@@ -211,7 +211,7 @@ __global__ void __launch_bounds__(THREADS) dequant_swiglu_quant_kernel(
 }
 
 // Second phase of the fused gate_up GEMM: h fp32 [rows, cols] + row amax bits -> int8 + scale; rows at or past the
-// rows covered by group_list give zeros.
+// rows covered by group_list are left untouched.
 template <int THREADS>
 __global__ void __launch_bounds__(THREADS) quant_from_f32_kernel(const float* __restrict__ h,
                                                                 const uint32_t* __restrict__ amax_bits,
@@ -236,11 +236,7 @@ __global__ void __launch_bounds__(THREADS) quant_from_f32_kernel(const float* __
   const int nchunk = cols >> 3;
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     int8_t* yr = y + row * cols;
-    if (row >= valid) {
-      for (int ch = threadIdx.x; ch < nchunk; ch += THREADS) *reinterpret_cast<uint2*>(yr + ch * 8) = make_uint2(0, 0);
-      if (threadIdx.x == 0) scale[row] = 0.f;
-      continue;
-    }
+    if (row >= valid) break;   // rows outside every group are not touched (they may be a large unused tail)
     const RowQuant sc = make_row_quant(__uint_as_float(amax_bits[row]));
     if (threadIdx.x == 0) scale[row] = sc.scale;
     const float* hr = h + row * cols;

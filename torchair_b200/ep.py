@@ -162,10 +162,7 @@ class CudaKernels:
     def exchange_rows(src, src_scales, plan, R, E_l, slot_rows, direction, dst_rows, zero_fill):
         dst = torch.empty((dst_rows, src.shape[1]), dtype=src.dtype, device=src.device)
         dst_scales = None if src_scales is None else torch.empty((dst_rows,), dtype=torch.float32, device=src.device)
-        if src.shape[0] == 0:  # nothing arrived: the kernel would have no source pointer to read
-            dst.zero_()
-            if dst_scales is not None:
-                dst_scales.zero_()
+        if src.shape[0] == 0:  # nothing arrived: no row of dst is defined, and the kernel would have no source to read
             return dst, dst_scales
         _lib.call("tab_moe_exchange_rows", _ptr(src), _ptr(src_scales), _ptr(plan), R, E_l, slot_rows, direction,
                   src.shape[1] * src.element_size(), dst_rows, int(zero_fill), _ptr(dst), _ptr(dst_scales), _stream(src))
@@ -288,7 +285,7 @@ def _dispatch_peer(kern, x, expert_ids, group_ep, pg, R, rank, E, quant_mode, nu
     plan, nums, ep_recv = kern.exchange_plan(px.counts_local.view(R, E_l), R, E_l, px.C, nums_type)
     expand_x = torch.empty((A, H), dtype=send_rows.dtype, device=dev)
     dyn = torch.empty((A,), dtype=torch.float32, device=dev)
-    _lib.call("tab_ep_unpack_rows", _ptr(px.recv_local), _ptr(plan), R, E_l, row_bytes, A, 1, _ptr(expand_x), _ptr(dyn), st)
+    _lib.call("tab_ep_unpack_rows", _ptr(px.recv_local), _ptr(plan), R, E_l, row_bytes, A, 0, _ptr(expand_x), _ptr(dyn), st)
     px.signal(px.KIND_ACK_D)
     counters["wire_bytes_sent"] += T * K * (row_bytes + 16)
     return expand_x, dyn, slot_idx, nums, ep_recv, tp_recv, expand_scales
@@ -327,6 +324,8 @@ def _remember(key, value):
 def dispatch(kern, x, expert_ids, group_ep, R, rank, E, quant_mode, nums_type, tp_slots=1):
     """Returns the seven outputs of npu_moe_distribute_dispatch.
 
+    Rows of expand_x / dynamic_scales past the received total (sum of expert_token_nums) are not written: expand_x is
+    sized for the worst case, and nothing downstream reads that tail.
     Handshake tensors (consumed only by combine): expand_idx[t*K+k] = position of that copy in this rank's
     send order (sorted by global expert id, stable); ep_recv_count[e*R+s] = rows received for local expert e
     from rank s; tp_recv_count and expand_scales are zero.
@@ -374,7 +373,7 @@ def dispatch(kern, x, expert_ids, group_ep, R, rank, E, quant_mode, nums_type, t
     dist.all_to_all_single(wire_scales, send_scales, recv_splits, send_splits, group=pg)
     counters["wire_bytes_sent"] += (sum(send_splits) - send_splits[rank]) * (H * send_rows.element_size() + 4)
     plan, nums, ep_recv = kern.exchange_plan(recv_counts.view(R, E_l), R, E_l, 0, nums_type)
-    expand_x, dyn_scales = kern.exchange_rows(wire_rows, wire_scales, plan, R, E_l, 0, 0, A, True)
+    expand_x, dyn_scales = kern.exchange_rows(wire_rows, wire_scales, plan, R, E_l, 0, 0, A, False)
     _remember((ep_recv.data_ptr(), expand_idx.data_ptr()), (send_splits, recv_splits))
     return expand_x, dyn_scales, expand_idx, nums, ep_recv, tp_recv, expand_scales
 

@@ -354,8 +354,9 @@ def _gmm_cuda(x, weight, *, bias=None, scale=None, offset=None, antiquant_scale=
             pts = pts.contiguous()
     xs = xs.contiguous()
     wp = packed_weight(w)
-    # rows outside every group are defined to be zero
-    y = torch.zeros((M, N), dtype=out_dt, device=xs.device)
+    # rows outside every group are left unwritten: with expert parallelism x is sized for the worst case and most of
+    # it is an unused tail, which nothing downstream reads
+    y = torch.empty((M, N), dtype=out_dt, device=xs.device)
     _lib.call("tab_grouped_matmul_w8a8", _ptr(xs), _ptr(wp), _ptr(sc), _ptr(pts), _ptr(group_list), int(group_list_type or 0),
               M, Kd, N, E, _ST_INV[out_dt], _ptr(y), _stream(xs))
     return [y]
