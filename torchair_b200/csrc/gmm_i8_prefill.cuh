@@ -201,7 +201,7 @@ gmm_i8_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
 #pragma unroll
               for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(h[j]));
 #pragma unroll
-              for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(hrow + c + j) = make_float4(h[j], h[j + 1], h[j + 2], h[j + 3]);
+              for (int j = 0; j < 16; j += 4) __stcs(reinterpret_cast<float4*>(hrow + c + j), make_float4(h[j], h[j + 1], h[j + 2], h[j + 3]));
             } else {
               for (int j = 0; j < 16; ++j)
                 if (cg0 + c + j < p.half) {
@@ -260,7 +260,7 @@ gmm_i8_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
               if (grow < row_end && cvalid) {
                 const uint4 v = *reinterpret_cast<const uint4*>(patch + r * kPfOutPitch + piece * 16);
                 uint8_t* o = static_cast<uint8_t*>(p.out) + (static_cast<int64_t>(grow) * p.N + c0 + c) * esz + piece * 16;
-                *reinterpret_cast<uint4*>(o) = v;
+                __stcs(reinterpret_cast<uint4*>(o), v);   // streamed: outputs must not push weights and rows out of L2
               }
             }
           }
