@@ -494,3 +494,24 @@ def test_quantiser_equals_ieee_division_on_a_large_sample(dev):
             want_q = torch.round(xf[lo:lo + 8192] / want_s[lo:lo + 8192, None]).clamp_(-127, 127).to(torch.int8)
             bad += int((want_q != q[lo:lo + 8192]).sum())
         assert bad == 0
+
+
+@pytest.mark.parametrize("M,Kd,I,E", [(3000, 512, 256, 4), (8192, 1024, 1536, 8), (700, 256, 136, 2)])
+def test_fused_gate_up_prefill_orientation_equals_unfused(dev, M, Kd, I, E):
+    """Experts with hundreds of rows take the prefill-orientation kernel (fp32 SwiGLU values + row amax, then the
+    requantise pass): results must equal int32 GEMM + npu_dequant_swiglu_quant bit for bit."""
+    g = torch.Generator().manual_seed(M + I)
+    x = torch.randint(-127, 128, (M, Kd), generator=g, dtype=torch.int8).to(dev)
+    w = torch.randint(-127, 128, (E, Kd, 2 * I), generator=g, dtype=torch.int8).to(dev)
+    ws = (torch.rand(E, 2 * I, generator=g) * 9e-3 + 1e-3).to(dev)
+    xs = (torch.rand(M, generator=g) * 1e-2).to(dev)
+    covered = M - 37
+    cnt = torch.bincount(torch.randint(0, E, (covered,), generator=g), minlength=E).to(dev)
+    for _ in range(2):      # twice: the row-amax scratch in the workspace must be reset by every call
+        hq, hs = npu.npu_grouped_matmul_swiglu_quant_v2(x, [w], [ws], xs, cnt, group_list_type=1)
+    _gmm_ok(dev)
+    h32 = npu.npu_grouped_matmul([x], [w], group_list=cnt, split_item=2, group_type=0, group_list_type=1, output_dtype=3)[0]
+    q2, s2 = npu.npu_dequant_swiglu_quant(h32, weight_scale=ws, activation_scale=xs, group_index=cnt, activate_left=True, quant_mode=1)
+    assert torch.equal(hq[:covered], q2[:covered]) and torch.equal(hs[:covered], s2[:covered])
+    ref32 = O.grouped_matmul_w8a8(x.cpu(), w.cpu(), None, None, cnt.cpu(), 1, 3)
+    assert torch.equal(ref32[:covered], h32.cpu()[:covered])
