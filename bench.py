@@ -262,13 +262,15 @@ def gpu_arm(args):
         else:
             layer(x_d, ids_d, wt_d)
 
-    def timed(fn, steps):
+    def timed(fn, steps, finish=None):
         sync_all()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t_a = time.time()
         e0.record()
         for _ in range(steps):
             fn()
+        if finish is not None:
+            finish()                 # the timed stream waits for the last result to reach the host buffer
         e1.record()
         torch.cuda.synchronize()
         t_b = time.time()
@@ -287,21 +289,60 @@ def gpu_arm(args):
     ms_per_step = total_ms / args.steps
     value = T * world * args.steps / (total_ms * 1e-3)
 
-    # (2) end to end through the public ops with host buffers: H2D of the step's inputs, layer, D2H of the result
-    def step_e2e():
-        x_d.copy_(x_h, non_blocking=True)
-        ids_d.copy_(ids_h, non_blocking=True)
-        wt_d.copy_(wt_h, non_blocking=True)
-        if graph is not None:
-            graph.replay()
-            out_h.copy_(out, non_blocking=True)
-        else:
+    # (2) end to end through the public ops with host buffers: H2D of the step's inputs, layer, D2H of the result.
+    # With a captured layer the three stages of consecutive steps overlap on three streams over two buffer sets (copy in
+    # step s+1 while step s computes and step s-1 copies out); the caller reads a result one step after it was issued.
+    finish_e2e = None
+    if graph is not None:
+        x_d2, ids_d2, wt_d2 = x_d.clone(), ids_d.clone(), wt_d.clone()
+        out_h2 = torch.empty_like(out_h).pin_memory()
+        graph2 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph2):
+            out2 = layer(x_d2, ids_d2, wt_d2)
+        sets = [(x_d, ids_d, wt_d, graph, out, out_h), (x_d2, ids_d2, wt_d2, graph2, out2, out_h2)]
+        copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
+        ev_in = [torch.cuda.Event(), torch.cuda.Event()]
+        ev_comp = [torch.cuda.Event(), torch.cuda.Event()]
+        ev_out = [torch.cuda.Event(), torch.cuda.Event()]
+        state = {"s": 0}
+
+        def step_e2e():
+            s_ = state["s"]
+            b = s_ & 1
+            xd, idd, wtd, g, o, oh = sets[b]
+            main = torch.cuda.current_stream()
+            with torch.cuda.stream(copy_in):
+                copy_in.wait_event(ev_comp[b])          # this set's previous compute has consumed its inputs
+                xd.copy_(x_h, non_blocking=True)
+                idd.copy_(ids_h, non_blocking=True)
+                wtd.copy_(wt_h, non_blocking=True)
+                ev_in[b].record(copy_in)
+            main.wait_event(ev_in[b])
+            main.wait_event(ev_out[b])                  # this set's previous result has left the device
+            g.replay()
+            ev_comp[b].record(main)
+            with torch.cuda.stream(copy_out):
+                copy_out.wait_event(ev_comp[b])
+                oh.copy_(o, non_blocking=True)
+                ev_out[b].record(copy_out)
+            if s_ >= 1:
+                ev_out[b ^ 1].synchronize()             # the caller reads the previous step's result
+            state["s"] = s_ + 1
+
+        def finish_e2e():
+            last = (state["s"] - 1) & 1
+            torch.cuda.current_stream().wait_event(ev_out[last])
+    else:
+        def step_e2e():
+            x_d.copy_(x_h, non_blocking=True)
+            ids_d.copy_(ids_h, non_blocking=True)
+            wt_d.copy_(wt_h, non_blocking=True)
             out_h.copy_(layer(x_d, ids_d, wt_d), non_blocking=True)
-        torch.cuda.current_stream().synchronize()     # the caller reads the result every step
+            torch.cuda.current_stream().synchronize()     # the caller reads the result every step
 
     for _ in range(args.warmup):
         step_e2e()
-    e2e_ms = timed(step_e2e, args.steps)
+    e2e_ms = timed(step_e2e, args.steps, finish_e2e)
     e2e_value = T * world * args.steps / (e2e_ms * 1e-3)
     h2d = x_h.numel() * 2 + ids_h.numel() * 4 + wt_h.numel() * 4
     d2h = out_h.numel() * 2
@@ -432,7 +473,9 @@ def gpu_arm(args):
                            "l2": "inputs larger than L2: every step streams this rank's int8 expert weights "
                                  f"({(w1.numel() + w2.numel()) / 1e9:.2f} GB) from HBM"},
                 "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                        "ms_per_step": e2e_ms / args.steps},
+                        "ms_per_step": e2e_ms / args.steps,
+                        "pipelining": "copy-in, compute and copy-out of consecutive steps overlap (two buffer sets)"
+                        if graph is not None else "none"},
                 "gpu_launches": launches_per_step * args.steps,
                 "roofline": roofline, "cpu_baseline": cpu,
                 "clocks": sampler.summary(windows) if sampler is not None else None}

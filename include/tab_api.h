@@ -160,7 +160,7 @@ TAB_API int tab_moe_exchange_rows(const void* src, const float* src_scales, cons
  *   layout on every rank: recv [R][slot_rows][row_bytes + 16] (the 16-byte tail carries the fp32 scale),
  *   counts int32 [R][E_l], ret [R][slot_rows][row_bytes], flag arrays uint64 [R], counters uint64.
  *   tab_ep_signal      stores (counter + 1) into peer_flags[r] for every r, then counter += 1.
- *   tab_ep_wait        waits (bounded, ~4 s) until flags[s] >= counter + pre_increment for every s, then
+ *   tab_ep_wait        waits (bounded, ~2 s) until flags[s] >= counter + pre_increment for every s, then
  *                      counter += 1; on expiry writes `code` into *status (device int) and continues.
  *   tab_ep_send_rows   sender: row p of the expert-sorted rows goes to rank d = owner of its expert, slot
  *                      [my_rank][p - first row of d]; per-expert counts go to peer_counts; expand_idx_slot[f]

@@ -515,3 +515,31 @@ def test_fused_gate_up_prefill_orientation_equals_unfused(dev, M, Kd, I, E):
     assert torch.equal(hq[:covered], q2[:covered]) and torch.equal(hs[:covered], s2[:covered])
     ref32 = O.grouped_matmul_w8a8(x.cpu(), w.cpu(), None, None, cnt.cpu(), 1, 3)
     assert torch.equal(ref32[:covered], h32.cpu()[:covered])
+
+
+def test_peer_flag_wait_runs_out_and_reports_instead_of_hanging(dev):
+    """Failure detection on the GPU without faulting it: a flag that nobody sets makes the bounded wait of the
+    peer-memory exchange give up (about 2 s), write its code into the status word and let the stream continue."""
+    import ctypes
+    import time
+    from torchair_b200 import _lib
+    R = 2
+    flags = torch.zeros(R, dtype=torch.int64, device=dev)        # arrival counters that no peer will ever advance
+    counter = torch.zeros(1, dtype=torch.int64, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    after = torch.zeros(1, dtype=torch.int32, device=dev)
+    stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    P = lambda t: ctypes.c_void_p(t.data_ptr())
+    t0 = time.time()
+    _lib.call("tab_ep_wait", P(flags), P(counter), R, 1, P(status), 123, stream)
+    after.fill_(7)                                                # work queued behind the wait still runs
+    torch.cuda.synchronize(dev)
+    dt = time.time() - t0
+    assert int(status.item()) == 123 and int(counter.item()) == 1 and int(after.item()) == 7
+    assert 0.5 < dt < 30.0
+    # an acknowledgement wait whose flags already hold the expected value returns at once
+    status.zero_()
+    flags.fill_(1)
+    _lib.call("tab_ep_wait", P(flags), P(counter), R, 0, P(status), 124, stream)
+    torch.cuda.synchronize(dev)
+    assert int(status.item()) == 0 and int(counter.item()) == 2

@@ -22,7 +22,7 @@
 namespace tab {
 
 constexpr int kEpMaxRanks = 64;
-constexpr long long kEpWaitCycles = 8000000000LL;   // ~4 s: peers may be seconds apart on their first call
+constexpr long long kEpWaitCycles = 4000000000LL;   // ~2 s; ranks are aligned by a host barrier when the buffers are created
 
 __device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
   unsigned long long v;
