@@ -220,6 +220,17 @@ TAB_API int tab_moe_compute_expert_tokens(const int32_t* sorted_experts, int64_t
                                   tab_stream_t stream);
 TAB_API int tab_moe_gating_top_k_softmax(const void* x, int dtype, int64_t tokens, int64_t num_experts, int64_t k, void* y,
                                  int32_t* expert_idx, int32_t* row_idx, tab_stream_t stream);
+ /* npu_moe_gating_top_k (converter npu_moe_gating_top_k.py:4-22 -> MoeGatingTopK, experiment_ops.h:3722-3761):
+  * scores = softmax(x) (norm_type 0) or sigmoid(x) (1) in fp32; selection score = scores + bias; with group_count > 1 the
+  * experts form contiguous groups, each scored by its maximum (group_select_mode 0) or by the sum of its two largest
+  * selection scores (1), and only the k_group best groups stay eligible; the k best eligible experts are taken (ties:
+  * lower id).  y [tokens, k] = the selected scores without bias, for sigmoid divided by (their sum + eps), times
+  * routed_scaling_factor; expert_idx int32 [tokens, k]; out fp32 [tokens, experts] = all scores (NULL to skip).
+  * num_experts <= 1024, k <= 32, group_count <= 32. */
+TAB_API int tab_moe_gating_top_k(const void* x, const void* bias, int dtype, int64_t tokens, int64_t num_experts, int64_t k,
+                         int64_t k_group, int64_t group_count, int group_select_mode, int norm_type,
+                         float routed_scaling_factor, float eps, void* y, int32_t* expert_idx, float* out,
+                         tab_stream_t stream);
 TAB_API int tab_moe_finalize_routing(const void* rows, int dtype, const void* skip1, const void* skip2, const void* bias,
                              const float* scales, const int32_t* src_to_dst, const int32_t* expert_for_row, int64_t T,
                              int64_t K, int64_t H, void* out, tab_stream_t stream);

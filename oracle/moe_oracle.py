@@ -270,6 +270,39 @@ def moe_gating_top_k_softmax(x: torch.Tensor, k: int):
     return order.values[:, :k].to(x.dtype), order.indices[:, :k].to(torch.int32), row_idx.contiguous()
 
 
+def moe_gating_top_k(x, k, bias=None, k_group=1, group_count=1, group_select_mode=0, norm_type=0, routed_scaling_factor=1.0,
+                     eps=1e-20):
+    """MoeGatingTopK (converter npu_moe_gating_top_k.py:4-22; experiment_ops.h:3722-3761).  Decisions: scores = softmax
+    (norm_type 0) or sigmoid (1) in fp32; the bias enters the selection only; groups are contiguous and scored by their
+    maximum (mode 0) or the sum of their two largest selection scores (mode 1); ties keep the lower index; y = selected
+    scores, for sigmoid divided by (their sum in selection order + eps), times routed_scaling_factor."""
+    T, E = x.shape
+    xf = x.float()
+    sc = torch.softmax(xf, dim=-1) if norm_type == 0 else 1.0 / (1.0 + torch.exp(-xf))
+    sel = sc + bias.float() if bias is not None else sc.clone()
+    if group_count > 1:
+        G = E // group_count
+        g = sel.view(T, group_count, G)
+        if group_select_mode == 0:
+            gs = g.amax(dim=-1)
+        else:
+            top2 = torch.sort(g, dim=-1, descending=True, stable=True).values[..., :2]
+            gs = top2[..., 0] + top2[..., 1]
+        keep = torch.sort(gs, dim=-1, descending=True, stable=True).indices[:, :k_group]
+        mask = torch.zeros(T, group_count, dtype=torch.bool)
+        mask.scatter_(1, keep, True)
+        sel = torch.where(mask.unsqueeze(-1).expand(T, group_count, G).reshape(T, E), sel, torch.full_like(sel, float("-inf")))
+    idx = torch.sort(sel, dim=-1, descending=True, stable=True).indices[:, :k]
+    y = torch.gather(sc, 1, idx)
+    if norm_type == 1:
+        ysum = torch.zeros(T)
+        for j in range(k):
+            ysum = ysum + y[:, j]
+        y = y / (ysum + eps).unsqueeze(-1)
+    y = y * routed_scaling_factor
+    return y.to(x.dtype), idx.to(torch.int32), sc
+
+
 def moe_finalize_routing(rows, skip1, skip2, bias, scales, src_to_dst, expert_for_row):
     """MoeFinalizeRouting, dropless (converter npu_moe_finalize_routing.py:21-41):
     out[t] = sum_k scales[t,k] * (rows[src_to_dst[k*T+t]] + bias[expert[t,k]]) + skip1[t] + skip2[t].

@@ -32,6 +32,9 @@ CONVERTER_FILES = {
     "npu_moe_gating_top_k_softmax": "moe_gating_top_k_softmax",
     "npu_moe_finalize_routing": "npu_moe_finalize_routing",
     "npu_moe_init_routing_v2": "npu_moe_init_routing_v2",
+    "npu_moe_gating_top_k": "npu_moe_gating_top_k",
+    "npu_moe_distribute_dispatch_v2": "moe_distribute_dispatch_v2",
+    "npu_moe_distribute_combine_v2": "moe_distribute_combine_v2",
 }
 
 

@@ -543,3 +543,39 @@ def test_peer_flag_wait_runs_out_and_reports_instead_of_hanging(dev):
     _lib.call("tab_ep_wait", P(flags), P(counter), R, 0, P(status), 124, stream)
     torch.cuda.synchronize(dev)
     assert int(status.item()) == 0 and int(counter.item()) == 2
+
+
+@pytest.mark.parametrize("E,groups,k_group,k,mode,norm", [(256, 8, 4, 8, 1, 1), (256, 1, 1, 8, 0, 0), (128, 4, 2, 6, 0, 1),
+                                                          (64, 8, 3, 4, 1, 0)])
+def test_gating_top_k_group_limited(dev, E, groups, k_group, k, mode, norm):
+    g = torch.Generator().manual_seed(E + k)
+    T = 333
+    x = torch.randn(T, E, generator=g)
+    bias = torch.randn(E, generator=g) * 0.1
+    y, idx, sc = O.moe_gating_top_k(x, k, bias, k_group, groups, mode, norm, 2.5, 1e-20)
+    yg, ig, sg = npu.npu_moe_gating_top_k(x.to(dev), k, bias=bias.to(dev), k_group=k_group, group_count=groups,
+                                          group_select_mode=mode, norm_type=norm, out_flag=True, routed_scaling_factor=2.5)
+    assert torch.equal(idx, ig.cpu()), "selected experts are index work: exact"
+    torch.testing.assert_close(sg.cpu(), sc, rtol=1e-5, atol=1e-7)
+    torch.testing.assert_close(yg.cpu(), y, rtol=1e-5, atol=1e-7)
+    with pytest.raises(NotImplementedError):
+        npu.npu_moe_gating_top_k(x.to(dev), k, renorm=1)
+    with pytest.raises(RuntimeError):
+        npu.npu_moe_gating_top_k(x.to(dev), k, k_group=groups + 1, group_count=groups)
+
+
+def test_second_generation_dispatch_combine_names(dev):
+    cfg = O.CONFIGS["cfg0"]
+    x, ids, wt = O.make_tokens(cfg, 0)
+    a = npu.npu_moe_distribute_dispatch(x.to(dev), ids.to(dev), "", 1, 0, cfg.E, quant_mode=2)
+    b = npu.npu_moe_distribute_dispatch_v2(x.to(dev), ids.to(dev), "", 1, 0, cfg.E, quant_mode=2)
+    for u, v in zip(a, b):
+        assert torch.equal(u, v)
+    y = torch.randn(cfg.T * cfg.K, cfg.H, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16).to(dev)
+    o1 = npu.npu_moe_distribute_combine(y, ids.to(dev), a[2], a[4], wt.to(dev), "", 1, 0, cfg.E)
+    o2 = npu.npu_moe_distribute_combine_v2(y, ids.to(dev), b[2], b[4], wt.to(dev), "", 1, 0, cfg.E)
+    assert torch.equal(o1, o2)
+    with pytest.raises(NotImplementedError):
+        npu.npu_moe_distribute_dispatch_v2(x.to(dev), ids.to(dev), "", 1, 0, cfg.E, quant_mode=2, zero_expert_num=1)
+    with pytest.raises(NotImplementedError):
+        npu.npu_moe_distribute_combine_v2(y, ids.to(dev), b[2], b[4], wt.to(dev), "", 1, 0, cfg.E, comm_alg="fullmesh")

@@ -192,3 +192,19 @@ def test_neighbour_ops_known_answers():
     assert torch.equal(ex, xx[[0, 1, 3, 0, 2, 3, 1, 2]])
     _, ridx1, tok0, _ = O.moe_init_routing_v2(xx, ids, 3, -1, 0, 1)
     assert tok0.tolist() == [3, 6, 8] and ridx1[ridx.long()].tolist() == list(range(8))
+
+
+def test_gating_top_k_group_limited_known_answer():
+    # 8 experts in 4 groups of 2; group scores (max): g0=.9 g1=.8 g2=.7 g3=.1 -> keep g0,g1; top-3 of {0,1,2,3}
+    x = torch.logit(torch.tensor([[0.9, 0.2, 0.8, 0.5, 0.7, 0.6, 0.1, 0.05]]))
+    y, idx, sc = O.moe_gating_top_k(x, 3, None, k_group=2, group_count=4, group_select_mode=0, norm_type=1)
+    assert idx.tolist() == [[0, 2, 3]]
+    assert torch.allclose(sc, torch.tensor([[0.9, 0.2, 0.8, 0.5, 0.7, 0.6, 0.1, 0.05]]), atol=1e-6)
+    assert torch.allclose(y, torch.tensor([[0.9, 0.8, 0.5]]) / 2.2, atol=1e-6)
+    # top-2 sums: g0=1.1 g1=1.3 g2=1.3 g3=.15 -> keep g1, g2 (tie keeps the lower group first; both kept)
+    _, idx2, _ = O.moe_gating_top_k(x, 2, None, k_group=2, group_count=4, group_select_mode=1, norm_type=1)
+    assert idx2.tolist() == [[2, 4]]
+    # the bias steers the selection but not the returned score
+    b = torch.tensor([0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 5.0, 0.0])
+    y3, idx3, _ = O.moe_gating_top_k(x, 1, b, norm_type=1, routed_scaling_factor=2.0)
+    assert idx3.tolist() == [[6]] and torch.allclose(y3, torch.tensor([[2.0]]), atol=1e-5)

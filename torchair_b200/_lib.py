@@ -31,6 +31,7 @@ SIGNATURES = {
     "tab_moe_exchange_rows": [_P, _P, _P, _L, _L, _L, _I, _L, _L, _I, _P, _P, _P],
     "tab_moe_compute_expert_tokens": [_P, _L, _L, _P, _P],
     "tab_moe_gating_top_k_softmax": [_P, _I, _L, _L, _L, _P, _P, _P, _P],
+    "tab_moe_gating_top_k": [_P, _P, _I, _L, _L, _L, _L, _L, _I, _I, c_float, c_float, _P, _P, _P, _P],
     "tab_moe_finalize_routing": [_P, _I, _P, _P, _P, _P, _P, _P, _L, _L, _L, _P, _P],
     "tab_moe_init_routing_v2": [_P, _I, _P, _L, _L, _L, _L, _I, _I, _I, _P, _P, _P, _P, _P, c_size_t, _P],
     "tab_ep_signal": [_P, _P, _L, _P],

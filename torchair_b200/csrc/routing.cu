@@ -834,3 +834,181 @@ extern "C" int tab_moe_init_routing_v2(const void* x, int x_dtype, const int32_t
   tokens_count_or_cumsum_kernel<<<1, 1024, 0, st>>>(counts, (int)expert_num, tokens_num_type, expert_tokens);
   return check_launch("init_routing_v2");
 }
+
+// ---- npu_moe_gating_top_k: softmax or sigmoid scores, optional selection bias, group-limited top-k ----------------
+namespace tab {
+
+__device__ __forceinline__ void warp_argmax(float& v, int& idx) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (ov > v || (ov == v && oi < idx)) {
+      v = ov;
+      idx = oi;
+    }
+  }
+}
+
+// One warp per token; E <= 1024 scores, 32 per lane (element e = i*32 + lane); group_count <= 32 contiguous groups.
+template <typename T>
+__global__ void __launch_bounds__(128) gating_topk_kernel(const T* __restrict__ x, const T* __restrict__ bias, int64_t tokens, int E,
+                                                          int k, int k_group, int group_count, int group_select_mode, int norm_type,
+                                                          float scaling, float eps, T* __restrict__ y, int32_t* __restrict__ expert_idx,
+                                                          float* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp_global = (blockIdx.x * 128 + threadIdx.x) >> 5;
+  const int64_t warps_total = static_cast<int64_t>(gridDim.x) * 4;
+  const int G = E / group_count;
+  const float kGone = -INFINITY;
+  for (int64_t t = warp_global; t < tokens; t += warps_total) {
+    float sc[kGateMaxPerLane], sel[kGateMaxPerLane];
+    float m = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < kGateMaxPerLane; ++i) {
+      const int e = i * 32 + lane;
+      sc[i] = e < E ? Elem<T>::to_f32(x[t * E + e]) : -INFINITY;
+      m = fmaxf(m, sc[i]);
+    }
+    if (norm_type == 0) {
+      m = warp_max(m);
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < kGateMaxPerLane; ++i) {
+        sc[i] = i * 32 + lane < E ? expf(sc[i] - m) : 0.f;
+        sum += sc[i];
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+#pragma unroll
+      for (int i = 0; i < kGateMaxPerLane; ++i) sc[i] = __fdiv_rn(sc[i], sum);
+    } else {
+#pragma unroll
+      for (int i = 0; i < kGateMaxPerLane; ++i) sc[i] = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-sc[i])));
+    }
+#pragma unroll
+    for (int i = 0; i < kGateMaxPerLane; ++i) {
+      const int e = i * 32 + lane;
+      if (e < E) {
+        if (out) out[t * E + e] = sc[i];
+        sel[i] = bias ? __fadd_rn(sc[i], Elem<T>::to_f32(bias[e])) : sc[i];
+      } else {
+        sel[i] = kGone;
+      }
+    }
+    if (group_count > 1) {
+      // score of group g lands in lane g: its maximum, or the sum of its two largest selection scores
+      float gscore = kGone;
+      for (int g = 0; g < group_count; ++g) {
+        float b1 = kGone;
+        int i1 = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < kGateMaxPerLane; ++i) {
+          const int e = i * 32 + lane;
+          if (e < E && e / G == g && sel[i] > b1) {
+            b1 = sel[i];
+            i1 = e;
+          }
+        }
+        warp_argmax(b1, i1);
+        float s = b1;
+        if (group_select_mode == 1) {
+          float b2 = kGone;
+          int i2 = 0x7fffffff;
+#pragma unroll
+          for (int i = 0; i < kGateMaxPerLane; ++i) {
+            const int e = i * 32 + lane;
+            if (e < E && e / G == g && e != i1 && sel[i] > b2) {
+              b2 = sel[i];
+              i2 = e;
+            }
+          }
+          warp_argmax(b2, i2);
+          s = __fadd_rn(b1, b2);
+        }
+        if (lane == g) gscore = s;
+      }
+      unsigned keep = 0u;
+      for (int j = 0; j < k_group; ++j) {
+        float v = gscore;
+        int gi = lane < group_count ? lane : 0x7fffffff;
+        if (lane >= group_count) v = kGone;
+        warp_argmax(v, gi);
+        keep |= 1u << gi;
+        if (lane == gi) gscore = kGone;
+      }
+#pragma unroll
+      for (int i = 0; i < kGateMaxPerLane; ++i) {
+        const int e = i * 32 + lane;
+        if (e < E && !((keep >> (e / G)) & 1u)) sel[i] = kGone;
+      }
+    }
+    float ysum = 0.f;
+    float mine = 0.f;       // lane j keeps the j-th selected score (k <= 32) for the normalisation pass
+    int mine_e = 0;
+    for (int j = 0; j < k; ++j) {
+      float best = kGone;
+      int best_e = 0x7fffffff;
+#pragma unroll
+      for (int i = 0; i < kGateMaxPerLane; ++i) {
+        if (sel[i] > best) {
+          best = sel[i];
+          best_e = i * 32 + lane;
+        }
+      }
+      warp_argmax(best, best_e);
+      float score = 0.f;
+#pragma unroll
+      for (int i = 0; i < kGateMaxPerLane; ++i) {
+        if ((best_e & 31) == lane && i == (best_e >> 5)) {
+          score = sc[i];
+          sel[i] = kGone;
+        }
+      }
+      score = __shfl_sync(0xffffffffu, score, best_e & 31);
+      ysum = __fadd_rn(ysum, score);
+      if (lane == j) {
+        mine = score;
+        mine_e = best_e;
+      }
+    }
+    if (lane < k) {
+      float v = mine;
+      if (norm_type == 1) v = __fdiv_rn(v, __fadd_rn(ysum, eps));
+      v = __fmul_rn(v, scaling);
+      y[t * k + lane] = Elem<T>::from_f32(v);
+      expert_idx[t * k + lane] = mine_e;
+    }
+  }
+}
+
+}  // namespace tab
+
+extern "C" int tab_moe_gating_top_k(const void* x, const void* bias, int dtype, int64_t tokens, int64_t num_experts, int64_t k,
+                                    int64_t k_group, int64_t group_count, int group_select_mode, int norm_type,
+                                    float routed_scaling_factor, float eps, void* y, int32_t* expert_idx, float* out,
+                                    tab_stream_t stream) {
+  if (tokens < 0 || num_experts <= 0 || k <= 0 || k > num_experts || k > 32)
+    return fail(TAB_ERR_BAD_ARG, "gating_top_k: tokens=%lld experts=%lld k=%lld (k must be in [1, 32])", (long long)tokens, (long long)num_experts, (long long)k);
+  if (num_experts > 32 * kGateMaxPerLane) return fail(TAB_ERR_UNSUPPORTED, "gating_top_k: more than %d experts", 32 * kGateMaxPerLane);
+  if (group_count < 1 || group_count > 32 || num_experts % group_count != 0 || k_group < 1 || k_group > group_count ||
+      k > k_group * (num_experts / group_count))
+    return fail(TAB_ERR_BAD_ARG, "gating_top_k: group_count=%lld k_group=%lld do not fit %lld experts and k=%lld", (long long)group_count, (long long)k_group, (long long)num_experts, (long long)k);
+  if ((group_select_mode != 0 && group_select_mode != 1) || (norm_type != 0 && norm_type != 1))
+    return fail(TAB_ERR_UNSUPPORTED, "gating_top_k: group_select_mode and norm_type must be 0 or 1");
+  if (group_select_mode == 1 && num_experts / group_count < 2) return fail(TAB_ERR_BAD_ARG, "gating_top_k: top-2 group score needs groups of at least two experts");
+  if (tokens == 0) return TAB_OK;
+  if (!x || !y || !expert_idx) return fail(TAB_ERR_BAD_ARG, "gating_top_k: null pointer");
+  const int grid = grid_for((tokens + 3) / 4, 8);
+  cudaStream_t st = as_stream(stream);
+#define TAB_GATE_LAUNCH(TYPE)                                                                                                     \
+  gating_topk_kernel<TYPE><<<grid, 128, 0, st>>>(static_cast<const TYPE*>(x), static_cast<const TYPE*>(bias), tokens, (int)num_experts, \
+                                                 (int)k, (int)k_group, (int)group_count, group_select_mode, norm_type,           \
+                                                 routed_scaling_factor, eps, static_cast<TYPE*>(y), expert_idx, out)
+  if (dtype == TAB_F32) TAB_GATE_LAUNCH(float);
+  else if (dtype == TAB_BF16) TAB_GATE_LAUNCH(__nv_bfloat16);
+  else if (dtype == TAB_F16) TAB_GATE_LAUNCH(__half);
+  else return fail(TAB_ERR_UNSUPPORTED, "gating_top_k: dtype %d (want 5, 6 or 15)", dtype);
+#undef TAB_GATE_LAUNCH
+  return check_launch("gating_top_k");
+}

@@ -54,6 +54,25 @@ _npu.define("npu_grouped_matmul_swiglu_quant_v2(Tensor x, Tensor[] weight, Tenso
             "int? x_scale_dtype=None) -> (Tensor, Tensor)")
 _npu.define("npu_moe_compute_expert_tokens(Tensor sorted_experts, int num_experts) -> Tensor")
 _npu.define("npu_moe_gating_top_k_softmax(Tensor x, Tensor? finished=None, int k=1) -> (Tensor, Tensor, Tensor)")
+_npu.define("npu_moe_gating_top_k(Tensor x, int k, *, Tensor? bias=None, int k_group=1, int group_count=1, int group_select_mode=0, "
+            "int renorm=0, int norm_type=0, bool out_flag=False, float routed_scaling_factor=1.0, float eps=1e-20) "
+            "-> (Tensor, Tensor, Tensor)")
+_V2_DISPATCH = ("(Tensor x, Tensor expert_ids, str group_ep, int ep_world_size, int ep_rank_id, int moe_expert_num, *, "
+                "Tensor? scales=None, Tensor? x_active_mask=None, Tensor? expert_scales=None, Tensor? elastic_info=None, "
+                "Tensor? performance_info=None, str group_tp=\"\", int tp_world_size=0, int tp_rank_id=0, int expert_shard_type=0, "
+                "int shared_expert_num=1, int shared_expert_rank_num=0, int quant_mode=0, int global_bs=0, "
+                "int expert_token_nums_type=1, str comm_alg=\"\", int zero_expert_num=0, int copy_expert_num=0, "
+                "int const_expert_num=0, int? y_dtype=None, int? x_dtype=None, int? scales_dtype=None) "
+                "-> (Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor)")
+_npu.define("npu_moe_distribute_dispatch_v2" + _V2_DISPATCH)
+_npu.define("npu_moe_distribute_combine_v2(Tensor expand_x, Tensor expert_ids, Tensor assist_info_for_combine, Tensor ep_send_counts, "
+            "Tensor expert_scales, str group_ep, int ep_world_size, int ep_rank_id, int moe_expert_num, *, "
+            "Tensor? tp_send_counts=None, Tensor? x_active_mask=None, Tensor? expand_scales=None, Tensor? shared_expert_x=None, "
+            "Tensor? elastic_info=None, Tensor? ori_x=None, Tensor? const_expert_alpha_1=None, Tensor? const_expert_alpha_2=None, "
+            "Tensor? const_expert_v=None, Tensor? performance_info=None, str group_tp=\"\", int tp_world_size=0, int tp_rank_id=0, "
+            "int expert_shard_type=0, int shared_expert_num=1, int shared_expert_rank_num=0, int global_bs=0, "
+            "int comm_quant_mode=0, str comm_alg=\"\", int zero_expert_num=0, int copy_expert_num=0, int const_expert_num=0) "
+            "-> Tensor")
 _npu.define("npu_moe_finalize_routing(Tensor expanded_permuted_rows, Tensor? skip1, Tensor? skip2, Tensor? bias, Tensor? scales, "
             "Tensor expanded_src_to_dst_row, Tensor? export_for_source_row, int? drop_pad_mode=0) -> Tensor")
 _npu.define("npu_moe_init_routing_v2(Tensor x, Tensor expert_idx, *, Tensor? scale=None, Tensor? offset=None, int active_num=-1, "
@@ -452,6 +471,79 @@ def _gating_cuda(x, finished=None, k=1):
     return y, ei, ri
 
 
+def _gating2_meta(x, k, *, bias=None, k_group=1, group_count=1, group_select_mode=0, renorm=0, norm_type=0, out_flag=False,
+                  routed_scaling_factor=1.0, eps=1e-20):
+    # shape rule of python/torchair/_contrib/custom_torch_ops/auto_register_custom_torch_ops.py:69-79
+    if x.dim() != 2 or k < 1 or k > x.shape[1]:
+        raise RuntimeError("npu_moe_gating_top_k: x must be [tokens, experts] and 1 <= k <= experts")
+    return (x.new_empty((x.size(0), k)), x.new_empty((x.size(0), k), dtype=torch.int32),
+            x.new_empty((x.size(0), x.size(1)), dtype=torch.float32))
+
+
+def _gating2_cuda(x, k, *, bias=None, k_group=1, group_count=1, group_select_mode=0, renorm=0, norm_type=0, out_flag=False,
+                  routed_scaling_factor=1.0, eps=1e-20):
+    op = "npu_moe_gating_top_k"
+    y, ei, out = _gating2_meta(x, k)
+    if renorm != 0:
+        raise NotImplementedError(f"{op}: renorm must be 0 (scores are normalised before the selection)")
+    xc = x.contiguous()
+    if bias is not None:
+        if bias.dtype != x.dtype or bias.numel() != x.shape[1]:
+            raise RuntimeError(f"{op}: bias must be [experts] of the dtype of x")
+        bias = bias.contiguous()
+    _lib.call("tab_moe_gating_top_k", _ptr(xc), _ptr(bias), _st(x.dtype, op), x.shape[0], x.shape[1], k, k_group, group_count,
+              int(group_select_mode), int(norm_type), float(routed_scaling_factor), float(eps), _ptr(y), _ptr(ei), _ptr(out),
+              _stream(xc))
+    return y, ei, out
+
+
+def _v2_extras(op, **kw):
+    for name, v in kw.items():
+        if isinstance(v, str):
+            if v != "":
+                raise NotImplementedError(f"{op}: `{name}`={v!r} is outside the path")
+        elif isinstance(v, int) and not isinstance(v, bool):
+            if v != 0:
+                raise NotImplementedError(f"{op}: `{name}`={v} is outside the path")
+        elif v is not None:
+            raise NotImplementedError(f"{op}: `{name}` is outside the path and must be None")
+
+
+def _dispatch_v2(impl):
+    def fn(x, expert_ids, group_ep, ep_world_size, ep_rank_id, moe_expert_num, *, scales=None, x_active_mask=None,
+           expert_scales=None, elastic_info=None, performance_info=None, group_tp="", tp_world_size=0, tp_rank_id=0,
+           expert_shard_type=0, shared_expert_num=1, shared_expert_rank_num=0, quant_mode=0, global_bs=0,
+           expert_token_nums_type=1, comm_alg="", zero_expert_num=0, copy_expert_num=0, const_expert_num=0, y_dtype=None,
+           x_dtype=None, scales_dtype=None):
+        _v2_extras("npu_moe_distribute_dispatch_v2", elastic_info=elastic_info, performance_info=performance_info,
+                   comm_alg=comm_alg, zero_expert_num=zero_expert_num, copy_expert_num=copy_expert_num,
+                   const_expert_num=const_expert_num, y_dtype=y_dtype, x_dtype=x_dtype, scales_dtype=scales_dtype)
+        return impl(x, expert_ids, group_ep, ep_world_size, ep_rank_id, moe_expert_num, scales=scales, x_active_mask=x_active_mask,
+                    expert_scales=expert_scales, group_tp=group_tp, tp_world_size=tp_world_size, tp_rank_id=tp_rank_id,
+                    expert_shard_type=expert_shard_type, shared_expert_num=shared_expert_num,
+                    shared_expert_rank_num=shared_expert_rank_num, quant_mode=quant_mode, global_bs=global_bs,
+                    expert_token_nums_type=expert_token_nums_type)
+    return fn
+
+
+def _combine_v2(impl):
+    def fn(expand_x, expert_ids, assist_info_for_combine, ep_send_counts, expert_scales, group_ep, ep_world_size, ep_rank_id,
+           moe_expert_num, *, tp_send_counts=None, x_active_mask=None, expand_scales=None, shared_expert_x=None, elastic_info=None,
+           ori_x=None, const_expert_alpha_1=None, const_expert_alpha_2=None, const_expert_v=None, performance_info=None,
+           group_tp="", tp_world_size=0, tp_rank_id=0, expert_shard_type=0, shared_expert_num=1, shared_expert_rank_num=0,
+           global_bs=0, comm_quant_mode=0, comm_alg="", zero_expert_num=0, copy_expert_num=0, const_expert_num=0):
+        _v2_extras("npu_moe_distribute_combine_v2", elastic_info=elastic_info, ori_x=ori_x, const_expert_alpha_1=const_expert_alpha_1,
+                   const_expert_alpha_2=const_expert_alpha_2, const_expert_v=const_expert_v, performance_info=performance_info,
+                   comm_alg=comm_alg, zero_expert_num=zero_expert_num, copy_expert_num=copy_expert_num,
+                   const_expert_num=const_expert_num)
+        return impl(expand_x, expert_ids, assist_info_for_combine, ep_send_counts, expert_scales, group_ep, ep_world_size,
+                    ep_rank_id, moe_expert_num, tp_send_counts=tp_send_counts, x_active_mask=x_active_mask,
+                    expand_scales=expand_scales, shared_expert_x=shared_expert_x, group_tp=group_tp, tp_world_size=tp_world_size,
+                    tp_rank_id=tp_rank_id, expert_shard_type=expert_shard_type, shared_expert_num=shared_expert_num,
+                    shared_expert_rank_num=shared_expert_rank_num, global_bs=global_bs, comm_quant_mode=comm_quant_mode)
+    return fn
+
+
 def _finalize_meta(expanded_permuted_rows, skip1, skip2, bias, scales, expanded_src_to_dst_row, export_for_source_row,
                    drop_pad_mode=0):
     rows = expanded_permuted_rows
@@ -603,14 +695,21 @@ for _name, _meta, _cuda in (
         ("npu_moe_compute_expert_tokens", _cet_meta, _cet_cuda),
         ("npu_moe_gating_top_k_softmax", _gating_meta, _gating_cuda),
         ("npu_moe_finalize_routing", _finalize_meta, _finalize_cuda),
+        ("npu_moe_gating_top_k", _gating2_meta, _gating2_cuda),
         ("npu_moe_init_routing_v2", _irv2_meta, _irv2_cuda),
         ("npu_moe_distribute_dispatch", _dispatch_meta, _dispatch_cuda),
         ("npu_moe_distribute_combine", _combine_meta, _combine_cuda)):
     _npu.impl(_name, _meta, "Meta")
     _npu.impl(_name, _cuda, "CUDA")
 _npu.impl("npu_dynamic_quant_asymmetric", _dynamic_quant_asym, "CompositeExplicitAutograd")
+# the second-generation dispatch / combine operators share the kernels; their additional arguments must stay at defaults
+_npu.impl("npu_moe_distribute_dispatch_v2", _dispatch_v2(_dispatch_meta), "Meta")
+_npu.impl("npu_moe_distribute_dispatch_v2", _dispatch_v2(_dispatch_cuda), "CUDA")
+_npu.impl("npu_moe_distribute_combine_v2", _combine_v2(_combine_meta), "Meta")
+_npu.impl("npu_moe_distribute_combine_v2", _combine_v2(_combine_cuda), "CUDA")
 
 OP_NAMES = ["npu_moe_init_routing", "npu_dynamic_quant", "npu_dynamic_quant_asymmetric", "npu_swiglu",
             "npu_dequant_swiglu_quant", "npu_grouped_matmul", "npu_grouped_matmul_swiglu_quant_v2",
             "npu_moe_distribute_dispatch", "npu_moe_distribute_combine", "npu_moe_compute_expert_tokens",
-            "npu_moe_gating_top_k_softmax", "npu_moe_finalize_routing", "npu_moe_init_routing_v2"]
+            "npu_moe_gating_top_k_softmax", "npu_moe_finalize_routing", "npu_moe_init_routing_v2", "npu_moe_gating_top_k",
+            "npu_moe_distribute_dispatch_v2", "npu_moe_distribute_combine_v2"]
