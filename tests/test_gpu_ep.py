@@ -45,6 +45,27 @@ def _worker(rank, world, port, outdir, transport):
                                 ep_world_size=world, ep_rank_id=rank, moe_expert_num=cfg.E, fused=fused)
                 results[(cfg_name, fused)] = out.cpu()
             results[(cfg_name, "disp")] = [t.cpu() for t in disp]
+        # the same layer through torch.compile: with the peer transport the whole expert-parallel layer is one CUDA graph
+        from torchair_b200 import backend as _backend
+        cfg = O.CONFIGS["cfg0"]
+        E_l = cfg.E // world
+        w = O.make_weights(cfg, 0, experts=range(rank * E_l, (rank + 1) * E_l))
+        gw = [t.to(dev) for t in (w.w1, w.s1, w.w2, w.s2)]
+        x, ids, wt = O.make_tokens(cfg, 0, rank)
+
+        def fn(x, ids, wt, w1, s1, w2, s2):
+            return moe_layer(x, ids, wt, w1, s1, w2, s2, group_ep="ep", ep_world_size=world, ep_rank_id=rank,
+                             moe_expert_num=cfg.E, fused=False)
+        config = torchair_b200.CompilerConfig()
+        config.mode = "reduce-overhead"
+        compiled = torch.compile(fn, backend=torchair_b200.get_npu_backend(compiler_config=config), fullgraph=True, dynamic=False)
+        caps = _backend.counters["captures"]
+        with torch.no_grad():
+            for _ in range(3):
+                out_c = compiled(x.to(dev), ids.to(dev), wt.to(dev), *gw)
+        torch.cuda.synchronize(dev)
+        results["compiled"] = out_c.cpu()
+        results["captures"] = _backend.counters["captures"] - caps
         results["status"] = torchair_b200.gmm_status(dev)
         from torchair_b200 import ep as _ep
         results["peer_status"] = _ep.peer_status()
@@ -103,3 +124,6 @@ def test_expert_parallel_layer_on_gpus_matches_oracle(world, transport, tmp_path
             for fused in (True, False):
                 torch.testing.assert_close(got[r][(cfg_name, fused)].float(), ref[r].float(), rtol=1e-2, atol=1e-2)
             assert torch.equal(got[r][(cfg_name, True)], got[r][(cfg_name, False)])
+            if cfg_name == "cfg0":
+                assert torch.equal(got[r]["compiled"], got[r][(cfg_name, False)]), "compiled and eager layers must agree"
+                assert got[r]["captures"] == (1 if transport == "peer" else 0)
