@@ -337,7 +337,14 @@ static int make_maps(const int8_t* x, const int8_t* wp, int64_t M, int64_t Kd, i
   return TAB_OK;
 }
 
+// Token-tile width of the decode orientation: the smallest of 16..256 that holds 1.5 x the average rows per expert.
+// TAB_GMM_NT=16|32|64|128|256 overrides it (tuning aid).
 static int pick_nt(int64_t M, int64_t E) {
+  const char* f = getenv("TAB_GMM_NT");
+  if (f != nullptr) {
+    const int v = atoi(f);
+    if (v == 16 || v == 32 || v == 64 || v == 128 || v == 256) return v;
+  }
   const double avg = static_cast<double>(M) / static_cast<double>(E);
   const int opts[5] = {16, 32, 64, 128, 256};
   for (int i = 0; i < 5; ++i)
