@@ -579,3 +579,43 @@ def test_second_generation_dispatch_combine_names(dev):
         npu.npu_moe_distribute_dispatch_v2(x.to(dev), ids.to(dev), "", 1, 0, cfg.E, quant_mode=2, zero_expert_num=1)
     with pytest.raises(NotImplementedError):
         npu.npu_moe_distribute_combine_v2(y, ids.to(dev), b[2], b[4], wt.to(dev), "", 1, 0, cfg.E, comm_alg="fullmesh")
+
+
+def test_full_size_prefill_layer_properties(dev):
+    """Config 4 at full size (4096 tokens, 128 experts, hidden 4096, intermediate 1536; 32768 rows through the
+    prefill-orientation GEMM): sampled experts against the oracle, every row of a sampled expert, plus the permutation
+    and count properties of the dispatch."""
+    cfg = O.CONFIGS["cfg4"]
+    g = torch.Generator(device=dev).manual_seed(11)
+    w1 = torch.randint(-127, 128, (cfg.E, cfg.H, 2 * cfg.I), generator=g, dtype=torch.int8, device=dev)
+    w2 = torch.randint(-127, 128, (cfg.E, cfg.I, cfg.H), generator=g, dtype=torch.int8, device=dev)
+    s1 = torch.rand(cfg.E, 2 * cfg.I, generator=g, device=dev) * 9e-3 + 1e-3
+    s2 = torch.rand(cfg.E, cfg.H, generator=g, device=dev) * 9e-3 + 1e-3
+    x, ids, wt = O.make_tokens(cfg, 0)
+    xd, idd, wtd = x.to(dev), ids.to(dev), wt.to(dev)
+    ex, xs, expand_idx, nums, ep_recv, _, _ = npu.npu_moe_distribute_dispatch(xd, idd, "", 1, 0, cfg.E, quant_mode=2)
+    M = cfg.T * cfg.K
+    assert int(nums.sum()) == M and torch.equal(torch.sort(expand_idx).values.cpu(), torch.arange(M, dtype=torch.int32))
+    assert torch.equal(nums.cpu(), torch.bincount(ids.reshape(-1).long(), minlength=cfg.E))
+    hq, hs = npu.npu_grouped_matmul_swiglu_quant_v2(ex, [w1], [s1], xs, nums, group_list_type=1)
+    y = npu.npu_grouped_matmul([hq], [w2], scale=[s2], per_token_scale=[hs], group_list=nums, split_item=2, group_type=0,
+                               group_list_type=1, output_dtype=15)[0]
+    _gmm_ok(dev)
+    starts = (torch.cumsum(nums, 0) - nums).cpu()
+    for e in (0, 63, 127):
+        s0, c = int(starts[e]), int(nums[e])
+        we = O.MoeWeights(w1[e:e + 1].cpu(), s1[e:e + 1].cpu(), w2[e:e + 1].cpu(), s2[e:e + 1].cpu())
+        col = {}
+        yref = O.expert_ffn(ex[s0:s0 + c].cpu(), xs[s0:s0 + c].cpu(), torch.tensor([c]), we, col)
+        _swiglu_quant_close(hq[s0:s0 + c], hs[s0:s0 + c], col["hq"], col["hs"])
+        # the down GEMM on the GPU's own int8 activations must be exact
+        yexact = O.grouped_matmul_w8a8(hq[s0:s0 + c].cpu(), we.w2, we.s2, hs[s0:s0 + c].cpu(), torch.tensor([c]), 1, 15)
+        assert torch.equal(y[s0:s0 + c].cpu(), yexact)
+        torch.testing.assert_close(y[s0:s0 + c].cpu().float(), yref.float(), rtol=1e-2, atol=1e-2)
+    out = npu.npu_moe_distribute_combine(y, idd, expand_idx, ep_recv, wtd, "", 1, 0, cfg.E)
+    pos = expand_idx.view(cfg.T, cfg.K).cpu()
+    ref_out = O.weighted_gather_sum(y.cpu(), pos, wt)
+    assert torch.equal(out.cpu(), ref_out)
+    del w1, w2
+    torchair_b200.clear_weight_cache()
+    torch.cuda.empty_cache()
