@@ -1,6 +1,6 @@
 """Generates tests/golden/conformance.json from the reference's own converter files.
 
-Run in a container that has the reference checked out (default /root/reference, or REFERENCE_ROOT):
+Run where the reference project is checked out (REFERENCE_ROOT points at it):
     python tests/golden/make_conformance.py
 It imports the reference's pure-Python converter layer over a stand-in for its native module
 ``torchair.core._torchair`` (the native module needs the vendor SDK and cannot be built), after this
