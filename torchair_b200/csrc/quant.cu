@@ -343,9 +343,9 @@ extern "C" int tab_dequant_swiglu_quant(const int32_t* x, const float* weight_sc
   cudaStream_t st = as_stream(stream);
   const int nchunk = (int)(half / 8);
   const size_t smem = group_index ? static_cast<size_t>(num_groups) * sizeof(int) : 0;
-  if (nchunk <= 64 * kDsqChunks)
+  if (nchunk <= 64 * kDsqChunks / 2)
     dequant_swiglu_quant_kernel<64><<<row_grid(rows, 64), 64, smem, st>>>(x, weight_scale, (int)ws_groups, activation_scale, group_index, (int)num_groups, activate_left, rows, (int)half, y, scale);
-  else if (nchunk <= 128 * kDsqChunks)
+  else if (nchunk <= 128 * kDsqChunks / 2)
     dequant_swiglu_quant_kernel<128><<<row_grid(rows, 128), 128, smem, st>>>(x, weight_scale, (int)ws_groups, activation_scale, group_index, (int)num_groups, activate_left, rows, (int)half, y, scale);
   else
     dequant_swiglu_quant_kernel<256><<<row_grid(rows, 256), 256, smem, st>>>(x, weight_scale, (int)ws_groups, activation_scale, group_index, (int)num_groups, activate_left, rows, (int)half, y, scale);
