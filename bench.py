@@ -442,6 +442,13 @@ def gpu_arm(args):
                         2 * M * H + 4 * M + 2 * T * H),
             "gmm_gate_up_fused": (ms_up, bytes_up), "gmm_down": (ms_down, bytes_down),
         }
+        # down GEMM + logit-weighted scatter-add as one operator (int32 accumulators round-trip through the workspace)
+        tok_of_row = torch.arange(M, device=dev) % T          # K rows per token; which ones does not matter for the timing
+        lg = torch.rand(M, device=dev)
+        table["gmm_down+finalize_routing"] = (
+            time_each(lambda: npu.npu_grouped_matmul_finalize_routing(hq, w2, nums, scale=s2, pertoken_scale=hs, logit=lg,
+                                                                      row_index=tok_of_row, output_bs=T, group_list_type=1), reps),
+            experts_hit * I * H + rows * I + 2 * rows * H * 4 + T * H * 4 + experts_hit * H * 4 + rows * 16)
         # context: what plain torch kernels reach on this GPU for write-only and copy traffic of 1 GiB
         probe = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
         probe2 = torch.empty_like(probe)

@@ -14,7 +14,7 @@
  *   - Return value: 0 on success, a negative tab_status otherwise.  tab_last_error() returns a message for
  *     the calling thread's most recent failure.  No call aborts or throws.
  *   - dtype arguments use the c10::ScalarType integers the reference's converters use
- *     (python/torchair/ge/_ge_graph.py:215-270): 1 int8, 3 int32, 5 float16, 6 float32, 15 bfloat16.
+ *     (python/torchair/ge/_ge_graph.py:215-270): 1 int8, 3 int32, 4 int64, 5 float16, 6 float32, 15 bfloat16.
  *   - Row-major, contiguous tensors; rows of 8-bit data must be 16-byte multiples.
  */
 #ifndef TAB_API_H_
@@ -45,7 +45,7 @@ enum tab_status {
   TAB_ERR_TIMEOUT = -6      /* a bounded device-side wait gave up (read back via tab_gmm_status) */
 };
 
-enum tab_dtype { TAB_I8 = 1, TAB_I32 = 3, TAB_F16 = 5, TAB_F32 = 6, TAB_BF16 = 15 };
+enum tab_dtype { TAB_I8 = 1, TAB_I32 = 3, TAB_I64 = 4, TAB_F16 = 5, TAB_F32 = 6, TAB_BF16 = 15 };
 
 /* Library version (major*10000 + minor*100 + patch).  Nearest reference analogue: the pybind module
  * `_torchair` (torchair/core/npu_wrapper.cpp:28-84). */
@@ -261,6 +261,16 @@ TAB_API int tab_moe_init_routing_v2(const void* x, int x_dtype, const int32_t* e
  *   weight_scale fp32 [E, 2*I]; x_scale fp32 [M]; yq int8 [M, I]; y_scale fp32 [M]; rows outside every
  *   group are left untouched.  Workspace holds the fp32 SwiGLU values between the two phases.
  *
+ * tab_grouped_matmul_finalize_routing: the down GEMM and the combine as one call (converter
+ *   grouped_matmul_finalize_routing.py:57-133 -> GroupedMatmulFinalizeRouting, fusion_ops.h:640-725), int8 x and
+ *   int8 weight only.  y fp32 [output_bs, N] = 0; rows [shared_input_offset, +shared_rows) = shared_input_weight *
+ *   shared_input (bf16 [shared_rows, N], NULL to skip); then for every row m inside a group e:
+ *   y[row_index[m]] += logit[m] * ((float(acc[m]) * per_token_scale[m]) * scale[e] + bias[e]),
+ *   scale fp32 [E, N], bias bf16 [E, N], logit fp32 [M], per_token_scale fp32 [M] (each NULL = neutral),
+ *   row_index int32 or int64 [M] (row_index_dtype 3 or 4; entries outside [0, output_bs) add nothing).
+ *   The additions into one output row are 16-byte L2 reductions in no fixed order.  Requires N % 4 == 0;
+ *   the workspace holds the int32 accumulators.
+ *
  * tab_gmm_status: host-side; copies the device status word of the last GEMM launches on this device
  *   (0 = fine, otherwise the code of the bounded wait that gave up) after synchronising `stream`.
  * ------------------------------------------------------------------------------------------------- */
@@ -276,6 +286,14 @@ TAB_API int tab_grouped_matmul_swiglu_quant(const int8_t* x, const int8_t* packe
                                     int64_t M, int64_t Kd, int64_t I, int64_t E, int activate_left,
                                     int8_t* yq, float* y_scale, void* workspace, size_t workspace_bytes,
                                     tab_stream_t stream);
+TAB_API int tab_grouped_matmul_finalize_routing_workspace_bytes(int64_t M, int64_t N, size_t* bytes);
+TAB_API int tab_grouped_matmul_finalize_routing(const int8_t* x, const int8_t* packed_weight, const float* scale,
+                                        const void* bias, const float* per_token_scale, const int64_t* group_list,
+                                        int group_list_type, int64_t M, int64_t Kd, int64_t N, int64_t E,
+                                        const void* shared_input, int64_t shared_rows, float shared_input_weight,
+                                        int64_t shared_input_offset, const float* logit, const void* row_index,
+                                        int row_index_dtype, int64_t output_bs, float* y, void* workspace,
+                                        size_t workspace_bytes, tab_stream_t stream);
 TAB_API int tab_gmm_status(int* status_host, tab_stream_t stream);
 
 #ifdef __cplusplus

@@ -183,6 +183,44 @@ def grouped_matmul_w8a8(x: torch.Tensor, weight: torch.Tensor, scale: Optional[t
     return y
 
 
+def grouped_matmul_finalize_routing(x, weight, group_list, scale=None, bias=None, pertoken_scale=None, shared_input=None,
+                                    logit=None, row_index=None, shared_input_weight=1.0, shared_input_offset=0,
+                                    output_bs=0, group_list_type=1):
+    """GroupedMatmulFinalizeRouting, int8 x int8 (fusion_ops.h:640-725; converter
+    grouped_matmul_finalize_routing.py:57-133, which sets output_bs = rows of x when it is 0).
+
+    y fp32 [output_bs, N] starts at zero; rows [shared_input_offset, +rows of shared_input) are
+    shared_input_weight * shared_input; then, in row order, every row m inside a group e adds
+    logit[m] * ((float(acc[m]) * pertoken_scale[m]) * scale[e] + bias[e]) into y[row_index[m]]
+    (decision: this operation order, every step rounded to fp32; the device adds in no fixed order).
+    """
+    M = x.shape[0]
+    E, Kd, N = weight.shape
+    rows = int(output_bs) or M
+    y = torch.zeros(rows, N, dtype=torch.float32)
+    if shared_input is not None:
+        off = int(shared_input_offset)
+        y[off:off + shared_input.shape[0]] = shared_input.float() * torch.tensor(shared_input_weight, dtype=torch.float32)
+    starts, counts = group_bounds(group_list, group_list_type)
+    for e in range(E):
+        s, c = int(starts[e]), int(counts[e])
+        if c <= 0:
+            continue
+        v = int8_matmul(x[s:s + c], weight[e]).float()
+        if pertoken_scale is not None:
+            v = v * pertoken_scale[s:s + c].float().unsqueeze(-1)
+        if scale is not None:
+            v = v * scale[e].float().unsqueeze(0)
+        if bias is not None:
+            v = v + bias[e].float().unsqueeze(0)
+        if logit is not None:
+            v = v * logit[s:s + c].float().unsqueeze(-1)
+        idx = row_index[s:s + c].long()
+        ok = (idx >= 0) & (idx < rows)
+        y.index_add_(0, idx[ok], v[ok])
+    return y
+
+
 # --------------------------------------------------------------------------------------------------
 # npu_dequant_swiglu_quant
 # --------------------------------------------------------------------------------------------------

@@ -104,6 +104,12 @@ def test_meta_shape_rules():
         assert len(out) == 1 and out[0].shape == (16, 96) and out[0].dtype == dt
     with pytest.raises(ValueError):   # the reference rejects int8 output (grouped_matmul.py:188-194)
         npu.npu_grouped_matmul([xq], [w], group_list=gl, split_item=2, group_type=0, output_dtype=1)
+    # output_bs == 0 means one output row per row of x (grouped_matmul_finalize_routing.py:113-114); only fp32 output
+    fr = npu.npu_grouped_matmul_finalize_routing(xq, w, gl)
+    assert fr.shape == (16, 96) and fr.dtype == torch.float32
+    assert npu.npu_grouped_matmul_finalize_routing(xq, w, gl, output_bs=5, dtype=torch.float32).shape == (5, 96)
+    with pytest.raises(RuntimeError, match="Not supported output dtype"):
+        npu.npu_grouped_matmul_finalize_routing(xq, w, gl, dtype=torch.bfloat16)
     with pytest.raises(NotImplementedError):
         npu.npu_grouped_matmul([xq.to(torch.bfloat16)], [w], group_list=gl, split_item=2, group_type=0, output_dtype=15)
     hq, hs = npu.npu_grouped_matmul_swiglu_quant_v2(xq, [w], [torch.empty(4, 96, device=m)], torch.empty(16, device=m), gl)

@@ -377,6 +377,55 @@ def test_torch_compile_backend_runs_the_ops_and_captures_a_cuda_graph(dev):
     assert backend.counters["captures"] == cap_before + 1 and backend.counters["replays"] >= 3
 
 
+def test_shared_expert_on_a_second_stream_inside_one_cuda_graph(dev):
+    """The documented use of npu_stream_switch: the shared expert's dense MLP on its own stream while the routed experts
+    run on the main one, joined by npu_wait_tensor.  The compiled graph must give exactly the result of the same ops run
+    one after the other, and must still be captured as one CUDA graph."""
+    from torchair_b200 import backend, scope
+    cfg = O.CONFIGS["cfg0"]
+    w = O.make_weights(cfg, 0)
+    x, ids, wt = O.make_tokens(cfg, 0)
+    w1, s1, w2, s2 = (t.to(dev) for t in (w.w1, w.s1, w.w2, w.s2))
+
+    def shared_expert(x):      # stands for the dense MLP; built from this library's deterministic kernels so that == holds
+        q, s = torch.ops.npu.npu_dynamic_quant(torch.cat([x, x * 0.5], dim=-1))
+        return torch.ops.npu.npu_swiglu((q.float() * s[:, None]).to(torch.bfloat16))
+
+    def block(x, ids, wt, streams):
+        if streams:
+            with scope.npu_stream_switch("shared_expert", 1):
+                shared = shared_expert(x)
+        else:
+            shared = shared_expert(x)
+        routed = moe_layer(x, ids, wt, w1, s1, w2, s2)
+        if streams:
+            routed = scope.npu_wait_tensor(routed, shared)
+        return routed + shared
+
+    xd, idd, wtd = x.to(dev), ids.to(dev), wt.to(dev)
+    want = block(xd, idd, wtd, False)
+    config = torchair_b200.CompilerConfig()
+    config.mode = "reduce-overhead"
+    cap_before = backend.counters["captures"]
+    model = torch.compile(lambda a, b, c: block(a, b, c, True), backend=torchair_b200.get_npu_backend(compiler_config=config),
+                          fullgraph=True, dynamic=False)
+    with torch.no_grad():
+        for _ in range(3):
+            out = model(xd, idd, wtd)
+    torch.cuda.synchronize()
+    _gmm_ok(dev)
+    assert torch.equal(out, want)
+    assert backend.counters["captures"] == cap_before + 1
+    # eager replay of the same graph (no capture) takes the same streams
+    config2 = torchair_b200.CompilerConfig()
+    model2 = torch.compile(lambda a, b, c: block(a, b, c, True), backend=torchair_b200.get_npu_backend(compiler_config=config2),
+                           fullgraph=True, dynamic=False)
+    with torch.no_grad():
+        out2 = model2(xd, idd, wtd)
+    torch.cuda.synchronize()
+    assert torch.equal(out2, want)
+
+
 def test_quantiser_fast_path_is_exact_at_ties_and_extreme_scales(dev):
     """The quantiser approximates v/scale by v*(1/scale) and redoes the division only near rounding ties: rows built
     from exact ties (k + 0.5) * scale, denormal-scale rows and huge rows must still match IEEE division bit for bit."""
@@ -452,6 +501,49 @@ def test_init_routing_v2_bit_exact(dev, quant_mode, tok_type, row_type):
         assert a.dtype == b.dtype and torch.equal(a, b.cpu())
     with pytest.raises(NotImplementedError):
         npu.npu_moe_init_routing_v2(x.to(dev), ids.to(dev), expert_num=cfg.E, drop_pad_mode=1)
+
+
+@pytest.mark.parametrize("M,Kd,N,E,idx_dtype,extras,gl_type", [
+    (256, 512, 1024, 8, torch.int64, True, 1),      # decode orientation, every optional input
+    (2000, 256, 516, 4, torch.int32, False, 0),     # prefill orientation, cumulative group list, N % 8 != 0
+    (640, 2048, 7168, 16, torch.int64, True, 1),    # the down projection's shape
+])
+def test_grouped_matmul_finalize_routing(dev, M, Kd, N, E, idx_dtype, extras, gl_type):
+    """Down GEMM + logit-weighted scatter-add (+ shared rows): every term is exact fp32 of exact int32 accumulators, the
+    only freedom is the order in which the K rows of a token are added, hence the fp32-ulp-sized tolerance."""
+    g = torch.Generator().manual_seed(M + N)
+    K = 4
+    T = M // K
+    x = torch.randint(-127, 128, (M, Kd), generator=g, dtype=torch.int8)
+    w = torch.randint(-127, 128, (E, Kd, N), generator=g, dtype=torch.int8)
+    cuts = torch.sort(torch.randint(0, M - 7, (E - 1,), generator=g)).values      # the last 7 rows belong to no group
+    ends = torch.cat([cuts, torch.tensor([M - 7])])
+    counts = torch.diff(ends, prepend=torch.tensor([0]))
+    group_list = (ends if gl_type == 0 else counts).to(torch.int64)
+    scale = torch.rand(E, N, generator=g) * 1e-3 + 1e-4
+    pts = torch.rand(M, generator=g) * 1e-2 + 1e-3
+    row_index = (torch.randperm(M, generator=g) % T).to(idx_dtype)               # K rows per token
+    kw = dict(scale=scale, pertoken_scale=pts, row_index=row_index, group_list_type=gl_type)
+    out_bs = T
+    if extras:
+        out_bs = T + 5
+        kw.update(bias=torch.randn(E, N, generator=g).to(torch.bfloat16), logit=torch.rand(M, generator=g),
+                  shared_input=torch.randn(T // 2, N, generator=g).to(torch.bfloat16), shared_input_weight=0.75,
+                  shared_input_offset=3)
+        row_index[5] = -1            # out-of-range rows add nothing
+        row_index[6] = out_bs
+    ref = O.grouped_matmul_finalize_routing(x, w, group_list, output_bs=out_bs, **kw)
+    d = lambda v: v.to(dev) if isinstance(v, torch.Tensor) else v
+    got = npu.npu_grouped_matmul_finalize_routing(x.to(dev), w.to(dev), group_list.to(dev), output_bs=out_bs,
+                                                  **{k: d(v) for k, v in kw.items()})
+    _gmm_ok(dev)
+    assert got.dtype == torch.float32 and got.shape == ref.shape
+    torch.testing.assert_close(got.cpu(), ref, rtol=2e-6, atol=2e-6 * float(ref.abs().max()))
+    if extras:     # rows no token points at and no shared row covers stay exactly zero
+        untouched = torch.ones(out_bs, dtype=torch.bool)
+        untouched[row_index[(row_index >= 0) & (row_index < out_bs)].long()] = False
+        untouched[3:3 + T // 2] = False
+        assert not got.cpu()[untouched].any()
 
 
 def test_layer_from_gating_to_finalize_with_neighbour_ops(dev):

@@ -208,3 +208,33 @@ def test_gating_top_k_group_limited_known_answer():
     b = torch.tensor([0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 5.0, 0.0])
     y3, idx3, _ = O.moe_gating_top_k(x, 1, b, norm_type=1, routed_scaling_factor=2.0)
     assert idx3.tolist() == [[6]] and torch.allclose(y3, torch.tensor([[2.0]]), atol=1e-5)
+
+
+def test_grouped_matmul_finalize_routing_known_answer_and_composition():
+    """A hand-checkable case, then: with logit = routing weight and row_index = token, the op equals the fp32 down GEMM
+    followed by the weighted sum over a token's rows."""
+    x = torch.tensor([[1, 2], [3, 4], [5, 6], [7, 8]], dtype=torch.int8)
+    w = torch.tensor([[[1, 0, 2, 0], [0, 1, 0, 2]], [[-1, 0, 1, 0], [0, -1, 0, 1]]], dtype=torch.int8)      # [2, 2, 4]
+    y = O.grouped_matmul_finalize_routing(x, w, torch.tensor([1, 2]), scale=torch.full((2, 4), 0.5),
+                                          pertoken_scale=torch.tensor([1.0, 2.0, 1.0, 9.0]), logit=torch.tensor([2.0, 1.0, 1.0, 1.0]),
+                                          row_index=torch.tensor([1, 0, 0, 1]), shared_input=torch.ones(1, 4, dtype=torch.bfloat16),
+                                          shared_input_weight=3.0, shared_input_offset=2, output_bs=3)
+    # row 0 -> expert 0 -> out 1: 2 * 0.5 * [1, 2, 2, 4]; rows 1, 2 -> expert 1 -> out 0; row 3 is in no group
+    assert torch.equal(y[1], torch.tensor([1.0, 2.0, 2.0, 4.0]))
+    assert torch.equal(y[0], torch.tensor([-3.0, -4.0, 3.0, 4.0]) + 0.5 * torch.tensor([-5.0, -6.0, 5.0, 6.0]))
+    assert torch.equal(y[2], torch.full((4,), 3.0))
+    g = torch.Generator().manual_seed(2)
+    M, Kd, N, E, K = 48, 32, 16, 3, 4
+    xq = torch.randint(-127, 128, (M, Kd), generator=g, dtype=torch.int8)
+    wq = torch.randint(-127, 128, (E, Kd, N), generator=g, dtype=torch.int8)
+    counts = torch.tensor([20, 0, 28])
+    sc, pts, lg = torch.rand(E, N, generator=g), torch.rand(M, generator=g), torch.rand(M, generator=g)
+    tok = torch.randperm(M, generator=g) % (M // K)
+    got = O.grouped_matmul_finalize_routing(xq, wq, counts, scale=sc, pertoken_scale=pts, logit=lg, row_index=tok, output_bs=M // K)
+    starts, cnt = O.group_bounds(counts, 1)
+    full = torch.zeros(M, N)
+    for e in range(E):
+        s, c = int(starts[e]), int(cnt[e])
+        full[s:s + c] = (O.int8_matmul(xq[s:s + c], wq[e]).float() * pts[s:s + c, None]) * sc[e][None]
+    want = torch.zeros(M // K, N).index_add_(0, tok, full * lg[:, None])
+    torch.testing.assert_close(got, want, rtol=1e-6, atol=1e-6)

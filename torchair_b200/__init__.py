@@ -15,10 +15,11 @@ from .configs import CompilerConfig
 from .backend import get_compiler, get_npu_backend, register_fx_node_ge_converter, declare_supported, logger
 from .ep import register_ep_group, get_ep_group
 from . import ops
+from . import scope
 from .ops import clear_weight_cache, gmm_status
 
 __all__ = ["get_npu_backend", "get_compiler", "CompilerConfig", "register_fx_node_ge_converter", "logger",
-           "register_ep_group", "install_as_torchair", "clear_weight_cache", "gmm_status"]
+           "register_ep_group", "install_as_torchair", "clear_weight_cache", "gmm_status", "scope"]
 
 
 def install_as_torchair() -> None:
@@ -26,3 +27,4 @@ def install_as_torchair() -> None:
     sys.modules.setdefault("torchair", sys.modules[__name__])
     sys.modules.setdefault("torchair.configs", sys.modules[__name__ + ".configs"])
     sys.modules.setdefault("torchair.configs.compiler_config", sys.modules[__name__ + ".configs"])
+    sys.modules.setdefault("torchair.scope", sys.modules[__name__ + ".scope"])

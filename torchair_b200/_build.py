@@ -9,7 +9,7 @@ from concurrent.futures import ThreadPoolExecutor
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libtorchair_b200.so")
-SOURCES = ["api.cu", "quant.cu", "routing.cu", "gmm_i8.cu", "ep_peer.cu"]
+SOURCES = ["api.cu", "quant.cu", "routing.cu", "gmm_i8.cu", "gmm_finalize.cu", "ep_peer.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"]
 

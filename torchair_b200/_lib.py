@@ -44,6 +44,9 @@ SIGNATURES = {
     "tab_grouped_matmul_w8a8": [_P, _P, _P, _P, _P, _I, _L, _L, _L, _L, _I, _P, _P],
     "tab_grouped_matmul_swiglu_quant_workspace_bytes": [_L, _L, POINTER(c_size_t)],
     "tab_grouped_matmul_swiglu_quant": [_P, _P, _P, _P, _P, _I, _L, _L, _L, _L, _I, _P, _P, _P, c_size_t, _P],
+    "tab_grouped_matmul_finalize_routing_workspace_bytes": [_L, _L, POINTER(c_size_t)],
+    "tab_grouped_matmul_finalize_routing": [_P, _P, _P, _P, _P, _P, _I, _L, _L, _L, _L, _P, _L, c_float, _L, _P, _P, _I, _L, _P, _P,
+                                            c_size_t, _P],
     "tab_gmm_status": [POINTER(c_int), _P],
 }
 _RESTYPE = {"tab_last_error": c_char_p}

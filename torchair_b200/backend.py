@@ -135,7 +135,10 @@ class _CompiledFxGraph:
     """Callable returned to AOT-autograd: eager FX replay, or CUDA-graph capture/replay keyed by input shapes."""
 
     def __init__(self, gm: torch.fx.GraphModule, config: CompilerConfig):
+        from . import scope
         self.gm = gm
+        # graphs with stream scopes are replayed node by node on CUDA streams; the others run their generated code
+        self.run = scope.StreamedReplay(gm) if scope.uses_scopes(gm) else gm
         self.capture = config.mode.raw in ("reduce-overhead", "npugraph_ex") and not config.debug.run_eagerly.raw \
             and not _has_multi_rank_exchange(gm)
         self.clone_input = bool(config.debug.aclgraph.clone_input.raw)
@@ -147,7 +150,7 @@ class _CompiledFxGraph:
         with torch.profiler.record_function("npu_fx_compiler inference"):
             if not self.capture or self.eager_forever or not all(isinstance(a, torch.Tensor) and a.is_cuda for a in args):
                 counters["eager_runs"] += 1
-                return self.gm(*args)
+                return self.run(*args)
             key = tuple((tuple(a.shape), a.dtype, a.device.index) for a in args)
             entry = self.graphs.get(key)
             if entry is None:
@@ -156,7 +159,7 @@ class _CompiledFxGraph:
                     # (python/torchair/_acl_concrete_graph/acl_graph.py:1001-1014)
                     logger.warning("capture count exceeded static_capture_size_limit=%d; running eagerly", self.limit)
                     self.eager_forever = True
-                    return self.gm(*args)
+                    return self.run(*args)
                 entry = self._capture(key, args)
             graph, static_in, static_out = entry
             for dst, src in zip(static_in, args):
@@ -172,11 +175,11 @@ class _CompiledFxGraph:
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):      # warm-up off the capture: fills the packed-weight cache, loads kernels
             for _ in range(2):
-                self.gm(*static_in)
+                self.run(*static_in)
         torch.cuda.current_stream().wait_stream(side)
         graph = torch.cuda.CUDAGraph()
         with torch.profiler.record_function("npu_fx_compiler capture"), torch.cuda.graph(graph):
-            static_out = self.gm(*static_in)
+            static_out = self.run(*static_in)
         counters["captures"] += 1
         self.graphs[key] = (graph, static_in, static_out)
         return self.graphs[key]

@@ -98,40 +98,6 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const T* __restrict__ x, in
   }
 }
 
-// Row ends (inclusive prefix of the per-group counts) in shared memory, computed once per CTA.
-constexpr int kMaxDsqGroups = 4096;
-template <int THREADS>
-__device__ void group_ends_to_smem(const int64_t* __restrict__ counts, int num_groups, int* s_end) {
-  if (threadIdx.x < 32) {   // one warp scans 32 groups per step
-    const int lane = threadIdx.x;
-    long long run = 0;
-    for (int g0 = 0; g0 < num_groups; g0 += 32) {
-      const int g = g0 + lane;
-      long long c = g < num_groups ? counts[g] : 0;
-      if (c < 0) c = 0;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const long long t = __shfl_up_sync(0xffffffffu, c, o);
-        if (lane >= o) c += t;
-      }
-      if (g < num_groups) s_end[g] = static_cast<int>(min(run + c, 2147483647LL));
-      run += __shfl_sync(0xffffffffu, c, 31);
-    }
-  }
-  __syncthreads();
-}
-
-// First group whose end is > row, or -1 when the row lies past every group.
-__device__ __forceinline__ int group_of_row(const int* s_end, int num_groups, int64_t row) {
-  if (num_groups == 0 || row >= s_end[num_groups - 1]) return -1;
-  int lo = 0, hi = num_groups - 1;   // invariant: s_end[hi] > row
-  while (lo < hi) {
-    const int mid = (lo + hi) >> 1;
-    if (s_end[mid] > row) hi = mid; else lo = mid + 1;
-  }
-  return lo;
-}
-
 // x int32 [rows, 2*half] -> y int8 [rows, half], scale [rows]; one CTA per row.
 constexpr int kDsqChunks = 4;
 template <int THREADS>
@@ -141,7 +107,7 @@ __global__ void __launch_bounds__(THREADS) dequant_swiglu_quant_kernel(
     int8_t* __restrict__ y, float* __restrict__ scale) {
   __shared__ float red[THREADS / 32];
   extern __shared__ int s_end[];
-  if (group_index != nullptr) group_ends_to_smem<THREADS>(group_index, num_groups, s_end);
+  if (group_index != nullptr) group_ends_to_smem(group_index, /*cumulative=*/0, num_groups, s_end);
   const int nchunk = half >> 3;
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const int g = group_index != nullptr ? group_of_row(s_end, num_groups, row) : 0;   // uniform over the CTA

@@ -274,4 +274,44 @@ __device__ __forceinline__ void copy_row16(uint4* __restrict__ dst, const uint4*
   }
 }
 
+// ---- rows -> group lookup for row kernels that follow a grouped GEMM ----
+// Row ends of the groups in shared memory, computed once per CTA by its first warp (followed by a CTA barrier):
+// the inclusive prefix of per-group counts, or the list itself when it already holds cumulative ends.
+constexpr int kMaxDsqGroups = 4096;
+__device__ __forceinline__ void group_ends_to_smem(const int64_t* __restrict__ list, int cumulative, int num_groups,
+                                                   int* s_end) {
+  if (threadIdx.x < 32) {   // one warp scans 32 groups per step
+    const int lane = threadIdx.x;
+    long long run = 0;
+    for (int g0 = 0; g0 < num_groups; g0 += 32) {
+      const int g = g0 + lane;
+      long long c = g < num_groups ? list[g] : 0;
+      if (c < 0) c = 0;
+      if (cumulative) {
+        if (g < num_groups) s_end[g] = static_cast<int>(min(c, 2147483647LL));
+        continue;
+      }
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const long long t = __shfl_up_sync(0xffffffffu, c, o);
+        if (lane >= o) c += t;
+      }
+      if (g < num_groups) s_end[g] = static_cast<int>(min(run + c, 2147483647LL));
+      run += __shfl_sync(0xffffffffu, c, 31);
+    }
+  }
+  __syncthreads();
+}
+
+// First group whose end is > row, or -1 when the row lies past every group.
+__device__ __forceinline__ int group_of_row(const int* s_end, int num_groups, int64_t row) {
+  if (num_groups == 0 || row >= s_end[num_groups - 1]) return -1;
+  int lo = 0, hi = num_groups - 1;   // invariant: s_end[hi] > row
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (s_end[mid] > row) hi = mid; else lo = mid + 1;
+  }
+  return lo;
+}
+
 }  // namespace tab

@@ -52,6 +52,11 @@ _npu.define("npu_grouped_matmul_swiglu_quant_v2(Tensor x, Tensor[] weight, Tenso
             "int? dequant_mode=0, int? dequant_dtype=0, int? quant_mode=0, int? quant_dtype=1, int? group_list_type=0, "
             "int[]? tuning_config=None, int? x_dtype=None, int? weight_dtype=None, int? weight_scale_dtype=None, "
             "int? x_scale_dtype=None) -> (Tensor, Tensor)")
+_npu.define("npu_grouped_matmul_finalize_routing(Tensor x, Tensor w, Tensor group_list, *, Tensor? scale=None, Tensor? bias=None, "
+            "Tensor? offset=None, Tensor? pertoken_scale=None, Tensor? shared_input=None, Tensor? logit=None, "
+            "Tensor? row_index=None, ScalarType? dtype=None, float? shared_input_weight=1.0, int? shared_input_offset=0, "
+            "int? output_bs=0, int? group_list_type=1, int[]? tuning_config=None, int? x_dtype=None, int? w_dtype=None, "
+            "int? scale_dtype=None, int? pertoken_scale_dtype=None) -> Tensor")
 _npu.define("npu_moe_compute_expert_tokens(Tensor sorted_experts, int num_experts) -> Tensor")
 _npu.define("npu_moe_gating_top_k_softmax(Tensor x, Tensor? finished=None, int k=1) -> (Tensor, Tensor, Tensor)")
 _npu.define("npu_moe_gating_top_k(Tensor x, int k, *, Tensor? bias=None, int k_group=1, int group_count=1, int group_select_mode=0, "
@@ -426,6 +431,66 @@ def fused_gate_up(x, w, w_scale, x_scale, group_list, group_list_type, activate_
     return yq, ys
 
 
+# --------------------------------------------------------------------------------------------------
+# npu_grouped_matmul_finalize_routing (converter grouped_matmul_finalize_routing.py:57-133): down GEMM + weighted
+# scatter-add into fp32 token rows, optionally on top of the shared experts' rows
+# --------------------------------------------------------------------------------------------------
+def _gmm_fr_meta(x, w, group_list, *, scale=None, bias=None, offset=None, pertoken_scale=None, shared_input=None, logit=None,
+                 row_index=None, dtype=None, shared_input_weight=1.0, shared_input_offset=0, output_bs=0, group_list_type=1,
+                 tuning_config=None, x_dtype=None, w_dtype=None, scale_dtype=None, pertoken_scale_dtype=None):
+    op = "npu_grouped_matmul_finalize_routing"
+    if x.dim() != 2 or w.dim() != 3 or w.shape[1] != x.shape[1]:
+        raise RuntimeError(f"{op}: x [M, K] and w [E, K, N] expected, got {tuple(x.shape)} and {tuple(w.shape)}")
+    if dtype is not None and dtype != torch.float32:
+        raise RuntimeError(f"Not supported output dtype is {dtype}")      # the converter's own message
+    rows = int(output_bs or 0) or x.shape[0]
+    return torch.empty((rows, w.shape[2]), dtype=torch.float32, device=x.device)
+
+
+def _gmm_fr_cuda(x, w, group_list, *, scale=None, bias=None, offset=None, pertoken_scale=None, shared_input=None, logit=None,
+                 row_index=None, dtype=None, shared_input_weight=1.0, shared_input_offset=0, output_bs=0, group_list_type=1,
+                 tuning_config=None, x_dtype=None, w_dtype=None, scale_dtype=None, pertoken_scale_dtype=None):
+    op = "npu_grouped_matmul_finalize_routing"
+    y = _gmm_fr_meta(x, w, group_list, dtype=dtype, output_bs=output_bs)
+    _only_none(op, offset=offset, x_dtype=x_dtype, w_dtype=w_dtype, scale_dtype=scale_dtype, pertoken_scale_dtype=pertoken_scale_dtype)
+    if x.dtype != torch.int8 or w.dtype != torch.int8:
+        raise NotImplementedError(f"{op}: only int8 x int8 (W8A8) is on the path")
+    M, Kd = x.shape
+    E, _, N = w.shape
+    if group_list.numel() != E:
+        raise RuntimeError(f"{op}: group_list must have one entry per expert ({E})")
+    if row_index is None or row_index.numel() != M or row_index.dtype not in (torch.int32, torch.int64):
+        raise RuntimeError(f"{op}: row_index must be int32 or int64 [M]")
+    if scale is not None:
+        if scale.numel() != E * N:
+            raise RuntimeError(f"{op}: scale must be [E, N]")
+        scale = scale.to(torch.float32).contiguous()
+    if bias is not None:
+        if bias.numel() != E * N:
+            raise RuntimeError(f"{op}: bias must be [E, N]")
+        bias = bias.to(torch.bfloat16).contiguous()
+    for name, t in (("pertoken_scale", pertoken_scale), ("logit", logit)):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != M):
+            raise RuntimeError(f"{op}: {name} must be fp32 [M]")
+    shared_rows = 0
+    if shared_input is not None:
+        if shared_input.dim() != 2 or shared_input.shape[1] != N or shared_input.dtype != torch.bfloat16:
+            raise RuntimeError(f"{op}: shared_input must be bfloat16 [rows, N]")
+        shared_rows = shared_input.shape[0]
+        shared_input = shared_input.contiguous()
+    group_list = group_list.to(torch.int64).contiguous()
+    x, row_index = x.contiguous(), row_index.contiguous()
+    pertoken_scale = None if pertoken_scale is None else pertoken_scale.contiguous()
+    logit = None if logit is None else logit.contiguous()
+    wp = packed_weight(w)
+    ws = _workspace(_lib.workspace_bytes("tab_grouped_matmul_finalize_routing_workspace_bytes", M, N), x.device)
+    _lib.call("tab_grouped_matmul_finalize_routing", _ptr(x), _ptr(wp), _ptr(scale), _ptr(bias), _ptr(pertoken_scale),
+              _ptr(group_list), int(1 if group_list_type is None else group_list_type), M, Kd, N, E, _ptr(shared_input), shared_rows,
+              float(1.0 if shared_input_weight is None else shared_input_weight), int(shared_input_offset or 0), _ptr(logit),
+              _ptr(row_index), 3 if row_index.dtype == torch.int32 else 4, y.shape[0], _ptr(y), _ptr(ws), ws.numel(), _stream(x))
+    return y
+
+
 def gmm_status(device=None) -> int:
     """Synchronises the current stream and returns the GEMM kernels' device status word (0 = fine)."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
@@ -692,6 +757,7 @@ for _name, _meta, _cuda in (
         ("npu_grouped_matmul", _gmm_meta, _gmm_cuda),
         ("npu_grouped_matmul.List", _gmm_meta, _gmm_cuda),
         ("npu_grouped_matmul_swiglu_quant_v2", _gmm_sq_meta, _gmm_sq_cuda),
+        ("npu_grouped_matmul_finalize_routing", _gmm_fr_meta, _gmm_fr_cuda),
         ("npu_moe_compute_expert_tokens", _cet_meta, _cet_cuda),
         ("npu_moe_gating_top_k_softmax", _gating_meta, _gating_cuda),
         ("npu_moe_finalize_routing", _finalize_meta, _finalize_cuda),
@@ -712,4 +778,4 @@ OP_NAMES = ["npu_moe_init_routing", "npu_dynamic_quant", "npu_dynamic_quant_asym
             "npu_dequant_swiglu_quant", "npu_grouped_matmul", "npu_grouped_matmul_swiglu_quant_v2",
             "npu_moe_distribute_dispatch", "npu_moe_distribute_combine", "npu_moe_compute_expert_tokens",
             "npu_moe_gating_top_k_softmax", "npu_moe_finalize_routing", "npu_moe_init_routing_v2", "npu_moe_gating_top_k",
-            "npu_moe_distribute_dispatch_v2", "npu_moe_distribute_combine_v2"]
+            "npu_moe_distribute_dispatch_v2", "npu_moe_distribute_combine_v2", "npu_grouped_matmul_finalize_routing"]
