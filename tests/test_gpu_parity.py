@@ -609,6 +609,37 @@ def test_fused_gate_up_prefill_orientation_equals_unfused(dev, M, Kd, I, E):
     assert torch.equal(ref32[:covered], h32.cpu()[:covered])
 
 
+@pytest.mark.parametrize("Kd,I", [(512, 256), (384, 200)])
+def test_prefill_narrow_tail_tiles_are_bit_exact(dev, Kd, I):
+    """Token tiles with at most 64 valid rows are computed with swapped operands (channels on the lanes, tokens on the
+    columns).  Experts sized around every boundary of that path (1, 15..17, 47..49, 63..65 rows, the same as tails behind
+    one and two full tiles, and an empty expert) must give the results of the wide tiles: raw int32, scaled bf16, and
+    the fused SwiGLU + requantise epilogue."""
+    counts = [1, 15, 16, 17, 47, 48, 49, 63, 64, 65, 0, 128 + 1, 128 + 33, 128 + 64, 128 + 65, 256 + 9, 256 + 127, 300]
+    E = len(counts)
+    M = sum(counts) + 11                       # 11 rows past the last group
+    assert M > 64 * E                          # the prefill orientation is taken by itself
+    g = torch.Generator().manual_seed(Kd + I)
+    x = torch.randint(-127, 128, (M, Kd), generator=g, dtype=torch.int8)
+    w = torch.randint(-127, 128, (E, Kd, 2 * I), generator=g, dtype=torch.int8)
+    ws = torch.rand(E, 2 * I, generator=g) * 9e-3 + 1e-3
+    xs = torch.rand(M, generator=g) * 1e-2
+    cnt = torch.tensor(counts, dtype=torch.int64)
+    covered = sum(counts)
+    xd, wd, wsd, xsd, cd = x.to(dev), w.to(dev), ws.to(dev), xs.to(dev), cnt.to(dev)
+    h32 = npu.npu_grouped_matmul([xd], [wd], group_list=cd, split_item=2, group_type=0, group_list_type=1, output_dtype=3)[0]
+    ref32 = O.grouped_matmul_w8a8(x, w, None, None, cnt, 1, 3)
+    assert torch.equal(ref32[:covered], h32.cpu()[:covered])
+    y16 = npu.npu_grouped_matmul([xd], [wd], scale=[wsd], per_token_scale=[xsd], group_list=cd, split_item=2, group_type=0,
+                                 group_list_type=1, output_dtype=15)[0]
+    ref16 = O.grouped_matmul_w8a8(x, w, ws, xs, cnt, 1, 15)
+    assert torch.equal(ref16[:covered], y16.cpu()[:covered])
+    hq, hs = npu.npu_grouped_matmul_swiglu_quant_v2(xd, [wd], [wsd], xsd, cd, group_list_type=1)
+    q2, s2 = npu.npu_dequant_swiglu_quant(h32, weight_scale=wsd, activation_scale=xsd, group_index=cd, activate_left=True, quant_mode=1)
+    _gmm_ok(dev)
+    assert torch.equal(hq[:covered], q2[:covered]) and torch.equal(hs[:covered], s2[:covered])
+
+
 def test_peer_flag_wait_runs_out_and_reports_instead_of_hanging(dev):
     """Failure detection on the GPU without faulting it: a flag that nobody sets makes the bounded wait of the
     peer-memory exchange give up (about 2 s), write its code into the status word and let the stream continue."""

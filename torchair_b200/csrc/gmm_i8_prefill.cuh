@@ -9,6 +9,13 @@
 //   - for the gate_up GEMM the 256 columns are [128 gate channels | the matching 128 up channels] (two TMA boxes
 //     into one operand tile), so gate and up of a channel meet in the same thread.
 // Roles, barriers, bounded waits and the work-item list are those of the decode-orientation kernel.
+//
+// Narrow tiles: an expert's last token tile often holds only a few rows (256 +- 16 rows per expert leave a third tile
+// of a dozen rows), and as a 128-row operand it would cost a full tile of MMA work.  A tile with at most kPfNarrowMax
+// valid rows is therefore computed with the operands swapped, out of the very same shared-memory stage: each
+// 128-channel half of the weight tile is the 128-row operand, the token tile the N operand with N = rows rounded up
+// to 16, into two accumulators (columns 0.. and 128.. of the buffer; lane = channel, column = token).  MMA work
+// shrinks in proportion to the rows; the epilogue for such tiles runs per channel lane and is masked per token.
 #pragma once
 
 #include "gmm_common.cuh"
@@ -30,10 +37,75 @@ constexpr int kPfOutStageBytes = 8 * 32 * kPfOutPitch;   // per epilogue warp: 3
 constexpr int kPfSmemBytes = 1024 + kPfStages * kPfStageBytes + kPfCtrlBytes + kPfScaleBytes + kPfTableBytes + kPfOutStageBytes;
 static_assert(kPfSmemBytes <= kSmemLimit, "prefill GEMM shared memory");
 
+constexpr int kPfNarrowMax = 64;                     // token tiles with at most this many valid rows swap the operands
 constexpr int kPfEpiWarps = 8;                       // two warps per TMEM lane quarter, each takes half of the columns
 constexpr int kPfThreads = 64 + kPfEpiWarps * 32;    // producer warp + MMA warp + epilogue warps
 
 __device__ __forceinline__ void epilogue_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+// Epilogue of a narrow tile (operands swapped): this thread's TMEM lane is channel `c_l` of the tile's 128-channel
+// halves, columns are tokens.  Plain GEMM: accumulator 0 holds channels [0,128) of the tile, accumulator 1 (128 columns
+// further) channels [128,256); the two warps of a lane quarter take one accumulator each.  Fused gate_up: accumulator 0
+// holds gate, accumulator 1 the matching up channels; the two warps alternate over the 16-token column chunks.  The
+// arithmetic per element is that of the wide tiles, so results do not depend on which form a tile took.
+template <bool FUSED>
+__device__ __forceinline__ void pf_narrow_epilogue(const GmmParams& p, const WorkItem& it, const float* ws, uint32_t t0,
+                                                   int row0, int nvalid, int c_l, int lane, int chalf) {
+  const int nv16 = (nvalid + 15) & ~15;
+  if constexpr (FUSED) {
+    const int ch = it.ct * 128 + c_l;                 // channel inside the half
+    const bool cvalid = ch < p.half;
+    const float wg = ws[c_l], wu = ws[128 + c_l];
+#pragma unroll 1
+    for (int c = chalf * 16; c < nv16; c += 32) {
+      int g[16], u[16];
+      __syncwarp();
+      ptx::tmem_ld16(t0 + c, g);
+      ptx::tmem_ld16(t0 + 128 + c, u);
+      ptx::tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const bool tvalid = c + j < nvalid;           // uniform over the warp
+        const int row = row0 + c + j;
+        const float ts = (tvalid && p.tok_scale) ? p.tok_scale[row] : 1.f;
+        const float gv = __fmul_rn(__fmul_rn(__int2float_rn(g[j]), ts), wg);
+        const float uv = __fmul_rn(__fmul_rn(__int2float_rn(u[j]), ts), wu);
+        const float h = p.activate_left ? silu_mul(gv, uv) : silu_mul(uv, gv);
+        if (tvalid) {
+          if (cvalid) __stcs(p.h_out + static_cast<int64_t>(row) * p.half + ch, h);
+          const float m = warp_max(cvalid ? fabsf(h) : 0.f);
+          if (lane == 0) atomicMax(p.amax + row, __float_as_uint(m));
+        }
+      }
+    }
+  } else {
+    const int ch = it.ct * 256 + chalf * 128 + c_l;
+    const bool cvalid = ch < p.N;
+    const float wv = ws[chalf * 128 + c_l];
+#pragma unroll 1
+    for (int c = 0; c < nv16; c += 16) {
+      int a[16];
+      __syncwarp();
+      ptx::tmem_ld16(t0 + chalf * 128 + c, a);
+      ptx::tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int row = row0 + c + j;
+        if (c + j < nvalid && cvalid) {
+          const int64_t o = static_cast<int64_t>(row) * p.N + ch;
+          if (p.out_dtype == TAB_I32) {
+            static_cast<int*>(p.out)[o] = a[j];
+          } else {
+            const float ts = p.tok_scale ? p.tok_scale[row] : 1.f;
+            const float f = __fmul_rn(__fmul_rn(__int2float_rn(a[j]), ts), wv);
+            if (p.out_dtype == TAB_BF16) static_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(f);
+            else static_cast<__half*>(p.out)[o] = __float2half_rn(f);
+          }
+        }
+      }
+    }
+  }
+}
 
 template <bool FUSED>
 __global__ void __launch_bounds__(kPfThreads, 1)
@@ -126,6 +198,10 @@ gmm_i8_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
       uint32_t phase = 0, tphase = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < total_items && ok; w += gridDim.x) {
+        const WorkItem it = decode_item(w, p.chan_tiles, E, s_pref);
+        const int nvalid = min(kPfTokens, s_start[it.e + 1] - (s_start[it.e] + it.tt * kPfTokens));
+        const bool narrow = nvalid <= kPfNarrowMax;
+        const uint32_t idesc_n = ptx::idesc_i8(128, (nvalid + 15) & ~15);
         if (!bounded_wait(bar_tempty(buf), tphase ^ 1u, s_abort, 12)) { ok = false; break; }
         ptx::tc_fence_after();
         const uint32_t d = tmem_base + buf * kPfCols;
@@ -135,8 +211,17 @@ gmm_i8_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
           const uint32_t st = tiles_addr + stage * kPfStageBytes;
           const uint64_t a = ptx::smem_desc_k128(st);
           const uint64_t b = ptx::smem_desc_k128(st + kPfATile);
+          if (!narrow) {
 #pragma unroll
-          for (int k = 0; k < kBlockK / 32; ++k) ptx::mma_i8(d, a + 2 * k, b + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < kBlockK / 32; ++k) ptx::mma_i8(d, a + 2 * k, b + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          } else {
+            const uint64_t b1 = ptx::smem_desc_k128(st + kPfATile + kWTileBytes);   // second 128 channels of the weight tile
+#pragma unroll
+            for (int k = 0; k < kBlockK / 32; ++k) {
+              ptx::mma_i8(d, b + 2 * k, a + 2 * k, idesc_n, (kb | k) != 0 ? 1u : 0u);
+              ptx::mma_i8(d + 128, b1 + 2 * k, a + 2 * k, idesc_n, (kb | k) != 0 ? 1u : 0u);
+            }
+          }
           ptx::mma_commit(bar_empty(stage));
           if (++stage == kPfStages) { stage = 0; phase ^= 1u; }
         }
@@ -178,7 +263,11 @@ gmm_i8_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
       const bool rvalid = row < s_start[it.e + 1];
       const float ts = (rvalid && p.tok_scale) ? p.tok_scale[row] : 1.f;
       const uint32_t t0 = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kPfCols;
-      if constexpr (FUSED) {
+      const int tile_row0 = s_start[it.e] + it.tt * kPfTokens;
+      const int nvalid = min(kPfTokens, s_start[it.e + 1] - tile_row0);
+      if (nvalid <= kPfNarrowMax) {
+        pf_narrow_epilogue<FUSED>(p, it, ws, t0, tile_row0, nvalid, r_local, lane, chalf);
+      } else if constexpr (FUSED) {
         const int cg0 = it.ct * 128;
         float amax = 0.f;
         float* hrow = p.h_out + static_cast<int64_t>(row) * p.half + cg0;
