@@ -170,6 +170,9 @@ TAB_API int tab_moe_exchange_rows(const void* src, const float* src_scales, cons
  *   tab_ep_return_rows expert side of combine: outputs go back to slot [my_rank][send offset] of the source
  *                      rank's `ret` buffer; the source then runs tab_moe_combine on its ret buffer with
  *                      expand_idx_slot.
+ *   tab_ep_return_plan the addresses tab_ep_return_rows would copy to, one per expert-output row (0 past the
+ *                      total), as the row table of tab_grouped_matmul_w8a8_scatter: the down GEMM then stores
+ *                      its rows into the source ranks' `ret` buffers itself and no copy kernel runs.
  * ------------------------------------------------------------------------------------------------- */
 TAB_API int tab_ep_signal(void* const* peer_flags, void* counter, int64_t R, tab_stream_t stream);
 TAB_API int tab_ep_wait(const void* flags, void* counter, int64_t R, int pre_increment, int* status, int code,
@@ -182,6 +185,10 @@ TAB_API int tab_ep_unpack_rows(const void* recv, const int32_t* plan, int64_t R,
                        int64_t dst_rows, int zero_fill, void* dst, float* dst_scales, tab_stream_t stream);
 TAB_API int tab_ep_return_rows(const void* y, const int32_t* plan, int64_t R, int64_t E_l, int64_t slot_rows,
                        int64_t row_bytes, int64_t max_rows, int64_t my_rank, void* const* peer_ret,
+                       tab_stream_t stream);
+
+TAB_API int tab_ep_return_plan(const int32_t* plan, int64_t R, int64_t E_l, int64_t slot_rows, int64_t row_bytes,
+                       int64_t max_rows, int64_t my_rank, void* const* peer_ret, uint64_t* row_dst,
                        tab_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------
@@ -255,6 +262,12 @@ TAB_API int tab_moe_init_routing_v2(const void* x, int x_dtype, const int32_t* e
  *   per_token_scale fp32 [M] (either may be NULL = 1).  Rows outside every group are left untouched.
  *   Requires Kd % 16 == 0.
  *
+ * tab_grouped_matmul_w8a8_scatter: the same GEMM with 16-bit output (out_dtype 15 or 5) whose row m is stored at the
+ *   address row_dst[m] (device array of M addresses, 16-byte aligned rows of N elements) instead of y + m*N.  The
+ *   addresses may lie in peer-mapped memory of another GPU: with tab_ep_return_plan this is the down projection of
+ *   npu_grouped_matmul fused with the row return of npu_moe_distribute_combine (moe_distribute_combine.py:4-60),
+ *   each tile leaving over NVLink as its epilogue finishes.  Rows outside every group are not stored.  N % 8 == 0.
+ *
  * tab_grouped_matmul_swiglu_quant: gate_up GEMM with the DequantSwigluQuant epilogue fused
  *   (grouped_matmul.py:210-365 followed by npu_dequant_swiglu_quant.py:5-64; the reference's own fused
  *   form is converter grouped_matmul_swiglu_quant_v2.py:86-166).  packed weight [E, 2*I, Kd];
@@ -280,6 +293,10 @@ TAB_API int tab_grouped_matmul_w8a8(const int8_t* x, const int8_t* packed_weight
                             const float* per_token_scale, const int64_t* group_list, int group_list_type,
                             int64_t M, int64_t Kd, int64_t N, int64_t E, int out_dtype, void* y,
                             tab_stream_t stream);
+TAB_API int tab_grouped_matmul_w8a8_scatter(const int8_t* x, const int8_t* packed_weight, const float* scale,
+                                    const float* per_token_scale, const int64_t* group_list, int group_list_type,
+                                    int64_t M, int64_t Kd, int64_t N, int64_t E, int out_dtype, const uint64_t* row_dst,
+                                    tab_stream_t stream);
 TAB_API int tab_grouped_matmul_swiglu_quant_workspace_bytes(int64_t M, int64_t I, size_t* bytes);
 TAB_API int tab_grouped_matmul_swiglu_quant(const int8_t* x, const int8_t* packed_weight, const float* weight_scale,
                                     const float* x_scale, const int64_t* group_list, int group_list_type,

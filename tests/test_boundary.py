@@ -240,3 +240,36 @@ def test_fx_pass_fuses_int32_matmul_with_dequant_swiglu_quant():
                                             activate_left=True, quant_mode=1)
         return q, s, h32
     assert fuse_gate_up(make_fx(other_user)(*args)) == 0
+
+
+def test_fx_pass_fuses_down_matmul_with_combine_only_over_peer_memory():
+    from torch.fx.experimental.proxy_tensor import make_fx
+    from torchair_b200.backend import fuse_down_combine
+    import torchair_b200
+    npu = torch.ops.npu
+    torchair_b200.register_ep_group("fx_peer", object(), transport="peer")
+    torchair_b200.register_ep_group("fx_nccl", object(), transport="nccl")
+
+    def make(group, world, keep_rows=False):
+        def fn(hq, w2, s2, hs, counts, ids, expand_idx, ep_recv, wt):
+            y = npu.npu_grouped_matmul([hq], [w2], scale=[s2], per_token_scale=[hs], group_list=counts, split_item=2, group_type=0,
+                                       group_list_type=1, output_dtype=15)[0]
+            out = npu.npu_moe_distribute_combine(y, ids, expand_idx, ep_recv, wt, group, world, 0, 8)
+            return (out, y) if keep_rows else out
+        return fn
+
+    m = "meta"
+    T, K, H, I, E_l, R = 8, 2, 64, 32, 4, 2
+    A = T * R * min(E_l, K)
+    args = (torch.empty(A, I, dtype=torch.int8, device=m), torch.empty(E_l, I, H, dtype=torch.int8, device=m),
+            torch.empty(E_l, H, device=m), torch.empty(A, device=m), torch.empty(E_l, dtype=torch.int64, device=m),
+            torch.empty(T, K, dtype=torch.int32, device=m), torch.empty(T * K, dtype=torch.int32, device=m),
+            torch.empty(E_l * R, dtype=torch.int32, device=m), torch.empty(T, K, device=m))
+    before = counters["fused_down_combine"]
+    gm = make_fx(make("fx_peer", R))(*args)
+    assert fuse_down_combine(gm) == 1 and counters["fused_down_combine"] == before + 1
+    targets = [n.target for n in gm.graph.nodes if n.op == "call_function"]
+    assert npu.npu_grouped_matmul.default not in targets and npu.npu_moe_distribute_combine.default not in targets
+    assert fuse_down_combine(make_fx(make("fx_nccl", R))(*args)) == 0          # NCCL transport: rows are sent by the collective
+    assert fuse_down_combine(make_fx(make("fx_peer", 1))(*args[:5], *args[5:])) == 0   # one rank: nothing to send
+    assert fuse_down_combine(make_fx(make("fx_peer", R, keep_rows=True))(*args)) == 0   # the rows escape: must stay

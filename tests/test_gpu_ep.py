@@ -60,12 +60,14 @@ def _worker(rank, world, port, outdir, transport):
         config.mode = "reduce-overhead"
         compiled = torch.compile(fn, backend=torchair_b200.get_npu_backend(compiler_config=config), fullgraph=True, dynamic=False)
         caps = _backend.counters["captures"]
+        fdc = _backend.counters["fused_down_combine"]
         with torch.no_grad():
             for _ in range(3):
                 out_c = compiled(x.to(dev), ids.to(dev), wt.to(dev), *gw)
         torch.cuda.synchronize(dev)
         results["compiled"] = out_c.cpu()
         results["captures"] = _backend.counters["captures"] - caps
+        results["fused_down_combine"] = _backend.counters["fused_down_combine"] - fdc
         results["status"] = torchair_b200.gmm_status(dev)
         from torchair_b200 import ep as _ep
         results["peer_status"] = _ep.peer_status()
@@ -123,7 +125,10 @@ def test_expert_parallel_layer_on_gpus_matches_oracle(world, transport, tmp_path
                 assert torch.equal(a, b), "dispatch outputs (int8 rows, scales, indices, counts) must be bit-exact"
             for fused in (True, False):
                 torch.testing.assert_close(got[r][(cfg_name, fused)].float(), ref[r].float(), rtol=1e-2, atol=1e-2)
+            # fused gate_up and (over peer memory) the down GEMM storing into the senders' buffers change no bit
+            assert torch.equal(got[r][(cfg_name, True)], got[r][(cfg_name, False)])
             assert torch.equal(got[r][(cfg_name, True)], got[r][(cfg_name, False)])
             if cfg_name == "cfg0":
                 assert torch.equal(got[r]["compiled"], got[r][(cfg_name, False)]), "compiled and eager layers must agree"
                 assert got[r]["captures"] == (1 if transport == "peer" else 0)
+                assert got[r]["fused_down_combine"] == (1 if transport == "peer" else 0)

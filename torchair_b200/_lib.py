@@ -39,9 +39,11 @@ SIGNATURES = {
     "tab_ep_send_rows": [_P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P, _P, _P, _P],
     "tab_ep_unpack_rows": [_P, _P, _L, _L, _L, _L, _I, _P, _P, _P],
     "tab_ep_return_rows": [_P, _P, _L, _L, _L, _L, _L, _L, _P, _P],
+    "tab_ep_return_plan": [_P, _L, _L, _L, _L, _L, _L, _P, _P, _P],
     "tab_moe_combine": [_P, _I, _P, _P, _P, _L, _L, _L, _P, _P],
     "tab_prepack_weight_i8": [_P, _L, _L, _L, _P, _P],
     "tab_grouped_matmul_w8a8": [_P, _P, _P, _P, _P, _I, _L, _L, _L, _L, _I, _P, _P],
+    "tab_grouped_matmul_w8a8_scatter": [_P, _P, _P, _P, _P, _I, _L, _L, _L, _L, _I, _P, _P],
     "tab_grouped_matmul_swiglu_quant_workspace_bytes": [_L, _L, POINTER(c_size_t)],
     "tab_grouped_matmul_swiglu_quant": [_P, _P, _P, _P, _P, _I, _L, _L, _L, _L, _I, _P, _P, _P, c_size_t, _P],
     "tab_grouped_matmul_finalize_routing_workspace_bytes": [_L, _L, POINTER(c_size_t)],

@@ -33,7 +33,7 @@ if not logger.handlers:
     logger.setLevel(logging.ERROR)
     logger.propagate = False
 
-counters = {"compiled_graphs": 0, "captures": 0, "replays": 0, "eager_runs": 0, "fused_gate_up": 0}
+counters = {"compiled_graphs": 0, "captures": 0, "replays": 0, "eager_runs": 0, "fused_gate_up": 0, "fused_down_combine": 0}
 
 _CONVERTERS: Dict[Any, Callable] = {}
 
@@ -118,6 +118,72 @@ def _fused_gate_up_call(x, w, w_scale, x_scale, group_counts, activate_left):
                              x_scale.reshape(-1), group_counts, 1, activate_left)
 
 
+def fuse_down_combine(gm: torch.fx.GraphModule) -> int:
+    """Rewrites  npu_grouped_matmul(int8, 16-bit output) -> getitem 0 -> npu_moe_distribute_combine(expand_x=that)  into one
+    step when the group has more than one rank and moves rows over peer memory: the GEMM's epilogue then stores its rows
+    into the senders' return buffers (ops.fused_down_combine) and the intermediate [rows, H] tensor disappears."""
+    import operator
+    from . import ep
+    gmm_ops = (torch.ops.npu.npu_grouped_matmul.default, torch.ops.npu.npu_grouped_matmul.List)
+    comb_ops = (torch.ops.npu.npu_moe_distribute_combine.default, torch.ops.npu.npu_moe_distribute_combine_v2.default)
+    fused = 0
+    for node in list(gm.graph.nodes):
+        if node.op != "call_function" or node.target not in comb_ops or len(node.args) < 9:
+            continue
+        src = node.args[0]
+        if not (isinstance(src, torch.fx.Node) and src.op == "call_function" and src.target is operator.getitem and src.args[1] == 0):
+            continue
+        gmm = src.args[0]
+        if not (isinstance(gmm, torch.fx.Node) and gmm.op == "call_function" and gmm.target in gmm_ops):
+            continue
+        if len(src.users) != 1 or len(gmm.users) != 1:
+            continue
+        group, R = node.args[5], node.args[6]
+        if not (isinstance(group, str) and isinstance(R, int) and R > 1):
+            continue
+        try:
+            if ep.transport_of(group, True) != "peer":
+                continue
+        except RuntimeError:
+            continue
+        gk, ck = gmm.kwargs, node.kwargs
+        if any(v is not None and k != "shared_expert_x" and v not in (0, 1, "") for k, v in ck.items()):
+            continue     # only the shared-expert rows may be passed besides the positional arguments
+        if any(gk.get(k) for k in ("bias", "offset", "antiquant_scale", "antiquant_offset")) or gk.get("output_dtype") not in (5, 15):
+            continue
+        x_list, w_list, sc, pts = gmm.args[0], gmm.args[1], gk.get("scale"), gk.get("per_token_scale")
+        if len(x_list) != 1 or len(w_list) != 1 or not sc or not pts or len(sc) != 1 or len(pts) != 1:
+            continue
+        if not isinstance(gk.get("group_list"), torch.fx.Node):
+            continue
+        val = x_list[0].meta.get("val") if isinstance(x_list[0], torch.fx.Node) else None
+        if val is None or val.dtype != torch.int8:
+            continue
+        with gm.graph.inserting_before(node):
+            new = gm.graph.call_function(_fused_down_combine_call, (
+                x_list[0], w_list[0], sc[0], pts[0], gk["group_list"], int(gk.get("group_list_type", 0) or 0), node.args[1],
+                node.args[2], node.args[3], node.args[4], group, R, node.args[7], node.args[8], ck.get("shared_expert_x"),
+                gk["output_dtype"]))
+        node.replace_all_uses_with(new)
+        gm.graph.erase_node(node)
+        gm.graph.erase_node(src)
+        gm.graph.erase_node(gmm)
+        fused += 1
+    if fused:
+        gm.graph.lint()
+        gm.recompile()
+        counters["fused_down_combine"] += fused
+    return fused
+
+
+def _fused_down_combine_call(hq, w2, s2, hs, group_list, group_list_type, expert_ids, expand_idx, ep_send_counts, expert_scales,
+                             group_ep, R, rank, E, shared, output_dtype):
+    from . import ops
+    return ops.fused_down_combine(hq, w2, s2, hs.reshape(-1), group_list, group_list_type, expert_ids, expand_idx, ep_send_counts,
+                                  expert_scales, group_ep, R, rank, E, shared,
+                                  torch.bfloat16 if output_dtype == 15 else torch.float16)
+
+
 def _has_multi_rank_exchange(gm: torch.fx.GraphModule) -> bool:
     ex = (torch.ops.npu.npu_moe_distribute_dispatch.default, torch.ops.npu.npu_moe_distribute_combine.default)
     for n in gm.graph.nodes:
@@ -196,6 +262,7 @@ def _npu_backend(gm: torch.fx.GraphModule, example_inputs: List[torch.Tensor], *
             pre(fx_gm.graph)
         if config.experimental_config.pattern_fusion_pass.raw:
             fuse_gate_up(fx_gm)
+            fuse_down_combine(fx_gm)
         if callable(post):
             post(fx_gm.graph)
         fx_gm.recompile()
@@ -215,6 +282,7 @@ def get_compiler(compiler_config: Optional[CompilerConfig] = None):
     def compiler(fx_gm, inputs):
         if config.experimental_config.pattern_fusion_pass.raw:
             fuse_gate_up(fx_gm)
+            fuse_down_combine(fx_gm)
         return _CompiledFxGraph(fx_gm, config)
     return compiler
 

@@ -177,6 +177,28 @@ __global__ void __launch_bounds__(kEpThreads) ep_return_kernel(const uint4* __re
   }
 }
 
+// Address of every expert-output row in its source rank's return buffer (the rows that ep_return_kernel would copy
+// there), for a GEMM epilogue that stores its output rows straight into peer memory.  Rows past the total get 0.
+__global__ void __launch_bounds__(256) ep_return_plan_kernel(const int32_t* __restrict__ plan, int R, int E_l, int C,
+                                                            int64_t row_bytes, int my_rank, int64_t max_rows,
+                                                            uint8_t* const* __restrict__ peer_ret,
+                                                            unsigned long long* __restrict__ row_dst) {
+  const int n = R * E_l;
+  const int32_t* wire_off = plan;
+  const int32_t* exp_off = plan + n;
+  const int total = exp_off[n];
+  for (int64_t i = blockIdx.x * 256LL + threadIdx.x; i < max_rows; i += gridDim.x * 256LL) {
+    unsigned long long a = 0ull;
+    if (i < total) {
+      const int b = ep_last_le(exp_off, 0, n, static_cast<int>(i));
+      const int e = b / R, s = b - e * R;
+      const int within = wire_off[s * E_l + e] - s * C + (static_cast<int>(i) - exp_off[b]);
+      a = reinterpret_cast<unsigned long long>(peer_ret[s] + (static_cast<int64_t>(my_rank) * C + within) * row_bytes);
+    }
+    row_dst[i] = a;
+  }
+}
+
 }  // namespace tab
 
 using namespace tab;
@@ -238,4 +260,18 @@ extern "C" int tab_ep_return_rows(const void* y, const int32_t* plan, int64_t R,
                                                                               (int)slot_rows, (int)(row_bytes / 16), (int)my_rank,
                                                                               reinterpret_cast<uint8_t* const*>(peer_ret));
   return check_launch("ep_return_rows");
+}
+
+extern "C" int tab_ep_return_plan(const int32_t* plan, int64_t R, int64_t E_l, int64_t slot_rows, int64_t row_bytes,
+                                  int64_t max_rows, int64_t my_rank, void* const* peer_ret, uint64_t* row_dst,
+                                  tab_stream_t stream) {
+  if (max_rows == 0) return TAB_OK;
+  if (!plan || !peer_ret || !row_dst || R < 1 || R > kEpMaxRanks || E_l < 1 || R * E_l > 2048 || slot_rows < 1 || my_rank < 0 ||
+      my_rank >= R || max_rows < 0 || max_rows > (1LL << 30))
+    return fail(TAB_ERR_BAD_ARG, "ep_return_plan: bad argument");
+  if (row_bytes <= 0 || row_bytes % 16 != 0) return fail(TAB_ERR_ALIGNMENT, "ep_return_plan: row_bytes=%lld must be a multiple of 16", (long long)row_bytes);
+  ep_return_plan_kernel<<<grid_for((max_rows + 255) / 256, 8), 256, 0, as_stream(stream)>>>(
+      plan, (int)R, (int)E_l, (int)slot_rows, row_bytes, (int)my_rank, max_rows, reinterpret_cast<uint8_t* const*>(peer_ret),
+      reinterpret_cast<unsigned long long*>(row_dst));
+  return check_launch("ep_return_plan");
 }

@@ -33,6 +33,7 @@ struct GmmParams {
   const float* tok_scale;  // [M] or null
   void* out;               // plain: [M, N] of out_dtype
   int out_dtype;
+  const unsigned long long* row_dst;   // plain, 16-bit output: address of every output row (may be peer memory), or null
   float* h_out;            // fused: [M, I] fp32
   unsigned int* amax;      // fused: [M] row amax as fp32 bits
   int activate_left;
@@ -54,6 +55,11 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, vola
     }
   }
   return true;
+}
+
+// First byte of output row `row`: the row's own address when a table is given, else row-major in p.out.
+__device__ __forceinline__ uint8_t* out_row_ptr(const GmmParams& p, int64_t row, int esz) {
+  return p.row_dst ? reinterpret_cast<uint8_t*>(p.row_dst[row]) : static_cast<uint8_t*>(p.out) + row * p.N * esz;
 }
 
 struct WorkItem {

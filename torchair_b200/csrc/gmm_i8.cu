@@ -235,11 +235,11 @@ gmm_i8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
                 const float f0 = __fmul_rn(__fmul_rn(__int2float_rn(a[j]), ts), w0);
                 const float f1 = __fmul_rn(__fmul_rn(__int2float_rn(b[j]), ts), w1);
                 if (p.out_dtype == TAB_BF16) {
-                  __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + row * p.N;
+                  __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out_row_ptr(p, row, 2));
                   if (v0) o[c0] = __float2bfloat16_rn(f0);
                   if (v1) o[c1] = __float2bfloat16_rn(f1);
                 } else {
-                  __half* o = static_cast<__half*>(p.out) + row * p.N;
+                  __half* o = reinterpret_cast<__half*>(out_row_ptr(p, row, 2));
                   if (v0) o[c0] = __float2half_rn(f0);
                   if (v1) o[c1] = __float2half_rn(f1);
                 }
@@ -430,16 +430,16 @@ extern "C" int tab_prepack_weight_i8(const int8_t* weight, int64_t E, int64_t Kd
   return check_launch("prepack_weight");
 }
 
-extern "C" int tab_grouped_matmul_w8a8(const int8_t* x, const int8_t* packed_weight, const float* scale,
-                                       const float* per_token_scale, const int64_t* group_list, int group_list_type,
-                                       int64_t M, int64_t Kd, int64_t N, int64_t E, int out_dtype, void* y,
-                                       tab_stream_t stream) {
+static int grouped_matmul_plain(const int8_t* x, const int8_t* packed_weight, const float* scale, const float* per_token_scale,
+                                const int64_t* group_list, int group_list_type, int64_t M, int64_t Kd, int64_t N, int64_t E,
+                                int out_dtype, void* y, const uint64_t* row_dst, tab_stream_t stream) {
   int rc = check_common("grouped_matmul", x, packed_weight, group_list, group_list_type, M, Kd, N, E);
   if (rc != TAB_OK) return rc;
   if (out_dtype != TAB_I32 && out_dtype != TAB_BF16 && out_dtype != TAB_F16)
     return fail(TAB_ERR_UNSUPPORTED, "grouped_matmul: output dtype %d (want 3, 5 or 15)", out_dtype);
+  if (row_dst && out_dtype == TAB_I32) return fail(TAB_ERR_UNSUPPORTED, "grouped_matmul: a row address table needs a 16-bit output dtype");
   if (M == 0) return TAB_OK;
-  if (!y) return fail(TAB_ERR_BAD_ARG, "grouped_matmul: null output");
+  if (!y && !row_dst) return fail(TAB_ERR_BAD_ARG, "grouped_matmul: null output");
   const int nt = use_prefill(M, E) ? 0 : pick_nt(M, E);     // 0 selects the prefill orientation
   CUtensorMap tm_w, tm_x;
   rc = make_maps(x, packed_weight, M, Kd, N, E, nt == 0 ? kPfTokens : nt, &tm_w, &tm_x);
@@ -454,7 +454,26 @@ extern "C" int tab_grouped_matmul_w8a8(const int8_t* x, const int8_t* packed_wei
   p.tok_scale = out_dtype == TAB_I32 ? nullptr : per_token_scale;
   p.out = y;
   p.out_dtype = out_dtype;
+  p.row_dst = reinterpret_cast<const unsigned long long*>(row_dst);
   return launch_gmm<false>(nt, tm_w, tm_x, p, as_stream(stream));
+}
+
+extern "C" int tab_grouped_matmul_w8a8(const int8_t* x, const int8_t* packed_weight, const float* scale,
+                                       const float* per_token_scale, const int64_t* group_list, int group_list_type,
+                                       int64_t M, int64_t Kd, int64_t N, int64_t E, int out_dtype, void* y,
+                                       tab_stream_t stream) {
+  return grouped_matmul_plain(x, packed_weight, scale, per_token_scale, group_list, group_list_type, M, Kd, N, E, out_dtype, y,
+                              nullptr, stream);
+}
+
+extern "C" int tab_grouped_matmul_w8a8_scatter(const int8_t* x, const int8_t* packed_weight, const float* scale,
+                                               const float* per_token_scale, const int64_t* group_list, int group_list_type,
+                                               int64_t M, int64_t Kd, int64_t N, int64_t E, int out_dtype,
+                                               const uint64_t* row_dst, tab_stream_t stream) {
+  if (!row_dst && M > 0) return fail(TAB_ERR_BAD_ARG, "grouped_matmul_scatter: null row address table");
+  if ((N * 2) % 16 != 0) return fail(TAB_ERR_ALIGNMENT, "grouped_matmul_scatter: N=%lld must be a multiple of 8", (long long)N);
+  return grouped_matmul_plain(x, packed_weight, scale, per_token_scale, group_list, group_list_type, M, Kd, N, E, out_dtype, nullptr,
+                              row_dst, stream);
 }
 
 extern "C" int tab_grouped_matmul_swiglu_quant_workspace_bytes(int64_t M, int64_t I, size_t* bytes) {

@@ -92,14 +92,13 @@ __device__ __forceinline__ void pf_narrow_epilogue(const GmmParams& p, const Wor
       for (int j = 0; j < 16; ++j) {
         const int row = row0 + c + j;
         if (c + j < nvalid && cvalid) {
-          const int64_t o = static_cast<int64_t>(row) * p.N + ch;
           if (p.out_dtype == TAB_I32) {
-            static_cast<int*>(p.out)[o] = a[j];
+            static_cast<int*>(p.out)[static_cast<int64_t>(row) * p.N + ch] = a[j];
           } else {
             const float ts = p.tok_scale ? p.tok_scale[row] : 1.f;
             const float f = __fmul_rn(__fmul_rn(__int2float_rn(a[j]), ts), wv);
-            if (p.out_dtype == TAB_BF16) static_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(f);
-            else static_cast<__half*>(p.out)[o] = __float2half_rn(f);
+            if (p.out_dtype == TAB_BF16) reinterpret_cast<__nv_bfloat16*>(out_row_ptr(p, row, 2))[ch] = __float2bfloat16_rn(f);
+            else reinterpret_cast<__half*>(out_row_ptr(p, row, 2))[ch] = __float2half_rn(f);
           }
         }
       }
@@ -348,7 +347,7 @@ gmm_i8_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
               const int grow = row_base + r;
               if (grow < row_end && cvalid) {
                 const uint4 v = *reinterpret_cast<const uint4*>(patch + r * kPfOutPitch + piece * 16);
-                uint8_t* o = static_cast<uint8_t*>(p.out) + (static_cast<int64_t>(grow) * p.N + c0 + c) * esz + piece * 16;
+                uint8_t* o = out_row_ptr(p, grow, esz) + static_cast<int64_t>(c0 + c) * esz + piece * 16;
                 __stcs(reinterpret_cast<uint4*>(o), v);   // streamed: outputs must not push weights and rows out of L2
               }
             }
@@ -374,8 +373,8 @@ gmm_i8_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
               for (int j = 0; j < 16; ++j) {
                 if (c0 + c + j >= p.N) break;
                 const float f = __fmul_rn(__fmul_rn(__int2float_rn(a[j]), ts), ws[c + j]);
-                if (p.out_dtype == TAB_BF16) static_cast<__nv_bfloat16*>(p.out)[static_cast<int64_t>(row) * p.N + c0 + c + j] = __float2bfloat16_rn(f);
-                else static_cast<__half*>(p.out)[static_cast<int64_t>(row) * p.N + c0 + c + j] = __float2half_rn(f);
+                if (p.out_dtype == TAB_BF16) reinterpret_cast<__nv_bfloat16*>(out_row_ptr(p, row, 2))[c0 + c + j] = __float2bfloat16_rn(f);
+                else reinterpret_cast<__half*>(out_row_ptr(p, row, 2))[c0 + c + j] = __float2half_rn(f);
               }
             }
           }

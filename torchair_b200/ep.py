@@ -315,6 +315,39 @@ def _combine_peer(kern, expand_x, expert_ids, expand_idx, ep_send_counts, expert
     return out
 
 
+def combine_from_producer(kern, produce_rows, rows, H, dtype, expert_ids, expand_idx, ep_send_counts, expert_scales, group_ep,
+                          R, rank, E, shared=None):
+    """Combine whose expert-output rows are stored into the source ranks' return buffers by their producer.
+
+    Peer transport only.  ``produce_rows(row_dst)`` must enqueue, on the current stream, work that stores output row i
+    (``H`` elements of ``dtype``, i < rows) at the address ``row_dst[i]`` (an int64 device tensor; 0 = row not in any
+    group); with the grouped GEMM's scatter epilogue the rows cross NVLink tile by tile while the GEMM runs, and
+    neither a local [rows, H] tensor nor a copy kernel exists.  Everything else is _combine_peer.
+    """
+    counters["combine_calls"] += 1
+    T, K = expert_ids.shape
+    E_l = E // R
+    if dtype not in (torch.bfloat16, torch.float16):
+        raise NotImplementedError("npu_moe_distribute_combine over peer memory: rows must be bfloat16 or float16")
+    px = _last_dispatch.get((group_ep, R, rank, T, K, H, E, expand_idx.device.index))
+    if px is None:
+        raise RuntimeError("npu_moe_distribute_combine: no matching npu_moe_distribute_dispatch ran on this group")
+    st = px._stream()
+    recv_counts = ep_send_counts.view(E_l, R).t().contiguous()
+    plan, _, _ = kern.exchange_plan(recv_counts, R, E_l, px.C, 1)
+    row_dst = torch.empty((rows,), dtype=torch.int64, device=expand_idx.device)
+    _lib.call("tab_ep_return_plan", _ptr(plan), R, E_l, px.C, H * 2, rows, rank, _ptr(px.peer_ret), _ptr(row_dst), st)
+    px.wait(px.KIND_ACK_C, 0)                     # the sources have reduced the rows of the previous combine
+    produce_rows(row_dst)
+    px.signal(px.KIND_DATA_C)
+    px.wait(px.KIND_DATA_C, 1)
+    back = px.ret_local.view(dtype).view(R * px.C, H)
+    out = kern.combine(back, expand_idx, expert_scales, shared, T, K)
+    px.signal(px.KIND_ACK_C)
+    counters["wire_bytes_sent"] += T * K * H * 2
+    return out
+
+
 def _remember(key, value):
     if len(_splits) >= _SPLITS_MAX:
         _splits.pop(next(iter(_splits)))

@@ -17,8 +17,9 @@ def moe_layer(x, expert_ids, expert_scales, w1, s1, w2, s2, *, group_ep: str = "
     """x [T, H] bf16; expert_ids int32 [T, K]; expert_scales fp32 [T, K]; w1 int8 [E_l, H, 2I]; s1 fp32 [E_l, 2I];
     w2 int8 [E_l, I, H]; s2 fp32 [E_l, H] (this rank's experts).  Returns [T, H] bf16.
 
-    fused=True issues gate_up + SwiGLU + requant as npu_grouped_matmul_swiglu_quant_v2; fused=False issues the
-    int32 grouped matmul and npu_dequant_swiglu_quant separately (what the FX fusion pass rewrites).
+    fused=True issues gate_up + SwiGLU + requant as npu_grouped_matmul_swiglu_quant_v2 and, with more than one rank, the
+    down projection together with the combine; fused=False issues the int32 grouped matmul, npu_dequant_swiglu_quant,
+    the down grouped matmul and the combine separately (what the FX fusion passes rewrite).
     """
     npu = torch.ops.npu
     R = ep_world_size
@@ -32,6 +33,11 @@ def moe_layer(x, expert_ids, expert_scales, w1, s1, w2, s2, *, group_ep: str = "
                                      output_dtype=3)[0]
         hq, hs = npu.npu_dequant_swiglu_quant(h32, weight_scale=s1, activation_scale=xs, group_index=nums,
                                               activate_left=True, quant_mode=1)
+    if fused and R > 1 and not torch.compiler.is_compiling():
+        # down GEMM and combine in one step: over peer memory the GEMM's epilogue stores its rows into the senders'
+        # return buffers (a compiled graph gets the same rewrite from the FX pass of the backend)
+        return ops.fused_down_combine(hq, w2, s2, hs, nums, 1, expert_ids, expand_idx, ep_recv, expert_scales, group_ep, R,
+                                      ep_rank_id, E, out_dtype=x.dtype)
     y = npu.npu_grouped_matmul([hq], [w2], scale=[s2], per_token_scale=[hs], group_list=nums, split_item=2,
-                               group_type=0, group_list_type=1, output_dtype=15)[0]
+                               group_type=0, group_list_type=1, output_dtype=15 if x.dtype == torch.bfloat16 else 5)[0]
     return npu.npu_moe_distribute_combine(y, expert_ids, expand_idx, ep_recv, expert_scales, group_ep, R, ep_rank_id, E)

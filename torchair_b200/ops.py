@@ -491,6 +491,41 @@ def _gmm_fr_cuda(x, w, group_list, *, scale=None, bias=None, offset=None, pertok
     return y
 
 
+def fused_down_combine(hq, w2, s2, hs, group_list, group_list_type, expert_ids, expand_idx, ep_send_counts, expert_scales,
+                       group_ep, ep_world_size, ep_rank_id, moe_expert_num, shared_expert_x=None, out_dtype=torch.bfloat16):
+    """Down projection + npu_moe_distribute_combine as one step.
+
+    With more than one rank on the peer-memory transport the grouped GEMM's epilogue stores every output row straight
+    into the return buffer of the rank that sent the token (NVLink stores from inside the GEMM kernel, tile by tile), so
+    the transfer overlaps the GEMM and no [rows, H] tensor or copy kernel exists.  Otherwise it is the two operators
+    one after the other.  Results are identical either way.
+    """
+    R = int(ep_world_size)
+    od = 15 if out_dtype == torch.bfloat16 else 5
+    if R == 1 or ep.transport_of(group_ep, hq.is_cuda) != "peer":
+        y = torch.ops.npu.npu_grouped_matmul([hq], [w2], scale=[s2], per_token_scale=[hs], group_list=group_list, split_item=2,
+                                             group_type=0, group_list_type=group_list_type, output_dtype=od)[0]
+        return torch.ops.npu.npu_moe_distribute_combine(y, expert_ids, expand_idx, ep_send_counts, expert_scales, group_ep, R,
+                                                        ep_rank_id, moe_expert_num, shared_expert_x=shared_expert_x)
+    if hq.dtype != torch.int8 or w2.dtype != torch.int8:
+        raise NotImplementedError("fused down + combine: only int8 x int8 (W8A8) is on the path")
+    ep.check_combine_args(hq, expert_ids, expert_scales, R, ep_rank_id, moe_expert_num, None, None, None, None, 0, 0, 0, 0, 0, 0)
+    M, Kd = hq.shape
+    E_l, _, N = w2.shape
+    if s2.dtype != torch.float32 or s2.numel() != E_l * N or hs.dtype != torch.float32 or hs.numel() != M or group_list.numel() != E_l:
+        raise RuntimeError("fused down + combine: scale must be fp32 [E_l, H], per-token scale fp32 [M], group_list [E_l]")
+    hq, s2, hs = hq.contiguous(), s2.contiguous(), hs.contiguous()
+    gl = group_list.to(torch.int64).contiguous()
+    wp = packed_weight(w2)
+
+    def produce_rows(row_dst):
+        _lib.call("tab_grouped_matmul_w8a8_scatter", _ptr(hq), _ptr(wp), _ptr(s2), _ptr(hs), _ptr(gl), int(group_list_type), M, Kd, N,
+                  E_l, od, _ptr(row_dst), _stream(hq))
+
+    return ep.combine_from_producer(ep.CudaKernels, produce_rows, M, N, out_dtype, expert_ids, expand_idx, ep_send_counts,
+                                    expert_scales, group_ep, R, ep_rank_id, moe_expert_num, shared_expert_x)
+
+
 def gmm_status(device=None) -> int:
     """Synchronises the current stream and returns the GEMM kernels' device status word (0 = fine)."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
