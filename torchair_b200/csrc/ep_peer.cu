@@ -69,12 +69,16 @@ __global__ void ep_wait_kernel(const unsigned long long* __restrict__ flags, uns
   }
 }
 
-// First sorted position of every destination rank's rows, from the per-expert counts (E = R * E_l entries).
+// First sorted position of every destination rank's rows, from the per-expert counts (E = R * E_l entries): one warp
+// per destination sums that rank's counts with coalesced loads and a shuffle reduction.
 __device__ __forceinline__ void rank_bases_to_smem(const int32_t* __restrict__ expert_counts, int R, int E_l, int* s_base) {
-  if (threadIdx.x < R) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int r = warp; r < R; r += nwarps) {
     int c = 0;
-    for (int e = 0; e < E_l; ++e) c += max(expert_counts[threadIdx.x * E_l + e], 0);
-    s_base[threadIdx.x + 1] = c;
+    for (int e = lane; e < E_l; e += 32) c += max(expert_counts[r * E_l + e], 0);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+    if (lane == 0) s_base[r + 1] = c;
   }
   __syncthreads();
   if (threadIdx.x == 0) {
