@@ -468,8 +468,8 @@ def gpu_arm(args):
     if sampler is not None:
         sampler.stop()
     if rank == 0:
-        # sort x3, pack, gemm, requant, gemm, combine; nccl adds plan + permute each way; peer adds send/unpack/return,
-        # two plans and eight flag kernels
+        # sort x3, pack, gemm, requant, gemm, combine; nccl adds plan + permute each way; peer adds send, unpack, two plans,
+        # the return-address table (the down GEMM stores into the peers itself) and eight flag kernels
         launches_per_step = 8 if world == 1 else (21 if args.ep_transport == "peer" else 12)
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
