@@ -119,13 +119,15 @@ TAB_API int tab_moe_init_routing_static(const void* x, int x_dtype, const int32_
  * token once (quant_mode 2: int8 rows + fp32 scales; quant_mode 0: rows keep x_dtype, scales = 0) and
  * writes the copies in sorted order:
  *   send_rows [T*K, H], send_scales fp32 [T*K], expand_idx int32 [T*K] (position of pair t*K+k),
- *   expert_counts int32 [num_experts] (copies per global expert).
- * With one rank this is the whole dispatch: send_rows is expand_x and expert_counts the token counts.
+ *   expert_counts int32 [num_experts] (copies per global expert); expert_token_nums int64 [num_experts] (NULL to
+ *   skip) = the same counts (nums_type 1) or their running total (0), the form the grouped GEMM's group_list takes.
+ * With one rank this is the whole dispatch: send_rows is expand_x and expert_token_nums the operator's output.
  * ------------------------------------------------------------------------------------------------- */
 TAB_API int tab_moe_dispatch_pack_workspace_bytes(int64_t T, int64_t K, int64_t num_experts, size_t* bytes);
 TAB_API int tab_moe_dispatch_pack(const void* x, int x_dtype, const int32_t* expert_ids, int64_t T, int64_t K,
                           int64_t H, int64_t num_experts, int quant_mode, void* send_rows,
                           float* send_scales, int32_t* expand_idx, int32_t* expert_counts,
+                          int64_t* expert_token_nums, int nums_type,
                           void* workspace, size_t workspace_bytes, tab_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------

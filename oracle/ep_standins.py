@@ -11,7 +11,7 @@ from . import moe_oracle as O
 
 class OracleKernels:
     @staticmethod
-    def dispatch_pack(x, expert_ids, E, quant_mode):
+    def dispatch_pack(x, expert_ids, E, quant_mode, nums_type=None):
         T, K = expert_ids.shape
         if quant_mode == 2:
             q, s = O.dynamic_quant(x)
@@ -23,7 +23,10 @@ class OracleKernels:
         expand_idx = torch.empty(T * K, dtype=torch.int32)
         expand_idx[order.indices] = torch.arange(T * K, dtype=torch.int32)
         counts = torch.bincount(flat, minlength=E).to(torch.int32)
-        return q[tok].contiguous(), s[tok].contiguous(), expand_idx, counts
+        nums = None
+        if nums_type is not None:
+            nums = counts.to(torch.int64) if nums_type == 1 else torch.cumsum(counts.to(torch.int64), 0)
+        return q[tok].contiguous(), s[tok].contiguous(), expand_idx, counts, nums
 
     @staticmethod
     def exchange_plan(recv_counts, R, E_l, slot_rows, nums_type):

@@ -26,7 +26,7 @@ SIGNATURES = {
     "tab_moe_init_routing": [_P, _I, _P, _P, _L, _L, _L, _L, _L, _P, _P, _P, _P, c_size_t, _P],
     "tab_moe_init_routing_static": [_P, _I, _P, _P, _L, _L, _L, _L, _L, _P, _P, _P, _P],
     "tab_moe_dispatch_pack_workspace_bytes": [_L, _L, _L, POINTER(c_size_t)],
-    "tab_moe_dispatch_pack": [_P, _I, _P, _L, _L, _L, _L, _I, _P, _P, _P, _P, _P, c_size_t, _P],
+    "tab_moe_dispatch_pack": [_P, _I, _P, _L, _L, _L, _L, _I, _P, _P, _P, _P, _P, _I, _P, c_size_t, _P],
     "tab_moe_exchange_plan": [_P, _L, _L, _L, _I, _P, _P, _P, _P],
     "tab_moe_exchange_rows": [_P, _P, _P, _L, _L, _L, _I, _L, _L, _I, _P, _P, _P],
     "tab_moe_compute_expert_tokens": [_P, _L, _L, _P, _P],

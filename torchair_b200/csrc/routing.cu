@@ -204,10 +204,29 @@ __global__ void __launch_bounds__(THREADS) dispatch_pack_kernel(const T* __restr
                                                                const int32_t* __restrict__ expand_idx,
                                                                int64_t tokens, int K, int cols,
                                                                void* __restrict__ send_rows,
-                                                               float* __restrict__ send_scales) {
+                                                               float* __restrict__ send_scales,
+                                                               const int32_t* __restrict__ counts,
+                                                               int64_t* __restrict__ nums64, int num_experts,
+                                                               int nums_type) {
   __shared__ float red[THREADS / 32];
   __shared__ int s_pos[kPackMaxK];
   const int nchunk = cols >> 3;
+  if (nums64 != nullptr && blockIdx.x == gridDim.x - 1 && threadIdx.x < 32) {
+    // the per-expert copies as int64 counts (nums_type 1) or their running total (0), the form the grouped GEMM reads
+    long long run = 0;
+    for (int e0 = 0; e0 < num_experts; e0 += 32) {
+      const int e = e0 + threadIdx.x;
+      const long long c = e < num_experts ? counts[e] : 0;
+      long long incl = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const long long t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (threadIdx.x >= o) incl += t;
+      }
+      if (e < num_experts) nums64[e] = nums_type == 1 ? c : run + incl;
+      run += __shfl_sync(0xffffffffu, incl, 31);
+    }
+  }
   for (int64_t t = blockIdx.x; t < tokens; t += gridDim.x) {
     const T* xr = x + t * cols;
     __syncthreads();   // previous token's positions are no longer read
@@ -269,16 +288,16 @@ __global__ void __launch_bounds__(THREADS) dispatch_pack_kernel(const T* __restr
 
 template <typename T>
 static void launch_pack(const void* x, const int32_t* expand_idx, int64_t T_, int K, int H, int quant_mode, void* rows,
-                        float* scales, cudaStream_t st) {
+                        float* scales, const int32_t* counts, int64_t* nums64, int num_experts, int nums_type, cudaStream_t st) {
   const T* xp = static_cast<const T*>(x);
   const bool small = H / 8 <= 128 * kPackChunks;
   const int grid = grid_for(T_, small ? 10 : 5);
   if (quant_mode == 2) {
-    if (small) dispatch_pack_kernel<T, true, 128><<<grid, 128, 0, st>>>(xp, expand_idx, T_, K, H, rows, scales);
-    else dispatch_pack_kernel<T, true, 256><<<grid, 256, 0, st>>>(xp, expand_idx, T_, K, H, rows, scales);
+    if (small) dispatch_pack_kernel<T, true, 128><<<grid, 128, 0, st>>>(xp, expand_idx, T_, K, H, rows, scales, counts, nums64, num_experts, nums_type);
+    else dispatch_pack_kernel<T, true, 256><<<grid, 256, 0, st>>>(xp, expand_idx, T_, K, H, rows, scales, counts, nums64, num_experts, nums_type);
   } else {
-    if (small) dispatch_pack_kernel<T, false, 128><<<grid, 128, 0, st>>>(xp, expand_idx, T_, K, H, rows, scales);
-    else dispatch_pack_kernel<T, false, 256><<<grid, 256, 0, st>>>(xp, expand_idx, T_, K, H, rows, scales);
+    if (small) dispatch_pack_kernel<T, false, 128><<<grid, 128, 0, st>>>(xp, expand_idx, T_, K, H, rows, scales, counts, nums64, num_experts, nums_type);
+    else dispatch_pack_kernel<T, false, 256><<<grid, 256, 0, st>>>(xp, expand_idx, T_, K, H, rows, scales, counts, nums64, num_experts, nums_type);
   }
 }
 
@@ -474,7 +493,8 @@ extern "C" int tab_moe_dispatch_pack_workspace_bytes(int64_t T, int64_t K, int64
 extern "C" int tab_moe_dispatch_pack(const void* x, int x_dtype, const int32_t* expert_ids, int64_t T, int64_t K,
                                      int64_t H, int64_t num_experts, int quant_mode, void* send_rows,
                                      float* send_scales, int32_t* expand_idx, int32_t* expert_counts,
-                                     void* workspace, size_t workspace_bytes, tab_stream_t stream) {
+                                     int64_t* expert_token_nums, int nums_type, void* workspace, size_t workspace_bytes,
+                                     tab_stream_t stream) {
   size_t need = 0;
   int rc = tab_moe_dispatch_pack_workspace_bytes(T, K, num_experts, &need);
   if (rc != TAB_OK) return rc;
@@ -482,10 +502,12 @@ extern "C" int tab_moe_dispatch_pack(const void* x, int x_dtype, const int32_t* 
   const int es = elem_size(x_dtype);
   if (x_dtype != TAB_BF16 && x_dtype != TAB_F16) return fail(TAB_ERR_UNSUPPORTED, "dispatch_pack: x dtype %d (want 5 or 15)", x_dtype);
   if (!expert_counts) return fail(TAB_ERR_BAD_ARG, "dispatch_pack: null pointer");
+  if (nums_type != 0 && nums_type != 1) return fail(TAB_ERR_BAD_ARG, "dispatch_pack: nums_type %d", nums_type);
   cudaStream_t st = as_stream(stream);
   const int64_t n = T * K;
   if (n == 0) {
     cudaError_t e = cudaMemsetAsync(expert_counts, 0, num_experts * sizeof(int32_t), st);
+    if (e == cudaSuccess && expert_token_nums) e = cudaMemsetAsync(expert_token_nums, 0, num_experts * sizeof(int64_t), st);
     return e == cudaSuccess ? TAB_OK : fail(TAB_ERR_CUDA, "dispatch_pack: memset: %s", cudaGetErrorString(e));
   }
   if (n > (1LL << 30) || K > 256) return fail(TAB_ERR_UNSUPPORTED, "dispatch_pack: T*K too large or K > 256");
@@ -498,8 +520,10 @@ extern "C" int tab_moe_dispatch_pack(const void* x, int x_dtype, const int32_t* 
   SortScratch s = carve(workspace, n, num_experts, true);
   rc = run_sort(expert_ids, nullptr, n, num_experts, s, s.sorted_expert, expand_idx, expert_counts, st);
   if (rc != TAB_OK) return rc;
-  if (x_dtype == TAB_BF16) launch_pack<__nv_bfloat16>(x, expand_idx, T, (int)K, (int)H, quant_mode, send_rows, send_scales, st);
-  else launch_pack<__half>(x, expand_idx, T, (int)K, (int)H, quant_mode, send_rows, send_scales, st);
+  if (x_dtype == TAB_BF16)
+    launch_pack<__nv_bfloat16>(x, expand_idx, T, (int)K, (int)H, quant_mode, send_rows, send_scales, expert_counts, expert_token_nums, (int)num_experts, nums_type, st);
+  else
+    launch_pack<__half>(x, expand_idx, T, (int)K, (int)H, quant_mode, send_rows, send_scales, expert_counts, expert_token_nums, (int)num_experts, nums_type, st);
   return check_launch("dispatch_pack");
 }
 
@@ -745,17 +769,6 @@ __global__ void __launch_bounds__(256) finalize_routing_kernel(const T* __restri
   }
 }
 
-// counts int32 [n] -> int64 counts (type 1) or inclusive cumulative sums (type 0); one CTA.
-__global__ void __launch_bounds__(1024) tokens_count_or_cumsum_kernel(const int32_t* __restrict__ counts, int n, int type,
-                                                                      int64_t* __restrict__ out) {
-  __shared__ int s_val[kMaxExperts];
-  __shared__ int s_warp[33];
-  for (int i = threadIdx.x; i < n; i += 1024) s_val[i] = counts[i];
-  __syncthreads();
-  if (type == 0) block_exclusive_scan(s_val, n, s_warp);
-  for (int i = threadIdx.x; i < n; i += 1024) out[i] = type == 0 ? static_cast<int64_t>(s_val[i]) + counts[i] : static_cast<int64_t>(s_val[i]);
-}
-
 }  // namespace tab
 
 extern "C" int tab_moe_compute_expert_tokens(const int32_t* sorted_experts, int64_t n, int64_t num_experts, int32_t* out,
@@ -821,8 +834,9 @@ extern "C" int tab_moe_init_routing_v2(const void* x, int x_dtype, const int32_t
   int32_t* scatter_idx = reinterpret_cast<int32_t*>(wsb + need);               // f -> position
   int32_t* counts = scatter_idx + ((n + 63) / 64) * 64;
   int32_t* idx_out = row_idx_type == 1 ? expanded_row_idx : scatter_idx;
+  // the pack kernel also writes the rows per expert as int64 counts or their running total
   rc = tab_moe_dispatch_pack(x, x_dtype, expert_idx, T, K, H, expert_num, quant_mode == 1 ? 2 : 0, expanded_x, expanded_scale, idx_out,
-                             counts, workspace, need, stream);
+                             counts, expert_tokens, tokens_num_type, workspace, need, stream);
   if (rc != TAB_OK) return rc;
   cudaStream_t st = as_stream(stream);
   if (row_idx_type == 0 && n > 0) {
@@ -831,7 +845,6 @@ extern "C" int tab_moe_init_routing_v2(const void* x, int x_dtype, const int32_t
     cudaError_t e = cudaMemcpyAsync(expanded_row_idx, s.sorted_src, n * sizeof(int32_t), cudaMemcpyDeviceToDevice, st);
     if (e != cudaSuccess) return fail(TAB_ERR_CUDA, "init_routing_v2: copy: %s", cudaGetErrorString(e));
   }
-  tokens_count_or_cumsum_kernel<<<1, 1024, 0, st>>>(counts, (int)expert_num, tokens_num_type, expert_tokens);
   return check_launch("init_routing_v2");
 }
 

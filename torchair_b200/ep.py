@@ -127,7 +127,7 @@ class CudaKernels:
     """The shipped provider: every step is one or more sm_100a kernels behind the C ABI."""
 
     @staticmethod
-    def dispatch_pack(x, expert_ids, E, quant_mode):
+    def dispatch_pack(x, expert_ids, E, quant_mode, nums_type=None):
         if not x.is_cuda:
             raise RuntimeError("torchair_b200 kernels need CUDA tensors; there is no CPU implementation")
         if expert_ids.dtype != torch.int32:
@@ -142,11 +142,12 @@ class CudaKernels:
         scales = torch.empty((T * K,), dtype=torch.float32, device=dev)
         expand_idx = torch.empty((T * K,), dtype=torch.int32, device=dev)
         counts = torch.empty((E,), dtype=torch.int32, device=dev)
+        nums = None if nums_type is None else torch.empty((E,), dtype=torch.int64, device=dev)   # counts / running total
         nbytes = _lib.workspace_bytes("tab_moe_dispatch_pack_workspace_bytes", T, K, E)
         ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=dev)
         _lib.call("tab_moe_dispatch_pack", _ptr(x), _ST_INV[x.dtype], _ptr(expert_ids), T, K, H, E, quant_mode, _ptr(rows),
-                  _ptr(scales), _ptr(expand_idx), _ptr(counts), _ptr(ws), ws.numel(), _stream(x))
-        return rows, scales, expand_idx, counts
+                  _ptr(scales), _ptr(expand_idx), _ptr(counts), _ptr(nums), int(nums_type or 0), _ptr(ws), ws.numel(), _stream(x))
+        return rows, scales, expand_idx, counts, nums
 
     @staticmethod
     def exchange_plan(recv_counts, R, E_l, slot_rows, nums_type):
@@ -266,7 +267,7 @@ def peer_status() -> int:
 
 
 def _dispatch_peer(kern, x, expert_ids, group_ep, pg, R, rank, E, quant_mode, nums_type, send, tp_recv, expand_scales):
-    send_rows, send_scales, expand_idx, counts = send
+    send_rows, send_scales, expand_idx, counts = send[:4]
     T, K = expert_ids.shape
     H = x.shape[1]
     E_l = E // R
@@ -354,6 +355,23 @@ def _remember(key, value):
     _splits[key] = value
 
 
+_zero_cache: Dict[tuple, torch.Tensor] = {}
+
+
+def _zeros(shape, dtype, device) -> torch.Tensor:
+    """The all-zero handshake outputs (tp_recv_count, expand_scales).  Nothing in this library writes them, so on a GPU
+    one tensor per shape is filled once and handed out again: no fill launch per call.  Callers must not write into them."""
+    if device.type != "cuda":
+        return torch.zeros(shape, dtype=dtype, device=device)
+    key = (tuple(shape), dtype, device.index)
+    t = _zero_cache.get(key)
+    if t is None:
+        if torch.cuda.is_current_stream_capturing():
+            return torch.zeros(shape, dtype=dtype, device=device)    # a capture's pool must not own the shared tensor
+        t = _zero_cache[key] = torch.zeros(shape, dtype=dtype, device=device)
+    return t
+
+
 def dispatch(kern, x, expert_ids, group_ep, R, rank, E, quant_mode, nums_type, tp_slots=1):
     """Returns the seven outputs of npu_moe_distribute_dispatch.
 
@@ -369,13 +387,10 @@ def dispatch(kern, x, expert_ids, group_ep, R, rank, E, quant_mode, nums_type, t
     E_l = E // R
     A = dispatch_rows(T, R, E, K)
     dev = x.device
-    send_rows, send_scales, expand_idx, counts = kern.dispatch_pack(x, expert_ids, E, quant_mode)
-    tp_recv = torch.zeros((tp_slots,), dtype=torch.int32, device=dev)
-    expand_scales = torch.zeros((A,), dtype=torch.float32, device=dev)
+    send_rows, send_scales, expand_idx, counts, nums = kern.dispatch_pack(x, expert_ids, E, quant_mode, nums_type if R == 1 else None)
+    tp_recv = _zeros((tp_slots,), torch.int32, dev)
+    expand_scales = _zeros((A,), torch.float32, dev)
     if R == 1:
-        nums = counts.to(torch.int64)
-        if nums_type == 0:
-            nums = torch.cumsum(nums, 0)
         if A != T * K:  # K > E: cannot happen with distinct experts per token, kept for shape safety
             pad_rows = torch.zeros((A, H), dtype=send_rows.dtype, device=dev)
             pad_rows[:T * K] = send_rows
