@@ -230,12 +230,14 @@ TAB_API int tab_moe_compute_expert_tokens(const int32_t* sorted_experts, int64_t
 TAB_API int tab_moe_gating_top_k_softmax(const void* x, int dtype, int64_t tokens, int64_t num_experts, int64_t k, void* y,
                                  int32_t* expert_idx, int32_t* row_idx, tab_stream_t stream);
  /* npu_moe_gating_top_k (converter npu_moe_gating_top_k.py:4-22 -> MoeGatingTopK, experiment_ops.h:3722-3761):
-  * scores = softmax(x) (norm_type 0) or sigmoid(x) (1) in fp32; selection score = scores + bias; with group_count > 1 the
+  * scores = softmax(x) (norm_type 0 and 2) or sigmoid(x) (1) in fp32; selection score = scores + bias; with group_count > 1 the
   * experts form contiguous groups, each scored by its maximum (group_select_mode 0) or by the sum of its two largest
   * selection scores (1), and only the k_group best groups stay eligible; the k best eligible experts are taken (ties:
-  * lower id).  y [tokens, k] = the selected scores without bias, for sigmoid divided by (their sum + eps), times
+  * lower id).  y [tokens, k] = the selected scores without bias, for norm_type 1 and 2 divided by (their sum + eps), times
   * routed_scaling_factor; expert_idx int32 [tokens, k]; out fp32 [tokens, experts] = all scores (NULL to skip).
-  * num_experts <= 1024, k <= 32, group_count <= 32. */
+  * num_experts <= 1024, k <= 32, group_count <= 32.  norm_type 2 with no bias and one group is
+ * npu_moe_gating_top_k_softmax_v2 with renorm = 1 (converter npu_moe_gating_top_k_softmax_v2.py:9-23 ->
+ * MoeGatingTopKSoftmaxV2, experiment_ops.h:2243-2265); norm_type 0 is its renorm = 0, `out` its softmax_result. */
 TAB_API int tab_moe_gating_top_k(const void* x, const void* bias, int dtype, int64_t tokens, int64_t num_experts, int64_t k,
                          int64_t k_group, int64_t group_count, int group_select_mode, int norm_type,
                          float routed_scaling_factor, float eps, void* y, int32_t* expert_idx, float* out,

@@ -308,6 +308,23 @@ def moe_gating_top_k_softmax(x: torch.Tensor, k: int):
     return order.values[:, :k].to(x.dtype), order.indices[:, :k].to(torch.int32), row_idx.contiguous()
 
 
+def moe_gating_top_k_softmax_v2(x: torch.Tensor, k: int, renorm: int = 0, output_softmax: bool = False):
+    """MoeGatingTopKSoftmaxV2 without `finished` (converter npu_moe_gating_top_k_softmax_v2.py:9-23;
+    experiment_ops.h:2243-2265).  Decisions: renorm 0 -> y = the k largest softmax probabilities, softmax_result = the
+    fp32 softmax over all experts when asked for; renorm 1 -> the same k probabilities divided by their sum taken in
+    selection order (equal, up to rounding, to a softmax over the k largest logits).  Ties keep the lower expert id."""
+    p = torch.softmax(x.float(), dim=-1)
+    order = torch.sort(p, dim=-1, descending=True, stable=True)
+    y = order.values[:, :k]
+    if renorm:
+        ysum = torch.zeros(x.shape[0])
+        for j in range(k):
+            ysum = ysum + y[:, j]
+        y = y / ysum.unsqueeze(-1)
+    full = p if (output_softmax and not renorm) else torch.empty(0, dtype=torch.float32)
+    return y.to(x.dtype), order.indices[:, :k].to(torch.int32), full
+
+
 def moe_gating_top_k(x, k, bias=None, k_group=1, group_count=1, group_select_mode=0, norm_type=0, routed_scaling_factor=1.0,
                      eps=1e-20):
     """MoeGatingTopK (converter npu_moe_gating_top_k.py:4-22; experiment_ops.h:3722-3761).  Decisions: scores = softmax

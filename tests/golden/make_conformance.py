@@ -36,6 +36,7 @@ CONVERTER_FILES = {
     "npu_moe_distribute_dispatch_v2": "moe_distribute_dispatch_v2",
     "npu_moe_distribute_combine_v2": "moe_distribute_combine_v2",
     "npu_grouped_matmul_finalize_routing": "grouped_matmul_finalize_routing",
+    "npu_moe_gating_top_k_softmax_v2": "npu_moe_gating_top_k_softmax_v2",
 }
 
 

@@ -110,6 +110,10 @@ def test_meta_shape_rules():
     assert npu.npu_grouped_matmul_finalize_routing(xq, w, gl, output_bs=5, dtype=torch.float32).shape == (5, 96)
     with pytest.raises(RuntimeError, match="Not supported output dtype"):
         npu.npu_grouped_matmul_finalize_routing(xq, w, gl, dtype=torch.bfloat16)
+    lg = torch.empty(5, 16, dtype=torch.bfloat16, device=m)
+    yv, ev, sv = npu.npu_moe_gating_top_k_softmax_v2(lg, k=4, output_softmax=True)
+    assert yv.shape == (5, 4) and yv.dtype == torch.bfloat16 and ev.dtype == torch.int32 and sv.shape == (5, 16) and sv.dtype == torch.float32
+    assert npu.npu_moe_gating_top_k_softmax_v2(lg, k=4, renorm=1, output_softmax=True)[2].numel() == 0
     with pytest.raises(NotImplementedError):
         npu.npu_grouped_matmul([xq.to(torch.bfloat16)], [w], group_list=gl, split_item=2, group_type=0, output_dtype=15)
     hq, hs = npu.npu_grouped_matmul_swiglu_quant_v2(xq, [w], [torch.empty(4, 96, device=m)], torch.empty(16, device=m), gl)

@@ -682,9 +682,33 @@ def test_gating_top_k_group_limited(dev, E, groups, k_group, k, mode, norm):
     torch.testing.assert_close(sg.cpu(), sc, rtol=1e-5, atol=1e-7)
     torch.testing.assert_close(yg.cpu(), y, rtol=1e-5, atol=1e-7)
     with pytest.raises(NotImplementedError):
-        npu.npu_moe_gating_top_k(x.to(dev), k, renorm=1)
+        npu.npu_moe_gating_top_k(x.to(dev), k, renorm=1, norm_type=1)
     with pytest.raises(RuntimeError):
         npu.npu_moe_gating_top_k(x.to(dev), k, k_group=groups + 1, group_count=groups)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("renorm,full", [(0, True), (0, False), (1, False), (1, True)])
+def test_gating_top_k_softmax_v2(dev, dtype, renorm, full):
+    g = torch.Generator().manual_seed(17 + renorm)
+    T, E, k = 515, 256, 8
+    x = torch.randn(T, E, generator=g).to(dtype)
+    y, ei, sm = O.moe_gating_top_k_softmax_v2(x, k, renorm, full)
+    yg, eg, sg = npu.npu_moe_gating_top_k_softmax_v2(x.to(dev), k=k, renorm=renorm, output_softmax=full)
+    same = ei == eg.cpu()
+    if dtype == torch.float32:
+        assert bool(same.all()), "expert ids are index work: exact"
+    else:
+        assert float(same.float().mean()) > 0.999     # 16-bit logits repeat values: equal probabilities may swap
+    torch.testing.assert_close(yg.cpu().float(), y.float(), rtol=2e-2 if dtype != torch.float32 else 1e-5, atol=1e-7)
+    assert sg.shape == sm.shape and sg.dtype == torch.float32
+    if sm.numel():
+        torch.testing.assert_close(sg.cpu(), sm, rtol=1e-5, atol=1e-7)
+    if renorm:
+        torch.testing.assert_close(yg.float().sum(-1).cpu(), torch.ones(T), rtol=0, atol=2e-2 if dtype != torch.float32 else 1e-5)
+        # the renormalised form of the general gating operator is the same kernel path
+        y2, e2, _ = npu.npu_moe_gating_top_k(x.to(dev), k, renorm=1, norm_type=0, eps=0.0)
+        assert torch.equal(y2, yg) and torch.equal(e2, eg)
 
 
 def test_second_generation_dispatch_combine_names(dev):

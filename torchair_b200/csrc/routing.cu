@@ -883,7 +883,7 @@ __global__ void __launch_bounds__(128) gating_topk_kernel(const T* __restrict__ 
       sc[i] = e < E ? Elem<T>::to_f32(x[t * E + e]) : -INFINITY;
       m = fmaxf(m, sc[i]);
     }
-    if (norm_type == 0) {
+    if (norm_type != 1) {
       m = warp_max(m);
       float sum = 0.f;
 #pragma unroll
@@ -987,7 +987,7 @@ __global__ void __launch_bounds__(128) gating_topk_kernel(const T* __restrict__ 
     }
     if (lane < k) {
       float v = mine;
-      if (norm_type == 1) v = __fdiv_rn(v, __fadd_rn(ysum, eps));
+      if (norm_type != 0) v = __fdiv_rn(v, __fadd_rn(ysum, eps));   // sigmoid scores, or softmax renormalised over the k
       v = __fmul_rn(v, scaling);
       y[t * k + lane] = Elem<T>::from_f32(v);
       expert_idx[t * k + lane] = mine_e;
@@ -1007,8 +1007,8 @@ extern "C" int tab_moe_gating_top_k(const void* x, const void* bias, int dtype, 
   if (group_count < 1 || group_count > 32 || num_experts % group_count != 0 || k_group < 1 || k_group > group_count ||
       k > k_group * (num_experts / group_count))
     return fail(TAB_ERR_BAD_ARG, "gating_top_k: group_count=%lld k_group=%lld do not fit %lld experts and k=%lld", (long long)group_count, (long long)k_group, (long long)num_experts, (long long)k);
-  if ((group_select_mode != 0 && group_select_mode != 1) || (norm_type != 0 && norm_type != 1))
-    return fail(TAB_ERR_UNSUPPORTED, "gating_top_k: group_select_mode and norm_type must be 0 or 1");
+  if ((group_select_mode != 0 && group_select_mode != 1) || norm_type < 0 || norm_type > 2)
+    return fail(TAB_ERR_UNSUPPORTED, "gating_top_k: group_select_mode must be 0 or 1 and norm_type 0, 1 or 2");
   if (group_select_mode == 1 && num_experts / group_count < 2) return fail(TAB_ERR_BAD_ARG, "gating_top_k: top-2 group score needs groups of at least two experts");
   if (tokens == 0) return TAB_OK;
   if (!x || !y || !expert_idx) return fail(TAB_ERR_BAD_ARG, "gating_top_k: null pointer");

@@ -59,6 +59,8 @@ _npu.define("npu_grouped_matmul_finalize_routing(Tensor x, Tensor w, Tensor grou
             "int? scale_dtype=None, int? pertoken_scale_dtype=None) -> Tensor")
 _npu.define("npu_moe_compute_expert_tokens(Tensor sorted_experts, int num_experts) -> Tensor")
 _npu.define("npu_moe_gating_top_k_softmax(Tensor x, Tensor? finished=None, int k=1) -> (Tensor, Tensor, Tensor)")
+_npu.define("npu_moe_gating_top_k_softmax_v2(Tensor x, *, int k=1, Tensor? finished=None, int? renorm=0, bool? output_softmax=False) "
+            "-> (Tensor, Tensor, Tensor)")
 _npu.define("npu_moe_gating_top_k(Tensor x, int k, *, Tensor? bias=None, int k_group=1, int group_count=1, int group_select_mode=0, "
             "int renorm=0, int norm_type=0, bool out_flag=False, float routed_scaling_factor=1.0, float eps=1e-20) "
             "-> (Tensor, Tensor, Tensor)")
@@ -571,6 +573,27 @@ def _gating_cuda(x, finished=None, k=1):
     return y, ei, ri
 
 
+def _gating_v2_meta(x, *, k=1, finished=None, renorm=0, output_softmax=False):
+    if x.dim() != 2 or k < 1 or k > x.shape[1]:
+        raise RuntimeError("npu_moe_gating_top_k_softmax_v2: x must be [tokens, experts] and 1 <= k <= experts")
+    T, E = x.shape
+    full = bool(output_softmax) and not renorm        # the softmax over all experts exists only without renormalisation
+    return (x.new_empty((T, k)), torch.empty((T, k), dtype=torch.int32, device=x.device),
+            torch.empty((T, E) if full else (0,), dtype=torch.float32, device=x.device))
+
+
+def _gating_v2_cuda(x, *, k=1, finished=None, renorm=0, output_softmax=False):
+    op = "npu_moe_gating_top_k_softmax_v2"
+    y, ei, sm = _gating_v2_meta(x, k=k, renorm=renorm, output_softmax=output_softmax)
+    _only_none(op, finished=finished)
+    if (renorm or 0) not in (0, 1):
+        raise RuntimeError(f"{op}: renorm must be 0 or 1")
+    xc = x.contiguous()
+    _lib.call("tab_moe_gating_top_k", _ptr(xc), None, _st(x.dtype, op), x.shape[0], x.shape[1], k, 1, 1, 0, 2 if renorm else 0,
+              1.0, 0.0, _ptr(y), _ptr(ei), _ptr(sm) if sm.numel() else None, _stream(xc))
+    return y, ei, sm
+
+
 def _gating2_meta(x, k, *, bias=None, k_group=1, group_count=1, group_select_mode=0, renorm=0, norm_type=0, out_flag=False,
                   routed_scaling_factor=1.0, eps=1e-20):
     # shape rule of python/torchair/_contrib/custom_torch_ops/auto_register_custom_torch_ops.py:69-79
@@ -584,16 +607,16 @@ def _gating2_cuda(x, k, *, bias=None, k_group=1, group_count=1, group_select_mod
                   routed_scaling_factor=1.0, eps=1e-20):
     op = "npu_moe_gating_top_k"
     y, ei, out = _gating2_meta(x, k)
-    if renorm != 0:
-        raise NotImplementedError(f"{op}: renorm must be 0 (scores are normalised before the selection)")
+    if renorm not in (0, 1) or (renorm == 1 and norm_type != 0):
+        raise NotImplementedError(f"{op}: renorm must be 0, or 1 together with norm_type 0 (softmax renormalised over the k)")
     xc = x.contiguous()
     if bias is not None:
         if bias.dtype != x.dtype or bias.numel() != x.shape[1]:
             raise RuntimeError(f"{op}: bias must be [experts] of the dtype of x")
         bias = bias.contiguous()
     _lib.call("tab_moe_gating_top_k", _ptr(xc), _ptr(bias), _st(x.dtype, op), x.shape[0], x.shape[1], k, k_group, group_count,
-              int(group_select_mode), int(norm_type), float(routed_scaling_factor), float(eps), _ptr(y), _ptr(ei), _ptr(out),
-              _stream(xc))
+              int(group_select_mode), 2 if renorm == 1 else int(norm_type), float(routed_scaling_factor), float(eps), _ptr(y),
+              _ptr(ei), _ptr(out), _stream(xc))
     return y, ei, out
 
 
@@ -797,6 +820,7 @@ for _name, _meta, _cuda in (
         ("npu_moe_gating_top_k_softmax", _gating_meta, _gating_cuda),
         ("npu_moe_finalize_routing", _finalize_meta, _finalize_cuda),
         ("npu_moe_gating_top_k", _gating2_meta, _gating2_cuda),
+        ("npu_moe_gating_top_k_softmax_v2", _gating_v2_meta, _gating_v2_cuda),
         ("npu_moe_init_routing_v2", _irv2_meta, _irv2_cuda),
         ("npu_moe_distribute_dispatch", _dispatch_meta, _dispatch_cuda),
         ("npu_moe_distribute_combine", _combine_meta, _combine_cuda)):
@@ -813,4 +837,5 @@ OP_NAMES = ["npu_moe_init_routing", "npu_dynamic_quant", "npu_dynamic_quant_asym
             "npu_dequant_swiglu_quant", "npu_grouped_matmul", "npu_grouped_matmul_swiglu_quant_v2",
             "npu_moe_distribute_dispatch", "npu_moe_distribute_combine", "npu_moe_compute_expert_tokens",
             "npu_moe_gating_top_k_softmax", "npu_moe_finalize_routing", "npu_moe_init_routing_v2", "npu_moe_gating_top_k",
-            "npu_moe_distribute_dispatch_v2", "npu_moe_distribute_combine_v2", "npu_grouped_matmul_finalize_routing"]
+            "npu_moe_distribute_dispatch_v2", "npu_moe_distribute_combine_v2", "npu_grouped_matmul_finalize_routing",
+            "npu_moe_gating_top_k_softmax_v2"]
