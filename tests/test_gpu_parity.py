@@ -718,6 +718,13 @@ def test_second_generation_dispatch_combine_names(dev):
     b = npu.npu_moe_distribute_dispatch_v2(x.to(dev), ids.to(dev), "", 1, 0, cfg.E, quant_mode=2)
     for u, v in zip(a, b):
         assert torch.equal(u, v)
+    # y_dtype may restate the output type, comm_alg is a hint without effect; special experts are outside the path
+    c = npu.npu_moe_distribute_dispatch_v2(x.to(dev), ids.to(dev), "", 1, 0, cfg.E, quant_mode=2, y_dtype=1, comm_alg="fullmesh")
+    assert torch.equal(c[0], a[0])
+    with pytest.raises(NotImplementedError):
+        npu.npu_moe_distribute_dispatch_v2(x.to(dev), ids.to(dev), "", 1, 0, cfg.E, quant_mode=2, y_dtype=15)
+    with pytest.raises(NotImplementedError):
+        npu.npu_moe_distribute_dispatch_v2(x.to(dev), ids.to(dev), "", 1, 0, cfg.E, quant_mode=2, zero_expert_num=1)
     y = torch.randn(cfg.T * cfg.K, cfg.H, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16).to(dev)
     o1 = npu.npu_moe_distribute_combine(y, ids.to(dev), a[2], a[4], wt.to(dev), "", 1, 0, cfg.E)
     o2 = npu.npu_moe_distribute_combine_v2(y, ids.to(dev), b[2], b[4], wt.to(dev), "", 1, 0, cfg.E)

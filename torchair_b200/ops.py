@@ -632,15 +632,36 @@ def _v2_extras(op, **kw):
             raise NotImplementedError(f"{op}: `{name}` is outside the path and must be None")
 
 
+_comm_alg_seen = set()
+
+
+def _comm_alg_hint(op, comm_alg):
+    """comm_alg names one of the vendor's exchange algorithms.  Here the transport of the group decides how rows move
+    (register_ep_group), so the hint changes nothing; it is accepted and reported once per value."""
+    if not isinstance(comm_alg, str):
+        raise RuntimeError(f"{op}: comm_alg must be a string")
+    if comm_alg and comm_alg not in _comm_alg_seen:
+        _comm_alg_seen.add(comm_alg)
+        import logging
+        logging.getLogger("torchair").warning("%s: comm_alg=%r has no effect on B200; the group's transport moves the rows", op, comm_alg)
+
+
 def _dispatch_v2(impl):
     def fn(x, expert_ids, group_ep, ep_world_size, ep_rank_id, moe_expert_num, *, scales=None, x_active_mask=None,
            expert_scales=None, elastic_info=None, performance_info=None, group_tp="", tp_world_size=0, tp_rank_id=0,
            expert_shard_type=0, shared_expert_num=1, shared_expert_rank_num=0, quant_mode=0, global_bs=0,
            expert_token_nums_type=1, comm_alg="", zero_expert_num=0, copy_expert_num=0, const_expert_num=0, y_dtype=None,
            x_dtype=None, scales_dtype=None):
-        _v2_extras("npu_moe_distribute_dispatch_v2", elastic_info=elastic_info, performance_info=performance_info,
-                   comm_alg=comm_alg, zero_expert_num=zero_expert_num, copy_expert_num=copy_expert_num,
-                   const_expert_num=const_expert_num, y_dtype=y_dtype, x_dtype=x_dtype, scales_dtype=scales_dtype)
+        op = "npu_moe_distribute_dispatch_v2"
+        _v2_extras(op, elastic_info=elastic_info, performance_info=performance_info, zero_expert_num=zero_expert_num,
+                   copy_expert_num=copy_expert_num, const_expert_num=const_expert_num, x_dtype=x_dtype, scales_dtype=scales_dtype)
+        _comm_alg_hint(op, comm_alg)
+        if y_dtype is not None:
+            # the converter's rule (moe_distribute_dispatch_v2.py:60-64): int8 unless quant_mode is 0, then the dtype of x;
+            # y_dtype may restate that, it cannot ask for another element type here
+            want = 1 if quant_mode != 0 else _ST_INV.get(x.dtype)
+            if y_dtype != want:
+                raise NotImplementedError(f"{op}: y_dtype={y_dtype} differs from the output type of quant_mode={quant_mode} ({want})")
         return impl(x, expert_ids, group_ep, ep_world_size, ep_rank_id, moe_expert_num, scales=scales, x_active_mask=x_active_mask,
                     expert_scales=expert_scales, group_tp=group_tp, tp_world_size=tp_world_size, tp_rank_id=tp_rank_id,
                     expert_shard_type=expert_shard_type, shared_expert_num=shared_expert_num,
@@ -657,8 +678,8 @@ def _combine_v2(impl):
            global_bs=0, comm_quant_mode=0, comm_alg="", zero_expert_num=0, copy_expert_num=0, const_expert_num=0):
         _v2_extras("npu_moe_distribute_combine_v2", elastic_info=elastic_info, ori_x=ori_x, const_expert_alpha_1=const_expert_alpha_1,
                    const_expert_alpha_2=const_expert_alpha_2, const_expert_v=const_expert_v, performance_info=performance_info,
-                   comm_alg=comm_alg, zero_expert_num=zero_expert_num, copy_expert_num=copy_expert_num,
-                   const_expert_num=const_expert_num)
+                   zero_expert_num=zero_expert_num, copy_expert_num=copy_expert_num, const_expert_num=const_expert_num)
+        _comm_alg_hint("npu_moe_distribute_combine_v2", comm_alg)
         return impl(expand_x, expert_ids, assist_info_for_combine, ep_send_counts, expert_scales, group_ep, ep_world_size,
                     ep_rank_id, moe_expert_num, tp_send_counts=tp_send_counts, x_active_mask=x_active_mask,
                     expand_scales=expand_scales, shared_expert_x=shared_expert_x, group_tp=group_tp, tp_world_size=tp_world_size,
