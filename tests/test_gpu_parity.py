@@ -731,8 +731,10 @@ def test_second_generation_dispatch_combine_names(dev):
     assert torch.equal(o1, o2)
     with pytest.raises(NotImplementedError):
         npu.npu_moe_distribute_dispatch_v2(x.to(dev), ids.to(dev), "", 1, 0, cfg.E, quant_mode=2, zero_expert_num=1)
+    o3 = npu.npu_moe_distribute_combine_v2(y, ids.to(dev), b[2], b[4], wt.to(dev), "", 1, 0, cfg.E, comm_alg="fullmesh")
+    assert torch.equal(o1, o3)
     with pytest.raises(NotImplementedError):
-        npu.npu_moe_distribute_combine_v2(y, ids.to(dev), b[2], b[4], wt.to(dev), "", 1, 0, cfg.E, comm_alg="fullmesh")
+        npu.npu_moe_distribute_combine_v2(y, ids.to(dev), b[2], b[4], wt.to(dev), "", 1, 0, cfg.E, copy_expert_num=1)
 
 
 def test_full_size_prefill_layer_properties(dev):
