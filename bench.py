@@ -456,15 +456,15 @@ def gpu_arm(args):
         m32 = h32.shape[0]
         ones = torch.ones(m32, dtype=torch.float32, device=dev)
         table = {
-            "init_routing": (time_each(lambda: npu.npu_moe_init_routing(x_d, row_idx, ids_d, T), reps), 2 * T * H + 2 * M * H + 24 * M),
-            "dynamic_quant": (time_each(lambda: npu.npu_dynamic_quant(exb), reps), 2 * M * H + M * H + 4 * M),
-            "dispatch_pack(sort+quant+scatter)": (time_each(lambda: npu.npu_moe_distribute_dispatch(x_d, ids_d, "", 1, 0, E, quant_mode=2), reps),
+            "init_routing": (time_launches(lambda: npu.npu_moe_init_routing(x_d, row_idx, ids_d, T), reps), 2 * T * H + 2 * M * H + 24 * M),
+            "dynamic_quant": (time_launches(lambda: npu.npu_dynamic_quant(exb), reps), 2 * M * H + M * H + 4 * M),
+            "dispatch_pack(sort+quant+scatter)": (time_launches(lambda: npu.npu_moe_distribute_dispatch(x_d, ids_d, "", 1, 0, E, quant_mode=2), reps),
                                                   2 * T * H + M * H + 4 * M),
-            "swiglu_bf16": (time_each(lambda: npu.npu_swiglu(hb), reps), 2 * M * 2 * I + 2 * M * I),
-            "dequant_swiglu_quant": (time_each(lambda: npu.npu_dequant_swiglu_quant(h32, weight_scale=s1[:1], activation_scale=ones,
+            "swiglu_bf16": (time_launches(lambda: npu.npu_swiglu(hb), reps), 2 * M * 2 * I + 2 * M * I),
+            "dequant_swiglu_quant": (time_launches(lambda: npu.npu_dequant_swiglu_quant(h32, weight_scale=s1[:1], activation_scale=ones,
                                                                                    activate_left=True, quant_mode=1), reps),
                                      m32 * (8 * I + I + 8)),
-            "combine": (time_each(lambda: npu.npu_moe_distribute_combine(y_bf16, ids_d, expand_idx, ep_recv, wt_d, "", 1, 0, E), reps),
+            "combine": (time_launches(lambda: npu.npu_moe_distribute_combine(y_bf16, ids_d, expand_idx, ep_recv, wt_d, "", 1, 0, E), reps),
                         2 * M * H + 4 * M + 2 * T * H),
             "gmm_gate_up_fused": (ms_up, bytes_up), "gmm_down": (ms_down, bytes_down),
         }
@@ -472,12 +472,13 @@ def gpu_arm(args):
         tok_of_row = torch.arange(M, device=dev) % T          # K rows per token; which ones does not matter for the timing
         lg = torch.rand(M, device=dev)
         table["gmm_down+finalize_routing"] = (
-            time_each(lambda: npu.npu_grouped_matmul_finalize_routing(hq, w2, nums, scale=s2, pertoken_scale=hs, logit=lg,
+            time_launches(lambda: npu.npu_grouped_matmul_finalize_routing(hq, w2, nums, scale=s2, pertoken_scale=hs, logit=lg,
                                                                       row_index=tok_of_row, output_bs=T, group_list_type=1), reps),
             experts_hit * I * H + rows * I + 2 * rows * H * 4 + T * H * 4 + experts_hit * H * 4 + rows * 16)
         # context: what plain torch kernels reach on this GPU for write-only and copy traffic of 1 GiB
         probe = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
         probe2 = torch.empty_like(probe)
+        # (single eager calls: inside a graph a device-to-device copy_ becomes a copy-engine node, not the kernel)
         table["context: torch fill (write only)"] = (time_each(lambda: probe.fill_(1), reps), probe.numel())
         table["context: torch copy (read + write)"] = (time_each(lambda: probe2.copy_(probe), reps), 2 * probe.numel())
         report = {k: {"ms": round(ms, 4), "GB/s": gbs(b, ms), "frac_hbm": round(gbs(b, ms) / peak_gbs, 3)} for k, (ms, b) in table.items()}
