@@ -203,7 +203,7 @@ gmm_i8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
               const float ts = p.tok_scale ? p.tok_scale[row] : 1.f;
               const float gv = __fmul_rn(__fmul_rn(__int2float_rn(g[j]), ts), wg);
               const float uv = __fmul_rn(__fmul_rn(__int2float_rn(u[j]), ts), wu);
-              h = p.activate_left ? silu_mul(gv, uv) : silu_mul(uv, gv);
+              h = silu_mul(p.activate_left ? gv : uv, p.activate_left ? uv : gv);   // one SwiGLU, operands picked first
               if (cvalid) p.h_out[static_cast<int64_t>(row) * p.half + cg] = h;
               const float m = warp_max(cvalid ? fabsf(h) : 0.f);
               if (lane == 0) atomicMax(p.amax + row, __float_as_uint(m));

@@ -70,7 +70,7 @@ __device__ __forceinline__ void pf_narrow_epilogue(const GmmParams& p, const Wor
         const float ts = (tvalid && p.tok_scale) ? p.tok_scale[row] : 1.f;
         const float gv = __fmul_rn(__fmul_rn(__int2float_rn(g[j]), ts), wg);
         const float uv = __fmul_rn(__fmul_rn(__int2float_rn(u[j]), ts), wu);
-        const float h = p.activate_left ? silu_mul(gv, uv) : silu_mul(uv, gv);
+        const float h = silu_mul(p.activate_left ? gv : uv, p.activate_left ? uv : gv);
         if (tvalid) {
           if (cvalid) __stcs(p.h_out + static_cast<int64_t>(row) * p.half + ch, h);
           const float m = warp_max(cvalid ? fabsf(h) : 0.f);
@@ -282,7 +282,7 @@ gmm_i8_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
           for (int j = 0; j < 16; ++j) {
             const float gv = __fmul_rn(__fmul_rn(__int2float_rn(g[j]), ts), ws[c + j]);
             const float uv = __fmul_rn(__fmul_rn(__int2float_rn(u[j]), ts), ws[128 + c + j]);
-            h[j] = p.activate_left ? silu_mul(gv, uv) : silu_mul(uv, gv);
+            h[j] = silu_mul(p.activate_left ? gv : uv, p.activate_left ? uv : gv);   // one SwiGLU, operands picked first
           }
           if (rvalid) {
             if (cg0 + c + 16 <= p.half) {

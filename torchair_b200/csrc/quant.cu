@@ -140,7 +140,7 @@ __global__ void __launch_bounds__(THREADS) dequant_swiglu_quant_kernel(
           lv = __fmul_rn(lv, wl[k]);
           rv = __fmul_rn(rv, wr[k]);
         }
-        o[k] = activate_left ? silu_mul(lv, rv) : silu_mul(rv, lv);
+        o[k] = silu_mul(activate_left ? lv : rv, activate_left ? rv : lv);   // one SwiGLU, operands picked first
       }
     };
     float h[kDsqChunks][8];
