@@ -153,6 +153,7 @@ def test_exchange_plan_and_rows_bit_exact(dev, R, E_l, slot):
 GMM_SHAPES = [  # M, Kd, N, E
     (128, 1024, 1024, 8), (64, 512, 256, 4), (700, 1024, 384, 3), (2048, 2048, 512, 64), (5, 64, 128, 2),
     (1000, 1536, 640, 2), (33, 7168, 256, 16), (4096, 256, 128, 1),
+    (40, 144, 72, 3), (300, 80, 200, 2),      # K ends inside a 128-byte block (zero-filled by TMA), channels not a multiple of 8
 ]
 
 
