@@ -46,7 +46,7 @@ __global__ void ep_signal_kernel(unsigned long long* const* __restrict__ peer_fl
 }
 
 // Waits until every source's flag has reached the expected sequence number.  pre_increment = 1: expect counter + 1
-// (new data); 0: expect the current counter (acknowledgement of the previous round).  The counter advances either way.
+// (new data); 0: expect the current counter (acknowledgement of the previous exchange).  The counter advances either way.
 __global__ void ep_wait_kernel(const unsigned long long* __restrict__ flags, unsigned long long* counter, int R,
                                int pre_increment, int* status, int code) {
   __shared__ int s_fail;
