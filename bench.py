@@ -200,7 +200,7 @@ def gpu_arm(args):
     import torch
     import torch.distributed as dist
     import torchair_b200
-    from torchair_b200 import ep, ops
+    from torchair_b200 import ep
     from torchair_b200.layer import moe_layer
     from oracle import moe_oracle as O
 

@@ -25,7 +25,6 @@ Reference anchors (paths inside the reference project):
 """
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass
 from typing import List, Optional, Sequence, Tuple
 

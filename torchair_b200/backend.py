@@ -68,7 +68,7 @@ def fuse_gate_up(gm: torch.fx.GraphModule) -> int:
 
     The reference does the same kind of rewrite with inductor pattern passes (python/torchair/patterns/*.py).
     """
-    from . import ops
+    from . import ops  # noqa: F401  (the operators must be registered before their overloads are looked up)
     import operator
     gmm_ops = (torch.ops.npu.npu_grouped_matmul.default, torch.ops.npu.npu_grouped_matmul.List)
     fused = 0

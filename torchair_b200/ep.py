@@ -19,7 +19,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, List, Tuple
 
 import torch
 import torch.distributed as dist

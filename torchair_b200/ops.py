@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import ctypes
 import weakref
-from typing import List, Optional
+from typing import Optional
 
 import torch
 from torch.library import Library
