@@ -48,7 +48,7 @@ def _worker(rank, world, port, cfg_name, nums_type, q, outdir):
         q.put((rank, "error", traceback.format_exc()))
 
 
-@pytest.mark.parametrize("world,nums_type", [(2, 1), (2, 0), (4, 1)])
+@pytest.mark.parametrize("world,nums_type", [(2, 1), (2, 0), (4, 1), (8, 1)])
 def test_expert_parallel_layer_over_gloo_matches_oracle(world, nums_type, tmp_path):
     cfg = O.CONFIGS["cfg0"]
     ctx = mp.get_context("spawn")
