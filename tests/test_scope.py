@@ -139,3 +139,35 @@ def test_eager_behaviour_and_module_alias():
         import torchair.scope as ts
         assert ts.npu_stream_switch is scope.npu_stream_switch
     assert not scope.uses_scopes(torch.fx.symbolic_trace(torch.nn.ReLU()))
+
+
+def test_two_parallel_streams_as_in_the_reference_scope_test():
+    """Shape of tests/st/torchair_scope_st.py:82-141: two stream scopes with their own priorities around independent work;
+    the wait's result may even be dropped by the caller (then it orders nothing, as an unused value orders nothing in the
+    reference's graph either) and the graph must still build and run."""
+    def model(in1, in2, in3, in4):
+        add_result = torch.add(in1, in2)
+        with scope.npu_stream_switch('1', 2):
+            scope.npu_wait_tensor(in4, add_result)
+            mm_result = torch.mm(in3, in4)
+        mm1 = torch.mm(in3, in4)
+        with scope.npu_stream_switch('2', 3, False):
+            in4b = scope.npu_wait_tensor(in4, mm_result)
+            add2 = torch.add(in3, in4b)
+        return add_result, mm_result, mm1, add2
+
+    rec, graphs = Recorder(), []
+    a = [torch.randn(4, 4) for _ in range(4)]
+    got = _compile(model, rec, graphs)(*a)
+    want = (a[0] + a[1], a[2] @ a[3], a[2] @ a[3], a[2] + a[3])
+    for g, w in zip(got, want):
+        torch.testing.assert_close(g, w)
+    labels, priorities = scope.stream_plan(graphs[0])
+    by_target = {}
+    for n, l in labels.items():
+        if n.op == "call_function" and not str(n.target).startswith("air."):
+            by_target.setdefault(str(n.target), []).append(l)
+    assert by_target["aten.mm.default"] == ['1', None] and by_target["aten.add.Tensor"] == [None, '2']
+    assert priorities == {'1': 2, '2': 3}
+    # stream '2' consumes mm_result of stream '1' through the kept wait: it must wait on an event recorded on '1'
+    assert ("wait", "2", "1") in rec.log
