@@ -277,3 +277,19 @@ def test_fx_pass_fuses_down_matmul_with_combine_only_over_peer_memory():
     assert fuse_down_combine(make_fx(make("fx_nccl", R))(*args)) == 0          # NCCL transport: rows are sent by the collective
     assert fuse_down_combine(make_fx(make("fx_peer", 1))(*args[:5], *args[5:])) == 0   # one rank: nothing to send
     assert fuse_down_combine(make_fx(make("fx_peer", R, keep_rows=True))(*args)) == 0   # the rows escape: must stay
+
+
+def test_remaining_public_names_of_the_reference_exist():
+    """python/torchair/__init__.py:1-3 lists the package's public names.  Those beside the path either do their B200
+    counterpart (use_internal_format_weight, patch_for_hcom) or say that they are outside it."""
+    import torchair_b200 as tb
+    for name in ("get_compiler", "get_npu_backend", "dynamo_export", "CompilerConfig", "use_internal_format_weight", "logger",
+                 "register_fx_node_ge_converter", "patch_for_hcom", "register_replacement", "npu_format_cast_via_cpu"):
+        assert hasattr(tb, name), name
+    tb.patch_for_hcom()
+    model = torch.nn.Linear(4, 4)
+    model.register_buffer("experts", torch.zeros(2, 4, 4, dtype=torch.int8))
+    assert tb.use_internal_format_weight(model) is None          # CPU tensors are left alone
+    for fn in (tb.dynamo_export, tb.register_replacement, tb.npu_format_cast_via_cpu):
+        with pytest.raises(NotImplementedError, match="outside the W8A8 MoE path"):
+            fn(model)

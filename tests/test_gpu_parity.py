@@ -209,6 +209,22 @@ def test_grouped_matmul_skewed_and_empty_groups(dev):
     assert zero.shape == (M, N)
 
 
+def test_use_internal_format_weight_packs_expert_weights_ahead_of_the_first_run(dev):
+    from torchair_b200 import ops
+    ops.clear_weight_cache()
+    m = torch.nn.Module()
+    m.register_buffer("w1", torch.randint(-127, 128, (2, 64, 128), dtype=torch.int8, device=dev))
+    m.register_buffer("other", torch.zeros(3, 3, device=dev))
+    before = len(ops._packed_cache)
+    torchair_b200.use_internal_format_weight(m)
+    assert len(ops._packed_cache) == before + 1
+    x = torch.randint(-127, 128, (16, 64), dtype=torch.int8, device=dev)
+    cnt = torch.tensor([10, 6], device=dev)
+    y = npu.npu_grouped_matmul([x], [m.w1], group_list=cnt, split_item=2, group_type=0, group_list_type=1, output_dtype=3)[0]
+    assert len(ops._packed_cache) == before + 1                  # the GEMM found the packed form
+    assert torch.equal(y.cpu(), O.grouped_matmul_w8a8(x.cpu(), m.w1.cpu(), None, None, cnt.cpu(), 1, 3))
+
+
 def test_packed_weight_cache_follows_storage_lifetime_and_version(dev):
     g = torch.Generator().manual_seed(5)
     x = torch.randint(-127, 128, (64, 256), generator=g, dtype=torch.int8).to(dev)

@@ -19,7 +19,42 @@ from . import scope
 from .ops import clear_weight_cache, gmm_status
 
 __all__ = ["get_npu_backend", "get_compiler", "CompilerConfig", "register_fx_node_ge_converter", "logger",
-           "register_ep_group", "install_as_torchair", "clear_weight_cache", "gmm_status", "scope"]
+           "register_ep_group", "install_as_torchair", "clear_weight_cache", "gmm_status", "scope",
+           "use_internal_format_weight", "patch_for_hcom", "dynamo_export", "register_replacement", "npu_format_cast_via_cpu"]
+
+
+def use_internal_format_weight(model) -> None:
+    """The reference casts a model's weights to the vendor's internal layout ahead of the first run
+    (python/torchair/experimental/inference.py:99-110).  Here the counterpart is the one-off relayout of every int8
+    [E, K, N] expert weight (parameter or buffer on a GPU) into the K-major packed form the grouped GEMM reads, so that
+    the first forward, or a CUDA-graph capture, does not pay for it."""
+    import torch
+    done = 0
+    for t in list(model.parameters()) + list(model.buffers()):
+        if t.is_cuda and t.dtype == torch.int8 and t.dim() == 3:
+            ops.packed_weight(t)
+            done += 1
+    logger.info("use_internal_format_weight: %d expert weight tensors packed", done)
+
+
+def patch_for_hcom() -> None:
+    """Kept for scripts that call it (python/torchair/__init__.py:53-70 patches torch.distributed for old PyTorch versions
+    on Ascend).  Nothing needs patching here: collectives of a compiled graph run through torch.distributed as they are."""
+    logger.info("patch_for_hcom: nothing to patch on this backend")
+
+
+def _outside_the_path(name):
+    def stub(*args, **kwargs):
+        raise NotImplementedError(f"torchair.{name} drives the Ascend graph compiler and is outside the W8A8 MoE path "
+                                  "this package implements")
+    stub.__name__ = name
+    stub.__doc__ = f"``torchair.{name}`` of the reference's public API; not part of the W8A8 MoE path: raises NotImplementedError."
+    return stub
+
+
+dynamo_export = _outside_the_path("dynamo_export")
+register_replacement = _outside_the_path("register_replacement")
+npu_format_cast_via_cpu = _outside_the_path("npu_format_cast_via_cpu")
 
 
 def install_as_torchair() -> None:
