@@ -303,6 +303,11 @@ def packed_weight(weight: torch.Tensor) -> torch.Tensor:
     E, Kd, N = w.shape
     out = torch.empty((E, N, Kd), dtype=torch.int8, device=w.device)
     _lib.call("tab_prepack_weight_i8", _ptr(w), E, Kd, N, _ptr(out), _stream(w))
+    if w.is_cuda and torch.cuda.is_current_stream_capturing():
+        # first use inside a CUDA-graph capture: the relayout becomes part of that graph and its result lives in the graph's
+        # pool, valid only after a replay, so it must not serve later eager calls (pack ahead with
+        # use_internal_format_weight, or run once eagerly, to keep the relayout out of the graph)
+        return out
     if hit is None:
         weakref.finalize(storage, _packed_cache.pop, ident, None)
     _packed_cache[ident] = (weight._version, out)
