@@ -51,6 +51,11 @@ enum tab_dtype { TAB_I8 = 1, TAB_I32 = 3, TAB_I64 = 4, TAB_F16 = 5, TAB_F32 = 6,
  * `_torchair` (torchair/core/npu_wrapper.cpp:28-84). */
 TAB_API int tab_version(void);
 
+/* Number of kernels this library has enqueued so far in this process, over all devices and streams (a launch
+ * recorded into a CUDA graph during capture counts once, its replays do not pass through the library).  For
+ * accounting in benchmarks; no counterpart in the reference. */
+TAB_API long long tab_launch_count(void);
+
 /* Message of the calling thread's last failing call.  Stands in for tng::Status -> RuntimeError
  * (torchair/core/torchair.cpp:98-120). */
 TAB_API const char* tab_last_error(void);
@@ -93,6 +98,14 @@ TAB_API int tab_moe_init_routing(const void* x, int x_dtype, const int32_t* row_
                          int64_t T, int64_t K, int64_t H, int64_t active_num, int64_t expert_bound,
                          void* expanded_x, int32_t* expanded_row_idx, int32_t* expanded_expert_idx,
                          void* workspace, size_t workspace_bytes, tab_stream_t stream);
+
+/* tab_routing_status: host-side; synchronises `stream`, copies the routing kernels' device status word to
+ * *status_host and clears it.  Bit 0: an expert id outside [0, bound) reached a sort (tab_moe_init_routing,
+ * tab_moe_init_routing_static, tab_moe_dispatch_pack, tab_moe_init_routing_v2) and was clamped to the nearest valid
+ * id; bit 1: a row_idx value outside [0, T*K) was skipped.  Neither accesses memory out of range; a non-zero word
+ * returns TAB_ERR_BAD_ARG with a message.  The reference's IR prototype (MoeInitRouting,
+ * experiment_ops.h:2111-2134) states no behaviour for ids out of range; this library clamps and reports. */
+TAB_API int tab_routing_status(int* status_host, tab_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------
  * tab_moe_init_routing_static: npu_moe_init_routing for callers that cannot hand over scratch memory.
@@ -166,15 +179,19 @@ TAB_API int tab_moe_exchange_rows(const void* src, const float* src_scales, cons
  *                      counter += 1; on expiry writes `code` into *status (device int) and continues.
  *   tab_ep_send_rows   sender: row p of the expert-sorted rows goes to rank d = owner of its expert, slot
  *                      [my_rank][p - first row of d]; per-expert counts go to peer_counts; expand_idx_slot[f]
- *                      = d*slot_rows + offset is the position at which the combined row comes back.
+ *                      = d*slot_rows + offset is the position at which the combined row comes back.  A row whose
+ *                      offset does not fit the slot (counts and slot_rows disagree) is not sent; `code` is then
+ *                      written to the device word `status` (the word tab_ep_wait reports into).
  *   tab_ep_unpack_rows receiver: slot records -> rows in (local expert, source) order + scales; `plan` from
  *                      tab_moe_exchange_plan(counts, R, E_l, slot_rows, ...).
  *   tab_ep_return_rows expert side of combine: outputs go back to slot [my_rank][send offset] of the source
  *                      rank's `ret` buffer; the source then runs tab_moe_combine on its ret buffer with
  *                      expand_idx_slot.
  *   tab_ep_return_plan the addresses tab_ep_return_rows would copy to, one per expert-output row (0 past the
- *                      total), as the row table of tab_grouped_matmul_w8a8_scatter: the down GEMM then stores
- *                      its rows into the source ranks' `ret` buffers itself and no copy kernel runs.
+ *                      total and for a row whose offset does not fit its slot), as the row table of
+ *                      tab_grouped_matmul_w8a8_scatter: the down GEMM then stores its rows into the source ranks'
+ *                      `ret` buffers itself and no copy kernel runs.
+ * Every flag wait is bounded (TAB_EP_WAIT_MS in the environment, read once; default 2000 ms).
  * ------------------------------------------------------------------------------------------------- */
 TAB_API int tab_ep_signal(void* const* peer_flags, void* counter, int64_t R, tab_stream_t stream);
 TAB_API int tab_ep_wait(const void* flags, void* counter, int64_t R, int pre_increment, int* status, int code,
@@ -182,7 +199,7 @@ TAB_API int tab_ep_wait(const void* flags, void* counter, int64_t R, int pre_inc
 TAB_API int tab_ep_send_rows(const void* rows, const float* scales, const int32_t* expert_counts,
                      const int32_t* expand_idx, int64_t R, int64_t E_l, int64_t slot_rows, int64_t row_bytes,
                      int64_t M, int64_t my_rank, void* const* peer_recv, void* const* peer_counts,
-                     int32_t* expand_idx_slot, tab_stream_t stream);
+                     int32_t* expand_idx_slot, int* status, int code, tab_stream_t stream);
 TAB_API int tab_ep_unpack_rows(const void* recv, const int32_t* plan, int64_t R, int64_t E_l, int64_t row_bytes,
                        int64_t dst_rows, int zero_fill, void* dst, float* dst_scales, tab_stream_t stream);
 TAB_API int tab_ep_return_rows(const void* y, const int32_t* plan, int64_t R, int64_t E_l, int64_t slot_rows,
@@ -270,7 +287,8 @@ TAB_API int tab_moe_init_routing_v2(const void* x, int x_dtype, const int32_t* e
  *   address row_dst[m] (device array of M addresses, 16-byte aligned rows of N elements) instead of y + m*N.  The
  *   addresses may lie in peer-mapped memory of another GPU: with tab_ep_return_plan this is the down projection of
  *   npu_grouped_matmul fused with the row return of npu_moe_distribute_combine (moe_distribute_combine.py:4-60),
- *   each tile leaving over NVLink as its epilogue finishes.  Rows outside every group are not stored.  N % 8 == 0.
+ *   each tile leaving over NVLink as its epilogue finishes.  Rows outside every group, and rows whose table entry
+ *   is 0, are not stored.  N % 8 == 0.
  *
  * tab_grouped_matmul_swiglu_quant: gate_up GEMM with the DequantSwigluQuant epilogue fused
  *   (grouped_matmul.py:210-365 followed by npu_dequant_swiglu_quant.py:5-64; the reference's own fused
@@ -288,8 +306,12 @@ TAB_API int tab_moe_init_routing_v2(const void* x, int x_dtype, const int32_t* e
  *   The additions into one output row are 16-byte L2 reductions in no fixed order.  Requires N % 4 == 0;
  *   the workspace holds the int32 accumulators.
  *
- * tab_gmm_status: host-side; copies the device status word of the last GEMM launches on this device
- *   (0 = fine, otherwise the code of the bounded wait that gave up) after synchronising `stream`.
+ * tab_gmm_status: host-side; copies the device status word of the GEMM launches on this device
+ *   (0 = fine, otherwise the code of the first bounded wait that gave up) after synchronising `stream`.  The word is
+ *   sticky; tab_gmm_status_reset (host-side, synchronises `stream`) clears it.  Every wait inside the kernels is
+ *   bounded (TAB_GMM_WAIT_MS in the environment, read once; default 2000 ms): on expiry the CTA records its code,
+ *   drains its copies, frees its tensor memory and returns with its tiles unwritten, so callers that need to know
+ *   poll this word where they synchronise anyway.
  * ------------------------------------------------------------------------------------------------- */
 TAB_API int tab_prepack_weight_i8(const int8_t* weight, int64_t E, int64_t Kd, int64_t N, int8_t* packed,
                           tab_stream_t stream);
@@ -316,6 +338,7 @@ TAB_API int tab_grouped_matmul_finalize_routing(const int8_t* x, const int8_t* p
                                         int row_index_dtype, int64_t output_bs, float* y, void* workspace,
                                         size_t workspace_bytes, tab_stream_t stream);
 TAB_API int tab_gmm_status(int* status_host, tab_stream_t stream);
+TAB_API int tab_gmm_status_reset(tab_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -109,12 +109,113 @@ def dynamic_quant(x: torch.Tensor, smooth_scales: Optional[torch.Tensor] = None)
 
 
 # --------------------------------------------------------------------------------------------------
+# SwiGLU arithmetic: silu(a) * b with a deterministic exp
+# --------------------------------------------------------------------------------------------------
+# Decision: silu(a) * b = RN(RN(a / (1 + e)) * b), e = exp(-a) by a fixed sequence of correctly rounded fp32 operations
+# (the same sequence as oracle/silu_exact.c and the CUDA kernels), so that CPU and GPU agree bit for bit.  A libm exp
+# (what F.silu calls) differs between CPU and GPU in the last place, which would move int8 values after SwiGLU by one
+# step at rounding ties.  SILU_IMPL = "libm" selects F.silu instead: the literal eager-torch formula, used by the timed
+# CPU baseline and by the test that bounds the distance between the two forms (a few ulp).
+SILU_IMPL = "exact"
+
+_LOG2E = 1.4426950216293335          # RN32(log2(e)) = 0x1.715476p+0
+_MAGIC = 12582912.0                  # 1.5 * 2^23
+# 2^f on [-0.5, 0.5], degree 6 (c0..c6), fp32 values
+_EXP2_COEF = (1.0, 0.6931471824645996, 0.24022646248340607, 0.05550328642129898, 0.009618489071726799,
+              0.0013399930903688073, 0.0001534581242594868)
+
+
+def _fma32(a: torch.Tensor, b, c) -> torch.Tensor:
+    """Correctly rounded fp32 fused multiply-add RN32(a*b + c) of fp32 tensors (b, c may be Python floats that are fp32
+    values).  The product is exact in fp64; the fp64 sum is rounded to odd (TwoSum gives the exact error; an inexact sum
+    with an even last bit moves to its odd neighbour on the side of the error), after which rounding to fp32 cannot be
+    a double rounding (53 >= 2*24 + 2 bits)."""
+    a64 = a.double()
+    b64 = b.double() if isinstance(b, torch.Tensor) else torch.tensor(b, dtype=torch.float64)
+    c64 = c.double() if isinstance(c, torch.Tensor) else torch.tensor(c, dtype=torch.float64)
+    p = a64 * b64
+    s = p + c64
+    bb = s - p
+    err = (p - (s - bb)) + (c64 - bb)
+    even = (s.view(torch.int64) & 1) == 0
+    toward = torch.where(err > 0, torch.full_like(s, float("inf")), torch.full_like(s, float("-inf")))
+    s = torch.where((err != 0) & even, torch.nextafter(s, toward), s)
+    return s.float()
+
+
+def _silu_mul_exact_torch(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """oracle/silu_exact.c op for op, in torch (fp32 tensors in, fp32 out)."""
+    x = torch.fmin(torch.fmax(-a, torch.tensor(-80.0)), torch.tensor(80.0))
+    nm = _fma32(x, _LOG2E, _MAGIC)
+    n = nm - torch.tensor(_MAGIC, dtype=torch.float32)
+    f = _fma32(x, _LOG2E, -n)
+    p = torch.full_like(f, _EXP2_COEF[6])
+    for c in _EXP2_COEF[5::-1]:
+        p = _fma32(p, f, c)
+    e = (p.view(torch.int32) + (n.to(torch.int32) << 23)).view(torch.float32)
+    d = 1.0 + e
+    return (a / d) * b
+
+
+_silu_lib = None
+
+
+def _load_silu_lib():
+    """oracle/_build/libsilu_exact.so (gcc build of oracle/silu_exact.c) when it exists or can be built; else None."""
+    global _silu_lib
+    if _silu_lib is None:
+        import ctypes
+        import os
+        import subprocess
+        here = os.path.dirname(os.path.abspath(__file__))
+        so = os.path.join(here, "_build", "libsilu_exact.so")
+        src = os.path.join(here, "silu_exact.c")
+        try:
+            if not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(src):
+                os.makedirs(os.path.dirname(so), exist_ok=True)
+                subprocess.run(["gcc", "-O2", "-fPIC", "-shared", "-fopenmp", "-ffp-contract=off", src, "-o", so, "-lm"],
+                               check=True, capture_output=True)
+            lib = ctypes.CDLL(so)
+            lib.tab_oracle_silu_mul.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64]
+            lib.tab_oracle_silu_mul.restype = None
+            _silu_lib = lib
+        except (OSError, subprocess.CalledProcessError):
+            _silu_lib = False
+    return _silu_lib or None
+
+
+def build_c_oracle() -> bool:
+    """Compiles the C restatement (called by the build step); True when the library is usable."""
+    return _load_silu_lib() is not None
+
+
+def silu_mul(a: torch.Tensor, b: torch.Tensor, impl: Optional[str] = None) -> torch.Tensor:
+    """silu(a) * b on fp32 tensors.  impl: "exact" (C when built, else the torch restatement of the same operations),
+    "exact_torch", or "libm" (F.silu); default SILU_IMPL."""
+    impl = impl or SILU_IMPL
+    a, b = a.float(), b.float()
+    if impl == "libm":
+        return F.silu(a) * b
+    if impl == "exact":
+        lib = _load_silu_lib()
+        if lib is not None:
+            a, b = torch.broadcast_tensors(a, b)
+            a, b = a.contiguous(), b.contiguous()
+            out = torch.empty_like(a)
+            lib.tab_oracle_silu_mul(a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel())
+            return out
+    elif impl != "exact_torch":
+        raise ValueError(f"unknown SwiGLU implementation {impl!r}")
+    return _silu_mul_exact_torch(a, b)
+
+
+# --------------------------------------------------------------------------------------------------
 # npu_swiglu
 # --------------------------------------------------------------------------------------------------
 def swiglu(x: torch.Tensor, dim: int = -1) -> torch.Tensor:
     """SwiGlu (converter npu_swiglu.py:8-14): a, b = halves of x along dim; y = silu(a)*b in fp32, cast back."""
     a, b = torch.chunk(x.float(), 2, dim=dim)
-    return (F.silu(a) * b).to(x.dtype)
+    return silu_mul(a, b).to(x.dtype)
 
 
 # --------------------------------------------------------------------------------------------------
@@ -247,7 +348,7 @@ def dequant_swiglu_f32(x: torch.Tensor, weight_scale: Optional[torch.Tensor], ac
             vv[:valid] = v[:valid] * ws[gid]
             v = vv
     left, right = torch.chunk(v, 2, dim=-1)
-    h = F.silu(left) * right if activate_left else F.silu(right) * left
+    h = silu_mul(left, right) if activate_left else silu_mul(right, left)
     if group_index is not None:
         valid = int(group_bounds(group_index, 1)[1].clamp(min=0).sum())
         h[valid:] = 0

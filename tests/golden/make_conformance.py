@@ -17,7 +17,7 @@ import types
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("REFERENCE_ROOT", "")     # checkout of the reference project; nothing is assumed when unset
 
 CONVERTER_FILES = {
     "npu_moe_init_routing": "moe_init_routing",
@@ -77,6 +77,8 @@ def describe(fn):
 
 
 def collect():
+    if not REF or not os.path.isdir(os.path.join(REF, "python", "torchair")):
+        raise RuntimeError("set REFERENCE_ROOT to a checkout of the reference project")
     sys.path.insert(0, ROOT)
     import torch
     import torchair_b200  # noqa: F401  defines torch.ops.npu.* first

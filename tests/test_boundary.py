@@ -164,8 +164,9 @@ def test_schemas_match_the_reference_converters():
     assert snap["_api"]["CompilerConfig_modes"] == list(torchair_b200.CompilerConfig.MODES)
 
 
-@pytest.mark.skipif(not os.path.isdir(os.path.join(os.environ.get("REFERENCE_ROOT", "/root/reference"), "python", "torchair")),
-                    reason="reference checkout not present")
+@pytest.mark.skipif(not os.environ.get("REFERENCE_ROOT") or
+                    not os.path.isdir(os.path.join(os.environ["REFERENCE_ROOT"], "python", "torchair")),
+                    reason="REFERENCE_ROOT does not point at a checkout of the reference")
 def test_conformance_snapshot_is_fresh():
     import subprocess, sys
     code = ("import json,sys; sys.path.insert(0, %r); from tests.golden.make_conformance import collect; "

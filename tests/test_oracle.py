@@ -238,3 +238,76 @@ def test_grouped_matmul_finalize_routing_known_answer_and_composition():
         full[s:s + c] = (O.int8_matmul(xq[s:s + c], wq[e]).float() * pts[s:s + c, None]) * sc[e][None]
     want = torch.zeros(M // K, N).index_add_(0, tok, full * lg[:, None])
     torch.testing.assert_close(got, want, rtol=1e-6, atol=1e-6)
+
+
+# ---------------------------------------------------------------------------------------------------
+# deterministic SwiGLU arithmetic
+# ---------------------------------------------------------------------------------------------------
+def _silu_inputs():
+    g = torch.Generator().manual_seed(5)
+    a = torch.cat([torch.randn(300_000, generator=g) * 5, torch.randn(50_000, generator=g) * 40, torch.linspace(-90, 90, 20001),
+                   torch.tensor([0.0, -0.0, 80.0, -80.0, 81.0, -81.0, 1e4, -1e4, 1e-30, -1e-30, 0.34657359, -0.34657359])])
+    b = torch.randn(a.numel(), generator=g)
+    return a, b
+
+
+def test_fma_emulation_is_correctly_rounded_on_hard_cases():
+    """RN32(a*b + c) through fp64 with round-to-odd, checked against exact rational arithmetic; the first case is one
+    where plain fp64 arithmetic double-rounds (the fp64 sum lands exactly on an fp32 tie that the true sum misses)."""
+    import fractions
+    u = 2.0 ** -23
+    a = torch.tensor([2.0 ** -24 * (1 + u), 1.0 + u, 1.0 + u, 3.0, 1.0, -5.5], dtype=torch.float32)
+    b = torch.tensor([1.0 - u, 1.0 + u, 1.0 - u, 1.0 / 3.0, 2.0 ** -24, 1.4426950216293335], dtype=torch.float32)
+    c = torch.tensor([1.0 + u, 2.0 ** -70, -(2.0 ** -60), 2.0 ** -80, 1.0, 12582912.0], dtype=torch.float32)
+    got = O._fma32(a, b, c)
+    for i in range(a.numel()):
+        exact = fractions.Fraction(float(a[i])) * fractions.Fraction(float(b[i])) + fractions.Fraction(float(c[i]))
+        lo = torch.nextafter(got[i], torch.tensor(-float("inf")))
+        hi = torch.nextafter(got[i], torch.tensor(float("inf")))
+        d = abs(fractions.Fraction(float(got[i])) - exact)
+        assert d <= abs(fractions.Fraction(float(lo)) - exact) and d <= abs(fractions.Fraction(float(hi)) - exact)
+    assert float(got[0]) == 1.0 + u
+    naive = (a[:1].double() * b[:1].double() + c[:1].double()).float()
+    assert float(naive[0]) == 1.0 + 2 * u, "the first case is meant to be one that plain fp64 arithmetic gets wrong"
+    assert float(got[4]) == 1.0                      # an exact tie rounds to even
+
+
+def test_c_and_torch_restatements_of_the_swiglu_arithmetic_agree_bit_for_bit():
+    if not O.build_c_oracle():
+        pytest.skip("gcc is not available to build oracle/silu_exact.c")
+    a, b = _silu_inputs()
+    c = O.silu_mul(a, b, "exact")
+    t = O.silu_mul(a, b, "exact_torch")
+    assert torch.equal(c.view(torch.int32), t.view(torch.int32))
+
+
+def test_deterministic_swiglu_stays_within_a_few_ulp_of_the_libm_formula():
+    a, b = _silu_inputs()
+    exact = O.silu_mul(a, b, "exact_torch")
+    ref = a.double() / (1 + torch.exp(-a.double())) * b.double()
+    near = a.abs() <= 20
+    rel = (exact.double() - ref).abs() / ref.abs().clamp_min(1e-300)
+    assert float(rel[near & (ref.abs() > 1e-30)].max()) < 6e-7
+    libm = O.silu_mul(a, b, "libm")
+    ulps = (exact.view(torch.int32) - libm.view(torch.int32)).abs()
+    assert int(ulps[near].max()) <= 8 and float((ulps[near] > 2).float().mean()) < 0.03
+    # far out the cap takes over: results are exactly a*b (1 + e == 1) or below 1e-30 in magnitude
+    big = a >= 81
+    assert torch.equal(exact[big], (a * b)[big])
+    assert float(exact[a <= -81].abs().max()) < 1e-30 * float(b.abs().max()) * 1e4
+
+
+def test_quantised_layer_barely_moves_between_the_two_swiglu_forms():
+    cfg = O.CONFIGS["cfg0"]
+    w = O.make_weights(cfg, 0)
+    x, ids, wt = O.make_tokens(cfg, 0)
+    a, b = [], []
+    O.moe_layer([x], [ids], [wt], w, a)
+    try:
+        O.SILU_IMPL = "libm"
+        O.moe_layer([x], [ids], [wt], w, b)
+    finally:
+        O.SILU_IMPL = "exact"
+    dq = (a[0]["hq"].int() - b[0]["hq"].int()).abs()
+    assert int(dq.max()) <= 1 and float((dq > 0).float().mean()) < 2e-3
+    assert bool(((a[0]["hs"].view(torch.int32) - b[0]["hs"].view(torch.int32)).abs() <= 8).all())

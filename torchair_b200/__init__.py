@@ -16,10 +16,11 @@ from .backend import get_compiler, get_npu_backend, register_fx_node_ge_converte
 from .ep import register_ep_group, get_ep_group
 from . import ops
 from . import scope
-from .ops import clear_weight_cache, gmm_status
+from .ops import clear_weight_cache, gmm_status, gmm_status_reset, routing_status, check_status
 
 __all__ = ["get_npu_backend", "get_compiler", "CompilerConfig", "register_fx_node_ge_converter", "logger",
-           "register_ep_group", "install_as_torchair", "clear_weight_cache", "gmm_status", "scope",
+           "register_ep_group", "install_as_torchair", "clear_weight_cache", "gmm_status", "gmm_status_reset", "routing_status",
+           "check_status", "scope",
            "use_internal_format_weight", "patch_for_hcom", "dynamo_export", "register_replacement", "npu_format_cast_via_cpu"]
 
 

@@ -19,6 +19,7 @@ _L = c_int64
 SIGNATURES = {
     "tab_version": [],
     "tab_last_error": [],
+    "tab_launch_count": [],
     "tab_dynamic_quant": [_P, _I, _P, _L, _L, _P, _P, _P],
     "tab_swiglu": [_P, _I, _L, _L, _P, _P],
     "tab_dequant_swiglu_quant": [_P, _P, _L, _P, _P, _L, _I, _L, _L, _P, _P, _P],
@@ -36,7 +37,7 @@ SIGNATURES = {
     "tab_moe_init_routing_v2": [_P, _I, _P, _L, _L, _L, _L, _I, _I, _I, _P, _P, _P, _P, _P, c_size_t, _P],
     "tab_ep_signal": [_P, _P, _L, _P],
     "tab_ep_wait": [_P, _P, _L, _I, _P, _I, _P],
-    "tab_ep_send_rows": [_P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P, _P, _P, _P],
+    "tab_ep_send_rows": [_P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P, _P, _P, _P, _I, _P],
     "tab_ep_unpack_rows": [_P, _P, _L, _L, _L, _L, _I, _P, _P, _P],
     "tab_ep_return_rows": [_P, _P, _L, _L, _L, _L, _L, _L, _P, _P],
     "tab_ep_return_plan": [_P, _L, _L, _L, _L, _L, _L, _P, _P, _P],
@@ -50,8 +51,10 @@ SIGNATURES = {
     "tab_grouped_matmul_finalize_routing": [_P, _P, _P, _P, _P, _P, _I, _L, _L, _L, _L, _P, _L, c_float, _L, _P, _P, _I, _L, _P, _P,
                                             c_size_t, _P],
     "tab_gmm_status": [POINTER(c_int), _P],
+    "tab_gmm_status_reset": [_P],
+    "tab_routing_status": [POINTER(c_int), _P],
 }
-_RESTYPE = {"tab_last_error": c_char_p}
+_RESTYPE = {"tab_last_error": c_char_p, "tab_launch_count": ctypes.c_longlong}
 
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libtorchair_b200.so")
 _lock = threading.Lock()
@@ -88,6 +91,11 @@ def call(name: str, *args) -> None:
     rc = getattr(load(), name)(*args)
     if rc != 0:
         raise RuntimeError(f"{name} failed ({rc}): {last_error()}")
+
+
+def launch_count() -> int:
+    """Kernels enqueued by the library so far in this process (launches recorded during a CUDA-graph capture count once)."""
+    return int(load().tab_launch_count())
 
 
 def workspace_bytes(name: str, *dims: int) -> int:

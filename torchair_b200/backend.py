@@ -185,16 +185,31 @@ def _fused_down_combine_call(hq, w2, s2, hs, group_list, group_list_type, expert
 
 
 def _has_multi_rank_exchange(gm: torch.fx.GraphModule) -> bool:
-    ex = (torch.ops.npu.npu_moe_distribute_dispatch.default, torch.ops.npu.npu_moe_distribute_combine.default)
+    """True when the graph holds a dispatch or combine (either generation of the operators) over more than one rank
+    whose group moves rows with NCCL: exact-size all-to-all splits need one host read, which no capture allows."""
+    npu = torch.ops.npu
+    dispatch_ops = (npu.npu_moe_distribute_dispatch.default, npu.npu_moe_distribute_dispatch_v2.default)
+    combine_ops = (npu.npu_moe_distribute_combine.default, npu.npu_moe_distribute_combine_v2.default)
     for n in gm.graph.nodes:
-        if n.op == "call_function" and n.target in ex and len(n.args) > 3:
-            ws = n.args[3] if n.target is ex[0] else n.args[6]
-            group = n.args[2] if n.target is ex[0] else n.args[5]
-            if not isinstance(ws, int) or ws > 1:
-                from . import ep
-                if not (isinstance(group, str) and ep.transport_of(group, True) == "peer"):
-                    return True     # NCCL all-to-all with exact splits reads the sizes on the host
+        if n.op != "call_function" or n.target not in dispatch_ops + combine_ops:
+            continue
+        # (x, expert_ids, group_ep, ep_world_size, ...) and (expand_x, expert_ids, idx, counts, scales, group_ep, ep_world_size, ...)
+        gi, wi = (2, 3) if n.target in dispatch_ops else (5, 6)
+        group = n.args[gi] if len(n.args) > gi else n.kwargs.get("group_ep")
+        ws = n.args[wi] if len(n.args) > wi else n.kwargs.get("ep_world_size")
+        if not isinstance(ws, int) or ws > 1:
+            from . import ep
+            if not (isinstance(group, str) and ep.transport_of(group, True) == "peer"):
+                return True
     return False
+
+
+def _is_static_input(t) -> bool:
+    """Parameters and tensors whose address the tracer marked as stable (buffers of inlined modules,
+    torch._dynamo.mark_static_address) keep their storage between calls: the reference treats them as static
+    addresses of its captured graph too (python/torchair/_acl_concrete_graph/fx2acl_converter.py:421-423)."""
+    return isinstance(t, torch.nn.Parameter) or getattr(t, "_dynamo_static_input_type", None) is not None \
+        or getattr(t, "_torchair_is_parameter", False)
 
 
 class _CompiledFxGraph:
@@ -208,6 +223,11 @@ class _CompiledFxGraph:
         self.capture = config.mode.raw in ("reduce-overhead", "npugraph_ex") and not config.debug.run_eagerly.raw \
             and not _has_multi_rank_exchange(gm)
         self.clone_input = bool(config.debug.aclgraph.clone_input.raw)
+        # Parameters and static-address tensors are used in place, never cloned or copied per replay, as in the reference
+        # (python/torchair/_acl_concrete_graph/acl_graph.py:263-278).  Without experimental_config.frozen_parameter their
+        # addresses (and here also their version counters) join the capture key, so a moved or updated weight is captured
+        # afresh; with it they are taken as frozen and the key is the input shapes alone.
+        self.frozen = bool(config.experimental_config.frozen_parameter.raw)
         self.limit = int(config.debug.aclgraph.static_capture_size_limit.raw)
         self.graphs: Dict[Any, Any] = {}
         self.eager_forever = False
@@ -217,7 +237,9 @@ class _CompiledFxGraph:
             if not self.capture or self.eager_forever or not all(isinstance(a, torch.Tensor) and a.is_cuda for a in args):
                 counters["eager_runs"] += 1
                 return self.run(*args)
-            key = tuple((tuple(a.shape), a.dtype, a.device.index) for a in args)
+            static = [_is_static_input(a) for a in args]
+            key = tuple((tuple(a.shape), a.dtype, a.device.index) + ((a.data_ptr(), a._version) if st and not self.frozen else ())
+                        for a, st in zip(args, static))
             entry = self.graphs.get(key)
             if entry is None:
                 if len(self.graphs) >= self.limit:
@@ -226,17 +248,17 @@ class _CompiledFxGraph:
                     logger.warning("capture count exceeded static_capture_size_limit=%d; running eagerly", self.limit)
                     self.eager_forever = True
                     return self.run(*args)
-                entry = self._capture(key, args)
+                entry = self._capture(key, args, static)
             graph, static_in, static_out = entry
-            for dst, src in zip(static_in, args):
-                if dst.data_ptr() != src.data_ptr():
+            for dst, src, st in zip(static_in, args, static):
+                if not st and dst.data_ptr() != src.data_ptr():
                     dst.copy_(src)
             graph.replay()
             counters["replays"] += 1
             return static_out
 
-    def _capture(self, key, args):
-        static_in = [a.clone() if self.clone_input else a for a in args]
+    def _capture(self, key, args, static):
+        static_in = [a if st or not self.clone_input else a.clone() for a, st in zip(args, static)]
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):      # warm-up off the capture: fills the packed-weight cache, loads kernels

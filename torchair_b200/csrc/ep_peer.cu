@@ -17,12 +17,27 @@
 // acquire loads.  The receiver acknowledges after it has copied the rows out, and a sender waits for the previous
 // acknowledgement before it overwrites a peer's buffer.  Counters live on the device so that a replayed CUDA graph
 // keeps counting.  A wait that runs out of time records a code in the status word and lets the stream continue.
+#include <stdlib.h>
+
 #include "tab_common.cuh"
 
 namespace tab {
 
 constexpr int kEpMaxRanks = 64;
-constexpr long long kEpWaitCycles = 4000000000LL;   // ~2 s; ranks are aligned by a host barrier when the buffers are created
+
+// Bound of a flag wait in SM clock ticks: TAB_EP_WAIT_MS from the environment (read once), default 2000 ms.  Ranks are
+// aligned by a host barrier when the buffers are created, so a healthy peer answers within microseconds.
+static long long ep_wait_cycles() {
+  static const long long cycles = []() {
+    long long ms = 2000;
+    if (const char* f = getenv("TAB_EP_WAIT_MS")) {
+      const long long v = atoll(f);
+      if (v >= 1 && v <= 600000) ms = v;
+    }
+    return ms * 2000000LL;
+  }();
+  return cycles;
+}
 
 __device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
   unsigned long long v;
@@ -48,7 +63,7 @@ __global__ void ep_signal_kernel(unsigned long long* const* __restrict__ peer_fl
 // Waits until every source's flag has reached the expected sequence number.  pre_increment = 1: expect counter + 1
 // (new data); 0: expect the current counter (acknowledgement of the previous exchange).  The counter advances either way.
 __global__ void ep_wait_kernel(const unsigned long long* __restrict__ flags, unsigned long long* counter, int R,
-                               int pre_increment, int* status, int code) {
+                               int pre_increment, int* status, int code, long long limit) {
   __shared__ int s_fail;
   if (threadIdx.x == 0) s_fail = 0;
   __syncthreads();
@@ -56,7 +71,7 @@ __global__ void ep_wait_kernel(const unsigned long long* __restrict__ flags, uns
   if (threadIdx.x < R) {
     const long long t0 = clock64();
     while (ld_acquire_sys(flags + threadIdx.x) < expect) {
-      if (clock64() - t0 > kEpWaitCycles) {
+      if (clock64() - t0 > limit) {
         s_fail = 1;
         break;
       }
@@ -104,7 +119,7 @@ __global__ void __launch_bounds__(kEpThreads) ep_send_kernel(const uint4* __rest
                                                             int vec_per_row, int M, int my_rank,
                                                             uint8_t* const* __restrict__ peer_recv,
                                                             int32_t* const* __restrict__ peer_counts,
-                                                            int32_t* __restrict__ expand_idx_slot) {
+                                                            int32_t* __restrict__ expand_idx_slot, int* status, int code) {
   __shared__ int s_base[kEpMaxRanks + 1];
   rank_bases_to_smem(expert_counts, R, E_l, s_base);
   const int64_t slot_bytes = static_cast<int64_t>(vec_per_row + 1) * 16;
@@ -116,6 +131,10 @@ __global__ void __launch_bounds__(kEpThreads) ep_send_kernel(const uint4* __rest
   }
   for (int p = blockIdx.x; p < M; p += gridDim.x) {
     const int d = rank_of_position(s_base, R, p);
+    if (p - s_base[d] >= C) {           // more rows for one destination than its slot holds (counts and C disagree): not sent
+      if (threadIdx.x == 0) atomicCAS(status, 0, code);
+      continue;
+    }
     uint8_t* slot = peer_recv[d] + (static_cast<int64_t>(my_rank) * C + (p - s_base[d])) * slot_bytes;
     copy_row16<kEpThreads>(reinterpret_cast<uint4*>(slot), rows + static_cast<int64_t>(p) * vec_per_row, vec_per_row);
     if (threadIdx.x == 0) {
@@ -176,6 +195,7 @@ __global__ void __launch_bounds__(kEpThreads) ep_return_kernel(const uint4* __re
     const int b = ep_last_le(exp_off, 0, n, i);
     const int e = b / R, s = b - e * R;
     const int within = wire_off[s * E_l + e] - s * C + (i - exp_off[b]);
+    if (within < 0 || within >= C) continue;   // a plan that does not fit the slots: the row has no place, nothing is stored
     uint8_t* dstp = peer_ret[s] + (static_cast<int64_t>(my_rank) * C + within) * vec_per_row * 16;
     copy_row16<kEpThreads>(reinterpret_cast<uint4*>(dstp), y + static_cast<int64_t>(i) * vec_per_row, vec_per_row);
   }
@@ -197,7 +217,8 @@ __global__ void __launch_bounds__(256) ep_return_plan_kernel(const int32_t* __re
       const int b = ep_last_le(exp_off, 0, n, static_cast<int>(i));
       const int e = b / R, s = b - e * R;
       const int within = wire_off[s * E_l + e] - s * C + (static_cast<int>(i) - exp_off[b]);
-      a = reinterpret_cast<unsigned long long>(peer_ret[s] + (static_cast<int64_t>(my_rank) * C + within) * row_bytes);
+      if (within >= 0 && within < C)    // else the plan does not fit the slots: the row keeps address 0 and is not stored
+        a = reinterpret_cast<unsigned long long>(peer_ret[s] + (static_cast<int64_t>(my_rank) * C + within) * row_bytes);
     }
     row_dst[i] = a;
   }
@@ -218,15 +239,16 @@ extern "C" int tab_ep_wait(const void* flags, void* counter, int64_t R, int pre_
                            tab_stream_t stream) {
   if (!flags || !counter || !status || R < 1 || R > kEpMaxRanks) return fail(TAB_ERR_BAD_ARG, "ep_wait: bad argument (R=%lld)", (long long)R);
   ep_wait_kernel<<<1, 64, 0, as_stream(stream)>>>(static_cast<const unsigned long long*>(flags),
-                                                 static_cast<unsigned long long*>(counter), (int)R, pre_increment, status, code);
+                                                 static_cast<unsigned long long*>(counter), (int)R, pre_increment, status, code,
+                                                 ep_wait_cycles());
   return check_launch("ep_wait");
 }
 
 extern "C" int tab_ep_send_rows(const void* rows, const float* scales, const int32_t* expert_counts, const int32_t* expand_idx,
                                 int64_t R, int64_t E_l, int64_t slot_rows, int64_t row_bytes, int64_t M, int64_t my_rank,
                                 void* const* peer_recv, void* const* peer_counts, int32_t* expand_idx_slot,
-                                tab_stream_t stream) {
-  if (!expert_counts || !peer_recv || !peer_counts || R < 1 || R > kEpMaxRanks || E_l < 1 || slot_rows < 1 || my_rank < 0 || my_rank >= R)
+                                int* status, int code, tab_stream_t stream) {
+  if (!expert_counts || !peer_recv || !peer_counts || !status || R < 1 || R > kEpMaxRanks || E_l < 1 || slot_rows < 1 || my_rank < 0 || my_rank >= R)
     return fail(TAB_ERR_BAD_ARG, "ep_send_rows: bad argument");
   if (M > 0 && (!rows || !expand_idx || !expand_idx_slot)) return fail(TAB_ERR_BAD_ARG, "ep_send_rows: null pointer");
   if (row_bytes <= 0 || row_bytes % 16 != 0 || (M > 0 && !aligned16(rows)) || M > (1LL << 30) || R * slot_rows > (1LL << 30))
@@ -235,7 +257,7 @@ extern "C" int tab_ep_send_rows(const void* rows, const float* scales, const int
   ep_send_kernel<<<grid, kEpThreads, 0, as_stream(stream)>>>(static_cast<const uint4*>(rows), scales, expert_counts, expand_idx, (int)R,
                                                             (int)E_l, (int)slot_rows, (int)(row_bytes / 16), (int)M, (int)my_rank,
                                                             reinterpret_cast<uint8_t* const*>(peer_recv),
-                                                            reinterpret_cast<int32_t* const*>(peer_counts), expand_idx_slot);
+                                                            reinterpret_cast<int32_t* const*>(peer_counts), expand_idx_slot, status, code);
   return check_launch("ep_send_rows");
 }
 

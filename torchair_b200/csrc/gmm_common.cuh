@@ -17,7 +17,7 @@ constexpr int kGmmThreads = 192;
 constexpr int kBlockK = 128;               // bytes of K per stage row = one swizzle span
 constexpr int kWTileBytes = 128 * kBlockK;  // one 128-channel weight tile
 constexpr int kMaxGroups = 1024;
-constexpr long long kWaitCycles = 400000000LL;  // bound of every device-side wait (~0.2 s)
+constexpr long long kCyclesPerMs = 2000000LL;   // SM clock ticks per millisecond at the top clock (1965 MHz), rounded up
 constexpr int kSmemLimit = 232448;
 
 struct GmmParams {
@@ -37,17 +37,19 @@ struct GmmParams {
   float* h_out;            // fused: [M, I] fp32
   unsigned int* amax;      // fused: [M] row amax as fp32 bits
   int activate_left;
+  long long wait_cycles;   // bound of every device-side wait, in SM clock ticks (TAB_GMM_WAIT_MS, default 2000 ms)
 };
 
-// Waits for a phase of an mbarrier; gives up after kWaitCycles or when another role already gave up.
-__device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+// Waits for a phase of an mbarrier; gives up after `limit` clock ticks or when another role already gave up.
+__device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
+                                             long long limit) {
   if (ptx::mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   unsigned spins = 0;
   while (!ptx::mbar_try_wait(bar, parity)) {
     if ((++spins & 255u) == 0) {
       if (*abort_flag != 0) return false;
-      if (clock64() - t0 > kWaitCycles) {
+      if (clock64() - t0 > limit) {
         *abort_flag = code;
         atomicCAS(&g_gmm_status, 0, code);
         return false;
@@ -57,7 +59,8 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, vola
   return true;
 }
 
-// First byte of output row `row`: the row's own address when a table is given, else row-major in p.out.
+// First byte of output row `row`: the row's own address when a table is given (0 there = the row belongs to no
+// destination and must not be stored), else row-major in p.out.  Callers skip the row on a null result.
 __device__ __forceinline__ uint8_t* out_row_ptr(const GmmParams& p, int64_t row, int esz) {
   return p.row_dst ? reinterpret_cast<uint8_t*>(p.row_dst[row]) : static_cast<uint8_t*>(p.out) + row * p.N * esz;
 }

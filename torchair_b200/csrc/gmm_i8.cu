@@ -106,7 +106,7 @@ gmm_i8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
         const int ch1 = FUSED ? p.half + it.ct * 128 : it.ct * 256 + 128;
         const int row0 = s_start[it.e] + it.tt * NT;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!bounded_wait(bar_empty(stage), phase ^ 1u, s_abort, 1)) { ok = false; break; }
+          if (!bounded_wait(bar_empty(stage), phase ^ 1u, s_abort, 1, p.wait_cycles)) { ok = false; break; }
           const uint32_t st = tiles_addr + stage * Cfg::kStageBytes;
           ptx::mbar_expect_tx(bar_full(stage), Cfg::kStageBytes);
           ptx::tma_load_3d(st, &tm_w, bar_full(stage), kb * kBlockK, ch0, it.e);
@@ -122,7 +122,7 @@ gmm_i8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
           const long long a = arms / kStages + (s < arms % kStages ? 1 : 0);
           if (a > 0) {
             const long long t0 = clock64();
-            while (!ptx::mbar_try_wait(bar_full(s), static_cast<uint32_t>((a - 1) & 1)) && clock64() - t0 < kWaitCycles) {}
+            while (!ptx::mbar_try_wait(bar_full(s), static_cast<uint32_t>((a - 1) & 1)) && clock64() - t0 < p.wait_cycles) {}
           }
         }
       }
@@ -135,12 +135,12 @@ gmm_i8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
       uint32_t phase = 0, tphase = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < total_items && ok; w += gridDim.x) {
-        if (!bounded_wait(bar_tempty(buf), tphase ^ 1u, s_abort, 2)) { ok = false; break; }
+        if (!bounded_wait(bar_tempty(buf), tphase ^ 1u, s_abort, 2, p.wait_cycles)) { ok = false; break; }
         ptx::tc_fence_after();
         const uint32_t d0 = tmem_base + buf * 2 * NT;
         const uint32_t d1 = d0 + NT;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!bounded_wait(bar_full(stage), phase, s_abort, 3)) { ok = false; break; }
+          if (!bounded_wait(bar_full(stage), phase, s_abort, 3, p.wait_cycles)) { ok = false; break; }
           ptx::tc_fence_after();
           const uint32_t st = tiles_addr + stage * Cfg::kStageBytes;
           const uint64_t a0 = ptx::smem_desc_k128(st);
@@ -163,7 +163,7 @@ gmm_i8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
         // Wait (bounded) for whatever was issued before tensor memory is released.
         ptx::mma_commit(bar_drain);
         const long long t0 = clock64();
-        while (!ptx::mbar_try_wait(bar_drain, 0) && clock64() - t0 < kWaitCycles) {}
+        while (!ptx::mbar_try_wait(bar_drain, 0) && clock64() - t0 < p.wait_cycles) {}
       }
     }
   } else {
@@ -174,7 +174,7 @@ gmm_i8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
     uint32_t tphase = 0;
     for (int w = blockIdx.x; w < total_items; w += gridDim.x) {
       int got = 0;
-      if (lane == 0) got = bounded_wait(bar_tfull(buf), tphase, s_abort, 4) ? 1 : 0;
+      if (lane == 0) got = bounded_wait(bar_tfull(buf), tphase, s_abort, 4, p.wait_cycles) ? 1 : 0;
       got = __shfl_sync(0xffffffffu, got, 0);
       if (!got) break;
       ptx::tc_fence_after();
@@ -234,12 +234,14 @@ gmm_i8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
                 const float ts = p.tok_scale ? p.tok_scale[row] : 1.f;
                 const float f0 = __fmul_rn(__fmul_rn(__int2float_rn(a[j]), ts), w0);
                 const float f1 = __fmul_rn(__fmul_rn(__int2float_rn(b[j]), ts), w1);
+                uint8_t* orow = out_row_ptr(p, row, 2);
+                if (orow == nullptr) continue;             // address table says: no destination for this row
                 if (p.out_dtype == TAB_BF16) {
-                  __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out_row_ptr(p, row, 2));
+                  __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(orow);
                   if (v0) o[c0] = __float2bfloat16_rn(f0);
                   if (v1) o[c1] = __float2bfloat16_rn(f1);
                 } else {
-                  __half* o = reinterpret_cast<__half*>(out_row_ptr(p, row, 2));
+                  __half* o = reinterpret_cast<__half*>(orow);
                   if (v0) o[c0] = __float2half_rn(f0);
                   if (v1) o[c1] = __float2half_rn(f1);
                 }
@@ -337,14 +339,37 @@ static int make_maps(const int8_t* x, const int8_t* wp, int64_t M, int64_t Kd, i
   return TAB_OK;
 }
 
-// Token-tile width of the decode orientation: the smallest of 16..256 that holds 1.5 x the average rows per expert.
-// TAB_GMM_NT=16|32|64|128|256 overrides it (tuning aid).
-static int pick_nt(int64_t M, int64_t E) {
-  const char* f = getenv("TAB_GMM_NT");
-  if (f != nullptr) {
-    const int v = atoi(f);
-    if (v == 16 || v == 32 || v == 64 || v == 128 || v == 256) return v;
+// Tuning and safety knobs from the environment, read once when the library is first used:
+//   TAB_GMM_NT=16|32|64|128|256          token-tile width of the decode orientation (default: from M / E)
+//   TAB_GMM_ORIENTATION=decode|prefill   kernel orientation (default: prefill when M > 64 * E)
+//   TAB_GMM_WAIT_MS=<ms>                 bound of every device-side wait inside the GEMM kernels (default 2000)
+struct GmmEnv {
+  int nt = 0;
+  int orientation = 0;   // 0 auto, 1 decode, 2 prefill
+  long long wait_cycles = 2000 * kCyclesPerMs;
+  GmmEnv() {
+    if (const char* f = getenv("TAB_GMM_NT")) {
+      const int v = atoi(f);
+      if (v == 16 || v == 32 || v == 64 || v == 128 || v == 256) nt = v;
+    }
+    if (const char* f = getenv("TAB_GMM_ORIENTATION")) {
+      if (strcmp(f, "decode") == 0) orientation = 1;
+      if (strcmp(f, "prefill") == 0) orientation = 2;
+    }
+    if (const char* f = getenv("TAB_GMM_WAIT_MS")) {
+      const long long ms = atoll(f);
+      if (ms >= 1 && ms <= 600000) wait_cycles = ms * kCyclesPerMs;
+    }
   }
+};
+static const GmmEnv& gmm_env() {
+  static const GmmEnv env;
+  return env;
+}
+
+// Token-tile width of the decode orientation: the smallest of 16..256 that holds 1.5 x the average rows per expert.
+static int pick_nt(int64_t M, int64_t E) {
+  if (gmm_env().nt != 0) return gmm_env().nt;
   const double avg = static_cast<double>(M) / static_cast<double>(E);
   const int opts[5] = {16, 32, 64, 128, 256};
   for (int i = 0; i < 5; ++i)
@@ -364,14 +389,9 @@ static int launch_one(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const Gm
 }
 
 // Orientation: experts with many rows run the prefill kernel (128-token tiles, overlapped epilogue); a handful of
-// rows per expert run the decode kernel (weights stationary, narrow token tile).  TAB_GMM_ORIENTATION=decode|prefill
-// overrides the choice (tuning aid).
+// rows per expert run the decode kernel (weights stationary, narrow token tile).
 static bool use_prefill(int64_t M, int64_t E) {
-  const char* f = getenv("TAB_GMM_ORIENTATION");
-  if (f != nullptr) {
-    if (strcmp(f, "prefill") == 0) return true;
-    if (strcmp(f, "decode") == 0) return false;
-  }
+  if (gmm_env().orientation != 0) return gmm_env().orientation == 2;
   return M > 64 * E;
 }
 
@@ -455,6 +475,7 @@ static int grouped_matmul_plain(const int8_t* x, const int8_t* packed_weight, co
   p.out = y;
   p.out_dtype = out_dtype;
   p.row_dst = reinterpret_cast<const unsigned long long*>(row_dst);
+  p.wait_cycles = gmm_env().wait_cycles;
   return launch_gmm<false>(nt, tm_w, tm_x, p, as_stream(stream));
 }
 
@@ -518,9 +539,18 @@ extern "C" int tab_grouped_matmul_swiglu_quant(const int8_t* x, const int8_t* pa
   p.h_out = h;
   p.amax = amax;
   p.activate_left = activate_left;
+  p.wait_cycles = gmm_env().wait_cycles;
   rc = launch_gmm<true>(nt, tm_w, tm_x, p, st);
   if (rc != TAB_OK) return rc;
   return launch_quant_from_f32(h, amax, group_list, group_list_type, (int)E, M, (int)I, yq, y_scale, st);
+}
+
+extern "C" int tab_gmm_status_reset(tab_stream_t stream) {
+  cudaError_t e = cudaStreamSynchronize(as_stream(stream));
+  const int zero = 0;
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_gmm_status, &zero, sizeof(int));
+  if (e != cudaSuccess) return fail(TAB_ERR_CUDA, "gmm_status_reset: %s", cudaGetErrorString(e));
+  return TAB_OK;
 }
 
 extern "C" int tab_gmm_status(int* status_host, tab_stream_t stream) {

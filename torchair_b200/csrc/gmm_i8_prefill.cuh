@@ -97,8 +97,10 @@ __device__ __forceinline__ void pf_narrow_epilogue(const GmmParams& p, const Wor
           } else {
             const float ts = p.tok_scale ? p.tok_scale[row] : 1.f;
             const float f = __fmul_rn(__fmul_rn(__int2float_rn(a[j]), ts), wv);
-            if (p.out_dtype == TAB_BF16) reinterpret_cast<__nv_bfloat16*>(out_row_ptr(p, row, 2))[ch] = __float2bfloat16_rn(f);
-            else reinterpret_cast<__half*>(out_row_ptr(p, row, 2))[ch] = __float2half_rn(f);
+            uint8_t* orow = out_row_ptr(p, row, 2);
+            if (orow == nullptr) continue;               // address table says: no destination for this row
+            if (p.out_dtype == TAB_BF16) reinterpret_cast<__nv_bfloat16*>(orow)[ch] = __float2bfloat16_rn(f);
+            else reinterpret_cast<__half*>(orow)[ch] = __float2half_rn(f);
           }
         }
       }
@@ -169,7 +171,7 @@ gmm_i8_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
         const int ch1 = FUSED ? p.half + it.ct * 128 : it.ct * 256 + 128;    // second 128 columns
         const int row0 = s_start[it.e] + it.tt * kPfTokens;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!bounded_wait(bar_empty(stage), phase ^ 1u, s_abort, 11)) { ok = false; break; }
+          if (!bounded_wait(bar_empty(stage), phase ^ 1u, s_abort, 11, p.wait_cycles)) { ok = false; break; }
           const uint32_t st = tiles_addr + stage * kPfStageBytes;
           ptx::mbar_expect_tx(bar_full(stage), kPfStageBytes);
           ptx::tma_load_2d(st, &tm_x, bar_full(stage), kb * kBlockK, row0);
@@ -184,7 +186,7 @@ gmm_i8_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
           const long long a = arms / kPfStages + (s < arms % kPfStages ? 1 : 0);
           if (a > 0) {
             const long long t0 = clock64();
-            while (!ptx::mbar_try_wait(bar_full(s), static_cast<uint32_t>((a - 1) & 1)) && clock64() - t0 < kWaitCycles) {}
+            while (!ptx::mbar_try_wait(bar_full(s), static_cast<uint32_t>((a - 1) & 1)) && clock64() - t0 < p.wait_cycles) {}
           }
         }
       }
@@ -201,11 +203,11 @@ gmm_i8_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
         const int nvalid = min(kPfTokens, s_start[it.e + 1] - (s_start[it.e] + it.tt * kPfTokens));
         const bool narrow = nvalid <= kPfNarrowMax;
         const uint32_t idesc_n = ptx::idesc_i8(128, (nvalid + 15) & ~15);
-        if (!bounded_wait(bar_tempty(buf), tphase ^ 1u, s_abort, 12)) { ok = false; break; }
+        if (!bounded_wait(bar_tempty(buf), tphase ^ 1u, s_abort, 12, p.wait_cycles)) { ok = false; break; }
         ptx::tc_fence_after();
         const uint32_t d = tmem_base + buf * kPfCols;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!bounded_wait(bar_full(stage), phase, s_abort, 13)) { ok = false; break; }
+          if (!bounded_wait(bar_full(stage), phase, s_abort, 13, p.wait_cycles)) { ok = false; break; }
           ptx::tc_fence_after();
           const uint32_t st = tiles_addr + stage * kPfStageBytes;
           const uint64_t a = ptx::smem_desc_k128(st);
@@ -231,7 +233,7 @@ gmm_i8_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
       if (!ok) {
         ptx::mma_commit(bar_drain);
         const long long t0 = clock64();
-        while (!ptx::mbar_try_wait(bar_drain, 0) && clock64() - t0 < kWaitCycles) {}
+        while (!ptx::mbar_try_wait(bar_drain, 0) && clock64() - t0 < p.wait_cycles) {}
       }
     }
   } else {
@@ -254,7 +256,7 @@ gmm_i8_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
         if (et < 128) ws[et] = (wrow && c_first + et < lim_first) ? wrow[c_first + et] : 1.f;
         else ws[et] = (wrow && c_second + et - 128 < p.N) ? wrow[c_second + et - 128] : 1.f;
       }
-      if (et == 0) s_got[buf] = bounded_wait(bar_tfull(buf), tphase, s_abort, 14) ? 1 : 0;
+      if (et == 0) s_got[buf] = bounded_wait(bar_tfull(buf), tphase, s_abort, 14, p.wait_cycles) ? 1 : 0;
       epilogue_bar_sync();
       if (!s_got[buf]) break;
       ptx::tc_fence_after();
@@ -347,8 +349,9 @@ gmm_i8_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
               const int grow = row_base + r;
               if (grow < row_end && cvalid) {
                 const uint4 v = *reinterpret_cast<const uint4*>(patch + r * kPfOutPitch + piece * 16);
-                uint8_t* o = out_row_ptr(p, grow, esz) + static_cast<int64_t>(c0 + c) * esz + piece * 16;
-                __stcs(reinterpret_cast<uint4*>(o), v);   // streamed: outputs must not push weights and rows out of L2
+                uint8_t* orow = out_row_ptr(p, grow, esz);
+                if (orow != nullptr)                      // a null table entry = no destination for this row
+                  __stcs(reinterpret_cast<uint4*>(orow + static_cast<int64_t>(c0 + c) * esz + piece * 16), v);   // streamed: outputs must not push weights and rows out of L2
               }
             }
           }
@@ -370,11 +373,12 @@ gmm_i8_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
                   if (c0 + c + j < p.N) o[j] = a[j];
               }
             } else {
-              for (int j = 0; j < 16; ++j) {
+              uint8_t* orow = out_row_ptr(p, row, 2);
+              for (int j = 0; j < 16 && orow != nullptr; ++j) {
                 if (c0 + c + j >= p.N) break;
                 const float f = __fmul_rn(__fmul_rn(__int2float_rn(a[j]), ts), ws[c + j]);
-                if (p.out_dtype == TAB_BF16) reinterpret_cast<__nv_bfloat16*>(out_row_ptr(p, row, 2))[c0 + c + j] = __float2bfloat16_rn(f);
-                else reinterpret_cast<__half*>(out_row_ptr(p, row, 2))[c0 + c + j] = __float2half_rn(f);
+                if (p.out_dtype == TAB_BF16) reinterpret_cast<__nv_bfloat16*>(orow)[c0 + c + j] = __float2bfloat16_rn(f);
+                else reinterpret_cast<__half*>(orow)[c0 + c + j] = __float2half_rn(f);
               }
             }
           }

@@ -46,9 +46,13 @@ __device__ int block_exclusive_scan(int* vals, int n, int* warp_sums) {
   return total;
 }
 
-__device__ __forceinline__ int clamp_expert(int key, int nb, int* status) {
+// Status word of the routing kernels on this device (tab_routing_status reads and clears it):
+// bit 0 = an expert id outside [0, bound) was clamped, bit 1 = a row_idx value outside [0, T*K) was skipped.
+__device__ int g_routing_status = 0;
+
+__device__ __forceinline__ int clamp_expert(int key, int nb) {
   if (key < 0 || key >= nb) {
-    *status = 1;  // expert id outside [0, bound): clamped so that no access goes out of range
+    atomicOr(&g_routing_status, 1);   // clamped so that no access goes out of range; the host can ask afterwards
     key = key < 0 ? 0 : nb - 1;
   }
   return key;
@@ -56,12 +60,12 @@ __device__ __forceinline__ int clamp_expert(int key, int nb, int* status) {
 
 // Phase 1: per-chunk histogram of expert ids.  chunk_hist [nchunks, nb].
 __global__ void __launch_bounds__(kChunk) route_hist_kernel(const int32_t* __restrict__ expert, int n, int nb,
-                                                            int* __restrict__ chunk_hist, int* status) {
+                                                            int* __restrict__ chunk_hist) {
   extern __shared__ int s_hist[];
   for (int i = threadIdx.x; i < nb; i += kChunk) s_hist[i] = 0;
   __syncthreads();
   const int f = blockIdx.x * kChunk + threadIdx.x;
-  if (f < n) atomicAdd(&s_hist[clamp_expert(expert[f], nb, status)], 1);
+  if (f < n) atomicAdd(&s_hist[clamp_expert(expert[f], nb)], 1);
   __syncthreads();
   for (int i = threadIdx.x; i < nb; i += kChunk) chunk_hist[blockIdx.x * nb + i] = s_hist[i];
 }
@@ -104,7 +108,7 @@ __global__ void __launch_bounds__(kChunk) route_scatter_kernel(const int32_t* __
                                                                const int* __restrict__ expert_count,
                                                                int32_t* __restrict__ sorted_expert,
                                                                int32_t* __restrict__ sorted_src,
-                                                               int32_t* __restrict__ inverse, int* status) {
+                                                               int32_t* __restrict__ inverse) {
   extern __shared__ unsigned short s_wcnt[];  // [32 warps][nb], then int s_base[nb]
   __shared__ int s_warp[33];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -115,7 +119,7 @@ __global__ void __launch_bounds__(kChunk) route_scatter_kernel(const int32_t* __
   block_exclusive_scan(s_base, nb, s_warp);
   const int f = blockIdx.x * kChunk + tid;
   const bool valid = f < n;
-  const int key = valid ? clamp_expert(expert[f], nb, status) : -1;
+  const int key = valid ? clamp_expert(expert[f], nb) : -1;
   const unsigned peers = __match_any_sync(0xffffffffu, key);
   const int rank_in_warp = __popc(peers & ((1u << lane) - 1u));
   if (valid && rank_in_warp == 0) s_wcnt[warp * nb + key] = static_cast<unsigned short>(__popc(peers));
@@ -132,17 +136,21 @@ __global__ void __launch_bounds__(kChunk) route_scatter_kernel(const int32_t* __
   __syncthreads();
   if (valid) {
     const int pos = s_base[key] + chunk_base[blockIdx.x * nb + key] + s_wcnt[warp * nb + key] + rank_in_warp;
-    const int sv = src_val ? src_val[f] : f;
+    int sv = src_val ? src_val[f] : f;
     sorted_expert[pos] = key;
+    if (sv < 0 || sv >= n) {            // a row_idx value that names no pair: nothing is written through it
+      atomicOr(&g_routing_status, 2);
+      sv = f;                            // the gather then reads the pair's own token instead of an arbitrary row
+    } else {
+      inverse[sv] = pos;
+    }
     if (sorted_src) sorted_src[pos] = sv;
-    inverse[sv] = pos;
   }
 }
 
 struct SortScratch {
   int* chunk_hist;    // [nchunks, nb]
   int* expert_count;  // [nb]
-  int* status;        // [1]
   int32_t* sorted_src;     // [n]
   int32_t* sorted_expert;  // [n] (dispatch only; init_routing writes the caller's output)
 };
@@ -159,7 +167,7 @@ static SortScratch carve(void* ws, int64_t n, int64_t nb, bool need_sorted_exper
   int* p = static_cast<int*>(ws);
   s.chunk_hist = p; p += nchunks * nb;
   s.expert_count = p; p += nb;
-  s.status = p; p += 4;
+  p += 4;   // spare words (keeps the following arrays 16-byte aligned when nb is a multiple of 4)
   s.sorted_src = p; p += n;
   s.sorted_expert = need_sorted_expert ? p : nullptr;
   return s;
@@ -173,12 +181,12 @@ static int run_sort(const int32_t* expert, const int32_t* src_val, int64_t n, in
     cudaError_t e = cudaFuncSetAttribute(route_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(scatter_smem));
     if (e != cudaSuccess) return fail(TAB_ERR_CUDA, "routing: shared memory opt-in failed: %s", cudaGetErrorString(e));
   }
-  route_hist_kernel<<<nchunks, kChunk, nb * sizeof(int), st>>>(expert, (int)n, (int)nb, s.chunk_hist, s.status);
+  route_hist_kernel<<<nchunks, kChunk, nb * sizeof(int), st>>>(expert, (int)n, (int)nb, s.chunk_hist);
   route_scan_kernel<<<(int)((nb + kScanWarps - 1) / kScanWarps), kScanWarps * 32, 0, st>>>(s.chunk_hist, nchunks, (int)nb,
                                                                                           s.expert_count, expert_count_out);
   route_scatter_kernel<<<nchunks, kChunk, scatter_smem, st>>>(expert, src_val, (int)n, (int)nb, s.chunk_hist, s.expert_count,
-                                                             sorted_expert, s.sorted_src, inverse, s.status);
-  return check_launch("routing sort");
+                                                             sorted_expert, s.sorted_src, inverse);
+  return check_launch("routing sort", 3);
 }
 
 // dst[i] = src[(idx[i] % mod)] for i < rows; one CTA per row, 16-byte vectors.
@@ -189,7 +197,7 @@ __global__ void __launch_bounds__(kRowCopyThreads) gather_rows_kernel(const uint
   int64_t i = blockIdx.x;
   int next = i < rows ? idx[i] : 0;
   for (; i < rows; i += gridDim.x) {
-    const int64_t s = next % mod;
+    const int64_t s = (next < 0 ? 0 : next) % mod;
     if (i + gridDim.x < rows) next = idx[i + gridDim.x];   // fetched while this row is being copied
     copy_row16<kRowCopyThreads>(dst + i * vec_per_row, src + s * vec_per_row, vec_per_row);
   }
@@ -575,6 +583,23 @@ extern "C" int tab_moe_combine(const void* rows, int dtype, const int32_t* expan
   return check_launch("combine");
 }
 
+extern "C" int tab_routing_status(int* status_host, tab_stream_t stream) {
+  if (!status_host) return fail(TAB_ERR_BAD_ARG, "routing_status: null pointer");
+  cudaStream_t st = as_stream(stream);
+  cudaError_t e = cudaStreamSynchronize(st);
+  if (e == cudaSuccess) e = cudaMemcpyFromSymbol(status_host, g_routing_status, sizeof(int));
+  if (e == cudaSuccess && *status_host != 0) {
+    const int zero = 0;
+    e = cudaMemcpyToSymbol(g_routing_status, &zero, sizeof(int));
+  }
+  if (e != cudaSuccess) return fail(TAB_ERR_CUDA, "routing_status: %s", cudaGetErrorString(e));
+  if (*status_host != 0)
+    return fail(TAB_ERR_BAD_ARG, "routing: %s%s%s since the last check (clamped / skipped, nothing was accessed out of range)",
+                (*status_host & 1) ? "an expert id outside [0, bound)" : "", (*status_host & 3) == 3 ? " and " : "",
+                (*status_host & 2) ? "a row_idx value outside [0, T*K)" : "");
+  return TAB_OK;
+}
+
 // ---- routing without caller-provided scratch -----------------------------------------------------------
 // Same work as tab_moe_init_routing, but the sort's scratch (chunk histograms, expert totals, sorted source
 // rows) lives in a fixed array inside the library's device image instead of a caller-supplied workspace.
@@ -619,7 +644,7 @@ extern "C" int tab_moe_init_routing_static(const void* x, int x_dtype, const int
                                            tab_stream_t stream) {
   if (T < 0 || K <= 0 || expert_bound <= 0)
     return fail(TAB_ERR_BAD_ARG, "init_routing_static: T=%lld K=%lld expert_bound=%lld", (long long)T, (long long)K, (long long)expert_bound);
-  if (T * K > kStaticMaxPairs || expert_bound > kStaticMaxExperts)
+  if (T > kStaticMaxPairs / K || T * K > kStaticMaxPairs || expert_bound > kStaticMaxExperts)
     return fail(TAB_ERR_UNSUPPORTED,
                 "init_routing_static: T*K=%lld (max %lld) or expert_bound=%lld (max %lld) exceeds the built-in scratch; "
                 "use tab_moe_init_routing with a workspace",
@@ -845,7 +870,7 @@ extern "C" int tab_moe_init_routing_v2(const void* x, int x_dtype, const int32_t
     cudaError_t e = cudaMemcpyAsync(expanded_row_idx, s.sorted_src, n * sizeof(int32_t), cudaMemcpyDeviceToDevice, st);
     if (e != cudaSuccess) return fail(TAB_ERR_CUDA, "init_routing_v2: copy: %s", cudaGetErrorString(e));
   }
-  return check_launch("init_routing_v2");
+  return check_launch("init_routing_v2", 0);   // the kernels were counted by the calls above
 }
 
 // ---- npu_moe_gating_top_k: softmax or sigmoid scores, optional selection bias, group-limited top-k ----------------

@@ -16,8 +16,9 @@ int fail(int code, const char* fmt, ...);
 
 inline cudaStream_t as_stream(tab_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
 
-// Reports a failed launch (bad configuration and the like) without synchronising.
-int check_launch(const char* what);
+// Reports a failed launch (bad configuration and the like) without synchronising; on success adds `kernels` to the
+// process-wide count of kernels this library has enqueued (tab_launch_count).
+int check_launch(const char* what, int kernels = 1);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -115,13 +116,19 @@ __device__ __forceinline__ uint32_t pack4_i8(int a, int b, int c, int d) {
          ((static_cast<uint32_t>(c) & 0xffu) << 16) | ((static_cast<uint32_t>(d) & 0xffu) << 24);
 }
 
-// silu(a) * b = a / (1 + exp(-a)) * b in fp32.  exp(-a) is one multiply and the hardware exp2 (relative error about
-// 2^-22 plus |a| * 2^-24 from the rounded product); it enters the result through 1 + exp(-a), so the result is within a
-// few ulp wherever it is not itself tiny (for a << 0 it is below 1e-7 in magnitude).  The quotient is formed as an
-// approximate reciprocal followed by one remainder correction (two FMAs), which is within half an ulp and a bit of the
-// IEEE quotient at a third of the instructions of the library division; -a is capped at 80 so that the denominator
-// stays finite (the capped results are below 2e-33 in magnitude).
+// silu(a) * b = RN(RN(a / (1 + e)) * b) in fp32 with e = exp(-a) from a fixed sequence of correctly rounded operations
+// (two FMAs of range reduction with the rounded log2(e), a degree-6 polynomial for 2^f on [-0.5, 0.5] in Horner form,
+// the integer part added into the exponent field, IEEE division), so that a CPU restatement of the same sequence gives
+// the same bits: int8 values quantised after SwiGLU then do not depend on whose exp() was used.  e is within 1.3 ulp of
+// exp(-a) apart from the rounded log2(e) (relative error |a| * 1.3e-8).  -a is capped to [-80, 80]: beyond it 1 + e is 1,
+// or the result is below 1e-33 in magnitude.  No special-function unit result enters the value (the division's
+// reciprocal seed is corrected to the IEEE quotient by the library).
+// Building with -DTAB_FAST_SILU swaps in the earlier form (hardware ex2.approx and an approximate reciprocal with one
+// remainder correction: about half the instructions, results within a few ulp but not reproducible on a CPU).
+constexpr float kLog2e = 0x1.715476p+0f;
+constexpr float kRoundMagicF = 12582912.0f;   // 1.5 * 2^23
 __device__ __forceinline__ float silu_mul(float a, float b) {
+#ifdef TAB_FAST_SILU
   float e;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(__fmul_rn(fminf(-a, 80.0f), 1.4426950408889634f)));
   const float d = __fadd_rn(1.0f, e);
@@ -131,6 +138,22 @@ __device__ __forceinline__ float silu_mul(float a, float b) {
   const float r = __fmaf_rn(-q0, d, a);
   const float s = __fmaf_rn(r, y, q0);
   return __fmul_rn(s, b);
+#else
+  const float x = fminf(fmaxf(-a, -80.0f), 80.0f);
+  const float nm = __fmaf_rn(x, kLog2e, kRoundMagicF);     // integer n = rint(x * log2e) in the low mantissa bits
+  const float n = __fadd_rn(nm, -kRoundMagicF);
+  const float f = __fmaf_rn(x, kLog2e, -n);                 // |f| <= 0.5
+  float p = 0x1.41d334p-13f;
+  p = __fmaf_rn(p, f, 0x1.5f456ap-10f);
+  p = __fmaf_rn(p, f, 0x1.3b2dbcp-7f);
+  p = __fmaf_rn(p, f, 0x1.c6aed4p-5f);
+  p = __fmaf_rn(p, f, 0x1.ebfbdap-3f);
+  p = __fmaf_rn(p, f, 0x1.62e430p-1f);
+  p = __fmaf_rn(p, f, 1.0f);
+  const float e = __uint_as_float(__float_as_uint(p) + (__float_as_uint(nm) << 23));   // p * 2^n
+  const float d = __fadd_rn(1.0f, e);
+  return __fmul_rn(__fdiv_rn(a, d), b);
+#endif
 }
 
 

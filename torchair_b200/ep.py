@@ -242,7 +242,8 @@ class PeerExchange:
                   int(pre_increment), ctypes.c_void_p(self.status_ptr), 100 + kind, self._stream())
 
     def status(self) -> int:
-        """Synchronises and returns 0, or 100 + kind of the first flag wait that ran out of time."""
+        """Synchronises and returns 0, 100 + kind of the first flag wait that ran out of time, or 110 when a sender held
+        more rows for one destination than its slot takes (those rows were not sent)."""
         torch.cuda.synchronize(self.buf.device)
         off = self.status_ptr - self.buf.data_ptr()
         return int(self.buf[off:off + 4].view(torch.int32).item())
@@ -280,7 +281,7 @@ def _dispatch_peer(kern, x, expert_ids, group_ep, pg, R, rank, E, quant_mode, nu
     slot_idx = torch.empty_like(expand_idx)
     px.wait(px.KIND_ACK_D, 0)                     # the peers have copied my previous rows out of their buffers
     _lib.call("tab_ep_send_rows", _ptr(send_rows), _ptr(send_scales), _ptr(counts), _ptr(expand_idx), R, E_l, px.C, row_bytes,
-              T * K, rank, _ptr(px.peer_recv), _ptr(px.peer_counts), _ptr(slot_idx), st)
+              T * K, rank, _ptr(px.peer_recv), _ptr(px.peer_counts), _ptr(slot_idx), ctypes.c_void_p(px.status_ptr), 110, st)
     px.signal(px.KIND_DATA_D)
     px.wait(px.KIND_DATA_D, 1)                    # every source's rows and counts have landed here
     plan, nums, ep_recv = kern.exchange_plan(px.counts_local.view(R, E_l), R, E_l, px.C, nums_type)

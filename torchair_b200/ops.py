@@ -533,13 +533,57 @@ def fused_down_combine(hq, w2, s2, hs, group_list, group_list_type, expert_ids, 
                                     expert_scales, group_ep, R, ep_rank_id, moe_expert_num, shared_expert_x)
 
 
+def _device(device):
+    return torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+
+
 def gmm_status(device=None) -> int:
-    """Synchronises the current stream and returns the GEMM kernels' device status word (0 = fine)."""
-    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    """Synchronises the current stream and returns the GEMM kernels' device status word: 0, or the code of the first
+    bounded wait that gave up since the last gmm_status_reset (raises RuntimeError in that case)."""
+    dev = _device(device)
     with torch.cuda.device(dev):
         st = ctypes.c_int(0)
         _lib.call("tab_gmm_status", ctypes.byref(st), ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
         return int(st.value)
+
+
+def gmm_status_reset(device=None) -> None:
+    """Clears the GEMM kernels' sticky status word (synchronises the current stream)."""
+    dev = _device(device)
+    with torch.cuda.device(dev):
+        _lib.call("tab_gmm_status_reset", ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+
+
+def routing_status(device=None) -> int:
+    """Synchronises the current stream, returns and clears the routing kernels' status word: bit 0 = an expert id
+    outside the valid range was clamped, bit 1 = a row_idx value outside [0, T*K) was skipped.  Does not raise."""
+    dev = _device(device)
+    with torch.cuda.device(dev):
+        st = ctypes.c_int(0)
+        rc = _lib.load().tab_routing_status(ctypes.byref(st), ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+        if rc != 0 and st.value == 0:
+            raise RuntimeError(f"tab_routing_status failed ({rc}): {_lib.last_error()}")
+        return int(st.value)
+
+
+def check_status(device=None) -> None:
+    """Raises RuntimeError if, since the last check, a bounded wait inside a GEMM or a peer-memory exchange gave up or
+    a routing kernel met an index out of range.  Synchronises the device: call it where the step synchronises anyway."""
+    st = routing_status(device)
+    if st:
+        raise RuntimeError(f"routing kernels met indices out of range (status {st}): " + _lib.last_error())
+    dev = _device(device)
+    with torch.cuda.device(dev):
+        st_ = ctypes.c_int(0)
+        rc = _lib.load().tab_gmm_status(ctypes.byref(st_), ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+        if rc != 0:
+            msg = _lib.last_error()
+            if st_.value:
+                gmm_status_reset(dev)
+            raise RuntimeError(f"grouped GEMM status {st_.value}: {msg}")
+    st = ep.peer_status()
+    if st:
+        raise RuntimeError(f"peer-memory exchange status {st}: a flag wait ran out of time or a slot overflowed")
 
 
 
