@@ -8,11 +8,18 @@
 One step = one pass of the layer (dispatch with per-token int8 quantisation -> gate_up grouped GEMM with the
 dequant+SwiGLU+requant epilogue -> down grouped GEMM -> combine) over one batch of seeded synthetic tokens.
 N = 1 runs the decode shape with all 256 experts local (256 tokens, hidden 7168, top-8, intermediate 2048);
-N > 1 runs the expert-parallel decode shape (128 tokens per rank, 256/N experts per rank, NCCL all-to-all).
+N > 1 runs the expert-parallel decode shape (128 tokens per rank, 256/N experts per rank).
 Prints ONE JSON line on rank 0.
+
+A timed block is exactly --steps steps between two barrier + synchronize pairs, timed with CUDA events, maximum over
+ranks; blocks are repeated until about a second has been measured and the median block is reported (`repeats`), so
+that the clock sampler sees the GPU under load.  At N = 1 the line also carries, under roofline.others, the kernels
+that the decode shape cannot show at a meaningful size: both grouped GEMMs on two tensor-bound shapes and the row
+kernels at 65536 x 7168, each timed inside a CUDA graph in the same process.
 """
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -26,24 +33,10 @@ if ROOT not in sys.path:
 
 METRIC = "int8_moe_layer_tokens_per_s"
 UNIT = "tokens/s"
-
-
-def parse_args():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--seed", type=int, default=0)
-    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (N=1)")
-    ap.add_argument("--ep-transport", default="peer", choices=["peer", "nccl"],
-                    help="N > 1: rows move by this library's peer-memory kernels (default) or by NCCL all-to-all")
-    ap.add_argument("--kernels", action="store_true",
-                    help="also time every kernel of the path alone and write the table to stderr (study aid, N=1)")
-    ap.add_argument("--workload", default="auto", choices=["auto", "cfg3"] + sorted(EXTRA_WORKLOADS),
-                    help="auto = the headline configuration for this GPU count; the others are single-GPU study cases")
-    return ap.parse_args()
-
+SCALING = "strong"
+SCALING_NOTE = ("the bytes that bound a step -- this rank's int8 expert weights -- are sharded, 1/N per rank (strong); tokens "
+                "per rank are fixed, so the token count grows with N; N=1 runs the all-experts-local shape (256 tokens). "
+                "stream_frac = per-rank weight bytes / step time / HBM peak is comparable across N")
 
 # single-GPU study cases: name -> (description, T, H, E, K, I, zipf exponent)
 EXTRA_WORKLOADS = {
@@ -56,12 +49,30 @@ EXTRA_WORKLOADS = {
     "cfg4": ("cfg4: Qwen3-235B-A22B shape, 4096 tokens, 128 experts local", 4096, 4096, 128, 8, 1536, 0.0),
 }
 
-
 # expert-parallel prefill cases (tokens per rank, total experts): usable at N > 1
 EP_WORKLOADS = {
     "cfg3": ("cfg3: expert-parallel prefill with Zipf(1.2) routing skew, DeepSeek-V3 shape, 8192 tokens/rank", 8192, 7168, 256, 8, 2048, 1.2),
     "cfg4": ("cfg4: Qwen3-235B-A22B shape, 4096 tokens/rank", 4096, 4096, 128, 8, 1536, 0.0),
 }
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (N=1)")
+    ap.add_argument("--no-others", action="store_true",
+                    help="N=1: skip the tensor-bound GEMM shapes and the row kernels under roofline.others")
+    ap.add_argument("--ep-transport", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: rows move by this library's peer-memory kernels (default) or by NCCL all-to-all")
+    ap.add_argument("--kernels", action="store_true",
+                    help="also write the per-kernel table of this workload to stderr (study aid, N=1)")
+    ap.add_argument("--workload", default="auto", choices=["auto", "cfg3"] + sorted(EXTRA_WORKLOADS),
+                    help="auto = the headline configuration for this GPU count; the others are single-GPU study cases")
+    return ap.parse_args()
 
 
 def workload(n_gpus, name="auto"):
@@ -79,39 +90,95 @@ def workload(n_gpus, name="auto"):
             128, 7168, 256, 8, 2048, 0.0)
 
 
+def config_dict(name, T, H, E, K, I, world):
+    return {"workload": name, "tokens_per_rank": T, "hidden": H, "experts": E, "experts_per_rank": E // world, "top_k": K,
+            "intermediate": I, "parallelism": f"ep{world}"}
+
+
 # ---------------------------------------------------------------------------------------------------
-# CPU arm: the oracle on the host cores, on a bounded sample of the workload
+# CPU arm: the oracle's formulas on the host cores
 # ---------------------------------------------------------------------------------------------------
-def cpu_sample_config(n_gpus=1):
-    """A bounded sample with the workload's rows per expert and expert shape.  N = 1: 32 tokens routed top-8 over 32
-    experts (1/8 of the 256-token / 256-expert layer).  N > 1: a 32-expert slice of one rank's experts with the tokens
-    scaled alike (128 tokens per rank spread over 256/N local experts)."""
+def _host_weights(cfg, seed):
+    """Weights for the CPU arm.  Eight experts are drawn from the seeded generator; the others are rolled copies of
+    them (same value distribution; drawing 11 GB from a serial generator would take a minute and times nothing)."""
+    import torch
     from oracle import moe_oracle as O
-    if n_gpus == 1:
-        return O.MoeConfig("cfg1_sample", 32, 7168, 32, 8, 2048), "1/8 of the 256-token/256-expert layer at the same rows per expert"
-    e_l = 256 // n_gpus
-    e_s = min(e_l, 32)
-    t_s = max(8, 128 * e_s // e_l)
-    return (O.MoeConfig("cfg2_sample", t_s, 7168, e_s, 8, 2048),
-            f"{e_s} of the {e_l} experts of one rank with {t_s} of its 128 tokens (same rows per expert)")
+    base = O.make_weights(cfg, seed, experts=range(min(8, cfg.E)))
+    if cfg.E <= 8:
+        return base
+    w1 = torch.empty((cfg.E, cfg.H, 2 * cfg.I), dtype=torch.int8)
+    w2 = torch.empty((cfg.E, cfg.I, cfg.H), dtype=torch.int8)
+    s1 = torch.empty((cfg.E, 2 * cfg.I))
+    s2 = torch.empty((cfg.E, cfg.H))
+    for e in range(cfg.E):
+        b, sh = e % 8, e // 8
+        w1[e] = torch.roll(base.w1[b], sh, 0)
+        w2[e] = torch.roll(base.w2[b], sh, 0)
+        s1[e] = torch.roll(base.s1[b], sh, 0)
+        s2[e] = torch.roll(base.s2[b], sh, 0)
+    return O.MoeWeights(w1, s1, w2, s2)
 
 
-def run_cpu(steps, warmup, seed, n_gpus=1):
+def _host_ram_available():
+    try:
+        import psutil
+        return int(psutil.virtual_memory().available)
+    except Exception:
+        return 0
+
+
+def run_cpu(steps, warmup, seed, n_gpus=1, budget_s=150.0):
+    """Times the oracle on the full configuration of this GPU count (all ranks simulated in one process) when the host
+    holds its weights and the run fits the time budget; else on a sample with the same rows per expert."""
     import torch
     from oracle import moe_oracle as O
     torch.set_num_threads(os.cpu_count() or 1)
-    cfg, what = cpu_sample_config(n_gpus)
-    w = O.make_weights(cfg, seed)
-    x, ids, wt = O.make_tokens(cfg, seed)
+    saved = O.SILU_IMPL
+    O.SILU_IMPL = "libm"                 # the literal eager-torch formula (F.silu); parity tests use the deterministic restatement
+    try:
+        return _run_cpu(torch, O, steps, warmup, seed, n_gpus, budget_s)
+    finally:
+        O.SILU_IMPL = saved
+
+
+def _run_cpu(torch, O, steps, warmup, seed, n_gpus, budget_s):
+    name, T, H, E, K, I, zipf = workload(n_gpus)
+    full = O.MoeConfig("full", T, H, E, K, I, zipf_s=zipf)
+    weight_bytes = E * 3 * H * I
+    ranks = n_gpus
+    what = f"the full configuration ({T * ranks} tokens over {E} experts, {weight_bytes / 1e9:.2f} GB of int8 weights on the host)"
+    cfg = full
+    if _host_ram_available() < 2.3 * weight_bytes:
+        cfg = None
+    if cfg is not None:
+        w = _host_weights(cfg, seed)
+        toks = [O.make_tokens(cfg, seed, r) for r in range(ranks)]
+        xs, ids, wts = zip(*toks)
+        t0 = time.perf_counter()
+        O.moe_layer(xs, ids, wts, w)
+        first = time.perf_counter() - t0
+        if first * (steps + warmup) > budget_s:
+            cfg = None
+            del w
+    if cfg is None:
+        e_s = 32
+        t_s = max(8, T * ranks * e_s // E)
+        cfg = O.MoeConfig("sample", t_s, H, e_s, K, I)
+        ranks = 1
+        what = (f"a sample: {t_s} tokens over {e_s} of the {E} experts (the same rows per expert), because the full configuration "
+                "does not fit the host's memory or the time budget")
+        w = _host_weights(cfg, seed)
+        xs, ids, wts = zip(*[O.make_tokens(cfg, seed, 0)])
     for _ in range(warmup):
-        O.moe_layer([x], [ids], [wt], w)
+        O.moe_layer(xs, ids, wts, w)
     t0 = time.perf_counter()
     for _ in range(steps):
-        O.moe_layer([x], [ids], [wt], w)
+        O.moe_layer(xs, ids, wts, w)
     dt = time.perf_counter() - t0
-    return {"value": cfg.T * steps / dt, "ms_per_step": dt / steps * 1e3, "cores": torch.get_num_threads(),
-            "sample": f"{cfg.T} tokens top-{cfg.K} over {cfg.E} experts (hidden {cfg.H}, intermediate {cfg.I}): {what}; "
-                      f"{steps} passes after {warmup} warm-up",
+    tokens = cfg.T * ranks
+    return {"value": tokens * steps / dt, "ms_per_step": dt / steps * 1e3, "cores": torch.get_num_threads(),
+            "full_config": cfg is full,
+            "sample": f"{what}; {steps} passes after {warmup} warm-up; eager torch on CPU (int8 matmul, F.silu)",
             "cpu_model": _cpu_model(), "torch": torch.__version__}
 
 
@@ -129,16 +196,15 @@ def reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 100))         # a pass is ~0.2 s of CPU work: the whole run stays well under a minute
-    warmup = max(1, min(args.warmup, 3))
-    r = run_cpu(steps, warmup, args.seed, args.gpus)
-    name = workload(args.gpus)[0]
-    line = {"impl": "reference", "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
-            "warmup": warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-            "config": {"workload": name, "sample": r["sample"]},
+    r = run_cpu(args.steps, args.warmup, args.seed, args.gpus)
+    name, T, H, E, K, I, _ = workload(args.gpus)
+    cfg = config_dict(name, T, H, E, K, I, args.gpus)
+    cfg["sample"] = r["sample"]
+    line = {"impl": "reference", "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": SCALING,
+            "vs_baseline": None, "dtype": "int8", "data": "synthetic", "config": cfg,
             "cpu_baseline": {"value": r["value"], "unit": UNIT, "cores": r["cores"], "kind": "port", "sample": r["sample"],
-                             "cpu_model": r["cpu_model"], "torch": r["torch"]},
+                             "full_config": r["full_config"], "cpu_model": r["cpu_model"], "torch": r["torch"]},
             "e2e": {"value": r["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0,
             "note": "the reference's arithmetic for this path is closed vendor code; this arm times its op formulas "
@@ -196,11 +262,162 @@ class ClockSampler:
 # ---------------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------------
+class Timer:
+    """Device timing with CUDA events on the current stream."""
+
+    def __init__(self, torch, windows):
+        self.torch = torch
+        self.windows = windows
+
+    def each(self, fn, reps):
+        torch = self.torch
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        times = []
+        t_a = time.time()
+        for _ in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            b.synchronize()
+            times.append(a.elapsed_time(b))
+        self.windows.append((t_a, time.time()))
+        return statistics.median(times)
+
+    def launches(self, fn, reps, inner=5):
+        """Device time of one call of fn: `inner` calls are captured into one CUDA graph and the replays are timed with
+        events, so that the host's per-call work (allocation, ctypes, launch latency) is not counted as kernel time."""
+        torch = self.torch
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        g_ = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g_):
+            for _ in range(inner):
+                fn()
+        g_.replay()
+        torch.cuda.synchronize()
+        times = []
+        t_a = time.time()
+        for _ in range(max(5, reps // inner)):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            g_.replay()
+            b.record()
+            b.synchronize()
+            times.append(a.elapsed_time(b) / inner)
+        self.windows.append((t_a, time.time()))
+        del g_
+        return statistics.median(times)
+
+
+def gemm_pair(torch, timer, dev, spec, seed, reps, peak_tops, peak_gbs, row_kernels):
+    """Both grouped GEMMs of the layer (gate_up with its fused epilogue, down) on one single-GPU shape, each timed inside
+    a CUDA graph; optionally the row kernels of the path on the same rows."""
+    import torchair_b200
+    from oracle import moe_oracle as O
+    npu = torch.ops.npu
+    desc, T, H, E, K, I, zipf = spec
+    cfg = O.MoeConfig("study", T, H, E, K, I, zipf_s=zipf)
+    g = torch.Generator(device=dev).manual_seed(seed * 100003 + 17)
+    w1 = torch.randint(-127, 128, (E, H, 2 * I), generator=g, dtype=torch.int8, device=dev)
+    w2 = torch.randint(-127, 128, (E, I, H), generator=g, dtype=torch.int8, device=dev)
+    s1 = torch.rand(E, 2 * I, generator=g, device=dev) * 9e-3 + 1e-3
+    s2 = torch.rand(E, H, generator=g, device=dev) * 9e-3 + 1e-3
+    x, ids, wt = (t.to(dev) for t in O.make_tokens(cfg, seed))
+    ex, xs, expand_idx, nums, ep_recv, _, _ = npu.npu_moe_distribute_dispatch(x, ids, "", 1, 0, E, quant_mode=2)
+    M = ex.shape[0]
+    hq, hs = npu.npu_grouped_matmul_swiglu_quant_v2(ex, [w1], [s1], xs, nums, group_list_type=1)
+    hit = int((nums > 0).sum().item())
+    ops_up, ops_down = 2.0 * M * H * 2 * I, 2.0 * M * I * H
+    bytes_up = hit * H * 2 * I + M * H + 2 * M * I * 4 + M * I + hit * 2 * I * 4 + M * 8      # weights, rows, fp32 h out and back, int8 out
+    bytes_down = hit * I * H + M * I + M * H * 2 + hit * H * 4 + M * 4
+    ms_up = timer.launches(lambda: npu.npu_grouped_matmul_swiglu_quant_v2(ex, [w1], [s1], xs, nums, group_list_type=1), reps)
+    down = lambda: npu.npu_grouped_matmul([hq], [w2], scale=[s2], per_token_scale=[hs], group_list=nums, split_item=2,
+                                          group_type=0, group_list_type=1, output_dtype=15)
+    ms_down = timer.launches(down, reps)
+
+    def tensor_entry(ms, ops, nbytes):
+        tops = ops / (ms * 1e-3) / 1e12
+        return {"ms": ms, "int8_tops": tops, "frac": tops / peak_tops, "frac_of_nominal_4500": tops / 4500.0,
+                "GB/s": nbytes / (ms * 1e-3) / 1e9, "ops": ops, "bytes": nbytes}
+    out = {"workload": desc, "rows": M, "experts_hit": hit, "bound": "tensor", "unit": "TOP/s", "peak": peak_tops,
+           "gate_up_fused(gemm+swiglu+requant)": tensor_entry(ms_up, ops_up, bytes_up), "down": tensor_entry(ms_down, ops_down, bytes_down)}
+    if row_kernels:
+        y = down()[0]
+        row_idx = torch.arange(T * K, dtype=torch.int32, device=dev).view(K, T).t().contiguous()
+        exb = x[torch.arange(M, device=dev) % T].contiguous()                  # [M, H] 16-bit rows for the quantiser
+        h32 = npu.npu_grouped_matmul([ex], [w1], group_list=nums, split_item=2, group_type=0, group_list_type=1, output_dtype=3)[0]
+        hb = (h32.float() * (xs[:, None] * 5.5e-3)).to(torch.bfloat16)         # [M, 2I] gate|up values as the layer's dequantisation spreads them
+        table = {
+            "init_routing(sort+gather)": (lambda: npu.npu_moe_init_routing(x, row_idx, ids, T), 2 * T * H + 2 * M * H + 24 * M),
+            "dynamic_quant": (lambda: npu.npu_dynamic_quant(exb), 2 * M * H + M * H + 4 * M),
+            "dispatch_pack(sort+quant+scatter)": (lambda: npu.npu_moe_distribute_dispatch(x, ids, "", 1, 0, E, quant_mode=2),
+                                                  2 * T * H + M * H + 4 * M),
+            "swiglu": (lambda: npu.npu_swiglu(hb), 2 * M * 2 * I + 2 * M * I),
+            "dequant_swiglu_quant": (lambda: npu.npu_dequant_swiglu_quant(h32, weight_scale=s1, activation_scale=xs, group_index=nums,
+                                                                         activate_left=True, quant_mode=1), M * (8 * I + I + 8)),
+            "combine": (lambda: npu.npu_moe_distribute_combine(y, ids, expand_idx, ep_recv, wt, "", 1, 0, E), 2 * M * H + 4 * M + 2 * T * H),
+        }
+        rows = {}
+        for k, (fn, nbytes) in table.items():
+            ms = timer.launches(fn, reps)
+            gbs = nbytes / (ms * 1e-3) / 1e9
+            rows[k] = {"ms": ms, "GB/s": gbs, "frac": gbs / peak_gbs, "bytes": nbytes}
+        out["row_kernels"] = {"rows": M, "cols": H, "bound": "hbm", "unit": "GB/s", "peak": peak_gbs, "kernels": rows}
+    torchair_b200.check_status(dev)
+    del w1, w2, ex, hq
+    torch.cuda.empty_cache()
+    return out
+
+
+def check_layer(torch, dist, world, rank, dev, layer, x_d, ids_d, wt_d, w1, s1, w2, s2, E):
+    """Before anything is timed: the fused and the unfused layer must agree bit for bit on every rank, and the rows of
+    two of this rank's experts (gate_up int8 + scales, down output) must equal the CPU formulas evaluated on the same
+    received rows."""
+    from oracle import moe_oracle as O
+    npu = torch.ops.npu
+    out_f = layer(x_d, ids_d, wt_d, fused=True)
+    out_u = layer(x_d, ids_d, wt_d, fused=False)
+    same = bool(torch.equal(out_f, out_u))
+    ex, xs, expand_idx, nums, ep_recv, _, _ = npu.npu_moe_distribute_dispatch(x_d, ids_d, "ep", world, rank, E, quant_mode=2)
+    hq, hs = npu.npu_grouped_matmul_swiglu_quant_v2(ex, [w1], [s1], xs, nums, group_list_type=1)
+    y = npu.npu_grouped_matmul([hq], [w2], scale=[s2], per_token_scale=[hs], group_list=nums, split_item=2, group_type=0,
+                               group_list_type=1, output_dtype=15)[0]
+    out_c = npu.npu_moe_distribute_combine(y, ids_d, expand_idx, ep_recv, wt_d, "ep", world, rank, E)
+    same = same and bool(torch.equal(out_c, out_u))
+    nums_h = nums.cpu()
+    starts = torch.cumsum(nums_h, 0) - nums_h
+    hit = [int(e) for e in torch.nonzero(nums_h > 0).reshape(-1)]
+    picked = sorted({hit[0], hit[-1]}) if hit else []
+    rows_checked, oracle_ok = 0, True
+    for e in picked:
+        s0, c = int(starts[e]), int(nums_h[e])
+        c = min(c, 64)
+        we = O.MoeWeights(w1[e:e + 1].cpu(), s1[e:e + 1].cpu(), w2[e:e + 1].cpu(), s2[e:e + 1].cpu())
+        col = {}
+        yref = O.expert_ffn(ex[s0:s0 + c].cpu(), xs[s0:s0 + c].cpu(), torch.tensor([c]), we, col)
+        oracle_ok = oracle_ok and torch.equal(hq[s0:s0 + c].cpu(), col["hq"][:c]) and torch.equal(hs[s0:s0 + c].cpu(), col["hs"][:c]) \
+            and torch.equal(y[s0:s0 + c].cpu(), yref[:c])
+        rows_checked += c
+    flags = torch.tensor([int(same), int(oracle_ok)], device=dev)
+    if world > 1:
+        dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+    ok_same, ok_oracle = bool(flags[0].item()), bool(flags[1].item())
+    if not (ok_same and ok_oracle):
+        raise RuntimeError(f"rank {rank}: output check failed before timing (fused == unfused on all ranks: {ok_same}; "
+                           f"sampled experts equal the CPU formulas on all ranks: {ok_oracle})")
+    return {"fused_equals_unfused_bit_for_bit": True, "ranks": world, "experts_vs_cpu_formulas": picked, "rows_vs_cpu_formulas": rows_checked,
+            "compared": "int8 gate_up output, its scales and the 16-bit down output of the sampled experts: equal"}
+
+
 def gpu_arm(args):
     import torch
     import torch.distributed as dist
     import torchair_b200
-    from torchair_b200 import ep
+    from torchair_b200 import _lib, ep
     from torchair_b200.layer import moe_layer
     from oracle import moe_oracle as O
 
@@ -227,13 +444,27 @@ def gpu_arm(args):
     w2 = torch.randint(-127, 128, (E_l, I, H), generator=g, dtype=torch.int8, device=dev)
     s1 = torch.rand(E_l, 2 * I, generator=g, device=dev) * 9e-3 + 1e-3
     s2 = torch.rand(E_l, H, generator=g, device=dev) * 9e-3 + 1e-3
-    x_h, ids_h, wt_h = O.make_tokens(cfg, args.seed, rank)
-    x_h, ids_h, wt_h = x_h.pin_memory(), ids_h.pin_memory(), wt_h.pin_memory()
-    out_h = torch.empty((T, H), dtype=torch.bfloat16).pin_memory()
-    x_d, ids_d, wt_d = x_h.to(dev), ids_h.to(dev), wt_h.to(dev)
+    x_src, ids_src, wt_src = O.make_tokens(cfg, args.seed, rank)
 
-    def layer(x, ids, wt):
-        return moe_layer(x, ids, wt, w1, s1, w2, s2, group_ep="ep", ep_world_size=world, ep_rank_id=rank, moe_expert_num=E)
+    # the step's inputs live in ONE pinned host buffer and one device buffer per set, so that a step's host-to-device
+    # transfer is a single copy: [x bf16 | expert ids int32 | routing weights fp32], each part 256-byte aligned
+    al = lambda n: (n + 255) // 256 * 256
+    nx, ni, nw = x_src.numel() * 2, ids_src.numel() * 4, wt_src.numel() * 4
+    off_i, off_w, in_bytes = al(nx), al(nx) + al(ni), al(nx) + al(ni) + al(nw)
+    in_h = torch.empty(in_bytes, dtype=torch.uint8).pin_memory()
+
+    def views(buf):
+        return (buf[:nx].view(torch.bfloat16).view(T, H), buf[off_i:off_i + ni].view(torch.int32).view(T, K),
+                buf[off_w:off_w + nw].view(torch.float32).view(T, K))
+    for dst, src in zip(views(in_h), (x_src, ids_src, wt_src)):
+        dst.copy_(src)
+    NSETS = 3
+    in_d = [in_h.to(dev) for _ in range(NSETS)]
+    x_d, ids_d, wt_d = views(in_d[0])
+    out_h = [torch.empty((T, H), dtype=torch.bfloat16).pin_memory() for _ in range(NSETS)]
+
+    def layer(x, ids, wt, fused=True):
+        return moe_layer(x, ids, wt, w1, s1, w2, s2, group_ep="ep", ep_world_size=world, ep_rank_id=rank, moe_expert_num=E, fused=fused)
 
     def sync_all():
         if world > 1:
@@ -242,23 +473,39 @@ def gpu_arm(args):
 
     sampler = ClockSampler(local_rank) if rank == 0 else None
     windows = []
+    timer = Timer(torch, windows)
 
-    # warm-up (also fills the packed-weight cache); single rank: capture the layer into one CUDA graph
-    for _ in range(max(args.warmup, 3)):
-        out = layer(x_d, ids_d, wt_d)
+    # warm-up (also fills the packed-weight cache), then the output check, then capture
+    for _ in range(3):
+        layer(x_d, ids_d, wt_d)
     torch.cuda.synchronize()
-    graph = None
-    if world == 1 or args.ep_transport == "peer":     # the peer-memory exchange has no host read: one graph per rank
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            out = layer(x_d, ids_d, wt_d)
-        for _ in range(3):
-            graph.replay()
+    checked = check_layer(torch, dist, world, rank, dev, layer, x_d, ids_d, wt_d, w1, s1, w2, s2, E)
+    torchair_b200.check_status(dev)
+
+    use_graph = world == 1 or args.ep_transport == "peer"     # the peer-memory exchange has no host read: one graph per rank
+    graphs, outs = [], []
+    launches_per_step = None
+    for b in range(NSETS if use_graph else 0):
+        gr = torch.cuda.CUDAGraph()
+        c0 = _lib.launch_count()
+        with torch.cuda.graph(gr):
+            o = layer(*views(in_d[b]))
+        if launches_per_step is None:
+            launches_per_step = _lib.launch_count() - c0      # this library's kernels recorded into one step's graph
+        graphs.append(gr)
+        outs.append(o)
+    if not use_graph:
         torch.cuda.synchronize()
+        c0 = _lib.launch_count()
+        layer(x_d, ids_d, wt_d)
+        launches_per_step = _lib.launch_count() - c0
+    for gr in graphs:
+        gr.replay()
+    torch.cuda.synchronize()
 
     def step_resident():
-        if graph is not None:
-            graph.replay()
+        if use_graph:
+            graphs[0].replay()
         else:
             layer(x_d, ids_d, wt_d)
 
@@ -270,7 +517,7 @@ def gpu_arm(args):
         for _ in range(steps):
             fn()
         if finish is not None:
-            finish()                 # the timed stream waits for the last result to reach the host buffer
+            finish()                 # the timed stream waits for the last results to reach the host buffers
         e1.record()
         torch.cuda.synchronize()
         t_b = time.time()
@@ -282,70 +529,73 @@ def gpu_arm(args):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
+    def timed_blocks(fn, steps, finish=None, target_ms=1000.0):
+        """Blocks of exactly `steps` steps; their number follows from the first block (a maximum over ranks, so every rank
+        computes the same count) so that about a second is measured in all; the median block is the result."""
+        first = timed(fn, steps, finish)
+        repeats = int(max(3, min(400, math.ceil(target_ms / max(first, 1e-3)))))
+        blocks = [first] + [timed(fn, steps, finish) for _ in range(repeats - 1)]
+        return statistics.median(blocks), blocks
+
     # (1) device-resident inputs
-    for _ in range(args.warmup):
+    for _ in range(max(args.warmup, 3)):
         step_resident()
-    total_ms = timed(step_resident, args.steps)
+    total_ms, blocks = timed_blocks(step_resident, args.steps)
     ms_per_step = total_ms / args.steps
     value = T * world * args.steps / (total_ms * 1e-3)
 
-    # (2) end to end through the public ops with host buffers: H2D of the step's inputs, layer, D2H of the result.
-    # With a captured layer the three stages of consecutive steps overlap on three streams over two buffer sets (copy in
-    # step s+1 while step s computes and step s-1 copies out); the caller reads a result one step after it was issued.
+    # (2) end to end through the public ops with host buffers: one H2D copy of the step's inputs, the layer, one D2H copy of
+    # the result.  With a captured layer the three stages of consecutive steps overlap on three streams over three buffer
+    # sets; the host waits for the result of the step issued two steps earlier, so the device queue never runs dry.
     finish_e2e = None
-    if graph is not None:
-        x_d2, ids_d2, wt_d2 = x_d.clone(), ids_d.clone(), wt_d.clone()
-        out_h2 = torch.empty_like(out_h).pin_memory()
-        graph2 = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph2):
-            out2 = layer(x_d2, ids_d2, wt_d2)
-        sets = [(x_d, ids_d, wt_d, graph, out, out_h), (x_d2, ids_d2, wt_d2, graph2, out2, out_h2)]
+    if use_graph:
         copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
-        ev_in = [torch.cuda.Event(), torch.cuda.Event()]
-        ev_comp = [torch.cuda.Event(), torch.cuda.Event()]
-        ev_out = [torch.cuda.Event(), torch.cuda.Event()]
+        ev_in = [torch.cuda.Event() for _ in range(NSETS)]
+        ev_comp = [torch.cuda.Event() for _ in range(NSETS)]
+        ev_out = [torch.cuda.Event() for _ in range(NSETS)]
         state = {"s": 0}
 
         def step_e2e():
             s_ = state["s"]
-            b = s_ & 1
-            xd, idd, wtd, g, o, oh = sets[b]
+            b = s_ % NSETS
             main = torch.cuda.current_stream()
             with torch.cuda.stream(copy_in):
                 copy_in.wait_event(ev_comp[b])          # this set's previous compute has consumed its inputs
-                xd.copy_(x_h, non_blocking=True)
-                idd.copy_(ids_h, non_blocking=True)
-                wtd.copy_(wt_h, non_blocking=True)
+                in_d[b].copy_(in_h, non_blocking=True)
                 ev_in[b].record(copy_in)
             main.wait_event(ev_in[b])
             main.wait_event(ev_out[b])                  # this set's previous result has left the device
-            g.replay()
+            graphs[b].replay()
             ev_comp[b].record(main)
             with torch.cuda.stream(copy_out):
                 copy_out.wait_event(ev_comp[b])
-                oh.copy_(o, non_blocking=True)
+                out_h[b].copy_(outs[b], non_blocking=True)
                 ev_out[b].record(copy_out)
-            if s_ >= 1:
-                ev_out[b ^ 1].synchronize()             # the caller reads the previous step's result
+            if s_ >= 2:
+                ev_out[(s_ - 2) % NSETS].synchronize()  # the caller reads the result of the step issued two steps ago
             state["s"] = s_ + 1
 
         def finish_e2e():
-            last = (state["s"] - 1) & 1
-            torch.cuda.current_stream().wait_event(ev_out[last])
+            main = torch.cuda.current_stream()
+            for k in (1, 2):
+                if state["s"] - k >= 0:
+                    main.wait_event(ev_out[(state["s"] - k) % NSETS])
     else:
         def step_e2e():
-            x_d.copy_(x_h, non_blocking=True)
-            ids_d.copy_(ids_h, non_blocking=True)
-            wt_d.copy_(wt_h, non_blocking=True)
-            out_h.copy_(layer(x_d, ids_d, wt_d), non_blocking=True)
+            in_d[0].copy_(in_h, non_blocking=True)
+            out_h[0].copy_(layer(x_d, ids_d, wt_d), non_blocking=True)
             torch.cuda.current_stream().synchronize()     # the caller reads the result every step
 
-    for _ in range(args.warmup):
+    for _ in range(max(args.warmup, 3)):
         step_e2e()
-    e2e_ms = timed(step_e2e, args.steps, finish_e2e)
+    e2e_ms, e2e_blocks = timed_blocks(step_e2e, args.steps, finish_e2e)
     e2e_value = T * world * args.steps / (e2e_ms * 1e-3)
-    h2d = x_h.numel() * 2 + ids_h.numel() * 4 + wt_h.numel() * 4
-    d2h = out_h.numel() * 2
+    h2d = nx + ni + nw
+    d2h = out_h[0].numel() * 2
+    if use_graph:                      # the pipelined result must be the layer's result
+        torch.cuda.synchronize()
+        if not torch.equal(out_h[(state["s"] - 1) % NSETS], outs[0].cpu()):
+            raise RuntimeError("the end-to-end pipeline returned a result that differs from the resident run")
 
     # (3) the dominant kernel alone: gate_up grouped GEMM (+ its two helper launches) and the down GEMM
     npu = torch.ops.npu
@@ -354,60 +604,14 @@ def gpu_arm(args):
     hq, hs = npu.npu_grouped_matmul_swiglu_quant_v2(ex, [w1], [s1], xs, nums, group_list_type=1)
     rows = int(nums.sum().item())
     experts_hit = int((nums > 0).sum().item())
-
-    def time_each(fn, reps):
-        times = []
-        for _ in range(3):
-            fn()
-        torch.cuda.synchronize()
-        t_a = time.time()
-        for _ in range(reps):
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            fn()
-            b.record()
-            b.synchronize()
-            times.append(a.elapsed_time(b))
-        windows.append((t_a, time.time()))
-        return sum(times) / len(times)
-
-    def time_launches(fn, reps, inner=5):
-        """Average device time of one call of fn: `inner` calls are captured into one CUDA graph and the replays are timed
-        with events, so that the host's per-call work (allocation, ctypes, launch latency) is not counted as kernel time."""
-        for _ in range(3):
-            fn()
-        torch.cuda.synchronize()
-        g_ = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g_):
-            for _ in range(inner):
-                fn()
-        g_.replay()
-        torch.cuda.synchronize()
-        times = []
-        t_a = time.time()
-        for _ in range(max(3, reps // inner)):
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            g_.replay()
-            b.record()
-            b.synchronize()
-            times.append(a.elapsed_time(b) / inner)
-        windows.append((t_a, time.time()))
-        del g_
-        return sum(times) / len(times)
-
-    reps = max(10, min(args.steps, 100))
-    ms_up = time_launches(lambda: npu.npu_grouped_matmul_swiglu_quant_v2(ex, [w1], [s1], xs, nums, group_list_type=1), reps)
-    ms_down = time_launches(lambda: npu.npu_grouped_matmul([hq], [w2], scale=[s2], per_token_scale=[hs], group_list=nums, split_item=2,
-                                                           group_type=0, group_list_type=1, output_dtype=15), reps)
-    ms_disp = time_each(lambda: npu.npu_moe_distribute_dispatch(x_d, ids_d, "", 1, 0, E, quant_mode=2), reps) if world == 1 else None
+    reps = max(20, min(args.steps * 2, 100))
+    ms_up = timer.launches(lambda: npu.npu_grouped_matmul_swiglu_quant_v2(ex, [w1], [s1], xs, nums, group_list_type=1), reps)
+    ms_down = timer.launches(lambda: npu.npu_grouped_matmul([hq], [w2], scale=[s2], per_token_scale=[hs], group_list=nums, split_item=2,
+                                                            group_type=0, group_list_type=1, output_dtype=15), reps)
+    ms_disp = timer.launches(lambda: npu.npu_moe_distribute_dispatch(x_d, ids_d, "", 1, 0, E, quant_mode=2), reps) if world == 1 else None
     bytes_up = experts_hit * H * 2 * I + rows * H + rows * I * 4 + experts_hit * 2 * I * 4 + rows * 4   # weights + A + fp32 h + scales
     bytes_down = experts_hit * I * H + rows * I + rows * H * 2 + experts_hit * H * 4 + rows * 4
-    status = torchair_b200.gmm_status(dev)
-    if status != 0:
-        raise RuntimeError(f"grouped GEMM reported a timed-out wait (code {status})")
-    if ep.peer_status() != 0:
-        raise RuntimeError(f"a peer-memory flag wait ran out of time (code {ep.peer_status()})")
+    torchair_b200.check_status(dev)
 
     peaks = {}
     try:
@@ -423,95 +627,72 @@ def gpu_arm(args):
     t_hbm, t_tc = bytes_up / (peak_gbs * 1e9), ops_up / (peak_tops * 1e12)
     gbs_up = bytes_up / (ms_up * 1e-3) / 1e9
     tops_up = ops_up / (ms_up * 1e-3) / 1e12
+    hbm_source = "measured copy bandwidth (MEASURED_PEAKS.json)" if measured else "fallback 6650 GB/s"
+    tc_source = ("2 x measured bf16 GEMM burst (MEASURED_PEAKS.json); nominal int8 dense is 4500"
+                 if measured else "2 x fallback bf16 1590; nominal int8 dense is 4500")
     if t_hbm >= t_tc:
-        main = {"bound": "hbm", "achieved": gbs_up, "peak": peak_gbs, "unit": "GB/s", "frac": gbs_up / peak_gbs,
-                "peak_source": "measured copy bandwidth (MEASURED_PEAKS.json)" if measured else "fallback 6650 GB/s"}
+        main = {"bound": "hbm", "achieved": gbs_up, "peak": peak_gbs, "unit": "GB/s", "frac": gbs_up / peak_gbs, "peak_source": hbm_source}
     else:
         main = {"bound": "tensor", "achieved": tops_up, "peak": peak_tops, "unit": "TOP/s", "frac": tops_up / peak_tops,
-                "peak_source": ("2 x measured bf16 GEMM burst (MEASURED_PEAKS.json); nominal int8 dense is 4500"
-                                if measured else "2 x fallback bf16 1590; nominal int8 dense is 4500"),
-                "frac_of_nominal_4500": tops_up / 4500.0}
-    # DRAM bytes per launch from the ncu capture of the 1/8-scale decode case (profiles/gmm_i8_kernel_decode_small.md):
-    # 948.42 MB for 32 experts; traffic is one pass over each hit expert's weights, so it scales with experts_hit.
+                "peak_source": tc_source, "frac_of_nominal_4500": tops_up / 4500.0}
+    # DRAM bytes per launch, from an ncu capture of this kernel on the 1/8-scale decode case: 948.42 MB for 32 experts hit; the
+    # traffic is one pass over each hit expert's weights, so it is scaled by the experts hit
     traffic = 948.417e6 / 32 * experts_hit if (H, I) == (7168, 2048) and rows <= 16 * experts_hit else None
     roofline = dict(main)
     roofline.update({"kernel": "gmm_i8_kernel<NT,fused> gate_up (timed with its memset and requantise helper launches)",
-                     "timing": "CUDA events around replays of a CUDA graph that holds five launches of the operator",
+                     "timing": "CUDA events around replays of a CUDA graph that holds five launches of the operator; median",
                      "algorithmic_bytes": bytes_up, "algorithmic_ops": ops_up, "ms_per_launch": ms_up, "traffic": traffic,
+                     "traffic_source": None if traffic is None else "ncu dram__bytes of the 1/8-scale decode case, scaled by experts hit",
                      "GB/s": gbs_up, "int8_tops": tops_up, "rows": rows, "experts_hit": experts_hit,
                      "others": {"down_gemm": {"ms": ms_down, "GB/s": bytes_down / (ms_down * 1e-3) / 1e9,
+                                              "frac": bytes_down / (ms_down * 1e-3) / 1e9 / peak_gbs,
                                               "int8_tops": ops_down / (ms_down * 1e-3) / 1e12},
                                 "dispatch_sort_quant_scatter": None if ms_disp is None else
-                                {"ms": ms_disp, "GB/s": (2 * T * H + M * H + 4 * M) / (ms_disp * 1e-3) / 1e9}}})
+                                {"ms": ms_disp, "GB/s": (2 * T * H + M * H + 4 * M) / (ms_disp * 1e-3) / 1e9,
+                                 "note": "latency-bound at this size; the bandwidth-bound size is under row_kernels"}}})
 
-    if args.kernels and world == 1:
-        def gbs(nbytes, ms):
-            return round(nbytes / (ms * 1e-3) / 1e9, 1)
-        row_idx = torch.arange(T * K, dtype=torch.int32, device=dev).view(K, T).t().contiguous()
-        y_bf16 = npu.npu_grouped_matmul([hq], [w2], scale=[s2], per_token_scale=[hs], group_list=nums, split_item=2,
-                                        group_type=0, group_list_type=1, output_dtype=15)[0]
-        exb = x_d[torch.arange(M, device=dev) % T].contiguous()          # [M, H] bf16 rows for the quantiser
-        h32 = torch.randint(-2000000, 2000000, (min(M, 16384), 2 * I), dtype=torch.int32, device=dev)
-        hb = torch.randn((M, 2 * I), dtype=torch.float32, device=dev).to(torch.bfloat16)
-        m32 = h32.shape[0]
-        ones = torch.ones(m32, dtype=torch.float32, device=dev)
-        table = {
-            "init_routing": (time_launches(lambda: npu.npu_moe_init_routing(x_d, row_idx, ids_d, T), reps), 2 * T * H + 2 * M * H + 24 * M),
-            "dynamic_quant": (time_launches(lambda: npu.npu_dynamic_quant(exb), reps), 2 * M * H + M * H + 4 * M),
-            "dispatch_pack(sort+quant+scatter)": (time_launches(lambda: npu.npu_moe_distribute_dispatch(x_d, ids_d, "", 1, 0, E, quant_mode=2), reps),
-                                                  2 * T * H + M * H + 4 * M),
-            "swiglu_bf16": (time_launches(lambda: npu.npu_swiglu(hb), reps), 2 * M * 2 * I + 2 * M * I),
-            "dequant_swiglu_quant": (time_launches(lambda: npu.npu_dequant_swiglu_quant(h32, weight_scale=s1[:1], activation_scale=ones,
-                                                                                   activate_left=True, quant_mode=1), reps),
-                                     m32 * (8 * I + I + 8)),
-            "combine": (time_launches(lambda: npu.npu_moe_distribute_combine(y_bf16, ids_d, expand_idx, ep_recv, wt_d, "", 1, 0, E), reps),
-                        2 * M * H + 4 * M + 2 * T * H),
-            "gmm_gate_up_fused": (ms_up, bytes_up), "gmm_down": (ms_down, bytes_down),
-        }
-        # down GEMM + logit-weighted scatter-add as one operator (int32 accumulators round-trip through the workspace)
-        tok_of_row = torch.arange(M, device=dev) % T          # K rows per token; which ones does not matter for the timing
-        lg = torch.rand(M, device=dev)
-        table["gmm_down+finalize_routing"] = (
-            time_launches(lambda: npu.npu_grouped_matmul_finalize_routing(hq, w2, nums, scale=s2, pertoken_scale=hs, logit=lg,
-                                                                      row_index=tok_of_row, output_bs=T, group_list_type=1), reps),
-            experts_hit * I * H + rows * I + 2 * rows * H * 4 + T * H * 4 + experts_hit * H * 4 + rows * 16)
-        # context: what plain torch kernels reach on this GPU for write-only and copy traffic of 1 GiB
-        probe = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
-        probe2 = torch.empty_like(probe)
-        # (single eager calls: inside a graph a device-to-device copy_ becomes a copy-engine node, not the kernel)
-        table["context: torch fill (write only)"] = (time_each(lambda: probe.fill_(1), reps), probe.numel())
-        table["context: torch copy (read + write)"] = (time_each(lambda: probe2.copy_(probe), reps), 2 * probe.numel())
-        report = {k: {"ms": round(ms, 4), "GB/s": gbs(b, ms), "frac_hbm": round(gbs(b, ms) / peak_gbs, 3)} for k, (ms, b) in table.items()}
-        report["gmm_gate_up_fused"]["int8_tops"] = round(tops_up, 1)
-        report["gmm_down"]["int8_tops"] = round(ops_down / (ms_down * 1e-3) / 1e12, 1)
-        print("KERNELS " + json.dumps({"workload": name, "kernels": report}), file=sys.stderr, flush=True)
+    others_on = world == 1 and not args.no_others and args.workload == "auto"
+    if others_on:
+        # the parts of the metric that the decode shape cannot show: tensor-bound grouped GEMMs and bandwidth-bound row kernels
+        oth = roofline["others"]
+        oth["peak_sources"] = {"tensor": tc_source, "hbm": hbm_source}
+        r3 = gemm_pair(torch, timer, dev, EXTRA_WORKLOADS["cfg3_rank"], args.seed, reps, peak_tops, peak_gbs, row_kernels=True)
+        oth["row_kernels_65536x7168"] = r3.pop("row_kernels")
+        oth["prefill_gemm_cfg3_rank"] = r3
+        oth["prefill_gemm_cfg4"] = gemm_pair(torch, timer, dev, EXTRA_WORKLOADS["cfg4"], args.seed, reps, peak_tops, peak_gbs, row_kernels=False)
+    if args.kernels and world == 1 and args.workload != "auto":
+        rep = gemm_pair(torch, timer, dev, EXTRA_WORKLOADS[args.workload], args.seed, reps, peak_tops, peak_gbs, row_kernels=True)
+        print("KERNELS " + json.dumps(rep), file=sys.stderr, flush=True)
 
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        r = run_cpu(steps=50, warmup=2, seed=args.seed)     # ~10-20 s of CPU work
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and args.workload == "auto":
+        r = run_cpu(steps=10, warmup=2, seed=args.seed, n_gpus=1, budget_s=60.0)
         cpu = {"value": r["value"], "unit": UNIT, "cores": r["cores"], "kind": "port", "sample": r["sample"],
-               "cpu_model": r["cpu_model"], "torch": r["torch"]}
+               "full_config": r["full_config"], "cpu_model": r["cpu_model"], "torch": r["torch"]}
 
     if sampler is not None:
         sampler.stop()
     if rank == 0:
-        # sort x3, pack, gemm, requant, gemm, combine; nccl adds plan + permute each way; peer adds send, unpack, two plans,
-        # the return-address table (the down GEMM stores into the peers itself) and eight flag kernels
-        launches_per_step = 8 if world == 1 else (21 if args.ep_transport == "peer" else 12)
+        weight_bytes = w1.numel() + w2.numel()
+        conf = config_dict(name, T, H, E, K, I, world)
+        conf.update({"cuda_graph": use_graph, "ep_transport": None if world == 1 else args.ep_transport,
+                     "exchange": None if world == 1 else ("this library's kernels store rows into the owners' buffers over NVLink peer "
+                                                          "memory; NCCL only carries the rendezvous" if args.ep_transport == "peer"
+                                                          else "NCCL all_to_all_single"),
+                     "l2": "inputs larger than L2: every step streams this rank's int8 expert weights "
+                           f"({weight_bytes / 1e9:.2f} GB) from HBM"})
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-                "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
-                "data": "synthetic",
-                "config": {"workload": name, "tokens_per_rank": T, "hidden": H, "experts": E, "experts_per_rank": E_l, "top_k": K,
-                           "intermediate": I, "parallelism": f"ep{world}", "cuda_graph": graph is not None,
-                           "ep_transport": None if world == 1 else args.ep_transport,
-                           "l2": "inputs larger than L2: every step streams this rank's int8 expert weights "
-                                 f"({(w1.numel() + w2.numel()) / 1e9:.2f} GB) from HBM"},
+                "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": SCALING, "scaling_note": SCALING_NOTE,
+                "vs_baseline": None, "dtype": "int8", "data": "synthetic", "config": conf,
+                "repeats": len(blocks), "block_ms": {"median": total_ms, "min": min(blocks), "max": max(blocks)},
+                "stream_frac": weight_bytes / (ms_per_step * 1e-3) / 1e9 / peak_gbs,
                 "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                        "ms_per_step": e2e_ms / args.steps,
-                        "pipelining": "copy-in, compute and copy-out of consecutive steps overlap (two buffer sets)"
-                        if graph is not None else "none"},
-                "gpu_launches": launches_per_step * args.steps,
-                "roofline": roofline, "cpu_baseline": cpu,
+                        "ms_per_step": e2e_ms / args.steps, "repeats": len(e2e_blocks),
+                        "pipelining": "copy-in, compute and copy-out of consecutive steps overlap (three buffer sets); the host "
+                                      "reads a result two steps after issuing it" if use_graph else "none"},
+                "gpu_launches": launches_per_step * args.steps, "gpu_launches_per_step": launches_per_step,
+                "gpu_launches_counted": "kernels this library enqueued while one step was recorded (tab_launch_count)",
+                "checked": checked, "roofline": roofline, "cpu_baseline": cpu,
                 "clocks": sampler.summary(windows) if sampler is not None else None}
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -79,22 +79,28 @@ __global__ void __launch_bounds__(THREADS) dynamic_quant_kernel(const T* __restr
   }
 }
 
-// y[r, c] = silu(x[r, c]) * x[r, c + half]; one thread per 8 output elements, grid-stride.
+// y[r, c] = silu(x[r, c]) * x[r, c + half]; one thread per 8 output elements.  A CTA of 256 threads covers
+// 256 / tpr rows at a time with tpr threads per row (tpr = a power of two, at most 256, chosen by the host so that
+// short rows still fill the CTA); no division in the loop.
 template <typename T>
-__global__ void __launch_bounds__(256) swiglu_kernel(const T* __restrict__ x, int64_t rows, int half,
+__global__ void __launch_bounds__(256) swiglu_kernel(const T* __restrict__ x, int64_t rows, int half, int tpr_log2,
                                                      T* __restrict__ y) {
   const int chunks_per_row = half >> 3;
-  const int64_t total = rows * chunks_per_row;
-  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t r = i / chunks_per_row;
-    const int c = static_cast<int>(i - r * chunks_per_row) * 8;
-    float a[8], b[8], o[8];
-    Elem<T>::load8(x + r * 2 * half + c, a);
-    Elem<T>::load8(x + r * 2 * half + half + c, b);
+  const int tpr = 1 << tpr_log2;
+  const int rows_per_cta = 256 >> tpr_log2;
+  const int lane_in_row = threadIdx.x & (tpr - 1);
+  for (int64_t r = static_cast<int64_t>(blockIdx.x) * rows_per_cta + (threadIdx.x >> tpr_log2); r < rows;
+       r += static_cast<int64_t>(gridDim.x) * rows_per_cta) {
+    const T* xr = x + r * 2 * half;
+    T* yr = y + r * half;
+    for (int ch = lane_in_row; ch < chunks_per_row; ch += tpr) {
+      float a[8], b[8], o[8];
+      Elem<T>::load8(xr + ch * 8, a);
+      Elem<T>::load8(xr + half + ch * 8, b);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) o[k] = silu_mul(a[k], b[k]);
-    Elem<T>::store8(y + r * half + c, o);
+      for (int k = 0; k < 8; ++k) o[k] = silu_mul(a[k], b[k]);
+      Elem<T>::store8(yr + ch * 8, o);
+    }
   }
 }
 
@@ -275,17 +281,20 @@ extern "C" int tab_swiglu(const void* x, int dtype, int64_t rows, int64_t cols, 
   const int64_t half = cols / 2;
   if (half % 8 != 0 || !aligned16(x) || !aligned16(y)) return fail(TAB_ERR_ALIGNMENT, "swiglu: cols/2=%lld must be a multiple of 8 and pointers 16-byte aligned", (long long)half);
   cudaStream_t st = as_stream(stream);
-  const int64_t work = rows * (half / 8);
-  const int grid = grid_for((work + 255) / 256, 8);
+  const int64_t chunks = half / 8;
+  int tpr_log2 = 0;
+  while ((1 << tpr_log2) < chunks && tpr_log2 < 8) ++tpr_log2;
+  const int64_t ctas = (rows + (256 >> tpr_log2) - 1) / (256 >> tpr_log2);
+  const int grid = grid_for(ctas, 8);
   switch (dtype) {
     case TAB_BF16:
-      swiglu_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), rows, (int)half, static_cast<__nv_bfloat16*>(y));
+      swiglu_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), rows, (int)half, tpr_log2, static_cast<__nv_bfloat16*>(y));
       break;
     case TAB_F16:
-      swiglu_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(x), rows, (int)half, static_cast<__half*>(y));
+      swiglu_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(x), rows, (int)half, tpr_log2, static_cast<__half*>(y));
       break;
     case TAB_F32:
-      swiglu_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(x), rows, (int)half, static_cast<float*>(y));
+      swiglu_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(x), rows, (int)half, tpr_log2, static_cast<float*>(y));
       break;
     default:
       return fail(TAB_ERR_UNSUPPORTED, "swiglu: dtype %d (want 5, 6 or 15)", dtype);
