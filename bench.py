@@ -373,7 +373,7 @@ def gemm_pair(torch, timer, dev, spec, seed, reps, peak_tops, peak_gbs, row_kern
     return out
 
 
-def check_layer(torch, dist, world, rank, dev, layer, x_d, ids_d, wt_d, w1, s1, w2, s2, E):
+def check_layer(torch, dist, world, rank, dev, layer, x_d, ids_d, wt_d, w1, s1, w2, s2, E, tune):
     """Before anything is timed: the fused and the unfused layer must agree bit for bit on every rank, and the rows of
     two of this rank's experts (gate_up int8 + scales, down output) must equal the CPU formulas evaluated on the same
     received rows."""
@@ -383,9 +383,9 @@ def check_layer(torch, dist, world, rank, dev, layer, x_d, ids_d, wt_d, w1, s1, 
     out_u = layer(x_d, ids_d, wt_d, fused=False)
     same = bool(torch.equal(out_f, out_u))
     ex, xs, expand_idx, nums, ep_recv, _, _ = npu.npu_moe_distribute_dispatch(x_d, ids_d, "ep", world, rank, E, quant_mode=2)
-    hq, hs = npu.npu_grouped_matmul_swiglu_quant_v2(ex, [w1], [s1], xs, nums, group_list_type=1)
+    hq, hs = npu.npu_grouped_matmul_swiglu_quant_v2(ex, [w1], [s1], xs, nums, group_list_type=1, tuning_config=tune)
     y = npu.npu_grouped_matmul([hq], [w2], scale=[s2], per_token_scale=[hs], group_list=nums, split_item=2, group_type=0,
-                               group_list_type=1, output_dtype=15)[0]
+                               group_list_type=1, output_dtype=15, tuning_config=tune)[0]
     out_c = npu.npu_moe_distribute_combine(y, ids_d, expand_idx, ep_recv, wt_d, "ep", world, rank, E)
     same = same and bool(torch.equal(out_c, out_u))
     nums_h = nums.cpu()
@@ -479,7 +479,8 @@ def gpu_arm(args):
     for _ in range(3):
         layer(x_d, ids_d, wt_d)
     torch.cuda.synchronize()
-    checked = check_layer(torch, dist, world, rank, dev, layer, x_d, ids_d, wt_d, w1, s1, w2, s2, E)
+    tune = [max(1, -(-T * K * world // E))]       # rows an expert is expected to receive: the grouped matmuls' tiling hint
+    checked = check_layer(torch, dist, world, rank, dev, layer, x_d, ids_d, wt_d, w1, s1, w2, s2, E, tune)
     torchair_b200.check_status(dev)
 
     use_graph = world == 1 or args.ep_transport == "peer"     # the peer-memory exchange has no host read: one graph per rank
@@ -601,13 +602,14 @@ def gpu_arm(args):
     npu = torch.ops.npu
     ex, xs, expand_idx, nums, ep_recv, _, _ = npu.npu_moe_distribute_dispatch(x_d, ids_d, "ep", world, rank, E, quant_mode=2)
     M = ex.shape[0]
-    hq, hs = npu.npu_grouped_matmul_swiglu_quant_v2(ex, [w1], [s1], xs, nums, group_list_type=1)
+    hq, hs = npu.npu_grouped_matmul_swiglu_quant_v2(ex, [w1], [s1], xs, nums, group_list_type=1, tuning_config=tune)
     rows = int(nums.sum().item())
     experts_hit = int((nums > 0).sum().item())
     reps = max(20, min(args.steps * 2, 100))
-    ms_up = timer.launches(lambda: npu.npu_grouped_matmul_swiglu_quant_v2(ex, [w1], [s1], xs, nums, group_list_type=1), reps)
+    ms_up = timer.launches(lambda: npu.npu_grouped_matmul_swiglu_quant_v2(ex, [w1], [s1], xs, nums, group_list_type=1,
+                                                                          tuning_config=tune), reps)
     ms_down = timer.launches(lambda: npu.npu_grouped_matmul([hq], [w2], scale=[s2], per_token_scale=[hs], group_list=nums, split_item=2,
-                                                            group_type=0, group_list_type=1, output_dtype=15), reps)
+                                                            group_type=0, group_list_type=1, output_dtype=15, tuning_config=tune), reps)
     ms_disp = timer.launches(lambda: npu.npu_moe_distribute_dispatch(x_d, ids_d, "", 1, 0, E, quant_mode=2), reps) if world == 1 else None
     bytes_up = experts_hit * H * 2 * I + rows * H + rows * I * 4 + experts_hit * 2 * I * 4 + rows * 4   # weights + A + fp32 h + scales
     bytes_down = experts_hit * I * H + rows * I + rows * H * 2 + experts_hit * H * 4 + rows * 4

@@ -191,6 +191,20 @@ TAB_API int tab_moe_exchange_rows(const void* src, const float* src_scales, cons
  *                      total and for a row whose offset does not fit its slot), as the row table of
  *                      tab_grouped_matmul_w8a8_scatter: the down GEMM then stores its rows into the source ranks'
  *                      `ret` buffers itself and no copy kernel runs.
+ * Fused forms that save launches on the decode path (same data movement, same buffers):
+ *   tab_ep_send_rows with ack_flags != NULL: every CTA first checks, bounded, that each source's acknowledgement
+ *                      flag has reached *ack_counter (the peers have copied the previous rows out); the counter is
+ *                      advanced by the tab_ep_signal_wait that follows (its bump_counter).  On expiry ack_code goes to
+ *                      *status and the rows are sent all the same.
+ *   tab_ep_signal_wait tab_ep_signal on (peer_flags, sig_counter) followed by tab_ep_wait with pre_increment = 1 on
+ *                      (flags, wait_counter) in one launch; *bump_counter += 1 when given.
+ *   tab_ep_unpack_rows_fused  tab_moe_exchange_plan + tab_ep_unpack_rows in one launch (every CTA derives the offsets
+ *                      from recv_counts int32 [R, E_l]); rows past the received total are left untouched; when
+ *                      ack_peer_flags != NULL the CTA that finishes last performs the tab_ep_signal on
+ *                      (ack_peer_flags, ack_sig_counter); done_counter: a zero-initialised device uint32 of the caller.
+ *   tab_ep_return_plan_fused  tab_moe_exchange_plan + tab_ep_return_plan in one launch from ep_send_counts int32
+ *                      [E_l, R]; when ack_flags != NULL its first CTA also performs tab_ep_wait(pre_increment = 0) on
+ *                      (ack_flags, ack_counter) with ack_code.
  * Every flag wait is bounded (TAB_EP_WAIT_MS in the environment, read once; default 2000 ms).
  * ------------------------------------------------------------------------------------------------- */
 TAB_API int tab_ep_signal(void* const* peer_flags, void* counter, int64_t R, tab_stream_t stream);
@@ -199,7 +213,8 @@ TAB_API int tab_ep_wait(const void* flags, void* counter, int64_t R, int pre_inc
 TAB_API int tab_ep_send_rows(const void* rows, const float* scales, const int32_t* expert_counts,
                      const int32_t* expand_idx, int64_t R, int64_t E_l, int64_t slot_rows, int64_t row_bytes,
                      int64_t M, int64_t my_rank, void* const* peer_recv, void* const* peer_counts,
-                     int32_t* expand_idx_slot, int* status, int code, tab_stream_t stream);
+                     int32_t* expand_idx_slot, int* status, int code, const void* ack_flags,
+                     const void* ack_counter, int ack_code, tab_stream_t stream);
 TAB_API int tab_ep_unpack_rows(const void* recv, const int32_t* plan, int64_t R, int64_t E_l, int64_t row_bytes,
                        int64_t dst_rows, int zero_fill, void* dst, float* dst_scales, tab_stream_t stream);
 TAB_API int tab_ep_return_rows(const void* y, const int32_t* plan, int64_t R, int64_t E_l, int64_t slot_rows,
@@ -209,6 +224,17 @@ TAB_API int tab_ep_return_rows(const void* y, const int32_t* plan, int64_t R, in
 TAB_API int tab_ep_return_plan(const int32_t* plan, int64_t R, int64_t E_l, int64_t slot_rows, int64_t row_bytes,
                        int64_t max_rows, int64_t my_rank, void* const* peer_ret, uint64_t* row_dst,
                        tab_stream_t stream);
+TAB_API int tab_ep_signal_wait(void* const* peer_flags, void* sig_counter, const void* flags, void* wait_counter,
+                       int64_t R, int* status, int code, void* bump_counter, tab_stream_t stream);
+TAB_API int tab_ep_unpack_rows_fused(const void* recv, const int32_t* recv_counts, int64_t R, int64_t E_l,
+                             int64_t slot_rows, int64_t row_bytes, int64_t dst_rows, int nums_type, void* dst,
+                             float* dst_scales, int64_t* expert_token_nums, int32_t* ep_recv_count,
+                             void* const* ack_peer_flags, void* ack_sig_counter, void* done_counter,
+                             tab_stream_t stream);
+TAB_API int tab_ep_return_plan_fused(const int32_t* ep_send_counts, int64_t R, int64_t E_l, int64_t slot_rows,
+                             int64_t row_bytes, int64_t max_rows, int64_t my_rank, void* const* peer_ret,
+                             uint64_t* row_dst, const void* ack_flags, void* ack_counter, int* status, int ack_code,
+                             tab_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------
  * npu_moe_distribute_combine, receiving side (converter moe_distribute_combine.py:4-60 ->
@@ -282,6 +308,12 @@ TAB_API int tab_moe_init_routing_v2(const void* x, int x_dtype, const int32_t* e
  *   out_dtype 15 / 5: y = (float(acc) * per_token_scale[m]) * scale[e, n], scale fp32 [E, N],
  *   per_token_scale fp32 [M] (either may be NULL = 1).  Rows outside every group are left untouched.
  *   Requires Kd % 16 == 0.
+ *   expected_rows_per_group (here and in the three entry points below): the rows a group is expected to hold, for the
+ *   choice of kernel orientation and tile width on the host; 0 = unknown (M / E is assumed).  It is the first element of
+ *   the operator's tuning_config, which the converter forwards to the IR attribute of that name without defining it
+ *   (grouped_matmul.py:245,361; experiment_ops.h:3651); decision: expected rows per group.  With expert parallelism
+ *   x is sized for the worst case, so M / E can be many times what arrives and the hint matters.  Any value gives
+ *   correct results: the counts themselves are read on the device.
  *
  * tab_grouped_matmul_w8a8_scatter: the same GEMM with 16-bit output (out_dtype 15 or 5) whose row m is stored at the
  *   address row_dst[m] (device array of M addresses, 16-byte aligned rows of N elements) instead of y + m*N.  The
@@ -318,17 +350,17 @@ TAB_API int tab_prepack_weight_i8(const int8_t* weight, int64_t E, int64_t Kd, i
 TAB_API int tab_grouped_matmul_w8a8(const int8_t* x, const int8_t* packed_weight, const float* scale,
                             const float* per_token_scale, const int64_t* group_list, int group_list_type,
                             int64_t M, int64_t Kd, int64_t N, int64_t E, int out_dtype, void* y,
-                            tab_stream_t stream);
+                            int64_t expected_rows_per_group, tab_stream_t stream);
 TAB_API int tab_grouped_matmul_w8a8_scatter(const int8_t* x, const int8_t* packed_weight, const float* scale,
                                     const float* per_token_scale, const int64_t* group_list, int group_list_type,
                                     int64_t M, int64_t Kd, int64_t N, int64_t E, int out_dtype, const uint64_t* row_dst,
-                                    tab_stream_t stream);
+                                    int64_t expected_rows_per_group, tab_stream_t stream);
 TAB_API int tab_grouped_matmul_swiglu_quant_workspace_bytes(int64_t M, int64_t I, size_t* bytes);
 TAB_API int tab_grouped_matmul_swiglu_quant(const int8_t* x, const int8_t* packed_weight, const float* weight_scale,
                                     const float* x_scale, const int64_t* group_list, int group_list_type,
                                     int64_t M, int64_t Kd, int64_t I, int64_t E, int activate_left,
                                     int8_t* yq, float* y_scale, void* workspace, size_t workspace_bytes,
-                                    tab_stream_t stream);
+                                    int64_t expected_rows_per_group, tab_stream_t stream);
 TAB_API int tab_grouped_matmul_finalize_routing_workspace_bytes(int64_t M, int64_t N, size_t* bytes);
 TAB_API int tab_grouped_matmul_finalize_routing(const int8_t* x, const int8_t* packed_weight, const float* scale,
                                         const void* bias, const float* per_token_scale, const int64_t* group_list,
@@ -336,7 +368,7 @@ TAB_API int tab_grouped_matmul_finalize_routing(const int8_t* x, const int8_t* p
                                         const void* shared_input, int64_t shared_rows, float shared_input_weight,
                                         int64_t shared_input_offset, const float* logit, const void* row_index,
                                         int row_index_dtype, int64_t output_bs, float* y, void* workspace,
-                                        size_t workspace_bytes, tab_stream_t stream);
+                                        size_t workspace_bytes, int64_t expected_rows_per_group, tab_stream_t stream);
 TAB_API int tab_gmm_status(int* status_host, tab_stream_t stream);
 TAB_API int tab_gmm_status_reset(tab_stream_t stream);
 

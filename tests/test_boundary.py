@@ -42,9 +42,9 @@ def test_argument_validation_happens_before_any_cuda_call(built_library):
         ("tab_moe_combine", (one, 3, one, one, n, 4, 2, 64, one, n), "dtype"),
         ("tab_moe_exchange_rows", (one, n, one, 2, 4, 0, 0, 24, 8, 1, one, n, n), "multiple of 16"),
         ("tab_moe_exchange_plan", (one, 64, 64, 0, 1, one, one, one, n), "R*E_l"),
-        ("tab_grouped_matmul_w8a8", (one, one, n, n, one, 0, 8, 24, 64, 2, 15, one, n), "Kd"),
-        ("tab_grouped_matmul_w8a8", (one, one, n, n, one, 0, 8, 32, 64, 2000, 15, one, n), "groups"),
-        ("tab_grouped_matmul_w8a8", (one, one, n, n, one, 0, 8, 32, 64, 2, 1, one, n), "output dtype"),
+        ("tab_grouped_matmul_w8a8", (one, one, n, n, one, 0, 8, 24, 64, 2, 15, one, 0, n), "Kd"),
+        ("tab_grouped_matmul_w8a8", (one, one, n, n, one, 0, 8, 32, 64, 2000, 15, one, 0, n), "groups"),
+        ("tab_grouped_matmul_w8a8", (one, one, n, n, one, 0, 8, 32, 64, 2, 1, one, 0, n), "output dtype"),
         ("tab_prepack_weight_i8", (one, 1, 32, 32, one, n), "in-place"),
     ]
     for name, args, needle in cases:
@@ -61,7 +61,7 @@ def test_zero_sized_calls_are_no_ops(built_library):
     _lib.call("tab_dynamic_quant", n, 15, n, 0, 1024, n, n, n)
     _lib.call("tab_swiglu", n, 15, 0, 1024, n, n)
     _lib.call("tab_moe_combine", n, 15, n, n, n, 0, 8, 1024, n, n)
-    _lib.call("tab_grouped_matmul_w8a8", n, n, n, n, n, 1, 0, 1024, 1024, 8, 15, n, n)
+    _lib.call("tab_grouped_matmul_w8a8", n, n, n, n, n, 1, 0, 1024, 1024, 8, 15, n, 0, n)
 
 
 def test_ops_have_no_cpu_fallback():

@@ -309,7 +309,7 @@ def test_fused_gate_up_fp32_values_and_quantiser_through_the_c_abi(dev, M, Kd, I
     yq = torch.zeros((M, I), dtype=torch.int8, device=dev)
     ys = torch.zeros((M,), dtype=torch.float32, device=dev)
     P = lambda t: ctypes.c_void_p(t.data_ptr())
-    _lib.call("tab_grouped_matmul_swiglu_quant", P(xd), P(wp), P(wsd), P(xsd), P(cd), 1, M, Kd, I, E, 1, P(yq), P(ys), P(wsp), nbytes,
+    _lib.call("tab_grouped_matmul_swiglu_quant", P(xd), P(wp), P(wsd), P(xsd), P(cd), 1, M, Kd, I, E, 1, P(yq), P(ys), P(wsp), nbytes, 0,
               ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
     _gmm_ok(dev)
     amax_bytes = (M * 4 + 255) // 256 * 256
@@ -884,7 +884,7 @@ def test_scatter_gemm_skips_rows_without_a_destination(dev):
         xd, sd, pd, cd, dd = x.to(dev), sc.to(dev), pts.to(dev), cnt.to(dev), dst.to(dev)
         wp = ops.packed_weight(w.to(dev))
         P = lambda t: ctypes.c_void_p(t.data_ptr())
-        _lib.call("tab_grouped_matmul_w8a8_scatter", P(xd), P(wp), P(sd), P(pd), P(cd), 1, M, Kd, N, E, 15, P(dd),
+        _lib.call("tab_grouped_matmul_w8a8_scatter", P(xd), P(wp), P(sd), P(pd), P(cd), 1, M, Kd, N, E, 15, P(dd), 0,
                   ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
         _gmm_ok(dev)
         got = out.cpu()

@@ -99,7 +99,8 @@ def fuse_gate_up(gm: torch.fx.GraphModule) -> int:
             continue
         with gm.graph.inserting_before(node):
             new = gm.graph.call_function(_fused_gate_up_call, (x_list[0], w_list[0], dk["weight_scale"], dk["activation_scale"],
-                                                              gk["group_list"], bool(dk.get("activate_left", False))))
+                                                              gk["group_list"], bool(dk.get("activate_left", False)),
+                                                              gk.get("tuning_config")))
         node.replace_all_uses_with(new)
         gm.graph.erase_node(node)
         gm.graph.erase_node(src)
@@ -112,10 +113,10 @@ def fuse_gate_up(gm: torch.fx.GraphModule) -> int:
     return fused
 
 
-def _fused_gate_up_call(x, w, w_scale, x_scale, group_counts, activate_left):
+def _fused_gate_up_call(x, w, w_scale, x_scale, group_counts, activate_left, tuning_config=None):
     from . import ops
     return ops.fused_gate_up(x, w, w_scale.reshape(w.shape[0], -1) if w_scale.dim() > 1 else w_scale.expand(w.shape[0], -1),
-                             x_scale.reshape(-1), group_counts, 1, activate_left)
+                             x_scale.reshape(-1), group_counts, 1, activate_left, expected_rows=ops._expected_rows(tuning_config))
 
 
 def fuse_down_combine(gm: torch.fx.GraphModule) -> int:
@@ -163,7 +164,7 @@ def fuse_down_combine(gm: torch.fx.GraphModule) -> int:
             new = gm.graph.call_function(_fused_down_combine_call, (
                 x_list[0], w_list[0], sc[0], pts[0], gk["group_list"], int(gk.get("group_list_type", 0) or 0), node.args[1],
                 node.args[2], node.args[3], node.args[4], group, R, node.args[7], node.args[8], ck.get("shared_expert_x"),
-                gk["output_dtype"]))
+                gk["output_dtype"], gk.get("tuning_config")))
         node.replace_all_uses_with(new)
         gm.graph.erase_node(node)
         gm.graph.erase_node(src)
@@ -177,11 +178,12 @@ def fuse_down_combine(gm: torch.fx.GraphModule) -> int:
 
 
 def _fused_down_combine_call(hq, w2, s2, hs, group_list, group_list_type, expert_ids, expand_idx, ep_send_counts, expert_scales,
-                             group_ep, R, rank, E, shared, output_dtype):
+                             group_ep, R, rank, E, shared, output_dtype, tuning_config=None):
     from . import ops
     return ops.fused_down_combine(hq, w2, s2, hs.reshape(-1), group_list, group_list_type, expert_ids, expand_idx, ep_send_counts,
                                   expert_scales, group_ep, R, rank, E, shared,
-                                  torch.bfloat16 if output_dtype == 15 else torch.float16)
+                                  torch.bfloat16 if output_dtype == 15 else torch.float16,
+                                  expected_rows=ops._expected_rows(tuning_config))
 
 
 def _has_multi_rank_exchange(gm: torch.fx.GraphModule) -> bool:

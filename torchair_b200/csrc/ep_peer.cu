@@ -24,6 +24,7 @@
 namespace tab {
 
 constexpr int kEpMaxRanks = 64;
+constexpr int kEpMaxExperts = 2048;   // R * E_l of one exchange
 
 // Bound of a flag wait in SM clock ticks: TAB_EP_WAIT_MS from the environment (read once), default 2000 ms.  Ranks are
 // aligned by a host barrier when the buffers are created, so a healthy peer answers within microseconds.
@@ -119,8 +120,23 @@ __global__ void __launch_bounds__(kEpThreads) ep_send_kernel(const uint4* __rest
                                                             int vec_per_row, int M, int my_rank,
                                                             uint8_t* const* __restrict__ peer_recv,
                                                             int32_t* const* __restrict__ peer_counts,
-                                                            int32_t* __restrict__ expand_idx_slot, int* status, int code) {
+                                                            int32_t* __restrict__ expand_idx_slot, int* status, int code,
+                                                            const unsigned long long* __restrict__ ack_flags,
+                                                            const unsigned long long* __restrict__ ack_counter,
+                                                            long long limit, int ack_code) {
   __shared__ int s_base[kEpMaxRanks + 1];
+  if (ack_flags != nullptr && threadIdx.x < R) {
+    // the peers have copied the rows of the previous exchange out of their buffers (every CTA checks before it
+    // stores; the counter is advanced by the hand-over kernel that follows this one)
+    const unsigned long long expect = *ack_counter;
+    const long long t0 = clock64();
+    while (ld_acquire_sys(ack_flags + threadIdx.x) < expect) {
+      if (clock64() - t0 > limit) {
+        atomicCAS(status, 0, ack_code);
+        break;
+      }
+    }
+  }
   rank_bases_to_smem(expert_counts, R, E_l, s_base);
   const int64_t slot_bytes = static_cast<int64_t>(vec_per_row + 1) * 16;
   if (blockIdx.x == 0) {
@@ -224,6 +240,207 @@ __global__ void __launch_bounds__(256) ep_return_plan_kernel(const int32_t* __re
   }
 }
 
+// ---- fused forms: fewer launches per exchange ------------------------------------------------------------------
+
+// Signal "my data is there" to every peer, then wait until every peer's data is here: the two one-CTA kernels of a
+// hand-over in one.  bump (optional) is a second counter advanced by one: the acknowledgement counter that the data
+// kernel before this one only read.
+__global__ void ep_signal_wait_kernel(unsigned long long* const* __restrict__ peer_flags, unsigned long long* sig_counter,
+                                      const unsigned long long* __restrict__ flags, unsigned long long* wait_counter, int R,
+                                      int* status, int code, long long limit, unsigned long long* bump) {
+  __shared__ unsigned long long s_value;
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) {
+    s_value = *sig_counter + 1;
+    s_fail = 0;
+  }
+  __syncthreads();
+  __threadfence_system();
+  if (threadIdx.x < R) st_release_sys(peer_flags[threadIdx.x], s_value);
+  const unsigned long long expect = *wait_counter + 1ull;
+  if (threadIdx.x < R) {
+    const long long t0 = clock64();
+    while (ld_acquire_sys(flags + threadIdx.x) < expect) {
+      if (clock64() - t0 > limit) {
+        s_fail = 1;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (s_fail) atomicCAS(status, 0, code);
+    *sig_counter = s_value;
+    *wait_counter = expect;
+    if (bump != nullptr) *bump = *bump + 1;
+  }
+}
+
+// Exclusive scan of vals[0..n) in shared memory by a CTA of THREADS threads (n <= 2048); returns the total.
+// tmp holds THREADS / 32 + 1 ints.  Ends with a barrier.
+template <int THREADS>
+__device__ int cta_exclusive_scan(int* vals, int n, int* tmp) {
+  const int per = (n + THREADS - 1) / THREADS;
+  const int lo = threadIdx.x * per, hi = min(lo + per, n);
+  int sum = 0;
+  for (int i = lo; i < hi; ++i) sum += vals[i];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int incl = sum;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  if (lane == 31) tmp[warp] = incl;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int w = 0; w < THREADS / 32; ++w) {
+      const int t = tmp[w];
+      tmp[w] = run;
+      run += t;
+    }
+    tmp[THREADS / 32] = run;
+  }
+  __syncthreads();
+  int run = tmp[warp] + incl - sum;
+  for (int i = lo; i < hi; ++i) {
+    const int v = vals[i];
+    vals[i] = run;
+    run += v;
+  }
+  const int total = tmp[THREADS / 32];
+  __syncthreads();
+  return total;
+}
+
+// Row offsets of both sides of an exchange with fixed slots of C rows per source, in shared memory:
+//   s_wire[s*E_l + e] = first slot row of the rows (source s, expert e);  s_exp[e*R + s] = first row of that block in
+//   (expert, source) order, s_exp[R*E_l] = total.  count(s, e) is read through `at`.
+template <int THREADS, typename CountAt>
+__device__ __forceinline__ int build_exchange_offsets(CountAt at, int R, int E_l, int C, int* s_wire, int* s_exp, int* tmp) {
+  const int n = R * E_l;
+  for (int i = threadIdx.x; i < n; i += THREADS) {
+    const int sr = i / E_l, e = i - sr * E_l;
+    const int c = max(at(sr, e), 0);
+    s_wire[i] = c;
+    s_exp[e * R + sr] = c;
+  }
+  __syncthreads();
+  cta_exclusive_scan<THREADS>(s_wire, n, tmp);
+  const int total = cta_exclusive_scan<THREADS>(s_exp, n, tmp);
+  // offset inside the source's fixed slot: subtract the source's first offset (read before anyone overwrites it)
+  int first[(kEpMaxExperts + THREADS - 1) / THREADS];
+  int k = 0;
+  for (int i = threadIdx.x; i < n; i += THREADS, ++k) first[k] = s_wire[(i / E_l) * E_l];
+  __syncthreads();
+  k = 0;
+  for (int i = threadIdx.x; i < n; i += THREADS, ++k) s_wire[i] = s_wire[i] - first[k] + (i / E_l) * C;
+  if (threadIdx.x == 0) s_exp[n] = total;
+  __syncthreads();
+  return total;
+}
+
+// Receiver side of dispatch in one kernel: every CTA derives the row offsets from the delivered counts (a few hundred
+// integers) and copies its share of the slot records into (local expert, source rank) order with their scales; CTA 0
+// also writes expert_token_nums and ep_recv_count; the CTA that finishes last tells the peers that their rows have
+// been copied out (the acknowledgement a sender checks before it overwrites the slots).
+__global__ void __launch_bounds__(kEpThreads) ep_unpack_fused_kernel(const uint8_t* __restrict__ recv, const int32_t* __restrict__ counts,
+                                                                    int R, int E_l, int C, int vec_per_row, int64_t dst_rows, int nums_type,
+                                                                    uint4* __restrict__ dst, float* __restrict__ dst_scales,
+                                                                    int64_t* __restrict__ expert_token_nums, int32_t* __restrict__ ep_recv_count,
+                                                                    unsigned long long* const* __restrict__ ack_peer_flags,
+                                                                    unsigned long long* ack_sig_counter, unsigned int* done_counter) {
+  __shared__ int s_wire[kEpMaxExperts];
+  __shared__ int s_exp[kEpMaxExperts + 1];
+  __shared__ int s_tmp[kEpThreads / 32 + 1];
+  __shared__ int s_last;
+  const int n = R * E_l;
+  const int total = build_exchange_offsets<kEpThreads>([&](int sr, int e) { return counts[sr * E_l + e]; }, R, E_l, C, s_wire, s_exp, s_tmp);
+  if (blockIdx.x == 0) {
+    for (int i = threadIdx.x; i < n; i += kEpThreads) {
+      const int e = i / R, sr = i - e * R;
+      ep_recv_count[i] = max(counts[sr * E_l + e], 0);
+    }
+    for (int e = threadIdx.x; e < E_l; e += kEpThreads) {
+      const int begin = s_exp[e * R], end = e + 1 < E_l ? s_exp[(e + 1) * R] : total;
+      expert_token_nums[e] = nums_type == 1 ? static_cast<int64_t>(end - begin) : static_cast<int64_t>(end);
+    }
+  }
+  const int64_t slot_bytes = static_cast<int64_t>(vec_per_row + 1) * 16;
+  const int64_t rows = total < dst_rows ? total : dst_rows;
+  for (int64_t i = blockIdx.x; i < rows; i += gridDim.x) {
+    const int b = ep_last_le(s_exp, 0, n, static_cast<int>(i));   // b = e*R + s
+    const int e = b / R, sr = b - e * R;
+    const uint8_t* rec = recv + (static_cast<int64_t>(s_wire[sr * E_l + e]) + (i - s_exp[b])) * slot_bytes;
+    copy_row16<kEpThreads>(dst + i * vec_per_row, reinterpret_cast<const uint4*>(rec), vec_per_row);
+    if (threadIdx.x == 0) dst_scales[i] = *reinterpret_cast<const float*>(rec + static_cast<int64_t>(vec_per_row) * 16);
+  }
+  if (ack_peer_flags != nullptr) {
+    __syncthreads();                       // every thread's loads of the slots have returned (their stores were issued)
+    if (threadIdx.x == 0) {
+      __threadfence();
+      s_last = atomicInc(done_counter, gridDim.x - 1) == gridDim.x - 1 ? 1 : 0;   // wraps to 0 for the next launch
+    }
+    __syncthreads();
+    if (s_last) {
+      const unsigned long long v = *ack_sig_counter + 1;
+      __syncthreads();
+      if (threadIdx.x < R) st_release_sys(ack_peer_flags[threadIdx.x], v);
+      if (threadIdx.x == 0) *ack_sig_counter = v;
+    }
+  }
+}
+
+// Expert side of combine in one kernel: every CTA derives the offsets from ep_send_counts (count of expert e from
+// source s at e*R + s) and writes its share of the row address table (see ep_return_plan_kernel); CTA 0 also waits,
+// bounded, until the sources have reduced the rows of the previous combine (the stores into their buffers come from
+// the kernel launched after this one).
+__global__ void __launch_bounds__(256) ep_return_plan_fused_kernel(const int32_t* __restrict__ ep_send_counts, int R, int E_l, int C,
+                                                                  int64_t row_bytes, int my_rank, int64_t max_rows,
+                                                                  uint8_t* const* __restrict__ peer_ret,
+                                                                  unsigned long long* __restrict__ row_dst,
+                                                                  const unsigned long long* __restrict__ ack_flags,
+                                                                  unsigned long long* ack_counter, int* status, int ack_code,
+                                                                  long long limit) {
+  __shared__ int s_wire[kEpMaxExperts];
+  __shared__ int s_exp[kEpMaxExperts + 1];
+  __shared__ int s_tmp[256 / 32 + 1];
+  const int n = R * E_l;
+  const int total = build_exchange_offsets<256>([&](int sr, int e) { return ep_send_counts[e * R + sr]; }, R, E_l, C, s_wire, s_exp, s_tmp);
+  for (int64_t i = blockIdx.x * 256LL + threadIdx.x; i < max_rows; i += gridDim.x * 256LL) {
+    unsigned long long a = 0ull;
+    if (i < total) {
+      const int b = ep_last_le(s_exp, 0, n, static_cast<int>(i));
+      const int e = b / R, sr = b - e * R;
+      const int within = s_wire[sr * E_l + e] - sr * C + (static_cast<int>(i) - s_exp[b]);
+      if (within >= 0 && within < C)
+        a = reinterpret_cast<unsigned long long>(peer_ret[sr] + (static_cast<int64_t>(my_rank) * C + within) * row_bytes);
+    }
+    row_dst[i] = a;
+  }
+  if (blockIdx.x == 0 && ack_flags != nullptr) {
+    __shared__ int s_fail;
+    if (threadIdx.x == 0) s_fail = 0;
+    __syncthreads();
+    const unsigned long long expect = *ack_counter;
+    if (threadIdx.x < R) {
+      const long long t0 = clock64();
+      while (ld_acquire_sys(ack_flags + threadIdx.x) < expect) {
+        if (clock64() - t0 > limit) {
+          s_fail = 1;
+          break;
+        }
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      if (s_fail) atomicCAS(status, 0, ack_code);
+      *ack_counter = expect + 1;
+    }
+  }
+}
+
 }  // namespace tab
 
 using namespace tab;
@@ -247,7 +464,8 @@ extern "C" int tab_ep_wait(const void* flags, void* counter, int64_t R, int pre_
 extern "C" int tab_ep_send_rows(const void* rows, const float* scales, const int32_t* expert_counts, const int32_t* expand_idx,
                                 int64_t R, int64_t E_l, int64_t slot_rows, int64_t row_bytes, int64_t M, int64_t my_rank,
                                 void* const* peer_recv, void* const* peer_counts, int32_t* expand_idx_slot,
-                                int* status, int code, tab_stream_t stream) {
+                                int* status, int code, const void* ack_flags, const void* ack_counter, int ack_code,
+                                tab_stream_t stream) {
   if (!expert_counts || !peer_recv || !peer_counts || !status || R < 1 || R > kEpMaxRanks || E_l < 1 || slot_rows < 1 || my_rank < 0 || my_rank >= R)
     return fail(TAB_ERR_BAD_ARG, "ep_send_rows: bad argument");
   if (M > 0 && (!rows || !expand_idx || !expand_idx_slot)) return fail(TAB_ERR_BAD_ARG, "ep_send_rows: null pointer");
@@ -257,7 +475,9 @@ extern "C" int tab_ep_send_rows(const void* rows, const float* scales, const int
   ep_send_kernel<<<grid, kEpThreads, 0, as_stream(stream)>>>(static_cast<const uint4*>(rows), scales, expert_counts, expand_idx, (int)R,
                                                             (int)E_l, (int)slot_rows, (int)(row_bytes / 16), (int)M, (int)my_rank,
                                                             reinterpret_cast<uint8_t* const*>(peer_recv),
-                                                            reinterpret_cast<int32_t* const*>(peer_counts), expand_idx_slot, status, code);
+                                                            reinterpret_cast<int32_t* const*>(peer_counts), expand_idx_slot, status, code,
+                                                            static_cast<const unsigned long long*>(ack_flags),
+                                                            static_cast<const unsigned long long*>(ack_counter), ep_wait_cycles(), ack_code);
   return check_launch("ep_send_rows");
 }
 
@@ -300,4 +520,51 @@ extern "C" int tab_ep_return_plan(const int32_t* plan, int64_t R, int64_t E_l, i
       plan, (int)R, (int)E_l, (int)slot_rows, row_bytes, (int)my_rank, max_rows, reinterpret_cast<uint8_t* const*>(peer_ret),
       reinterpret_cast<unsigned long long*>(row_dst));
   return check_launch("ep_return_plan");
+}
+
+extern "C" int tab_ep_signal_wait(void* const* peer_flags, void* sig_counter, const void* flags, void* wait_counter, int64_t R,
+                                  int* status, int code, void* bump_counter, tab_stream_t stream) {
+  if (!peer_flags || !sig_counter || !flags || !wait_counter || !status || R < 1 || R > kEpMaxRanks)
+    return fail(TAB_ERR_BAD_ARG, "ep_signal_wait: bad argument (R=%lld)", (long long)R);
+  ep_signal_wait_kernel<<<1, 64, 0, as_stream(stream)>>>(reinterpret_cast<unsigned long long* const*>(peer_flags),
+                                                        static_cast<unsigned long long*>(sig_counter),
+                                                        static_cast<const unsigned long long*>(flags),
+                                                        static_cast<unsigned long long*>(wait_counter), (int)R, status, code,
+                                                        ep_wait_cycles(), static_cast<unsigned long long*>(bump_counter));
+  return check_launch("ep_signal_wait");
+}
+
+extern "C" int tab_ep_unpack_rows_fused(const void* recv, const int32_t* recv_counts, int64_t R, int64_t E_l, int64_t slot_rows,
+                                        int64_t row_bytes, int64_t dst_rows, int nums_type, void* dst, float* dst_scales,
+                                        int64_t* expert_token_nums, int32_t* ep_recv_count, void* const* ack_peer_flags,
+                                        void* ack_sig_counter, void* done_counter, tab_stream_t stream) {
+  if (!recv || !recv_counts || !dst || !dst_scales || !expert_token_nums || !ep_recv_count || R < 1 || R > kEpMaxRanks || E_l < 1 ||
+      R * E_l > kEpMaxExperts || slot_rows < 1 || dst_rows < 1 || dst_rows > (1LL << 30) || (nums_type != 0 && nums_type != 1))
+    return fail(TAB_ERR_BAD_ARG, "ep_unpack_rows_fused: bad argument");
+  if ((ack_peer_flags != nullptr) != (ack_sig_counter != nullptr) || (ack_peer_flags != nullptr) != (done_counter != nullptr))
+    return fail(TAB_ERR_BAD_ARG, "ep_unpack_rows_fused: the acknowledgement needs its flags, its counter and the arrival counter");
+  if (row_bytes <= 0 || row_bytes % 16 != 0 || !aligned16(recv) || !aligned16(dst))
+    return fail(TAB_ERR_ALIGNMENT, "ep_unpack_rows_fused: row_bytes=%lld must be a multiple of 16 and pointers 16-byte aligned", (long long)row_bytes);
+  ep_unpack_fused_kernel<<<grid_for(dst_rows, 16), kEpThreads, 0, as_stream(stream)>>>(
+      static_cast<const uint8_t*>(recv), recv_counts, (int)R, (int)E_l, (int)slot_rows, (int)(row_bytes / 16), dst_rows, nums_type,
+      static_cast<uint4*>(dst), dst_scales, expert_token_nums, ep_recv_count,
+      reinterpret_cast<unsigned long long* const*>(ack_peer_flags), static_cast<unsigned long long*>(ack_sig_counter),
+      static_cast<unsigned int*>(done_counter));
+  return check_launch("ep_unpack_rows_fused");
+}
+
+extern "C" int tab_ep_return_plan_fused(const int32_t* ep_send_counts, int64_t R, int64_t E_l, int64_t slot_rows, int64_t row_bytes,
+                                        int64_t max_rows, int64_t my_rank, void* const* peer_ret, uint64_t* row_dst,
+                                        const void* ack_flags, void* ack_counter, int* status, int ack_code, tab_stream_t stream) {
+  if (max_rows == 0) return TAB_OK;
+  if (!ep_send_counts || !peer_ret || !row_dst || R < 1 || R > kEpMaxRanks || E_l < 1 || R * E_l > kEpMaxExperts || slot_rows < 1 ||
+      my_rank < 0 || my_rank >= R || max_rows < 0 || max_rows > (1LL << 30))
+    return fail(TAB_ERR_BAD_ARG, "ep_return_plan_fused: bad argument");
+  if ((ack_flags != nullptr) && (!ack_counter || !status)) return fail(TAB_ERR_BAD_ARG, "ep_return_plan_fused: the wait needs its counter and a status word");
+  if (row_bytes <= 0 || row_bytes % 16 != 0) return fail(TAB_ERR_ALIGNMENT, "ep_return_plan_fused: row_bytes=%lld must be a multiple of 16", (long long)row_bytes);
+  ep_return_plan_fused_kernel<<<grid_for((max_rows + 255) / 256, 4), 256, 0, as_stream(stream)>>>(
+      ep_send_counts, (int)R, (int)E_l, (int)slot_rows, row_bytes, (int)my_rank, max_rows, reinterpret_cast<uint8_t* const*>(peer_ret),
+      reinterpret_cast<unsigned long long*>(row_dst), static_cast<const unsigned long long*>(ack_flags),
+      static_cast<unsigned long long*>(ack_counter), status, ack_code, ep_wait_cycles());
+  return check_launch("ep_return_plan_fused");
 }

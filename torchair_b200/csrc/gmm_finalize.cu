@@ -94,7 +94,7 @@ extern "C" int tab_grouped_matmul_finalize_routing(const int8_t* x, const int8_t
                                                    int64_t shared_input_offset, const float* logit,
                                                    const void* row_index, int row_index_dtype, int64_t output_bs,
                                                    float* y, void* workspace, size_t workspace_bytes,
-                                                   tab_stream_t stream) {
+                                                   int64_t expected_rows_per_group, tab_stream_t stream) {
   const char* op = "grouped_matmul_finalize_routing";
   if (M < 0 || N <= 0 || Kd <= 0 || E <= 0 || output_bs < 0 || shared_rows < 0)
     return fail(TAB_ERR_BAD_ARG, "%s: M=%lld Kd=%lld N=%lld E=%lld output_bs=%lld", op, (long long)M, (long long)Kd, (long long)N, (long long)E, (long long)output_bs);
@@ -116,7 +116,8 @@ extern "C" int tab_grouped_matmul_finalize_routing(const int8_t* x, const int8_t
   cudaStream_t st = as_stream(stream);
   int32_t* acc = static_cast<int32_t*>(workspace);
   if (M > 0) {
-    const int rc = tab_grouped_matmul_w8a8(x, packed_weight, nullptr, nullptr, group_list, group_list_type, M, Kd, N, E, TAB_I32, acc, stream);
+    const int rc = tab_grouped_matmul_w8a8(x, packed_weight, nullptr, nullptr, group_list, group_list_type, M, Kd, N, E, TAB_I32, acc,
+                                           expected_rows_per_group, stream);
     if (rc != TAB_OK) return rc;
   }
   finalize_init_kernel<<<grid_for(output_bs, 8), kFinThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(shared_input), shared_rows,

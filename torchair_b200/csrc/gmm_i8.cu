@@ -367,10 +367,16 @@ static const GmmEnv& gmm_env() {
   return env;
 }
 
+// Rows per group the tiling is chosen for: the caller's expectation when it gave one (the first element of the
+// operator's tuning_config), else the allocated rows spread evenly.  With expert parallelism x is sized for the worst
+// case (every rank sending everything here), so M / E can be many times the rows that actually arrive.
+static double rows_per_group(int64_t M, int64_t E, int64_t expected) {
+  return expected > 0 ? static_cast<double>(expected) : static_cast<double>(M) / static_cast<double>(E);
+}
+
 // Token-tile width of the decode orientation: the smallest of 16..256 that holds 1.5 x the average rows per expert.
-static int pick_nt(int64_t M, int64_t E) {
+static int pick_nt(double avg) {
   if (gmm_env().nt != 0) return gmm_env().nt;
-  const double avg = static_cast<double>(M) / static_cast<double>(E);
   const int opts[5] = {16, 32, 64, 128, 256};
   for (int i = 0; i < 5; ++i)
     if (opts[i] >= 1.5 * avg) return opts[i];
@@ -390,9 +396,9 @@ static int launch_one(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const Gm
 
 // Orientation: experts with many rows run the prefill kernel (128-token tiles, overlapped epilogue); a handful of
 // rows per expert run the decode kernel (weights stationary, narrow token tile).
-static bool use_prefill(int64_t M, int64_t E) {
+static bool use_prefill(double avg) {
   if (gmm_env().orientation != 0) return gmm_env().orientation == 2;
-  return M > 64 * E;
+  return avg > 64.0;
 }
 
 template <bool FUSED>
@@ -452,7 +458,8 @@ extern "C" int tab_prepack_weight_i8(const int8_t* weight, int64_t E, int64_t Kd
 
 static int grouped_matmul_plain(const int8_t* x, const int8_t* packed_weight, const float* scale, const float* per_token_scale,
                                 const int64_t* group_list, int group_list_type, int64_t M, int64_t Kd, int64_t N, int64_t E,
-                                int out_dtype, void* y, const uint64_t* row_dst, tab_stream_t stream) {
+                                int out_dtype, void* y, const uint64_t* row_dst, int64_t expected_rows_per_group,
+                                tab_stream_t stream) {
   int rc = check_common("grouped_matmul", x, packed_weight, group_list, group_list_type, M, Kd, N, E);
   if (rc != TAB_OK) return rc;
   if (out_dtype != TAB_I32 && out_dtype != TAB_BF16 && out_dtype != TAB_F16)
@@ -460,7 +467,8 @@ static int grouped_matmul_plain(const int8_t* x, const int8_t* packed_weight, co
   if (row_dst && out_dtype == TAB_I32) return fail(TAB_ERR_UNSUPPORTED, "grouped_matmul: a row address table needs a 16-bit output dtype");
   if (M == 0) return TAB_OK;
   if (!y && !row_dst) return fail(TAB_ERR_BAD_ARG, "grouped_matmul: null output");
-  const int nt = use_prefill(M, E) ? 0 : pick_nt(M, E);     // 0 selects the prefill orientation
+  const double avg = rows_per_group(M, E, expected_rows_per_group);
+  const int nt = use_prefill(avg) ? 0 : pick_nt(avg);     // 0 selects the prefill orientation
   CUtensorMap tm_w, tm_x;
   rc = make_maps(x, packed_weight, M, Kd, N, E, nt == 0 ? kPfTokens : nt, &tm_w, &tm_x);
   if (rc != TAB_OK) return rc;
@@ -482,19 +490,20 @@ static int grouped_matmul_plain(const int8_t* x, const int8_t* packed_weight, co
 extern "C" int tab_grouped_matmul_w8a8(const int8_t* x, const int8_t* packed_weight, const float* scale,
                                        const float* per_token_scale, const int64_t* group_list, int group_list_type,
                                        int64_t M, int64_t Kd, int64_t N, int64_t E, int out_dtype, void* y,
-                                       tab_stream_t stream) {
+                                       int64_t expected_rows_per_group, tab_stream_t stream) {
   return grouped_matmul_plain(x, packed_weight, scale, per_token_scale, group_list, group_list_type, M, Kd, N, E, out_dtype, y,
-                              nullptr, stream);
+                              nullptr, expected_rows_per_group, stream);
 }
 
 extern "C" int tab_grouped_matmul_w8a8_scatter(const int8_t* x, const int8_t* packed_weight, const float* scale,
                                                const float* per_token_scale, const int64_t* group_list, int group_list_type,
                                                int64_t M, int64_t Kd, int64_t N, int64_t E, int out_dtype,
-                                               const uint64_t* row_dst, tab_stream_t stream) {
+                                               const uint64_t* row_dst, int64_t expected_rows_per_group,
+                                               tab_stream_t stream) {
   if (!row_dst && M > 0) return fail(TAB_ERR_BAD_ARG, "grouped_matmul_scatter: null row address table");
   if ((N * 2) % 16 != 0) return fail(TAB_ERR_ALIGNMENT, "grouped_matmul_scatter: N=%lld must be a multiple of 8", (long long)N);
   return grouped_matmul_plain(x, packed_weight, scale, per_token_scale, group_list, group_list_type, M, Kd, N, E, out_dtype, nullptr,
-                              row_dst, stream);
+                              row_dst, expected_rows_per_group, stream);
 }
 
 extern "C" int tab_grouped_matmul_swiglu_quant_workspace_bytes(int64_t M, int64_t I, size_t* bytes) {
@@ -508,7 +517,7 @@ extern "C" int tab_grouped_matmul_swiglu_quant(const int8_t* x, const int8_t* pa
                                                const float* x_scale, const int64_t* group_list, int group_list_type,
                                                int64_t M, int64_t Kd, int64_t I, int64_t E, int activate_left,
                                                int8_t* yq, float* y_scale, void* workspace, size_t workspace_bytes,
-                                               tab_stream_t stream) {
+                                               int64_t expected_rows_per_group, tab_stream_t stream) {
   int rc = check_common("grouped_matmul_swiglu_quant", x, packed_weight, group_list, group_list_type, M, Kd, 2 * I, E);
   if (rc != TAB_OK) return rc;
   if (M == 0) return TAB_OK;
@@ -524,7 +533,8 @@ extern "C" int tab_grouped_matmul_swiglu_quant(const int8_t* x, const int8_t* pa
   float* h = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + amax_bytes);
   cudaError_t ce = cudaMemsetAsync(amax, 0, amax_bytes, st);
   if (ce != cudaSuccess) return fail(TAB_ERR_CUDA, "grouped_matmul_swiglu_quant: memset: %s", cudaGetErrorString(ce));
-  const int nt = use_prefill(M, E) ? 0 : pick_nt(M, E);     // 0 selects the prefill orientation
+  const double avg = rows_per_group(M, E, expected_rows_per_group);
+  const int nt = use_prefill(avg) ? 0 : pick_nt(avg);     // 0 selects the prefill orientation
   CUtensorMap tm_w, tm_x;
   rc = make_maps(x, packed_weight, M, Kd, 2 * I, E, nt == 0 ? kPfTokens : nt, &tm_w, &tm_x);
   if (rc != TAB_OK) return rc;

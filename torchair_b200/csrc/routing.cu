@@ -207,24 +207,47 @@ __global__ void __launch_bounds__(kRowCopyThreads) gather_rows_kernel(const uint
 // to their sorted positions.  cols % 16 == 0.  The row stays in registers in raw form between the passes.
 constexpr int kPackChunks = 8;
 constexpr int kPackMaxK = 256;
-template <typename T, bool kQuant, int THREADS>
+constexpr int kSmallPairs = 4096;   // T*K up to which the sort runs inside the pack kernel (one launch instead of four)
+
+// kSortInside = false: expand_idx holds the sorted position of every pair (written by the three sort kernels) and
+// counts the rows per expert.  kSortInside = true (T*K <= kSmallPairs): the kernel sorts by itself -- every CTA keeps
+// the clamped expert ids of ALL pairs in shared memory and ranks the K pairs of its token directly (position = pairs
+// with a smaller id, plus earlier pairs with the same id: the stable order of the counting sort); the last CTA also
+// builds the per-expert counts.  expand_idx, counts and sorted_src are then outputs, expert_ids the input.
+template <typename T, bool kQuant, int THREADS, bool kSortInside>
 __global__ void __launch_bounds__(THREADS) dispatch_pack_kernel(const T* __restrict__ x,
-                                                               const int32_t* __restrict__ expand_idx,
+                                                               int32_t* __restrict__ expand_idx,
                                                                int64_t tokens, int K, int cols,
                                                                void* __restrict__ send_rows,
                                                                float* __restrict__ send_scales,
-                                                               const int32_t* __restrict__ counts,
+                                                               int32_t* __restrict__ counts,
                                                                int64_t* __restrict__ nums64, int num_experts,
-                                                               int nums_type) {
+                                                               int nums_type, const int32_t* __restrict__ expert_ids,
+                                                               int32_t* __restrict__ sorted_src) {
   __shared__ float red[THREADS / 32];
   __shared__ int s_pos[kPackMaxK];
+  __shared__ short s_e[kSortInside ? kSmallPairs : 1];
+  __shared__ int s_hist[kSortInside ? kMaxExperts : 1];
   const int nchunk = cols >> 3;
+  if constexpr (kSortInside) {
+    const int n = static_cast<int>(tokens) * K;
+    const bool last = blockIdx.x == gridDim.x - 1;
+    if (last)
+      for (int e = threadIdx.x; e < num_experts; e += THREADS) s_hist[e] = 0;
+    for (int f = threadIdx.x; f < n; f += THREADS) s_e[f] = static_cast<short>(clamp_expert(expert_ids[f], num_experts));
+    __syncthreads();
+    if (last) {
+      for (int f = threadIdx.x; f < n; f += THREADS) atomicAdd(&s_hist[s_e[f]], 1);
+      __syncthreads();
+      for (int e = threadIdx.x; e < num_experts; e += THREADS) counts[e] = s_hist[e];
+    }
+  }
   if (nums64 != nullptr && blockIdx.x == gridDim.x - 1 && threadIdx.x < 32) {
     // the per-expert copies as int64 counts (nums_type 1) or their running total (0), the form the grouped GEMM reads
     long long run = 0;
     for (int e0 = 0; e0 < num_experts; e0 += 32) {
       const int e = e0 + threadIdx.x;
-      const long long c = e < num_experts ? counts[e] : 0;
+      const long long c = e < num_experts ? (kSortInside ? s_hist[e] : counts[e]) : 0;
       long long incl = c;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
@@ -238,7 +261,29 @@ __global__ void __launch_bounds__(THREADS) dispatch_pack_kernel(const T* __restr
   for (int64_t t = blockIdx.x; t < tokens; t += gridDim.x) {
     const T* xr = x + t * cols;
     __syncthreads();   // previous token's positions are no longer read
-    for (int k = threadIdx.x; k < K; k += THREADS) s_pos[k] = expand_idx[t * K + k];
+    if constexpr (kSortInside) {
+      const int n = static_cast<int>(tokens) * K;
+      const int lane = threadIdx.x & 31;
+      for (int k = threadIdx.x >> 5; k < K; k += THREADS / 32) {     // one warp per pair of this token
+        const int f0 = static_cast<int>(t) * K + k;
+        const int e0 = s_e[f0];
+        int before = 0;
+        for (int f = lane; f < n; f += 32) {
+          const int e = s_e[f];
+          before += (e < e0 || (e == e0 && f < f0)) ? 1 : 0;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) before += __shfl_xor_sync(0xffffffffu, before, o);
+        if (lane == 0) {
+          s_pos[k] = before;
+          expand_idx[f0] = before;
+          if (sorted_src != nullptr) sorted_src[before] = f0;
+        }
+      }
+      if constexpr (!kQuant) __syncthreads();   // (the quantising branch publishes s_pos with the barriers of its reduction)
+    } else {
+      for (int k = threadIdx.x; k < K; k += THREADS) s_pos[k] = expand_idx[t * K + k];
+    }
     if constexpr (kQuant) {
       Raw8<T> raw[kPackChunks];
 #pragma unroll
@@ -294,19 +339,22 @@ __global__ void __launch_bounds__(THREADS) dispatch_pack_kernel(const T* __restr
   }
 }
 
-template <typename T>
-static void launch_pack(const void* x, const int32_t* expand_idx, int64_t T_, int K, int H, int quant_mode, void* rows,
-                        float* scales, const int32_t* counts, int64_t* nums64, int num_experts, int nums_type, cudaStream_t st) {
+template <typename T, bool kSortInside>
+static void launch_pack(const void* x, int32_t* expand_idx, int64_t T_, int K, int H, int quant_mode, void* rows,
+                        float* scales, int32_t* counts, int64_t* nums64, int num_experts, int nums_type,
+                        const int32_t* expert_ids, int32_t* sorted_src, cudaStream_t st) {
   const T* xp = static_cast<const T*>(x);
   const bool small = H / 8 <= 128 * kPackChunks;
   const int grid = grid_for(T_, small ? 10 : 5);
+#define TAB_PACK(Q, TH)                                                                                                   \
+  dispatch_pack_kernel<T, Q, TH, kSortInside><<<grid, TH, 0, st>>>(xp, expand_idx, T_, K, H, rows, scales, counts, nums64, \
+                                                                   num_experts, nums_type, expert_ids, sorted_src)
   if (quant_mode == 2) {
-    if (small) dispatch_pack_kernel<T, true, 128><<<grid, 128, 0, st>>>(xp, expand_idx, T_, K, H, rows, scales, counts, nums64, num_experts, nums_type);
-    else dispatch_pack_kernel<T, true, 256><<<grid, 256, 0, st>>>(xp, expand_idx, T_, K, H, rows, scales, counts, nums64, num_experts, nums_type);
+    if (small) TAB_PACK(true, 128); else TAB_PACK(true, 256);
   } else {
-    if (small) dispatch_pack_kernel<T, false, 128><<<grid, 128, 0, st>>>(xp, expand_idx, T_, K, H, rows, scales, counts, nums64, num_experts, nums_type);
-    else dispatch_pack_kernel<T, false, 256><<<grid, 256, 0, st>>>(xp, expand_idx, T_, K, H, rows, scales, counts, nums64, num_experts, nums_type);
+    if (small) TAB_PACK(false, 128); else TAB_PACK(false, 256);
   }
+#undef TAB_PACK
 }
 
 // ---- receiver side ---------------------------------------------------------------------------------
@@ -526,12 +574,20 @@ extern "C" int tab_moe_dispatch_pack(const void* x, int x_dtype, const int32_t* 
     return fail(TAB_ERR_ALIGNMENT, "dispatch_pack: H=%lld must be a multiple of 16 and pointers 16-byte aligned", (long long)H);
   (void)es;
   SortScratch s = carve(workspace, n, num_experts, true);
+  if (n <= kSmallPairs) {
+    // decode-sized batches: the sort runs inside the pack kernel, one launch in all
+    if (x_dtype == TAB_BF16)
+      launch_pack<__nv_bfloat16, true>(x, expand_idx, T, (int)K, (int)H, quant_mode, send_rows, send_scales, expert_counts, expert_token_nums, (int)num_experts, nums_type, expert_ids, s.sorted_src, st);
+    else
+      launch_pack<__half, true>(x, expand_idx, T, (int)K, (int)H, quant_mode, send_rows, send_scales, expert_counts, expert_token_nums, (int)num_experts, nums_type, expert_ids, s.sorted_src, st);
+    return check_launch("dispatch_pack");
+  }
   rc = run_sort(expert_ids, nullptr, n, num_experts, s, s.sorted_expert, expand_idx, expert_counts, st);
   if (rc != TAB_OK) return rc;
   if (x_dtype == TAB_BF16)
-    launch_pack<__nv_bfloat16>(x, expand_idx, T, (int)K, (int)H, quant_mode, send_rows, send_scales, expert_counts, expert_token_nums, (int)num_experts, nums_type, st);
+    launch_pack<__nv_bfloat16, false>(x, expand_idx, T, (int)K, (int)H, quant_mode, send_rows, send_scales, expert_counts, expert_token_nums, (int)num_experts, nums_type, nullptr, nullptr, st);
   else
-    launch_pack<__half>(x, expand_idx, T, (int)K, (int)H, quant_mode, send_rows, send_scales, expert_counts, expert_token_nums, (int)num_experts, nums_type, st);
+    launch_pack<__half, false>(x, expand_idx, T, (int)K, (int)H, quant_mode, send_rows, send_scales, expert_counts, expert_token_nums, (int)num_experts, nums_type, nullptr, nullptr, st);
   return check_launch("dispatch_pack");
 }
 

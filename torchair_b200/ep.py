@@ -226,6 +226,7 @@ class PeerExchange:
         self.sig_counter = [cbase + k * 8 for k in range(4)]
         self.wait_counter = [cbase + 32 + k * 8 for k in range(4)]
         self.status_ptr = cbase + 64
+        self.done_ptr = cbase + 72          # arrival counter of the unpack kernel's CTAs (wraps to zero by itself)
         self.recv_local = self.buf[self.off_recv:self.off_counts]
         self.counts_local = self.buf[self.off_counts:self.off_counts + R * self.E_l * 4].view(torch.int32)
         self.ret_local = self.buf[self.off_ret:self.off_ret + R * self.C * self.ret_row_bytes]
@@ -240,6 +241,14 @@ class PeerExchange:
     def wait(self, kind, pre_increment):
         _lib.call("tab_ep_wait", ctypes.c_void_p(self.flags_local[kind]), ctypes.c_void_p(self.wait_counter[kind]), self.R,
                   int(pre_increment), ctypes.c_void_p(self.status_ptr), 100 + kind, self._stream())
+
+    def signal_wait(self, kind, bump_kind=None):
+        """signal(kind) followed by wait(kind, pre_increment=1) as one launch; bump_kind: an acknowledgement counter that the
+        preceding data kernel only read and that advances here."""
+        bump = None if bump_kind is None else ctypes.c_void_p(self.wait_counter[bump_kind])
+        _lib.call("tab_ep_signal_wait", _ptr(self.peer_flags[kind]), ctypes.c_void_p(self.sig_counter[kind]),
+                  ctypes.c_void_p(self.flags_local[kind]), ctypes.c_void_p(self.wait_counter[kind]), self.R,
+                  ctypes.c_void_p(self.status_ptr), 100 + kind, bump, self._stream())
 
     def status(self) -> int:
         """Synchronises and returns 0, 100 + kind of the first flag wait that ran out of time, or 110 when a sender held
@@ -279,16 +288,19 @@ def _dispatch_peer(kern, x, expert_ids, group_ep, pg, R, rank, E, quant_mode, nu
     A = R * px.C
     st = px._stream()
     slot_idx = torch.empty_like(expand_idx)
-    px.wait(px.KIND_ACK_D, 0)                     # the peers have copied my previous rows out of their buffers
+    # four launches: send (checks the peers' acknowledgement of the previous exchange itself), hand-over (signal + wait),
+    # unpack (derives the row offsets from the delivered counts itself; its last CTA acknowledges)
     _lib.call("tab_ep_send_rows", _ptr(send_rows), _ptr(send_scales), _ptr(counts), _ptr(expand_idx), R, E_l, px.C, row_bytes,
-              T * K, rank, _ptr(px.peer_recv), _ptr(px.peer_counts), _ptr(slot_idx), ctypes.c_void_p(px.status_ptr), 110, st)
-    px.signal(px.KIND_DATA_D)
-    px.wait(px.KIND_DATA_D, 1)                    # every source's rows and counts have landed here
-    plan, nums, ep_recv = kern.exchange_plan(px.counts_local.view(R, E_l), R, E_l, px.C, nums_type)
+              T * K, rank, _ptr(px.peer_recv), _ptr(px.peer_counts), _ptr(slot_idx), ctypes.c_void_p(px.status_ptr), 110,
+              ctypes.c_void_p(px.flags_local[px.KIND_ACK_D]), ctypes.c_void_p(px.wait_counter[px.KIND_ACK_D]), 100 + px.KIND_ACK_D, st)
+    px.signal_wait(px.KIND_DATA_D, bump_kind=px.KIND_ACK_D)    # every source's rows and counts have landed here
     expand_x = torch.empty((A, H), dtype=send_rows.dtype, device=dev)
     dyn = torch.empty((A,), dtype=torch.float32, device=dev)
-    _lib.call("tab_ep_unpack_rows", _ptr(px.recv_local), _ptr(plan), R, E_l, row_bytes, A, 0, _ptr(expand_x), _ptr(dyn), st)
-    px.signal(px.KIND_ACK_D)
+    nums = torch.empty((E_l,), dtype=torch.int64, device=dev)
+    ep_recv = torch.empty((E_l * R,), dtype=torch.int32, device=dev)
+    _lib.call("tab_ep_unpack_rows_fused", _ptr(px.recv_local), _ptr(px.counts_local), R, E_l, px.C, row_bytes, A, nums_type,
+              _ptr(expand_x), _ptr(dyn), _ptr(nums), _ptr(ep_recv), _ptr(px.peer_flags[px.KIND_ACK_D]),
+              ctypes.c_void_p(px.sig_counter[px.KIND_ACK_D]), ctypes.c_void_p(px.done_ptr), st)
     counters["wire_bytes_sent"] += T * K * (row_bytes + 16)
     return expand_x, dyn, slot_idx, nums, ep_recv, tp_recv, expand_scales
 
@@ -335,14 +347,14 @@ def combine_from_producer(kern, produce_rows, rows, H, dtype, expert_ids, expand
     if px is None:
         raise RuntimeError("npu_moe_distribute_combine: no matching npu_moe_distribute_dispatch ran on this group")
     st = px._stream()
-    recv_counts = ep_send_counts.view(E_l, R).t().contiguous()
-    plan, _, _ = kern.exchange_plan(recv_counts, R, E_l, px.C, 1)
     row_dst = torch.empty((rows,), dtype=torch.int64, device=expand_idx.device)
-    _lib.call("tab_ep_return_plan", _ptr(plan), R, E_l, px.C, H * 2, rows, rank, _ptr(px.peer_ret), _ptr(row_dst), st)
-    px.wait(px.KIND_ACK_C, 0)                     # the sources have reduced the rows of the previous combine
+    # address table from ep_send_counts in one launch; its first CTA also waits until the sources have reduced the rows of
+    # the previous combine
+    _lib.call("tab_ep_return_plan_fused", _ptr(ep_send_counts.contiguous()), R, E_l, px.C, H * 2, rows, rank, _ptr(px.peer_ret),
+              _ptr(row_dst), ctypes.c_void_p(px.flags_local[px.KIND_ACK_C]), ctypes.c_void_p(px.wait_counter[px.KIND_ACK_C]),
+              ctypes.c_void_p(px.status_ptr), 100 + px.KIND_ACK_C, st)
     produce_rows(row_dst)
-    px.signal(px.KIND_DATA_C)
-    px.wait(px.KIND_DATA_C, 1)
+    px.signal_wait(px.KIND_DATA_C)
     back = px.ret_local.view(dtype).view(R * px.C, H)
     out = kern.combine(back, expand_idx, expert_scales, shared, T, K)
     px.signal(px.KIND_ACK_C)

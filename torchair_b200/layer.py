@@ -24,20 +24,24 @@ def moe_layer(x, expert_ids, expert_scales, w1, s1, w2, s2, *, group_ep: str = "
     npu = torch.ops.npu
     R = ep_world_size
     E = moe_expert_num if moe_expert_num is not None else w1.shape[0] * R
+    # rows an expert is expected to receive (all ranks' copies spread over all experts): the tiling hint of the grouped
+    # matmuls.  With R > 1 the dispatch output is sized for the worst case, so the row count of `ex` says little.
+    tune = [max(1, -(-x.shape[0] * expert_ids.shape[1] * R // E))]
     ex, xs, expand_idx, nums, ep_recv, _tp, _es = npu.npu_moe_distribute_dispatch(
         x, expert_ids, group_ep, R, ep_rank_id, E, quant_mode=2, expert_token_nums_type=1)
     if fused:
-        hq, hs = npu.npu_grouped_matmul_swiglu_quant_v2(ex, [w1], [s1], xs, nums, group_list_type=1)
+        hq, hs = npu.npu_grouped_matmul_swiglu_quant_v2(ex, [w1], [s1], xs, nums, group_list_type=1, tuning_config=tune)
     else:
         h32 = npu.npu_grouped_matmul([ex], [w1], group_list=nums, split_item=2, group_type=0, group_list_type=1,
-                                     output_dtype=3)[0]
+                                     output_dtype=3, tuning_config=tune)[0]
         hq, hs = npu.npu_dequant_swiglu_quant(h32, weight_scale=s1, activation_scale=xs, group_index=nums,
                                               activate_left=True, quant_mode=1)
     if fused and R > 1 and not torch.compiler.is_compiling():
         # down GEMM and combine in one step: over peer memory the GEMM's epilogue stores its rows into the senders'
         # return buffers (a compiled graph gets the same rewrite from the FX pass of the backend)
         return ops.fused_down_combine(hq, w2, s2, hs, nums, 1, expert_ids, expand_idx, ep_recv, expert_scales, group_ep, R,
-                                      ep_rank_id, E, out_dtype=x.dtype)
+                                      ep_rank_id, E, out_dtype=x.dtype, expected_rows=tune[0])
     y = npu.npu_grouped_matmul([hq], [w2], scale=[s2], per_token_scale=[hs], group_list=nums, split_item=2,
-                               group_type=0, group_list_type=1, output_dtype=15 if x.dtype == torch.bfloat16 else 5)[0]
+                               group_type=0, group_list_type=1, output_dtype=15 if x.dtype == torch.bfloat16 else 5,
+                               tuning_config=tune)[0]
     return npu.npu_moe_distribute_combine(y, expert_ids, expand_idx, ep_recv, expert_scales, group_ep, R, ep_rank_id, E)

@@ -333,6 +333,16 @@ def _gmm_common_check(op, x, weight, split_item, group_type, group_list, act_typ
     return xs, w
 
 
+def _expected_rows(tuning_config) -> int:
+    """First element of tuning_config = the rows a group is expected to hold (0 / absent = unknown).  The converters forward
+    the list to the IR attribute of the same name without defining it (grouped_matmul.py:245,361); decision: expected
+    rows per group, used only to choose the kernel orientation and tile width."""
+    if tuning_config is None or len(tuning_config) == 0:
+        return 0
+    v = int(tuning_config[0])
+    return v if v > 0 else 0
+
+
 def _gmm_out_dtype(output_dtype):
     # converter grouped_matmul.py:178-195: fp16 -> 0, bf16 -> 1, int32 -> 2; int8 is rejected
     if output_dtype is None:
@@ -389,7 +399,7 @@ def _gmm_cuda(x, weight, *, bias=None, scale=None, offset=None, antiquant_scale=
     # it is an unused tail, which nothing downstream reads
     y = torch.empty((M, N), dtype=out_dt, device=xs.device)
     _lib.call("tab_grouped_matmul_w8a8", _ptr(xs), _ptr(wp), _ptr(sc), _ptr(pts), _ptr(group_list), int(group_list_type or 0),
-              M, Kd, N, E, _ST_INV[out_dt], _ptr(y), _stream(xs))
+              M, Kd, N, E, _ST_INV[out_dt], _ptr(y), _expected_rows(tuning_config), _stream(xs))
     return [y]
 
 
@@ -412,10 +422,11 @@ def _gmm_sq_cuda(x, weight, weight_scale, x_scale, group_list, *, smooth_scale=N
     if weight_assist_matrix is not None and len(weight_assist_matrix):
         raise NotImplementedError(f"{op}: weight_assist_matrix is outside the W8A8 MoE path")
     _only_default(op, dequant_mode=(dequant_mode or 0, 0), quant_mode=(quant_mode or 0, 0), quant_dtype=(quant_dtype or 1, 1))
-    return fused_gate_up(x, weight[0], weight_scale[0], x_scale, group_list, int(group_list_type or 0), True, yq, ys)
+    return fused_gate_up(x, weight[0], weight_scale[0], x_scale, group_list, int(group_list_type or 0), True, yq, ys,
+                         _expected_rows(tuning_config))
 
 
-def fused_gate_up(x, w, w_scale, x_scale, group_list, group_list_type, activate_left, yq=None, ys=None):
+def fused_gate_up(x, w, w_scale, x_scale, group_list, group_list_type, activate_left, yq=None, ys=None, expected_rows=0):
     """gate_up grouped GEMM + dequant + SwiGLU + per-row int8 requant in one call (two kernels)."""
     if x.dtype != torch.int8 or w.dtype != torch.int8:
         raise NotImplementedError("fused gate_up: only int8 x int8 (W8A8) is on the path")
@@ -434,7 +445,8 @@ def fused_gate_up(x, w, w_scale, x_scale, group_list, group_list_type, activate_
     wp = packed_weight(w)
     ws = _workspace(_lib.workspace_bytes("tab_grouped_matmul_swiglu_quant_workspace_bytes", M, I), x.device)
     _lib.call("tab_grouped_matmul_swiglu_quant", _ptr(x), _ptr(wp), _ptr(w_scale), _ptr(x_scale), _ptr(group_list),
-              group_list_type, M, Kd, I, E, int(bool(activate_left)), _ptr(yq), _ptr(ys), _ptr(ws), ws.numel(), _stream(x))
+              group_list_type, M, Kd, I, E, int(bool(activate_left)), _ptr(yq), _ptr(ys), _ptr(ws), ws.numel(), int(expected_rows),
+              _stream(x))
     return yq, ys
 
 
@@ -494,12 +506,14 @@ def _gmm_fr_cuda(x, w, group_list, *, scale=None, bias=None, offset=None, pertok
     _lib.call("tab_grouped_matmul_finalize_routing", _ptr(x), _ptr(wp), _ptr(scale), _ptr(bias), _ptr(pertoken_scale),
               _ptr(group_list), int(1 if group_list_type is None else group_list_type), M, Kd, N, E, _ptr(shared_input), shared_rows,
               float(1.0 if shared_input_weight is None else shared_input_weight), int(shared_input_offset or 0), _ptr(logit),
-              _ptr(row_index), 3 if row_index.dtype == torch.int32 else 4, y.shape[0], _ptr(y), _ptr(ws), ws.numel(), _stream(x))
+              _ptr(row_index), 3 if row_index.dtype == torch.int32 else 4, y.shape[0], _ptr(y), _ptr(ws), ws.numel(),
+              _expected_rows(tuning_config), _stream(x))
     return y
 
 
 def fused_down_combine(hq, w2, s2, hs, group_list, group_list_type, expert_ids, expand_idx, ep_send_counts, expert_scales,
-                       group_ep, ep_world_size, ep_rank_id, moe_expert_num, shared_expert_x=None, out_dtype=torch.bfloat16):
+                       group_ep, ep_world_size, ep_rank_id, moe_expert_num, shared_expert_x=None, out_dtype=torch.bfloat16,
+                       expected_rows=0):
     """Down projection + npu_moe_distribute_combine as one step.
 
     With more than one rank on the peer-memory transport the grouped GEMM's epilogue stores every output row straight
@@ -511,7 +525,8 @@ def fused_down_combine(hq, w2, s2, hs, group_list, group_list_type, expert_ids, 
     od = 15 if out_dtype == torch.bfloat16 else 5
     if R == 1 or ep.transport_of(group_ep, hq.is_cuda) != "peer":
         y = torch.ops.npu.npu_grouped_matmul([hq], [w2], scale=[s2], per_token_scale=[hs], group_list=group_list, split_item=2,
-                                             group_type=0, group_list_type=group_list_type, output_dtype=od)[0]
+                                             group_type=0, group_list_type=group_list_type, output_dtype=od,
+                                             tuning_config=[int(expected_rows)])[0]
         return torch.ops.npu.npu_moe_distribute_combine(y, expert_ids, expand_idx, ep_send_counts, expert_scales, group_ep, R,
                                                         ep_rank_id, moe_expert_num, shared_expert_x=shared_expert_x)
     if hq.dtype != torch.int8 or w2.dtype != torch.int8:
@@ -527,7 +542,7 @@ def fused_down_combine(hq, w2, s2, hs, group_list, group_list_type, expert_ids, 
 
     def produce_rows(row_dst):
         _lib.call("tab_grouped_matmul_w8a8_scatter", _ptr(hq), _ptr(wp), _ptr(s2), _ptr(hs), _ptr(gl), int(group_list_type), M, Kd, N,
-                  E_l, od, _ptr(row_dst), _stream(hq))
+                  E_l, od, _ptr(row_dst), int(expected_rows), _stream(hq))
 
     return ep.combine_from_producer(ep.CudaKernels, produce_rows, M, N, out_dtype, expert_ids, expand_idx, ep_send_counts,
                                     expert_scales, group_ep, R, ep_rank_id, moe_expert_num, shared_expert_x)
