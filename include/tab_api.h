@@ -68,6 +68,17 @@ TAB_API const char* tab_last_error(void);
 TAB_API int tab_dynamic_quant(const void* x, int x_dtype, const void* smooth, int64_t rows, int64_t cols,
                       int8_t* y, float* scale, tab_stream_t stream);
 
+/* tab_quant_status: host-side; synchronises `stream` and copies the status word of the row kernels that stream rows
+ * through shared memory (tab_dynamic_quant, tab_dequant_swiglu_quant): 0, or 1 after a bounded wait for a bulk copy gave
+ * up (TAB_ERR_TIMEOUT); the CTA then stops and leaves its remaining rows unwritten.  No counterpart in the reference. */
+TAB_API int tab_quant_status(int* status_host, tab_stream_t stream);
+
+/* tab_selftest_reciprocal: adds to *mismatches (device uint64, zeroed by the caller) the number of significands, out
+ * of all 2^23 at the binary exponent `exponent`, for which the reciprocal used inside SwiGLU (hardware seed + one
+ * Newton step) differs from the IEEE reciprocal.  The SwiGLU results are reproducible on a CPU exactly when this is 0;
+ * the GPU tests check it.  No counterpart in the reference. */
+TAB_API int tab_selftest_reciprocal(int exponent, unsigned long long* mismatches, tab_stream_t stream);
+
 /* ---------------------------------------------------------------------------------------------------
  * npu_swiglu  (converter npu_swiglu.py:8-14 -> SwiGlu), last-dimension split only.
  * x [rows, cols] (cols even) of dtype 5, 6 or 15; y [rows, cols/2] = silu(x[:, :cols/2]) * x[:, cols/2:].

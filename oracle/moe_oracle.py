@@ -111,7 +111,7 @@ def dynamic_quant(x: torch.Tensor, smooth_scales: Optional[torch.Tensor] = None)
 # --------------------------------------------------------------------------------------------------
 # SwiGLU arithmetic: silu(a) * b with a deterministic exp
 # --------------------------------------------------------------------------------------------------
-# Decision: silu(a) * b = RN(RN(a / (1 + e)) * b), e = exp(-a) by a fixed sequence of correctly rounded fp32 operations
+# Decision: silu(a) * b = RN(RN(a * RN(1 / (1 + e))) * b), e = exp(-a) by a fixed sequence of correctly rounded fp32 operations
 # (the same sequence as oracle/silu_exact.c and the CUDA kernels), so that CPU and GPU agree bit for bit.  A libm exp
 # (what F.silu calls) differs between CPU and GPU in the last place, which would move int8 values after SwiGLU by one
 # step at rounding ties.  SILU_IMPL = "libm" selects F.silu instead: the literal eager-torch formula, used by the timed
@@ -154,7 +154,8 @@ def _silu_mul_exact_torch(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
         p = _fma32(p, f, c)
     e = (p.view(torch.int32) + (n.to(torch.int32) << 23)).view(torch.float32)
     d = 1.0 + e
-    return (a / d) * b
+    y = torch.ones_like(d) / d          # IEEE reciprocal (tensor / tensor)
+    return (a * y) * b
 
 
 _silu_lib = None

@@ -2,8 +2,8 @@
  *
  * The reference defines SwiGLU only as an IR node (SwiGlu: converter npu_swiglu.py:8-14; DequantSwigluQuant:
  * third_party/ascend/include/ops/op_proto/inc/experiment_ops.h:3764-3811); its arithmetic is vendor code.  Decision:
- * silu(a) * b = RN(RN(a / (1 + e)) * b) with e = exp(-a) evaluated by the fixed sequence of fp32 operations below
- * (fused multiply-adds, one exponent insertion), each of them correctly rounded, so that a CPU and a GPU that run the
+ * silu(a) * b = RN(RN(a * RN(1 / (1 + e))) * b) with e = exp(-a) evaluated by the fixed sequence of fp32 operations below
+ * (fused multiply-adds, one exponent insertion, one IEEE reciprocal), each of them correctly rounded, so that a CPU and a GPU that run the
  * same sequence agree bit for bit.  e is within 1.3 ulp of exp(-a) for |a| <= 80 apart from the rounded log2(e)
  * (relative error |a| * 1.3e-8); beyond that -a is capped, where 1 + e is 1 or the result is below 1e-33.
  *
@@ -44,8 +44,9 @@ static inline float silu_mul_exact(float a, float b) {
   float e;
   memcpy(&e, &pb, 4);
   const float d = 1.0f + e;
-  const float q = a / d;
-  return q * b;
+  const float y = 1.0f / d;            /* IEEE reciprocal */
+  const float s = a * y;
+  return s * b;
 }
 
 /* out[i] = silu(a[i]) * b[i] */

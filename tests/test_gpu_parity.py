@@ -891,3 +891,17 @@ def test_scatter_gemm_skips_rows_without_a_destination(dev):
         keep = ~skipped
         assert torch.equal(got[perm[keep]], ref[keep])
         assert bool((got[perm[skipped]] == 7.0).all()), "rows with a null destination must stay untouched"
+
+
+def test_swiglu_reciprocal_is_the_ieee_reciprocal_for_every_significand(dev):
+    """SwiGLU divides through a reciprocal built from the hardware seed and one Newton step.  Its results are reproducible
+    on a CPU only if that reciprocal is the correctly rounded one: checked exhaustively, all 2^23 significands, at the
+    exponents that 1 + exp(-a) takes between its bounds (2^0 .. 2^115) and below."""
+    import ctypes
+    from torchair_b200 import _lib
+    bad = torch.zeros(1, dtype=torch.int64, device=dev)
+    stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    for exponent in (0, 1, 2, 23, 24, 57, 100, 115, -3):
+        _lib.call("tab_selftest_reciprocal", exponent, ctypes.c_void_p(bad.data_ptr()), stream)
+    torch.cuda.synchronize(dev)
+    assert int(bad.item()) == 0

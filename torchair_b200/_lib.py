@@ -56,6 +56,8 @@ SIGNATURES = {
     "tab_gmm_status": [POINTER(c_int), _P],
     "tab_gmm_status_reset": [_P],
     "tab_routing_status": [POINTER(c_int), _P],
+    "tab_quant_status": [POINTER(c_int), _P],
+    "tab_selftest_reciprocal": [_I, _P, _P],
 }
 _RESTYPE = {"tab_last_error": c_char_p, "tab_launch_count": ctypes.c_longlong}
 

@@ -3,11 +3,207 @@
 // (64, 128 or 256 threads, picked so that a thread owns a few 16-byte chunks), the row kept in registers in its
 // raw form between the amax pass and the store pass, many small CTAs per SM so that loads of one row overlap the
 // reduction and stores of others.
+#include "row_pipe.cuh"
 #include "tab_common.cuh"
 
 namespace tab {
 
+// Status word of the staged row kernels on this device: 0, or 1 after a bulk-copy wait ran out (tab_quant_status).
+__device__ int g_quant_status = 0;
+
 constexpr int kMaxChunks = 8;  // chunks of 8 elements a thread keeps in registers; longer rows re-read their tail
+
+// ---- staged form: rows of 1 KB .. 64 KB stream through a ring of shared-memory stages (row_pipe.cuh) ----------------
+constexpr int kRowStages = 3;
+constexpr int kRowThreads = 256;
+constexpr size_t kRowSmemBudget = 200 * 1024;   // per SM, for the rings of all resident CTAs
+
+// x [rows, cols] -> y int8, scale fp32; same arithmetic as dynamic_quant_kernel.  cols % 8 == 0, row bytes % 16 == 0.
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads) dynamic_quant_staged_kernel(const T* __restrict__ x, const T* __restrict__ smooth,
+                                                                          int64_t rows, int cols, int8_t* __restrict__ y,
+                                                                          float* __restrict__ scale) {
+  extern __shared__ __align__(128) uint8_t ring_mem[];
+  __shared__ uint64_t bars[kRowStages];
+  __shared__ float red[kRowThreads / 32];
+  const uint32_t row_bytes = static_cast<uint32_t>(cols) * sizeof(T);
+  RowRing<kRowStages> ring(ring_mem, bars, row_bytes, row_bytes);
+  __syncthreads();
+  const int64_t first = blockIdx.x, stride = gridDim.x;
+  if (threadIdx.x == 0)
+    for (int k = 0; k < kRowStages; ++k)
+      if (first + k * stride < rows) ring.issue(k, x + (first + k * stride) * cols);
+  const int nchunk = cols >> 3;
+  auto value = [&](const T* sr, int ch, float (&v)[8]) {
+    Raw8<T> raw;
+    raw.load(sr + ch * 8);
+    raw.unpack(v);
+    if (smooth != nullptr) {
+      float sm[8];
+      Elem<T>::load8(smooth + ch * 8, sm);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(v[i], sm[i]);
+    }
+  };
+  int k = 0;
+  for (int64_t row = first; row < rows; row += stride, ++k) {
+    if (!__syncthreads_and(ring.wait(k) ? 1 : 0)) {
+      if (threadIdx.x == 0) atomicCAS(&g_quant_status, 0, 1);
+      break;
+    }
+    const T* sr = reinterpret_cast<const T*>(ring_mem + ring.stage_offset(k));
+    float amax = 0.f;
+    if (smooth == nullptr) {
+#pragma unroll 4
+      for (int ch = threadIdx.x; ch < nchunk; ch += kRowThreads) {
+        Raw8<T> raw;
+        raw.load(sr + ch * 8);
+        amax = fmaxf(amax, raw_amax(raw));
+      }
+    } else {
+      for (int ch = threadIdx.x; ch < nchunk; ch += kRowThreads) {
+        float v[8];
+        value(sr, ch, v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+      }
+    }
+    amax = cta_max<kRowThreads>(amax, red);
+    const RowQuant sc = make_row_quant(amax);
+    if (threadIdx.x == 0) scale[row] = sc.scale;
+    int8_t* yr = y + row * cols;
+    if (smooth == nullptr && sc.scale > 0.f && !sc.exact) {
+      // the common case, free of per-element branches: raw row, four full-rate instructions per element
+      const float inv = sc.inv, scl = sc.scale;
+#pragma unroll 2
+      for (int ch = threadIdx.x; ch < nchunk; ch += kRowThreads) {
+        Raw8<T> raw;
+        raw.load(sr + ch * 8);
+        float v[8];
+        raw.unpack(v);
+        uint32_t w[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float q0 = __fmul_rn(v[i], inv);
+          const float r = __fmaf_rn(-q0, scl, v[i]);
+          w[i] = __float_as_uint(__fadd_rn(__fmaf_rn(r, inv, q0), kRoundMagic));
+        }
+        __stcs(reinterpret_cast<uint2*>(yr + ch * 8), make_uint2(pack4_words(w[0], w[1], w[2], w[3]), pack4_words(w[4], w[5], w[6], w[7])));
+      }
+    } else {
+      for (int ch = threadIdx.x; ch < nchunk; ch += kRowThreads) {
+        float v[8];
+        value(sr, ch, v);
+        __stcs(reinterpret_cast<uint2*>(yr + ch * 8), quant8(v, sc));
+      }
+    }
+    __syncthreads();   // the stage has been read by everyone: refill it
+    if (threadIdx.x == 0 && row + kRowStages * stride < rows) ring.issue(k + kRowStages, x + (row + kRowStages * stride) * cols);
+  }
+}
+
+// x int32 [rows, 2*half] -> y int8 [rows, half], scale [rows]; same arithmetic as dequant_swiglu_quant_kernel.  A thread
+// takes four channels at a time: gate and up quadruples from the staged row, the fp32 SwiGLU values go back into the
+// row's gate half in place, the second pass quantises them from there.  half % 8 == 0.
+template <bool kLeft, bool kHasWs>
+__global__ void __launch_bounds__(kRowThreads) dequant_swiglu_quant_staged_kernel(
+    const int32_t* __restrict__ x, const float* __restrict__ wscale, int ws_groups, const float* __restrict__ ascale,
+    const int64_t* __restrict__ group_index, int num_groups, int64_t rows, int half,
+    int8_t* __restrict__ y, float* __restrict__ scale) {
+  extern __shared__ __align__(128) uint8_t ring_mem[];
+  __shared__ uint64_t bars[kRowStages];
+  __shared__ float red[kRowThreads / 32];
+  const uint32_t row_bytes = static_cast<uint32_t>(half) * 8u;
+  int* s_end = reinterpret_cast<int*>(ring_mem + kRowStages * row_bytes);   // [num_groups], behind the ring
+  if (group_index != nullptr) group_ends_to_smem(group_index, /*cumulative=*/0, num_groups, s_end);
+  RowRing<kRowStages> ring(ring_mem, bars, row_bytes, row_bytes);
+  __syncthreads();
+  const int64_t first = blockIdx.x, stride = gridDim.x;
+  if (threadIdx.x == 0)
+    for (int k = 0; k < kRowStages; ++k)
+      if (first + k * stride < rows) ring.issue(k, x + (first + k * stride) * 2 * half);
+  const int nquad = half >> 2;
+  int k = 0;
+  for (int64_t row = first; row < rows; row += stride, ++k) {
+    if (!__syncthreads_and(ring.wait(k) ? 1 : 0)) {
+      if (threadIdx.x == 0) atomicCAS(&g_quant_status, 0, 1);
+      break;
+    }
+    int32_t* sr = reinterpret_cast<int32_t*>(ring_mem + ring.stage_offset(k));
+    const int g = group_index != nullptr ? group_of_row(s_end, num_groups, row) : 0;   // uniform over the CTA
+    int8_t* yr = y + row * half;
+    if (g < 0) {  // row outside every group
+      for (int q = threadIdx.x; q < nquad; q += kRowThreads) *reinterpret_cast<uint32_t*>(yr + q * 4) = 0u;
+      if (threadIdx.x == 0) scale[row] = 0.f;
+    } else {
+      const float as = ascale ? ascale[row] : 1.0f;
+      const float* ws = kHasWs ? wscale + (ws_groups > 1 ? static_cast<int64_t>(g) * 2 * half : 0) : nullptr;
+      float amax = 0.f;
+#pragma unroll 2
+      for (int q = threadIdx.x; q < nquad; q += kRowThreads) {
+        const int4 l = *reinterpret_cast<const int4*>(sr + q * 4);
+        const int4 r = *reinterpret_cast<const int4*>(sr + half + q * 4);
+        float lv[4] = {__fmul_rn(__int2float_rn(l.x), as), __fmul_rn(__int2float_rn(l.y), as), __fmul_rn(__int2float_rn(l.z), as),
+                       __fmul_rn(__int2float_rn(l.w), as)};
+        float rv[4] = {__fmul_rn(__int2float_rn(r.x), as), __fmul_rn(__int2float_rn(r.y), as), __fmul_rn(__int2float_rn(r.z), as),
+                       __fmul_rn(__int2float_rn(r.w), as)};
+        if constexpr (kHasWs) {
+          const float4 wl = __ldg(reinterpret_cast<const float4*>(ws + q * 4));
+          const float4 wr = __ldg(reinterpret_cast<const float4*>(ws + half + q * 4));
+          lv[0] = __fmul_rn(lv[0], wl.x); lv[1] = __fmul_rn(lv[1], wl.y); lv[2] = __fmul_rn(lv[2], wl.z); lv[3] = __fmul_rn(lv[3], wl.w);
+          rv[0] = __fmul_rn(rv[0], wr.x); rv[1] = __fmul_rn(rv[1], wr.y); rv[2] = __fmul_rn(rv[2], wr.z); rv[3] = __fmul_rn(rv[3], wr.w);
+        }
+        float h[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          h[i] = kLeft ? silu_mul(lv[i], rv[i]) : silu_mul(rv[i], lv[i]);
+          amax = fmaxf(amax, fabsf(h[i]));
+        }
+        *reinterpret_cast<float4*>(sr + q * 4) = make_float4(h[0], h[1], h[2], h[3]);     // in place over the gate quadruple
+      }
+      amax = cta_max<kRowThreads>(amax, red);
+      const RowQuant sc = make_row_quant(amax);
+      if (threadIdx.x == 0) scale[row] = sc.scale;
+      const float* hr = reinterpret_cast<const float*>(sr);
+      if (sc.scale > 0.f && !sc.exact) {
+        const float inv = sc.inv, scl = sc.scale;
+#pragma unroll 2
+        for (int q = threadIdx.x; q < nquad; q += kRowThreads) {          // every thread re-reads the quadruples it wrote
+          const float4 a = *reinterpret_cast<const float4*>(hr + q * 4);
+          const float v[4] = {a.x, a.y, a.z, a.w};
+          uint32_t w[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float q0 = __fmul_rn(v[i], inv);
+            const float r = __fmaf_rn(-q0, scl, v[i]);
+            w[i] = __float_as_uint(__fadd_rn(__fmaf_rn(r, inv, q0), kRoundMagic));
+          }
+          __stcs(reinterpret_cast<uint32_t*>(yr + q * 4), pack4_words(w[0], w[1], w[2], w[3]));
+        }
+      } else {
+        for (int q = threadIdx.x; q < nquad; q += kRowThreads) {
+          const float4 a = *reinterpret_cast<const float4*>(hr + q * 4);
+          const float v[4] = {a.x, a.y, a.z, a.w};
+          __stcs(reinterpret_cast<uint32_t*>(yr + q * 4), quant4(v, sc));
+        }
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && row + kRowStages * stride < rows)
+      ring.issue(k + kRowStages, x + (row + kRowStages * stride) * 2 * half);
+  }
+}
+
+// Persistent grid and ring size for a staged row kernel, or 0 when the rows do not suit it (tiny or too long for three
+// stages): CTAs per SM by the shared-memory budget, at most 8.
+static int staged_grid(int64_t rows, size_t row_bytes, size_t* smem_bytes) {
+  if (row_bytes < 1024 || row_bytes % 16 != 0 || row_bytes * kRowStages > 100 * 1024) return 0;
+  *smem_bytes = row_bytes * kRowStages;
+  size_t per_sm = kRowSmemBudget / (*smem_bytes + 1024);
+  if (per_sm > 8) per_sm = 8;
+  if (per_sm < 1) per_sm = 1;
+  return grid_for(rows, static_cast<int>(per_sm));
+}
 
 // x [rows, cols] -> y int8, scale fp32.  cols % 8 == 0.
 template <typename T, int THREADS>
@@ -81,7 +277,7 @@ __global__ void __launch_bounds__(THREADS) dynamic_quant_kernel(const T* __restr
 
 // y[r, c] = silu(x[r, c]) * x[r, c + half]; one thread per 8 output elements.  A CTA of 256 threads covers
 // 256 / tpr rows at a time with tpr threads per row (tpr = a power of two, at most 256, chosen by the host so that
-// short rows still fill the CTA); no division in the loop.
+// short rows still fill the CTA).  Pointers advance by a constant per row step: no multiply or division in the loop.
 template <typename T>
 __global__ void __launch_bounds__(256) swiglu_kernel(const T* __restrict__ x, int64_t rows, int half, int tpr_log2,
                                                      T* __restrict__ y) {
@@ -89,10 +285,12 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const T* __restrict__ x, in
   const int tpr = 1 << tpr_log2;
   const int rows_per_cta = 256 >> tpr_log2;
   const int lane_in_row = threadIdx.x & (tpr - 1);
-  for (int64_t r = static_cast<int64_t>(blockIdx.x) * rows_per_cta + (threadIdx.x >> tpr_log2); r < rows;
-       r += static_cast<int64_t>(gridDim.x) * rows_per_cta) {
-    const T* xr = x + r * 2 * half;
-    T* yr = y + r * half;
+  const int64_t r0 = static_cast<int64_t>(blockIdx.x) * rows_per_cta + (threadIdx.x >> tpr_log2);
+  const int64_t row_step = static_cast<int64_t>(gridDim.x) * rows_per_cta;
+  const T* xr = x + r0 * 2 * half;
+  T* yr = y + r0 * half;
+  const int64_t x_step = row_step * 2 * half, y_step = row_step * half;
+  for (int64_t r = r0; r < rows; r += row_step, xr += x_step, yr += y_step) {
     for (int ch = lane_in_row; ch < chunks_per_row; ch += tpr) {
       float a[8], b[8], o[8];
       Elem<T>::load8(xr + ch * 8, a);
@@ -245,6 +443,13 @@ static void launch_dynamic_quant(const void* x, const void* smooth, int64_t rows
   const int nchunk = cols / 8;
   const T* xp = static_cast<const T*>(x);
   const T* sp = static_cast<const T*>(smooth);
+  size_t smem = 0;
+  const int sgrid = rows >= 64 ? staged_grid(rows, static_cast<size_t>(cols) * sizeof(T), &smem) : 0;
+  if (sgrid > 0 &&
+      cudaFuncSetAttribute(dynamic_quant_staged_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) == cudaSuccess) {
+    dynamic_quant_staged_kernel<T><<<sgrid, kRowThreads, smem, st>>>(xp, sp, rows, cols, y, scale);
+    return;
+  }
   if (nchunk <= 64 * kMaxChunks / 2)
     dynamic_quant_kernel<T, 64><<<grid_for(rows, 16), 64, 0, st>>>(xp, sp, rows, cols, y, scale);
   else if (nchunk <= 128 * kMaxChunks)
@@ -317,6 +522,25 @@ extern "C" int tab_dequant_swiglu_quant(const int32_t* x, const float* weight_sc
   if (num_groups > kMaxDsqGroups) return fail(TAB_ERR_UNSUPPORTED, "dequant_swiglu_quant: more than %d groups", kMaxDsqGroups);
   cudaStream_t st = as_stream(stream);
   const int nchunk = (int)(half / 8);
+  size_t ring_bytes = 0;
+  int sgrid = rows >= 64 ? staged_grid(rows, static_cast<size_t>(half) * 8, &ring_bytes) : 0;
+  ring_bytes += static_cast<size_t>(num_groups) * sizeof(int);
+  if (ring_bytes > 200 * 1024) sgrid = 0;
+  if (sgrid > 0) {
+#define TAB_DSQ(L, W)                                                                                                            \
+  if (cudaFuncSetAttribute(dequant_swiglu_quant_staged_kernel<L, W>, cudaFuncAttributeMaxDynamicSharedMemorySize,               \
+                           static_cast<int>(ring_bytes)) == cudaSuccess) {                                                      \
+    dequant_swiglu_quant_staged_kernel<L, W><<<sgrid, kRowThreads, ring_bytes, st>>>(x, weight_scale, (int)ws_groups, activation_scale, \
+                                                                                    group_index, (int)num_groups, rows, (int)half, y, scale); \
+    return check_launch("dequant_swiglu_quant");                                                                               \
+  }
+    if (activate_left) {
+      if (weight_scale) { TAB_DSQ(true, true) } else { TAB_DSQ(true, false) }
+    } else {
+      if (weight_scale) { TAB_DSQ(false, true) } else { TAB_DSQ(false, false) }
+    }
+#undef TAB_DSQ
+  }
   const size_t smem = group_index ? static_cast<size_t>(num_groups) * sizeof(int) : 0;
   if (nchunk <= 64 * kDsqChunks / 2)
     dequant_swiglu_quant_kernel<64><<<row_grid(rows, 64), 64, smem, st>>>(x, weight_scale, (int)ws_groups, activation_scale, group_index, (int)num_groups, activate_left, rows, (int)half, y, scale);
@@ -325,4 +549,28 @@ extern "C" int tab_dequant_swiglu_quant(const int32_t* x, const float* weight_sc
   else
     dequant_swiglu_quant_kernel<256><<<row_grid(rows, 256), 256, smem, st>>>(x, weight_scale, (int)ws_groups, activation_scale, group_index, (int)num_groups, activate_left, rows, (int)half, y, scale);
   return check_launch("dequant_swiglu_quant");
+}
+
+extern "C" int tab_quant_status(int* status_host, tab_stream_t stream) {
+  if (!status_host) return fail(TAB_ERR_BAD_ARG, "quant_status: null pointer");
+  cudaError_t e = cudaStreamSynchronize(as_stream(stream));
+  if (e == cudaSuccess) e = cudaMemcpyFromSymbol(status_host, g_quant_status, sizeof(int));
+  if (e != cudaSuccess) return fail(TAB_ERR_CUDA, "quant_status: %s", cudaGetErrorString(e));
+  if (*status_host != 0) return fail(TAB_ERR_TIMEOUT, "row kernels: a bulk-copy wait gave up (status %d)", *status_host);
+  return TAB_OK;
+}
+
+// Exhaustive self-test of rcp_rn_normal against the library's IEEE reciprocal: all 2^23 significands at one exponent.
+namespace tab {
+__global__ void __launch_bounds__(256) selftest_reciprocal_kernel(int exponent, unsigned long long* mismatches) {
+  const unsigned m = blockIdx.x * 256u + threadIdx.x;
+  const float d = __uint_as_float((static_cast<unsigned>(127 + exponent) << 23) | m);
+  if (rcp_rn_normal(d) != __frcp_rn(d)) atomicAdd(mismatches, 1ull);
+}
+}  // namespace tab
+
+extern "C" int tab_selftest_reciprocal(int exponent, unsigned long long* mismatches, tab_stream_t stream) {
+  if (!mismatches || exponent < -100 || exponent > 120) return fail(TAB_ERR_BAD_ARG, "selftest_reciprocal: exponent %d (want -100..120)", exponent);
+  selftest_reciprocal_kernel<<<(1 << 23) / 256, 256, 0, as_stream(stream)>>>(exponent, mismatches);
+  return check_launch("selftest_reciprocal");
 }

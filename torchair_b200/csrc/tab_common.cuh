@@ -116,15 +116,25 @@ __device__ __forceinline__ uint32_t pack4_i8(int a, int b, int c, int d) {
          ((static_cast<uint32_t>(c) & 0xffu) << 16) | ((static_cast<uint32_t>(d) & 0xffu) << 24);
 }
 
-// silu(a) * b = RN(RN(a / (1 + e)) * b) in fp32 with e = exp(-a) from a fixed sequence of correctly rounded operations
-// (two FMAs of range reduction with the rounded log2(e), a degree-6 polynomial for 2^f on [-0.5, 0.5] in Horner form,
-// the integer part added into the exponent field, IEEE division), so that a CPU restatement of the same sequence gives
-// the same bits: int8 values quantised after SwiGLU then do not depend on whose exp() was used.  e is within 1.3 ulp of
-// exp(-a) apart from the rounded log2(e) (relative error |a| * 1.3e-8).  -a is capped to [-80, 80]: beyond it 1 + e is 1,
-// or the result is below 1e-33 in magnitude.  No special-function unit result enters the value (the division's
-// reciprocal seed is corrected to the IEEE quotient by the library).
+// IEEE reciprocal RN(1/d) of a normal d whose reciprocal is normal too (here d = 1 + e lies in [1, 5.6e34]): the
+// hardware seed followed by one Newton step in FMAs.  On sm_100 this equals the correctly rounded reciprocal for every
+// one of the 2^23 significands (checked exhaustively against the library's IEEE reciprocal by tab_selftest_reciprocal,
+// which the GPU tests run); scaling by a power of two changes no step, so it holds for every exponent in range.  Two
+// FMAs instead of the library's checked sequence with its out-of-line slow path.
+__device__ __forceinline__ float rcp_rn_normal(float d) {
+  float y;
+  asm("rcp.approx.f32 %0, %1;" : "=f"(y) : "f"(d));
+  return __fmaf_rn(__fmaf_rn(-d, y, 1.0f), y, y);
+}
+
+// silu(a) * b = RN(RN(a * RN(1 / (1 + e))) * b) in fp32 with e = exp(-a) from a fixed sequence of correctly rounded
+// operations (two FMAs of range reduction with the rounded log2(e), a degree-6 polynomial for 2^f on [-0.5, 0.5] in
+// Horner form, the integer part added into the exponent field, the IEEE reciprocal), so that a CPU restatement of the
+// same sequence gives the same bits: int8 values quantised after SwiGLU then do not depend on whose exp() was used.  e
+// is within 1.3 ulp of exp(-a) apart from the rounded log2(e) (relative error |a| * 1.3e-8).  -a is capped to
+// [-80, 80]: beyond it 1 + e is 1, or the result is below 1e-33 in magnitude.  20 instructions, no branch.
 // Building with -DTAB_FAST_SILU swaps in the earlier form (hardware ex2.approx and an approximate reciprocal with one
-// remainder correction: about half the instructions, results within a few ulp but not reproducible on a CPU).
+// remainder correction: half the instructions, results within a few ulp but not reproducible on a CPU).
 constexpr float kLog2e = 0x1.715476p+0f;
 constexpr float kRoundMagicF = 12582912.0f;   // 1.5 * 2^23
 __device__ __forceinline__ float silu_mul(float a, float b) {
@@ -152,7 +162,7 @@ __device__ __forceinline__ float silu_mul(float a, float b) {
   p = __fmaf_rn(p, f, 1.0f);
   const float e = __uint_as_float(__float_as_uint(p) + (__float_as_uint(nm) << 23));   // p * 2^n
   const float d = __fadd_rn(1.0f, e);
-  return __fmul_rn(__fdiv_rn(a, d), b);
+  return __fmul_rn(__fmul_rn(a, rcp_rn_normal(d)), b);
 #endif
 }
 
@@ -269,6 +279,25 @@ __device__ __forceinline__ uint2 quant8(const float (&v)[8], const RowQuant& rq)
   o.x = pack4_words(w[0], w[1], w[2], w[3]);
   o.y = pack4_words(w[4], w[5], w[6], w[7]);
   return o;
+}
+
+// Four values -> four int8 in one word; the arithmetic of quant8.
+__device__ __forceinline__ uint32_t quant4(const float (&v)[4], const RowQuant& rq) {
+  if (!(rq.scale > 0.f)) return 0u;
+  uint32_t w[4];
+  if (!rq.exact) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float q0 = __fmul_rn(v[i], rq.inv);
+      const float r = __fmaf_rn(-q0, rq.scale, v[i]);
+      const float q1 = __fmaf_rn(r, rq.inv, q0);
+      w[i] = __float_as_uint(__fadd_rn(q1, kRoundMagic));
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) w[i] = quant_word_exact(v[i], rq.scale);
+  }
+  return pack4_words(w[0], w[1], w[2], w[3]);
 }
 
 // max |x| over the 8 packed 16-bit elements of a raw chunk, without unpacking

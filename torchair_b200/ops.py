@@ -596,6 +596,7 @@ def check_status(device=None) -> None:
             if st_.value:
                 gmm_status_reset(dev)
             raise RuntimeError(f"grouped GEMM status {st_.value}: {msg}")
+        _lib.call("tab_quant_status", ctypes.byref(st_), ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
     st = ep.peer_status()
     if st:
         raise RuntimeError(f"peer-memory exchange status {st}: a flag wait ran out of time or a slot overflowed")
