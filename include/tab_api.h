@@ -75,8 +75,9 @@ TAB_API int tab_quant_status(int* status_host, tab_stream_t stream);
 
 /* tab_selftest_reciprocal: adds to *mismatches (device uint64, zeroed by the caller) the number of significands, out
  * of all 2^23 at the binary exponent `exponent`, for which the reciprocal used inside SwiGLU (hardware seed + one
- * Newton step) differs from the IEEE reciprocal.  The SwiGLU results are reproducible on a CPU exactly when this is 0;
- * the GPU tests check it.  No counterpart in the reference. */
+ * Newton step) differs from the IEEE reciprocal, plus those for which the row quantiser's short forms of amax / 127
+ * and of its reciprocal differ from IEEE division.  Results are reproducible on a CPU exactly when this is 0; the GPU
+ * tests check it.  No counterpart in the reference. */
 TAB_API int tab_selftest_reciprocal(int exponent, unsigned long long* mismatches, tab_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------

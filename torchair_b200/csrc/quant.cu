@@ -13,21 +13,60 @@ __device__ int g_quant_status = 0;
 
 constexpr int kMaxChunks = 8;  // chunks of 8 elements a thread keeps in registers; longer rows re-read their tail
 
-// ---- staged form: rows of 1 KB .. 64 KB stream through a ring of shared-memory stages (row_pipe.cuh) ----------------
+// ---- staged form: rows of 1 KB .. 48 KB stream through a ring of shared-memory stages (row_pipe.cuh) ----------------
+// One CTA barrier per row: the warps publish their maxima (double-buffered by row parity), every thread then reduces the
+// eight values and derives the row's scale itself (a handful of instructions, see make_row_quant_fast); the stage of the
+// previous row is refilled right after that barrier, when every thread is provably done with it.
 constexpr int kRowStages = 3;
 constexpr int kRowThreads = 256;
 constexpr size_t kRowSmemBudget = 200 * 1024;   // per SM, for the rings of all resident CTAs
 
+// amax / 127 and its reciprocal without the library's checked division: q = RN(amax / 127) by one correction step from
+// the correctly rounded reciprocal of 127 (exact for every amax whose quotient and remainder are normal), inv by
+// rcp_rn_normal.  Rows outside the safe range, and scales whose significand is all ones, take make_row_quant.
+__device__ __forceinline__ RowQuant make_row_quant_fast(float amax) {
+  if (!(amax > 1e-24f && amax < 1e30f)) return make_row_quant(amax);
+  constexpr float kInv127 = 0x1.020408p-7f;    // RN(1 / 127)
+  const float q0 = __fmul_rn(amax, kInv127);
+  const float r = __fmaf_rn(-127.0f, q0, amax);
+  RowQuant rq;
+  rq.scale = __fmaf_rn(r, kInv127, q0);
+  rq.inv = rcp_rn_normal(rq.scale);
+  rq.exact = (__float_as_uint(rq.scale) & 0x7fffffu) == 0x7fffffu;
+  return rq;
+}
+
+// Maximum over the CTA with one barrier; `red` is this row's buffer of one float per warp.
+__device__ __forceinline__ float cta_max_once(float v, float* red) {
+  v = warp_max(v);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  const float4 a = *reinterpret_cast<const float4*>(red), b = *reinterpret_cast<const float4*>(red + 4);
+  return fmaxf(fmaxf(fmaxf(a.x, a.y), fmaxf(a.z, a.w)), fmaxf(fmaxf(b.x, b.y), fmaxf(b.z, b.w)));
+}
+
+// Waits for ring slot k unless an earlier wait of this CTA already ran out; a wait that runs out is recorded.
+template <int STAGES>
+__device__ __forceinline__ void ring_wait_or_flag(const RowRing<STAGES>& ring, int k, volatile int* s_fail) {
+  if (*s_fail == 0 && !ring.wait(k)) {
+    *s_fail = 1;
+    atomicCAS(&g_quant_status, 0, 1);
+  }
+}
+
 // x [rows, cols] -> y int8, scale fp32; same arithmetic as dynamic_quant_kernel.  cols % 8 == 0, row bytes % 16 == 0.
-template <typename T>
+template <typename T, bool kSmooth>
 __global__ void __launch_bounds__(kRowThreads) dynamic_quant_staged_kernel(const T* __restrict__ x, const T* __restrict__ smooth,
                                                                           int64_t rows, int cols, int8_t* __restrict__ y,
                                                                           float* __restrict__ scale) {
+  static_assert(kRowThreads == 256, "cta_max_once reads eight warp maxima");
   extern __shared__ __align__(128) uint8_t ring_mem[];
   __shared__ uint64_t bars[kRowStages];
-  __shared__ float red[kRowThreads / 32];
+  __shared__ __align__(16) float red[2][kRowThreads / 32];
+  __shared__ int s_fail;
   const uint32_t row_bytes = static_cast<uint32_t>(cols) * sizeof(T);
   RowRing<kRowStages> ring(ring_mem, bars, row_bytes, row_bytes);
+  if (threadIdx.x == 0) s_fail = 0;
   __syncthreads();
   const int64_t first = blockIdx.x, stride = gridDim.x;
   if (threadIdx.x == 0)
@@ -38,7 +77,7 @@ __global__ void __launch_bounds__(kRowThreads) dynamic_quant_staged_kernel(const
     Raw8<T> raw;
     raw.load(sr + ch * 8);
     raw.unpack(v);
-    if (smooth != nullptr) {
+    if constexpr (kSmooth) {
       float sm[8];
       Elem<T>::load8(smooth + ch * 8, sm);
 #pragma unroll
@@ -47,13 +86,10 @@ __global__ void __launch_bounds__(kRowThreads) dynamic_quant_staged_kernel(const
   };
   int k = 0;
   for (int64_t row = first; row < rows; row += stride, ++k) {
-    if (!__syncthreads_and(ring.wait(k) ? 1 : 0)) {
-      if (threadIdx.x == 0) atomicCAS(&g_quant_status, 0, 1);
-      break;
-    }
+    ring_wait_or_flag(ring, k, &s_fail);
     const T* sr = reinterpret_cast<const T*>(ring_mem + ring.stage_offset(k));
     float amax = 0.f;
-    if (smooth == nullptr) {
+    if constexpr (!kSmooth) {
 #pragma unroll 4
       for (int ch = threadIdx.x; ch < nchunk; ch += kRowThreads) {
         Raw8<T> raw;
@@ -68,19 +104,20 @@ __global__ void __launch_bounds__(kRowThreads) dynamic_quant_staged_kernel(const
         for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
       }
     }
-    amax = cta_max<kRowThreads>(amax, red);
-    const RowQuant sc = make_row_quant(amax);
+    amax = cta_max_once(amax, red[k & 1]);
+    // every thread has left the previous row behind: its stage takes the row kRowStages - 1 ahead of this one
+    if (threadIdx.x == 0 && k >= 1 && row + (kRowStages - 1) * stride < rows)
+      ring.issue(k - 1 + kRowStages, x + (row + (kRowStages - 1) * stride) * cols);
+    const RowQuant sc = make_row_quant_fast(amax);
     if (threadIdx.x == 0) scale[row] = sc.scale;
     int8_t* yr = y + row * cols;
-    if (smooth == nullptr && sc.scale > 0.f && !sc.exact) {
-      // the common case, free of per-element branches: raw row, four full-rate instructions per element
+    if (sc.scale > 0.f && !sc.exact) {
+      // the common case, free of per-element branches: four full-rate instructions per element
       const float inv = sc.inv, scl = sc.scale;
 #pragma unroll 2
       for (int ch = threadIdx.x; ch < nchunk; ch += kRowThreads) {
-        Raw8<T> raw;
-        raw.load(sr + ch * 8);
         float v[8];
-        raw.unpack(v);
+        value(sr, ch, v);
         uint32_t w[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -97,50 +134,51 @@ __global__ void __launch_bounds__(kRowThreads) dynamic_quant_staged_kernel(const
         __stcs(reinterpret_cast<uint2*>(yr + ch * 8), quant8(v, sc));
       }
     }
-    __syncthreads();   // the stage has been read by everyone: refill it
-    if (threadIdx.x == 0 && row + kRowStages * stride < rows) ring.issue(k + kRowStages, x + (row + kRowStages * stride) * cols);
   }
 }
 
 // x int32 [rows, 2*half] -> y int8 [rows, half], scale [rows]; same arithmetic as dequant_swiglu_quant_kernel.  A thread
 // takes four channels at a time: gate and up quadruples from the staged row, the fp32 SwiGLU values go back into the
-// row's gate half in place, the second pass quantises them from there.  half % 8 == 0.
-template <bool kLeft, bool kHasWs>
+// row's gate half in place (each thread re-reads only what it wrote), the second pass quantises them from there.
+// half % 8 == 0.
+// kQuads > 0: half == kQuads * 4 * kRowThreads exactly, the loops over a thread's quadruples unroll completely.
+template <bool kLeft, bool kHasWs, int kQuads>
 __global__ void __launch_bounds__(kRowThreads) dequant_swiglu_quant_staged_kernel(
     const int32_t* __restrict__ x, const float* __restrict__ wscale, int ws_groups, const float* __restrict__ ascale,
     const int64_t* __restrict__ group_index, int num_groups, int64_t rows, int half,
     int8_t* __restrict__ y, float* __restrict__ scale) {
   extern __shared__ __align__(128) uint8_t ring_mem[];
   __shared__ uint64_t bars[kRowStages];
-  __shared__ float red[kRowThreads / 32];
+  __shared__ __align__(16) float red[2][kRowThreads / 32];
+  __shared__ int s_fail;
   const uint32_t row_bytes = static_cast<uint32_t>(half) * 8u;
   int* s_end = reinterpret_cast<int*>(ring_mem + kRowStages * row_bytes);   // [num_groups], behind the ring
   if (group_index != nullptr) group_ends_to_smem(group_index, /*cumulative=*/0, num_groups, s_end);
   RowRing<kRowStages> ring(ring_mem, bars, row_bytes, row_bytes);
+  if (threadIdx.x == 0) s_fail = 0;
   __syncthreads();
   const int64_t first = blockIdx.x, stride = gridDim.x;
   if (threadIdx.x == 0)
     for (int k = 0; k < kRowStages; ++k)
       if (first + k * stride < rows) ring.issue(k, x + (first + k * stride) * 2 * half);
   const int nquad = half >> 2;
+  int g = 0;       // group of the current row: rows only move forward, so the cursor does too
   int k = 0;
   for (int64_t row = first; row < rows; row += stride, ++k) {
-    if (!__syncthreads_and(ring.wait(k) ? 1 : 0)) {
-      if (threadIdx.x == 0) atomicCAS(&g_quant_status, 0, 1);
-      break;
-    }
+    ring_wait_or_flag(ring, k, &s_fail);
     int32_t* sr = reinterpret_cast<int32_t*>(ring_mem + ring.stage_offset(k));
-    const int g = group_index != nullptr ? group_of_row(s_end, num_groups, row) : 0;   // uniform over the CTA
-    int8_t* yr = y + row * half;
-    if (g < 0) {  // row outside every group
-      for (int q = threadIdx.x; q < nquad; q += kRowThreads) *reinterpret_cast<uint32_t*>(yr + q * 4) = 0u;
-      if (threadIdx.x == 0) scale[row] = 0.f;
-    } else {
-      const float as = ascale ? ascale[row] : 1.0f;
-      const float* ws = kHasWs ? wscale + (ws_groups > 1 ? static_cast<int64_t>(g) * 2 * half : 0) : nullptr;
-      float amax = 0.f;
-#pragma unroll 2
-      for (int q = threadIdx.x; q < nquad; q += kRowThreads) {
+    if (group_index != nullptr)
+      while (g < num_groups && s_end[g] <= row) ++g;
+    const bool covered = group_index == nullptr || g < num_groups;      // uniform over the CTA
+    const float as = (covered && ascale) ? ascale[row] : 1.0f;
+    const float* ws = (kHasWs && covered) ? wscale + (ws_groups > 1 ? static_cast<int64_t>(g) * 2 * half : 0) : nullptr;
+    float amax = 0.f;
+    float keep[kQuads > 0 ? kQuads : 1][4];     // kQuads > 0: the thread's SwiGLU values stay in registers between the passes
+    if (covered) {
+#pragma unroll
+      for (int it = 0; it < (kQuads > 0 ? kQuads : (nquad + kRowThreads - 1) / kRowThreads); ++it) {
+        const int q = threadIdx.x + it * kRowThreads;
+        if (kQuads == 0 && q >= nquad) break;
         const int4 l = *reinterpret_cast<const int4*>(sr + q * 4);
         const int4 r = *reinterpret_cast<const int4*>(sr + half + q * 4);
         float lv[4] = {__fmul_rn(__int2float_rn(l.x), as), __fmul_rn(__int2float_rn(l.y), as), __fmul_rn(__int2float_rn(l.z), as),
@@ -159,45 +197,74 @@ __global__ void __launch_bounds__(kRowThreads) dequant_swiglu_quant_staged_kerne
           h[i] = kLeft ? silu_mul(lv[i], rv[i]) : silu_mul(rv[i], lv[i]);
           amax = fmaxf(amax, fabsf(h[i]));
         }
-        *reinterpret_cast<float4*>(sr + q * 4) = make_float4(h[0], h[1], h[2], h[3]);     // in place over the gate quadruple
-      }
-      amax = cta_max<kRowThreads>(amax, red);
-      const RowQuant sc = make_row_quant(amax);
-      if (threadIdx.x == 0) scale[row] = sc.scale;
-      const float* hr = reinterpret_cast<const float*>(sr);
-      if (sc.scale > 0.f && !sc.exact) {
-        const float inv = sc.inv, scl = sc.scale;
-#pragma unroll 2
-        for (int q = threadIdx.x; q < nquad; q += kRowThreads) {          // every thread re-reads the quadruples it wrote
-          const float4 a = *reinterpret_cast<const float4*>(hr + q * 4);
-          const float v[4] = {a.x, a.y, a.z, a.w};
-          uint32_t w[4];
+        if constexpr (kQuads > 0) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float q0 = __fmul_rn(v[i], inv);
-            const float r = __fmaf_rn(-q0, scl, v[i]);
-            w[i] = __float_as_uint(__fadd_rn(__fmaf_rn(r, inv, q0), kRoundMagic));
-          }
-          __stcs(reinterpret_cast<uint32_t*>(yr + q * 4), pack4_words(w[0], w[1], w[2], w[3]));
-        }
-      } else {
-        for (int q = threadIdx.x; q < nquad; q += kRowThreads) {
-          const float4 a = *reinterpret_cast<const float4*>(hr + q * 4);
-          const float v[4] = {a.x, a.y, a.z, a.w};
-          __stcs(reinterpret_cast<uint32_t*>(yr + q * 4), quant4(v, sc));
+          for (int i = 0; i < 4; ++i) keep[it][i] = h[i];
+        } else {
+          *reinterpret_cast<float4*>(sr + q * 4) = make_float4(h[0], h[1], h[2], h[3]);   // in place over the gate quadruple
         }
       }
     }
-    __syncthreads();
-    if (threadIdx.x == 0 && row + kRowStages * stride < rows)
-      ring.issue(k + kRowStages, x + (row + kRowStages * stride) * 2 * half);
+    amax = cta_max_once(amax, red[k & 1]);
+    if (threadIdx.x == 0 && k >= 1 && row + (kRowStages - 1) * stride < rows)
+      ring.issue(k - 1 + kRowStages, x + (row + (kRowStages - 1) * stride) * 2 * half);
+    int8_t* yr = y + row * half;
+    if (!covered) {  // row outside every group
+      for (int q = threadIdx.x; q < nquad; q += kRowThreads) *reinterpret_cast<uint32_t*>(yr + q * 4) = 0u;
+      if (threadIdx.x == 0) scale[row] = 0.f;
+      continue;
+    }
+    const RowQuant sc = make_row_quant_fast(amax);
+    if (threadIdx.x == 0) scale[row] = sc.scale;
+    const float* hr = reinterpret_cast<const float*>(sr);
+    if (sc.scale > 0.f && !sc.exact) {
+      const float inv = sc.inv, scl = sc.scale;
+#pragma unroll
+      for (int it = 0; it < (kQuads > 0 ? kQuads : (nquad + kRowThreads - 1) / kRowThreads); ++it) {
+        const int q = threadIdx.x + it * kRowThreads;
+        if (kQuads == 0 && q >= nquad) break;
+        float v[4];
+        if constexpr (kQuads > 0) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) v[i] = keep[it][i];
+        } else {
+          const float4 a = *reinterpret_cast<const float4*>(hr + q * 4);
+          v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+        }
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float q0 = __fmul_rn(v[i], inv);
+          const float r = __fmaf_rn(-q0, scl, v[i]);
+          w[i] = __float_as_uint(__fadd_rn(__fmaf_rn(r, inv, q0), kRoundMagic));
+        }
+        __stcs(reinterpret_cast<uint32_t*>(yr + q * 4), pack4_words(w[0], w[1], w[2], w[3]));
+      }
+    } else {
+      for (int it = 0; it * kRowThreads + static_cast<int>(threadIdx.x) < nquad; ++it) {
+        const int q = threadIdx.x + it * kRowThreads;
+        float v[4];
+        if constexpr (kQuads > 0) {
+#pragma unroll
+          for (int j = 0; j < kQuads; ++j)
+            if (j == it) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) v[i] = keep[j][i];
+            }
+        } else {
+          const float4 a = *reinterpret_cast<const float4*>(hr + q * 4);
+          v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+        }
+        __stcs(reinterpret_cast<uint32_t*>(yr + q * 4), quant4(v, sc));
+      }
+    }
   }
 }
 
 // Persistent grid and ring size for a staged row kernel, or 0 when the rows do not suit it (tiny or too long for three
 // stages): CTAs per SM by the shared-memory budget, at most 8.
 static int staged_grid(int64_t rows, size_t row_bytes, size_t* smem_bytes) {
-  if (row_bytes < 1024 || row_bytes % 16 != 0 || row_bytes * kRowStages > 100 * 1024) return 0;
+  if (row_bytes < 1024 || row_bytes % 16 != 0 || row_bytes * kRowStages > 192 * 1024) return 0;
   *smem_bytes = row_bytes * kRowStages;
   size_t per_sm = kRowSmemBudget / (*smem_bytes + 1024);
   if (per_sm > 8) per_sm = 8;
@@ -445,9 +512,14 @@ static void launch_dynamic_quant(const void* x, const void* smooth, int64_t rows
   const T* sp = static_cast<const T*>(smooth);
   size_t smem = 0;
   const int sgrid = rows >= 64 ? staged_grid(rows, static_cast<size_t>(cols) * sizeof(T), &smem) : 0;
-  if (sgrid > 0 &&
-      cudaFuncSetAttribute(dynamic_quant_staged_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) == cudaSuccess) {
-    dynamic_quant_staged_kernel<T><<<sgrid, kRowThreads, smem, st>>>(xp, sp, rows, cols, y, scale);
+  if (sgrid > 0 && sp == nullptr &&
+      cudaFuncSetAttribute(dynamic_quant_staged_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) == cudaSuccess) {
+    dynamic_quant_staged_kernel<T, false><<<sgrid, kRowThreads, smem, st>>>(xp, sp, rows, cols, y, scale);
+    return;
+  }
+  if (sgrid > 0 && sp != nullptr &&
+      cudaFuncSetAttribute(dynamic_quant_staged_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) == cudaSuccess) {
+    dynamic_quant_staged_kernel<T, true><<<sgrid, kRowThreads, smem, st>>>(xp, sp, rows, cols, y, scale);
     return;
   }
   if (nchunk <= 64 * kMaxChunks / 2)
@@ -527,18 +599,23 @@ extern "C" int tab_dequant_swiglu_quant(const int32_t* x, const float* weight_sc
   ring_bytes += static_cast<size_t>(num_groups) * sizeof(int);
   if (ring_bytes > 200 * 1024) sgrid = 0;
   if (sgrid > 0) {
-#define TAB_DSQ(L, W)                                                                                                            \
-  if (cudaFuncSetAttribute(dequant_swiglu_quant_staged_kernel<L, W>, cudaFuncAttributeMaxDynamicSharedMemorySize,               \
+#define TAB_DSQ(L, W, Q)                                                                                                         \
+  if (cudaFuncSetAttribute(dequant_swiglu_quant_staged_kernel<L, W, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize,            \
                            static_cast<int>(ring_bytes)) == cudaSuccess) {                                                      \
-    dequant_swiglu_quant_staged_kernel<L, W><<<sgrid, kRowThreads, ring_bytes, st>>>(x, weight_scale, (int)ws_groups, activation_scale, \
-                                                                                    group_index, (int)num_groups, rows, (int)half, y, scale); \
+    dequant_swiglu_quant_staged_kernel<L, W, Q><<<sgrid, kRowThreads, ring_bytes, st>>>(x, weight_scale, (int)ws_groups, activation_scale, \
+                                                                                       group_index, (int)num_groups, rows, (int)half, y, scale); \
     return check_launch("dequant_swiglu_quant");                                                                               \
   }
+#define TAB_DSQ_Q(L, W)                                                       \
+  if (half == 2 * 4 * kRowThreads) { TAB_DSQ(L, W, 2) }                        \
+  else if (half == 4 * kRowThreads) { TAB_DSQ(L, W, 1) }                       \
+  else { TAB_DSQ(L, W, 0) }
     if (activate_left) {
-      if (weight_scale) { TAB_DSQ(true, true) } else { TAB_DSQ(true, false) }
+      if (weight_scale) { TAB_DSQ_Q(true, true) } else { TAB_DSQ_Q(true, false) }
     } else {
-      if (weight_scale) { TAB_DSQ(false, true) } else { TAB_DSQ(false, false) }
+      if (weight_scale) { TAB_DSQ_Q(false, true) } else { TAB_DSQ_Q(false, false) }
     }
+#undef TAB_DSQ_Q
 #undef TAB_DSQ
   }
   const size_t smem = group_index ? static_cast<size_t>(num_groups) * sizeof(int) : 0;
@@ -560,12 +637,15 @@ extern "C" int tab_quant_status(int* status_host, tab_stream_t stream) {
   return TAB_OK;
 }
 
-// Exhaustive self-test of rcp_rn_normal against the library's IEEE reciprocal: all 2^23 significands at one exponent.
+// Exhaustive self-test of rcp_rn_normal and of make_row_quant_fast against the library's IEEE reciprocal and division:
+// all 2^23 significands at one exponent.
 namespace tab {
 __global__ void __launch_bounds__(256) selftest_reciprocal_kernel(int exponent, unsigned long long* mismatches) {
   const unsigned m = blockIdx.x * 256u + threadIdx.x;
   const float d = __uint_as_float((static_cast<unsigned>(127 + exponent) << 23) | m);
   if (rcp_rn_normal(d) != __frcp_rn(d)) atomicAdd(mismatches, 1ull);
+  const RowQuant fast = make_row_quant_fast(d), lib = make_row_quant(d);        // d as a row maximum: amax / 127 and its reciprocal
+  if (fast.scale != lib.scale || fast.inv != lib.inv) atomicAdd(mismatches, 1ull);
 }
 }  // namespace tab
 

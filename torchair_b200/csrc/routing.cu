@@ -4,6 +4,7 @@
 // npu_moe_distribute_combine.  Integer/byte movers: HBM-bound, 16-byte accesses, grids sized to the SMs.
 #include <mutex>
 
+#include "row_pipe.cuh"
 #include "tab_common.cuh"
 
 namespace tab {
@@ -47,7 +48,8 @@ __device__ int block_exclusive_scan(int* vals, int n, int* warp_sums) {
 }
 
 // Status word of the routing kernels on this device (tab_routing_status reads and clears it):
-// bit 0 = an expert id outside [0, bound) was clamped, bit 1 = a row_idx value outside [0, T*K) was skipped.
+// bit 0 = an expert id outside [0, bound) was clamped, bit 1 = a row_idx value outside [0, T*K) was skipped,
+// bit 2 = a bounded wait for a bulk copy gave up.
 __device__ int g_routing_status = 0;
 
 __device__ __forceinline__ int clamp_expert(int key, int nb) {
@@ -201,6 +203,55 @@ __global__ void __launch_bounds__(kRowCopyThreads) gather_rows_kernel(const uint
     if (i + gridDim.x < rows) next = idx[i + gridDim.x];   // fetched while this row is being copied
     copy_row16<kRowCopyThreads>(dst + i * vec_per_row, src + s * vec_per_row, vec_per_row);
   }
+}
+
+// Token-major form of the same gather for rows of 512 B .. 48 KB, moved entirely by the copy engine of the SM: a
+// one-warp CTA streams its tokens' rows into a ring of shared-memory stages with bulk loads and sends every staged
+// row to the K sorted positions of its copies with bulk stores (no register traffic, 16 KB per instruction).  The K
+// copies of token t are the pairs whose row_idx value is t + j*T (value % T == t); inverse[value] is their position;
+// positions at or past out_rows are dropped (active_num).
+constexpr int kBulkStages = 4;
+__global__ void __launch_bounds__(32) scatter_rows_bulk_kernel(const uint8_t* __restrict__ x, const int32_t* __restrict__ inverse,
+                                                               int64_t tokens, int K, int64_t out_rows, uint32_t row_bytes,
+                                                               uint8_t* __restrict__ dst) {
+  extern __shared__ __align__(128) uint8_t ring_mem[];
+  __shared__ uint64_t bars[kBulkStages];
+  RowRing<kBulkStages> ring(ring_mem, bars, row_bytes, row_bytes);
+  __syncwarp();
+  const int lane = threadIdx.x;
+  const int64_t first = blockIdx.x, stride = gridDim.x;
+  if (lane == 0)
+    for (int k = 0; k < kBulkStages; ++k)
+      if (first + k * stride < tokens) ring.issue(k, x + (first + k * stride) * row_bytes);
+  int k = 0;
+  for (int64_t t = first; t < tokens; t += stride, ++k) {
+    bool ok = true;
+    for (int j0 = 0; j0 < K && ok; j0 += 32) {
+      const int j = j0 + lane;
+      const int pos = j < K ? inverse[t + static_cast<int64_t>(j) * tokens] : -1;   // in flight while the row lands
+      if (j0 == 0) ok = __all_sync(0xffffffffu, ring.wait(k) ? 1 : 0) != 0;
+      if (!ok) break;
+      const int n = min(32, K - j0);
+      for (int jj = 0; jj < n; ++jj) {      // lane 0 issues the stores; the positions come from the lanes that loaded them
+        const int p = __shfl_sync(0xffffffffu, pos, jj);
+        if (lane == 0 && p >= 0 && p < out_rows)
+          asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                       ::"l"(dst + static_cast<int64_t>(p) * row_bytes), "r"(ring.base + ring.stage_offset(k)), "r"(row_bytes) : "memory");
+      }
+    }
+    if (!ok) {                               // a row that never landed: report and stop (nothing was stored from its stage)
+      if (lane == 0) atomicOr(&g_routing_status, 4);
+      break;
+    }
+    if (lane == 0) {
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      // once the stores of the previous token have read their stage, it takes the row kBulkStages - 1 tokens ahead
+      asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+      if (k >= 1 && t + (kBulkStages - 1) * stride < tokens)
+        ring.issue(k - 1 + kBulkStages, x + (t + (kBulkStages - 1) * stride) * row_bytes);
+    }
+  }
+  if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
 
 // Sender side of dispatch: one CTA per token; quantise the row once (or copy it), then write the K copies
@@ -532,8 +583,20 @@ extern "C" int tab_moe_init_routing(const void* x, int x_dtype, const int32_t* r
   if (rc != TAB_OK) return rc;
   const int64_t out_rows = (T < active_num ? T : active_num) * K;
   if (out_rows > 0) {
-    gather_rows_kernel<<<grid_for(out_rows, 16), kRowCopyThreads, 0, st>>>(static_cast<const uint4*>(x), s.sorted_src, (int)T, out_rows,
-                                                              (int)(H * es / 16), static_cast<uint4*>(expanded_x));
+    const int64_t row_bytes = H * es;
+    const size_t ring_bytes = static_cast<size_t>(row_bytes) * kBulkStages;
+    if (row_bytes >= 512 && ring_bytes <= 192 * 1024 && T >= 32 &&
+        cudaFuncSetAttribute(scatter_rows_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(ring_bytes)) == cudaSuccess) {
+      size_t per_sm = (200 * 1024) / (ring_bytes + 1024);
+      if (per_sm > 8) per_sm = 8;
+      if (per_sm < 1) per_sm = 1;
+      scatter_rows_bulk_kernel<<<grid_for(T, static_cast<int>(per_sm)), 32, ring_bytes, st>>>(
+          static_cast<const uint8_t*>(x), expanded_row_idx, T, (int)K, out_rows, static_cast<uint32_t>(row_bytes),
+          static_cast<uint8_t*>(expanded_x));
+    } else {
+      gather_rows_kernel<<<grid_for(out_rows, 16), kRowCopyThreads, 0, st>>>(static_cast<const uint4*>(x), s.sorted_src, (int)T, out_rows,
+                                                                (int)(H * es / 16), static_cast<uint4*>(expanded_x));
+    }
     rc = check_launch("init_routing gather");
   }
   return rc;

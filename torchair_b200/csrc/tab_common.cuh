@@ -123,7 +123,7 @@ __device__ __forceinline__ uint32_t pack4_i8(int a, int b, int c, int d) {
 // FMAs instead of the library's checked sequence with its out-of-line slow path.
 __device__ __forceinline__ float rcp_rn_normal(float d) {
   float y;
-  asm("rcp.approx.f32 %0, %1;" : "=f"(y) : "f"(d));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(d));   // d and 1/d are normal: the flush-to-zero form is the bare seed instruction
   return __fmaf_rn(__fmaf_rn(-d, y, 1.0f), y, y);
 }
 
