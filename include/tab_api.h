@@ -147,8 +147,30 @@ TAB_API int tab_moe_init_routing_static(const void* x, int x_dtype, const int32_
  *   expert_counts int32 [num_experts] (copies per global expert); expert_token_nums int64 [num_experts] (NULL to
  *   skip) = the same counts (nums_type 1) or their running total (0), the form the grouped GEMM's group_list takes.
  * With one rank this is the whole dispatch: send_rows is expand_x and expert_token_nums the operator's output.
+ *
+ * tab_moe_dispatch_pack_ex adds the optional arguments of the operators built on this step (decisions where the
+ * reference gives a name only):
+ *   expert_lo, expert_hi  experts [lo, hi) are kept and numbered from 0 (num_experts = hi - lo in every output).  An id
+ *                         outside the range is dropped when drop_outside != 0 (active_expert_range of
+ *                         npu_moe_init_routing_v2, npu_moe_init_routing_v2.py:55,81; ids >= moe_expert_num of the
+ *                         second-generation dispatch name special experts that are not sent,
+ *                         moe_distribute_dispatch_v2.py:15-18), else clamped into the range and reported.
+ *   x_active_mask         bytes [T] or NULL (moe_distribute_dispatch.py:14,31): tokens whose byte is 0 send nothing.
+ *   smooth                fp32 [smooth_rows, H] or NULL (`scales` of dispatch, `scale` of init_routing_v2 with dynamic
+ *                         quantisation): copy (t, k) is quantised after the fp32 product x[t] * smooth[expert - lo]
+ *                         (smooth_rows == num_experts) or x[t] * smooth[0] (smooth_rows == 1), each copy with its own
+ *                         scale.  quant_mode 2 only.
+ *   passthrough_scale     fp32 [T] or NULL, quant_mode 0 only: send_scales of a copy = the value of its token.
+ *   pos_limit             > 0: copies at sorted positions >= pos_limit get no row (active_num); 0 = no limit.
+ * Dropped pairs get expand_idx = -1 and no row; they are not counted.
  * ------------------------------------------------------------------------------------------------- */
 TAB_API int tab_moe_dispatch_pack_workspace_bytes(int64_t T, int64_t K, int64_t num_experts, size_t* bytes);
+TAB_API int tab_moe_dispatch_pack_ex(const void* x, int x_dtype, const int32_t* expert_ids, int64_t T, int64_t K, int64_t H,
+                             int64_t expert_lo, int64_t expert_hi, int drop_outside, const uint8_t* x_active_mask,
+                             const float* smooth, int64_t smooth_rows, const float* passthrough_scale,
+                             int64_t pos_limit, int quant_mode, void* send_rows, float* send_scales,
+                             int32_t* expand_idx, int32_t* expert_counts, int64_t* expert_token_nums, int nums_type,
+                             void* workspace, size_t workspace_bytes, tab_stream_t stream);
 TAB_API int tab_moe_dispatch_pack(const void* x, int x_dtype, const int32_t* expert_ids, int64_t T, int64_t K,
                           int64_t H, int64_t num_experts, int quant_mode, void* send_rows,
                           float* send_scales, int32_t* expand_idx, int32_t* expert_counts,
@@ -256,6 +278,19 @@ TAB_API int tab_ep_return_plan_fused(const int32_t* ep_send_counts, int64_t R, i
  * ------------------------------------------------------------------------------------------------- */
 TAB_API int tab_moe_combine(const void* rows, int dtype, const int32_t* expand_idx, const float* expert_scales,
                     const void* shared, int64_t T, int64_t K, int64_t H, void* out, tab_stream_t stream);
+/* tab_moe_combine_ex: the same with the optional inputs (decisions where the converters give names only):
+ *   x_active_mask bytes [T] or NULL (moe_distribute_combine.py:17): a 0 byte gives an all-zero output row;
+ *   a negative expand_idx entry (a pair that was not dispatched) contributes 0;
+ *   special experts of the second-generation operator (moe_distribute_combine_v2.py:17-20,47-50): a pair whose
+ *   expert_ids entry (int32 [T, K]) is num_experts + s stands for a row formed here -- s < zero_expert_num: 0; the next
+ *   copy_expert_num: the token itself, ori_x [T, H]; the next const_expert_num (index c): const_expert_alpha_1[c] *
+ *   ori_x[t] + const_expert_alpha_2[c] * const_expert_v[c] ([const_expert_num, H] each, of `dtype`), two fp32 products
+ *   and one fp32 sum per element -- which then enters the weighted sum like a gathered row. */
+TAB_API int tab_moe_combine_ex(const void* rows, int dtype, const int32_t* expand_idx, const float* expert_scales,
+                       const void* shared, int64_t T, int64_t K, int64_t H, void* out, const uint8_t* x_active_mask,
+                       const int32_t* expert_ids, int64_t num_experts, int64_t zero_expert_num, int64_t copy_expert_num,
+                       int64_t const_expert_num, const void* ori_x, const void* const_expert_alpha_1,
+                       const void* const_expert_alpha_2, const void* const_expert_v, tab_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------
  * Operators next to the path.
@@ -264,9 +299,13 @@ TAB_API int tab_moe_combine(const void* rows, int dtype, const int32_t* expand_i
  *   sorted_experts int32 [n] ascending; out int32 [num_experts], out[e] = number of entries <= e.
  *
  * npu_moe_gating_top_k_softmax (converter moe_gating_top_k_softmax.py:9-19 -> MoeGatingTopKSoftmax,
- *   experiment_ops.h:2222-2241), `finished` absent: softmax over the experts in fp32, then the k largest
+ *   experiment_ops.h:2222-2241): softmax over the experts in fp32, then the k largest
  *   (ties: lower expert id).  x [tokens, num_experts] of dtype 5, 6 or 15 (num_experts <= 1024);
  *   y [tokens, k] same dtype; expert_idx, row_idx int32 [tokens, k], row_idx[t, j] = j*tokens + t.
+ *   finished: bytes [tokens] or NULL (moe_gating_top_k_softmax.py:10-19); decision: a row whose byte is non-zero
+ *   reports expert_idx = num_experts in every slot (an id past the experts, which the routing ops drop or clamp),
+ *   y and row_idx as for any other row.  The same argument of tab_moe_gating_top_k serves
+ *   npu_moe_gating_top_k_softmax_v2.
  *
  * npu_moe_finalize_routing (converter npu_moe_finalize_routing.py:21-41 -> MoeFinalizeRouting(V2)), drop_pad_mode 0:
  *   out[t] = sum_k scales[t,k] * (rows[src_to_dst[k*T + t]] + bias[expert_for_row[t,k]]) + skip1[t] + skip2[t];
@@ -275,15 +314,21 @@ TAB_API int tab_moe_combine(const void* rows, int dtype, const int32_t* expand_i
  *
  * npu_moe_init_routing_v2 (converter npu_moe_init_routing_v2.py:41-95 -> MoeInitRoutingV3, experiment_ops.h:2137-2192),
  *   dropless: stable sort of the T*K pairs (flattened index f = t*K + k) by expert id, rows copied (quant_mode -1)
- *   or quantised per token to int8 (quant_mode 1).  expanded_x [T*K, H]; expanded_row_idx int32 [T*K]
- *   (row_idx_type 0: sorted position -> f, 1: f -> sorted position); expert_tokens int64 [expert_num] counts
- *   (tokens_num_type 1) or cumulative sums (0); expanded_scale fp32 [T*K] (zero when not quantising).
+ *   or quantised to int8 (quant_mode 1).  Experts [expert_lo, expert_hi) are kept (active_expert_range; expert_num
+ *   below = expert_hi - expert_lo); pairs of other experts get no row and sort behind the kept ones.
+ *   expanded_x [T*K, H], of which only rows at positions < active_rows are written when active_rows > 0 (active_num);
+ *   expanded_row_idx int32 [T*K] (row_idx_type 0: sorted position -> f; 1: f -> sorted position, -1 for a pair that
+ *   was not kept); expert_tokens int64 [expert_num] counts (tokens_num_type 1) or cumulative sums (0);
+ *   expanded_scale fp32 [T*K].  scale: quant_mode -1: fp32 [T] (scale_rows == T), copied to expanded_scale of the
+ *   token's copies (zero when NULL); quant_mode 1: fp32 smooth scales [expert_num, H] or [1, H] (scale_rows) applied
+ *   before the per-copy quantisation, or NULL (one quantisation per token).
  *   Workspace: tab_moe_dispatch_pack_workspace_bytes(T, K, expert_num) + 4*(T*K + expert_num) + 1024 bytes.
  * ------------------------------------------------------------------------------------------------- */
 TAB_API int tab_moe_compute_expert_tokens(const int32_t* sorted_experts, int64_t n, int64_t num_experts, int32_t* out,
                                   tab_stream_t stream);
-TAB_API int tab_moe_gating_top_k_softmax(const void* x, int dtype, int64_t tokens, int64_t num_experts, int64_t k, void* y,
-                                 int32_t* expert_idx, int32_t* row_idx, tab_stream_t stream);
+TAB_API int tab_moe_gating_top_k_softmax(const void* x, int dtype, const uint8_t* finished, int64_t tokens,
+                                 int64_t num_experts, int64_t k, void* y, int32_t* expert_idx, int32_t* row_idx,
+                                 tab_stream_t stream);
  /* npu_moe_gating_top_k (converter npu_moe_gating_top_k.py:4-22 -> MoeGatingTopK, experiment_ops.h:3722-3761):
   * scores = softmax(x) (norm_type 0 and 2) or sigmoid(x) (1) in fp32; selection score = scores + bias; with group_count > 1 the
   * experts form contiguous groups, each scored by its maximum (group_select_mode 0) or by the sum of its two largest
@@ -293,7 +338,8 @@ TAB_API int tab_moe_gating_top_k_softmax(const void* x, int dtype, int64_t token
   * num_experts <= 1024, k <= 32, group_count <= 32.  norm_type 2 with no bias and one group is
  * npu_moe_gating_top_k_softmax_v2 with renorm = 1 (converter npu_moe_gating_top_k_softmax_v2.py:9-23 ->
  * MoeGatingTopKSoftmaxV2, experiment_ops.h:2243-2265); norm_type 0 is its renorm = 0, `out` its softmax_result. */
-TAB_API int tab_moe_gating_top_k(const void* x, const void* bias, int dtype, int64_t tokens, int64_t num_experts, int64_t k,
+TAB_API int tab_moe_gating_top_k(const void* x, const void* bias, const uint8_t* finished, int dtype, int64_t tokens,
+                         int64_t num_experts, int64_t k,
                          int64_t k_group, int64_t group_count, int group_select_mode, int norm_type,
                          float routed_scaling_factor, float eps, void* y, int32_t* expert_idx, float* out,
                          tab_stream_t stream);
@@ -301,7 +347,8 @@ TAB_API int tab_moe_finalize_routing(const void* rows, int dtype, const void* sk
                              const float* scales, const int32_t* src_to_dst, const int32_t* expert_for_row, int64_t T,
                              int64_t K, int64_t H, void* out, tab_stream_t stream);
 TAB_API int tab_moe_init_routing_v2(const void* x, int x_dtype, const int32_t* expert_idx, int64_t T, int64_t K, int64_t H,
-                            int64_t expert_num, int quant_mode, int tokens_num_type, int row_idx_type, void* expanded_x,
+                            int64_t expert_lo, int64_t expert_hi, int quant_mode, int tokens_num_type, int row_idx_type,
+                            int64_t active_rows, const float* scale, int64_t scale_rows, void* expanded_x,
                             int32_t* expanded_row_idx, int64_t* expert_tokens, float* expanded_scale, void* workspace,
                             size_t workspace_bytes, tab_stream_t stream);
 
@@ -316,6 +363,7 @@ TAB_API int tab_moe_init_routing_v2(const void* x, int x_dtype, const int32_t* e
  *
  * tab_grouped_matmul_w8a8: x int8 [M, Kd]; packed weight; group_list int64 [E] (group_list_type 0 =
  *   cumulative row ends, 1 = row counts); expert e owns a contiguous row range.
+ *   bias int32 [E, N] or NULL (the int8 mode's bias, grouped_matmul.py:258-262): acc += bias[e, n] in int32.
  *   out_dtype 3: y int32 [M, N] raw accumulators (scale, per_token_scale ignored);
  *   out_dtype 15 / 5: y = (float(acc) * per_token_scale[m]) * scale[e, n], scale fp32 [E, N],
  *   per_token_scale fp32 [M] (either may be NULL = 1).  Rows outside every group are left untouched.
@@ -360,7 +408,7 @@ TAB_API int tab_moe_init_routing_v2(const void* x, int x_dtype, const int32_t* e
 TAB_API int tab_prepack_weight_i8(const int8_t* weight, int64_t E, int64_t Kd, int64_t N, int8_t* packed,
                           tab_stream_t stream);
 TAB_API int tab_grouped_matmul_w8a8(const int8_t* x, const int8_t* packed_weight, const float* scale,
-                            const float* per_token_scale, const int64_t* group_list, int group_list_type,
+                            const float* per_token_scale, const int32_t* bias, const int64_t* group_list, int group_list_type,
                             int64_t M, int64_t Kd, int64_t N, int64_t E, int out_dtype, void* y,
                             int64_t expected_rows_per_group, tab_stream_t stream);
 TAB_API int tab_grouped_matmul_w8a8_scatter(const int8_t* x, const int8_t* packed_weight, const float* scale,

@@ -11,22 +11,34 @@ from . import moe_oracle as O
 
 class OracleKernels:
     @staticmethod
-    def dispatch_pack(x, expert_ids, E, quant_mode, nums_type=None):
+    def dispatch_pack(x, expert_ids, E, quant_mode, nums_type=None, mask=None, scales=None, special=0):
         T, K = expert_ids.shape
-        if quant_mode == 2:
-            q, s = O.dynamic_quant(x)
-        else:
-            q, s = x, torch.zeros(T, dtype=torch.float32)
         flat = expert_ids.reshape(-1).to(torch.int64)
-        order = torch.sort(flat, stable=True)
-        tok = order.indices // K
-        expand_idx = torch.empty(T * K, dtype=torch.int32)
-        expand_idx[order.indices] = torch.arange(T * K, dtype=torch.int32)
-        counts = torch.bincount(flat, minlength=E).to(torch.int32)
+        keep = flat < E if special > 0 else torch.ones_like(flat, dtype=torch.bool)
+        if mask is not None:
+            keep = keep & mask.to(torch.bool).repeat_interleave(K)
+        keys = torch.where(keep, flat.clamp(0, E - 1), torch.full_like(flat, E))
+        order = torch.sort(keys, stable=True)
+        kept = int(keep.sum())
+        tok = (order.indices // K)[:kept]
+        rows = torch.zeros(T * K, x.shape[1], dtype=torch.int8 if quant_mode == 2 else x.dtype)
+        out_scales = torch.zeros(T * K, dtype=torch.float32)
+        if quant_mode == 2 and scales is not None:
+            sm = scales.float()
+            srow = sm[order.values[:kept]] if sm.shape[0] > 1 else sm[:1].expand(kept, -1)
+            rows[:kept], out_scales[:kept] = O.quantize_rows_f32(x[tok].float() * srow)
+        elif quant_mode == 2:
+            q, s = O.dynamic_quant(x)
+            rows[:kept], out_scales[:kept] = q[tok], s[tok]
+        else:
+            rows[:kept] = x[tok]
+        expand_idx = torch.full((T * K,), -1, dtype=torch.int32)
+        expand_idx[order.indices[:kept]] = torch.arange(kept, dtype=torch.int32)
+        counts = torch.bincount(keys, minlength=E + 1)[:E].to(torch.int32)
         nums = None
         if nums_type is not None:
             nums = counts.to(torch.int64) if nums_type == 1 else torch.cumsum(counts.to(torch.int64), 0)
-        return q[tok].contiguous(), s[tok].contiguous(), expand_idx, counts, nums
+        return rows, out_scales, expand_idx, counts, nums
 
     @staticmethod
     def exchange_plan(recv_counts, R, E_l, slot_rows, nums_type):
@@ -74,5 +86,14 @@ class OracleKernels:
         return dst, dsc
 
     @staticmethod
-    def combine(rows, expand_idx, expert_scales, shared, T, K):
-        return O.weighted_gather_sum(rows, expand_idx.reshape(T, K), expert_scales, shared)
+    def combine(rows, expand_idx, expert_scales, shared, T, K, mask=None, special=None):
+        if mask is None and special is None:
+            return O.weighted_gather_sum(rows, expand_idx.reshape(T, K), expert_scales, shared)
+        sp = None
+        ids = torch.zeros(T, K, dtype=torch.int32)
+        E = 1 << 30
+        if special is not None:
+            ids, E = special["expert_ids"], special["E"]
+            sp = {"ori_x": special.get("ori_x"), "zero": special.get("zero", 0), "copy": special.get("copy", 0),
+                  "alpha_1": special.get("alpha_1"), "alpha_2": special.get("alpha_2"), "const_v": special.get("const_v")}
+        return O.combine_rows(rows, expand_idx.reshape(T, K), expert_scales, ids, E, shared, mask, sp)

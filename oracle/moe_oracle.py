@@ -398,18 +398,23 @@ def moe_compute_expert_tokens(sorted_experts: torch.Tensor, num_experts: int) ->
     return torch.cumsum(torch.bincount(sorted_experts.long().clamp(min=0), minlength=num_experts)[:num_experts], 0).to(torch.int32)
 
 
-def moe_gating_top_k_softmax(x: torch.Tensor, k: int):
-    """MoeGatingTopKSoftmax without `finished` (converter moe_gating_top_k_softmax.py:9-19; experiment_ops.h:2222-2241):
+def moe_gating_top_k_softmax(x: torch.Tensor, k: int, finished: Optional[torch.Tensor] = None):
+    """MoeGatingTopKSoftmax (converter moe_gating_top_k_softmax.py:9-19; experiment_ops.h:2222-2241):
     y = k largest softmax probabilities (in x's dtype), expert_idx int32, row_idx[t, j] = j*T + t.
-    Decision: ties keep the lower expert id."""
-    T = x.shape[0]
+    Decisions: ties keep the lower expert id; a row whose `finished` flag is set reports expert_idx = number of experts
+    (an id past the last expert) in every slot, its y and row_idx as usual."""
+    T, E = x.shape
     p = torch.softmax(x.float(), dim=-1)
     order = torch.sort(p, dim=-1, descending=True, stable=True)
     row_idx = (torch.arange(k, dtype=torch.int32).view(1, k) * T + torch.arange(T, dtype=torch.int32).view(T, 1))
-    return order.values[:, :k].to(x.dtype), order.indices[:, :k].to(torch.int32), row_idx.contiguous()
+    idx = order.indices[:, :k].to(torch.int32)
+    if finished is not None:
+        idx = torch.where(finished.to(torch.bool).view(T, 1), torch.full_like(idx, E), idx)
+    return order.values[:, :k].to(x.dtype), idx, row_idx.contiguous()
 
 
-def moe_gating_top_k_softmax_v2(x: torch.Tensor, k: int, renorm: int = 0, output_softmax: bool = False):
+def moe_gating_top_k_softmax_v2(x: torch.Tensor, k: int, renorm: int = 0, output_softmax: bool = False,
+                                finished: Optional[torch.Tensor] = None):
     """MoeGatingTopKSoftmaxV2 without `finished` (converter npu_moe_gating_top_k_softmax_v2.py:9-23;
     experiment_ops.h:2243-2265).  Decisions: renorm 0 -> y = the k largest softmax probabilities, softmax_result = the
     fp32 softmax over all experts when asked for; renorm 1 -> the same k probabilities divided by their sum taken in
@@ -423,7 +428,10 @@ def moe_gating_top_k_softmax_v2(x: torch.Tensor, k: int, renorm: int = 0, output
             ysum = ysum + y[:, j]
         y = y / ysum.unsqueeze(-1)
     full = p if (output_softmax and not renorm) else torch.empty(0, dtype=torch.float32)
-    return y.to(x.dtype), order.indices[:, :k].to(torch.int32), full
+    idx = order.indices[:, :k].to(torch.int32)
+    if finished is not None:     # decision as in moe_gating_top_k_softmax: finished rows point past the experts
+        idx = torch.where(finished.to(torch.bool).view(-1, 1), torch.full_like(idx, x.shape[1]), idx)
+    return y.to(x.dtype), idx, full
 
 
 def moe_gating_top_k(x, k, bias=None, k_group=1, group_count=1, group_select_mode=0, norm_type=0, routed_scaling_factor=1.0,
@@ -480,24 +488,47 @@ def moe_finalize_routing(rows, skip1, skip2, bias, scales, src_to_dst, expert_fo
     return acc.to(rows.dtype)
 
 
-def moe_init_routing_v2(x, expert_idx, expert_num, quant_mode=-1, expert_tokens_num_type=0, row_idx_type=0):
+def moe_init_routing_v2(x, expert_idx, expert_num, quant_mode=-1, expert_tokens_num_type=0, row_idx_type=0,
+                        active_expert_range=None, active_num=-1, scale=None):
     """MoeInitRoutingV3, dropless (converter npu_moe_init_routing_v2.py:41-95; experiment_ops.h:2137-2192).
-    Decision: pairs are numbered f = t*K + k; gather index = sorted position -> f, scatter index = f -> position."""
+    Decisions: pairs are numbered f = t*K + k; gather index = sorted position -> f, scatter index = f -> position.
+    active_expert_range [lo, hi): only those experts keep rows and are counted (expert_tokens has hi - lo entries);
+    the other pairs sort behind the kept ones (stable), get no row, and -1 in the scatter index.  active_num > 0:
+    only rows at sorted positions < active_num are materialised (the indices still describe the whole sort).
+    scale: without quantisation a per-token fp32 value that is carried to the copies (expanded_scale); with dynamic
+    quantisation fp32 smooth scales [hi - lo, H] or [1, H] multiplied in (fp32) before each copy is quantised on its own."""
     T, K = expert_idx.shape
+    lo, hi = (0, expert_num) if active_expert_range is None else (int(active_expert_range[0]), int(active_expert_range[1]))
+    nk = hi - lo
     flat = expert_idx.reshape(-1).to(torch.int64)
-    order = torch.sort(flat, stable=True)
+    keys = torch.where((flat >= lo) & (flat < hi), flat - lo, torch.full_like(flat, nk))
+    order = torch.sort(keys, stable=True)
+    kept = int((keys < nk).sum())
     tok = order.indices // K
+    M, H = T * K, x.shape[1]
+    limit = kept if active_num is None or active_num <= 0 else min(kept, int(active_num))
     if quant_mode == 1:
-        q, s = dynamic_quant(x)
-        ex, es = q[tok], s[tok]
+        if scale is None:
+            q, s = dynamic_quant(x)
+            ex_all, es_all = q[tok], s[tok]
+        else:
+            sm = scale.float().reshape(-1, H)
+            srow = sm[order.values.clamp(max=nk - 1)] if sm.shape[0] > 1 else sm[:1].expand(M, H)
+            ex_all, es_all = quantize_rows_f32(x[tok].float() * srow)
+        ex = torch.zeros(M, H, dtype=torch.int8)
     else:
-        ex, es = x[tok], torch.zeros(T * K, dtype=torch.float32)
+        ex_all = x[tok]
+        es_all = scale.float()[tok] if scale is not None else torch.zeros(M, dtype=torch.float32)
+        ex = torch.zeros(M, H, dtype=x.dtype)
+    es = torch.zeros(M, dtype=torch.float32)
+    ex[:limit] = ex_all[:limit]
+    es[:limit] = es_all[:limit]
     if row_idx_type == 0:
         ridx = order.indices.to(torch.int32)
     else:
-        ridx = torch.empty(T * K, dtype=torch.int32)
-        ridx[order.indices] = torch.arange(T * K, dtype=torch.int32)
-    cnt = torch.bincount(flat, minlength=expert_num)[:expert_num]
+        ridx = torch.full((M,), -1, dtype=torch.int32)
+        ridx[order.indices[:kept]] = torch.arange(kept, dtype=torch.int32)
+    cnt = torch.bincount(keys, minlength=nk + 1)[:nk]
     tokens = cnt if expert_tokens_num_type == 1 else torch.cumsum(cnt, 0)
     return ex.contiguous(), ridx, tokens.to(torch.int64), es.contiguous()
 
@@ -522,35 +553,53 @@ def dispatch_rows(T: int, R: int, E: int, K: int) -> int:
 
 
 def moe_distribute_dispatch(xs: Sequence[torch.Tensor], ids: Sequence[torch.Tensor], E: int,
-                            quant_mode: int = 2, expert_token_nums_type: int = 1) -> List[DispatchOut]:
+                            quant_mode: int = 2, expert_token_nums_type: int = 1,
+                            x_active_mask: Optional[Sequence[Optional[torch.Tensor]]] = None,
+                            scales: Optional[torch.Tensor] = None, special_experts: int = 0,
+                            global_bs: int = 0) -> List[DispatchOut]:
     """MoeDistributeDispatch for all R ranks at once (converter moe_distribute_dispatch.py:4-45).
 
     Rank r owns experts [r*E_l, (r+1)*E_l).  Each rank quantises its tokens once (quant_mode 2), sorts
     its T*K copies by expert id (stable in t*K+k) and sends each copy to the owner of its expert.  The
     receiver orders rows by (local expert, source rank, send order).  Decisions: the contents of the
     handshake tensors (see DispatchOut) and zero fill of rows past the received total.
+    Optional arguments (decisions; the converters name them without defining them): x_active_mask[r] bool [T] --
+    tokens marked False send nothing (their expand_idx entries are -1); scales fp32 [E, H] -- smooth scales: copy
+    (t, k) is quantised on its own after the fp32 product x[t] * scales[expert]; special_experts > 0 (second-generation
+    op, moe_distribute_dispatch_v2.py:15-18): ids in [E, E + special_experts) name zero / copy / constant experts
+    that the combine evaluates at the sender, so those pairs are not sent either; global_bs != 0: the ranks may hold
+    different numbers of tokens, at most global_bs / R each, and expand_x is sized for that maximum.
     """
     R = len(xs)
     E_l = E // R
-    T, K = ids[0].shape
+    K = ids[0].shape[1]
     H = xs[0].shape[1]
-    A = dispatch_rows(T, R, E, K)
+    A = dispatch_rows(global_bs // R if global_bs else ids[0].shape[0], R, E, K)
     send_rows, send_scales, send_e, expand_idx = [], [], [], []
     for r in range(R):
-        if quant_mode == 2:
-            q, s = dynamic_quant(xs[r])
+        T = ids[r].shape[0]
+        flat_e = ids[r].reshape(-1).to(torch.int64)
+        keep = flat_e < E if special_experts > 0 else torch.ones_like(flat_e, dtype=torch.bool)
+        if x_active_mask is not None and x_active_mask[r] is not None:
+            keep = keep & x_active_mask[r].to(torch.bool).repeat_interleave(K)
+        keys = torch.where(keep, flat_e, torch.full_like(flat_e, E))
+        order = torch.sort(keys, stable=True)
+        kept = int(keep.sum())
+        tok = (order.indices // K)[:kept]
+        if quant_mode == 2 and scales is not None:
+            q, s = quantize_rows_f32(xs[r][tok].float() * scales.float()[order.values[:kept]])
+        elif quant_mode == 2:
+            q0, s0 = dynamic_quant(xs[r])
+            q, s = q0[tok], s0[tok]
         elif quant_mode == 0:
-            q, s = xs[r], torch.zeros(T, dtype=torch.float32)
+            q, s = xs[r][tok], torch.zeros(kept, dtype=torch.float32)
         else:
             raise NotImplementedError("quant_mode must be 0 or 2")
-        flat_e = ids[r].reshape(-1).to(torch.int64)
-        order = torch.sort(flat_e, stable=True)
-        tok = order.indices // K
-        send_rows.append(q[tok])
-        send_scales.append(s[tok])
-        send_e.append(order.values)
-        inv = torch.empty(T * K, dtype=torch.int32)
-        inv[order.indices] = torch.arange(T * K, dtype=torch.int32)
+        send_rows.append(q)
+        send_scales.append(s)
+        send_e.append(order.values[:kept])
+        inv = torch.full((T * K,), -1, dtype=torch.int32)
+        inv[order.indices[:kept]] = torch.arange(kept, dtype=torch.int32)
         expand_idx.append(inv)
     outs = []
     for d in range(R):
@@ -575,17 +624,66 @@ def moe_distribute_dispatch(xs: Sequence[torch.Tensor], ids: Sequence[torch.Tens
     return outs
 
 
+def special_expert_row(kind_index: int, ori_x: torch.Tensor, zero_num: int, copy_num: int, alpha_1=None, alpha_2=None,
+                       const_v=None) -> torch.Tensor:
+    """fp32 rows [T, H] that special expert number `kind_index` (its id minus moe_expert_num) stands for.  Decision (the
+    second-generation combine names these inputs without defining them, moe_distribute_combine_v2.py:17-20,47-50): zero
+    experts give 0, copy experts the token itself (ori_x), constant expert c gives alpha_1[c] * ori_x + alpha_2[c] *
+    const_v[c], two fp32 products and one fp32 sum per element."""
+    x = ori_x.float()
+    if kind_index < zero_num:
+        return torch.zeros_like(x)
+    if kind_index < zero_num + copy_num:
+        return x
+    c = kind_index - zero_num - copy_num
+    return alpha_1[c].float().unsqueeze(0) * x + alpha_2[c].float().unsqueeze(0) * const_v[c].float().unsqueeze(0)
+
+
+def combine_rows(recv: torch.Tensor, pos: torch.Tensor, weights: torch.Tensor, ids: torch.Tensor, E: int,
+                 shared=None, x_active_mask=None, special=None) -> torch.Tensor:
+    """weighted_gather_sum with the optional inputs: pairs of special experts (id >= E) take special_expert_row instead
+    of a returned row; tokens whose mask is False give an all-zero output row (decision)."""
+    T, K = weights.shape
+    H = recv.shape[1] if recv.numel() else special["ori_x"].shape[1]
+    acc = None
+    for k in range(K):
+        idk = ids[:, k].long()
+        row = torch.zeros(T, H, dtype=torch.float32)
+        normal = idk < E
+        if special is None:
+            normal = torch.ones_like(normal)
+        p = pos[:, k].long()
+        ok = normal & (p >= 0)
+        row[ok] = recv[p[ok]].float()
+        if special is not None:
+            for sidx in torch.unique(idk[~normal]).tolist():
+                sel = idk == sidx
+                row[sel] = special_expert_row(int(sidx) - E, special["ori_x"], special["zero"], special["copy"],
+                                              special.get("alpha_1"), special.get("alpha_2"), special.get("const_v"))[sel]
+        term = weights[:, k].float().unsqueeze(-1) * row
+        acc = term if acc is None else acc + term
+    if shared is not None:
+        acc = acc + shared.float()
+    if x_active_mask is not None:
+        acc[~x_active_mask.to(torch.bool)] = 0
+    dtype = recv.dtype if recv.numel() else special["ori_x"].dtype
+    return acc.to(dtype)
+
+
 def moe_distribute_combine(ys: Sequence[torch.Tensor], ids: Sequence[torch.Tensor],
                            disp: Sequence[DispatchOut], weights: Sequence[torch.Tensor], E: int,
-                           shared: Optional[Sequence[torch.Tensor]] = None) -> List[torch.Tensor]:
+                           shared: Optional[Sequence[torch.Tensor]] = None,
+                           x_active_mask: Optional[Sequence[Optional[torch.Tensor]]] = None,
+                           special: Optional[Sequence[dict]] = None) -> List[torch.Tensor]:
     """MoeDistributeCombine for all R ranks (converter moe_distribute_combine.py:4-60).
 
     Every expert-output row returns to the rank that sent it, landing at its position in that rank's send
-    order; then out[t] = sum_k expert_scales[t,k] * row(t,k) as in weighted_gather_sum.
+    order; then out[t] = sum_k expert_scales[t,k] * row(t,k) as in weighted_gather_sum (combine_rows when a mask or
+    special experts are given: special[s] = {"ori_x", "zero", "copy", "alpha_1", "alpha_2", "const_v"} of rank s).
     """
     R = len(ys)
     E_l = E // R
-    T, K = ids[0].shape
+    K = ids[0].shape[1]
     H = ys[0].shape[1]
     back = [[None] * R for _ in range(R)]      # back[src][owner] -> list of row blocks in expert order
     for d in range(R):
@@ -602,8 +700,13 @@ def moe_distribute_combine(ys: Sequence[torch.Tensor], ids: Sequence[torch.Tenso
     outs = []
     for s in range(R):
         recv = torch.cat([back[s][d] for d in range(R)])      # == send order (sorted by global expert id)
+        T = ids[s].shape[0]
         pos = disp[s].expand_idx.reshape(T, K)
-        outs.append(weighted_gather_sum(recv, pos, weights[s], None if shared is None else shared[s]))
+        if x_active_mask is None and special is None:
+            outs.append(weighted_gather_sum(recv, pos, weights[s], None if shared is None else shared[s]))
+        else:
+            outs.append(combine_rows(recv, pos, weights[s], ids[s], E, None if shared is None else shared[s],
+                                     None if x_active_mask is None else x_active_mask[s], None if special is None else special[s]))
     return outs
 
 

@@ -42,9 +42,9 @@ def test_argument_validation_happens_before_any_cuda_call(built_library):
         ("tab_moe_combine", (one, 3, one, one, n, 4, 2, 64, one, n), "dtype"),
         ("tab_moe_exchange_rows", (one, n, one, 2, 4, 0, 0, 24, 8, 1, one, n, n), "multiple of 16"),
         ("tab_moe_exchange_plan", (one, 64, 64, 0, 1, one, one, one, n), "R*E_l"),
-        ("tab_grouped_matmul_w8a8", (one, one, n, n, one, 0, 8, 24, 64, 2, 15, one, 0, n), "Kd"),
-        ("tab_grouped_matmul_w8a8", (one, one, n, n, one, 0, 8, 32, 64, 2000, 15, one, 0, n), "groups"),
-        ("tab_grouped_matmul_w8a8", (one, one, n, n, one, 0, 8, 32, 64, 2, 1, one, 0, n), "output dtype"),
+        ("tab_grouped_matmul_w8a8", (one, one, n, n, n, one, 0, 8, 24, 64, 2, 15, one, 0, n), "Kd"),
+        ("tab_grouped_matmul_w8a8", (one, one, n, n, n, one, 0, 8, 32, 64, 2000, 15, one, 0, n), "groups"),
+        ("tab_grouped_matmul_w8a8", (one, one, n, n, n, one, 0, 8, 32, 64, 2, 1, one, 0, n), "output dtype"),
         ("tab_prepack_weight_i8", (one, 1, 32, 32, one, n), "in-place"),
     ]
     for name, args, needle in cases:
@@ -61,7 +61,7 @@ def test_zero_sized_calls_are_no_ops(built_library):
     _lib.call("tab_dynamic_quant", n, 15, n, 0, 1024, n, n, n)
     _lib.call("tab_swiglu", n, 15, 0, 1024, n, n)
     _lib.call("tab_moe_combine", n, 15, n, n, n, 0, 8, 1024, n, n)
-    _lib.call("tab_grouped_matmul_w8a8", n, n, n, n, n, 1, 0, 1024, 1024, 8, 15, n, 0, n)
+    _lib.call("tab_grouped_matmul_w8a8", n, n, n, n, n, n, 1, 0, 1024, 1024, 8, 15, n, 0, n)
 
 
 def test_ops_have_no_cpu_fallback():
@@ -127,9 +127,13 @@ def test_meta_shape_rules():
     out = npu.npu_moe_distribute_combine(torch.empty(A, 64, dtype=torch.bfloat16, device=m), ids, outs[2], outs[4],
                                          torch.empty(6, 2, device=m), "ep", R, 1, E)
     assert out.shape == (6, 64) and out.dtype == torch.bfloat16
-    for bad in (dict(tp_world_size=2), dict(expert_shard_type=1), dict(shared_expert_rank_num=1), dict(quant_mode=1), dict(global_bs=8)):
+    for bad in (dict(tp_world_size=2), dict(expert_shard_type=1), dict(shared_expert_rank_num=1), dict(quant_mode=1)):
         with pytest.raises(NotImplementedError):
             npu.npu_moe_distribute_dispatch(x, ids, "ep", R, 1, E, **bad)
+    with pytest.raises(RuntimeError, match="global_bs"):          # must hold every rank's tokens: >= R * T, a multiple of R
+        npu.npu_moe_distribute_dispatch(x, ids, "ep", R, 1, E, global_bs=8)
+    big = npu.npu_moe_distribute_dispatch(x, ids, "ep", R, 1, E, quant_mode=2, global_bs=R * 10)
+    assert big[0].shape == (10 * R * min(E // R, K), 64) and big[2].shape == (T * K,)
     with pytest.raises(RuntimeError):
         npu.npu_moe_distribute_dispatch(x, ids, "ep", 3, 1, E)     # E not divisible by R
     with pytest.raises(NotImplementedError):

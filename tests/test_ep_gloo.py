@@ -138,3 +138,70 @@ def test_single_rank_dispatch_needs_no_group():
     d = O.moe_distribute_dispatch([x], [ids], cfg.E, expert_token_nums_type=0)[0]
     assert torch.equal(outs[0], d.expand_x) and torch.equal(outs[3], d.expert_token_nums)
     assert torch.equal(outs[2], d.expand_idx) and torch.equal(outs[4], d.ep_recv_count)
+
+
+def _options_inputs(world):
+    """Ranks with different numbers of tokens (global_bs), a token mask each, and special experts among the ids."""
+    E, K, H, special = 8, 3, 64, 3
+    toks, g = [], torch.Generator().manual_seed(99)
+    for r in range(world):
+        T = 12 + 5 * r
+        x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+        ids = torch.stack([torch.randperm(E + special, generator=g)[:K] for _ in range(T)]).to(torch.int32)
+        wt = torch.rand(T, K, generator=g)
+        mask = torch.rand(T, generator=g) < 0.8
+        toks.append((x, ids, wt, mask))
+    consts = [torch.randn(1, H, generator=g).to(torch.bfloat16) for _ in range(3)]
+    return E, K, H, special, toks, consts
+
+
+def _options_worker(rank, world, port, q, outdir):
+    try:
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        ep.register_ep_group("ep_opt", dist.group.WORLD)
+        E, K, H, special, toks, consts = _options_inputs(world)
+        x, ids, wt, mask = toks[rank]
+        gbs = world * max(t[0].shape[0] for t in toks)
+        outs = ep.dispatch(OracleKernels, x, ids, "ep_opt", world, rank, E, 0, 1, mask=mask, special=special, global_bs=gbs)
+        ex, ds, expand_idx, nums, ep_recv = outs[:5]
+        y = (ex.float() * 2).to(torch.bfloat16)                      # a stand-in for the experts: every row doubled
+        sp = {"expert_ids": ids, "E": E, "zero": 1, "copy": 1, "const": 1, "ori_x": x, "alpha_1": consts[0], "alpha_2": consts[1],
+              "const_v": consts[2]}
+        out = ep.combine(OracleKernels, y, ids, expand_idx, ep_recv, wt, "ep_opt", world, rank, E, mask=mask, special=sp)
+        torch.save((out, ex, nums, ep_recv, expand_idx), os.path.join(outdir, f"rank{rank}.pt"))
+        q.put((rank, "ok"))
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception:
+        q.put((rank, "error", traceback.format_exc()))
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_mask_special_experts_and_uneven_batches_over_gloo(world, tmp_path):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_options_worker, args=(r, world, port, q, str(tmp_path))) for r in range(world)]
+    for p in procs:
+        p.start()
+    for _ in range(world):
+        item = q.get(timeout=180)
+        assert item[1] == "ok", item[2]
+    for p in procs:
+        p.join(timeout=60)
+    E, K, H, special, toks, consts = _options_inputs(world)
+    xs, idl, wl, masks = zip(*toks)
+    gbs = world * max(x.shape[0] for x in xs)
+    disp = O.moe_distribute_dispatch(xs, idl, E, quant_mode=0, x_active_mask=masks, special_experts=special, global_bs=gbs)
+    ys = [(d.expand_x.float() * 2).to(torch.bfloat16) for d in disp]
+    sps = [{"ori_x": xs[r], "zero": 1, "copy": 1, "alpha_1": consts[0], "alpha_2": consts[1], "const_v": consts[2]} for r in range(world)]
+    ref = O.moe_distribute_combine(ys, idl, disp, wl, E, None, masks, sps)
+    for r in range(world):
+        out, ex, nums, ep_recv, expand_idx = torch.load(os.path.join(str(tmp_path), f"rank{r}.pt"))
+        n_rows = int(disp[r].expert_token_nums.sum())
+        assert ex.shape == disp[r].expand_x.shape and torch.equal(ex[:n_rows], disp[r].expand_x[:n_rows])
+        assert torch.equal(nums, disp[r].expert_token_nums) and torch.equal(ep_recv, disp[r].ep_recv_count)
+        assert torch.equal(expand_idx, disp[r].expand_idx)
+        assert torch.equal(out, ref[r])

@@ -31,10 +31,11 @@ SIGNATURES = {
     "tab_moe_exchange_plan": [_P, _L, _L, _L, _I, _P, _P, _P, _P],
     "tab_moe_exchange_rows": [_P, _P, _P, _L, _L, _L, _I, _L, _L, _I, _P, _P, _P],
     "tab_moe_compute_expert_tokens": [_P, _L, _L, _P, _P],
-    "tab_moe_gating_top_k_softmax": [_P, _I, _L, _L, _L, _P, _P, _P, _P],
-    "tab_moe_gating_top_k": [_P, _P, _I, _L, _L, _L, _L, _L, _I, _I, c_float, c_float, _P, _P, _P, _P],
+    "tab_moe_gating_top_k_softmax": [_P, _I, _P, _L, _L, _L, _P, _P, _P, _P],
+    "tab_moe_gating_top_k": [_P, _P, _P, _I, _L, _L, _L, _L, _L, _I, _I, c_float, c_float, _P, _P, _P, _P],
     "tab_moe_finalize_routing": [_P, _I, _P, _P, _P, _P, _P, _P, _L, _L, _L, _P, _P],
-    "tab_moe_init_routing_v2": [_P, _I, _P, _L, _L, _L, _L, _I, _I, _I, _P, _P, _P, _P, _P, c_size_t, _P],
+    "tab_moe_init_routing_v2": [_P, _I, _P, _L, _L, _L, _L, _L, _I, _I, _I, _L, _P, _L, _P, _P, _P, _P, _P, c_size_t, _P],
+    "tab_moe_dispatch_pack_ex": [_P, _I, _P, _L, _L, _L, _L, _L, _I, _P, _P, _L, _P, _L, _I, _P, _P, _P, _P, _P, _I, _P, c_size_t, _P],
     "tab_ep_signal": [_P, _P, _L, _P],
     "tab_ep_wait": [_P, _P, _L, _I, _P, _I, _P],
     "tab_ep_send_rows": [_P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P, _P, _P, _P, _I, _P, _P, _I, _P],
@@ -45,8 +46,9 @@ SIGNATURES = {
     "tab_ep_return_rows": [_P, _P, _L, _L, _L, _L, _L, _L, _P, _P],
     "tab_ep_return_plan": [_P, _L, _L, _L, _L, _L, _L, _P, _P, _P],
     "tab_moe_combine": [_P, _I, _P, _P, _P, _L, _L, _L, _P, _P],
+    "tab_moe_combine_ex": [_P, _I, _P, _P, _P, _L, _L, _L, _P, _P, _P, _L, _L, _L, _L, _P, _P, _P, _P, _P],
     "tab_prepack_weight_i8": [_P, _L, _L, _L, _P, _P],
-    "tab_grouped_matmul_w8a8": [_P, _P, _P, _P, _P, _I, _L, _L, _L, _L, _I, _P, _L, _P],
+    "tab_grouped_matmul_w8a8": [_P, _P, _P, _P, _P, _P, _I, _L, _L, _L, _L, _I, _P, _L, _P],
     "tab_grouped_matmul_w8a8_scatter": [_P, _P, _P, _P, _P, _I, _L, _L, _L, _L, _I, _P, _L, _P],
     "tab_grouped_matmul_swiglu_quant_workspace_bytes": [_L, _L, POINTER(c_size_t)],
     "tab_grouped_matmul_swiglu_quant": [_P, _P, _P, _P, _P, _I, _L, _L, _L, _L, _I, _P, _P, _P, c_size_t, _L, _P],

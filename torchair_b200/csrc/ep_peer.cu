@@ -145,7 +145,8 @@ __global__ void __launch_bounds__(kEpThreads) ep_send_kernel(const uint4* __rest
       peer_counts[d][my_rank * E_l + e] = max(expert_counts[i], 0);
     }
   }
-  for (int p = blockIdx.x; p < M; p += gridDim.x) {
+  const int total = min(M, s_base[R]);     // pairs that were dropped before the sort have no row
+  for (int p = blockIdx.x; p < total; p += gridDim.x) {
     const int d = rank_of_position(s_base, R, p);
     if (p - s_base[d] >= C) {           // more rows for one destination than its slot holds (counts and C disagree): not sent
       if (threadIdx.x == 0) atomicCAS(status, 0, code);
@@ -160,8 +161,8 @@ __global__ void __launch_bounds__(kEpThreads) ep_send_kernel(const uint4* __rest
   }
   for (int f = blockIdx.x * kEpThreads + threadIdx.x; f < M; f += gridDim.x * kEpThreads) {
     const int p = expand_idx[f];
-    const int d = rank_of_position(s_base, R, p);
-    expand_idx_slot[f] = d * C + (p - s_base[d]);
+    const int d = rank_of_position(s_base, R, p < 0 ? 0 : p);
+    expand_idx_slot[f] = p < 0 ? -1 : d * C + (p - s_base[d]);
   }
 }
 

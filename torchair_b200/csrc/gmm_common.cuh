@@ -30,6 +30,7 @@ struct GmmParams {
   int chan_tiles;  // plain: ceil(N/256); fused: ceil(I/128)
   int half;        // fused: I
   const float* w_scale;    // [E, N] or null
+  const int32_t* bias;     // plain: [E, N] added to the int32 accumulators before anything else, or null
   const float* tok_scale;  // [M] or null
   void* out;               // plain: [M, N] of out_dtype
   int out_dtype;

@@ -116,7 +116,7 @@ extern "C" int tab_grouped_matmul_finalize_routing(const int8_t* x, const int8_t
   cudaStream_t st = as_stream(stream);
   int32_t* acc = static_cast<int32_t*>(workspace);
   if (M > 0) {
-    const int rc = tab_grouped_matmul_w8a8(x, packed_weight, nullptr, nullptr, group_list, group_list_type, M, Kd, N, E, TAB_I32, acc,
+    const int rc = tab_grouped_matmul_w8a8(x, packed_weight, nullptr, nullptr, nullptr, group_list, group_list_type, M, Kd, N, E, TAB_I32, acc,
                                            expected_rows_per_group, stream);
     if (rc != TAB_OK) return rc;
   }

@@ -216,12 +216,19 @@ gmm_i8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
         const bool v0 = c0 < p.N, v1 = c1 < p.N;
         const float w0 = (v0 && p.w_scale) ? p.w_scale[static_cast<int64_t>(it.e) * p.N + c0] : 1.f;
         const float w1 = (v1 && p.w_scale) ? p.w_scale[static_cast<int64_t>(it.e) * p.N + c1] : 1.f;
+        const int bias0 = (v0 && p.bias) ? p.bias[static_cast<int64_t>(it.e) * p.N + c0] : 0;
+        const int bias1 = (v1 && p.bias) ? p.bias[static_cast<int64_t>(it.e) * p.N + c1] : 0;
         for (int col0 = 0; col0 < nvalid; col0 += 16) {
           int a[16], b[16];
           __syncwarp();
           ptx::tmem_ld16(t0 + col0, a);
           ptx::tmem_ld16(t0 + NT + col0, b);
           ptx::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            a[j] += bias0;
+            b[j] += bias1;
+          }
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             if (col0 + j < nvalid) {
@@ -457,6 +464,7 @@ extern "C" int tab_prepack_weight_i8(const int8_t* weight, int64_t E, int64_t Kd
 }
 
 static int grouped_matmul_plain(const int8_t* x, const int8_t* packed_weight, const float* scale, const float* per_token_scale,
+                                const int32_t* bias,
                                 const int64_t* group_list, int group_list_type, int64_t M, int64_t Kd, int64_t N, int64_t E,
                                 int out_dtype, void* y, const uint64_t* row_dst, int64_t expected_rows_per_group,
                                 tab_stream_t stream) {
@@ -480,6 +488,7 @@ static int grouped_matmul_plain(const int8_t* x, const int8_t* packed_weight, co
   p.half = 0;
   p.w_scale = out_dtype == TAB_I32 ? nullptr : scale;
   p.tok_scale = out_dtype == TAB_I32 ? nullptr : per_token_scale;
+  p.bias = bias;
   p.out = y;
   p.out_dtype = out_dtype;
   p.row_dst = reinterpret_cast<const unsigned long long*>(row_dst);
@@ -488,10 +497,10 @@ static int grouped_matmul_plain(const int8_t* x, const int8_t* packed_weight, co
 }
 
 extern "C" int tab_grouped_matmul_w8a8(const int8_t* x, const int8_t* packed_weight, const float* scale,
-                                       const float* per_token_scale, const int64_t* group_list, int group_list_type,
-                                       int64_t M, int64_t Kd, int64_t N, int64_t E, int out_dtype, void* y,
+                                       const float* per_token_scale, const int32_t* bias, const int64_t* group_list,
+                                       int group_list_type, int64_t M, int64_t Kd, int64_t N, int64_t E, int out_dtype, void* y,
                                        int64_t expected_rows_per_group, tab_stream_t stream) {
-  return grouped_matmul_plain(x, packed_weight, scale, per_token_scale, group_list, group_list_type, M, Kd, N, E, out_dtype, y,
+  return grouped_matmul_plain(x, packed_weight, scale, per_token_scale, bias, group_list, group_list_type, M, Kd, N, E, out_dtype, y,
                               nullptr, expected_rows_per_group, stream);
 }
 
@@ -502,8 +511,8 @@ extern "C" int tab_grouped_matmul_w8a8_scatter(const int8_t* x, const int8_t* pa
                                                tab_stream_t stream) {
   if (!row_dst && M > 0) return fail(TAB_ERR_BAD_ARG, "grouped_matmul_scatter: null row address table");
   if ((N * 2) % 16 != 0) return fail(TAB_ERR_ALIGNMENT, "grouped_matmul_scatter: N=%lld must be a multiple of 8", (long long)N);
-  return grouped_matmul_plain(x, packed_weight, scale, per_token_scale, group_list, group_list_type, M, Kd, N, E, out_dtype, nullptr,
-                              row_dst, expected_rows_per_group, stream);
+  return grouped_matmul_plain(x, packed_weight, scale, per_token_scale, nullptr, group_list, group_list_type, M, Kd, N, E, out_dtype,
+                              nullptr, row_dst, expected_rows_per_group, stream);
 }
 
 extern "C" int tab_grouped_matmul_swiglu_quant_workspace_bytes(int64_t M, int64_t I, size_t* bytes) {

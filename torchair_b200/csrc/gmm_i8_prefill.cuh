@@ -82,6 +82,7 @@ __device__ __forceinline__ void pf_narrow_epilogue(const GmmParams& p, const Wor
     const int ch = it.ct * 256 + chalf * 128 + c_l;
     const bool cvalid = ch < p.N;
     const float wv = ws[chalf * 128 + c_l];
+    const int bias = (cvalid && p.bias) ? p.bias[static_cast<int64_t>(it.e) * p.N + ch] : 0;
 #pragma unroll 1
     for (int c = 0; c < nv16; c += 16) {
       int a[16];
@@ -90,6 +91,7 @@ __device__ __forceinline__ void pf_narrow_epilogue(const GmmParams& p, const Wor
       ptx::tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
+        a[j] += bias;
         const int row = row0 + c + j;
         if (c + j < nvalid && cvalid) {
           if (p.out_dtype == TAB_I32) {
@@ -319,6 +321,14 @@ gmm_i8_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
             ptx::tmem_ld16(t0 + c, a);
             ptx::tmem_ld16(t0 + c + 16, b);
             ptx::tmem_ld_wait();
+            if (p.bias != nullptr) {                   // uniform: the same bias entry for every lane (token rows), a broadcast load
+              const int* brow = p.bias + static_cast<int64_t>(it.e) * p.N + c0 + c;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                a[j] += c0 + c + j < p.N ? __ldg(brow + j) : 0;
+                b[j] += c0 + c + 16 + j < p.N ? __ldg(brow + 16 + j) : 0;
+              }
+            }
             float f[32];
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
@@ -362,6 +372,11 @@ gmm_i8_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
           __syncwarp();                                // the loads below are warp-collective
           ptx::tmem_ld16(t0 + c, a);
           ptx::tmem_ld_wait();
+          if (p.bias != nullptr) {
+            const int* brow = p.bias + static_cast<int64_t>(it.e) * p.N + c0 + c;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) a[j] += c0 + c + j < p.N ? __ldg(brow + j) : 0;
+          }
           if (rvalid && c0 + c < p.N) {
             if (p.out_dtype == TAB_I32) {
               int* o = static_cast<int*>(p.out) + static_cast<int64_t>(row) * p.N + c0 + c;

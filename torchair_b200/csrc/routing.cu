@@ -52,22 +52,35 @@ __device__ int block_exclusive_scan(int* vals, int n, int* warp_sums) {
 // bit 2 = a bounded wait for a bulk copy gave up.
 __device__ int g_routing_status = 0;
 
-__device__ __forceinline__ int clamp_expert(int key, int nb) {
-  if (key < 0 || key >= nb) {
-    atomicOr(&g_routing_status, 1);   // clamped so that no access goes out of range; the host can ask afterwards
-    key = key < 0 ? 0 : nb - 1;
-  }
-  return key;
+// Which (token, k) pairs take part in a sort and under which key.  Experts [lo, hi) are kept under key id - lo; the
+// bin after them (key hi - lo, the last of nb = hi - lo + 1 bins) collects the pairs that are dropped: pairs of tokens
+// whose mask byte is 0, and -- when drop_outside is set -- pairs whose expert lies outside the range (an expert range
+// narrower than the model's, or special experts that are not dispatched).  Without drop_outside an id outside the
+// range is clamped to the nearest kept expert and reported in the status word: no access goes out of range either way.
+struct PairFilter {
+  const uint8_t* mask;   // [T] or null
+  int K;                 // pairs per token
+  int lo, hi;
+  int drop_outside;
+};
+
+__device__ __forceinline__ int pair_key(const PairFilter& pf, int id, int f) {
+  const int dropped = pf.hi - pf.lo;
+  if (pf.mask != nullptr && pf.mask[f / pf.K] == 0) return dropped;
+  if (id >= pf.lo && id < pf.hi) return id - pf.lo;
+  if (pf.drop_outside) return dropped;
+  atomicOr(&g_routing_status, 1);
+  return id < pf.lo ? 0 : dropped - 1;
 }
 
 // Phase 1: per-chunk histogram of expert ids.  chunk_hist [nchunks, nb].
-__global__ void __launch_bounds__(kChunk) route_hist_kernel(const int32_t* __restrict__ expert, int n, int nb,
+__global__ void __launch_bounds__(kChunk) route_hist_kernel(const int32_t* __restrict__ expert, int n, int nb, const PairFilter pf,
                                                             int* __restrict__ chunk_hist) {
   extern __shared__ int s_hist[];
   for (int i = threadIdx.x; i < nb; i += kChunk) s_hist[i] = 0;
   __syncthreads();
   const int f = blockIdx.x * kChunk + threadIdx.x;
-  if (f < n) atomicAdd(&s_hist[clamp_expert(expert[f], nb)], 1);
+  if (f < n) atomicAdd(&s_hist[pair_key(pf, expert[f], f)], 1);
   __syncthreads();
   for (int i = threadIdx.x; i < nb; i += kChunk) chunk_hist[blockIdx.x * nb + i] = s_hist[i];
 }
@@ -77,7 +90,7 @@ __global__ void __launch_bounds__(kChunk) route_hist_kernel(const int32_t* __res
 constexpr int kScanWarps = 8;
 __global__ void __launch_bounds__(kScanWarps * 32) route_scan_kernel(int* __restrict__ chunk_hist, int nchunks, int nb,
                                                                     int* __restrict__ expert_count,
-                                                                    int* __restrict__ expert_count_out) {
+                                                                    int* __restrict__ expert_count_out, int nb_out) {
   const int lane = threadIdx.x & 31;
   const int e = blockIdx.x * kScanWarps + (threadIdx.x >> 5);
   if (e >= nb) return;
@@ -96,16 +109,17 @@ __global__ void __launch_bounds__(kScanWarps * 32) route_scan_kernel(int* __rest
   }
   if (lane == 0) {
     expert_count[e] = run;
-    if (expert_count_out) expert_count_out[e] = run;
+    if (expert_count_out && e < nb_out) expert_count_out[e] = run;   // the bin of dropped pairs is not reported
   }
 }
 
 // Phase 3: stable rank of every pair inside its chunk (warp match + per-warp counts) plus the chunk base.
-//   sorted_expert[pos] = expert id, sorted_src[pos] = src_val[f] (or f when src_val is null),
+//   sorted_expert[pos] = key (expert id - lo), sorted_src[pos] = src_val[f] (or f when src_val is null),
 //   inverse[inv_key] = pos where inv_key = src_val[f] (init_routing: expanded_row_idx is indexed by the
-//   row_idx VALUE) or f (dispatch: expand_idx is indexed by the flattened pair index).
+//   row_idx VALUE) or f (dispatch: expand_idx is indexed by the flattened pair index); -1 for a dropped pair.
 __global__ void __launch_bounds__(kChunk) route_scatter_kernel(const int32_t* __restrict__ expert,
                                                                const int32_t* __restrict__ src_val, int n, int nb,
+                                                               const PairFilter pf,
                                                                const int* __restrict__ chunk_base,
                                                                const int* __restrict__ expert_count,
                                                                int32_t* __restrict__ sorted_expert,
@@ -121,7 +135,7 @@ __global__ void __launch_bounds__(kChunk) route_scatter_kernel(const int32_t* __
   block_exclusive_scan(s_base, nb, s_warp);
   const int f = blockIdx.x * kChunk + tid;
   const bool valid = f < n;
-  const int key = valid ? clamp_expert(expert[f], nb) : -1;
+  const int key = valid ? pair_key(pf, expert[f], f) : -1;
   const unsigned peers = __match_any_sync(0xffffffffu, key);
   const int rank_in_warp = __popc(peers & ((1u << lane) - 1u));
   if (valid && rank_in_warp == 0) s_wcnt[warp * nb + key] = static_cast<unsigned short>(__popc(peers));
@@ -144,7 +158,7 @@ __global__ void __launch_bounds__(kChunk) route_scatter_kernel(const int32_t* __
       atomicOr(&g_routing_status, 2);
       sv = f;                            // the gather then reads the pair's own token instead of an arbitrary row
     } else {
-      inverse[sv] = pos;
+      inverse[sv] = key == nb - 1 ? -1 : pos;
     }
     if (sorted_src) sorted_src[pos] = sv;
   }
@@ -175,18 +189,20 @@ static SortScratch carve(void* ws, int64_t n, int64_t nb, bool need_sorted_exper
   return s;
 }
 
-static int run_sort(const int32_t* expert, const int32_t* src_val, int64_t n, int64_t nb, const SortScratch& s,
+// nb = pf.hi - pf.lo + 1 bins (the last one takes the dropped pairs); expert_count_out gets the nb - 1 kept experts.
+static int run_sort(const int32_t* expert, const int32_t* src_val, int64_t n, const PairFilter& pf, const SortScratch& s,
                     int32_t* sorted_expert, int32_t* inverse, int32_t* expert_count_out, cudaStream_t st) {
+  const int64_t nb = pf.hi - pf.lo + 1;
   const int nchunks = static_cast<int>((n + kChunk - 1) / kChunk);
   const size_t scatter_smem = static_cast<size_t>(32) * nb * sizeof(unsigned short) + static_cast<size_t>(nb) * sizeof(int);
   if (scatter_smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(route_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(scatter_smem));
     if (e != cudaSuccess) return fail(TAB_ERR_CUDA, "routing: shared memory opt-in failed: %s", cudaGetErrorString(e));
   }
-  route_hist_kernel<<<nchunks, kChunk, nb * sizeof(int), st>>>(expert, (int)n, (int)nb, s.chunk_hist);
+  route_hist_kernel<<<nchunks, kChunk, nb * sizeof(int), st>>>(expert, (int)n, (int)nb, pf, s.chunk_hist);
   route_scan_kernel<<<(int)((nb + kScanWarps - 1) / kScanWarps), kScanWarps * 32, 0, st>>>(s.chunk_hist, nchunks, (int)nb,
-                                                                                          s.expert_count, expert_count_out);
-  route_scatter_kernel<<<nchunks, kChunk, scatter_smem, st>>>(expert, src_val, (int)n, (int)nb, s.chunk_hist, s.expert_count,
+                                                                                          s.expert_count, expert_count_out, (int)nb - 1);
+  route_scatter_kernel<<<nchunks, kChunk, scatter_smem, st>>>(expert, src_val, (int)n, (int)nb, pf, s.chunk_hist, s.expert_count,
                                                              sorted_expert, s.sorted_src, inverse);
   return check_launch("routing sort", 3);
 }
@@ -260,52 +276,68 @@ constexpr int kPackChunks = 8;
 constexpr int kPackMaxK = 256;
 constexpr int kSmallPairs = 4096;   // T*K up to which the sort runs inside the pack kernel (one launch instead of four)
 
-// kSortInside = false: expand_idx holds the sorted position of every pair (written by the three sort kernels) and
-// counts the rows per expert.  kSortInside = true (T*K <= kSmallPairs): the kernel sorts by itself -- every CTA keeps
-// the clamped expert ids of ALL pairs in shared memory and ranks the K pairs of its token directly (position = pairs
-// with a smaller id, plus earlier pairs with the same id: the stable order of the counting sort); the last CTA also
-// builds the per-expert counts.  expand_idx, counts and sorted_src are then outputs, expert_ids the input.
-template <typename T, bool kQuant, int THREADS, bool kSortInside>
-__global__ void __launch_bounds__(THREADS) dispatch_pack_kernel(const T* __restrict__ x,
-                                                               int32_t* __restrict__ expand_idx,
-                                                               int64_t tokens, int K, int cols,
-                                                               void* __restrict__ send_rows,
-                                                               float* __restrict__ send_scales,
-                                                               int32_t* __restrict__ counts,
-                                                               int64_t* __restrict__ nums64, int num_experts,
-                                                               int nums_type, const int32_t* __restrict__ expert_ids,
-                                                               int32_t* __restrict__ sorted_src) {
+// kSortInside = false: expand_idx holds the sorted position of every pair (written by the three sort kernels; -1 for
+// a dropped pair) and counts the rows per expert.  kSortInside = true (T*K <= kSmallPairs): the kernel sorts by itself
+// -- every CTA keeps the keys of ALL pairs in shared memory and ranks the K pairs of its token directly (position =
+// pairs with a smaller key, plus earlier pairs with the same key: the stable order of the counting sort); the last CTA
+// also builds the per-expert counts.  expand_idx, counts and sorted_src are then outputs, expert_ids the input.
+// kSmooth (quantising only): every copy is quantised on its own after multiplying the row by the fp32 smooth-scale row
+// of its expert (smooth [smooth_rows, cols]; one row for all experts when smooth_rows == 1).
+struct PackArgs {
+  int32_t* expand_idx;
+  int64_t tokens;
+  int K, cols;
+  void* send_rows;
+  float* send_scales;
+  int32_t* counts;
+  int64_t* nums64;
+  int num_experts;      // kept experts = pf.hi - pf.lo
+  int nums_type;
+  const int32_t* expert_ids;
+  int32_t* sorted_src;
+  const float* smooth;
+  int smooth_rows;
+  const float* passthrough_scale;   // not quantising: per-token value copied to send_scales of every copy (or null: 0)
+  int pos_limit;                    // copies at sorted positions >= pos_limit get no row (their indices are still reported)
+  PairFilter pf;
+};
+
+template <typename T, bool kQuant, int THREADS, bool kSortInside, bool kSmooth>
+__global__ void __launch_bounds__(THREADS) dispatch_pack_kernel(const T* __restrict__ x, const PackArgs a) {
   __shared__ float red[THREADS / 32];
   __shared__ int s_pos[kPackMaxK];
+  __shared__ int s_key[kSmooth ? kPackMaxK : 1];
   __shared__ short s_e[kSortInside ? kSmallPairs : 1];
-  __shared__ int s_hist[kSortInside ? kMaxExperts : 1];
+  __shared__ int s_hist[kSortInside ? kMaxExperts + 1 : 1];
+  const int K = a.K, cols = a.cols, num_experts = a.num_experts;
+  const int64_t tokens = a.tokens;
   const int nchunk = cols >> 3;
   if constexpr (kSortInside) {
     const int n = static_cast<int>(tokens) * K;
     const bool last = blockIdx.x == gridDim.x - 1;
     if (last)
-      for (int e = threadIdx.x; e < num_experts; e += THREADS) s_hist[e] = 0;
-    for (int f = threadIdx.x; f < n; f += THREADS) s_e[f] = static_cast<short>(clamp_expert(expert_ids[f], num_experts));
+      for (int e = threadIdx.x; e <= num_experts; e += THREADS) s_hist[e] = 0;
+    for (int f = threadIdx.x; f < n; f += THREADS) s_e[f] = static_cast<short>(pair_key(a.pf, a.expert_ids[f], f));
     __syncthreads();
     if (last) {
       for (int f = threadIdx.x; f < n; f += THREADS) atomicAdd(&s_hist[s_e[f]], 1);
       __syncthreads();
-      for (int e = threadIdx.x; e < num_experts; e += THREADS) counts[e] = s_hist[e];
+      for (int e = threadIdx.x; e < num_experts; e += THREADS) a.counts[e] = s_hist[e];
     }
   }
-  if (nums64 != nullptr && blockIdx.x == gridDim.x - 1 && threadIdx.x < 32) {
+  if (a.nums64 != nullptr && blockIdx.x == gridDim.x - 1 && threadIdx.x < 32) {
     // the per-expert copies as int64 counts (nums_type 1) or their running total (0), the form the grouped GEMM reads
     long long run = 0;
     for (int e0 = 0; e0 < num_experts; e0 += 32) {
       const int e = e0 + threadIdx.x;
-      const long long c = e < num_experts ? (kSortInside ? s_hist[e] : counts[e]) : 0;
+      const long long c = e < num_experts ? (kSortInside ? s_hist[e] : a.counts[e]) : 0;
       long long incl = c;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const long long t = __shfl_up_sync(0xffffffffu, incl, o);
         if (threadIdx.x >= o) incl += t;
       }
-      if (e < num_experts) nums64[e] = nums_type == 1 ? c : run + incl;
+      if (e < num_experts) a.nums64[e] = a.nums_type == 1 ? c : run + incl;
       run += __shfl_sync(0xffffffffu, incl, 31);
     }
   }
@@ -326,15 +358,21 @@ __global__ void __launch_bounds__(THREADS) dispatch_pack_kernel(const T* __restr
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) before += __shfl_xor_sync(0xffffffffu, before, o);
         if (lane == 0) {
-          s_pos[k] = before;
-          expand_idx[f0] = before;
-          if (sorted_src != nullptr) sorted_src[before] = f0;
+          if (a.sorted_src != nullptr) a.sorted_src[before] = f0;
+          if (e0 == num_experts) before = -1;                         // dropped pair: no row
+          a.expand_idx[f0] = before;
+          s_pos[k] = before < a.pos_limit ? before : -1;
+          if constexpr (kSmooth) s_key[k] = e0;
         }
       }
-      if constexpr (!kQuant) __syncthreads();   // (the quantising branch publishes s_pos with the barriers of its reduction)
     } else {
-      for (int k = threadIdx.x; k < K; k += THREADS) s_pos[k] = expand_idx[t * K + k];
+      for (int k = threadIdx.x; k < K; k += THREADS) {
+        const int p = a.expand_idx[t * K + k];
+        s_pos[k] = p < a.pos_limit ? p : -1;
+        if constexpr (kSmooth) s_key[k] = pair_key(a.pf, a.expert_ids[t * K + k], static_cast<int>(t) * K + k);
+      }
     }
+    __syncthreads();   // positions (and keys) are published
     if constexpr (kQuant) {
       Raw8<T> raw[kPackChunks];
 #pragma unroll
@@ -342,68 +380,121 @@ __global__ void __launch_bounds__(THREADS) dispatch_pack_kernel(const T* __restr
         const int ch = threadIdx.x + c * THREADS;
         if (ch < nchunk) raw[c].load(xr + ch * 8);
       }
-      float amax = 0.f;
+      int8_t* out = static_cast<int8_t*>(a.send_rows);
+      if constexpr (!kSmooth) {
+        float amax = 0.f;
 #pragma unroll
-      for (int c = 0; c < kPackChunks; ++c) {
-        const int ch = threadIdx.x + c * THREADS;
-        if (ch < nchunk) amax = fmaxf(amax, raw_amax(raw[c]));
-      }
-      for (int ch = threadIdx.x + kPackChunks * THREADS; ch < nchunk; ch += THREADS) {
-        float v[8];
-        Elem<T>::load8(xr + ch * 8, v);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-      }
-      amax = cta_max<THREADS>(amax, red);   // its barriers also publish s_pos
-      const RowQuant rq = make_row_quant(amax);
-      const float sc = rq.scale;
-      int8_t* out = static_cast<int8_t*>(send_rows);
-#pragma unroll
-      for (int c = 0; c < kPackChunks; ++c) {
-        const int ch = threadIdx.x + c * THREADS;
-        if (ch < nchunk) {
+        for (int c = 0; c < kPackChunks; ++c) {
+          const int ch = threadIdx.x + c * THREADS;
+          if (ch < nchunk) amax = fmaxf(amax, raw_amax(raw[c]));
+        }
+        for (int ch = threadIdx.x + kPackChunks * THREADS; ch < nchunk; ch += THREADS) {
           float v[8];
-          raw[c].unpack(v);
+          Elem<T>::load8(xr + ch * 8, v);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+        }
+        amax = cta_max<THREADS>(amax, red);
+        const RowQuant rq = make_row_quant(amax);
+        const float sc = rq.scale;
+#pragma unroll
+        for (int c = 0; c < kPackChunks; ++c) {
+          const int ch = threadIdx.x + c * THREADS;
+          if (ch < nchunk) {
+            float v[8];
+            raw[c].unpack(v);
+            const uint2 o = quant8(v, rq);
+            for (int k = 0; k < K; ++k)
+              if (s_pos[k] >= 0) __stcs(reinterpret_cast<uint2*>(out + static_cast<int64_t>(s_pos[k]) * cols + ch * 8), o);
+          }
+        }
+        for (int ch = threadIdx.x + kPackChunks * THREADS; ch < nchunk; ch += THREADS) {
+          float v[8];
+          Elem<T>::load8(xr + ch * 8, v);
           const uint2 o = quant8(v, rq);
-          for (int k = 0; k < K; ++k) __stcs(reinterpret_cast<uint2*>(out + static_cast<int64_t>(s_pos[k]) * cols + ch * 8), o);
+          for (int k = 0; k < K; ++k)
+            if (s_pos[k] >= 0) __stcs(reinterpret_cast<uint2*>(out + static_cast<int64_t>(s_pos[k]) * cols + ch * 8), o);
+        }
+        for (int k = threadIdx.x; k < K; k += THREADS)
+          if (s_pos[k] >= 0) a.send_scales[s_pos[k]] = sc;
+      } else {
+        // per copy: row * smooth row of its expert (fp32 product), own maximum, own scale
+        for (int k = 0; k < K; ++k) {
+          const int pos = s_pos[k];                        // uniform over the CTA
+          if (pos < 0) continue;
+          const float* sm = a.smooth + (a.smooth_rows > 1 ? static_cast<int64_t>(s_key[k]) * cols : 0);
+          auto value = [&](int c, int ch, float (&v)[8]) {
+            if (c >= 0) raw[c].unpack(v); else Elem<T>::load8(xr + ch * 8, v);
+            float m[8];
+            Elem<float>::load8(sm + ch * 8, m);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(v[i], m[i]);
+          };
+          float amax = 0.f;
+#pragma unroll
+          for (int c = 0; c < kPackChunks; ++c) {
+            const int ch = threadIdx.x + c * THREADS;
+            if (ch < nchunk) {
+              float v[8];
+              value(c, ch, v);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+            }
+          }
+          for (int ch = threadIdx.x + kPackChunks * THREADS; ch < nchunk; ch += THREADS) {
+            float v[8];
+            value(-1, ch, v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+          }
+          amax = cta_max<THREADS>(amax, red);
+          const RowQuant rq = make_row_quant(amax);
+          int8_t* orow = out + static_cast<int64_t>(pos) * cols;
+#pragma unroll
+          for (int c = 0; c < kPackChunks; ++c) {
+            const int ch = threadIdx.x + c * THREADS;
+            if (ch < nchunk) {
+              float v[8];
+              value(c, ch, v);
+              __stcs(reinterpret_cast<uint2*>(orow + ch * 8), quant8(v, rq));
+            }
+          }
+          for (int ch = threadIdx.x + kPackChunks * THREADS; ch < nchunk; ch += THREADS) {
+            float v[8];
+            value(-1, ch, v);
+            __stcs(reinterpret_cast<uint2*>(orow + ch * 8), quant8(v, rq));
+          }
+          if (threadIdx.x == 0) a.send_scales[pos] = rq.scale;
         }
       }
-      for (int ch = threadIdx.x + kPackChunks * THREADS; ch < nchunk; ch += THREADS) {
-        float v[8];
-        Elem<T>::load8(xr + ch * 8, v);
-        const uint2 o = quant8(v, rq);
-        for (int k = 0; k < K; ++k) __stcs(reinterpret_cast<uint2*>(out + static_cast<int64_t>(s_pos[k]) * cols + ch * 8), o);
-      }
-      if (threadIdx.x < K) send_scales[s_pos[threadIdx.x]] = sc;
-      for (int k = threadIdx.x + THREADS; k < K; k += THREADS) send_scales[s_pos[k]] = sc;
     } else {
-      __syncthreads();
-      T* out = static_cast<T*>(send_rows);
+      T* out = static_cast<T*>(a.send_rows);
       const int nvec = cols * static_cast<int>(sizeof(T)) / 16;
       const uint4* sp = reinterpret_cast<const uint4*>(xr);
       for (int vi = threadIdx.x; vi < nvec; vi += THREADS) {
         const uint4 val = sp[vi];
-        for (int k = 0; k < K; ++k) reinterpret_cast<uint4*>(out + static_cast<int64_t>(s_pos[k]) * cols)[vi] = val;
+        for (int k = 0; k < K; ++k)
+          if (s_pos[k] >= 0) reinterpret_cast<uint4*>(out + static_cast<int64_t>(s_pos[k]) * cols)[vi] = val;
       }
-      for (int k = threadIdx.x; k < K; k += THREADS) send_scales[s_pos[k]] = 0.f;
+      const float pass = a.passthrough_scale ? a.passthrough_scale[t] : 0.f;
+      for (int k = threadIdx.x; k < K; k += THREADS)
+        if (s_pos[k] >= 0) a.send_scales[s_pos[k]] = pass;
     }
   }
 }
 
 template <typename T, bool kSortInside>
-static void launch_pack(const void* x, int32_t* expand_idx, int64_t T_, int K, int H, int quant_mode, void* rows,
-                        float* scales, int32_t* counts, int64_t* nums64, int num_experts, int nums_type,
-                        const int32_t* expert_ids, int32_t* sorted_src, cudaStream_t st) {
+static void launch_pack(const void* x, const PackArgs& a, int quant_mode, cudaStream_t st) {
   const T* xp = static_cast<const T*>(x);
-  const bool small = H / 8 <= 128 * kPackChunks;
-  const int grid = grid_for(T_, small ? 10 : 5);
-#define TAB_PACK(Q, TH)                                                                                                   \
-  dispatch_pack_kernel<T, Q, TH, kSortInside><<<grid, TH, 0, st>>>(xp, expand_idx, T_, K, H, rows, scales, counts, nums64, \
-                                                                   num_experts, nums_type, expert_ids, sorted_src)
-  if (quant_mode == 2) {
-    if (small) TAB_PACK(true, 128); else TAB_PACK(true, 256);
+  const bool small = a.cols / 8 <= 128 * kPackChunks;
+  const int grid = grid_for(a.tokens, small ? 10 : 5);
+#define TAB_PACK(Q, TH, SM) dispatch_pack_kernel<T, Q, TH, kSortInside, SM><<<grid, TH, 0, st>>>(xp, a)
+  if (quant_mode == 2 && a.smooth != nullptr) {
+    if (small) TAB_PACK(true, 128, true); else TAB_PACK(true, 256, true);
+  } else if (quant_mode == 2) {
+    if (small) TAB_PACK(true, 128, false); else TAB_PACK(true, 256, false);
   } else {
-    if (small) TAB_PACK(false, 128); else TAB_PACK(false, 256);
+    if (small) TAB_PACK(false, 128, false); else TAB_PACK(false, 256, false);
   }
 #undef TAB_PACK
 }
@@ -499,20 +590,44 @@ __global__ void __launch_bounds__(kRowCopyThreads) exchange_rows_kernel(const ui
   }
 }
 
-// out[t] = sum_k w[t,k] * rows[idx[t*K+k]] (+ shared[t]); fp32, separate multiply and add, ascending k.
-template <typename T>
+// Optional inputs of the combine (all may be absent): a token mask, and the special experts of the second-generation
+// operator -- pairs whose expert id is >= num_experts stand for rows that are formed here instead of being gathered:
+// zero experts (0), copy experts (the token itself, ori_x) and constant experts (alpha_1[c] * ori_x + alpha_2[c] * v[c]).
+struct CombineExtra {
+  const uint8_t* mask;         // [T] or null: a 0 byte gives an all-zero output row
+  const int32_t* expert_ids;   // [T, K], read only when special experts exist
+  int num_experts, zero_num, copy_num, const_num;
+  const void* ori_x;           // [T, H]
+  const void* alpha_1;         // [const_num, H]
+  const void* alpha_2;         // [const_num, H]
+  const void* const_v;         // [const_num, H]
+};
+
+// out[t] = sum_k w[t,k] * rows[idx[t*K+k]] (+ shared[t]); fp32, separate multiply and add, ascending k.  A negative
+// index (a pair that was dropped and is no special expert) contributes 0.
+template <typename T, bool kExtra>
 __global__ void __launch_bounds__(256) combine_kernel(const T* __restrict__ rows, const int32_t* __restrict__ expand_idx,
                                                       const float* __restrict__ weights, const T* __restrict__ shared,
-                                                      int64_t tokens, int K, int cols, T* __restrict__ out) {
-  extern __shared__ int s_meta[];  // [K] positions, [K] weights
+                                                      int64_t tokens, int K, int cols, T* __restrict__ out, const CombineExtra ex) {
+  extern __shared__ int s_meta[];  // [K] positions, [K] weights, [K] special kinds
   int* s_pos = s_meta;
   float* s_w = reinterpret_cast<float*>(s_meta + K);
+  int* s_kind = s_meta + 2 * K;    // -1: gathered row; else index among the special experts
   const int nchunk = cols >> 3;
+  const int specials = kExtra ? ex.zero_num + ex.copy_num + ex.const_num : 0;
   for (int64_t t = blockIdx.x; t < tokens; t += gridDim.x) {
+    if (kExtra && ex.mask != nullptr && ex.mask[t] == 0) {     // uniform over the CTA
+      for (int ch = threadIdx.x; ch < nchunk; ch += 256) *reinterpret_cast<uint4*>(out + t * cols + ch * 8) = make_uint4(0, 0, 0, 0);
+      continue;
+    }
     __syncthreads();
     for (int k = threadIdx.x; k < K; k += 256) {
       s_pos[k] = expand_idx[t * K + k];
       s_w[k] = weights[t * K + k];
+      if constexpr (kExtra) {
+        const int id = specials > 0 ? ex.expert_ids[t * K + k] : 0;
+        s_kind[k] = (specials > 0 && id >= ex.num_experts && id < ex.num_experts + specials) ? id - ex.num_experts : -1;
+      }
     }
     __syncthreads();
     for (int ch = threadIdx.x; ch < nchunk; ch += 256) {
@@ -520,7 +635,29 @@ __global__ void __launch_bounds__(256) combine_kernel(const T* __restrict__ rows
 #pragma unroll 4
       for (int k = 0; k < K; ++k) {
         float v[8];
-        Elem<T>::load8(rows + static_cast<int64_t>(s_pos[k]) * cols + ch * 8, v);
+        const int kind = kExtra ? s_kind[k] : -1;
+        if (kind < 0) {
+          if (s_pos[k] >= 0) {
+            Elem<T>::load8(rows + static_cast<int64_t>(s_pos[k]) * cols + ch * 8, v);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = 0.f;
+          }
+        } else if (kind < ex.zero_num) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = 0.f;
+        } else {
+          Elem<T>::load8(static_cast<const T*>(ex.ori_x) + t * cols + ch * 8, v);
+          if (kind >= ex.zero_num + ex.copy_num) {
+            const int64_t c = kind - ex.zero_num - ex.copy_num;
+            float a1[8], a2[8], cv[8];
+            Elem<T>::load8(static_cast<const T*>(ex.alpha_1) + c * cols + ch * 8, a1);
+            Elem<T>::load8(static_cast<const T*>(ex.alpha_2) + c * cols + ch * 8, a2);
+            Elem<T>::load8(static_cast<const T*>(ex.const_v) + c * cols + ch * 8, cv);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = __fadd_rn(__fmul_rn(a1[i], v[i]), __fmul_rn(a2[i], cv[i]));
+          }
+        }
         const float w = s_w[k];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -555,7 +692,7 @@ using namespace tab;
 extern "C" int tab_moe_init_routing_workspace_bytes(int64_t T, int64_t K, int64_t expert_bound, size_t* bytes) {
   if (!bytes || T < 0 || K <= 0 || expert_bound <= 0 || expert_bound > kMaxExperts)
     return fail(TAB_ERR_BAD_ARG, "init_routing: T=%lld K=%lld expert_bound=%lld (bound must be in [1, %d])", (long long)T, (long long)K, (long long)expert_bound, kMaxExperts);
-  *bytes = sort_scratch_bytes(T * K, expert_bound, false);
+  *bytes = sort_scratch_bytes(T * K, expert_bound + 1, false);
   return TAB_OK;
 }
 
@@ -578,8 +715,9 @@ extern "C" int tab_moe_init_routing(const void* x, int x_dtype, const int32_t* r
   if ((H * es) % 16 != 0 || !aligned16(x) || !aligned16(expanded_x) || !aligned16(workspace))
     return fail(TAB_ERR_ALIGNMENT, "init_routing: rows must be 16-byte multiples and pointers 16-byte aligned");
   cudaStream_t st = as_stream(stream);
-  SortScratch s = carve(workspace, n, expert_bound, false);
-  rc = run_sort(expert_idx, row_idx, n, expert_bound, s, expanded_expert_idx, expanded_row_idx, nullptr, st);
+  SortScratch s = carve(workspace, n, expert_bound + 1, false);
+  const PairFilter pf = {nullptr, (int)K, 0, (int)expert_bound, 0};
+  rc = run_sort(expert_idx, row_idx, n, pf, s, expanded_expert_idx, expanded_row_idx, nullptr, st);
   if (rc != TAB_OK) return rc;
   const int64_t out_rows = (T < active_num ? T : active_num) * K;
   if (out_rows > 0) {
@@ -605,23 +743,28 @@ extern "C" int tab_moe_init_routing(const void* x, int x_dtype, const int32_t* r
 extern "C" int tab_moe_dispatch_pack_workspace_bytes(int64_t T, int64_t K, int64_t num_experts, size_t* bytes) {
   if (!bytes || T < 0 || K <= 0 || num_experts <= 0 || num_experts > kMaxExperts)
     return fail(TAB_ERR_BAD_ARG, "dispatch_pack: T=%lld K=%lld experts=%lld (experts must be in [1, %d])", (long long)T, (long long)K, (long long)num_experts, kMaxExperts);
-  *bytes = sort_scratch_bytes(T * K, num_experts, true);
+  *bytes = sort_scratch_bytes(T * K, num_experts + 1, true);
   return TAB_OK;
 }
 
-extern "C" int tab_moe_dispatch_pack(const void* x, int x_dtype, const int32_t* expert_ids, int64_t T, int64_t K,
-                                     int64_t H, int64_t num_experts, int quant_mode, void* send_rows,
-                                     float* send_scales, int32_t* expand_idx, int32_t* expert_counts,
-                                     int64_t* expert_token_nums, int nums_type, void* workspace, size_t workspace_bytes,
-                                     tab_stream_t stream) {
+extern "C" int tab_moe_dispatch_pack_ex(const void* x, int x_dtype, const int32_t* expert_ids, int64_t T, int64_t K, int64_t H,
+                                        int64_t expert_lo, int64_t expert_hi, int drop_outside, const uint8_t* x_active_mask,
+                                        const float* smooth, int64_t smooth_rows, const float* passthrough_scale, int64_t pos_limit,
+                                        int quant_mode, void* send_rows, float* send_scales, int32_t* expand_idx,
+                                        int32_t* expert_counts, int64_t* expert_token_nums, int nums_type, void* workspace,
+                                        size_t workspace_bytes, tab_stream_t stream) {
+  const int64_t num_experts = expert_hi - expert_lo;
+  if (expert_lo < 0 || num_experts <= 0) return fail(TAB_ERR_BAD_ARG, "dispatch_pack: expert range [%lld, %lld)", (long long)expert_lo, (long long)expert_hi);
   size_t need = 0;
   int rc = tab_moe_dispatch_pack_workspace_bytes(T, K, num_experts, &need);
   if (rc != TAB_OK) return rc;
   if (quant_mode != 0 && quant_mode != 2) return fail(TAB_ERR_UNSUPPORTED, "dispatch_pack: quant_mode %d (want 0 or 2)", quant_mode);
-  const int es = elem_size(x_dtype);
   if (x_dtype != TAB_BF16 && x_dtype != TAB_F16) return fail(TAB_ERR_UNSUPPORTED, "dispatch_pack: x dtype %d (want 5 or 15)", x_dtype);
   if (!expert_counts) return fail(TAB_ERR_BAD_ARG, "dispatch_pack: null pointer");
   if (nums_type != 0 && nums_type != 1) return fail(TAB_ERR_BAD_ARG, "dispatch_pack: nums_type %d", nums_type);
+  if (smooth && (quant_mode != 2 || (smooth_rows != 1 && smooth_rows != num_experts) || !aligned16(smooth)))
+    return fail(TAB_ERR_BAD_ARG, "dispatch_pack: smooth scales need quant_mode 2, 1 or %lld rows (got %lld) and 16-byte alignment", (long long)num_experts, (long long)smooth_rows);
+  if (passthrough_scale && quant_mode != 0) return fail(TAB_ERR_BAD_ARG, "dispatch_pack: a pass-through scale needs quant_mode 0");
   cudaStream_t st = as_stream(stream);
   const int64_t n = T * K;
   if (n == 0) {
@@ -635,23 +778,40 @@ extern "C" int tab_moe_dispatch_pack(const void* x, int x_dtype, const int32_t* 
   if (workspace_bytes < need) return fail(TAB_ERR_WORKSPACE, "dispatch_pack: workspace %zu < %zu bytes", workspace_bytes, need);
   if (H <= 0 || H % 16 != 0 || !aligned16(x) || !aligned16(send_rows) || !aligned16(workspace))
     return fail(TAB_ERR_ALIGNMENT, "dispatch_pack: H=%lld must be a multiple of 16 and pointers 16-byte aligned", (long long)H);
-  (void)es;
-  SortScratch s = carve(workspace, n, num_experts, true);
+  SortScratch s = carve(workspace, n, num_experts + 1, true);
+  PackArgs a = {};
+  a.expand_idx = expand_idx;
+  a.tokens = T; a.K = (int)K; a.cols = (int)H;
+  a.send_rows = send_rows; a.send_scales = send_scales;
+  a.counts = expert_counts; a.nums64 = expert_token_nums;
+  a.num_experts = (int)num_experts; a.nums_type = nums_type;
+  a.expert_ids = expert_ids;
+  a.sorted_src = s.sorted_src;
+  a.smooth = smooth; a.smooth_rows = (int)smooth_rows;
+  a.passthrough_scale = passthrough_scale;
+  a.pos_limit = pos_limit > 0 && pos_limit < 0x7fffffffLL ? (int)pos_limit : 0x7fffffff;
+  a.pf = PairFilter{x_active_mask, (int)K, (int)expert_lo, (int)expert_hi, drop_outside};
   if (n <= kSmallPairs) {
     // decode-sized batches: the sort runs inside the pack kernel, one launch in all
-    if (x_dtype == TAB_BF16)
-      launch_pack<__nv_bfloat16, true>(x, expand_idx, T, (int)K, (int)H, quant_mode, send_rows, send_scales, expert_counts, expert_token_nums, (int)num_experts, nums_type, expert_ids, s.sorted_src, st);
-    else
-      launch_pack<__half, true>(x, expand_idx, T, (int)K, (int)H, quant_mode, send_rows, send_scales, expert_counts, expert_token_nums, (int)num_experts, nums_type, expert_ids, s.sorted_src, st);
+    if (x_dtype == TAB_BF16) launch_pack<__nv_bfloat16, true>(x, a, quant_mode, st);
+    else launch_pack<__half, true>(x, a, quant_mode, st);
     return check_launch("dispatch_pack");
   }
-  rc = run_sort(expert_ids, nullptr, n, num_experts, s, s.sorted_expert, expand_idx, expert_counts, st);
+  rc = run_sort(expert_ids, nullptr, n, a.pf, s, s.sorted_expert, expand_idx, expert_counts, st);
   if (rc != TAB_OK) return rc;
-  if (x_dtype == TAB_BF16)
-    launch_pack<__nv_bfloat16, false>(x, expand_idx, T, (int)K, (int)H, quant_mode, send_rows, send_scales, expert_counts, expert_token_nums, (int)num_experts, nums_type, nullptr, nullptr, st);
-  else
-    launch_pack<__half, false>(x, expand_idx, T, (int)K, (int)H, quant_mode, send_rows, send_scales, expert_counts, expert_token_nums, (int)num_experts, nums_type, nullptr, nullptr, st);
+  if (x_dtype == TAB_BF16) launch_pack<__nv_bfloat16, false>(x, a, quant_mode, st);
+  else launch_pack<__half, false>(x, a, quant_mode, st);
   return check_launch("dispatch_pack");
+}
+
+extern "C" int tab_moe_dispatch_pack(const void* x, int x_dtype, const int32_t* expert_ids, int64_t T, int64_t K,
+                                     int64_t H, int64_t num_experts, int quant_mode, void* send_rows,
+                                     float* send_scales, int32_t* expand_idx, int32_t* expert_counts,
+                                     int64_t* expert_token_nums, int nums_type, void* workspace, size_t workspace_bytes,
+                                     tab_stream_t stream) {
+  return tab_moe_dispatch_pack_ex(x, x_dtype, expert_ids, T, K, H, 0, num_experts, 0, nullptr, nullptr, 0, nullptr, 0, quant_mode,
+                                  send_rows, send_scales, expand_idx, expert_counts, expert_token_nums, nums_type, workspace,
+                                  workspace_bytes, stream);
 }
 
 extern "C" int tab_moe_exchange_plan(const int32_t* recv_counts, int64_t R, int64_t E_l, int64_t slot_rows,
@@ -683,23 +843,47 @@ extern "C" int tab_moe_exchange_rows(const void* src, const float* src_scales, c
   return check_launch("exchange_rows");
 }
 
-extern "C" int tab_moe_combine(const void* rows, int dtype, const int32_t* expand_idx, const float* expert_scales,
-                               const void* shared, int64_t T, int64_t K, int64_t H, void* out, tab_stream_t stream) {
+extern "C" int tab_moe_combine_ex(const void* rows, int dtype, const int32_t* expand_idx, const float* expert_scales,
+                                  const void* shared, int64_t T, int64_t K, int64_t H, void* out, const uint8_t* x_active_mask,
+                                  const int32_t* expert_ids, int64_t num_experts, int64_t zero_expert_num, int64_t copy_expert_num,
+                                  int64_t const_expert_num, const void* ori_x, const void* const_expert_alpha_1,
+                                  const void* const_expert_alpha_2, const void* const_expert_v, tab_stream_t stream) {
   if (T < 0 || K <= 0 || K > 1024 || H <= 0) return fail(TAB_ERR_BAD_ARG, "combine: T=%lld K=%lld H=%lld", (long long)T, (long long)K, (long long)H);
   if (T == 0) return TAB_OK;
   if (!rows || !expand_idx || !expert_scales || !out) return fail(TAB_ERR_BAD_ARG, "combine: null pointer");
   if (H % 8 != 0 || !aligned16(rows) || !aligned16(out) || (shared && !aligned16(shared)))
     return fail(TAB_ERR_ALIGNMENT, "combine: H=%lld must be a multiple of 8 and pointers 16-byte aligned", (long long)H);
+  if (zero_expert_num < 0 || copy_expert_num < 0 || const_expert_num < 0) return fail(TAB_ERR_BAD_ARG, "combine: negative special expert count");
+  const int64_t specials = zero_expert_num + copy_expert_num + const_expert_num;
+  if (specials > 0 && (!expert_ids || num_experts <= 0)) return fail(TAB_ERR_BAD_ARG, "combine: special experts need expert_ids and the number of routed experts");
+  if (copy_expert_num + const_expert_num > 0 && (!ori_x || !aligned16(ori_x))) return fail(TAB_ERR_BAD_ARG, "combine: copy and constant experts need ori_x (16-byte aligned)");
+  if (const_expert_num > 0 && (!const_expert_alpha_1 || !const_expert_alpha_2 || !const_expert_v || !aligned16(const_expert_alpha_1) ||
+                               !aligned16(const_expert_alpha_2) || !aligned16(const_expert_v)))
+    return fail(TAB_ERR_BAD_ARG, "combine: constant experts need alpha_1, alpha_2 and v (16-byte aligned)");
   cudaStream_t st = as_stream(stream);
   const int grid = grid_for(T, 8);
-  const size_t smem = static_cast<size_t>(K) * 8;
-  if (dtype == TAB_BF16)
-    combine_kernel<__nv_bfloat16><<<grid, 256, smem, st>>>(static_cast<const __nv_bfloat16*>(rows), expand_idx, expert_scales, static_cast<const __nv_bfloat16*>(shared), T, (int)K, (int)H, static_cast<__nv_bfloat16*>(out));
-  else if (dtype == TAB_F16)
-    combine_kernel<__half><<<grid, 256, smem, st>>>(static_cast<const __half*>(rows), expand_idx, expert_scales, static_cast<const __half*>(shared), T, (int)K, (int)H, static_cast<__half*>(out));
-  else
+  const size_t smem = static_cast<size_t>(K) * 12;
+  const bool extra = x_active_mask != nullptr || specials > 0;
+  const CombineExtra ex = {x_active_mask, expert_ids, (int)num_experts, (int)zero_expert_num, (int)copy_expert_num, (int)const_expert_num,
+                           ori_x, const_expert_alpha_1, const_expert_alpha_2, const_expert_v};
+#define TAB_COMBINE(TYPE, EX)                                                                                                   \
+  combine_kernel<TYPE, EX><<<grid, 256, smem, st>>>(static_cast<const TYPE*>(rows), expand_idx, expert_scales,                  \
+                                                    static_cast<const TYPE*>(shared), T, (int)K, (int)H, static_cast<TYPE*>(out), ex)
+  if (dtype == TAB_BF16) {
+    if (extra) TAB_COMBINE(__nv_bfloat16, true); else TAB_COMBINE(__nv_bfloat16, false);
+  } else if (dtype == TAB_F16) {
+    if (extra) TAB_COMBINE(__half, true); else TAB_COMBINE(__half, false);
+  } else {
     return fail(TAB_ERR_UNSUPPORTED, "combine: dtype %d (want 5 or 15)", dtype);
+  }
+#undef TAB_COMBINE
   return check_launch("combine");
+}
+
+extern "C" int tab_moe_combine(const void* rows, int dtype, const int32_t* expand_idx, const float* expert_scales,
+                               const void* shared, int64_t T, int64_t K, int64_t H, void* out, tab_stream_t stream) {
+  return tab_moe_combine_ex(rows, dtype, expand_idx, expert_scales, shared, T, K, H, out, nullptr, nullptr, 0, 0, 0, 0, nullptr,
+                            nullptr, nullptr, nullptr, stream);
 }
 
 extern "C" int tab_routing_status(int* status_host, tab_stream_t stream) {
@@ -727,7 +911,7 @@ namespace tab {
 constexpr int64_t kStaticMaxPairs = 32768;    // T*K
 constexpr int64_t kStaticMaxExperts = 512;    // expert_bound
 constexpr size_t kStaticScratchBytes = 256 * 1024;
-static_assert(((kStaticMaxPairs / kChunk) * kStaticMaxExperts + kStaticMaxExperts + 4 + kStaticMaxPairs) * 4 + 256 <=
+static_assert(((kStaticMaxPairs / kChunk) * (kStaticMaxExperts + 1) + (kStaticMaxExperts + 1) + 4 + kStaticMaxPairs) * 4 + 256 <=
                   kStaticScratchBytes, "static routing scratch must hold the largest accepted problem");
 
 // One copy per GPU that loads the library, resident until the process exits.
@@ -799,7 +983,8 @@ __global__ void __launch_bounds__(256) compute_expert_tokens_kernel(const int32_
 // row_idx int32 [T, k] with row_idx[t, j] = j*T + t.
 constexpr int kGateMaxPerLane = 32;
 template <typename T>
-__global__ void __launch_bounds__(128) gating_topk_softmax_kernel(const T* __restrict__ x, int64_t tokens, int E, int k,
+__global__ void __launch_bounds__(128) gating_topk_softmax_kernel(const T* __restrict__ x, const uint8_t* __restrict__ finished,
+                                                                  int64_t tokens, int E, int k,
                                                                   T* __restrict__ y, int32_t* __restrict__ expert_idx,
                                                                   int32_t* __restrict__ row_idx) {
   const int lane = threadIdx.x & 31;
@@ -851,7 +1036,7 @@ __global__ void __launch_bounds__(128) gating_topk_softmax_kernel(const T* __res
       }
       if (lane == 0) {
         y[t * k + j] = Elem<T>::from_f32(best);
-        expert_idx[t * k + j] = best_e;
+        expert_idx[t * k + j] = (finished != nullptr && finished[t] != 0) ? E : best_e;   // a finished row points past the experts
         row_idx[t * k + j] = static_cast<int32_t>(j * tokens + t);
       }
     }
@@ -923,17 +1108,17 @@ extern "C" int tab_moe_compute_expert_tokens(const int32_t* sorted_experts, int6
   return check_launch("compute_expert_tokens");
 }
 
-extern "C" int tab_moe_gating_top_k_softmax(const void* x, int dtype, int64_t tokens, int64_t num_experts, int64_t k, void* y,
-                                            int32_t* expert_idx, int32_t* row_idx, tab_stream_t stream) {
+extern "C" int tab_moe_gating_top_k_softmax(const void* x, int dtype, const uint8_t* finished, int64_t tokens, int64_t num_experts,
+                                            int64_t k, void* y, int32_t* expert_idx, int32_t* row_idx, tab_stream_t stream) {
   if (tokens < 0 || num_experts <= 0 || k <= 0 || k > num_experts) return fail(TAB_ERR_BAD_ARG, "gating_top_k_softmax: tokens=%lld experts=%lld k=%lld", (long long)tokens, (long long)num_experts, (long long)k);
   if (num_experts > 32 * kGateMaxPerLane) return fail(TAB_ERR_UNSUPPORTED, "gating_top_k_softmax: more than %d experts", 32 * kGateMaxPerLane);
   if (tokens == 0) return TAB_OK;
   if (!x || !y || !expert_idx || !row_idx) return fail(TAB_ERR_BAD_ARG, "gating_top_k_softmax: null pointer");
   const int grid = grid_for((tokens + 3) / 4, 8);
   cudaStream_t st = as_stream(stream);
-  if (dtype == TAB_F32) gating_topk_softmax_kernel<float><<<grid, 128, 0, st>>>(static_cast<const float*>(x), tokens, (int)num_experts, (int)k, static_cast<float*>(y), expert_idx, row_idx);
-  else if (dtype == TAB_BF16) gating_topk_softmax_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(x), tokens, (int)num_experts, (int)k, static_cast<__nv_bfloat16*>(y), expert_idx, row_idx);
-  else if (dtype == TAB_F16) gating_topk_softmax_kernel<__half><<<grid, 128, 0, st>>>(static_cast<const __half*>(x), tokens, (int)num_experts, (int)k, static_cast<__half*>(y), expert_idx, row_idx);
+  if (dtype == TAB_F32) gating_topk_softmax_kernel<float><<<grid, 128, 0, st>>>(static_cast<const float*>(x), finished, tokens, (int)num_experts, (int)k, static_cast<float*>(y), expert_idx, row_idx);
+  else if (dtype == TAB_BF16) gating_topk_softmax_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(x), finished, tokens, (int)num_experts, (int)k, static_cast<__nv_bfloat16*>(y), expert_idx, row_idx);
+  else if (dtype == TAB_F16) gating_topk_softmax_kernel<__half><<<grid, 128, 0, st>>>(static_cast<const __half*>(x), finished, tokens, (int)num_experts, (int)k, static_cast<__half*>(y), expert_idx, row_idx);
   else return fail(TAB_ERR_UNSUPPORTED, "gating_top_k_softmax: dtype %d (want 5, 6 or 15)", dtype);
   return check_launch("gating_top_k_softmax");
 }
@@ -961,12 +1146,14 @@ extern "C" int tab_moe_finalize_routing(const void* rows, int dtype, const void*
 }
 
 extern "C" int tab_moe_init_routing_v2(const void* x, int x_dtype, const int32_t* expert_idx, int64_t T, int64_t K, int64_t H,
-                                       int64_t expert_num, int quant_mode, int tokens_num_type, int row_idx_type, void* expanded_x,
+                                       int64_t expert_lo, int64_t expert_hi, int quant_mode, int tokens_num_type, int row_idx_type,
+                                       int64_t active_rows, const float* scale, int64_t scale_rows, void* expanded_x,
                                        int32_t* expanded_row_idx, int64_t* expert_tokens, float* expanded_scale, void* workspace,
                                        size_t workspace_bytes, tab_stream_t stream) {
   // Sort + (quantise or copy) + scatter are the dispatch sender's steps; this entry point adds the v2 outputs.
   if (quant_mode != -1 && quant_mode != 1) return fail(TAB_ERR_UNSUPPORTED, "init_routing_v2: quant_mode %d (want -1 or 1)", quant_mode);
   if ((tokens_num_type != 0 && tokens_num_type != 1) || (row_idx_type != 0 && row_idx_type != 1)) return fail(TAB_ERR_BAD_ARG, "init_routing_v2: bad type flag");
+  const int64_t expert_num = expert_hi - expert_lo;
   size_t need = 0;
   int rc = tab_moe_dispatch_pack_workspace_bytes(T, K, expert_num, &need);
   if (rc != TAB_OK) return rc;
@@ -974,18 +1161,22 @@ extern "C" int tab_moe_init_routing_v2(const void* x, int x_dtype, const int32_t
   const size_t extra = static_cast<size_t>((n + expert_num) * 4 + 512);
   if (!workspace || workspace_bytes < need + extra) return fail(TAB_ERR_WORKSPACE, "init_routing_v2: workspace %zu < %zu bytes", workspace_bytes, need + extra);
   if (!expanded_row_idx || !expert_tokens || !expanded_scale) return fail(TAB_ERR_BAD_ARG, "init_routing_v2: null pointer");
+  if (scale && quant_mode == -1 && scale_rows != T) return fail(TAB_ERR_BAD_ARG, "init_routing_v2: without quantisation `scale` holds one value per token");
   uint8_t* wsb = static_cast<uint8_t*>(workspace);
   int32_t* scatter_idx = reinterpret_cast<int32_t*>(wsb + need);               // f -> position
   int32_t* counts = scatter_idx + ((n + 63) / 64) * 64;
   int32_t* idx_out = row_idx_type == 1 ? expanded_row_idx : scatter_idx;
   // the pack kernel also writes the rows per expert as int64 counts or their running total
-  rc = tab_moe_dispatch_pack(x, x_dtype, expert_idx, T, K, H, expert_num, quant_mode == 1 ? 2 : 0, expanded_x, expanded_scale, idx_out,
-                             counts, expert_tokens, tokens_num_type, workspace, need, stream);
+  rc = tab_moe_dispatch_pack_ex(x, x_dtype, expert_idx, T, K, H, expert_lo, expert_hi, /*drop_outside=*/1, nullptr,
+                                quant_mode == 1 ? scale : nullptr, quant_mode == 1 ? scale_rows : 0,
+                                quant_mode == -1 ? scale : nullptr, active_rows, quant_mode == 1 ? 2 : 0, expanded_x, expanded_scale,
+                                idx_out, counts, expert_tokens, tokens_num_type, workspace, need, stream);
   if (rc != TAB_OK) return rc;
   cudaStream_t st = as_stream(stream);
   if (row_idx_type == 0 && n > 0) {
-    // gather form: position -> source pair index, kept by the sort in its scratch (SortScratch::sorted_src)
-    SortScratch s = carve(workspace, n, expert_num, true);
+    // gather form: position -> source pair index, kept by the sort in its scratch (SortScratch::sorted_src); the pairs
+    // of experts outside the range come after the kept ones
+    SortScratch s = carve(workspace, n, expert_num + 1, true);
     cudaError_t e = cudaMemcpyAsync(expanded_row_idx, s.sorted_src, n * sizeof(int32_t), cudaMemcpyDeviceToDevice, st);
     if (e != cudaSuccess) return fail(TAB_ERR_CUDA, "init_routing_v2: copy: %s", cudaGetErrorString(e));
   }
@@ -1009,7 +1200,8 @@ __device__ __forceinline__ void warp_argmax(float& v, int& idx) {
 
 // One warp per token; E <= 1024 scores, 32 per lane (element e = i*32 + lane); group_count <= 32 contiguous groups.
 template <typename T>
-__global__ void __launch_bounds__(128) gating_topk_kernel(const T* __restrict__ x, const T* __restrict__ bias, int64_t tokens, int E,
+__global__ void __launch_bounds__(128) gating_topk_kernel(const T* __restrict__ x, const T* __restrict__ bias,
+                                                          const uint8_t* __restrict__ finished, int64_t tokens, int E,
                                                           int k, int k_group, int group_count, int group_select_mode, int norm_type,
                                                           float scaling, float eps, T* __restrict__ y, int32_t* __restrict__ expert_idx,
                                                           float* __restrict__ out) {
@@ -1134,14 +1326,15 @@ __global__ void __launch_bounds__(128) gating_topk_kernel(const T* __restrict__ 
       if (norm_type != 0) v = __fdiv_rn(v, __fadd_rn(ysum, eps));   // sigmoid scores, or softmax renormalised over the k
       v = __fmul_rn(v, scaling);
       y[t * k + lane] = Elem<T>::from_f32(v);
-      expert_idx[t * k + lane] = mine_e;
+      expert_idx[t * k + lane] = (finished != nullptr && finished[t] != 0) ? E : mine_e;
     }
   }
 }
 
 }  // namespace tab
 
-extern "C" int tab_moe_gating_top_k(const void* x, const void* bias, int dtype, int64_t tokens, int64_t num_experts, int64_t k,
+extern "C" int tab_moe_gating_top_k(const void* x, const void* bias, const uint8_t* finished, int dtype, int64_t tokens,
+                                    int64_t num_experts, int64_t k,
                                     int64_t k_group, int64_t group_count, int group_select_mode, int norm_type,
                                     float routed_scaling_factor, float eps, void* y, int32_t* expert_idx, float* out,
                                     tab_stream_t stream) {
@@ -1159,7 +1352,7 @@ extern "C" int tab_moe_gating_top_k(const void* x, const void* bias, int dtype, 
   const int grid = grid_for((tokens + 3) / 4, 8);
   cudaStream_t st = as_stream(stream);
 #define TAB_GATE_LAUNCH(TYPE)                                                                                                     \
-  gating_topk_kernel<TYPE><<<grid, 128, 0, st>>>(static_cast<const TYPE*>(x), static_cast<const TYPE*>(bias), tokens, (int)num_experts, \
+  gating_topk_kernel<TYPE><<<grid, 128, 0, st>>>(static_cast<const TYPE*>(x), static_cast<const TYPE*>(bias), finished, tokens, (int)num_experts, \
                                                  (int)k, (int)k_group, (int)group_count, group_select_mode, norm_type,           \
                                                  routed_scaling_factor, eps, static_cast<TYPE*>(y), expert_idx, out)
   if (dtype == TAB_F32) TAB_GATE_LAUNCH(float);

@@ -73,9 +73,15 @@ def get_ep_group(name: str):
                        "torchair_b200.register_ep_group(name, process_group) first")
 
 
-def dispatch_rows(T: int, R: int, E: int, K: int) -> int:
-    """Static row count of expand_x (global_bs == 0): every rank may send min(E/R, K) copies of each token."""
-    return T * R * min(E // R, K)
+def slot_tokens(T: int, R: int, global_bs: int) -> int:
+    """Tokens a rank may hold: T when global_bs == 0 (every rank holds the same number), else global_bs / R (decision:
+    global_bs is R times the largest per-rank batch, so that ranks may hold different numbers of tokens up to that)."""
+    return T if not global_bs else global_bs // R
+
+
+def dispatch_rows(T: int, R: int, E: int, K: int, global_bs: int = 0) -> int:
+    """Static row count of expand_x: every rank may send min(E/R, K) copies of each of its (at most) slot_tokens tokens."""
+    return slot_tokens(T, R, global_bs) * R * min(E // R, K)
 
 
 def check_dispatch_args(x, expert_ids, R, rank, E, scales, x_active_mask, tp_world_size, expert_shard_type,
@@ -85,16 +91,21 @@ def check_dispatch_args(x, expert_ids, R, rank, E, scales, x_active_mask, tp_wor
         raise RuntimeError(f"{op}: x must be [T, H] and expert_ids [T, K]")
     if R < 1 or E < 1 or E % R != 0 or not (0 <= rank < R):
         raise RuntimeError(f"{op}: ep_world_size={R}, ep_rank_id={rank}, moe_expert_num={E} are inconsistent")
-    if scales is not None or x_active_mask is not None:
-        raise NotImplementedError(f"{op}: `scales` and `x_active_mask` are outside the W8A8 MoE path")
+    if scales is not None:
+        if quant_mode != 2:
+            raise RuntimeError(f"{op}: `scales` (smooth scales) need quant_mode 2")
+        if scales.dtype != torch.float32 or scales.dim() != 2 or scales.shape[1] != x.shape[1] or scales.shape[0] not in (1, E):
+            raise RuntimeError(f"{op}: scales must be float32 [{E}, {x.shape[1]}] (one row per expert) or [1, {x.shape[1]}]")
+    if x_active_mask is not None and (x_active_mask.dtype != torch.bool or x_active_mask.shape != (x.shape[0],)):
+        raise RuntimeError(f"{op}: x_active_mask must be bool [T]")
+    if global_bs < 0 or (global_bs and (global_bs % R != 0 or global_bs // R < x.shape[0])):
+        raise RuntimeError(f"{op}: global_bs={global_bs} must be a multiple of ep_world_size and at least ep_world_size * T")
     if tp_world_size not in (0, 1):
         raise NotImplementedError(f"{op}: tensor parallelism inside an expert (tp_world_size={tp_world_size}) is not sharded here")
     if expert_shard_type != 0 or shared_expert_rank_num != 0:
         raise NotImplementedError(f"{op}: shared-expert ranks / expert_shard_type != 0 are not sharded here")
     if quant_mode not in (0, 2):
         raise NotImplementedError(f"{op}: quant_mode must be 0 (none) or 2 (per-token dynamic int8)")
-    if global_bs != 0:
-        raise NotImplementedError(f"{op}: global_bs must be 0 (every rank holds the same number of tokens)")
     if nums_type not in (0, 1):
         raise RuntimeError(f"{op}: expert_token_nums_type must be 0 (cumsum) or 1 (counts)")
 
@@ -107,12 +118,16 @@ def check_combine_args(expand_x, expert_ids, expert_scales, R, rank, E, x_active
         raise RuntimeError(f"{op}: expand_x must be [A, H]; expert_ids and expert_scales [T, K]")
     if R < 1 or E < 1 or E % R != 0 or not (0 <= rank < R):
         raise RuntimeError(f"{op}: ep_world_size={R}, ep_rank_id={rank}, moe_expert_num={E} are inconsistent")
-    if x_active_mask is not None or activation_scale is not None or weight_scale is not None or group_list is not None:
-        raise NotImplementedError(f"{op}: x_active_mask / dequant-in-combine arguments are outside the W8A8 MoE path")
+    if activation_scale is not None or weight_scale is not None or group_list is not None:
+        raise NotImplementedError(f"{op}: the dequant-in-combine arguments (int32 expand_x) are outside the W8A8 MoE path")
+    if x_active_mask is not None and (x_active_mask.dtype != torch.bool or x_active_mask.shape != (expert_ids.shape[0],)):
+        raise RuntimeError(f"{op}: x_active_mask must be bool [T]")
     if tp_world_size not in (0, 1) or expert_shard_type != 0 or shared_expert_rank_num != 0:
         raise NotImplementedError(f"{op}: tensor-parallel / shared-expert-rank sharding is not supported")
-    if global_bs != 0 or comm_quant_mode != 0 or out_dtype != 0:
-        raise NotImplementedError(f"{op}: global_bs, comm_quant_mode and out_dtype must be 0")
+    if global_bs < 0 or (global_bs and (global_bs % R != 0 or global_bs // R < expert_ids.shape[0])):
+        raise RuntimeError(f"{op}: global_bs={global_bs} must be a multiple of ep_world_size and at least ep_world_size * T")
+    if comm_quant_mode != 0 or out_dtype != 0:
+        raise NotImplementedError(f"{op}: comm_quant_mode and out_dtype must be 0")
 
 
 def _ptr(t):
@@ -127,7 +142,9 @@ class CudaKernels:
     """The shipped provider: every step is one or more sm_100a kernels behind the C ABI."""
 
     @staticmethod
-    def dispatch_pack(x, expert_ids, E, quant_mode, nums_type=None):
+    def dispatch_pack(x, expert_ids, E, quant_mode, nums_type=None, mask=None, scales=None, special=0):
+        """Sort + quantise + scatter of this rank's copies.  mask: bool [T] (False = the token sends nothing); scales: fp32
+        smooth scales [E, H] or [1, H]; special > 0: expert ids >= E are special experts that are not sent."""
         if not x.is_cuda:
             raise RuntimeError("torchair_b200 kernels need CUDA tensors; there is no CPU implementation")
         if expert_ids.dtype != torch.int32:
@@ -139,15 +156,18 @@ class CudaKernels:
         H = x.shape[1]
         dev = x.device
         rows = torch.empty((T * K, H), dtype=torch.int8 if quant_mode == 2 else x.dtype, device=dev)
-        scales = torch.empty((T * K,), dtype=torch.float32, device=dev)
+        out_scales = torch.empty((T * K,), dtype=torch.float32, device=dev)
         expand_idx = torch.empty((T * K,), dtype=torch.int32, device=dev)
         counts = torch.empty((E,), dtype=torch.int32, device=dev)
         nums = None if nums_type is None else torch.empty((E,), dtype=torch.int64, device=dev)   # counts / running total
         nbytes = _lib.workspace_bytes("tab_moe_dispatch_pack_workspace_bytes", T, K, E)
         ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=dev)
-        _lib.call("tab_moe_dispatch_pack", _ptr(x), _ST_INV[x.dtype], _ptr(expert_ids), T, K, H, E, quant_mode, _ptr(rows),
-                  _ptr(scales), _ptr(expand_idx), _ptr(counts), _ptr(nums), int(nums_type or 0), _ptr(ws), ws.numel(), _stream(x))
-        return rows, scales, expand_idx, counts, nums
+        mask = None if mask is None else mask.contiguous()
+        scales = None if scales is None else scales.contiguous()
+        _lib.call("tab_moe_dispatch_pack_ex", _ptr(x), _ST_INV[x.dtype], _ptr(expert_ids), T, K, H, 0, E, int(special > 0), _ptr(mask),
+                  _ptr(scales), 0 if scales is None else scales.shape[0], None, 0, quant_mode, _ptr(rows), _ptr(out_scales),
+                  _ptr(expand_idx), _ptr(counts), _ptr(nums), int(nums_type or 0), _ptr(ws), ws.numel(), _stream(x))
+        return rows, out_scales, expand_idx, counts, nums
 
     @staticmethod
     def exchange_plan(recv_counts, R, E_l, slot_rows, nums_type):
@@ -170,7 +190,8 @@ class CudaKernels:
         return dst, dst_scales
 
     @staticmethod
-    def combine(rows, expand_idx, expert_scales, shared, T, K):
+    def combine(rows, expand_idx, expert_scales, shared, T, K, mask=None, special=None):
+        """special: None, or a dict with expert_ids [T, K], E, zero, copy, const, ori_x, alpha_1, alpha_2, const_v."""
         if rows.dtype not in (torch.bfloat16, torch.float16):
             raise NotImplementedError("npu_moe_distribute_combine: expand_x must be bfloat16 or float16")
         rows = rows.contiguous()
@@ -181,8 +202,18 @@ class CudaKernels:
             if shared.dtype != rows.dtype or shared.shape != out.shape:
                 raise RuntimeError("npu_moe_distribute_combine: shared_expert_x must match the output")
             shared = shared.contiguous()
-        _lib.call("tab_moe_combine", _ptr(rows), _ST_INV[rows.dtype], _ptr(expand_idx.contiguous()),
-                  _ptr(expert_scales.contiguous()), _ptr(shared), T, K, rows.shape[1], _ptr(out), _stream(rows))
+        if mask is None and special is None:
+            _lib.call("tab_moe_combine", _ptr(rows), _ST_INV[rows.dtype], _ptr(expand_idx.contiguous()),
+                      _ptr(expert_scales.contiguous()), _ptr(shared), T, K, rows.shape[1], _ptr(out), _stream(rows))
+            return out
+        sp = special or {}
+        c = lambda t: None if t is None else t.to(rows.dtype).contiguous()
+        ids = sp.get("expert_ids")
+        _lib.call("tab_moe_combine_ex", _ptr(rows), _ST_INV[rows.dtype], _ptr(expand_idx.contiguous()), _ptr(expert_scales.contiguous()),
+                  _ptr(shared), T, K, rows.shape[1], _ptr(out), _ptr(None if mask is None else mask.contiguous()),
+                  _ptr(None if ids is None else ids.contiguous()), int(sp.get("E", 0)), int(sp.get("zero", 0)), int(sp.get("copy", 0)),
+                  int(sp.get("const", 0)), _ptr(c(sp.get("ori_x"))), _ptr(c(sp.get("alpha_1"))), _ptr(c(sp.get("alpha_2"))),
+                  _ptr(c(sp.get("const_v"))), _stream(rows))
         return out
 
 
@@ -276,14 +307,14 @@ def peer_status() -> int:
     return 0
 
 
-def _dispatch_peer(kern, x, expert_ids, group_ep, pg, R, rank, E, quant_mode, nums_type, send, tp_recv, expand_scales):
+def _dispatch_peer(kern, x, expert_ids, group_ep, pg, R, rank, E, quant_mode, nums_type, send, tp_recv, expand_scales, t_slot):
     send_rows, send_scales, expand_idx, counts = send[:4]
     T, K = expert_ids.shape
     H = x.shape[1]
     E_l = E // R
     dev = x.device
     row_bytes = H * send_rows.element_size()
-    px = peer_exchange(group_ep, pg, R, rank, T, K, H, E, row_bytes, dev)
+    px = peer_exchange(group_ep, pg, R, rank, t_slot, K, H, E, row_bytes, dev)
     _last_dispatch[(group_ep, R, rank, T, K, H, E, dev.index)] = px     # the matching combine returns through the same buffers
     A = R * px.C
     st = px._stream()
@@ -305,7 +336,8 @@ def _dispatch_peer(kern, x, expert_ids, group_ep, pg, R, rank, E, quant_mode, nu
     return expand_x, dyn, slot_idx, nums, ep_recv, tp_recv, expand_scales
 
 
-def _combine_peer(kern, expand_x, expert_ids, expand_idx, ep_send_counts, expert_scales, group_ep, pg, R, rank, E, shared):
+def _combine_peer(kern, expand_x, expert_ids, expand_idx, ep_send_counts, expert_scales, group_ep, pg, R, rank, E, shared,
+                  mask=None, special=None):
     T, K = expert_ids.shape
     H = expand_x.shape[1]
     E_l = E // R
@@ -323,14 +355,14 @@ def _combine_peer(kern, expand_x, expert_ids, expand_idx, ep_send_counts, expert
     px.signal(px.KIND_DATA_C)
     px.wait(px.KIND_DATA_C, 1)
     back = px.ret_local.view(expand_x.dtype).view(R * px.C, H)
-    out = kern.combine(back, expand_idx, expert_scales, shared, T, K)
+    out = kern.combine(back, expand_idx, expert_scales, shared, T, K, mask, special)
     px.signal(px.KIND_ACK_C)
     counters["wire_bytes_sent"] += T * K * H * 2
     return out
 
 
 def combine_from_producer(kern, produce_rows, rows, H, dtype, expert_ids, expand_idx, ep_send_counts, expert_scales, group_ep,
-                          R, rank, E, shared=None):
+                          R, rank, E, shared=None, mask=None, special=None):
     """Combine whose expert-output rows are stored into the source ranks' return buffers by their producer.
 
     Peer transport only.  ``produce_rows(row_dst)`` must enqueue, on the current stream, work that stores output row i
@@ -356,7 +388,7 @@ def combine_from_producer(kern, produce_rows, rows, H, dtype, expert_ids, expand
     produce_rows(row_dst)
     px.signal_wait(px.KIND_DATA_C)
     back = px.ret_local.view(dtype).view(R * px.C, H)
-    out = kern.combine(back, expand_idx, expert_scales, shared, T, K)
+    out = kern.combine(back, expand_idx, expert_scales, shared, T, K, mask, special)
     px.signal(px.KIND_ACK_C)
     counters["wire_bytes_sent"] += T * K * H * 2
     return out
@@ -385,26 +417,32 @@ def _zeros(shape, dtype, device) -> torch.Tensor:
     return t
 
 
-def dispatch(kern, x, expert_ids, group_ep, R, rank, E, quant_mode, nums_type, tp_slots=1):
+def dispatch(kern, x, expert_ids, group_ep, R, rank, E, quant_mode, nums_type, tp_slots=1, mask=None, scales=None, special=0,
+             global_bs=0):
     """Returns the seven outputs of npu_moe_distribute_dispatch.
 
     Rows of expand_x / dynamic_scales past the received total (sum of expert_token_nums) are not written: expand_x is
     sized for the worst case, and nothing downstream reads that tail.
     Handshake tensors (consumed only by combine): expand_idx[t*K+k] = position of that copy in this rank's
-    send order (sorted by global expert id, stable); ep_recv_count[e*R+s] = rows received for local expert e
-    from rank s; tp_recv_count and expand_scales are zero.
+    send order (sorted by global expert id, stable), -1 for a copy that is not sent; ep_recv_count[e*R+s] = rows received
+    for local expert e from rank s; tp_recv_count and expand_scales are zero.
+    mask (x_active_mask): tokens marked False send nothing; scales: smooth scales before the quantisation of each copy;
+    special > 0: ids >= E are special experts of the second-generation operator, evaluated by the combine, not sent;
+    global_bs: R times the largest per-rank batch when the ranks hold different numbers of tokens.
     """
     counters["dispatch_calls"] += 1
     T, K = expert_ids.shape
     H = x.shape[1]
     E_l = E // R
-    A = dispatch_rows(T, R, E, K)
+    t_slot = slot_tokens(T, R, global_bs)
+    A = dispatch_rows(T, R, E, K, global_bs)
     dev = x.device
-    send_rows, send_scales, expand_idx, counts, nums = kern.dispatch_pack(x, expert_ids, E, quant_mode, nums_type if R == 1 else None)
+    send_rows, send_scales, expand_idx, counts, nums = kern.dispatch_pack(x, expert_ids, E, quant_mode, nums_type if R == 1 else None,
+                                                                          mask, scales, special)
     tp_recv = _zeros((tp_slots,), torch.int32, dev)
     expand_scales = _zeros((A,), torch.float32, dev)
     if R == 1:
-        if A != T * K:  # K > E: cannot happen with distinct experts per token, kept for shape safety
+        if A != T * K:  # K > E or a larger slot: the static shape is padded
             pad_rows = torch.zeros((A, H), dtype=send_rows.dtype, device=dev)
             pad_rows[:T * K] = send_rows
             pad_scales = torch.zeros((A,), dtype=torch.float32, device=dev)
@@ -418,7 +456,7 @@ def dispatch(kern, x, expert_ids, group_ep, R, rank, E, quant_mode, nums_type, t
                            f"{dist.get_world_size(pg)}/{dist.get_rank(pg)}, arguments say {R}/{rank}")
     if transport_of(group_ep, x.is_cuda) == "peer":
         return _dispatch_peer(kern, x, expert_ids, group_ep, pg, R, rank, E, quant_mode, nums_type,
-                              (send_rows, send_scales, expand_idx, counts), tp_recv, expand_scales)
+                              (send_rows, send_scales, expand_idx, counts), tp_recv, expand_scales, t_slot)
     recv_counts = torch.empty_like(counts)                       # [R, E_l]: rows from rank s for my expert e
     dist.all_to_all_single(recv_counts, counts, group=pg)
     sums = torch.stack([counts.view(R, E_l).sum(1), recv_counts.view(R, E_l).sum(1)]).cpu()   # the one host read
@@ -430,8 +468,9 @@ def dispatch(kern, x, expert_ids, group_ep, R, rank, E, quant_mode, nums_type, t
                            "every rank must pass the same number of tokens when global_bs == 0")
     wire_rows = torch.empty((total, H), dtype=send_rows.dtype, device=dev)
     wire_scales = torch.empty((total,), dtype=torch.float32, device=dev)
-    dist.all_to_all_single(wire_rows, send_rows, recv_splits, send_splits, group=pg)
-    dist.all_to_all_single(wire_scales, send_scales, recv_splits, send_splits, group=pg)
+    sent = sum(send_splits)                                      # copies that were dropped have no row
+    dist.all_to_all_single(wire_rows, send_rows[:sent], recv_splits, send_splits, group=pg)
+    dist.all_to_all_single(wire_scales, send_scales[:sent], recv_splits, send_splits, group=pg)
     counters["wire_bytes_sent"] += (sum(send_splits) - send_splits[rank]) * (H * send_rows.element_size() + 4)
     plan, nums, ep_recv = kern.exchange_plan(recv_counts.view(R, E_l), R, E_l, 0, nums_type)
     expand_x, dyn_scales = kern.exchange_rows(wire_rows, wire_scales, plan, R, E_l, 0, 0, A, False)
@@ -439,23 +478,29 @@ def dispatch(kern, x, expert_ids, group_ep, R, rank, E, quant_mode, nums_type, t
     return expand_x, dyn_scales, expand_idx, nums, ep_recv, tp_recv, expand_scales
 
 
-def combine(kern, expand_x, expert_ids, expand_idx, ep_send_counts, expert_scales, group_ep, R, rank, E, shared=None):
-    """out[t] = sum_k expert_scales[t,k] * (expert output of copy (t,k)), after returning rows to their senders."""
+def combine(kern, expand_x, expert_ids, expand_idx, ep_send_counts, expert_scales, group_ep, R, rank, E, shared=None, mask=None,
+            special=None):
+    """out[t] = sum_k expert_scales[t,k] * (expert output of copy (t,k)), after returning rows to their senders.
+    mask (x_active_mask): tokens marked False get an all-zero row; special: the special experts of the second-generation
+    operator (see CudaKernels.combine)."""
     counters["combine_calls"] += 1
     T, K = expert_ids.shape
     H = expand_x.shape[1]
     if R == 1:
-        return kern.combine(expand_x, expand_idx, expert_scales, shared, T, K)
+        return kern.combine(expand_x, expand_idx, expert_scales, shared, T, K, mask, special)
     pg = get_ep_group(group_ep)
     E_l = E // R
     if transport_of(group_ep, expand_x.is_cuda) == "peer":
-        return _combine_peer(kern, expand_x, expert_ids, expand_idx, ep_send_counts, expert_scales, group_ep, pg, R, rank, E, shared)
+        return _combine_peer(kern, expand_x, expert_ids, expand_idx, ep_send_counts, expert_scales, group_ep, pg, R, rank, E, shared,
+                             mask, special)
     remembered = _splits.get((ep_send_counts.data_ptr(), expand_idx.data_ptr()))
     if remembered is not None:
         send_splits, recv_splits = remembered
     else:  # handshake tensors were copied: rebuild the split sizes (one host read)
         got = ep_send_counts.view(E_l, R).sum(0)
-        sent = torch.bincount((expert_ids.reshape(-1) // E_l).to(torch.int64), minlength=R).to(got.dtype)
+        sent_to = (expert_ids.reshape(-1) // E_l).to(torch.int64)
+        sent_ok = (expand_idx.reshape(-1) >= 0) & (sent_to < R)
+        sent = torch.bincount(sent_to[sent_ok], minlength=R).to(got.dtype)
         sums = torch.stack([sent, got]).cpu()
         send_splits = [int(v) for v in sums[0]]
         recv_splits = [int(v) for v in sums[1]]
@@ -464,6 +509,6 @@ def combine(kern, expand_x, expert_ids, expand_idx, ep_send_counts, expert_scale
     total = sum(recv_splits)
     wire, _ = kern.exchange_rows(expand_x.contiguous(), None, plan, R, E_l, 0, 1, total, False)
     back = torch.empty((T * K, H), dtype=expand_x.dtype, device=expand_x.device)
-    dist.all_to_all_single(back, wire, send_splits, recv_splits, group=pg)
+    dist.all_to_all_single(back[:sum(send_splits)], wire, send_splits, recv_splits, group=pg)
     counters["wire_bytes_sent"] += (total - recv_splits[rank]) * H * expand_x.element_size()
-    return kern.combine(back, expand_idx, expert_scales, shared, T, K)
+    return kern.combine(back, expand_idx, expert_scales, shared, T, K, mask, special)

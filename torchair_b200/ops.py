@@ -368,7 +368,7 @@ def _gmm_cuda(x, weight, *, bias=None, scale=None, offset=None, antiquant_scale=
               per_token_scale_dtype=None):
     op = "npu_grouped_matmul"
     xs, w = _gmm_common_check(op, x, weight, split_item, group_type, group_list, act_type)
-    for name, v in (("bias", bias), ("offset", offset), ("antiquant_scale", antiquant_scale),
+    for name, v in (("offset", offset), ("antiquant_scale", antiquant_scale),
                     ("antiquant_offset", antiquant_offset), ("activation_input", activation_input),
                     ("activation_quant_scale", activation_quant_scale), ("activation_quant_offset", activation_quant_offset)):
         if v is not None and len(v) > 0:
@@ -384,11 +384,17 @@ def _gmm_cuda(x, weight, *, bias=None, scale=None, offset=None, antiquant_scale=
     group_list = group_list.to(torch.int64).contiguous()
     sc = scale[0] if scale is not None and len(scale) else None
     pts = per_token_scale[0] if per_token_scale is not None and len(per_token_scale) else None
+    bs = bias[0] if bias is not None and len(bias) else None
+    if bs is not None:
+        # the int8 mode takes an int32 bias (converter grouped_matmul.py:258-262), added to the accumulators
+        if bs.dtype != torch.int32 or bs.numel() != E * N:
+            raise NotImplementedError(f"{op}: bias must be int32 [E, N] for int8 inputs")
+        bs = bs.contiguous()
     if out_dt != torch.int32:
         if sc is not None:
-            if sc.dtype != torch.float32 or sc.numel() != E * N:
-                raise NotImplementedError(f"{op}: scale must be fp32 [E, N] on this path")
-            sc = sc.contiguous()
+            if sc.dtype not in (torch.float32, torch.bfloat16) or sc.numel() != E * N:
+                raise NotImplementedError(f"{op}: scale must be float32 or bfloat16 [E, N] on this path")
+            sc = sc.float().contiguous()          # a bfloat16 scale is an exact float32 value
         if pts is not None:
             if pts.dtype != torch.float32 or pts.numel() != M:
                 raise RuntimeError(f"{op}: per_token_scale must be fp32 [M]")
@@ -398,7 +404,7 @@ def _gmm_cuda(x, weight, *, bias=None, scale=None, offset=None, antiquant_scale=
     # rows outside every group are left unwritten: with expert parallelism x is sized for the worst case and most of
     # it is an unused tail, which nothing downstream reads
     y = torch.empty((M, N), dtype=out_dt, device=xs.device)
-    _lib.call("tab_grouped_matmul_w8a8", _ptr(xs), _ptr(wp), _ptr(sc), _ptr(pts), _ptr(group_list), int(group_list_type or 0),
+    _lib.call("tab_grouped_matmul_w8a8", _ptr(xs), _ptr(wp), _ptr(sc), _ptr(pts), _ptr(bs), _ptr(group_list), int(group_list_type or 0),
               M, Kd, N, E, _ST_INV[out_dt], _ptr(y), _expected_rows(tuning_config), _stream(xs))
     return [y]
 
@@ -629,12 +635,20 @@ def _gating_meta(x, finished=None, k=1):
             torch.empty((T, k), dtype=torch.int32, device=x.device))
 
 
+def _finished_mask(op, finished, tokens):
+    if finished is None:
+        return None
+    if finished.dtype != torch.bool or finished.numel() != tokens:
+        raise RuntimeError(f"{op}: finished must be bool [tokens]")
+    return finished.contiguous()
+
+
 def _gating_cuda(x, finished=None, k=1):
     y, ei, ri = _gating_meta(x, finished, k)
-    _only_none("npu_moe_gating_top_k_softmax", finished=finished)
+    fin = _finished_mask("npu_moe_gating_top_k_softmax", finished, x.shape[0])
     xc = x.contiguous()
-    _lib.call("tab_moe_gating_top_k_softmax", _ptr(xc), _st(x.dtype, "npu_moe_gating_top_k_softmax"), x.shape[0], x.shape[1], k,
-              _ptr(y), _ptr(ei), _ptr(ri), _stream(xc))
+    _lib.call("tab_moe_gating_top_k_softmax", _ptr(xc), _st(x.dtype, "npu_moe_gating_top_k_softmax"), _ptr(fin), x.shape[0],
+              x.shape[1], k, _ptr(y), _ptr(ei), _ptr(ri), _stream(xc))
     return y, ei, ri
 
 
@@ -650,11 +664,11 @@ def _gating_v2_meta(x, *, k=1, finished=None, renorm=0, output_softmax=False):
 def _gating_v2_cuda(x, *, k=1, finished=None, renorm=0, output_softmax=False):
     op = "npu_moe_gating_top_k_softmax_v2"
     y, ei, sm = _gating_v2_meta(x, k=k, renorm=renorm, output_softmax=output_softmax)
-    _only_none(op, finished=finished)
+    fin = _finished_mask(op, finished, x.shape[0])
     if (renorm or 0) not in (0, 1):
         raise RuntimeError(f"{op}: renorm must be 0 or 1")
     xc = x.contiguous()
-    _lib.call("tab_moe_gating_top_k", _ptr(xc), None, _st(x.dtype, op), x.shape[0], x.shape[1], k, 1, 1, 0, 2 if renorm else 0,
+    _lib.call("tab_moe_gating_top_k", _ptr(xc), None, _ptr(fin), _st(x.dtype, op), x.shape[0], x.shape[1], k, 1, 1, 0, 2 if renorm else 0,
               1.0, 0.0, _ptr(y), _ptr(ei), _ptr(sm) if sm.numel() else None, _stream(xc))
     return y, ei, sm
 
@@ -679,22 +693,10 @@ def _gating2_cuda(x, k, *, bias=None, k_group=1, group_count=1, group_select_mod
         if bias.dtype != x.dtype or bias.numel() != x.shape[1]:
             raise RuntimeError(f"{op}: bias must be [experts] of the dtype of x")
         bias = bias.contiguous()
-    _lib.call("tab_moe_gating_top_k", _ptr(xc), _ptr(bias), _st(x.dtype, op), x.shape[0], x.shape[1], k, k_group, group_count,
+    _lib.call("tab_moe_gating_top_k", _ptr(xc), _ptr(bias), None, _st(x.dtype, op), x.shape[0], x.shape[1], k, k_group, group_count,
               int(group_select_mode), 2 if renorm == 1 else int(norm_type), float(routed_scaling_factor), float(eps), _ptr(y),
               _ptr(ei), _ptr(out), _stream(xc))
     return y, ei, out
-
-
-def _v2_extras(op, **kw):
-    for name, v in kw.items():
-        if isinstance(v, str):
-            if v != "":
-                raise NotImplementedError(f"{op}: `{name}`={v!r} is outside the path")
-        elif isinstance(v, int) and not isinstance(v, bool):
-            if v != 0:
-                raise NotImplementedError(f"{op}: `{name}`={v} is outside the path")
-        elif v is not None:
-            raise NotImplementedError(f"{op}: `{name}` is outside the path and must be None")
 
 
 _comm_alg_seen = set()
@@ -711,45 +713,102 @@ def _comm_alg_hint(op, comm_alg):
         logging.getLogger("torchair").warning("%s: comm_alg=%r has no effect on B200; the group's transport moves the rows", op, comm_alg)
 
 
-def _dispatch_v2(impl):
+_elastic_checked = {}
+
+
+def _check_elastic_info(op, elastic_info, R):
+    """elastic_info (moe_distribute_dispatch_v2.py:16,72): int32 [4 + 2 * ep_world_size].  Decision: entry 0 says whether the
+    group runs in a shrunk (elastic) state; the rest is the rank table of that state.  Only the full group is served here
+    (entry 0 == 0); a shrunk group is re-registered under a new name with register_ep_group instead.  The contents are read
+    once per tensor version, outside CUDA-graph capture (a host read)."""
+    if elastic_info is None:
+        return
+    if elastic_info.dtype != torch.int32 or elastic_info.numel() != 4 + 2 * R:
+        raise RuntimeError(f"{op}: elastic_info must be int32 with 4 + 2 * ep_world_size = {4 + 2 * R} entries")
+    key = (elastic_info.data_ptr(), elastic_info._version)
+    if key in _elastic_checked or (elastic_info.is_cuda and torch.cuda.is_current_stream_capturing()):
+        return
+    if int(elastic_info.reshape(-1)[0].item()) != 0:
+        raise NotImplementedError(f"{op}: a shrunk (elastic) group is not served through elastic_info; register the surviving "
+                                  "ranks as a new group")
+    if len(_elastic_checked) > 64:
+        _elastic_checked.clear()
+    _elastic_checked[key] = True
+
+
+def _check_performance_info(op, performance_info, R):
+    """performance_info (moe_distribute_dispatch_v2.py:17,73): int64 [ep_world_size] in which the vendor kernel accumulates how
+    long it waited for each rank.  Accepted and left unchanged: the waits of this implementation are device-side and
+    report through the status words."""
+    if performance_info is not None and (performance_info.dtype != torch.int64 or performance_info.numel() != R):
+        raise RuntimeError(f"{op}: performance_info must be int64 [ep_world_size]")
+
+
+def _special_counts(op, zero_expert_num, copy_expert_num, const_expert_num):
+    for n in (zero_expert_num, copy_expert_num, const_expert_num):
+        if not isinstance(n, int) or n < 0:
+            raise RuntimeError(f"{op}: zero_expert_num, copy_expert_num and const_expert_num must be non-negative integers")
+    return zero_expert_num + copy_expert_num + const_expert_num
+
+
+def _dispatch_v2(impl, is_meta):
     def fn(x, expert_ids, group_ep, ep_world_size, ep_rank_id, moe_expert_num, *, scales=None, x_active_mask=None,
            expert_scales=None, elastic_info=None, performance_info=None, group_tp="", tp_world_size=0, tp_rank_id=0,
            expert_shard_type=0, shared_expert_num=1, shared_expert_rank_num=0, quant_mode=0, global_bs=0,
            expert_token_nums_type=1, comm_alg="", zero_expert_num=0, copy_expert_num=0, const_expert_num=0, y_dtype=None,
            x_dtype=None, scales_dtype=None):
         op = "npu_moe_distribute_dispatch_v2"
-        _v2_extras(op, elastic_info=elastic_info, performance_info=performance_info, zero_expert_num=zero_expert_num,
-                   copy_expert_num=copy_expert_num, const_expert_num=const_expert_num, x_dtype=x_dtype, scales_dtype=scales_dtype)
+        _only_none(op, x_dtype=x_dtype, scales_dtype=scales_dtype)
         _comm_alg_hint(op, comm_alg)
+        _check_performance_info(op, performance_info, ep_world_size)
+        special = _special_counts(op, zero_expert_num, copy_expert_num, const_expert_num)
         if y_dtype is not None:
             # the converter's rule (moe_distribute_dispatch_v2.py:60-64): int8 unless quant_mode is 0, then the dtype of x;
             # y_dtype may restate that, it cannot ask for another element type here
             want = 1 if quant_mode != 0 else _ST_INV.get(x.dtype)
             if y_dtype != want:
                 raise NotImplementedError(f"{op}: y_dtype={y_dtype} differs from the output type of quant_mode={quant_mode} ({want})")
-        return impl(x, expert_ids, group_ep, ep_world_size, ep_rank_id, moe_expert_num, scales=scales, x_active_mask=x_active_mask,
-                    expert_scales=expert_scales, group_tp=group_tp, tp_world_size=tp_world_size, tp_rank_id=tp_rank_id,
-                    expert_shard_type=expert_shard_type, shared_expert_num=shared_expert_num,
-                    shared_expert_rank_num=shared_expert_rank_num, quant_mode=quant_mode, global_bs=global_bs,
-                    expert_token_nums_type=expert_token_nums_type)
+        kw = dict(scales=scales, x_active_mask=x_active_mask, expert_scales=expert_scales, group_tp=group_tp,
+                  tp_world_size=tp_world_size, tp_rank_id=tp_rank_id, expert_shard_type=expert_shard_type,
+                  shared_expert_num=shared_expert_num, shared_expert_rank_num=shared_expert_rank_num, quant_mode=quant_mode,
+                  global_bs=global_bs, expert_token_nums_type=expert_token_nums_type)
+        if not is_meta:
+            _check_elastic_info(op, elastic_info, ep_world_size)
+            kw["_special"] = special
+        return impl(x, expert_ids, group_ep, ep_world_size, ep_rank_id, moe_expert_num, **kw)
     return fn
 
 
-def _combine_v2(impl):
+def _combine_v2(impl, is_meta):
     def fn(expand_x, expert_ids, assist_info_for_combine, ep_send_counts, expert_scales, group_ep, ep_world_size, ep_rank_id,
            moe_expert_num, *, tp_send_counts=None, x_active_mask=None, expand_scales=None, shared_expert_x=None, elastic_info=None,
            ori_x=None, const_expert_alpha_1=None, const_expert_alpha_2=None, const_expert_v=None, performance_info=None,
            group_tp="", tp_world_size=0, tp_rank_id=0, expert_shard_type=0, shared_expert_num=1, shared_expert_rank_num=0,
            global_bs=0, comm_quant_mode=0, comm_alg="", zero_expert_num=0, copy_expert_num=0, const_expert_num=0):
-        _v2_extras("npu_moe_distribute_combine_v2", elastic_info=elastic_info, ori_x=ori_x, const_expert_alpha_1=const_expert_alpha_1,
-                   const_expert_alpha_2=const_expert_alpha_2, const_expert_v=const_expert_v, performance_info=performance_info,
-                   zero_expert_num=zero_expert_num, copy_expert_num=copy_expert_num, const_expert_num=const_expert_num)
-        _comm_alg_hint("npu_moe_distribute_combine_v2", comm_alg)
+        op = "npu_moe_distribute_combine_v2"
+        _comm_alg_hint(op, comm_alg)
+        _check_performance_info(op, performance_info, ep_world_size)
+        specials = _special_counts(op, zero_expert_num, copy_expert_num, const_expert_num)
+        T, H = expert_ids.shape[0], expand_x.shape[1]
+        if copy_expert_num + const_expert_num > 0 and (ori_x is None or tuple(ori_x.shape) != (T, H)):
+            raise RuntimeError(f"{op}: copy and constant experts need ori_x [T, H]")
+        if const_expert_num > 0:
+            for name, t in (("const_expert_alpha_1", const_expert_alpha_1), ("const_expert_alpha_2", const_expert_alpha_2),
+                            ("const_expert_v", const_expert_v)):
+                if t is None or tuple(t.shape) != (const_expert_num, H):
+                    raise RuntimeError(f"{op}: {name} must be [const_expert_num, H]")
+        kw = dict(tp_send_counts=tp_send_counts, x_active_mask=x_active_mask, expand_scales=expand_scales,
+                  shared_expert_x=shared_expert_x, group_tp=group_tp, tp_world_size=tp_world_size, tp_rank_id=tp_rank_id,
+                  expert_shard_type=expert_shard_type, shared_expert_num=shared_expert_num,
+                  shared_expert_rank_num=shared_expert_rank_num, global_bs=global_bs, comm_quant_mode=comm_quant_mode)
+        if not is_meta:
+            _check_elastic_info(op, elastic_info, ep_world_size)
+            if specials > 0:
+                kw["_special"] = {"expert_ids": expert_ids, "E": moe_expert_num, "zero": zero_expert_num, "copy": copy_expert_num,
+                                  "const": const_expert_num, "ori_x": ori_x, "alpha_1": const_expert_alpha_1,
+                                  "alpha_2": const_expert_alpha_2, "const_v": const_expert_v}
         return impl(expand_x, expert_ids, assist_info_for_combine, ep_send_counts, expert_scales, group_ep, ep_world_size,
-                    ep_rank_id, moe_expert_num, tp_send_counts=tp_send_counts, x_active_mask=x_active_mask,
-                    expand_scales=expand_scales, shared_expert_x=shared_expert_x, group_tp=group_tp, tp_world_size=tp_world_size,
-                    tp_rank_id=tp_rank_id, expert_shard_type=expert_shard_type, shared_expert_num=shared_expert_num,
-                    shared_expert_rank_num=shared_expert_rank_num, global_bs=global_bs, comm_quant_mode=comm_quant_mode)
+                    ep_rank_id, moe_expert_num, **kw)
     return fn
 
 
@@ -793,37 +852,54 @@ def _finalize_cuda(expanded_permuted_rows, skip1, skip2, bias, scales, expanded_
 
 def _irv2_check(x, expert_idx, scale, offset, active_num, expert_capacity, expert_num, drop_pad_mode, quant_mode,
                 active_expert_range, x_dtype):
+    """Returns (expert_lo, expert_hi, rows of expanded_x, active_rows)."""
     op = "npu_moe_init_routing_v2"
     if x.dim() != 2 or expert_idx.dim() != 2 or x.shape[0] != expert_idx.shape[0]:
         raise RuntimeError(f"{op}: x must be [T, H] and expert_idx [T, K]")
-    _only_none(op, scale=scale, offset=offset, x_dtype=x_dtype)
+    _only_none(op, offset=offset, x_dtype=x_dtype)
     if expert_num <= 0:
         raise RuntimeError(f"{op}: expert_num must be given")
     if drop_pad_mode != 0 or expert_capacity not in (-1, 0):
         raise NotImplementedError(f"{op}: only the dropless mode is on the path")
     if quant_mode not in (-1, 1):
         raise NotImplementedError(f"{op}: quant_mode must be -1 (none) or 1 (per-token dynamic int8)")
-    if active_num not in (-1, 0) and active_num < x.shape[0] * expert_idx.shape[1]:
-        raise NotImplementedError(f"{op}: active_num below T*K is outside the path")
-    if active_expert_range is not None and list(active_expert_range) != [0, expert_num]:
-        raise NotImplementedError(f"{op}: active_expert_range must cover [0, expert_num)")
+    lo, hi = 0, expert_num
+    if active_expert_range is not None and len(active_expert_range):
+        if len(active_expert_range) != 2:
+            raise RuntimeError(f"{op}: active_expert_range must be [expert_start, expert_end]")
+        lo, hi = int(active_expert_range[0]), int(active_expert_range[1])
+        if not (0 <= lo < hi <= expert_num):
+            raise RuntimeError(f"{op}: active_expert_range [{lo}, {hi}) must lie inside [0, expert_num = {expert_num})")
+    T, K = expert_idx.shape
+    M, H = T * K, x.shape[1]
+    active_rows = int(active_num) if active_num is not None and 0 < active_num < M else 0
+    if scale is not None:
+        if scale.dtype != torch.float32:
+            raise RuntimeError(f"{op}: scale must be float32")
+        if quant_mode == -1 and scale.numel() != T:
+            raise RuntimeError(f"{op}: without quantisation scale holds one value per token ({T})")
+        if quant_mode == 1 and (scale.numel() not in (H, (hi - lo) * H) or scale.shape[-1] != H):
+            raise RuntimeError(f"{op}: with dynamic quantisation scale must be [{hi - lo}, {H}] or [1, {H}]")
+    return lo, hi, (active_rows or M), active_rows
 
 
 def _irv2_meta(x, expert_idx, *, scale=None, offset=None, active_num=-1, expert_capacity=-1, expert_num=-1, drop_pad_mode=0,
                expert_tokens_num_type=0, expert_tokens_num_flag=False, quant_mode=-1, active_expert_range=None, row_idx_type=0,
                x_dtype=None):
-    _irv2_check(x, expert_idx, scale, offset, active_num, expert_capacity, expert_num, drop_pad_mode, quant_mode,
-                active_expert_range, x_dtype)
+    lo, hi, rows, _ = _irv2_check(x, expert_idx, scale, offset, active_num, expert_capacity, expert_num, drop_pad_mode, quant_mode,
+                                  active_expert_range, x_dtype)
     M = expert_idx.numel()
     dev = x.device
-    return (torch.empty((M, x.shape[1]), dtype=torch.int8 if quant_mode == 1 else x.dtype, device=dev),
-            torch.empty((M,), dtype=torch.int32, device=dev), torch.empty((expert_num,), dtype=torch.int64, device=dev),
+    return (torch.empty((rows, x.shape[1]), dtype=torch.int8 if quant_mode == 1 else x.dtype, device=dev),
+            torch.empty((M,), dtype=torch.int32, device=dev), torch.empty((hi - lo,), dtype=torch.int64, device=dev),
             torch.empty((M,), dtype=torch.float32, device=dev))
 
 
 def _irv2_cuda(x, expert_idx, *, scale=None, offset=None, active_num=-1, expert_capacity=-1, expert_num=-1, drop_pad_mode=0,
                expert_tokens_num_type=0, expert_tokens_num_flag=False, quant_mode=-1, active_expert_range=None, row_idx_type=0,
                x_dtype=None):
+    lo, hi, rows, active_rows = _irv2_check(x, expert_idx, scale, offset, active_num, expert_capacity, expert_num, drop_pad_mode,
+                                            quant_mode, active_expert_range, x_dtype)
     ex, eri, tokens, esc = _irv2_meta(x, expert_idx, scale=scale, offset=offset, active_num=active_num,
                                       expert_capacity=expert_capacity, expert_num=expert_num, drop_pad_mode=drop_pad_mode,
                                       quant_mode=quant_mode, active_expert_range=active_expert_range, x_dtype=x_dtype)
@@ -831,11 +907,13 @@ def _irv2_cuda(x, expert_idx, *, scale=None, offset=None, active_num=-1, expert_
         raise NotImplementedError("npu_moe_init_routing_v2: x must be bfloat16/float16 and expert_idx int32")
     T, K = expert_idx.shape
     xc, ic = x.contiguous(), expert_idx.contiguous()
-    nbytes = _lib.workspace_bytes("tab_moe_dispatch_pack_workspace_bytes", T, K, expert_num) + 4 * (T * K + expert_num) + 1024
+    sc = None if scale is None else scale.contiguous()
+    scale_rows = 0 if sc is None else (T if quant_mode == -1 else sc.numel() // x.shape[1])
+    nbytes = _lib.workspace_bytes("tab_moe_dispatch_pack_workspace_bytes", T, K, hi - lo) + 4 * (T * K + hi - lo) + 1024
     ws = _workspace(nbytes, x.device)
-    _lib.call("tab_moe_init_routing_v2", _ptr(xc), _st(x.dtype, "npu_moe_init_routing_v2"), _ptr(ic), T, K, x.shape[1], expert_num,
-              quant_mode, int(expert_tokens_num_type), int(row_idx_type), _ptr(ex), _ptr(eri), _ptr(tokens), _ptr(esc), _ptr(ws),
-              ws.numel(), _stream(xc))
+    _lib.call("tab_moe_init_routing_v2", _ptr(xc), _st(x.dtype, "npu_moe_init_routing_v2"), _ptr(ic), T, K, x.shape[1], lo, hi,
+              quant_mode, int(expert_tokens_num_type), int(row_idx_type), active_rows, _ptr(sc), scale_rows, _ptr(ex), _ptr(eri),
+              _ptr(tokens), _ptr(esc), _ptr(ws), ws.numel(), _stream(xc))
     return ex, eri, tokens, esc
 
 
@@ -850,7 +928,7 @@ def _dispatch_meta(x, expert_ids, group_ep, ep_world_size, ep_rank_id, moe_exper
     T, K = expert_ids.shape
     R = ep_world_size
     E_l = moe_expert_num // R
-    A = ep.dispatch_rows(T, R, moe_expert_num, K)
+    A = ep.dispatch_rows(T, R, moe_expert_num, K, global_bs)
     dev = x.device
     return (torch.empty((A, x.shape[1]), dtype=torch.int8 if quant_mode == 2 else x.dtype, device=dev),
             torch.empty((A,), dtype=torch.float32, device=dev),
@@ -863,11 +941,11 @@ def _dispatch_meta(x, expert_ids, group_ep, ep_world_size, ep_rank_id, moe_exper
 
 def _dispatch_cuda(x, expert_ids, group_ep, ep_world_size, ep_rank_id, moe_expert_num, *, scales=None, x_active_mask=None,
                    expert_scales=None, group_tp="", tp_world_size=0, tp_rank_id=0, expert_shard_type=0, shared_expert_num=1,
-                   shared_expert_rank_num=0, quant_mode=0, global_bs=0, expert_token_nums_type=1):
+                   shared_expert_rank_num=0, quant_mode=0, global_bs=0, expert_token_nums_type=1, _special=0):
     ep.check_dispatch_args(x, expert_ids, ep_world_size, ep_rank_id, moe_expert_num, scales, x_active_mask, tp_world_size,
                            expert_shard_type, shared_expert_rank_num, quant_mode, global_bs, expert_token_nums_type)
     return ep.dispatch(ep.CudaKernels, x, expert_ids, group_ep, ep_world_size, ep_rank_id, moe_expert_num, quant_mode,
-                       expert_token_nums_type, max(tp_world_size, 1))
+                       expert_token_nums_type, max(tp_world_size, 1), x_active_mask, scales, _special, global_bs)
 
 
 def _combine_meta(expand_x, expert_ids, expand_idx, ep_send_counts, expert_scales, group_ep, ep_world_size, ep_rank_id,
@@ -885,12 +963,12 @@ def _combine_cuda(expand_x, expert_ids, expand_idx, ep_send_counts, expert_scale
                   moe_expert_num, *, tp_send_counts=None, x_active_mask=None, activation_scale=None, weight_scale=None,
                   group_list=None, expand_scales=None, shared_expert_x=None, group_tp="", tp_world_size=0, tp_rank_id=0,
                   expert_shard_type=0, shared_expert_num=1, shared_expert_rank_num=0, global_bs=0, out_dtype=0,
-                  comm_quant_mode=0, group_list_type=0):
+                  comm_quant_mode=0, group_list_type=0, _special=None):
     ep.check_combine_args(expand_x, expert_ids, expert_scales, ep_world_size, ep_rank_id, moe_expert_num, x_active_mask,
                           activation_scale, weight_scale, group_list, tp_world_size, expert_shard_type,
                           shared_expert_rank_num, global_bs, out_dtype, comm_quant_mode)
     return ep.combine(ep.CudaKernels, expand_x, expert_ids, expand_idx, ep_send_counts, expert_scales, group_ep,
-                      ep_world_size, ep_rank_id, moe_expert_num, shared_expert_x)
+                      ep_world_size, ep_rank_id, moe_expert_num, shared_expert_x, x_active_mask, _special)
 
 
 for _name, _meta, _cuda in (
@@ -913,11 +991,12 @@ for _name, _meta, _cuda in (
     _npu.impl(_name, _meta, "Meta")
     _npu.impl(_name, _cuda, "CUDA")
 _npu.impl("npu_dynamic_quant_asymmetric", _dynamic_quant_asym, "CompositeExplicitAutograd")
-# the second-generation dispatch / combine operators share the kernels; their additional arguments must stay at defaults
-_npu.impl("npu_moe_distribute_dispatch_v2", _dispatch_v2(_dispatch_meta), "Meta")
-_npu.impl("npu_moe_distribute_dispatch_v2", _dispatch_v2(_dispatch_cuda), "CUDA")
-_npu.impl("npu_moe_distribute_combine_v2", _combine_v2(_combine_meta), "Meta")
-_npu.impl("npu_moe_distribute_combine_v2", _combine_v2(_combine_cuda), "CUDA")
+# the second-generation dispatch / combine operators share the kernels: special experts are dropped from the exchange and
+# evaluated by the combine; elastic_info and performance_info are accepted (see _check_elastic_info)
+_npu.impl("npu_moe_distribute_dispatch_v2", _dispatch_v2(_dispatch_meta, True), "Meta")
+_npu.impl("npu_moe_distribute_dispatch_v2", _dispatch_v2(_dispatch_cuda, False), "CUDA")
+_npu.impl("npu_moe_distribute_combine_v2", _combine_v2(_combine_meta, True), "Meta")
+_npu.impl("npu_moe_distribute_combine_v2", _combine_v2(_combine_cuda, False), "CUDA")
 
 OP_NAMES = ["npu_moe_init_routing", "npu_dynamic_quant", "npu_dynamic_quant_asymmetric", "npu_swiglu",
             "npu_dequant_swiglu_quant", "npu_grouped_matmul", "npu_grouped_matmul_swiglu_quant_v2",
