@@ -905,3 +905,58 @@ def test_swiglu_reciprocal_is_the_ieee_reciprocal_for_every_significand(dev):
         _lib.call("tab_selftest_reciprocal", exponent, ctypes.c_void_p(bad.data_ptr()), stream)
     torch.cuda.synchronize(dev)
     assert int(bad.item()) == 0
+
+
+@pytest.mark.parametrize("counts,Kd,N", [([3000, 1096], 256, 512), ([0, 2500, 3407], 384, 264), ([1025, 1, 2300], 144, 1024)])
+def test_cta_pair_gemm_plain_outputs_are_bit_exact(dev, counts, Kd, N):
+    """Experts that hold many rows run on CTA pairs (256-token x 256-channel tiles, tcgen05.mma.cta_group::2, each CTA
+    loading half of the weight tile): raw int32, scaled bf16 with an int32 bias, and rows past the last group untouched.
+    Counts are chosen to leave last tiles with one row, with 129 rows (one row in the second CTA) and an empty expert."""
+    E, covered = len(counts), sum(counts)
+    M = covered + 13
+    g = torch.Generator().manual_seed(Kd + N)
+    x = torch.randint(-127, 128, (M, Kd), generator=g, dtype=torch.int8)
+    w = torch.randint(-127, 128, (E, Kd, N), generator=g, dtype=torch.int8)
+    sc = torch.rand(E, N, generator=g) * 9e-3 + 1e-3
+    pts = torch.rand(M, generator=g) * 1e-2
+    bias = torch.randint(-50000, 50000, (E, N), generator=g, dtype=torch.int32)
+    cnt = torch.tensor(counts, dtype=torch.int64)
+    hint = [max(counts)]                      # the tiling hint that selects the pair kernel (>= 768 rows per group)
+    xd, wd, cd = x.to(dev), w.to(dev), cnt.to(dev)
+    h32 = npu.npu_grouped_matmul([xd], [wd], group_list=cd, split_item=2, group_type=0, group_list_type=1, output_dtype=3,
+                                 tuning_config=hint)[0]
+    _gmm_ok(dev)
+    assert torch.equal(O.grouped_matmul_w8a8(x, w, None, None, cnt, 1, 3)[:covered], h32.cpu()[:covered])
+    y = torch.full((M, N), 3.0, dtype=torch.bfloat16, device=dev)
+    got = npu.npu_grouped_matmul([xd], [wd], bias=[bias.to(dev)], scale=[sc.to(dev)], per_token_scale=[pts.to(dev)], group_list=cd,
+                                 split_item=2, group_type=0, group_list_type=1, output_dtype=15, tuning_config=hint)[0]
+    _gmm_ok(dev)
+    ref = O.grouped_matmul_w8a8(x, w, sc, pts, cnt, 1, 15, bias=bias)
+    assert torch.equal(ref[:covered], got.cpu()[:covered])
+    # the same through the kernel that takes one CTA per tile: the choice of kernel changes no bit
+    one = npu.npu_grouped_matmul([xd], [wd], bias=[bias.to(dev)], scale=[sc.to(dev)], per_token_scale=[pts.to(dev)], group_list=cd,
+                                 split_item=2, group_type=0, group_list_type=1, output_dtype=15, tuning_config=[300])[0]
+    assert torch.equal(one[:covered], got[:covered])
+
+
+@pytest.mark.parametrize("counts,Kd,I", [([3000, 1096], 512, 256), ([2049, 0, 2900], 256, 136), ([4096], 1024, 1536)])
+def test_cta_pair_gemm_fused_gate_up_is_bit_exact(dev, counts, Kd, I):
+    """gate_up + SwiGLU + requantise on CTA pairs (each CTA loads 64 gate and the matching 64 up channels of a tile)
+    against the oracle and against the unfused pair of operators."""
+    E, covered = len(counts), sum(counts)
+    M = covered + 5
+    g = torch.Generator().manual_seed(Kd + I)
+    x = torch.randint(-127, 128, (M, Kd), generator=g, dtype=torch.int8)
+    w = torch.randint(-127, 128, (E, Kd, 2 * I), generator=g, dtype=torch.int8)
+    ws = torch.rand(E, 2 * I, generator=g) * 9e-3 + 1e-3
+    xs = torch.rand(M, generator=g) * 1e-2
+    cnt = torch.tensor(counts, dtype=torch.int64)
+    xd, wd, wsd, xsd, cd = x.to(dev), w.to(dev), ws.to(dev), xs.to(dev), cnt.to(dev)
+    for _ in range(2):
+        hq, hs = npu.npu_grouped_matmul_swiglu_quant_v2(xd, [wd], [wsd], xsd, cd, group_list_type=1, tuning_config=[max(counts)])
+    _gmm_ok(dev)
+    h32 = O.grouped_matmul_w8a8(x, w, None, None, cnt, 1, 3)
+    q_ref, s_ref = O.dequant_swiglu_quant(h32, ws, xs, cnt, True, 1)
+    _swiglu_quant_equal(hq[:covered], hs[:covered], q_ref[:covered], s_ref[:covered])
+    hq1, hs1 = npu.npu_grouped_matmul_swiglu_quant_v2(xd, [wd], [wsd], xsd, cd, group_list_type=1, tuning_config=[300])
+    assert torch.equal(hq1[:covered], hq[:covered]) and torch.equal(hs1[:covered], hs[:covered])

@@ -24,6 +24,7 @@
 
 #include "gmm_common.cuh"
 #include "gmm_i8_prefill.cuh"
+#include "gmm_i8_pair.cuh"
 
 namespace tab {
 
@@ -320,15 +321,15 @@ static int num_sms() {
 
 // Weight map: 3-D (K, channel, expert), box 128 bytes x 128 channels; token map: 2-D (K, row), box 128 x NT.
 static int make_maps(const int8_t* x, const int8_t* wp, int64_t M, int64_t Kd, int64_t N, int64_t E, int nt,
-                     CUtensorMap* tm_w, CUtensorMap* tm_x) {
+                     CUtensorMap* tm_w, CUtensorMap* tm_x, CUtensorMap* tm_w64 = nullptr) {
   EncodeTiledFn enc = encode_fn();
   if (!enc) return fail(TAB_ERR_CUDA, "grouped_matmul: cuTensorMapEncodeTiled is not available from the driver");
-  {
+  for (int half_box = 0; half_box < (tm_w64 ? 2 : 1); ++half_box) {      // 128-channel boxes; 64-channel boxes for the pair kernel's gate | up halves
     cuuint64_t dims[3] = {(cuuint64_t)Kd, (cuuint64_t)N, (cuuint64_t)E};
     cuuint64_t strides[2] = {(cuuint64_t)Kd, (cuuint64_t)(Kd * N)};
-    cuuint32_t box[3] = {kBlockK, 128, 1};
+    cuuint32_t box[3] = {kBlockK, half_box ? 64u : 128u, 1};
     cuuint32_t es[3] = {1, 1, 1};
-    CUresult r = enc(tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<int8_t*>(wp), dims, strides, box, es,
+    CUresult r = enc(half_box ? tm_w64 : tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<int8_t*>(wp), dims, strides, box, es,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(TAB_ERR_CUDA, "grouped_matmul: weight tensor map rejected (CUresult %d)", (int)r);
@@ -348,11 +349,11 @@ static int make_maps(const int8_t* x, const int8_t* wp, int64_t M, int64_t Kd, i
 
 // Tuning and safety knobs from the environment, read once when the library is first used:
 //   TAB_GMM_NT=16|32|64|128|256          token-tile width of the decode orientation (default: from M / E)
-//   TAB_GMM_ORIENTATION=decode|prefill   kernel orientation (default: prefill when M > 64 * E)
+//   TAB_GMM_ORIENTATION=decode|prefill|pair   kernel (default: by the expected rows per group, see use_prefill / use_pair)
 //   TAB_GMM_WAIT_MS=<ms>                 bound of every device-side wait inside the GEMM kernels (default 2000)
 struct GmmEnv {
   int nt = 0;
-  int orientation = 0;   // 0 auto, 1 decode, 2 prefill
+  int orientation = 0;   // 0 auto, 1 decode, 2 prefill (one CTA per tile), 3 prefill on CTA pairs
   long long wait_cycles = 2000 * kCyclesPerMs;
   GmmEnv() {
     if (const char* f = getenv("TAB_GMM_NT")) {
@@ -362,6 +363,7 @@ struct GmmEnv {
     if (const char* f = getenv("TAB_GMM_ORIENTATION")) {
       if (strcmp(f, "decode") == 0) orientation = 1;
       if (strcmp(f, "prefill") == 0) orientation = 2;
+      if (strcmp(f, "pair") == 0) orientation = 3;
     }
     if (const char* f = getenv("TAB_GMM_WAIT_MS")) {
       const long long ms = atoll(f);
@@ -404,8 +406,15 @@ static int launch_one(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const Gm
 // Orientation: experts with many rows run the prefill kernel (128-token tiles, overlapped epilogue); a handful of
 // rows per expert run the decode kernel (weights stationary, narrow token tile).
 static bool use_prefill(double avg) {
-  if (gmm_env().orientation != 0) return gmm_env().orientation == 2;
+  if (gmm_env().orientation != 0) return gmm_env().orientation >= 2;
   return avg > 64.0;
+}
+
+// The CTA-pair kernel computes whole 256-token tiles, so an expert's last tile costs a full tile whatever it holds:
+// it pays when experts hold many tiles (expected rows per group >= 768: at most one tile in four is a partial one).
+static bool use_pair(double avg) {
+  if (gmm_env().orientation != 0) return gmm_env().orientation == 3;
+  return avg >= 768.0;
 }
 
 template <bool FUSED>
@@ -417,6 +426,17 @@ static int launch_prefill(const CUtensorMap& tm_w, const CUtensorMap& tm_x, cons
   if (e != cudaSuccess) return fail(TAB_ERR_CUDA, "grouped_matmul: shared memory opt-in failed: %s", cudaGetErrorString(e));
   gmm_i8_prefill_kernel<FUSED><<<grid, kPfThreads, kPfSmemBytes, st>>>(tm_w, tm_x, p);
   return check_launch("grouped_matmul (prefill)");
+}
+
+template <bool FUSED>
+static int launch_pair(const CUtensorMap& tm_w, const CUtensorMap& tm_w64, const CUtensorMap& tm_x, const GmmParams& p, cudaStream_t st) {
+  const int64_t max_items = ((static_cast<int64_t>(p.M) + kPairTokens - 1) / kPairTokens + p.E) * p.chan_tiles;
+  const int pairs = num_sms() / 2;
+  const int grid = 2 * static_cast<int>(max_items < pairs ? max_items : pairs);
+  cudaError_t e = cudaFuncSetAttribute(gmm_i8_pair_kernel<FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes);
+  if (e != cudaSuccess) return fail(TAB_ERR_CUDA, "grouped_matmul: shared memory opt-in failed: %s", cudaGetErrorString(e));
+  gmm_i8_pair_kernel<FUSED><<<grid, kPfThreads, kPairSmemBytes, st>>>(tm_w, tm_w64, tm_x, p);
+  return check_launch("grouped_matmul (CTA pairs)");
 }
 
 template <bool FUSED>
@@ -477,8 +497,9 @@ static int grouped_matmul_plain(const int8_t* x, const int8_t* packed_weight, co
   if (!y && !row_dst) return fail(TAB_ERR_BAD_ARG, "grouped_matmul: null output");
   const double avg = rows_per_group(M, E, expected_rows_per_group);
   const int nt = use_prefill(avg) ? 0 : pick_nt(avg);     // 0 selects the prefill orientation
-  CUtensorMap tm_w, tm_x;
-  rc = make_maps(x, packed_weight, M, Kd, N, E, nt == 0 ? kPfTokens : nt, &tm_w, &tm_x);
+  const bool pair = nt == 0 && use_pair(avg);
+  CUtensorMap tm_w, tm_x, tm_w64;
+  rc = make_maps(x, packed_weight, M, Kd, N, E, nt == 0 ? kPfTokens : nt, &tm_w, &tm_x, pair ? &tm_w64 : nullptr);
   if (rc != TAB_OK) return rc;
   GmmParams p = {};
   p.group_list = group_list;
@@ -493,6 +514,7 @@ static int grouped_matmul_plain(const int8_t* x, const int8_t* packed_weight, co
   p.out_dtype = out_dtype;
   p.row_dst = reinterpret_cast<const unsigned long long*>(row_dst);
   p.wait_cycles = gmm_env().wait_cycles;
+  if (pair) return launch_pair<false>(tm_w, tm_w64, tm_x, p, as_stream(stream));
   return launch_gmm<false>(nt, tm_w, tm_x, p, as_stream(stream));
 }
 
@@ -544,8 +566,9 @@ extern "C" int tab_grouped_matmul_swiglu_quant(const int8_t* x, const int8_t* pa
   if (ce != cudaSuccess) return fail(TAB_ERR_CUDA, "grouped_matmul_swiglu_quant: memset: %s", cudaGetErrorString(ce));
   const double avg = rows_per_group(M, E, expected_rows_per_group);
   const int nt = use_prefill(avg) ? 0 : pick_nt(avg);     // 0 selects the prefill orientation
-  CUtensorMap tm_w, tm_x;
-  rc = make_maps(x, packed_weight, M, Kd, 2 * I, E, nt == 0 ? kPfTokens : nt, &tm_w, &tm_x);
+  const bool pair = nt == 0 && use_pair(avg);
+  CUtensorMap tm_w, tm_x, tm_w64;
+  rc = make_maps(x, packed_weight, M, Kd, 2 * I, E, nt == 0 ? kPfTokens : nt, &tm_w, &tm_x, pair ? &tm_w64 : nullptr);
   if (rc != TAB_OK) return rc;
   GmmParams p = {};
   p.group_list = group_list;
@@ -559,7 +582,7 @@ extern "C" int tab_grouped_matmul_swiglu_quant(const int8_t* x, const int8_t* pa
   p.amax = amax;
   p.activate_left = activate_left;
   p.wait_cycles = gmm_env().wait_cycles;
-  rc = launch_gmm<true>(nt, tm_w, tm_x, p, st);
+  rc = pair ? launch_pair<true>(tm_w, tm_w64, tm_x, p, st) : launch_gmm<true>(nt, tm_w, tm_x, p, st);
   if (rc != TAB_OK) return rc;
   return launch_quant_from_f32(h, amax, group_list, group_list_type, (int)E, M, (int)I, yq, y_scale, st);
 }
