@@ -13,13 +13,14 @@ import sys
 from . import _lib
 from .configs import CompilerConfig
 from .backend import get_compiler, get_npu_backend, register_fx_node_ge_converter, declare_supported, logger
-from .ep import register_ep_group, get_ep_group
+from .ep import register_ep_group, get_ep_group, watchdog_of
+from .watchdog import EpGroupFailed, EpWatchdog
 from . import ops
 from . import scope
 from .ops import clear_weight_cache, gmm_status, gmm_status_reset, routing_status, check_status
 
 __all__ = ["get_npu_backend", "get_compiler", "CompilerConfig", "register_fx_node_ge_converter", "logger",
-           "register_ep_group", "install_as_torchair", "clear_weight_cache", "gmm_status", "gmm_status_reset", "routing_status",
+           "register_ep_group", "watchdog_of", "EpGroupFailed", "EpWatchdog", "install_as_torchair", "clear_weight_cache", "gmm_status", "gmm_status_reset", "routing_status",
            "check_status", "scope",
            "use_internal_format_weight", "patch_for_hcom", "dynamo_export", "register_replacement", "npu_format_cast_via_cpu"]
 

@@ -312,7 +312,20 @@ __global__ void __launch_bounds__(THREADS) dispatch_pack_kernel(const T* __restr
   const int K = a.K, cols = a.cols, num_experts = a.num_experts;
   const int64_t tokens = a.tokens;
   const int nchunk = cols >> 3;
+  // A row's loads do not depend on its positions: they are issued before the ranking so that their latency covers it (with
+  // the sort inside, before the keys of all pairs are read; the first token of a CTA is then already on its way).
+  Raw8<T> raw[kQuant ? kPackChunks : 1];
+  auto load_row = [&](int64_t t) {
+    if constexpr (kQuant) {
+#pragma unroll
+      for (int c = 0; c < kPackChunks; ++c) {
+        const int ch = threadIdx.x + c * THREADS;
+        if (ch < nchunk) raw[c].load(x + t * cols + ch * 8);
+      }
+    }
+  };
   if constexpr (kSortInside) {
+    if (blockIdx.x < tokens) load_row(blockIdx.x);
     const int n = static_cast<int>(tokens) * K;
     const bool last = blockIdx.x == gridDim.x - 1;
     if (last)
@@ -343,6 +356,7 @@ __global__ void __launch_bounds__(THREADS) dispatch_pack_kernel(const T* __restr
   }
   for (int64_t t = blockIdx.x; t < tokens; t += gridDim.x) {
     const T* xr = x + t * cols;
+    if (!kSortInside || t != blockIdx.x) load_row(t);
     __syncthreads();   // previous token's positions are no longer read
     if constexpr (kSortInside) {
       const int n = static_cast<int>(tokens) * K;
@@ -374,12 +388,6 @@ __global__ void __launch_bounds__(THREADS) dispatch_pack_kernel(const T* __restr
     }
     __syncthreads();   // positions (and keys) are published
     if constexpr (kQuant) {
-      Raw8<T> raw[kPackChunks];
-#pragma unroll
-      for (int c = 0; c < kPackChunks; ++c) {
-        const int ch = threadIdx.x + c * THREADS;
-        if (ch < nchunk) raw[c].load(xr + ch * 8);
-      }
       int8_t* out = static_cast<int8_t*>(a.send_rows);
       if constexpr (!kSmooth) {
         float amax = 0.f;
@@ -608,16 +616,22 @@ struct CombineExtra {
 template <typename T, bool kExtra>
 __global__ void __launch_bounds__(256) combine_kernel(const T* __restrict__ rows, const int32_t* __restrict__ expand_idx,
                                                       const float* __restrict__ weights, const T* __restrict__ shared,
-                                                      int64_t tokens, int K, int cols, T* __restrict__ out, const CombineExtra ex) {
+                                                      int64_t tokens, int K, int cols, int slices, T* __restrict__ out,
+                                                      const CombineExtra ex) {
   extern __shared__ int s_meta[];  // [K] positions, [K] weights, [K] special kinds
   int* s_pos = s_meta;
   float* s_w = reinterpret_cast<float*>(s_meta + K);
   int* s_kind = s_meta + 2 * K;    // -1: gathered row; else index among the special experts
-  const int nchunk = cols >> 3;
+  const int nchunk_all = cols >> 3;
+  const int per_slice = (nchunk_all + slices - 1) / slices;
   const int specials = kExtra ? ex.zero_num + ex.copy_num + ex.const_num : 0;
-  for (int64_t t = blockIdx.x; t < tokens; t += gridDim.x) {
+  // work item = (token, column slice): with few tokens a row is cut into slices so that the launch still fills the GPU
+  for (int64_t item = blockIdx.x; item < tokens * slices; item += gridDim.x) {
+    const int64_t t = item / slices;
+    const int ch0 = static_cast<int>(item - t * slices) * per_slice;
+    const int nchunk = min(ch0 + per_slice, nchunk_all);
     if (kExtra && ex.mask != nullptr && ex.mask[t] == 0) {     // uniform over the CTA
-      for (int ch = threadIdx.x; ch < nchunk; ch += 256) *reinterpret_cast<uint4*>(out + t * cols + ch * 8) = make_uint4(0, 0, 0, 0);
+      for (int ch = ch0 + threadIdx.x; ch < nchunk; ch += 256) *reinterpret_cast<uint4*>(out + t * cols + ch * 8) = make_uint4(0, 0, 0, 0);
       continue;
     }
     __syncthreads();
@@ -630,7 +644,7 @@ __global__ void __launch_bounds__(256) combine_kernel(const T* __restrict__ rows
       }
     }
     __syncthreads();
-    for (int ch = threadIdx.x; ch < nchunk; ch += 256) {
+    for (int ch = ch0 + threadIdx.x; ch < nchunk; ch += 256) {
       float acc[8];
 #pragma unroll 4
       for (int k = 0; k < K; ++k) {
@@ -861,14 +875,17 @@ extern "C" int tab_moe_combine_ex(const void* rows, int dtype, const int32_t* ex
                                !aligned16(const_expert_alpha_2) || !aligned16(const_expert_v)))
     return fail(TAB_ERR_BAD_ARG, "combine: constant experts need alpha_1, alpha_2 and v (16-byte aligned)");
   cudaStream_t st = as_stream(stream);
-  const int grid = grid_for(T, 8);
+  // few tokens: cut every row into slices of at least 128 16-byte chunks until the launch has about four CTAs per SM
+  int slices = 1;
+  while (T * slices < 4 * kNumSMs && (H / 8) / (slices * 2) >= 128) slices *= 2;
+  const int grid = grid_for(T * slices, 8);
   const size_t smem = static_cast<size_t>(K) * 12;
   const bool extra = x_active_mask != nullptr || specials > 0;
   const CombineExtra ex = {x_active_mask, expert_ids, (int)num_experts, (int)zero_expert_num, (int)copy_expert_num, (int)const_expert_num,
                            ori_x, const_expert_alpha_1, const_expert_alpha_2, const_expert_v};
 #define TAB_COMBINE(TYPE, EX)                                                                                                   \
   combine_kernel<TYPE, EX><<<grid, 256, smem, st>>>(static_cast<const TYPE*>(rows), expand_idx, expert_scales,                  \
-                                                    static_cast<const TYPE*>(shared), T, (int)K, (int)H, static_cast<TYPE*>(out), ex)
+                                                    static_cast<const TYPE*>(shared), T, (int)K, (int)H, slices, static_cast<TYPE*>(out), ex)
   if (dtype == TAB_BF16) {
     if (extra) TAB_COMBINE(__nv_bfloat16, true); else TAB_COMBINE(__nv_bfloat16, false);
   } else if (dtype == TAB_F16) {

@@ -25,6 +25,7 @@ import torch
 import torch.distributed as dist
 
 from . import _lib
+from .watchdog import EpGroupFailed, EpWatchdog, backend_abort
 
 _ST_INV = {torch.int8: 1, torch.int32: 3, torch.float16: 5, torch.float32: 6, torch.bfloat16: 15}
 
@@ -39,15 +40,22 @@ counters = {"dispatch_calls": 0, "combine_calls": 0, "wire_bytes_sent": 0}
 _transport: Dict[str, str] = {}
 _peer: Dict[tuple, "PeerExchange"] = {}
 _last_dispatch: Dict[tuple, "PeerExchange"] = {}
+_watchdogs: Dict[str, "EpWatchdog"] = {}
 
 
-def register_ep_group(name: str, process_group, transport: str = "auto") -> None:
+def register_ep_group(name: str, process_group, transport: str = "auto", watchdog=None) -> None:
     """Associates a group_ep name with a torch.distributed process group.
 
     transport: "peer" = rows are stored straight into the owner's receive buffer over NVLink peer memory by this
     library's kernels (one node, CUDA-graph capturable, no host read); "nccl" = all_to_all_single with exact split
     sizes (one host read per dispatch; also the path used for CPU tensors in tests); "auto" = peer for CUDA tensors
     when symmetric memory can be set up, else nccl.  Every rank of the group must pass the same value.
+
+    watchdog: None (off), True, or a dict with any of interval_s, timeout_s, store, device: starts a host thread that
+    exchanges heartbeats with the other ranks through the rendezvous store and follows the events of the exchanges
+    (torchair_b200/watchdog.py).  With it a dispatch / combine raises EpGroupFailed before launching anything once a
+    rank has been silent for timeout_s, and an 'nccl' exchange that does not finish within timeout_s gets its
+    communicator aborted.
     """
     if not isinstance(name, str) or not name:
         raise ValueError("group name must be a non-empty string")
@@ -55,6 +63,32 @@ def register_ep_group(name: str, process_group, transport: str = "auto") -> None
         raise ValueError("transport must be 'auto', 'peer' or 'nccl'")
     _groups[name] = process_group
     _transport[name] = transport
+    old = _watchdogs.pop(name, None)
+    if old is not None:
+        old.stop()
+    if watchdog:
+        opts = dict(watchdog) if isinstance(watchdog, dict) else {}
+        store = opts.pop("store", None) or dist.distributed_c10d._get_default_store()
+        device = opts.pop("device", None)
+        if device is None:
+            device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+        _watchdogs[name] = EpWatchdog(name, store, dist.get_rank(process_group), dist.get_world_size(process_group),
+                                      abort=backend_abort(process_group, device), **opts).start()
+
+
+def watchdog_of(name: str):
+    """The running watchdog of a registered group, or None."""
+    return _watchdogs.get(name)
+
+
+def _watch(group_ep, tensor, what):
+    """Hands the watchdog an event recorded after the collectives that were just enqueued (eager CUDA work only)."""
+    wd = _watchdogs.get(group_ep)
+    if wd is None or not tensor.is_cuda or torch.cuda.is_current_stream_capturing():
+        return
+    ev = torch.cuda.Event()
+    ev.record(torch.cuda.current_stream(tensor.device))
+    wd.watch(ev, what)
 
 
 def transport_of(name: str, is_cuda: bool) -> str:
@@ -378,6 +412,9 @@ def combine_from_producer(kern, produce_rows, rows, H, dtype, expert_ids, expand
     px = _last_dispatch.get((group_ep, R, rank, T, K, H, E, expand_idx.device.index))
     if px is None:
         raise RuntimeError("npu_moe_distribute_combine: no matching npu_moe_distribute_dispatch ran on this group")
+    wd = _watchdogs.get(group_ep)
+    if wd is not None:
+        wd.check()
     st = px._stream()
     row_dst = torch.empty((rows,), dtype=torch.int64, device=expand_idx.device)
     # address table from ep_send_counts in one launch; its first CTA also waits until the sources have reduced the rows of
@@ -451,6 +488,9 @@ def dispatch(kern, x, expert_ids, group_ep, R, rank, E, quant_mode, nums_type, t
         return send_rows, send_scales, expand_idx, nums, counts, tp_recv, expand_scales
 
     pg = get_ep_group(group_ep)
+    wd = _watchdogs.get(group_ep)
+    if wd is not None:
+        wd.check()                      # a rank that is gone: raise before enqueueing work that would wait for it
     if dist.get_world_size(pg) != R or dist.get_rank(pg) != rank:
         raise RuntimeError(f"npu_moe_distribute_dispatch: group {group_ep!r} has size/rank "
                            f"{dist.get_world_size(pg)}/{dist.get_rank(pg)}, arguments say {R}/{rank}")
@@ -475,6 +515,7 @@ def dispatch(kern, x, expert_ids, group_ep, R, rank, E, quant_mode, nums_type, t
     plan, nums, ep_recv = kern.exchange_plan(recv_counts.view(R, E_l), R, E_l, 0, nums_type)
     expand_x, dyn_scales = kern.exchange_rows(wire_rows, wire_scales, plan, R, E_l, 0, 0, A, False)
     _remember((ep_recv.data_ptr(), expand_idx.data_ptr()), (send_splits, recv_splits))
+    _watch(group_ep, expand_x, "the dispatch exchange")
     return expand_x, dyn_scales, expand_idx, nums, ep_recv, tp_recv, expand_scales
 
 
@@ -489,6 +530,9 @@ def combine(kern, expand_x, expert_ids, expand_idx, ep_send_counts, expert_scale
     if R == 1:
         return kern.combine(expand_x, expand_idx, expert_scales, shared, T, K, mask, special)
     pg = get_ep_group(group_ep)
+    wd = _watchdogs.get(group_ep)
+    if wd is not None:
+        wd.check()
     E_l = E // R
     if transport_of(group_ep, expand_x.is_cuda) == "peer":
         return _combine_peer(kern, expand_x, expert_ids, expand_idx, ep_send_counts, expert_scales, group_ep, pg, R, rank, E, shared,
@@ -511,4 +555,6 @@ def combine(kern, expand_x, expert_ids, expand_idx, ep_send_counts, expert_scale
     back = torch.empty((T * K, H), dtype=expand_x.dtype, device=expand_x.device)
     dist.all_to_all_single(back[:sum(send_splits)], wire, send_splits, recv_splits, group=pg)
     counters["wire_bytes_sent"] += (total - recv_splits[rank]) * H * expand_x.element_size()
-    return kern.combine(back, expand_idx, expert_scales, shared, T, K, mask, special)
+    out = kern.combine(back, expand_idx, expert_scales, shared, T, K, mask, special)
+    _watch(group_ep, out, "the combine exchange")
+    return out
