@@ -71,6 +71,22 @@ def _worker(rank, world, port, outdir, transport):
         results["status"] = torchair_b200.gmm_status(dev)
         from torchair_b200 import ep as _ep
         results["peer_status"] = _ep.peer_status()
+        if transport == "peer":
+            # one exchange, two streams: the second stream's call arrives while the first one's work is still pending
+            # (behind a 0.2 s device-side delay) and must be refused on the host, before anything is launched
+            xd, idd = x.to(dev), ids.to(dev)
+            side = torch.cuda.Stream(dev)
+            torch.cuda.synchronize(dev)
+            torch.cuda._sleep(400_000_000)
+            torch.ops.npu.npu_moe_distribute_dispatch(xd, idd, "ep", world, rank, cfg.E, quant_mode=2)
+            try:
+                with torch.cuda.stream(side):
+                    torch.ops.npu.npu_moe_distribute_dispatch(xd, idd, "ep", world, rank, cfg.E, quant_mode=2)
+                results["two_streams"] = "accepted"
+            except RuntimeError as exc:
+                results["two_streams"] = str(exc)
+            torch.cuda.synchronize(dev)
+            results["peer_status_after"] = _ep.peer_status()
         torch.save(results, os.path.join(outdir, f"rank{rank}.pt"))
         dist.barrier()
         dist.destroy_process_group()
@@ -128,6 +144,9 @@ def test_expert_parallel_layer_on_gpus_matches_oracle(world, transport, tmp_path
             # fused gate_up and (over peer memory) the down GEMM storing into the senders' buffers change no bit
             assert torch.equal(got[r][(cfg_name, True)], got[r][(cfg_name, False)])
             assert torch.equal(got[r][(cfg_name, True)], got[r][(cfg_name, False)])
+            if transport == "peer":
+                assert "two group names" in got[r]["two_streams"], got[r]["two_streams"]
+                assert got[r]["peer_status_after"] == 0
             if cfg_name == "cfg0":
                 assert torch.equal(got[r]["compiled"], got[r][(cfg_name, False)]), "compiled and eager layers must agree"
                 assert got[r]["captures"] == (1 if transport == "peer" else 0)

@@ -960,3 +960,34 @@ def test_cta_pair_gemm_fused_gate_up_is_bit_exact(dev, counts, Kd, I):
     _swiglu_quant_equal(hq[:covered], hs[:covered], q_ref[:covered], s_ref[:covered])
     hq1, hs1 = npu.npu_grouped_matmul_swiglu_quant_v2(xd, [wd], [wsd], xsd, cd, group_list_type=1, tuning_config=[300])
     assert torch.equal(hq1[:covered], hq[:covered]) and torch.equal(hs1[:covered], hs[:covered])
+
+
+def test_weights_can_be_held_once_in_the_packed_layout(dev):
+    """use_internal_format_weight(model, release_original=True) turns every int8 [E, K, N] expert weight into an [E, K, N]
+    view of its K-major relayout: same values element for element, the grouped GEMM uses the buffer underneath without
+    another relayout or a cache entry, and its results do not change by a bit."""
+    import torchair_b200
+    E, Kd, N, M = 4, 256, 384, 96
+    g = torch.Generator().manual_seed(5)
+    w = torch.randint(-127, 128, (E, Kd, N), generator=g, dtype=torch.int8)
+    x = torch.randint(-127, 128, (M, Kd), generator=g, dtype=torch.int8)
+    cnt = torch.tensor([20, 0, 50, 26], dtype=torch.int64)
+
+    class Experts(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.w = torch.nn.Parameter(w.to(dev), requires_grad=False)
+
+    m = Experts()
+    before = npu.npu_grouped_matmul([x.to(dev)], [m.w], group_list=cnt.to(dev), split_item=2, group_type=0, group_list_type=1,
+                                    output_dtype=3)[0].cpu()
+    old_ptr = m.w.data_ptr()
+    torchair_b200.use_internal_format_weight(m, release_original=True)
+    assert m.w.shape == (E, Kd, N) and m.w.stride() == (Kd * N, 1, Kd) and m.w.data_ptr() != old_ptr
+    assert torch.equal(m.w.cpu(), w)                                         # the same tensor, element for element
+    assert ops.packed_weight(m.w).data_ptr() == m.w.data_ptr() and len(ops._packed_cache) == 0
+    after = npu.npu_grouped_matmul([x.to(dev)], [m.w], group_list=cnt.to(dev), split_item=2, group_type=0, group_list_type=1,
+                                   output_dtype=3)[0].cpu()
+    covered = int(cnt.sum())
+    assert torch.equal(before[:covered], after[:covered])
+    assert torch.equal(after[:covered], O.grouped_matmul_w8a8(x, w, None, None, cnt, 1, 3)[:covered])

@@ -300,6 +300,28 @@ class PeerExchange:
     def _stream(self):
         return ctypes.c_void_p(torch.cuda.current_stream(self.buf.device).cuda_stream)
 
+    def enter(self):
+        """Buffers and flag counters of one exchange are used in call order, which only one stream at a time can give.
+        Outside CUDA-graph capture this is checked: a call from another stream while the previous call's work is still
+        pending raises (use a second group name for the second stream).  Inside a capture the graph's own edges order
+        the work, and nothing is checked."""
+        dev = self.buf.device
+        if torch.cuda.is_current_stream_capturing():
+            return
+        sid = torch.cuda.current_stream(dev).cuda_stream
+        last = getattr(self, "_last", None)
+        if last is not None and last[0] != sid and not last[1].query():
+            raise RuntimeError("expert-parallel exchange over peer memory: this (group, shape) is still busy on another stream; "
+                               "exchanges that overlap on two streams need two group names (register_ep_group twice)")
+
+    def leave(self):
+        if torch.cuda.is_current_stream_capturing():
+            return
+        st = torch.cuda.current_stream(self.buf.device)
+        ev = torch.cuda.Event()
+        ev.record(st)
+        self._last = (st.cuda_stream, ev)
+
     def signal(self, kind):
         _lib.call("tab_ep_signal", _ptr(self.peer_flags[kind]), ctypes.c_void_p(self.sig_counter[kind]), self.R, self._stream())
 
@@ -350,6 +372,7 @@ def _dispatch_peer(kern, x, expert_ids, group_ep, pg, R, rank, E, quant_mode, nu
     row_bytes = H * send_rows.element_size()
     px = peer_exchange(group_ep, pg, R, rank, t_slot, K, H, E, row_bytes, dev)
     _last_dispatch[(group_ep, R, rank, T, K, H, E, dev.index)] = px     # the matching combine returns through the same buffers
+    px.enter()
     A = R * px.C
     st = px._stream()
     slot_idx = torch.empty_like(expand_idx)
@@ -367,6 +390,7 @@ def _dispatch_peer(kern, x, expert_ids, group_ep, pg, R, rank, E, quant_mode, nu
               _ptr(expand_x), _ptr(dyn), _ptr(nums), _ptr(ep_recv), _ptr(px.peer_flags[px.KIND_ACK_D]),
               ctypes.c_void_p(px.sig_counter[px.KIND_ACK_D]), ctypes.c_void_p(px.done_ptr), st)
     counters["wire_bytes_sent"] += T * K * (row_bytes + 16)
+    px.leave()
     return expand_x, dyn, slot_idx, nums, ep_recv, tp_recv, expand_scales
 
 
@@ -380,6 +404,7 @@ def _combine_peer(kern, expand_x, expert_ids, expand_idx, ep_send_counts, expert
     px = _last_dispatch.get((group_ep, R, rank, T, K, H, E, expand_x.device.index))
     if px is None:
         raise RuntimeError("npu_moe_distribute_combine: no matching npu_moe_distribute_dispatch ran on this group")
+    px.enter()
     st = px._stream()
     y = expand_x.contiguous()
     recv_counts = ep_send_counts.view(E_l, R).t().contiguous()
@@ -392,6 +417,7 @@ def _combine_peer(kern, expand_x, expert_ids, expand_idx, ep_send_counts, expert
     out = kern.combine(back, expand_idx, expert_scales, shared, T, K, mask, special)
     px.signal(px.KIND_ACK_C)
     counters["wire_bytes_sent"] += T * K * H * 2
+    px.leave()
     return out
 
 
@@ -415,6 +441,7 @@ def combine_from_producer(kern, produce_rows, rows, H, dtype, expert_ids, expand
     wd = _watchdogs.get(group_ep)
     if wd is not None:
         wd.check()
+    px.enter()
     st = px._stream()
     row_dst = torch.empty((rows,), dtype=torch.int64, device=expand_idx.device)
     # address table from ep_send_counts in one launch; its first CTA also waits until the sources have reduced the rows of
@@ -428,6 +455,7 @@ def combine_from_producer(kern, produce_rows, rows, H, dtype, expert_ids, expand
     out = kern.combine(back, expand_idx, expert_scales, shared, T, K, mask, special)
     px.signal(px.KIND_ACK_C)
     counters["wire_bytes_sent"] += T * K * H * 2
+    px.leave()
     return out
 
 

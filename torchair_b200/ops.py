@@ -294,6 +294,10 @@ def packed_weight(weight: torch.Tensor) -> torch.Tensor:
     finaliser when the storage is freed, so a new tensor that reuses the address never sees a stale relayout)
     and to the tensor's version counter (an in-place update of the weights triggers a fresh relayout).
     """
+    if weight.dim() == 3 and weight.shape[1] > 1 and weight.shape[2] > 1 and weight.permute(0, 2, 1).is_contiguous():
+        # already K-major underneath: an [E, Kd, N] view of a packed [E, N, Kd] buffer, as use_internal_format_weight(...,
+        # release_original=True) leaves it.  Nothing to relay out, nothing to cache.
+        return weight.permute(0, 2, 1)
     storage = weight.untyped_storage()
     ident = (storage._cdata, weight.storage_offset(), tuple(weight.shape), tuple(weight.stride()))
     hit = _packed_cache.get(ident)
