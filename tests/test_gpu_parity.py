@@ -991,3 +991,83 @@ def test_weights_can_be_held_once_in_the_packed_layout(dev):
     covered = int(cnt.sum())
     assert torch.equal(before[:covered], after[:covered])
     assert torch.equal(after[:covered], O.grouped_matmul_w8a8(x, w, None, None, cnt, 1, 3)[:covered])
+
+
+_PAIR_TAILS = [256 + 16, 512 + 17, 256 + 33, 48, 64, 65 + 256, 256 + 63, 0, 9]
+
+
+@pytest.mark.parametrize("Kd,N", [(256, 512), (144, 264)])
+def test_cta_pair_narrow_tail_tiles_plain_are_bit_exact(dev, Kd, N):
+    """On CTA pairs an expert's last tile with at most 64 rows is computed with the operands swapped (weights as the 256-row
+    operand, 16..64 tokens as N, each CTA loading half of them).  Tails of 9, 16, 17, 33, 48, 63 and 64 rows take that form,
+    65 rows the wide one; raw int32, scaled bf16 with bias, against the oracle and against the one-CTA kernel."""
+    counts = _PAIR_TAILS
+    E, covered = len(counts), sum(counts)
+    M = covered + 11
+    g = torch.Generator().manual_seed(Kd * 5 + N)
+    x = torch.randint(-127, 128, (M, Kd), generator=g, dtype=torch.int8)
+    w = torch.randint(-127, 128, (E, Kd, N), generator=g, dtype=torch.int8)
+    sc = torch.rand(E, N, generator=g) * 9e-3 + 1e-3
+    pts = torch.rand(M, generator=g) * 1e-2
+    bias = torch.randint(-50000, 50000, (E, N), generator=g, dtype=torch.int32)
+    cnt = torch.tensor(counts, dtype=torch.int64)
+    xd, wd, cd = x.to(dev), w.to(dev), cnt.to(dev)
+    hint = [1000]
+    h32 = npu.npu_grouped_matmul([xd], [wd], group_list=cd, split_item=2, group_type=0, group_list_type=1, output_dtype=3,
+                                 tuning_config=hint)[0]
+    _gmm_ok(dev)
+    assert torch.equal(O.grouped_matmul_w8a8(x, w, None, None, cnt, 1, 3)[:covered], h32.cpu()[:covered])
+    for dt, code in ((torch.bfloat16, 15), (torch.float16, 5)):
+        got = npu.npu_grouped_matmul([xd], [wd], bias=[bias.to(dev)], scale=[sc.to(dev)], per_token_scale=[pts.to(dev)], group_list=cd,
+                                     split_item=2, group_type=0, group_list_type=1, output_dtype=code, tuning_config=hint)[0]
+        _gmm_ok(dev)
+        ref = O.grouped_matmul_w8a8(x, w, sc, pts, cnt, 1, code, bias=bias)
+        assert torch.equal(ref[:covered], got.cpu()[:covered])
+        one = npu.npu_grouped_matmul([xd], [wd], bias=[bias.to(dev)], scale=[sc.to(dev)], per_token_scale=[pts.to(dev)], group_list=cd,
+                                     split_item=2, group_type=0, group_list_type=1, output_dtype=code, tuning_config=[100])[0]
+        assert torch.equal(one[:covered], got[:covered])
+
+
+@pytest.mark.parametrize("Kd,I,left", [(512, 256, True), (256, 136, True), (256, 192, False)])
+def test_cta_pair_narrow_tail_tiles_fused_are_bit_exact(dev, Kd, I, left):
+    """The fused gate_up on narrow pair tiles: a CTA's accumulator lanes hold 64 gate channels and the 64 matching up channels,
+    the up warps hand their values to the gate warps through shared memory.  Against the oracle (both activation orders)
+    and against the one-CTA kernel."""
+    counts = _PAIR_TAILS
+    E, covered = len(counts), sum(counts)
+    M = covered + 5
+    g = torch.Generator().manual_seed(Kd + 11 * I)
+    x = torch.randint(-127, 128, (M, Kd), generator=g, dtype=torch.int8)
+    w = torch.randint(-127, 128, (E, Kd, 2 * I), generator=g, dtype=torch.int8)
+    ws = torch.rand(E, 2 * I, generator=g) * 9e-3 + 1e-3
+    xs = torch.rand(M, generator=g) * 1e-2
+    cnt = torch.tensor(counts, dtype=torch.int64)
+    xd, wd, wsd, xsd, cd = x.to(dev), w.to(dev), ws.to(dev), xs.to(dev), cnt.to(dev)
+    h32 = O.grouped_matmul_w8a8(x, w, None, None, cnt, 1, 3)
+    if left:
+        for _ in range(2):
+            hq, hs = npu.npu_grouped_matmul_swiglu_quant_v2(xd, [wd], [wsd], xsd, cd, group_list_type=1, tuning_config=[1000])
+        _gmm_ok(dev)
+        q_ref, s_ref = O.dequant_swiglu_quant(h32, ws, xs, cnt, True, 1)
+        _swiglu_quant_equal(hq[:covered], hs[:covered], q_ref[:covered], s_ref[:covered])
+        hq1, hs1 = npu.npu_grouped_matmul_swiglu_quant_v2(xd, [wd], [wsd], xsd, cd, group_list_type=1, tuning_config=[100])
+        assert torch.equal(hq1[:covered], hq[:covered]) and torch.equal(hs1[:covered], hs[:covered])
+    else:
+        # activate_left=False through the C entry point (the fused operator of the reference has no such argument)
+        import ctypes
+        from torchair_b200 import _lib
+        wp = ops.packed_weight(wd)
+        nbytes = _lib.workspace_bytes("tab_grouped_matmul_swiglu_quant_workspace_bytes", M, I)
+        wsp = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+        P = lambda t: ctypes.c_void_p(t.data_ptr())
+        outs = []
+        for hint in (1000, 100):
+            yq = torch.zeros((M, I), dtype=torch.int8, device=dev)
+            ys = torch.zeros((M,), dtype=torch.float32, device=dev)
+            _lib.call("tab_grouped_matmul_swiglu_quant", P(xd), P(wp), P(wsd), P(xsd), P(cd), 1, M, Kd, I, E, 0, P(yq), P(ys), P(wsp),
+                      nbytes, hint, ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+            _gmm_ok(dev)
+            outs.append((yq.cpu(), ys.cpu()))
+        q_ref, s_ref = O.dequant_swiglu_quant(h32, ws, xs, cnt, False, 1)
+        _swiglu_quant_equal(outs[0][0][:covered], outs[0][1][:covered], q_ref[:covered], s_ref[:covered])
+        assert torch.equal(outs[0][0][:covered], outs[1][0][:covered]) and torch.equal(outs[0][1][:covered], outs[1][1][:covered])

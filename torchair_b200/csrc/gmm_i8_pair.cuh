@@ -23,8 +23,16 @@
 // Only the leader issues MMAs.  Tensor memory is allocated and released by each CTA with the cta_group::2 forms.
 // Every wait is bounded as in the other kernels; a CTA that gives up records its code, skips to the end, and the final
 // hand-shake between the two CTAs (each tells the other that it no longer touches the pair's shared state) is bounded
-// too.  Tiles are 256 tokens: an expert's last tile is computed in full whatever its rows, so this kernel is chosen by
-// the host only when experts are expected to hold many rows (see use_pair in gmm_i8.cu).
+// too.
+//
+// Narrow tiles.  Tiles are 256 tokens; an expert's last tile with at most 64 rows (kPairNarrowMax) would waste nearly a
+// whole tile of MMA work, so it is computed with the operands swapped, out of the same shared-memory stages: each CTA's
+// half of the weight tile (128 rows) is its half of the 256-row operand, the tokens are the N operand with N = rows
+// rounded up to 16, every CTA loading half of them.  An accumulator lane is then a channel and a column a token; the
+// epilogue does the same arithmetic per element, so results do not depend on the form a tile took.  In the fused
+// gate_up a CTA's lanes hold 64 gate channels followed by the 64 matching up channels: the up warps hand their
+// dequantised values to the gate warps through shared memory.  Tails of 65..255 rows still cost a whole tile, so the host
+// chooses this kernel where experts hold many rows or sit just above a multiple of 256 (see use_pair in gmm_i8.cu).
 #pragma once
 
 #include "gmm_common.cuh"
@@ -35,6 +43,8 @@ namespace tab {
 constexpr int kPairTokens = 256;                      // token rows per pair tile
 constexpr int kPairStageBytes = kPfATile + kWTileBytes;   // 16 KB of tokens + 16 KB of weights per CTA
 constexpr int kPairStages = 6;
+constexpr int kPairNarrowMax = 64;                    // last tiles with at most this many rows swap the operands
+static_assert(kPairNarrowMax * 64 * 4 <= kPfOutStageBytes, "the gate/up exchange of a narrow tile uses the output staging area");
 constexpr int kPairSmemBytes = 1024 + kPairStages * kPairStageBytes + kPfCtrlBytes + kPfScaleBytes + kPfTableBytes + kPfOutStageBytes;
 static_assert(kPairSmemBytes <= kSmemLimit, "pair GEMM shared memory");
 static_assert(2 * kPairStages * 8 + 2 * kPfBufs * 8 + 16 <= 224, "barriers overflow the control block");
@@ -109,6 +119,93 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
 
 }  // namespace ptx
 
+// Epilogue of a narrow tile on a pair (operands swapped): this thread's TMEM lane l is a channel of this CTA's half of the
+// weight tile, columns are the tile's tokens (column j = row tile_start + j).  Plain: channel 256 ct + 128 rank + l.  Fused:
+// lanes 0..63 hold gate channels 128 ct + 64 rank + l, lanes 64..127 the matching up channels; the up warps (lane quarters
+// 2, 3) write their dequantised values to `xchg` [token][64], all eight warps meet, the gate warps finish.  The two warps
+// of a lane quarter alternate over the 16-token column chunks.  Same arithmetic per element as the wide tiles.
+template <bool FUSED>
+__device__ __forceinline__ void pair_narrow_epilogue(const GmmParams& p, const WorkItem& it, const float* ws, uint32_t t0,
+                                                     int tile_start, int nvalid, int rank, int quarter, int lane, int chalf,
+                                                     float* xchg) {
+  const int nv16 = (nvalid + 15) & ~15;
+  const int l = quarter * 32 + lane;
+  const float wv = ws[rank * 128 + l];
+  if constexpr (FUSED) {
+    const bool is_up = quarter >= 2;
+    const int lc = l & 63;
+    const int ch = it.ct * 128 + rank * 64 + lc;
+    const bool cvalid = ch < p.half;
+    if (is_up) {
+#pragma unroll 1
+      for (int c = chalf * 16; c < nv16; c += 32) {
+        int u[16];
+        __syncwarp();
+        ptx::tmem_ld16(t0 + c, u);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const bool tvalid = c + j < nvalid;           // uniform over the warp
+          const float ts = (tvalid && p.tok_scale) ? p.tok_scale[tile_start + c + j] : 1.f;
+          xchg[(c + j) * 64 + lc] = __fmul_rn(__fmul_rn(__int2float_rn(u[j]), ts), wv);
+        }
+      }
+    }
+    epilogue_bar_sync();
+    if (!is_up) {
+#pragma unroll 1
+      for (int c = chalf * 16; c < nv16; c += 32) {
+        int g[16];
+        __syncwarp();
+        ptx::tmem_ld16(t0 + c, g);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const bool tvalid = c + j < nvalid;
+          const int row = tile_start + c + j;
+          const float ts = (tvalid && p.tok_scale) ? p.tok_scale[row] : 1.f;
+          const float gv = __fmul_rn(__fmul_rn(__int2float_rn(g[j]), ts), wv);
+          const float uv = xchg[(c + j) * 64 + lc];
+          const float h = silu_mul(p.activate_left ? gv : uv, p.activate_left ? uv : gv);
+          if (tvalid) {
+            if (cvalid) __stcs(p.h_out + static_cast<int64_t>(row) * p.half + ch, h);
+            const float m = warp_max(cvalid ? fabsf(h) : 0.f);
+            if (lane == 0) atomicMax(p.amax + row, __float_as_uint(m));
+          }
+        }
+      }
+    }
+  } else {
+    const int ch = it.ct * 256 + rank * 128 + l;
+    const bool cvalid = ch < p.N;
+    const int bias = (cvalid && p.bias) ? p.bias[static_cast<int64_t>(it.e) * p.N + ch] : 0;
+#pragma unroll 1
+    for (int c = chalf * 16; c < nv16; c += 32) {
+      int a[16];
+      __syncwarp();
+      ptx::tmem_ld16(t0 + c, a);
+      ptx::tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        a[j] += bias;
+        const int row = tile_start + c + j;
+        if (c + j < nvalid && cvalid) {
+          if (p.out_dtype == TAB_I32) {
+            static_cast<int*>(p.out)[static_cast<int64_t>(row) * p.N + ch] = a[j];
+          } else {
+            const float ts = p.tok_scale ? p.tok_scale[row] : 1.f;
+            const float f = __fmul_rn(__fmul_rn(__int2float_rn(a[j]), ts), wv);
+            uint8_t* orow = out_row_ptr(p, row, 2);
+            if (orow == nullptr) continue;               // address table says: no destination for this row
+            if (p.out_dtype == TAB_BF16) reinterpret_cast<__nv_bfloat16*>(orow)[ch] = __float2bfloat16_rn(f);
+            else reinterpret_cast<__half*>(orow)[ch] = __float2half_rn(f);
+          }
+        }
+      }
+    }
+  }
+}
+
 template <bool FUSED>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPfThreads, 1)
 gmm_i8_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_w64,
@@ -175,7 +272,11 @@ gmm_i8_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       bool ok = true;
       for (int w = cluster_id; w < total_items && ok; w += num_clusters) {
         const WorkItem it = decode_item(w, p.chan_tiles, E, s_pref);
-        const int row0 = s_start[it.e] + it.tt * kPairTokens + static_cast<int>(rank) * kPfTokens;
+        const int tile_start = s_start[it.e] + it.tt * kPairTokens;
+        const int nvalid = min(kPairTokens, s_start[it.e + 1] - tile_start);
+        // narrow tile: the tokens are the N operand, this CTA brings half of them (the box still holds 128 rows)
+        const int row0 = nvalid <= kPairNarrowMax ? tile_start + static_cast<int>(rank) * (((nvalid + 15) & ~15) >> 1)
+                                                  : tile_start + static_cast<int>(rank) * kPfTokens;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!bounded_wait(bar_empty(stage), phase ^ 1u, s_abort, 21, p.wait_cycles)) { ok = false; break; }
           const uint32_t st = tiles_addr + stage * kPairStageBytes;
@@ -203,15 +304,21 @@ gmm_i8_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       for (int w = cluster_id; w < total_items && ok; w += num_clusters) {
         if (!bounded_wait(bar_tempty(buf), tphase ^ 1u, s_abort, 22, p.wait_cycles)) { ok = false; break; }
         ptx::tc_fence_after();
+        const WorkItem it = decode_item(w, p.chan_tiles, E, s_pref);
+        const int nvalid = min(kPairTokens, s_start[it.e + 1] - (s_start[it.e] + it.tt * kPairTokens));
+        const bool narrow = nvalid <= kPairNarrowMax;
+        const uint32_t idesc_item = narrow ? ptx::idesc_i8(256, (nvalid + 15) & ~15) : idesc;
         const uint32_t d = tmem_base + buf * kPfCols;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!bounded_wait(bar_full(stage), phase, s_abort, 23, p.wait_cycles)) { ok = false; break; }
           ptx::tc_fence_after();
           const uint32_t st = tiles_addr + stage * kPairStageBytes;
-          const uint64_t a = ptx::smem_desc_k128(st);
-          const uint64_t b = ptx::smem_desc_k128(st + kPfATile);
+          const uint64_t tok = ptx::smem_desc_k128(st);
+          const uint64_t wgt = ptx::smem_desc_k128(st + kPfATile);
+          const uint64_t a = narrow ? wgt : tok;             // narrow: the weights are the 256-row operand
+          const uint64_t b = narrow ? tok : wgt;
 #pragma unroll
-          for (int k = 0; k < kBlockK / 32; ++k) ptx::mma_i8_pair(d, a + 2 * k, b + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          for (int k = 0; k < kBlockK / 32; ++k) ptx::mma_i8_pair(d, a + 2 * k, b + 2 * k, idesc_item, (kb | k) != 0 ? 1u : 0u);
           ptx::mma_commit_pair(bar_empty(stage));
           if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
         }
@@ -255,13 +362,17 @@ gmm_i8_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       epilogue_bar_sync();
       if (!s_got[buf]) break;
       ptx::tc_fence_after();
-      const int tile_row0 = s_start[it.e] + it.tt * kPairTokens + static_cast<int>(rank) * kPfTokens;
+      const int tile_start = s_start[it.e] + it.tt * kPairTokens;
+      const int tile_row0 = tile_start + static_cast<int>(rank) * kPfTokens;
       const int row_end = s_start[it.e + 1];
       const int row = tile_row0 + r_local;
       const bool rvalid = row < row_end;
       const float ts = (rvalid && p.tok_scale) ? p.tok_scale[row] : 1.f;
       const uint32_t t0 = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kPfCols;
-      if (tile_row0 < row_end) {                     // (a tile whose second half holds no rows leaves the peer nothing to store)
+      if (row_end - tile_start <= kPairNarrowMax) {
+        pair_narrow_epilogue<FUSED>(p, it, ws, t0, tile_start, row_end - tile_start, static_cast<int>(rank), quarter, lane, chalf,
+                                    reinterpret_cast<float*>(s_out));
+      } else if (tile_row0 < row_end) {              // (a tile whose second half holds no rows leaves the peer nothing to store)
         if constexpr (FUSED) {
           // this warp takes the gate/up block of CTA `chalf`: accumulator columns [128 chalf, +64) and [128 chalf + 64, +64)
           const int cg0 = it.ct * 128 + chalf * 64;
