@@ -291,6 +291,17 @@ TAB_API int tab_moe_combine_ex(const void* rows, int dtype, const int32_t* expan
                        const int32_t* expert_ids, int64_t num_experts, int64_t zero_expert_num, int64_t copy_expert_num,
                        int64_t const_expert_num, const void* ori_x, const void* const_expert_alpha_1,
                        const void* const_expert_alpha_2, const void* const_expert_v, tab_stream_t stream);
+/* tab_moe_combine_ack: tab_moe_combine_ex as the last step of a combine over peer memory (tab_ep_* below): when every CTA has
+ *   read its rows, the last one stores the next sequence number (ack_sig_counter + 1, device counter, updated) into the flag
+ *   slots ack_peer_flags[0..ack_ranks) of the peers, telling them that their stores into this rank's return buffer may go
+ *   on; done_counter is a zero-initialised device word the CTAs count in (it is zero again afterwards).  Saves the
+ *   separate tab_ep_signal launch.  T must be positive. */
+TAB_API int tab_moe_combine_ack(const void* rows, int dtype, const int32_t* expand_idx, const float* expert_scales,
+                        const void* shared, int64_t T, int64_t K, int64_t H, void* out, const uint8_t* x_active_mask,
+                        const int32_t* expert_ids, int64_t num_experts, int64_t zero_expert_num, int64_t copy_expert_num,
+                        int64_t const_expert_num, const void* ori_x, const void* const_expert_alpha_1,
+                        const void* const_expert_alpha_2, const void* const_expert_v, void* const* ack_peer_flags,
+                        void* ack_sig_counter, void* done_counter, int64_t ack_ranks, tab_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------
  * Operators next to the path.

@@ -47,6 +47,7 @@ SIGNATURES = {
     "tab_ep_return_plan": [_P, _L, _L, _L, _L, _L, _L, _P, _P, _P],
     "tab_moe_combine": [_P, _I, _P, _P, _P, _L, _L, _L, _P, _P],
     "tab_moe_combine_ex": [_P, _I, _P, _P, _P, _L, _L, _L, _P, _P, _P, _L, _L, _L, _L, _P, _P, _P, _P, _P],
+    "tab_moe_combine_ack": [_P, _I, _P, _P, _P, _L, _L, _L, _P, _P, _P, _L, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, _L, _P],
     "tab_prepack_weight_i8": [_P, _L, _L, _L, _P, _P],
     "tab_grouped_matmul_w8a8": [_P, _P, _P, _P, _P, _P, _I, _L, _L, _L, _L, _I, _P, _L, _P],
     "tab_grouped_matmul_w8a8_scatter": [_P, _P, _P, _P, _P, _I, _L, _L, _L, _L, _I, _P, _L, _P],

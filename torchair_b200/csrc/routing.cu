@@ -609,6 +609,12 @@ struct CombineExtra {
   const void* alpha_1;         // [const_num, H]
   const void* alpha_2;         // [const_num, H]
   const void* const_v;         // [const_num, H]
+  // expert-parallel combine over peer memory: once every CTA has read its rows, the last one tells the ack_ranks peers
+  // (flag slots ack_peer_flags[r], next sequence number from ack_sig_counter) that their return buffers may be reused
+  unsigned long long* const* ack_peer_flags;
+  unsigned long long* ack_sig_counter;
+  unsigned int* done_counter;
+  int ack_ranks;
 };
 
 // out[t] = sum_k w[t,k] * rows[idx[t*K+k]] (+ shared[t]); fp32, separate multiply and add, ascending k.  A negative
@@ -686,6 +692,22 @@ __global__ void __launch_bounds__(256) combine_kernel(const T* __restrict__ rows
         for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], v[i]);
       }
       Elem<T>::store8(out + t * cols + ch * 8, acc);
+    }
+  }
+  if (ex.ack_peer_flags != nullptr) {
+    __shared__ int s_last;
+    __syncthreads();                       // every thread's loads of the returned rows have been consumed
+    if (threadIdx.x == 0) {
+      __threadfence();
+      s_last = atomicInc(ex.done_counter, gridDim.x - 1) == gridDim.x - 1 ? 1 : 0;   // wraps to 0 for the next launch
+    }
+    __syncthreads();
+    if (s_last) {
+      const unsigned long long v = *ex.ack_sig_counter + 1;
+      __syncthreads();
+      if (threadIdx.x < ex.ack_ranks)
+        asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(ex.ack_peer_flags[threadIdx.x]), "l"(v) : "memory");
+      if (threadIdx.x == 0) *ex.ack_sig_counter = v;
     }
   }
 }
@@ -857,11 +879,14 @@ extern "C" int tab_moe_exchange_rows(const void* src, const float* src_scales, c
   return check_launch("exchange_rows");
 }
 
-extern "C" int tab_moe_combine_ex(const void* rows, int dtype, const int32_t* expand_idx, const float* expert_scales,
-                                  const void* shared, int64_t T, int64_t K, int64_t H, void* out, const uint8_t* x_active_mask,
-                                  const int32_t* expert_ids, int64_t num_experts, int64_t zero_expert_num, int64_t copy_expert_num,
-                                  int64_t const_expert_num, const void* ori_x, const void* const_expert_alpha_1,
-                                  const void* const_expert_alpha_2, const void* const_expert_v, tab_stream_t stream) {
+static int combine_impl(const void* rows, int dtype, const int32_t* expand_idx, const float* expert_scales,
+                        const void* shared, int64_t T, int64_t K, int64_t H, void* out, const uint8_t* x_active_mask,
+                        const int32_t* expert_ids, int64_t num_experts, int64_t zero_expert_num, int64_t copy_expert_num,
+                        int64_t const_expert_num, const void* ori_x, const void* const_expert_alpha_1,
+                        const void* const_expert_alpha_2, const void* const_expert_v, void* const* ack_peer_flags,
+                        void* ack_sig_counter, void* done_counter, int64_t ack_ranks, tab_stream_t stream) {
+  if (ack_peer_flags != nullptr && (T <= 0 || !ack_sig_counter || !done_counter || ack_ranks < 1 || ack_ranks > 256))
+    return fail(TAB_ERR_BAD_ARG, "combine: the acknowledgement needs T > 0, both counters and 1..256 ranks");
   if (T < 0 || K <= 0 || K > 1024 || H <= 0) return fail(TAB_ERR_BAD_ARG, "combine: T=%lld K=%lld H=%lld", (long long)T, (long long)K, (long long)H);
   if (T == 0) return TAB_OK;
   if (!rows || !expand_idx || !expert_scales || !out) return fail(TAB_ERR_BAD_ARG, "combine: null pointer");
@@ -882,7 +907,9 @@ extern "C" int tab_moe_combine_ex(const void* rows, int dtype, const int32_t* ex
   const size_t smem = static_cast<size_t>(K) * 12;
   const bool extra = x_active_mask != nullptr || specials > 0;
   const CombineExtra ex = {x_active_mask, expert_ids, (int)num_experts, (int)zero_expert_num, (int)copy_expert_num, (int)const_expert_num,
-                           ori_x, const_expert_alpha_1, const_expert_alpha_2, const_expert_v};
+                           ori_x, const_expert_alpha_1, const_expert_alpha_2, const_expert_v,
+                           reinterpret_cast<unsigned long long* const*>(ack_peer_flags), static_cast<unsigned long long*>(ack_sig_counter),
+                           static_cast<unsigned int*>(done_counter), (int)ack_ranks};
 #define TAB_COMBINE(TYPE, EX)                                                                                                   \
   combine_kernel<TYPE, EX><<<grid, 256, smem, st>>>(static_cast<const TYPE*>(rows), expand_idx, expert_scales,                  \
                                                     static_cast<const TYPE*>(shared), T, (int)K, (int)H, slices, static_cast<TYPE*>(out), ex)
@@ -895,6 +922,28 @@ extern "C" int tab_moe_combine_ex(const void* rows, int dtype, const int32_t* ex
   }
 #undef TAB_COMBINE
   return check_launch("combine");
+}
+
+extern "C" int tab_moe_combine_ex(const void* rows, int dtype, const int32_t* expand_idx, const float* expert_scales,
+                                  const void* shared, int64_t T, int64_t K, int64_t H, void* out, const uint8_t* x_active_mask,
+                                  const int32_t* expert_ids, int64_t num_experts, int64_t zero_expert_num, int64_t copy_expert_num,
+                                  int64_t const_expert_num, const void* ori_x, const void* const_expert_alpha_1,
+                                  const void* const_expert_alpha_2, const void* const_expert_v, tab_stream_t stream) {
+  return combine_impl(rows, dtype, expand_idx, expert_scales, shared, T, K, H, out, x_active_mask, expert_ids, num_experts, zero_expert_num,
+                      copy_expert_num, const_expert_num, ori_x, const_expert_alpha_1, const_expert_alpha_2, const_expert_v, nullptr,
+                      nullptr, nullptr, 0, stream);
+}
+
+extern "C" int tab_moe_combine_ack(const void* rows, int dtype, const int32_t* expand_idx, const float* expert_scales,
+                                   const void* shared, int64_t T, int64_t K, int64_t H, void* out, const uint8_t* x_active_mask,
+                                   const int32_t* expert_ids, int64_t num_experts, int64_t zero_expert_num, int64_t copy_expert_num,
+                                   int64_t const_expert_num, const void* ori_x, const void* const_expert_alpha_1,
+                                   const void* const_expert_alpha_2, const void* const_expert_v, void* const* ack_peer_flags,
+                                   void* ack_sig_counter, void* done_counter, int64_t ack_ranks, tab_stream_t stream) {
+  if (!ack_peer_flags) return fail(TAB_ERR_BAD_ARG, "combine_ack: null flag table");
+  return combine_impl(rows, dtype, expand_idx, expert_scales, shared, T, K, H, out, x_active_mask, expert_ids, num_experts, zero_expert_num,
+                      copy_expert_num, const_expert_num, ori_x, const_expert_alpha_1, const_expert_alpha_2, const_expert_v,
+                      ack_peer_flags, ack_sig_counter, done_counter, ack_ranks, stream);
 }
 
 extern "C" int tab_moe_combine(const void* rows, int dtype, const int32_t* expand_idx, const float* expert_scales,

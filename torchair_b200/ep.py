@@ -224,7 +224,7 @@ class CudaKernels:
         return dst, dst_scales
 
     @staticmethod
-    def combine(rows, expand_idx, expert_scales, shared, T, K, mask=None, special=None):
+    def combine(rows, expand_idx, expert_scales, shared, T, K, mask=None, special=None, ack=None):
         """special: None, or a dict with expert_ids [T, K], E, zero, copy, const, ori_x, alpha_1, alpha_2, const_v."""
         if rows.dtype not in (torch.bfloat16, torch.float16):
             raise NotImplementedError("npu_moe_distribute_combine: expand_x must be bfloat16 or float16")
@@ -236,18 +236,23 @@ class CudaKernels:
             if shared.dtype != rows.dtype or shared.shape != out.shape:
                 raise RuntimeError("npu_moe_distribute_combine: shared_expert_x must match the output")
             shared = shared.contiguous()
-        if mask is None and special is None:
+        if mask is None and special is None and ack is None:
             _lib.call("tab_moe_combine", _ptr(rows), _ST_INV[rows.dtype], _ptr(expand_idx.contiguous()),
                       _ptr(expert_scales.contiguous()), _ptr(shared), T, K, rows.shape[1], _ptr(out), _stream(rows))
             return out
         sp = special or {}
         c = lambda t: None if t is None else t.to(rows.dtype).contiguous()
         ids = sp.get("expert_ids")
-        _lib.call("tab_moe_combine_ex", _ptr(rows), _ST_INV[rows.dtype], _ptr(expand_idx.contiguous()), _ptr(expert_scales.contiguous()),
-                  _ptr(shared), T, K, rows.shape[1], _ptr(out), _ptr(None if mask is None else mask.contiguous()),
-                  _ptr(None if ids is None else ids.contiguous()), int(sp.get("E", 0)), int(sp.get("zero", 0)), int(sp.get("copy", 0)),
-                  int(sp.get("const", 0)), _ptr(c(sp.get("ori_x"))), _ptr(c(sp.get("alpha_1"))), _ptr(c(sp.get("alpha_2"))),
-                  _ptr(c(sp.get("const_v"))), _stream(rows))
+        args = (_ptr(rows), _ST_INV[rows.dtype], _ptr(expand_idx.contiguous()), _ptr(expert_scales.contiguous()),
+                _ptr(shared), T, K, rows.shape[1], _ptr(out), _ptr(None if mask is None else mask.contiguous()),
+                _ptr(None if ids is None else ids.contiguous()), int(sp.get("E", 0)), int(sp.get("zero", 0)), int(sp.get("copy", 0)),
+                int(sp.get("const", 0)), _ptr(c(sp.get("ori_x"))), _ptr(c(sp.get("alpha_1"))), _ptr(c(sp.get("alpha_2"))),
+                _ptr(c(sp.get("const_v"))))
+        if ack is None:
+            _lib.call("tab_moe_combine_ex", *args, _stream(rows))
+        else:   # (device table of the peers' flag slots, signal counter, arrival counter, ranks): the last CTA acknowledges
+            _lib.call("tab_moe_combine_ack", *args, _ptr(ack[0]), ctypes.c_void_p(ack[1]), ctypes.c_void_p(ack[2]), int(ack[3]),
+                      _stream(rows))
         return out
 
 
@@ -337,6 +342,16 @@ class PeerExchange:
                   ctypes.c_void_p(self.flags_local[kind]), ctypes.c_void_p(self.wait_counter[kind]), self.R,
                   ctypes.c_void_p(self.status_ptr), 100 + kind, bump, self._stream())
 
+    def combine_and_acknowledge(self, kern, back, expand_idx, expert_scales, shared, T, K, mask, special):
+        """The weighted sum over the returned rows; its last CTA tells the peers that this rank's return buffer is free
+        again (a separate one-CTA launch when the kernels provider has no such form or the rank holds no token)."""
+        if T > 0 and kern is CudaKernels:
+            ack = (self.peer_flags[self.KIND_ACK_C], self.sig_counter[self.KIND_ACK_C], self.done_ptr, self.R)
+            return kern.combine(back, expand_idx, expert_scales, shared, T, K, mask, special, ack)
+        out = kern.combine(back, expand_idx, expert_scales, shared, T, K, mask, special)
+        self.signal(self.KIND_ACK_C)
+        return out
+
     def status(self) -> int:
         """Synchronises and returns 0, 100 + kind of the first flag wait that ran out of time, or 110 when a sender held
         more rows for one destination than its slot takes (those rows were not sent)."""
@@ -414,8 +429,7 @@ def _combine_peer(kern, expand_x, expert_ids, expand_idx, ep_send_counts, expert
     px.signal(px.KIND_DATA_C)
     px.wait(px.KIND_DATA_C, 1)
     back = px.ret_local.view(expand_x.dtype).view(R * px.C, H)
-    out = kern.combine(back, expand_idx, expert_scales, shared, T, K, mask, special)
-    px.signal(px.KIND_ACK_C)
+    out = px.combine_and_acknowledge(kern, back, expand_idx, expert_scales, shared, T, K, mask, special)
     counters["wire_bytes_sent"] += T * K * H * 2
     px.leave()
     return out
@@ -452,8 +466,7 @@ def combine_from_producer(kern, produce_rows, rows, H, dtype, expert_ids, expand
     produce_rows(row_dst)
     px.signal_wait(px.KIND_DATA_C)
     back = px.ret_local.view(dtype).view(R * px.C, H)
-    out = kern.combine(back, expand_idx, expert_scales, shared, T, K, mask, special)
-    px.signal(px.KIND_ACK_C)
+    out = px.combine_and_acknowledge(kern, back, expand_idx, expert_scales, shared, T, K, mask, special)
     counters["wire_bytes_sent"] += T * K * H * 2
     px.leave()
     return out
