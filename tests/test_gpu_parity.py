@@ -921,7 +921,7 @@ def test_cta_pair_gemm_plain_outputs_are_bit_exact(dev, counts, Kd, N):
     pts = torch.rand(M, generator=g) * 1e-2
     bias = torch.randint(-50000, 50000, (E, N), generator=g, dtype=torch.int32)
     cnt = torch.tensor(counts, dtype=torch.int64)
-    hint = [max(counts)]                      # the tiling hint that selects the pair kernel (>= 768 rows per group)
+    hint = [max(counts)]                      # the tiling hint that selects the pair kernel (>= 1024 rows per group at this K)
     xd, wd, cd = x.to(dev), w.to(dev), cnt.to(dev)
     h32 = npu.npu_grouped_matmul([xd], [wd], group_list=cd, split_item=2, group_type=0, group_list_type=1, output_dtype=3,
                                  tuning_config=hint)[0]
@@ -1012,7 +1012,7 @@ def test_cta_pair_narrow_tail_tiles_plain_are_bit_exact(dev, Kd, N):
     bias = torch.randint(-50000, 50000, (E, N), generator=g, dtype=torch.int32)
     cnt = torch.tensor(counts, dtype=torch.int64)
     xd, wd, cd = x.to(dev), w.to(dev), cnt.to(dev)
-    hint = [1000]
+    hint = [2000]
     h32 = npu.npu_grouped_matmul([xd], [wd], group_list=cd, split_item=2, group_type=0, group_list_type=1, output_dtype=3,
                                  tuning_config=hint)[0]
     _gmm_ok(dev)
@@ -1046,7 +1046,7 @@ def test_cta_pair_narrow_tail_tiles_fused_are_bit_exact(dev, Kd, I, left):
     h32 = O.grouped_matmul_w8a8(x, w, None, None, cnt, 1, 3)
     if left:
         for _ in range(2):
-            hq, hs = npu.npu_grouped_matmul_swiglu_quant_v2(xd, [wd], [wsd], xsd, cd, group_list_type=1, tuning_config=[1000])
+            hq, hs = npu.npu_grouped_matmul_swiglu_quant_v2(xd, [wd], [wsd], xsd, cd, group_list_type=1, tuning_config=[2000])
         _gmm_ok(dev)
         q_ref, s_ref = O.dequant_swiglu_quant(h32, ws, xs, cnt, True, 1)
         _swiglu_quant_equal(hq[:covered], hs[:covered], q_ref[:covered], s_ref[:covered])
@@ -1061,7 +1061,7 @@ def test_cta_pair_narrow_tail_tiles_fused_are_bit_exact(dev, Kd, I, left):
         wsp = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
         P = lambda t: ctypes.c_void_p(t.data_ptr())
         outs = []
-        for hint in (1000, 100):
+        for hint in (2000, 100):
             yq = torch.zeros((M, I), dtype=torch.int8, device=dev)
             ys = torch.zeros((M,), dtype=torch.float32, device=dev)
             _lib.call("tab_grouped_matmul_swiglu_quant", P(xd), P(wp), P(wsd), P(xsd), P(cd), 1, M, Kd, I, E, 0, P(yq), P(ys), P(wsp),
@@ -1071,3 +1071,33 @@ def test_cta_pair_narrow_tail_tiles_fused_are_bit_exact(dev, Kd, I, left):
         q_ref, s_ref = O.dequant_swiglu_quant(h32, ws, xs, cnt, False, 1)
         _swiglu_quant_equal(outs[0][0][:covered], outs[0][1][:covered], q_ref[:covered], s_ref[:covered])
         assert torch.equal(outs[0][0][:covered], outs[1][0][:covered]) and torch.equal(outs[0][1][:covered], outs[1][1][:covered])
+
+
+def test_combine_that_acknowledges_from_its_last_cta(dev):
+    """tab_moe_combine_ack = the weighted sum of tab_moe_combine plus, once every CTA has read its rows, one release store of
+    the next sequence number into each peer's flag slot.  One GPU stands for three peers here (three local flag words):
+    same output, flags = counter + 1, the signal counter advanced, the arrival counter back at zero; twice in a row."""
+    import ctypes
+    from torchair_b200 import _lib
+    T, K, H, M = 96, 4, 512, 400
+    g = torch.Generator().manual_seed(3)
+    rows = torch.randn(M, H, generator=g).to(torch.bfloat16).to(dev)
+    idx = torch.randint(0, M, (T * K,), generator=g, dtype=torch.int32).to(dev)
+    wts = torch.rand(T, K, generator=g).to(dev)
+    want = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+    P = lambda t: ctypes.c_void_p(t.data_ptr())
+    st = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    _lib.call("tab_moe_combine", P(rows), 15, P(idx), P(wts), None, T, K, H, P(want), st)
+    flags = torch.zeros(3, dtype=torch.int64, device=dev)
+    table = torch.tensor([flags.data_ptr() + 8 * i for i in range(3)], dtype=torch.int64, device=dev)
+    counters_ = torch.tensor([41, 0], dtype=torch.int64, device=dev)       # [signal counter, arrival counter (low 32 bits)]
+    for step in (1, 2):
+        got = torch.zeros((T, H), dtype=torch.bfloat16, device=dev)
+        _lib.call("tab_moe_combine_ack", P(rows), 15, P(idx), P(wts), None, T, K, H, P(got), None, None, 0, 0, 0, 0, None, None, None,
+                  None, P(table), ctypes.c_void_p(counters_.data_ptr()), ctypes.c_void_p(counters_.data_ptr() + 8), 3, st)
+        torch.cuda.synchronize(dev)
+        assert torch.equal(got, want)
+        assert flags.tolist() == [41 + step] * 3 and counters_.tolist() == [41 + step, 0]
+    with pytest.raises(RuntimeError):       # no tokens: nothing would acknowledge
+        _lib.call("tab_moe_combine_ack", P(rows), 15, P(idx), P(wts), None, 0, K, H, P(got), None, None, 0, 0, 0, 0, None, None, None,
+                  None, P(table), ctypes.c_void_p(counters_.data_ptr()), ctypes.c_void_p(counters_.data_ptr() + 8), 3, st)

@@ -410,11 +410,15 @@ static bool use_prefill(double avg) {
   return avg > 64.0;
 }
 
-// The CTA-pair kernel computes whole 256-token tiles, so an expert's last tile costs a full tile whatever it holds:
-// it pays when experts hold many tiles (expected rows per group >= 768: at most one tile in four is a partial one).
-static bool use_pair(double avg) {
+// The CTA-pair kernel computes 256-token tiles: an expert's last tile of 65..255 rows costs a whole tile, and per tile the
+// pair's epilogue is as long as that of two one-CTA tiles while its main loop saves operand traffic in proportion to K.
+// Measured cross-over (rows per group, counts spread by a quarter around the mean): about 450 rows at K = 7168, 750 at
+// K = 4096, 1000 at K = 1536..2048.
+static bool use_pair(double avg, int64_t Kd) {
   if (gmm_env().orientation != 0) return gmm_env().orientation == 3;
-  return avg >= 768.0;
+  if (Kd >= 6144) return avg >= 448.0;
+  if (Kd >= 3072) return avg >= 768.0;
+  return avg >= 1024.0;
 }
 
 template <bool FUSED>
@@ -497,7 +501,7 @@ static int grouped_matmul_plain(const int8_t* x, const int8_t* packed_weight, co
   if (!y && !row_dst) return fail(TAB_ERR_BAD_ARG, "grouped_matmul: null output");
   const double avg = rows_per_group(M, E, expected_rows_per_group);
   const int nt = use_prefill(avg) ? 0 : pick_nt(avg);     // 0 selects the prefill orientation
-  const bool pair = nt == 0 && use_pair(avg);
+  const bool pair = nt == 0 && use_pair(avg, Kd);
   CUtensorMap tm_w, tm_x, tm_w64;
   rc = make_maps(x, packed_weight, M, Kd, N, E, nt == 0 ? kPfTokens : nt, &tm_w, &tm_x, pair ? &tm_w64 : nullptr);
   if (rc != TAB_OK) return rc;
@@ -566,7 +570,7 @@ extern "C" int tab_grouped_matmul_swiglu_quant(const int8_t* x, const int8_t* pa
   if (ce != cudaSuccess) return fail(TAB_ERR_CUDA, "grouped_matmul_swiglu_quant: memset: %s", cudaGetErrorString(ce));
   const double avg = rows_per_group(M, E, expected_rows_per_group);
   const int nt = use_prefill(avg) ? 0 : pick_nt(avg);     // 0 selects the prefill orientation
-  const bool pair = nt == 0 && use_pair(avg);
+  const bool pair = nt == 0 && use_pair(avg, Kd);
   CUtensorMap tm_w, tm_x, tm_w64;
   rc = make_maps(x, packed_weight, M, Kd, 2 * I, E, nt == 0 ? kPfTokens : nt, &tm_w, &tm_x, pair ? &tm_w64 : nullptr);
   if (rc != TAB_OK) return rc;
