@@ -1101,3 +1101,30 @@ def test_combine_that_acknowledges_from_its_last_cta(dev):
     with pytest.raises(RuntimeError):       # no tokens: nothing would acknowledge
         _lib.call("tab_moe_combine_ack", P(rows), 15, P(idx), P(wts), None, 0, K, H, P(got), None, None, 0, 0, 0, 0, None, None, None,
                   None, P(table), ctypes.c_void_p(counters_.data_ptr()), ctypes.c_void_p(counters_.data_ptr() + 8), 3, st)
+
+
+def test_combine_on_many_tokens_with_some_pairs_that_have_no_row(dev):
+    """From 2048 tokens on, tab_moe_combine runs a lean kernel for the tokens whose pairs all have rows and a second pass for
+    the others (a negative index contributes an exact zero).  Both kinds of token against the oracle, bit for bit, with
+    and without the shared-expert rows."""
+    import ctypes
+    from torchair_b200 import _lib
+    T, K, H, M = 2304, 4, 256, 5000
+    g = torch.Generator().manual_seed(17)
+    rows = torch.randn(M, H, generator=g).to(torch.bfloat16)
+    pos = torch.randint(0, M, (T, K), generator=g, dtype=torch.int32)
+    drop = torch.rand(T, K, generator=g) < 0.02
+    drop[5] = True                                    # one token without any row
+    pos[drop] = -1
+    wts = torch.rand(T, K, generator=g)
+    shared = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    ids = torch.zeros(T, K, dtype=torch.int32)
+    P = lambda t: None if t is None else ctypes.c_void_p(t.data_ptr())
+    st = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    rd, pd, wd, sd = rows.to(dev), pos.to(dev), wts.to(dev), shared.to(dev)
+    for sh_cpu, sh_dev in ((None, None), (shared, sd)):
+        out = torch.full((T, H), 9.0, dtype=torch.bfloat16, device=dev)
+        _lib.call("tab_moe_combine", P(rd), 15, P(pd), P(wd), P(sh_dev), T, K, H, P(out), st)
+        want = O.combine_rows(rows, pos, wts, ids, 1, shared=sh_cpu)
+        assert torch.equal(out.cpu(), want)
+    assert int((drop.any(dim=1)).sum()) > 20 and int((~drop.any(dim=1)).sum()) > 1000

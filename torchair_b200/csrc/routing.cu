@@ -356,7 +356,7 @@ __global__ void __launch_bounds__(THREADS) dispatch_pack_kernel(const T* __restr
   }
   for (int64_t t = blockIdx.x; t < tokens; t += gridDim.x) {
     const T* xr = x + t * cols;
-    if (!kSortInside || t != blockIdx.x) load_row(t);
+    if (kSortInside && t != blockIdx.x) load_row(t);
     __syncthreads();   // previous token's positions are no longer read
     if constexpr (kSortInside) {
       const int n = static_cast<int>(tokens) * K;
@@ -388,6 +388,7 @@ __global__ void __launch_bounds__(THREADS) dispatch_pack_kernel(const T* __restr
     }
     __syncthreads();   // positions (and keys) are published
     if constexpr (kQuant) {
+      if constexpr (!kSortInside) load_row(t);     // many tokens per CTA: the loads of a row directly before its arithmetic
       int8_t* out = static_cast<int8_t*>(a.send_rows);
       if constexpr (!kSmooth) {
         float amax = 0.f;
@@ -619,37 +620,111 @@ struct CombineExtra {
 
 // out[t] = sum_k w[t,k] * rows[idx[t*K+k]] (+ shared[t]); fp32, separate multiply and add, ascending k.  A negative
 // index (a pair that was dropped and is no special expert) contributes 0.
-template <typename T, bool kExtra>
+// The bandwidth-bound case on its own: many tokens, no mask, no special experts, nothing to acknowledge.  A token with a
+// pair that has no row (negative index) is left to combine_kernel, launched after this one for those tokens only.
+template <typename T>
+__global__ void __launch_bounds__(256) combine_plain_kernel(const T* __restrict__ rows, const int32_t* __restrict__ expand_idx,
+                                                            const float* __restrict__ weights, const T* __restrict__ shared,
+                                                            int64_t tokens, int K, int cols, T* __restrict__ out) {
+  extern __shared__ int s_meta[];  // [K] positions, [K] weights
+  int* s_pos = s_meta;
+  float* s_w = reinterpret_cast<float*>(s_meta + K);
+  const int nchunk = cols >> 3;
+  for (int64_t t = blockIdx.x; t < tokens; t += gridDim.x) {
+    __syncthreads();
+    int no_row = 0;
+    for (int k = threadIdx.x; k < K; k += 256) {
+      const int pos = expand_idx[t * K + k];
+      no_row |= pos < 0 ? 1 : 0;
+      s_pos[k] = pos;
+      s_w[k] = weights[t * K + k];
+    }
+    if (__syncthreads_or(no_row)) continue;
+    for (int ch = threadIdx.x; ch < nchunk; ch += 256) {
+      float acc[8];
+#pragma unroll 4
+      for (int k = 0; k < K; ++k) {
+        float v[8];
+        Elem<T>::load8(rows + static_cast<int64_t>(s_pos[k]) * cols + ch * 8, v);
+        const float w = s_w[k];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float term = __fmul_rn(w, v[i]);
+          acc[i] = k == 0 ? term : __fadd_rn(acc[i], term);
+        }
+      }
+      if (shared) {
+        float v[8];
+        Elem<T>::load8(shared + t * cols + ch * 8, v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], v[i]);
+      }
+      Elem<T>::store8(out + t * cols + ch * 8, acc);
+    }
+  }
+}
+
+template <typename T, bool kExtra, bool kSliced>
 __global__ void __launch_bounds__(256) combine_kernel(const T* __restrict__ rows, const int32_t* __restrict__ expand_idx,
                                                       const float* __restrict__ weights, const T* __restrict__ shared,
-                                                      int64_t tokens, int K, int cols, int slices, T* __restrict__ out,
-                                                      const CombineExtra ex) {
+                                                      int64_t tokens, int K, int cols, int slices, int only_no_row,
+                                                      T* __restrict__ out, const CombineExtra ex) {
   extern __shared__ int s_meta[];  // [K] positions, [K] weights, [K] special kinds
   int* s_pos = s_meta;
   float* s_w = reinterpret_cast<float*>(s_meta + K);
   int* s_kind = s_meta + 2 * K;    // -1: gathered row; else index among the special experts
   const int nchunk_all = cols >> 3;
-  const int per_slice = (nchunk_all + slices - 1) / slices;
+  const int per_slice = kSliced ? (nchunk_all + slices - 1) / slices : nchunk_all;
   const int specials = kExtra ? ex.zero_num + ex.copy_num + ex.const_num : 0;
-  // work item = (token, column slice): with few tokens a row is cut into slices so that the launch still fills the GPU
-  for (int64_t item = blockIdx.x; item < tokens * slices; item += gridDim.x) {
-    const int64_t t = item / slices;
-    const int ch0 = static_cast<int>(item - t * slices) * per_slice;
-    const int nchunk = min(ch0 + per_slice, nchunk_all);
+  // work item = (token, column slice): with few tokens (kSliced) a row is cut into slices so that the launch still fills
+  // the GPU; otherwise an item is a whole token and the column loop has fixed bounds
+  for (int64_t item = blockIdx.x; item < (kSliced ? tokens * slices : tokens); item += gridDim.x) {
+    const int64_t t = kSliced ? item / slices : item;
+    const int ch0 = kSliced ? static_cast<int>(item - t * slices) * per_slice : 0;
+    const int nchunk = kSliced ? min(ch0 + per_slice, nchunk_all) : nchunk_all;
     if (kExtra && ex.mask != nullptr && ex.mask[t] == 0) {     // uniform over the CTA
       for (int ch = ch0 + threadIdx.x; ch < nchunk; ch += 256) *reinterpret_cast<uint4*>(out + t * cols + ch * 8) = make_uint4(0, 0, 0, 0);
       continue;
     }
     __syncthreads();
+    int no_row = 0;
     for (int k = threadIdx.x; k < K; k += 256) {
-      s_pos[k] = expand_idx[t * K + k];
+      const int pos = expand_idx[t * K + k];
+      no_row |= pos < 0 ? 1 : 0;
+      s_pos[k] = pos;
       s_w[k] = weights[t * K + k];
       if constexpr (kExtra) {
         const int id = specials > 0 ? ex.expert_ids[t * K + k] : 0;
         s_kind[k] = (specials > 0 && id >= ex.num_experts && id < ex.num_experts + specials) ? id - ex.num_experts : -1;
       }
     }
-    __syncthreads();
+    no_row = __syncthreads_or(no_row);
+    if (only_no_row && !no_row) continue;          // second launch after combine_plain_kernel: those tokens are done
+    if (!kExtra && !no_row) {
+      // every pair of this token has a row (the common case): K plain gathers per chunk, nothing to select
+      for (int ch = ch0 + threadIdx.x; ch < nchunk; ch += 256) {
+        float acc[8];
+#pragma unroll 4
+        for (int k = 0; k < K; ++k) {
+          float v[8];
+          Elem<T>::load8(rows + static_cast<int64_t>(s_pos[k]) * cols + ch * 8, v);
+          const float w = s_w[k];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float term = __fmul_rn(w, v[i]);
+            acc[i] = k == 0 ? term : __fadd_rn(acc[i], term);
+          }
+        }
+        if (shared) {
+          float v[8];
+          Elem<T>::load8(shared + t * cols + ch * 8, v);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], v[i]);
+        }
+        Elem<T>::store8(out + t * cols + ch * 8, acc);
+      }
+      continue;
+    }
     for (int ch = ch0 + threadIdx.x; ch < nchunk; ch += 256) {
       float acc[8];
 #pragma unroll 4
@@ -657,12 +732,12 @@ __global__ void __launch_bounds__(256) combine_kernel(const T* __restrict__ rows
         float v[8];
         const int kind = kExtra ? s_kind[k] : -1;
         if (kind < 0) {
-          if (s_pos[k] >= 0) {
-            Elem<T>::load8(rows + static_cast<int64_t>(s_pos[k]) * cols + ch * 8, v);
-          } else {
+          // the load is unconditional (row 0 stands in for a pair that has no row) so that the K loads of a chunk are in
+          // flight together; a select then puts the exact zero of a dropped pair in place
+          const int pos = s_pos[k];
+          Elem<T>::load8(rows + static_cast<int64_t>(pos < 0 ? 0 : pos) * cols + ch * 8, v);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = 0.f;
-          }
+          for (int i = 0; i < 8; ++i) v[i] = pos < 0 ? 0.f : v[i];
         } else if (kind < ex.zero_num) {
 #pragma unroll
           for (int i = 0; i < 8; ++i) v[i] = 0.f;
@@ -910,18 +985,36 @@ static int combine_impl(const void* rows, int dtype, const int32_t* expand_idx, 
                            ori_x, const_expert_alpha_1, const_expert_alpha_2, const_expert_v,
                            reinterpret_cast<unsigned long long* const*>(ack_peer_flags), static_cast<unsigned long long*>(ack_sig_counter),
                            static_cast<unsigned int*>(done_counter), (int)ack_ranks};
-#define TAB_COMBINE(TYPE, EX)                                                                                                   \
-  combine_kernel<TYPE, EX><<<grid, 256, smem, st>>>(static_cast<const TYPE*>(rows), expand_idx, expert_scales,                  \
-                                                    static_cast<const TYPE*>(shared), T, (int)K, (int)H, slices, static_cast<TYPE*>(out), ex)
+  // many tokens and none of the optional inputs: the lean kernel, then the general one for the tokens it left (if any)
+  const bool two_step = !extra && ack_peer_flags == nullptr && slices == 1 && T >= 2048;
+  const int only_no_row = two_step ? 1 : 0;
+  int launches = 1;
+  if (two_step) {
+    if (dtype == TAB_BF16)
+      combine_plain_kernel<__nv_bfloat16><<<grid, 256, smem, st>>>(static_cast<const __nv_bfloat16*>(rows), expand_idx, expert_scales,
+                                                                  static_cast<const __nv_bfloat16*>(shared), T, (int)K, (int)H,
+                                                                  static_cast<__nv_bfloat16*>(out));
+    else if (dtype == TAB_F16)
+      combine_plain_kernel<__half><<<grid, 256, smem, st>>>(static_cast<const __half*>(rows), expand_idx, expert_scales,
+                                                           static_cast<const __half*>(shared), T, (int)K, (int)H, static_cast<__half*>(out));
+    launches = 2;
+  }
+#define TAB_COMBINE(TYPE, EX, SL)                                                                                               \
+  combine_kernel<TYPE, EX, SL><<<grid, 256, smem, st>>>(static_cast<const TYPE*>(rows), expand_idx, expert_scales,              \
+                                                        static_cast<const TYPE*>(shared), T, (int)K, (int)H, slices, only_no_row, \
+                                                        static_cast<TYPE*>(out), ex)
+#define TAB_COMBINE2(TYPE, EX)                                                                                                  \
+  do { if (slices > 1) TAB_COMBINE(TYPE, EX, true); else TAB_COMBINE(TYPE, EX, false); } while (0)
   if (dtype == TAB_BF16) {
-    if (extra) TAB_COMBINE(__nv_bfloat16, true); else TAB_COMBINE(__nv_bfloat16, false);
+    if (extra) TAB_COMBINE2(__nv_bfloat16, true); else TAB_COMBINE2(__nv_bfloat16, false);
   } else if (dtype == TAB_F16) {
-    if (extra) TAB_COMBINE(__half, true); else TAB_COMBINE(__half, false);
+    if (extra) TAB_COMBINE2(__half, true); else TAB_COMBINE2(__half, false);
   } else {
     return fail(TAB_ERR_UNSUPPORTED, "combine: dtype %d (want 5 or 15)", dtype);
   }
+#undef TAB_COMBINE2
 #undef TAB_COMBINE
-  return check_launch("combine");
+  return check_launch("combine", launches);
 }
 
 extern "C" int tab_moe_combine_ex(const void* rows, int dtype, const int32_t* expand_idx, const float* expert_scales,
