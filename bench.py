@@ -340,9 +340,14 @@ def gemm_pair(torch, timer, dev, spec, seed, reps, peak_tops, peak_gbs, row_kern
     ms_down = timer.launches(down, reps)
 
     def tensor_entry(ms, ops, nbytes):
+        # "frac" is of the tensor peak; which roof is the nearer one for this launch (its bytes at the measured copy bandwidth
+        # against its operations at the tensor peak) is said beside it, with the fraction of that roof
         tops = ops / (ms * 1e-3) / 1e12
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        t_hbm, t_tc = nbytes / (peak_gbs * 1e9), ops / (peak_tops * 1e12)
         return {"ms": ms, "int8_tops": tops, "frac": tops / peak_tops, "frac_of_nominal_4500": tops / 4500.0,
-                "GB/s": nbytes / (ms * 1e-3) / 1e9, "ops": ops, "bytes": nbytes}
+                "GB/s": gbs, "frac_of_hbm": gbs / peak_gbs, "nearer_roof": "hbm" if t_hbm >= t_tc else "tensor",
+                "frac_of_nearer_roof": max(t_hbm, t_tc) / (ms * 1e-3), "ops": ops, "bytes": nbytes}
     out = {"workload": desc, "rows": M, "experts_hit": hit, "bound": "tensor", "unit": "TOP/s", "peak": peak_tops,
            "gate_up_fused(gemm+swiglu+requant)": tensor_entry(ms_up, ops_up, bytes_up), "down": tensor_entry(ms_down, ops_down, bytes_down)}
     if row_kernels:
