@@ -463,7 +463,8 @@ def gpu_arm(args):
                 buf[off_w:off_w + nw].view(torch.float32).view(T, K))
     for dst, src in zip(views(in_h), (x_src, ids_src, wt_src)):
         dst.copy_(src)
-    NSETS = 3
+    NSETS = 3                # buffer sets of the end-to-end pipeline: previous step's result, this step, next step's inputs
+    LAG = 2                  # the host reads a result two steps after issuing it
     in_d = [in_h.to(dev) for _ in range(NSETS)]
     x_d, ids_d, wt_d = views(in_d[0])
     out_h = [torch.empty((T, H), dtype=torch.bfloat16).pin_memory() for _ in range(NSETS)]
@@ -550,42 +551,49 @@ def gpu_arm(args):
     ms_per_step = total_ms / args.steps
     value = T * world * args.steps / (total_ms * 1e-3)
 
-    # (2) end to end through the public ops with host buffers: one H2D copy of the step's inputs, the layer, one D2H copy of
-    # the result.  With a captured layer the three stages of consecutive steps overlap on three streams over three buffer
-    # sets; the host waits for the result of the step issued two steps earlier, so the device queue never runs dry.
+    # (2) end to end through the public ops with host buffers: every step copies its inputs from pinned host memory and its
+    # result back into pinned host memory.  With a captured layer the step's graph has three branches that run side by
+    # side: the layer on set b, the host-to-device copy of the NEXT step's inputs into set b + 1, and the device-to-host
+    # copy of the PREVIOUS step's result (set b - 1).  A step is then one graph launch; the host waits for the result of the
+    # step issued two steps earlier, so the device queue never runs dry, and no cross-stream event sits between two steps
+    # (with expert parallelism the ranks move in lock step, so a late start on one rank delays all of them).
     finish_e2e = None
     if use_graph:
-        copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
-        ev_in = [torch.cuda.Event() for _ in range(NSETS)]
-        ev_comp = [torch.cuda.Event() for _ in range(NSETS)]
-        ev_out = [torch.cuda.Event() for _ in range(NSETS)]
+        side_in, side_out = torch.cuda.Stream(), torch.cuda.Stream()
+        stage = [torch.empty((T, H), dtype=torch.bfloat16, device=dev) for _ in range(NSETS)]    # a step's result on the device
+        e2e_graphs = []
+        for b_ in range(NSETS):
+            nxt, prv = (b_ + 1) % NSETS, (b_ - 1) % NSETS
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                main = torch.cuda.current_stream()
+                side_in.wait_stream(main)
+                side_out.wait_stream(main)
+                with torch.cuda.stream(side_in):
+                    in_d[nxt].copy_(in_h, non_blocking=True)
+                with torch.cuda.stream(side_out):
+                    out_h[prv].copy_(stage[prv], non_blocking=True)
+                stage[b_].copy_(layer(*views(in_d[b_])))
+                main.wait_stream(side_in)
+                main.wait_stream(side_out)
+            e2e_graphs.append(gr)
+        ev_step = [torch.cuda.Event() for _ in range(NSETS)]
         state = {"s": 0}
+        in_d[0].copy_(in_h, non_blocking=True)          # the first step's inputs (every later copy-in rides in a step's graph)
 
         def step_e2e():
             s_ = state["s"]
             b = s_ % NSETS
-            main = torch.cuda.current_stream()
-            with torch.cuda.stream(copy_in):
-                copy_in.wait_event(ev_comp[b])          # this set's previous compute has consumed its inputs
-                in_d[b].copy_(in_h, non_blocking=True)
-                ev_in[b].record(copy_in)
-            main.wait_event(ev_in[b])
-            main.wait_event(ev_out[b])                  # this set's previous result has left the device
-            graphs[b].replay()
-            ev_comp[b].record(main)
-            with torch.cuda.stream(copy_out):
-                copy_out.wait_event(ev_comp[b])
-                out_h[b].copy_(outs[b], non_blocking=True)
-                ev_out[b].record(copy_out)
-            if s_ >= 2:
-                ev_out[(s_ - 2) % NSETS].synchronize()  # the caller reads the result of the step issued two steps ago
+            e2e_graphs[b].replay()
+            ev_step[b].record()
+            if s_ >= LAG:
+                ev_step[(s_ - LAG + 1) % NSETS].synchronize()   # that graph carried the copy-out of step s - LAG: the caller reads it
             state["s"] = s_ + 1
 
         def finish_e2e():
-            main = torch.cuda.current_stream()
-            for k in (1, 2):
-                if state["s"] - k >= 0:
-                    main.wait_event(ev_out[(state["s"] - k) % NSETS])
+            # the result of the block's last step leaves with the next step's graph; at the end of a block it is copied here
+            last = (state["s"] - 1) % NSETS
+            out_h[last].copy_(stage[last], non_blocking=True)
     else:
         def step_e2e():
             in_d[0].copy_(in_h, non_blocking=True)
@@ -695,8 +703,9 @@ def gpu_arm(args):
                 "stream_frac": weight_bytes / (ms_per_step * 1e-3) / 1e9 / peak_gbs,
                 "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                         "ms_per_step": e2e_ms / args.steps, "repeats": len(e2e_blocks),
-                        "pipelining": "copy-in, compute and copy-out of consecutive steps overlap (three buffer sets); the host "
-                                      "reads a result two steps after issuing it" if use_graph else "none"},
+                        "pipelining": ("a step is one CUDA-graph launch with three branches: the layer, the copy-in of the next step's "
+                                       "inputs and the copy-out of the previous step's result (three buffer sets); the host reads a "
+                                       "result two steps after issuing it") if use_graph else "none"},
                 "gpu_launches": launches_per_step * args.steps, "gpu_launches_per_step": launches_per_step,
                 "gpu_launches_counted": "kernels this library enqueued while one step was recorded (tab_launch_count)",
                 "checked": checked, "roofline": roofline, "cpu_baseline": cpu,

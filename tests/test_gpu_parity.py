@@ -1128,3 +1128,47 @@ def test_combine_on_many_tokens_with_some_pairs_that_have_no_row(dev):
         want = O.combine_rows(rows, pos, wts, ids, 1, shared=sh_cpu)
         assert torch.equal(out.cpu(), want)
     assert int((drop.any(dim=1)).sum()) > 20 and int((~drop.any(dim=1)).sum()) > 1000
+
+
+def test_full_size_skewed_prefill_share_on_cta_pairs(dev):
+    """One rank's share of the skewed expert-parallel prefill at full size (8192 tokens top-8 over 32 experts with Zipf(1.2)
+    routing, hidden 7168, intermediate 2048: 65536 rows, hundreds to thousands per expert) runs on CTA pairs.  The
+    least-loaded expert in full and the first and last rows of the most-loaded one (its narrow or partial last tile
+    included) against the oracle, bit for bit; dispatch permutation and counts; the combine over all rows."""
+    cfg = O.MoeConfig("cfg3_rank", 8192, 7168, 32, 8, 2048, zipf_s=1.2)
+    g = torch.Generator(device=dev).manual_seed(13)
+    w1 = torch.randint(-127, 128, (cfg.E, cfg.H, 2 * cfg.I), generator=g, dtype=torch.int8, device=dev)
+    w2 = torch.randint(-127, 128, (cfg.E, cfg.I, cfg.H), generator=g, dtype=torch.int8, device=dev)
+    s1 = torch.rand(cfg.E, 2 * cfg.I, generator=g, device=dev) * 9e-3 + 1e-3
+    s2 = torch.rand(cfg.E, cfg.H, generator=g, device=dev) * 9e-3 + 1e-3
+    x, ids, wt = O.make_tokens(cfg, 0)
+    xd, idd, wtd = x.to(dev), ids.to(dev), wt.to(dev)
+    ex, xs, expand_idx, nums, ep_recv, _, _ = npu.npu_moe_distribute_dispatch(xd, idd, "", 1, 0, cfg.E, quant_mode=2)
+    M = cfg.T * cfg.K
+    assert int(nums.sum()) == M and torch.equal(torch.sort(expand_idx).values.cpu(), torch.arange(M, dtype=torch.int32))
+    assert torch.equal(nums.cpu(), torch.bincount(ids.reshape(-1).long(), minlength=cfg.E))
+    hq, hs = npu.npu_grouped_matmul_swiglu_quant_v2(ex, [w1], [s1], xs, nums, group_list_type=1)     # 2048 rows per expert on average
+    y = npu.npu_grouped_matmul([hq], [w2], scale=[s2], per_token_scale=[hs], group_list=nums, split_item=2, group_type=0,
+                               group_list_type=1, output_dtype=15)[0]
+    _gmm_ok(dev)
+    counts = nums.cpu()
+    starts = torch.cumsum(counts, 0) - counts
+    small, big = int(torch.argmin(counts)), int(torch.argmax(counts))
+    assert int(counts[big]) > 4 * int(counts[small]) > 0            # the skew is there
+    picks = [(small, torch.arange(int(counts[small])))]
+    cb = int(counts[big])
+    picks.append((big, torch.cat([torch.arange(48), torch.arange(cb - 80, cb)])))
+    for e, rel in picks:
+        rows_ = (int(starts[e]) + rel).to(dev)
+        c = rel.numel()
+        we = O.MoeWeights(w1[e:e + 1].cpu(), s1[e:e + 1].cpu(), w2[e:e + 1].cpu(), s2[e:e + 1].cpu())
+        col = {}
+        yref = O.expert_ffn(ex[rows_].cpu(), xs[rows_].cpu(), torch.tensor([c]), we, col)
+        _swiglu_quant_equal(hq[rows_], hs[rows_], col["hq"], col["hs"])
+        assert torch.equal(y[rows_].cpu(), yref)
+    out = npu.npu_moe_distribute_combine(y, idd, expand_idx, ep_recv, wtd, "", 1, 0, cfg.E)
+    ref_out = O.weighted_gather_sum(y.cpu(), expand_idx.view(cfg.T, cfg.K).cpu(), wt)
+    assert torch.equal(out.cpu(), ref_out)
+    del w1, w2
+    torchair_b200.clear_weight_cache()
+    torch.cuda.empty_cache()
