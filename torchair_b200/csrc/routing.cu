@@ -664,11 +664,60 @@ __global__ void __launch_bounds__(256) combine_plain_kernel(const T* __restrict_
   }
 }
 
+// Second pass after combine_plain_kernel: the tokens it skipped (a pair without a row).  Every thread looks at one token
+// of a block of 256; the flagged ones, normally none, are then summed by the whole CTA with an exact zero in place of the
+// missing rows.  A few CTAs read T*K indices: the pass costs little more than its launch.
+template <typename T>
+__global__ void __launch_bounds__(256) combine_fixup_kernel(const T* __restrict__ rows, const int32_t* __restrict__ expand_idx,
+                                                            const float* __restrict__ weights, const T* __restrict__ shared,
+                                                            int64_t tokens, int K, int cols, T* __restrict__ out) {
+  __shared__ int s_list[256];
+  __shared__ int s_count;
+  const int nchunk = cols >> 3;
+  for (int64_t base = static_cast<int64_t>(blockIdx.x) * 256; base < tokens; base += static_cast<int64_t>(gridDim.x) * 256) {
+    __syncthreads();
+    if (threadIdx.x == 0) s_count = 0;
+    __syncthreads();
+    const int64_t mine = base + threadIdx.x;
+    if (mine < tokens) {
+      bool no_row = false;
+      for (int k = 0; k < K; ++k) no_row |= expand_idx[mine * K + k] < 0;
+      if (no_row) s_list[atomicAdd(&s_count, 1)] = threadIdx.x;
+    }
+    __syncthreads();
+    const int n = s_count;
+    for (int q = 0; q < n; ++q) {
+      const int64_t t = base + s_list[q];
+      for (int ch = threadIdx.x; ch < nchunk; ch += 256) {
+        float acc[8];
+        for (int k = 0; k < K; ++k) {
+          const int pos = expand_idx[t * K + k];
+          float v[8];
+          Elem<T>::load8(rows + static_cast<int64_t>(pos < 0 ? 0 : pos) * cols + ch * 8, v);
+          const float w = weights[t * K + k];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float term = __fmul_rn(w, pos < 0 ? 0.f : v[i]);
+            acc[i] = k == 0 ? term : __fadd_rn(acc[i], term);
+          }
+        }
+        if (shared) {
+          float v[8];
+          Elem<T>::load8(shared + t * cols + ch * 8, v);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], v[i]);
+        }
+        Elem<T>::store8(out + t * cols + ch * 8, acc);
+      }
+    }
+  }
+}
+
 template <typename T, bool kExtra, bool kSliced>
 __global__ void __launch_bounds__(256) combine_kernel(const T* __restrict__ rows, const int32_t* __restrict__ expand_idx,
                                                       const float* __restrict__ weights, const T* __restrict__ shared,
-                                                      int64_t tokens, int K, int cols, int slices, int only_no_row,
-                                                      T* __restrict__ out, const CombineExtra ex) {
+                                                      int64_t tokens, int K, int cols, int slices, T* __restrict__ out,
+                                                      const CombineExtra ex) {
   extern __shared__ int s_meta[];  // [K] positions, [K] weights, [K] special kinds
   int* s_pos = s_meta;
   float* s_w = reinterpret_cast<float*>(s_meta + K);
@@ -699,7 +748,6 @@ __global__ void __launch_bounds__(256) combine_kernel(const T* __restrict__ rows
       }
     }
     no_row = __syncthreads_or(no_row);
-    if (only_no_row && !no_row) continue;          // second launch after combine_plain_kernel: those tokens are done
     if (!kExtra && !no_row) {
       // every pair of this token has a row (the common case): K plain gathers per chunk, nothing to select
       for (int ch = ch0 + threadIdx.x; ch < nchunk; ch += 256) {
@@ -985,23 +1033,28 @@ static int combine_impl(const void* rows, int dtype, const int32_t* expand_idx, 
                            ori_x, const_expert_alpha_1, const_expert_alpha_2, const_expert_v,
                            reinterpret_cast<unsigned long long* const*>(ack_peer_flags), static_cast<unsigned long long*>(ack_sig_counter),
                            static_cast<unsigned int*>(done_counter), (int)ack_ranks};
-  // many tokens and none of the optional inputs: the lean kernel, then the general one for the tokens it left (if any)
-  const bool two_step = !extra && ack_peer_flags == nullptr && slices == 1 && T >= 2048;
-  const int only_no_row = two_step ? 1 : 0;
-  int launches = 1;
-  if (two_step) {
-    if (dtype == TAB_BF16)
-      combine_plain_kernel<__nv_bfloat16><<<grid, 256, smem, st>>>(static_cast<const __nv_bfloat16*>(rows), expand_idx, expert_scales,
-                                                                  static_cast<const __nv_bfloat16*>(shared), T, (int)K, (int)H,
-                                                                  static_cast<__nv_bfloat16*>(out));
-    else if (dtype == TAB_F16)
-      combine_plain_kernel<__half><<<grid, 256, smem, st>>>(static_cast<const __half*>(rows), expand_idx, expert_scales,
-                                                           static_cast<const __half*>(shared), T, (int)K, (int)H, static_cast<__half*>(out));
-    launches = 2;
+  // many tokens and none of the optional inputs: the lean kernel, then a small pass for the tokens it left (if any)
+  if (!extra && ack_peer_flags == nullptr && slices == 1 && T >= 2048) {
+    const int fix_grid = static_cast<int>((T + 255) / 256 < 2 * kNumSMs ? (T + 255) / 256 : 2 * kNumSMs);
+    const size_t smem2 = static_cast<size_t>(K) * 8;
+    if (dtype == TAB_BF16) {
+      const __nv_bfloat16* r = static_cast<const __nv_bfloat16*>(rows);
+      const __nv_bfloat16* sh = static_cast<const __nv_bfloat16*>(shared);
+      combine_plain_kernel<__nv_bfloat16><<<grid, 256, smem2, st>>>(r, expand_idx, expert_scales, sh, T, (int)K, (int)H, static_cast<__nv_bfloat16*>(out));
+      combine_fixup_kernel<__nv_bfloat16><<<fix_grid, 256, 0, st>>>(r, expand_idx, expert_scales, sh, T, (int)K, (int)H, static_cast<__nv_bfloat16*>(out));
+    } else if (dtype == TAB_F16) {
+      const __half* r = static_cast<const __half*>(rows);
+      const __half* sh = static_cast<const __half*>(shared);
+      combine_plain_kernel<__half><<<grid, 256, smem2, st>>>(r, expand_idx, expert_scales, sh, T, (int)K, (int)H, static_cast<__half*>(out));
+      combine_fixup_kernel<__half><<<fix_grid, 256, 0, st>>>(r, expand_idx, expert_scales, sh, T, (int)K, (int)H, static_cast<__half*>(out));
+    } else {
+      return fail(TAB_ERR_UNSUPPORTED, "combine: dtype %d (want 5 or 15)", dtype);
+    }
+    return check_launch("combine", 2);
   }
 #define TAB_COMBINE(TYPE, EX, SL)                                                                                               \
   combine_kernel<TYPE, EX, SL><<<grid, 256, smem, st>>>(static_cast<const TYPE*>(rows), expand_idx, expert_scales,              \
-                                                        static_cast<const TYPE*>(shared), T, (int)K, (int)H, slices, only_no_row, \
+                                                        static_cast<const TYPE*>(shared), T, (int)K, (int)H, slices,           \
                                                         static_cast<TYPE*>(out), ex)
 #define TAB_COMBINE2(TYPE, EX)                                                                                                  \
   do { if (slices > 1) TAB_COMBINE(TYPE, EX, true); else TAB_COMBINE(TYPE, EX, false); } while (0)
@@ -1014,7 +1067,7 @@ static int combine_impl(const void* rows, int dtype, const int32_t* expand_idx, 
   }
 #undef TAB_COMBINE2
 #undef TAB_COMBINE
-  return check_launch("combine", launches);
+  return check_launch("combine");
 }
 
 extern "C" int tab_moe_combine_ex(const void* rows, int dtype, const int32_t* expand_idx, const float* expert_scales,
