@@ -469,8 +469,9 @@ def gpu_arm(args):
     x_d, ids_d, wt_d = views(in_d[0])
     out_h = [torch.empty((T, H), dtype=torch.bfloat16).pin_memory() for _ in range(NSETS)]
 
-    def layer(x, ids, wt, fused=True):
-        return moe_layer(x, ids, wt, w1, s1, w2, s2, group_ep="ep", ep_world_size=world, ep_rank_id=rank, moe_expert_num=E, fused=fused)
+    def layer(x, ids, wt, fused=True, after_dispatch=None):
+        return moe_layer(x, ids, wt, w1, s1, w2, s2, group_ep="ep", ep_world_size=world, ep_rank_id=rank, moe_expert_num=E, fused=fused,
+                         after_dispatch=after_dispatch)
 
     def sync_all():
         if world > 1:
@@ -552,9 +553,9 @@ def gpu_arm(args):
     value = T * world * args.steps / (total_ms * 1e-3)
 
     # (2) end to end through the public ops with host buffers: every step copies its inputs from pinned host memory and its
-    # result back into pinned host memory.  With a captured layer the step's graph has three branches that run side by
-    # side: the layer on set b, the host-to-device copy of the NEXT step's inputs into set b + 1, and the device-to-host
-    # copy of the PREVIOUS step's result (set b - 1).  A step is then one graph launch; the host waits for the result of the
+    # result back into pinned host memory.  With a captured layer the step's graph has three branches: the layer on set b
+    # and, forked off after its dispatch, the host-to-device copy of the NEXT step's inputs into set b + 1 and the
+    # device-to-host copy of the PREVIOUS step's result (set b - 1).  A step is then one graph launch; the host waits for the result of the
     # step issued two steps earlier, so the device queue never runs dry, and no cross-stream event sits between two steps
     # (with expert parallelism the ranks move in lock step, so a late start on one rank delays all of them).
     finish_e2e = None
@@ -567,13 +568,18 @@ def gpu_arm(args):
             gr = torch.cuda.CUDAGraph()
             with torch.cuda.graph(gr):
                 main = torch.cuda.current_stream()
-                side_in.wait_stream(main)
-                side_out.wait_stream(main)
-                with torch.cuda.stream(side_in):
-                    in_d[nxt].copy_(in_h, non_blocking=True)
-                with torch.cuda.stream(side_out):
-                    out_h[prv].copy_(stage[prv], non_blocking=True)
-                stage[b_].copy_(layer(*views(in_d[b_])))
+
+                def fork_copies():
+                    # Called by the layer once its dispatch is enqueued: the transfers then run beside the expert GEMMs.
+                    # Forked at the start of the step they ran beside the latency-bound exchange and cost the step 31 us
+                    # on 2 GPUs; here 12 us.
+                    side_in.wait_stream(main)
+                    side_out.wait_stream(main)
+                    with torch.cuda.stream(side_in):
+                        in_d[nxt].copy_(in_h, non_blocking=True)
+                    with torch.cuda.stream(side_out):
+                        out_h[prv].copy_(stage[prv], non_blocking=True)
+                stage[b_].copy_(layer(*views(in_d[b_]), after_dispatch=fork_copies))
                 main.wait_stream(side_in)
                 main.wait_stream(side_out)
             e2e_graphs.append(gr)
@@ -703,9 +709,9 @@ def gpu_arm(args):
                 "stream_frac": weight_bytes / (ms_per_step * 1e-3) / 1e9 / peak_gbs,
                 "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                         "ms_per_step": e2e_ms / args.steps, "repeats": len(e2e_blocks),
-                        "pipelining": ("a step is one CUDA-graph launch with three branches: the layer, the copy-in of the next step's "
-                                       "inputs and the copy-out of the previous step's result (three buffer sets); the host reads a "
-                                       "result two steps after issuing it") if use_graph else "none"},
+                        "pipelining": ("a step is one CUDA-graph launch with three branches: the layer and, beside its expert GEMMs, the "
+                                       "copy-in of the next step's inputs and the copy-out of the previous step's result (three buffer "
+                                       "sets); the host reads a result two steps after issuing it") if use_graph else "none"},
                 "gpu_launches": launches_per_step * args.steps, "gpu_launches_per_step": launches_per_step,
                 "gpu_launches_counted": "kernels this library enqueued while one step was recorded (tab_launch_count)",
                 "checked": checked, "roofline": roofline, "cpu_baseline": cpu,

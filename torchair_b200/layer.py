@@ -13,13 +13,17 @@ from . import ops  # noqa: F401  (registers torch.ops.npu.*)
 
 
 def moe_layer(x, expert_ids, expert_scales, w1, s1, w2, s2, *, group_ep: str = "", ep_world_size: int = 1,
-              ep_rank_id: int = 0, moe_expert_num: int = None, fused: bool = True):
+              ep_rank_id: int = 0, moe_expert_num: int = None, fused: bool = True, after_dispatch=None):
     """x [T, H] bf16; expert_ids int32 [T, K]; expert_scales fp32 [T, K]; w1 int8 [E_l, H, 2I]; s1 fp32 [E_l, 2I];
     w2 int8 [E_l, I, H]; s2 fp32 [E_l, H] (this rank's experts).  Returns [T, H] bf16.
 
     fused=True issues gate_up + SwiGLU + requant as npu_grouped_matmul_swiglu_quant_v2 and, with more than one rank, the
     down projection together with the combine; fused=False issues the int32 grouped matmul, npu_dequant_swiglu_quant,
     the down grouped matmul and the combine separately (what the FX fusion passes rewrite).
+
+    after_dispatch: optional callable without arguments, called once the dispatch has been enqueued.  A caller that has
+    work of its own to run beside the layer (transfers for the next step on other streams, say) forks it there: next to
+    the expert GEMMs it disturbs the step less than next to the latency-bound exchange at the step's start.
     """
     npu = torch.ops.npu
     R = ep_world_size
@@ -29,6 +33,8 @@ def moe_layer(x, expert_ids, expert_scales, w1, s1, w2, s2, *, group_ep: str = "
     tune = [max(1, -(-x.shape[0] * expert_ids.shape[1] * R // E))]
     ex, xs, expand_idx, nums, ep_recv, _tp, _es = npu.npu_moe_distribute_dispatch(
         x, expert_ids, group_ep, R, ep_rank_id, E, quant_mode=2, expert_token_nums_type=1)
+    if after_dispatch is not None:
+        after_dispatch()
     if fused:
         hq, hs = npu.npu_grouped_matmul_swiglu_quant_v2(ex, [w1], [s1], xs, nums, group_list_type=1, tuning_config=tune)
     else:
