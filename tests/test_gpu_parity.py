@@ -863,10 +863,11 @@ def test_out_of_range_indices_are_reported_not_silently_clamped(dev):
 
 def test_scatter_gemm_skips_rows_without_a_destination(dev):
     """Row table of the scatter epilogue with null entries (rows the exchange plan does not cover): those rows are
-    not stored, every other row lands at its address, nothing faults.  Both GEMM orientations."""
+    not stored, every other row lands at its address, nothing faults.  Both GEMM orientations and the CTA-pair kernel
+    (its wide and narrow tiles)."""
     import ctypes
     from torchair_b200 import _lib
-    for M, Kd, N, E in ((96, 256, 512, 8), (1200, 256, 264, 3)):
+    for M, Kd, N, E, hint in ((96, 256, 512, 8, 0), (1200, 256, 264, 3, 0), (2600, 256, 264, 2, 2000)):
         g = torch.Generator().manual_seed(M)
         x = torch.randint(-127, 128, (M, Kd), generator=g, dtype=torch.int8)
         w = torch.randint(-127, 128, (E, Kd, N), generator=g, dtype=torch.int8)
@@ -884,7 +885,7 @@ def test_scatter_gemm_skips_rows_without_a_destination(dev):
         xd, sd, pd, cd, dd = x.to(dev), sc.to(dev), pts.to(dev), cnt.to(dev), dst.to(dev)
         wp = ops.packed_weight(w.to(dev))
         P = lambda t: ctypes.c_void_p(t.data_ptr())
-        _lib.call("tab_grouped_matmul_w8a8_scatter", P(xd), P(wp), P(sd), P(pd), P(cd), 1, M, Kd, N, E, 15, P(dd), 0,
+        _lib.call("tab_grouped_matmul_w8a8_scatter", P(xd), P(wp), P(sd), P(pd), P(cd), 1, M, Kd, N, E, 15, P(dd), hint,
                   ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
         _gmm_ok(dev)
         got = out.cpu()
