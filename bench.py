@@ -90,6 +90,22 @@ def workload(n_gpus, name="auto"):
             128, 7168, 256, 8, 2048, 0.0)
 
 
+def synthetic_tokens(torch, T, H, E, K, zipf, seed, rank=0):
+    """Seeded synthetic inputs of the benchmark's shapes and distributions: tokens bf16 ~ N(0, 1); router logits fp32 ~ N(0, 1),
+    plus a Zipf(zipf) bias over a permutation of the experts when zipf > 0; the K most probable experts of a token (ties to
+    the lower id) and their probabilities renormalised to sum 1.  Returns (x [T, H], expert ids int32 [T, K], weights fp32)."""
+    g = torch.Generator().manual_seed(seed * 1000 + rank)
+    x = torch.randn(T, H, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    logits = torch.randn(T, E, generator=g, dtype=torch.float32)
+    if zipf > 0:
+        perm = torch.randperm(E, generator=torch.Generator().manual_seed(seed))
+        p = (torch.arange(E, dtype=torch.float64) + 1.0) ** (-zipf)
+        logits = logits + torch.log(p / p.sum())[perm].float()
+    order = torch.sort(torch.softmax(logits, dim=-1), dim=-1, descending=True, stable=True)
+    w = order.values[:, :K]
+    return x, order.indices[:, :K].to(torch.int32).contiguous(), (w / w.sum(dim=-1, keepdim=True)).contiguous()
+
+
 def config_dict(name, T, H, E, K, I, world):
     return {"workload": name, "tokens_per_rank": T, "hidden": H, "experts": E, "experts_per_rank": E // world, "top_k": K,
             "intermediate": I, "parallelism": f"ep{world}"}
@@ -317,16 +333,14 @@ def gemm_pair(torch, timer, dev, spec, seed, reps, peak_tops, peak_gbs, row_kern
     """Both grouped GEMMs of the layer (gate_up with its fused epilogue, down) on one single-GPU shape, each timed inside
     a CUDA graph; optionally the row kernels of the path on the same rows."""
     import torchair_b200
-    from oracle import moe_oracle as O
     npu = torch.ops.npu
     desc, T, H, E, K, I, zipf = spec
-    cfg = O.MoeConfig("study", T, H, E, K, I, zipf_s=zipf)
     g = torch.Generator(device=dev).manual_seed(seed * 100003 + 17)
     w1 = torch.randint(-127, 128, (E, H, 2 * I), generator=g, dtype=torch.int8, device=dev)
     w2 = torch.randint(-127, 128, (E, I, H), generator=g, dtype=torch.int8, device=dev)
     s1 = torch.rand(E, 2 * I, generator=g, device=dev) * 9e-3 + 1e-3
     s2 = torch.rand(E, H, generator=g, device=dev) * 9e-3 + 1e-3
-    x, ids, wt = (t.to(dev) for t in O.make_tokens(cfg, seed))
+    x, ids, wt = (t.to(dev) for t in synthetic_tokens(torch, T, H, E, K, zipf, seed))
     ex, xs, expand_idx, nums, ep_recv, _, _ = npu.npu_moe_distribute_dispatch(x, ids, "", 1, 0, E, quant_mode=2)
     M = ex.shape[0]
     hq, hs = npu.npu_grouped_matmul_swiglu_quant_v2(ex, [w1], [s1], xs, nums, group_list_type=1)
@@ -424,7 +438,6 @@ def gpu_arm(args):
     import torchair_b200
     from torchair_b200 import _lib, ep
     from torchair_b200.layer import moe_layer
-    from oracle import moe_oracle as O
 
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py needs a CUDA device: the CUDA path has no CPU fallback (use --impl reference for the CPU arm)")
@@ -441,7 +454,6 @@ def gpu_arm(args):
         ep.register_ep_group("ep", dist.group.WORLD, transport=args.ep_transport)
     name, T, H, E, K, I, zipf = workload(world, args.workload)
     E_l = E // world
-    cfg = O.MoeConfig("bench", T, H, E, K, I, zipf_s=zipf)
 
     # weights of this rank's experts, generated on the device; tokens generated on the host (seeded)
     g = torch.Generator(device=dev).manual_seed(args.seed * 100003 + rank)
@@ -449,7 +461,7 @@ def gpu_arm(args):
     w2 = torch.randint(-127, 128, (E_l, I, H), generator=g, dtype=torch.int8, device=dev)
     s1 = torch.rand(E_l, 2 * I, generator=g, device=dev) * 9e-3 + 1e-3
     s2 = torch.rand(E_l, H, generator=g, device=dev) * 9e-3 + 1e-3
-    x_src, ids_src, wt_src = O.make_tokens(cfg, args.seed, rank)
+    x_src, ids_src, wt_src = synthetic_tokens(torch, T, H, E, K, zipf, args.seed, rank)
 
     # the step's inputs live in ONE pinned host buffer and one device buffer per set, so that a step's host-to-device
     # transfer is a single copy: [x bf16 | expert ids int32 | routing weights fp32], each part 256-byte aligned
